@@ -1,0 +1,531 @@
+// Persistent warp-specialised BF16 GEMM for sm_100a.
+//
+//   warp 0      : TMA producer (one lane) - streams 128x64 A tiles and 256x64 B tiles into a
+//                 4-stage shared-memory ring (128-byte swizzle), one mbarrier per stage.
+//   warp 1      : TMEM owner + MMA issuer (one lane) - tcgen05.mma 128x256x16, FP32 accumulators
+//                 in TMEM, two accumulator buffers (2 x 256 columns) so that the epilogue of
+//                 tile i overlaps the main loop of tile i+1.
+//   warps 2..5  : epilogue - tcgen05.ld of the warp's 32-lane quarter, fused epilogue math,
+//                 vectorised global stores.
+//
+// Operand layouts: each operand is either K-major (contraction contiguous, the nn.Linear
+// layout) or MN-major (output dimension contiguous); MN-major lets dX = dY*W and
+// dW = dY^T*X read the tensors exactly as the forward pass left them, with no transposes.
+// One CTA per SM; tiles are visited in a grouped order so that concurrently running CTAs
+// share A row-panels and B column-panels in L2.
+//
+// Role of this file in the model: every projection of a WarpState core (in_proj, out_proj,
+// up_gate, down; reference call sites warpstate/model.py:109,177,59,60) and their dX / dW
+// products, plus the epilogues the reference runs as separate kernels (SwiGLU forward
+// ops/matmul_epilogue.py:30-83 and backward ops/activation_execution.py:36-55, residual adds,
+// the BF16->FP32 gradient accumulation of autograd's AccumulateGrad).
+#include "ws_ptx.cuh"
+#include "ws_api.h"
+
+#include <atomic>
+#include <mutex>
+#include <unordered_map>
+#include <cstdio>
+#include <cstring>
+
+namespace ws {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
+constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int GEMM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int GROUP_M = 8;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+
+struct GemmParams {
+  int m, n, k;
+  int epi_n;  // width of one logical N tile in output columns (256, or 128 for SwiGLU)
+  int h;      // SwiGLU half width
+  void* out;
+  int ldo;
+  void* out2;
+  int ldo2;
+  const void* aux;
+  int ldaux;
+  const float* row_scale;
+  float alpha, beta;
+  int* error_flag;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& mb, int& nb) {
+  const int group_size = GROUP_M * num_n;
+  const int group = tile / group_size;
+  const int first_m = group * GROUP_M;
+  const int gsz = min(num_m - first_m, GROUP_M);
+  const int r = tile - group * group_size;
+  mb = first_m + (r % gsz);
+  nb = r / gsz;
+}
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + __expf(-x)); }
+
+template <bool A_MN, bool B_MN, int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+            const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + STAGES;
+  uint64_t* tfull = bars + 2 * STAGES;
+  uint64_t* tempty = bars + 2 * STAGES + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tfull[b], 1);
+      mbar_init(&tempty[b], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  constexpr bool kSwiglu = (EPI == WS_EPI_SWIGLU);
+  const int n_tile = kSwiglu ? 128 : BN;  // logical output columns per tile
+  const int num_m = (p.m + BM - 1) / BM;
+  const int num_n = (p.n + n_tile - 1) / n_tile;
+  const int tiles = num_m * num_n;
+  const int num_k = (p.k + BK - 1) / BK;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+        int mb, nb;
+        tile_coords(tile, num_m, num_n, mb, nb);
+        for (int kb = 0; kb < num_k; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&full[s], STAGE_BYTES);
+          uint8_t* a_dst = sA + s * A_STAGE_BYTES;
+          uint8_t* b_dst = sB + s * B_STAGE_BYTES;
+          if (!A_MN) {
+            tma_load_2d(a_dst, &tma_a, &full[s], kb * BK, mb * BM);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BM / 64; ++i)
+              tma_load_2d(a_dst + i * (BK * 128), &tma_a, &full[s], mb * BM + i * 64, kb * BK);
+          }
+          if (!B_MN) {
+            const int r0 = kSwiglu ? nb * 128 : nb * BN;
+            const int r1 = kSwiglu ? p.h + nb * 128 : nb * BN + 128;
+            tma_load_2d(b_dst, &tma_b, &full[s], kb * BK, r0);
+            tma_load_2d(b_dst + 128 * 128, &tma_b, &full[s], kb * BK, r1);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BN / 64; ++i)
+              tma_load_2d(b_dst + i * (BK * 128), &tma_b, &full[s], nb * BN + i * 64, kb * BK);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      int it = 0;
+      int tcount = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++tcount) {
+        const int buf = tcount & 1;
+        const uint32_t tph = (tcount >> 1) & 1;
+        if (!mbar_wait(&tempty[buf], tph ^ 1, abort_flag)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < num_k; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&full[s], ph, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_base = smem_u32(sA + s * A_STAGE_BYTES);
+          const uint32_t b_base = smem_u32(sB + s * B_STAGE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // K-major: 8-row groups are 1024 B apart (SBO); a K step of 16 elements is 32 B
+            // inside the 128-byte swizzle row.  MN-major: 64-element column groups are
+            // BK*128 B apart (LBO), 8-row K groups 1024 B apart (SBO); a K step is 16 rows.
+            const uint64_t da = A_MN ? make_smem_desc_sw128(a_base + k * UMMA_K * 128, BK * 128, 1024)
+                                     : make_smem_desc_sw128(a_base + k * UMMA_K * 2, 0, 1024);
+            const uint64_t db = B_MN ? make_smem_desc_sw128(b_base + k * UMMA_K * 128, BK * 128, 1024)
+                                     : make_smem_desc_sw128(b_base + k * UMMA_K * 2, 0, 1024);
+            umma_bf16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);
+        }
+        if (ok) umma_commit(&tfull[buf]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    const int quarter = warp & 3;
+    int tcount = 0;
+    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++tcount) {
+      int mb, nb;
+      tile_coords(tile, num_m, num_n, mb, nb);
+      const int buf = tcount & 1;
+      const uint32_t tph = (tcount >> 1) & 1;
+      if (!mbar_wait(&tfull[buf], tph, abort_flag)) break;
+      tc_fence_after_sync();
+      const int row = mb * BM + quarter * 32 + lane;
+      const bool row_ok = row < p.m;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+      const float rs = (p.row_scale != nullptr && row_ok) ? p.row_scale[row] : 1.0f;
+
+      if constexpr (EPI == WS_EPI_BF16) {
+        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(row) * p.ldo;
+        const int n0 = nb * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          if (n0 + c >= p.n) break;
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + c, r);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (n0 + c + j < p.n) {
+                uint4 v;
+                v.x = pack_bf16x2(__uint_as_float(r[j + 0]) * rs, __uint_as_float(r[j + 1]) * rs);
+                v.y = pack_bf16x2(__uint_as_float(r[j + 2]) * rs, __uint_as_float(r[j + 3]) * rs);
+                v.z = pack_bf16x2(__uint_as_float(r[j + 4]) * rs, __uint_as_float(r[j + 5]) * rs);
+                v.w = pack_bf16x2(__uint_as_float(r[j + 6]) * rs, __uint_as_float(r[j + 7]) * rs);
+                *reinterpret_cast<uint4*>(out + n0 + c + j) = v;
+              }
+            }
+          }
+        }
+      } else if constexpr (EPI == WS_EPI_RESID_F32 || EPI == WS_EPI_ACC_F32 || EPI == WS_EPI_F32) {
+        float* out = reinterpret_cast<float*>(p.out) + static_cast<size_t>(row) * p.ldo;
+        const float* res = reinterpret_cast<const float*>(p.aux) + static_cast<size_t>(row) * p.ldaux;
+        const int n0 = nb * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          if (n0 + c >= p.n) break;
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + c, r);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              if (n0 + c + j < p.n) {
+                float4 v;
+                v.x = __uint_as_float(r[j + 0]);
+                v.y = __uint_as_float(r[j + 1]);
+                v.z = __uint_as_float(r[j + 2]);
+                v.w = __uint_as_float(r[j + 3]);
+                if constexpr (EPI == WS_EPI_RESID_F32) {
+                  const float4 q = *reinterpret_cast<const float4*>(res + n0 + c + j);
+                  v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
+                } else if constexpr (EPI == WS_EPI_ACC_F32) {
+                  v.x *= p.alpha; v.y *= p.alpha; v.z *= p.alpha; v.w *= p.alpha;
+                  if (p.beta != 0.0f) {
+                    const float4 q = *reinterpret_cast<const float4*>(out + n0 + c + j);
+                    v.x += p.beta * q.x; v.y += p.beta * q.y; v.z += p.beta * q.z; v.w += p.beta * q.w;
+                  }
+                }
+                *reinterpret_cast<float4*>(out + n0 + c + j) = v;
+              }
+            }
+          }
+        }
+      } else if constexpr (EPI == WS_EPI_RESID_BF16) {
+        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(row) * p.ldo;
+        const __nv_bfloat16* res =
+            reinterpret_cast<const __nv_bfloat16*>(p.aux) + static_cast<size_t>(row) * p.ldaux;
+        const int n0 = nb * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          if (n0 + c >= p.n) break;
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + c, r);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (n0 + c + j < p.n) {
+                const uint4 q = *reinterpret_cast<const uint4*>(res + n0 + c + j);
+                const __nv_bfloat162* qb = reinterpret_cast<const __nv_bfloat162*>(&q);
+                uint4 v;
+                uint32_t* vw = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                  const float2 f = __bfloat1622float2(qb[t]);
+                  vw[t] = pack_bf16x2(f.x + bf16_round(__uint_as_float(r[j + 2 * t])),
+                                      f.y + bf16_round(__uint_as_float(r[j + 2 * t + 1])));
+                }
+                *reinterpret_cast<uint4*>(out + n0 + c + j) = v;
+              }
+            }
+          }
+        }
+      } else if constexpr (EPI == WS_EPI_SWIGLU) {
+        // Accumulator columns 0..127 are `up`, 128..255 are `gate` of the same 128 features.
+        // Both halves are rounded to BF16 first (what a BF16 GEMM would have returned); the
+        // activation is computed in FP32 from the rounded values and rounded once.
+        __nv_bfloat16* packed = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(row) * p.ldo;
+        __nv_bfloat16* act = reinterpret_cast<__nv_bfloat16*>(p.out2) + static_cast<size_t>(row) * p.ldo2;
+        const int n0 = nb * 128;
+#pragma unroll 1
+        for (int c = 0; c < 128; c += 16) {
+          if (n0 + c >= p.h) break;
+          uint32_t ru[16], rg[16];
+          tmem_ld_32x32b_x16(taddr + c, ru);
+          tmem_ld_32x32b_x16(taddr + 128 + c, rg);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int j = 0; j < 16; j += 8) {
+              if (n0 + c + j < p.h) {
+                uint4 vu, vg, va;
+                uint32_t* wu = reinterpret_cast<uint32_t*>(&vu);
+                uint32_t* wg = reinterpret_cast<uint32_t*>(&vg);
+                uint32_t* wa = reinterpret_cast<uint32_t*>(&va);
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                  const float u0 = bf16_round(__uint_as_float(ru[j + 2 * t]) * rs);
+                  const float u1 = bf16_round(__uint_as_float(ru[j + 2 * t + 1]) * rs);
+                  const float g0 = bf16_round(__uint_as_float(rg[j + 2 * t]) * rs);
+                  const float g1 = bf16_round(__uint_as_float(rg[j + 2 * t + 1]) * rs);
+                  wu[t] = pack_bf16x2(u0, u1);
+                  wg[t] = pack_bf16x2(g0, g1);
+                  wa[t] = pack_bf16x2(g0 * sigmoidf_(g0) * u0, g1 * sigmoidf_(g1) * u1);
+                }
+                if (p.out != nullptr) {
+                  *reinterpret_cast<uint4*>(packed + n0 + c + j) = vu;
+                  *reinterpret_cast<uint4*>(packed + p.h + n0 + c + j) = vg;
+                }
+                *reinterpret_cast<uint4*>(act + n0 + c + j) = va;
+              }
+            }
+          }
+        }
+      } else if constexpr (EPI == WS_EPI_SWIGLU_BWD) {
+        // acc = dAct; aux = packed (up|gate) of the forward; out = packed (dUp|dGate).
+        __nv_bfloat16* dpk = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(row) * p.ldo;
+        const __nv_bfloat16* pk =
+            reinterpret_cast<const __nv_bfloat16*>(p.aux) + static_cast<size_t>(row) * p.ldaux;
+        const int n0 = nb * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 16) {
+          if (n0 + c >= p.n) break;
+          uint32_t r[16];
+          tmem_ld_32x32b_x16(taddr + c, r);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int j = 0; j < 16; j += 8) {
+              if (n0 + c + j < p.n) {
+                const uint4 qu = *reinterpret_cast<const uint4*>(pk + n0 + c + j);
+                const uint4 qg = *reinterpret_cast<const uint4*>(pk + p.n + n0 + c + j);
+                const __nv_bfloat162* bu = reinterpret_cast<const __nv_bfloat162*>(&qu);
+                const __nv_bfloat162* bg = reinterpret_cast<const __nv_bfloat162*>(&qg);
+                uint4 vu, vg;
+                uint32_t* wu = reinterpret_cast<uint32_t*>(&vu);
+                uint32_t* wg = reinterpret_cast<uint32_t*>(&vg);
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                  const float2 u = __bfloat1622float2(bu[t]);
+                  const float2 g = __bfloat1622float2(bg[t]);
+                  const float d0 = bf16_round(__uint_as_float(r[j + 2 * t]));
+                  const float d1 = bf16_round(__uint_as_float(r[j + 2 * t + 1]));
+                  const float s0 = sigmoidf_(g.x), s1 = sigmoidf_(g.y);
+                  wu[t] = pack_bf16x2(d0 * g.x * s0, d1 * g.y * s1);
+                  wg[t] = pack_bf16x2(d0 * u.x * s0 * (1.0f + g.x * (1.0f - s0)),
+                                      d1 * u.y * s1 * (1.0f + g.y * (1.0f - s1)));
+                }
+                *reinterpret_cast<uint4*>(dpk + n0 + c + j) = vu;
+                *reinterpret_cast<uint4*>(dpk + p.n + n0 + c + j) = vg;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[buf]);
+    }
+  }
+
+  // ------------------------------------------------------------------ tear-down
+  tc_fence_before_sync();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag != 0 && p.error_flag != nullptr) atomicExch(p.error_flag, 1);
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// =============================================================================== host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// 2-D BF16 tensor map with 128-byte swizzle: `inner` contiguous elements per row, `outer` rows,
+// row pitch `ld` elements, box = box_inner x box_outer.
+static int make_map_bf16(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer,
+                         uint64_t ld, uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return -10;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (ld * 2) % 16 != 0) return -11;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -12;
+}
+
+static std::atomic<long long> g_launches{0};
+static std::atomic<int> g_sm_limit{0};
+
+template <bool A_MN, bool B_MN, int EPI>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
+                  cudaStream_t stream) {
+  static bool configured = false;  // per-instantiation; the attribute is per function
+  auto kern = gemm_kernel<A_MN, B_MN, EPI>;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return -20;
+    configured = true;
+  }
+  kern<<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+static int sm_count() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return sms;
+}
+
+}  // namespace ws
+
+extern "C" long long ws_launch_count(void) { return ws::g_launches.load(); }
+extern "C" void ws_count_launch(void) { ws::g_launches.fetch_add(1, std::memory_order_relaxed); }
+extern "C" void ws_gemm_set_sm_limit(int sms) { ws::g_sm_limit.store(sms); }
+
+extern "C" int ws_gemm(const WsGemm* g, cudaStream_t stream) {
+  using namespace ws;
+  if (g->m <= 0 || g->n <= 0 || g->k <= 0) return -1;
+  const bool swiglu = g->epilogue == WS_EPI_SWIGLU;
+  const int b_rows = swiglu ? 2 * g->n : g->n;  // output features held by B
+  CUtensorMap ta, tb;
+  int rc;
+  if (!g->a_mn)
+    rc = make_map_bf16(&ta, g->a, g->k, g->m, g->lda, BK, BM);
+  else
+    rc = make_map_bf16(&ta, g->a, g->m, g->k, g->lda, 64, BK);
+  if (rc) return rc;
+  if (!g->b_mn)
+    rc = make_map_bf16(&tb, g->b, g->k, b_rows, g->ldb, BK, 128);
+  else
+    rc = make_map_bf16(&tb, g->b, b_rows, g->k, g->ldb, 64, BK);
+  if (rc) return rc;
+
+  GemmParams p;
+  p.m = g->m; p.n = g->n; p.k = g->k;
+  p.h = g->n;
+  p.epi_n = swiglu ? 128 : BN;
+  p.out = g->out; p.ldo = g->ldo;
+  p.out2 = g->out2; p.ldo2 = g->ldo2;
+  p.aux = g->aux; p.ldaux = g->ldaux;
+  p.row_scale = g->row_scale;
+  p.alpha = g->alpha; p.beta = g->beta;
+  p.error_flag = g->error_flag;
+
+  // Vector-store alignment of the epilogues (8 BF16 or 4 FP32 per store).
+  const bool f32_out = g->epilogue == WS_EPI_RESID_F32 || g->epilogue == WS_EPI_ACC_F32 ||
+                       g->epilogue == WS_EPI_F32;
+  const int vec = f32_out ? 4 : 8;
+  if (g->n % vec != 0 || g->ldo % vec != 0) return -2;
+  if ((g->epilogue == WS_EPI_RESID_F32 || g->epilogue == WS_EPI_RESID_BF16) &&
+      (g->aux == nullptr || g->ldaux % vec != 0)) return -3;
+  if (swiglu && (g->out2 == nullptr || g->ldo2 % 8 != 0)) return -4;
+  if (g->epilogue == WS_EPI_SWIGLU_BWD && (g->aux == nullptr || g->ldaux % 8 != 0)) return -5;
+
+  const int n_tile = swiglu ? 128 : BN;
+  const int tiles = ((g->m + BM - 1) / BM) * ((g->n + n_tile - 1) / n_tile);
+  int sms = sm_count();
+  const int lim = g_sm_limit.load();
+  if (lim > 0 && lim < sms) sms = lim;
+  const int grid = tiles < sms ? tiles : sms;
+
+  const int key = (g->a_mn ? 1 : 0) | (g->b_mn ? 2 : 0) | (g->epilogue << 2);
+  switch (key) {
+    case (0 | (WS_EPI_BF16 << 2)): return launch<false, false, WS_EPI_BF16>(ta, tb, p, grid, stream);
+    case (2 | (WS_EPI_BF16 << 2)): return launch<false, true, WS_EPI_BF16>(ta, tb, p, grid, stream);
+    case (0 | (WS_EPI_RESID_F32 << 2)): return launch<false, false, WS_EPI_RESID_F32>(ta, tb, p, grid, stream);
+    case (0 | (WS_EPI_RESID_BF16 << 2)): return launch<false, false, WS_EPI_RESID_BF16>(ta, tb, p, grid, stream);
+    case (0 | (WS_EPI_SWIGLU << 2)): return launch<false, false, WS_EPI_SWIGLU>(ta, tb, p, grid, stream);
+    case (0 | (WS_EPI_F32 << 2)): return launch<false, false, WS_EPI_F32>(ta, tb, p, grid, stream);
+    case (3 | (WS_EPI_ACC_F32 << 2)): return launch<true, true, WS_EPI_ACC_F32>(ta, tb, p, grid, stream);
+    case (3 | (WS_EPI_BF16 << 2)): return launch<true, true, WS_EPI_BF16>(ta, tb, p, grid, stream);
+    case (2 | (WS_EPI_SWIGLU_BWD << 2)): return launch<false, true, WS_EPI_SWIGLU_BWD>(ta, tb, p, grid, stream);
+    default: return -6;
+  }
+}
