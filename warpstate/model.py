@@ -1,0 +1,5 @@
+from warpstate_ai_b200.models.warpstate import (LayerCache, RMSNorm, SwiGLU, WarpStateCore, WarpStateLM,
+                                                apply_rope, rope_cos_sin, rotate_half)
+
+__all__ = ["LayerCache", "RMSNorm", "SwiGLU", "WarpStateCore", "WarpStateLM", "apply_rope",
+           "rope_cos_sin", "rotate_half"]

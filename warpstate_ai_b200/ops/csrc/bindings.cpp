@@ -79,14 +79,193 @@ void gemm(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool b_mn, int64_
   check_rc(ws_gemm(&g, cur_stream()), "gemm");
 }
 
+// ----------------------------------------------------------------------------- row kernels
+std::tuple<at::Tensor, at::Tensor, at::Tensor> rmsnorm_fwd(const at::Tensor& x,
+                                                           const c10::optional<at::Tensor>& col_scale,
+                                                           const c10::optional<at::Tensor>& col_bias,
+                                                           const at::Tensor& w, double eps, bool want_xmod) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.is_contiguous(), "rmsnorm_fwd: x must be contiguous [rows,d]");
+  TORCH_CHECK(x.scalar_type() == at::kFloat || x.scalar_type() == at::kBFloat16, "rmsnorm_fwd: x dtype");
+  TORCH_CHECK(w.scalar_type() == at::kFloat && w.is_contiguous() && w.numel() == x.size(1), "rmsnorm_fwd: w");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int rows = (int)x.size(0), d = (int)x.size(1);
+  const bool mod = col_scale.has_value() && col_scale->defined();
+  if (mod) {
+    TORCH_CHECK(col_scale->scalar_type() == at::kFloat && col_scale->is_contiguous() && col_scale->numel() == d &&
+                col_bias.has_value() && col_bias->scalar_type() == at::kFloat && col_bias->is_contiguous() &&
+                col_bias->numel() == d, "rmsnorm_fwd: depth modulation vectors must be float32 [d]");
+  }
+  at::Tensor z = at::empty({rows, d}, x.options().dtype(at::kBFloat16));
+  at::Tensor rstd = at::empty({rows}, x.options().dtype(at::kFloat));
+  at::Tensor xmod = (mod && want_xmod) ? at::empty_like(x) : at::Tensor();
+  check_rc(ws_rmsnorm_fwd(x.data_ptr(), x.scalar_type() == at::kBFloat16,
+                          mod ? col_scale->data_ptr<float>() : nullptr,
+                          mod ? col_bias->data_ptr<float>() : nullptr, w.data_ptr<float>(), (float)eps, rows, d,
+                          xmod.defined() ? xmod.data_ptr() : nullptr, z.data_ptr(), rstd.data_ptr<float>(),
+                          cur_stream()), "rmsnorm_fwd");
+  return {z, rstd, xmod.defined() ? xmod : x};
+}
+
+// returns (dx, dx_bf16, dw) ; dw is the finished column sum [d]
+std::tuple<at::Tensor, at::Tensor, at::Tensor> rmsnorm_bwd(const at::Tensor& dz, const at::Tensor& x,
+                                                           const at::Tensor& rstd, const at::Tensor& w,
+                                                           const c10::optional<at::Tensor>& dres,
+                                                           const c10::optional<at::Tensor>& out_scale,
+                                                           bool want_bf16) {
+  TORCH_CHECK(dz.is_cuda() && dz.scalar_type() == at::kBFloat16 && dz.is_contiguous(), "rmsnorm_bwd: dz");
+  TORCH_CHECK(x.is_contiguous() && x.sizes() == dz.sizes(), "rmsnorm_bwd: x");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int rows = (int)x.size(0), d = (int)x.size(1);
+  const bool has_res = dres.has_value() && dres->defined();
+  if (has_res) { TORCH_CHECK(dres->scalar_type() == x.scalar_type() && dres->is_contiguous() && dres->sizes() == x.sizes(), "rmsnorm_bwd: dres"); }
+  const bool has_scale = out_scale.has_value() && out_scale->defined();
+  at::Tensor dx = at::empty_like(x);
+  at::Tensor dxb = want_bf16 ? at::empty({rows, d}, x.options().dtype(at::kBFloat16)) : at::Tensor();
+  const int parts = ws_rmsnorm_bwd_parts(rows);
+  at::Tensor partial = at::empty({parts, d}, x.options().dtype(at::kFloat));
+  check_rc(ws_rmsnorm_bwd(dz.data_ptr(), x.data_ptr(), x.scalar_type() == at::kBFloat16, rstd.data_ptr<float>(),
+                          w.data_ptr<float>(), has_res ? dres->data_ptr() : nullptr,
+                          has_scale ? out_scale->data_ptr<float>() : nullptr, rows, d, dx.data_ptr(),
+                          want_bf16 ? dxb.data_ptr() : nullptr, partial.data_ptr<float>(), cur_stream()),
+           "rmsnorm_bwd");
+  at::Tensor dw = at::empty({d}, x.options().dtype(at::kFloat));
+  check_rc(ws_colsum_finalize(partial.data_ptr<float>(), parts, d, nullptr, 0.f, dw.data_ptr<float>(), cur_stream()),
+           "colsum_finalize");
+  return {dx, dxb, dw};
+}
+
+// (sum_rows a / (1+inv_scale), sum_rows a*b / (1+inv_scale))
+std::tuple<at::Tensor, at::Tensor> colsum2(const at::Tensor& a, const at::Tensor& b,
+                                           const c10::optional<at::Tensor>& inv_scale) {
+  TORCH_CHECK(a.is_cuda() && a.is_contiguous() && b.is_contiguous() && a.sizes() == b.sizes() &&
+              a.scalar_type() == b.scalar_type(), "colsum2: a, b");
+  c10::cuda::CUDAGuard guard(a.device());
+  const int rows = (int)a.size(0), d = (int)a.size(1);
+  const int parts = ws_colsum_parts(rows);
+  at::Tensor pa = at::empty({parts, d}, a.options().dtype(at::kFloat));
+  at::Tensor pab = at::empty({parts, d}, a.options().dtype(at::kFloat));
+  check_rc(ws_colsum2(a.data_ptr(), b.data_ptr(), a.scalar_type() == at::kBFloat16, rows, d, pa.data_ptr<float>(),
+                      pab.data_ptr<float>(), cur_stream()), "colsum2");
+  at::Tensor sa = at::empty({d}, a.options().dtype(at::kFloat));
+  at::Tensor sab = at::empty({d}, a.options().dtype(at::kFloat));
+  const float* inv = inv_scale.has_value() && inv_scale->defined() ? inv_scale->data_ptr<float>() : nullptr;
+  check_rc(ws_colsum_finalize(pa.data_ptr<float>(), parts, d, inv, 0.f, sa.data_ptr<float>(), cur_stream()), "colsum_finalize");
+  check_rc(ws_colsum_finalize(pab.data_ptr<float>(), parts, d, inv, 0.f, sab.data_ptr<float>(), cur_stream()), "colsum_finalize");
+  return {sa, sab};
+}
+
+at::Tensor cast_bf16(const at::Tensor& x, c10::optional<at::Tensor> out) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kFloat && x.is_contiguous(), "cast_bf16: x");
+  c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor o = out.has_value() && out->defined() ? *out : at::empty(x.sizes(), x.options().dtype(at::kBFloat16));
+  TORCH_CHECK(o.scalar_type() == at::kBFloat16 && o.is_contiguous() && o.numel() == x.numel(), "cast_bf16: out");
+  if (x.numel() % 4 == 0 && (reinterpret_cast<uintptr_t>(x.data_ptr()) % 16 == 0) &&
+      (reinterpret_cast<uintptr_t>(o.data_ptr()) % 8 == 0)) {
+    check_rc(ws_cast_f32_bf16(x.data_ptr<float>(), o.data_ptr(), (size_t)x.numel(), cur_stream()), "cast_bf16");
+  } else {
+    o.copy_(x);
+  }
+  return o;
+}
+
+at::Tensor embed_fwd(const at::Tensor& ids, const at::Tensor& table, bool out_bf16) {
+  TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == at::kLong && ids.is_contiguous(), "embed_fwd: ids");
+  TORCH_CHECK(table.dim() == 2 && table.is_contiguous(), "embed_fwd: table");
+  c10::cuda::CUDAGuard guard(table.device());
+  const int rows = (int)ids.numel(), d = (int)table.size(1);
+  at::Tensor out = at::empty({rows, d}, table.options().dtype(out_bf16 ? at::kBFloat16 : at::kFloat));
+  check_rc(ws_embed_fwd(ids.data_ptr<int64_t>() ? reinterpret_cast<const long long*>(ids.data_ptr<int64_t>()) : nullptr,
+                        table.data_ptr(), table.scalar_type() == at::kBFloat16, rows, d, (int)table.size(0),
+                        out.data_ptr(), out_bf16, cur_stream()), "embed_fwd");
+  return out;
+}
+
+// grad_table [V,d] FP32 += scatter of dx rows by token id, deterministic (sorted segments).
+void embed_bwd(const at::Tensor& dx, const at::Tensor& ids, at::Tensor grad_table) {
+  TORCH_CHECK(dx.is_cuda() && dx.dim() == 2 && dx.is_contiguous(), "embed_bwd: dx");
+  TORCH_CHECK(grad_table.scalar_type() == at::kFloat && grad_table.is_contiguous(), "embed_bwd: grad_table");
+  c10::cuda::CUDAGuard guard(dx.device());
+  const int rows = (int)dx.size(0), d = (int)dx.size(1);
+  at::Tensor flat = ids.reshape({-1});
+  auto sorted = flat.sort();
+  at::Tensor sorted_ids = std::get<0>(sorted).contiguous();
+  at::Tensor order = std::get<1>(sorted).contiguous();
+  // first position of each run of equal ids
+  at::Tensor is_start = at::ones({rows}, flat.options().dtype(at::kBool));
+  if (rows > 1) is_start.slice(0, 1).copy_(sorted_ids.slice(0, 1).ne(sorted_ids.slice(0, 0, rows - 1)));
+  at::Tensor seg_start = is_start.nonzero().reshape({-1}).to(at::kInt).contiguous();
+  const int n_seg = (int)seg_start.numel();
+  check_rc(ws_embed_bwd(dx.data_ptr(), dx.scalar_type() == at::kBFloat16,
+                        reinterpret_cast<const long long*>(sorted_ids.data_ptr<int64_t>()),
+                        reinterpret_cast<const long long*>(order.data_ptr<int64_t>()), seg_start.data_ptr<int>(),
+                        n_seg, rows, d, grad_table.data_ptr<float>(), cur_stream()), "embed_bwd");
+}
+
+// ----------------------------------------------------------------------------- optimizer
+at::Tensor grad_norm_clip(const at::Tensor& g, double max_norm, const c10::optional<at::Tensor>& extra_sumsq) {
+  TORCH_CHECK(g.is_cuda() && g.scalar_type() == at::kFloat && g.is_contiguous() && g.numel() % 4 == 0,
+              "grad_norm_clip: flat float32 buffer with numel % 4 == 0 required");
+  c10::cuda::CUDAGuard guard(g.device());
+  at::Tensor partial = at::empty({ws_sumsq_parts()}, g.options());
+  at::Tensor stats = at::empty({3}, g.options());
+  const float* extra = extra_sumsq.has_value() && extra_sumsq->defined() ? extra_sumsq->data_ptr<float>() : nullptr;
+  check_rc(ws_grad_norm_clip(g.data_ptr<float>(), (size_t)g.numel(), partial.data_ptr<float>(), extra,
+                             (float)max_norm, stats.data_ptr<float>(), cur_stream()), "grad_norm_clip");
+  return stats;
+}
+
+void adamw_step(at::Tensor p, const at::Tensor& g, at::Tensor m, at::Tensor v, c10::optional<at::Tensor> p_bf16,
+                double lr, double beta1, double beta2, double eps, double wd, int64_t step,
+                const c10::optional<at::Tensor>& grad_scale, double grad_scale_const) {
+  TORCH_CHECK(p.is_cuda() && p.scalar_type() == at::kFloat && p.is_contiguous(), "adamw_step: p");
+  TORCH_CHECK(g.numel() == p.numel() && m.numel() == p.numel() && v.numel() == p.numel(), "adamw_step: sizes");
+  TORCH_CHECK(g.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat &&
+              g.is_contiguous() && m.is_contiguous() && v.is_contiguous(), "adamw_step: float32 contiguous");
+  c10::cuda::CUDAGuard guard(p.device());
+  void* pb = nullptr;
+  if (p_bf16.has_value() && p_bf16->defined()) {
+    TORCH_CHECK(p_bf16->scalar_type() == at::kBFloat16 && p_bf16->numel() == p.numel() && p_bf16->is_contiguous(),
+                "adamw_step: p_bf16");
+    pb = p_bf16->data_ptr();
+  }
+  const float* gs = grad_scale.has_value() && grad_scale->defined() ? grad_scale->data_ptr<float>() : nullptr;
+  check_rc(ws_adamw(p.data_ptr<float>(), g.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), pb,
+                    (size_t)p.numel(), (float)lr, (float)beta1, (float)beta2, (float)eps, (float)wd, (int)step, gs,
+                    (float)grad_scale_const, cur_stream()), "adamw_step");
+}
+
+int64_t launch_count() { return (int64_t)ws_launch_count(); }
+
 }  // namespace
 
 TORCH_LIBRARY(ws_b200, m) {
+  m.def("rmsnorm_fwd(Tensor x, Tensor? col_scale, Tensor? col_bias, Tensor w, float eps, bool want_xmod) -> (Tensor, Tensor, Tensor)");
+  m.def("rmsnorm_bwd(Tensor dz, Tensor x, Tensor rstd, Tensor w, Tensor? dres, Tensor? out_scale, bool want_bf16) -> (Tensor, Tensor, Tensor)");
+  m.def("colsum2(Tensor a, Tensor b, Tensor? inv_scale) -> (Tensor, Tensor)");
+  m.def("cast_bf16(Tensor x, Tensor(a!)? out) -> Tensor");
+  m.def("embed_fwd(Tensor ids, Tensor table, bool out_bf16) -> Tensor");
+  m.def("embed_bwd(Tensor dx, Tensor ids, Tensor(a!) grad_table) -> ()");
+  m.def("launch_count() -> int");
+  m.def("grad_norm_clip(Tensor g, float max_norm, Tensor? extra_sumsq) -> Tensor");
+  m.def("adamw_step(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, Tensor(d!)? p_bf16, float lr, float beta1, "
+        "float beta2, float eps, float wd, int step, Tensor? grad_scale, float grad_scale_const) -> ()");
   m.def("gemm(Tensor a, Tensor b, bool a_mn, bool b_mn, int epilogue, int m, int n, int k, "
         "Tensor(a!) out, Tensor(b!)? out2, Tensor? aux, Tensor? row_scale, float alpha, float beta, "
         "Tensor(c!)? error_flag) -> ()");
 }
 
+TORCH_LIBRARY_IMPL(ws_b200, CompositeExplicitAutograd, m) {
+  m.impl("launch_count", &launch_count);
+}
+
 TORCH_LIBRARY_IMPL(ws_b200, CUDA, m) {
   m.impl("gemm", &gemm);
+  m.impl("rmsnorm_fwd", &rmsnorm_fwd);
+  m.impl("rmsnorm_bwd", &rmsnorm_bwd);
+  m.impl("colsum2", &colsum2);
+  m.impl("cast_bf16", &cast_bf16);
+  m.impl("embed_fwd", &embed_fwd);
+  m.impl("embed_bwd", &embed_bwd);
+  m.impl("grad_norm_clip", &grad_norm_clip);
+  m.impl("adamw_step", &adamw_step);
 }

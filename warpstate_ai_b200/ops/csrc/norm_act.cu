@@ -1,0 +1,370 @@
+// Bandwidth-bound row kernels: RMSNorm forward / backward (with the depth modulation of the
+// residual stream folded in), casts, column sums and the embedding gather / scatter.
+//
+// One warp owns one row; a lane owns columns {lane*4 + 128*i}.  Row statistics are FP32
+// (the reference norm, warpstate/model.py:22-28; its Triton twin ops/activation_execution.py:96-158).
+// Weight-gradient column sums are accumulated per lane in registers, reduced across the warps
+// of a block in shared memory and written as one partial row per block; a second kernel adds the
+// partial rows in a fixed order, so the result does not depend on scheduling.
+#include "ws_ptx.cuh"
+#include "ws_api.h"
+
+namespace ws {
+
+extern "C" void ws_count_launch(void);
+
+constexpr int ROW_WARPS = 8;
+constexpr int ROW_THREADS = ROW_WARPS * 32;
+constexpr int MAX_CHUNKS = 16;  // d <= 2048 for the register-accumulating backward
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 ld4(const __nv_bfloat16* p) {
+  const uint2 v = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void st4(__nv_bfloat16* p, float4 v) {
+  uint2 o;
+  o.x = pack_bf16x2(v.x, v.y);
+  o.y = pack_bf16x2(v.z, v.w);
+  *reinterpret_cast<uint2*>(p) = o;
+}
+
+// --------------------------------------------------------------------------- RMSNorm forward
+// x_mod = x * (1 + col_scale) + col_bias (when given); z = bf16(x_mod * rstd * w).
+template <typename T>
+__global__ void __launch_bounds__(ROW_THREADS)
+rmsnorm_fwd_kernel(const T* __restrict__ x, const float* __restrict__ col_scale,
+                   const float* __restrict__ col_bias, const float* __restrict__ w, float eps, int rows,
+                   int d, T* __restrict__ xmod_out, __nv_bfloat16* __restrict__ z,
+                   float* __restrict__ rstd_out) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int row = blockIdx.x * ROW_WARPS + warp; row < rows; row += gridDim.x * ROW_WARPS) {
+    const T* xr = x + static_cast<size_t>(row) * d;
+    float ss = 0.f;
+    for (int c = lane * 4; c < d; c += 128) {
+      float4 v = ld4(xr + c);
+      if (col_scale != nullptr) {
+        const float4 s = ld4(col_scale + c), b = ld4(col_bias + c);
+        v.x = v.x * (1.f + s.x) + b.x; v.y = v.y * (1.f + s.y) + b.y;
+        v.z = v.z * (1.f + s.z) + b.z; v.w = v.w * (1.f + s.w) + b.w;
+        if (sizeof(T) == 2) { v.x = bf16_round(v.x); v.y = bf16_round(v.y); v.z = bf16_round(v.z); v.w = bf16_round(v.w); }
+      }
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / static_cast<float>(d) + eps);
+    if (lane == 0 && rstd_out != nullptr) rstd_out[row] = rstd;
+    for (int c = lane * 4; c < d; c += 128) {
+      float4 v = ld4(xr + c);
+      if (col_scale != nullptr) {
+        const float4 s = ld4(col_scale + c), b = ld4(col_bias + c);
+        v.x = v.x * (1.f + s.x) + b.x; v.y = v.y * (1.f + s.y) + b.y;
+        v.z = v.z * (1.f + s.z) + b.z; v.w = v.w * (1.f + s.w) + b.w;
+        if (sizeof(T) == 2) { v.x = bf16_round(v.x); v.y = bf16_round(v.y); v.z = bf16_round(v.z); v.w = bf16_round(v.w); }
+      }
+      if (xmod_out != nullptr) st4(xmod_out + static_cast<size_t>(row) * d + c, v);
+      const float4 ww = ld4(w + c);
+      float4 o;
+      if (sizeof(T) == 2) {  // BF16 stream: round x_hat and w first, as an eager BF16 norm does
+        o.x = bf16_round(v.x * rstd) * bf16_round(ww.x); o.y = bf16_round(v.y * rstd) * bf16_round(ww.y);
+        o.z = bf16_round(v.z * rstd) * bf16_round(ww.z); o.w = bf16_round(v.w * rstd) * bf16_round(ww.w);
+      } else {
+        o.x = v.x * rstd * ww.x; o.y = v.y * rstd * ww.y; o.z = v.z * rstd * ww.z; o.w = v.w * rstd * ww.w;
+      }
+      st4(z + static_cast<size_t>(row) * d + c, o);
+    }
+  }
+}
+
+// --------------------------------------------------------------------------- RMSNorm backward
+// dxn = rstd * (dz*w - x_hat * mean(dz*w*x_hat));  out = (dres + dxn) * (1 + out_scale)
+// dw_partial[block] = sum over the block's rows of dz * x_hat.
+template <typename T>
+__global__ void __launch_bounds__(ROW_THREADS)
+rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dz, const T* __restrict__ x,
+                   const float* __restrict__ rstd_in, const float* __restrict__ w,
+                   const T* __restrict__ dres, const float* __restrict__ out_scale, int rows, int d,
+                   T* __restrict__ dx_out, __nv_bfloat16* __restrict__ dx_bf16,
+                   float* __restrict__ dw_partial) {
+  __shared__ float red[ROW_WARPS][128];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nchunk = d / 128;
+  float4 acc[MAX_CHUNKS];
+#pragma unroll
+  for (int i = 0; i < MAX_CHUNKS; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  const float inv_d = 1.0f / static_cast<float>(d);
+
+  for (int row = blockIdx.x * ROW_WARPS + warp; row < rows; row += gridDim.x * ROW_WARPS) {
+    const size_t base = static_cast<size_t>(row) * d;
+    const float rstd = rstd_in[row];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAX_CHUNKS; ++i) {
+      if (i < nchunk) {
+        const int c = lane * 4 + i * 128;
+        const float4 g = ld4(dz + base + c);
+        const float4 xv = ld4(x + base + c);
+        const float4 ww = ld4(w + c);
+        dot += g.x * ww.x * xv.x + g.y * ww.y * xv.y + g.z * ww.z * xv.z + g.w * ww.w * xv.w;
+      }
+    }
+    dot = warp_sum(dot) * rstd * inv_d;  // mean(dz*w*x_hat)
+#pragma unroll
+    for (int i = 0; i < MAX_CHUNKS; ++i) {
+      if (i < nchunk) {
+        const int c = lane * 4 + i * 128;
+        const float4 g = ld4(dz + base + c);
+        const float4 xv = ld4(x + base + c);
+        const float4 ww = ld4(w + c);
+        float4 xh = make_float4(xv.x * rstd, xv.y * rstd, xv.z * rstd, xv.w * rstd);
+        acc[i].x += g.x * xh.x; acc[i].y += g.y * xh.y; acc[i].z += g.z * xh.z; acc[i].w += g.w * xh.w;
+        float4 o;
+        o.x = rstd * (g.x * ww.x - xh.x * dot); o.y = rstd * (g.y * ww.y - xh.y * dot);
+        o.z = rstd * (g.z * ww.z - xh.z * dot); o.w = rstd * (g.w * ww.w - xh.w * dot);
+        if (dres != nullptr) {
+          const float4 r = ld4(dres + base + c);
+          o.x += r.x; o.y += r.y; o.z += r.z; o.w += r.w;
+        }
+        if (out_scale != nullptr) {
+          const float4 s = ld4(out_scale + c);
+          o.x *= 1.f + s.x; o.y *= 1.f + s.y; o.z *= 1.f + s.z; o.w *= 1.f + s.w;
+        }
+        st4(dx_out + base + c, o);
+        if (dx_bf16 != nullptr) st4(dx_bf16 + base + c, o);
+      }
+    }
+  }
+  // Block reduction of the column sums, one 128-column chunk at a time.
+  if (dw_partial != nullptr) {
+#pragma unroll
+    for (int i = 0; i < MAX_CHUNKS; ++i) {
+      if (i < nchunk) {
+        __syncthreads();
+        *reinterpret_cast<float4*>(&red[warp][lane * 4]) = acc[i];
+        __syncthreads();
+        if (threadIdx.x < 128) {
+          float s = 0.f;
+#pragma unroll
+          for (int wgt = 0; wgt < ROW_WARPS; ++wgt) s += red[wgt][threadIdx.x];
+          dw_partial[static_cast<size_t>(blockIdx.x) * d + i * 128 + threadIdx.x] = s;
+        }
+      }
+    }
+  }
+}
+
+// --------------------------------------------------------------------------- column sums
+// partial_a[block] = sum_rows a ; partial_ab[block] = sum_rows a*b  (a, b: [rows, d])
+template <typename T>
+__global__ void __launch_bounds__(ROW_THREADS)
+colsum2_kernel(const T* __restrict__ a, const T* __restrict__ b, int rows, int d,
+               float* __restrict__ partial_a, float* __restrict__ partial_ab) {
+  // thread t owns columns t*4 .. t*4+3 of a 1024-wide panel; rows strided over blocks
+  for (int c0 = 0; c0 < d; c0 += ROW_THREADS * 4) {
+    const int c = c0 + threadIdx.x * 4;
+    if (c >= d) continue;
+    float4 sa = make_float4(0.f, 0.f, 0.f, 0.f), sab = sa;
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+      const float4 va = ld4(a + static_cast<size_t>(row) * d + c);
+      sa.x += va.x; sa.y += va.y; sa.z += va.z; sa.w += va.w;
+      if (b != nullptr) {
+        const float4 vb = ld4(b + static_cast<size_t>(row) * d + c);
+        sab.x += va.x * vb.x; sab.y += va.y * vb.y; sab.z += va.z * vb.z; sab.w += va.w * vb.w;
+      }
+    }
+    st4(partial_a + static_cast<size_t>(blockIdx.x) * d + c, sa);
+    if (b != nullptr) st4(partial_ab + static_cast<size_t>(blockIdx.x) * d + c, sab);
+  }
+}
+
+// out[c] = beta*out[c] + scale(c) * sum_p partial[p][c];  scale(c) = 1/(1+inv_scale[c]) if given
+__global__ void colsum_finalize_kernel(const float* __restrict__ partial, int parts, int d,
+                                       const float* __restrict__ inv_scale, float beta,
+                                       float* __restrict__ out) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= d) return;
+  float s = 0.f;
+  for (int p = 0; p < parts; ++p) s += partial[static_cast<size_t>(p) * d + c];
+  if (inv_scale != nullptr) {
+    const float den = 1.f + inv_scale[c];
+    s = den != 0.f ? s / den : 0.f;
+  }
+  out[c] = (beta != 0.f ? beta * out[c] : 0.f) + s;
+}
+
+// --------------------------------------------------------------------------- casts
+__global__ void cast_f32_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out,
+                                     size_t n4) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n4;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    st4(out + i * 4, ld4(in + i * 4));
+  }
+}
+
+// --------------------------------------------------------------------------- embedding
+// out[row] = table[ids[row]] ; table FP32 (master) or BF16, out FP32 or BF16
+template <typename TT, typename TO>
+__global__ void __launch_bounds__(ROW_THREADS)
+embed_fwd_kernel(const long long* __restrict__ ids, const TT* __restrict__ table, int rows, int d,
+                 int vocab, TO* __restrict__ out) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int row = blockIdx.x * ROW_WARPS + warp; row < rows; row += gridDim.x * ROW_WARPS) {
+    long long id = ids[row];
+    if (id < 0 || id >= vocab) id = 0;
+    const TT* src = table + static_cast<size_t>(id) * d;
+    for (int c = lane * 4; c < d; c += 128) st4(out + static_cast<size_t>(row) * d + c, ld4(src + c));
+  }
+}
+
+// Deterministic embedding backward: rows were sorted by token id on the host side of the op
+// (`order` = argsort of ids, `seg_start` = first position of each distinct id in that order).
+// One warp adds all gradient rows of one distinct token in order and accumulates into the
+// FP32 gradient table - no atomics, run-to-run identical.
+template <typename T>
+__global__ void __launch_bounds__(ROW_THREADS)
+embed_bwd_kernel(const T* __restrict__ dx, const long long* __restrict__ sorted_ids,
+                 const long long* __restrict__ order, const int* __restrict__ seg_start, int n_seg,
+                 int rows, int d, float* __restrict__ grad_table) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int seg = blockIdx.x * ROW_WARPS + warp; seg < n_seg; seg += gridDim.x * ROW_WARPS) {
+    const int begin = seg_start[seg];
+    const int end = (seg + 1 < n_seg) ? seg_start[seg + 1] : rows;
+    const long long id = sorted_ids[begin];
+    float* dst = grad_table + static_cast<size_t>(id) * d;
+    for (int c = lane * 4; c < d; c += 128) {
+      float4 s = ld4(dst + c);
+      for (int j = begin; j < end; ++j) {
+        const float4 v = ld4(dx + static_cast<size_t>(order[j]) * d + c);
+        s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+      }
+      st4(dst + c, s);
+    }
+  }
+}
+
+static int row_grid(int rows) {
+  int blocks = (rows + ROW_WARPS - 1) / ROW_WARPS;
+  const int cap = 148 * 8;
+  return blocks < cap ? (blocks > 0 ? blocks : 1) : cap;
+}
+
+}  // namespace ws
+
+using namespace ws;
+
+extern "C" int ws_rmsnorm_fwd(const void* x, int x_bf16, const float* col_scale, const float* col_bias,
+                              const float* w, float eps, int rows, int d, void* xmod_out, void* z,
+                              float* rstd, cudaStream_t stream) {
+  if (d % 128 != 0 || rows <= 0) return -1;
+  const int grid = row_grid(rows);
+  if (x_bf16)
+    rmsnorm_fwd_kernel<__nv_bfloat16><<<grid, ROW_THREADS, 0, stream>>>(
+        (const __nv_bfloat16*)x, col_scale, col_bias, w, eps, rows, d, (__nv_bfloat16*)xmod_out,
+        (__nv_bfloat16*)z, rstd);
+  else
+    rmsnorm_fwd_kernel<float><<<grid, ROW_THREADS, 0, stream>>>(
+        (const float*)x, col_scale, col_bias, w, eps, rows, d, (float*)xmod_out, (__nv_bfloat16*)z, rstd);
+  ws_count_launch();
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// Number of partial rows ws_rmsnorm_bwd writes (the caller sizes dw_partial as parts*d floats).
+extern "C" int ws_rmsnorm_bwd_parts(int rows) {
+  int blocks = (rows + ROW_WARPS - 1) / ROW_WARPS;
+  const int cap = 148 * 2;
+  return blocks < cap ? (blocks > 0 ? blocks : 1) : cap;
+}
+
+extern "C" int ws_rmsnorm_bwd(const void* dz, const void* x, int x_bf16, const float* rstd, const float* w,
+                              const void* dres, const float* out_scale, int rows, int d, void* dx_out,
+                              void* dx_bf16, float* dw_partial, cudaStream_t stream) {
+  if (d % 128 != 0 || d > 128 * MAX_CHUNKS || rows <= 0) return -1;
+  const int grid = ws_rmsnorm_bwd_parts(rows);
+  if (x_bf16)
+    rmsnorm_bwd_kernel<__nv_bfloat16><<<grid, ROW_THREADS, 0, stream>>>(
+        (const __nv_bfloat16*)dz, (const __nv_bfloat16*)x, rstd, w, (const __nv_bfloat16*)dres, out_scale,
+        rows, d, (__nv_bfloat16*)dx_out, (__nv_bfloat16*)dx_bf16, dw_partial);
+  else
+    rmsnorm_bwd_kernel<float><<<grid, ROW_THREADS, 0, stream>>>(
+        (const __nv_bfloat16*)dz, (const float*)x, rstd, w, (const float*)dres, out_scale, rows, d,
+        (float*)dx_out, (__nv_bfloat16*)dx_bf16, dw_partial);
+  ws_count_launch();
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int ws_colsum_parts(int rows) { return rows < 296 ? (rows > 0 ? rows : 1) : 296; }
+
+extern "C" int ws_colsum2(const void* a, const void* b, int is_bf16, int rows, int d, float* partial_a,
+                          float* partial_ab, cudaStream_t stream) {
+  if (d % 4 != 0 || rows <= 0) return -1;
+  const int grid = ws_colsum_parts(rows);
+  if (is_bf16)
+    colsum2_kernel<__nv_bfloat16><<<grid, ROW_THREADS, 0, stream>>>(
+        (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, rows, d, partial_a, partial_ab);
+  else
+    colsum2_kernel<float><<<grid, ROW_THREADS, 0, stream>>>((const float*)a, (const float*)b, rows, d,
+                                                            partial_a, partial_ab);
+  ws_count_launch();
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int ws_colsum_finalize(const float* partial, int parts, int d, const float* inv_scale, float beta,
+                                  float* out, cudaStream_t stream) {
+  colsum_finalize_kernel<<<(d + 255) / 256, 256, 0, stream>>>(partial, parts, d, inv_scale, beta, out);
+  ws_count_launch();
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int ws_cast_f32_bf16(const float* in, void* out, size_t n, cudaStream_t stream) {
+  if (n % 4 != 0) return -1;
+  if (n == 0) return 0;
+  const size_t n4 = n / 4;
+  size_t blocks = (n4 + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  cast_f32_bf16_kernel<<<(int)blocks, 256, 0, stream>>>(in, (__nv_bfloat16*)out, n4);
+  ws_count_launch();
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int ws_embed_fwd(const long long* ids, const void* table, int table_bf16, int rows, int d,
+                            int vocab, void* out, int out_bf16, cudaStream_t stream) {
+  if (d % 4 != 0 || rows <= 0) return -1;
+  const int grid = row_grid(rows);
+  if (table_bf16 && out_bf16)
+    embed_fwd_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, ROW_THREADS, 0, stream>>>(
+        ids, (const __nv_bfloat16*)table, rows, d, vocab, (__nv_bfloat16*)out);
+  else if (!table_bf16 && out_bf16)
+    embed_fwd_kernel<float, __nv_bfloat16><<<grid, ROW_THREADS, 0, stream>>>(
+        ids, (const float*)table, rows, d, vocab, (__nv_bfloat16*)out);
+  else if (!table_bf16 && !out_bf16)
+    embed_fwd_kernel<float, float><<<grid, ROW_THREADS, 0, stream>>>(ids, (const float*)table, rows, d,
+                                                                     vocab, (float*)out);
+  else
+    return -3;
+  ws_count_launch();
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+extern "C" int ws_embed_bwd(const void* dx, int dx_bf16, const long long* sorted_ids, const long long* order,
+                            const int* seg_start, int n_seg, int rows, int d, float* grad_table,
+                            cudaStream_t stream) {
+  if (d % 4 != 0 || rows <= 0 || n_seg <= 0) return -1;
+  const int grid = row_grid(n_seg);
+  if (dx_bf16)
+    embed_bwd_kernel<__nv_bfloat16><<<grid, ROW_THREADS, 0, stream>>>(
+        (const __nv_bfloat16*)dx, sorted_ids, order, seg_start, n_seg, rows, d, grad_table);
+  else
+    embed_bwd_kernel<float><<<grid, ROW_THREADS, 0, stream>>>((const float*)dx, sorted_ids, order,
+                                                              seg_start, n_seg, rows, d, grad_table);
+  ws_count_launch();
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}

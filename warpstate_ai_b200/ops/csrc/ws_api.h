@@ -4,6 +4,7 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stddef.h>
 
 #ifdef __cplusplus
 extern "C" {
@@ -51,6 +52,45 @@ void ws_gemm_set_sm_limit(int sms);
 
 // Number of kernels this library has launched in this process.
 long long ws_launch_count(void);
+void ws_count_launch(void);
+
+// ----------------------------------------------------------------------------- row kernels
+// RMSNorm forward over `rows` rows of width d (d % 128 == 0).  The residual stream `x` is FP32
+// (x_bf16 = 0) or BF16.  When col_scale/col_bias are given the depth modulation
+// x*(1+scale)+bias is applied first and (optionally) written to xmod_out.  z is BF16.
+int ws_rmsnorm_fwd(const void* x, int x_bf16, const float* col_scale, const float* col_bias,
+                   const float* w, float eps, int rows, int d, void* xmod_out, void* z, float* rstd,
+                   cudaStream_t stream);
+// RMSNorm backward: dx_out = (dres + norm_bwd(dz)) * (1 + out_scale); optional BF16 copy;
+// dw_partial holds ws_rmsnorm_bwd_parts(rows) partial rows of d floats (d <= 2048).
+int ws_rmsnorm_bwd_parts(int rows);
+int ws_rmsnorm_bwd(const void* dz, const void* x, int x_bf16, const float* rstd, const float* w,
+                   const void* dres, const float* out_scale, int rows, int d, void* dx_out,
+                   void* dx_bf16, float* dw_partial, cudaStream_t stream);
+// Column sums of a and a*b over rows, as ws_colsum_parts(rows) partial rows.
+int ws_colsum_parts(int rows);
+int ws_colsum2(const void* a, const void* b, int is_bf16, int rows, int d, float* partial_a,
+               float* partial_ab, cudaStream_t stream);
+// out[c] = beta*out[c] + (sum_p partial[p][c]) / (1 + inv_scale[c])   (inv_scale may be NULL)
+int ws_colsum_finalize(const float* partial, int parts, int d, const float* inv_scale, float beta,
+                       float* out, cudaStream_t stream);
+int ws_cast_f32_bf16(const float* in, void* out, size_t n, cudaStream_t stream);
+int ws_embed_fwd(const long long* ids, const void* table, int table_bf16, int rows, int d, int vocab,
+                 void* out, int out_bf16, cudaStream_t stream);
+int ws_embed_bwd(const void* dx, int dx_bf16, const long long* sorted_ids, const long long* order,
+                 const int* seg_start, int n_seg, int rows, int d, float* grad_table,
+                 cudaStream_t stream);
+
+// ----------------------------------------------------------------------------- optimizer
+int ws_sumsq_parts(void);
+// stats[0] = ||g||_2, stats[1] = min(1, max_norm / (||g|| + 1e-6)), stats[2] = ||g||^2 (+ *extra_sumsq)
+int ws_grad_norm_clip(const float* g, size_t n, float* partial, const float* extra_sumsq, float max_norm,
+                      float* stats, cudaStream_t stream);
+// AdamW over flat FP32 arenas (n % 4 == 0); gradients are multiplied by *grad_scale_ptr (device,
+// may be NULL) times grad_scale_const first; p_bf16 (may be NULL) receives the BF16 copy of p.
+int ws_adamw(float* p, const float* g, float* m, float* v, void* p_bf16, size_t n, float lr, float beta1,
+             float beta2, float eps, float wd, int step, const float* grad_scale_ptr,
+             float grad_scale_const, cudaStream_t stream);
 
 #ifdef __cplusplus
 }
