@@ -1,0 +1,555 @@
+// Backward kernels of the middle of a WarpState core (chunk 128, head_dim 64).
+//
+//   dstate_kernel       : dState[b,n,h] = rope(Q)^T (dy * (1 - sigmoid(g)) / 8)           (64x64)
+//   memory_scan_bwd     : reverse scan over chunks: dState -> dWrites (BF16) and the partial
+//                         gradients of the three per-head scalars (decays, mix); FP32, fixed order
+//   attn_bwd_kernel     : per (batch, chunk, head) tile recomputes S / P / O / Mem, then
+//                            dP = dlocal V^T, dV = P^T dlocal, dS = P*(dP - D)/8,
+//                            dQr = dS Kr + dmem State^T, dKr = dS^T Qr,
+//                            dtK = tU dW^T, dtU = tK dW   (write path),
+//                         and writes the packed gradient [tokens, 5d] = (dQ, dK, dV, dGate, dU)
+//                         with the RoPE transpose and the tanh / sigmoid derivatives applied --
+//                         the region the reference handles with flash-attention backward plus
+//                         its "paired backward layout" kernels (ops/backward_layout.py:114-210).
+//
+// All ten matrix products of the tile run on tcgen05 with accumulators in TMEM; one thread owns
+// one token row in every element-wise stage.
+#include "ws_ptx.cuh"
+#include "ws_api.h"
+#include "attention_common.cuh"
+
+namespace ws {
+
+extern "C" void ws_count_launch(void);
+
+// =============================================================================== dState
+constexpr int DS_SMEM = 2 * TILE_BYTES + 1024 + 128;
+
+__global__ void __launch_bounds__(128, 3)
+dstate_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_constant__ CUtensorMap tm_dy,
+              const __nv_bfloat16* __restrict__ qkvgu, const float2* __restrict__ rope,
+              float* __restrict__ dstate, int T, int H, int d, int* error_flag) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  uint8_t* sQ = smem;
+  uint8_t* sD = smem + TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * TILE_BYTES);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int n_chunks = T / CHUNK;
+  const int tile = blockIdx.x;
+  const int h = tile % H, n = (tile / H) % n_chunks, b = tile / (H * n_chunks);
+  const int row0 = b * T + n * CHUNK;
+
+  if (tid == 0) {
+    mbar_init(&bars[0], 1);
+    mbar_init(&bars[1], 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, 64);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+
+  if (tid == 0) {
+    mbar_expect_tx(&bars[0], 2 * TILE_BYTES);
+    tma_load_2d(sQ, &tm_qkvgu, &bars[0], h * HD, row0);
+    tma_load_2d(sD, &tm_dy, &bars[0], h * HD, row0);
+  }
+  bool ok = mbar_wait(&bars[0], 0, abort_flag);
+  if (ok) {
+    rope_tanh_row(sQ, tid, rope, true, false);
+    const __nv_bfloat16* gate = qkvgu + static_cast<size_t>(row0 + tid) * (5 * static_cast<size_t>(d)) + 3 * d + h * HD;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      uint4* p = reinterpret_cast<uint4*>(tile_chunk(sD, tid, j));
+      uint4 v = *p;
+      const uint4 gq = *reinterpret_cast<const uint4*>(gate + j * 8);
+      uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+      const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&gq);
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float2 dyv = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&w[t]));
+        const float2 gf = __bfloat1622float2(gb[t]);
+        w[t] = pack_bf16x2(dyv.x * (1.f - sigmoid_f(gf.x)) * 0.125f, dyv.y * (1.f - sigmoid_f(gf.y)) * 0.125f);
+      }
+      *p = v;
+    }
+  }
+  fence_proxy_async_smem();
+  __syncthreads();
+  if (tid == 0 && ok) {
+    constexpr uint32_t idesc = make_idesc_bf16(128, 64, true, true);
+#pragma unroll
+    for (int k = 0; k < CHUNK / 16; ++k)
+      umma_bf16(tmem, make_smem_desc_sw128(smem_u32(sQ) + k * 2048, 0, 1024),
+                make_smem_desc_sw128(smem_u32(sD) + k * 2048, 0, 1024), idesc, k > 0);
+    umma_commit(&bars[1]);
+  }
+  ok = ok && mbar_wait(&bars[1], 0, abort_flag);
+  tc_fence_after_sync();
+  if (warp < 2) {
+    float* out = dstate + (static_cast<size_t>(tile) * HD + tid) * HD;
+#pragma unroll
+    for (int c = 0; c < HD; c += 16) {
+      uint32_t r[16];
+      tmem_ld_32x32b_x16(tmem + (static_cast<uint32_t>(warp * 32) << 16) + c, r);
+      tmem_ld_wait();
+      if (ok) {
+#pragma unroll
+        for (int j = 0; j < 16; j += 4)
+          *reinterpret_cast<float4*>(out + c + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                               __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (tid == 0 && *abort_flag != 0 && error_flag != nullptr) atomicExch(error_flag, 4);
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, 64);
+  }
+}
+
+// =============================================================================== reverse scan
+constexpr int SCAN_MAX_CHUNKS = 64;
+
+// dstate [B,N,H,4096] FP32 (gradient of the mixed state read by chunk n), writes [B,N,H,4096] FP32
+// -> dwrites [B,N,H,4096] BF16 and partial sums [B*H*16][3] of d(fast decay), d(slow decay), d(mix).
+__global__ void __launch_bounds__(256)
+memory_scan_bwd_kernel(const float* __restrict__ dstate, const float* __restrict__ writes,
+                       const float* __restrict__ fast_logit, const float* __restrict__ slow_logit,
+                       const float* __restrict__ mix_logit, __nv_bfloat16* __restrict__ dwrites,
+                       float* __restrict__ partials, int B, int N, int H) {
+  __shared__ float red[3][8];
+  const size_t idx = blockIdx.x * static_cast<size_t>(256) + threadIdx.x;  // over B*H*4096 (exact multiple)
+  const int e = idx % 4096;
+  const int h = (idx / 4096) % H;
+  const int b = idx / (4096 * static_cast<size_t>(H));
+  const float df = 1.f / (1.f + expf(-fast_logit[h]));
+  const float ds = 1.f / (1.f + expf(-slow_logit[h]));
+  const float mix = 1.f / (1.f + expf(-mix_logit[h]));
+  float F[SCAN_MAX_CHUNKS], S[SCAN_MAX_CHUNKS];
+  float f = 0.f, s = 0.f;
+  for (int n = 0; n < N; ++n) {  // forward: state seen by chunk n
+    F[n] = f;
+    S[n] = s;
+    const float w = writes[((static_cast<size_t>(b) * N + n) * H + h) * 4096 + e];
+    f = df * f + (1.f - df) * w;
+    s = ds * s + (1.f - ds) * w;
+  }
+  float a = 0.f, bb = 0.f, g_df = 0.f, g_ds = 0.f, g_mix = 0.f;
+  for (int n = N - 1; n >= 0; --n) {
+    const size_t off = ((static_cast<size_t>(b) * N + n) * H + h) * 4096 + e;
+    dwrites[off] = __float2bfloat16_rn((1.f - df) * a + (1.f - ds) * bb);  // a, bb = grads of F_{n+1}, S_{n+1}
+    const float g = dstate[off];
+    g_mix += g * (F[n] - S[n]);
+    a = mix * g + df * a;         // gradient of F_n
+    bb = (1.f - mix) * g + ds * bb;
+    if (n > 0) {
+      const float w_prev = writes[off - static_cast<size_t>(H) * 4096];
+      g_df += a * (F[n - 1] - w_prev);
+      g_ds += bb * (S[n - 1] - w_prev);
+    }
+  }
+  // block reduction (fixed order)
+  float vals[3] = {g_df, g_ds, g_mix};
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+  for (int q = 0; q < 3; ++q) {
+    float v = vals[q];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (lane == 0) red[q][warp] = v;
+  }
+  __syncthreads();
+  if (threadIdx.x < 3) {
+    float v = 0.f;
+#pragma unroll
+    for (int wi = 0; wi < 8; ++wi) v += red[threadIdx.x][wi];
+    partials[static_cast<size_t>(blockIdx.x) * 3 + threadIdx.x] = v;
+  }
+}
+
+// =============================================================================== attention bwd
+// smem tiles (16 KiB each unless noted):
+//   sQ | sK | sV | sTK | sTU | sDL (dy -> dlocal) | sDLs (dlocal / l) | sDM (dmem/8) | sP (32K: P~ -> dS)
+//   | sSt (8K) | sDW (8K) | bars
+constexpr int AB_SMEM = 8 * TILE_BYTES + 2 * TILE_BYTES + 2 * 8192 + 1024 + 128;
+
+__global__ void __launch_bounds__(128, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_constant__ CUtensorMap tm_state,
+                const __grid_constant__ CUtensorMap tm_dy, const __grid_constant__ CUtensorMap tm_dw,
+                const __nv_bfloat16* __restrict__ qkvgu, const float2* __restrict__ rope,
+                __nv_bfloat16* __restrict__ dqkvgu, int T, int H, int d, int* error_flag) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + TILE_BYTES;
+  uint8_t* sV = sK + TILE_BYTES;
+  uint8_t* sTK = sV + TILE_BYTES;
+  uint8_t* sTU = sTK + TILE_BYTES;
+  uint8_t* sDL = sTU + TILE_BYTES;
+  uint8_t* sDLs = sDL + TILE_BYTES;
+  uint8_t* sDM = sDLs + TILE_BYTES;
+  uint8_t* sP = sDM + TILE_BYTES;
+  uint8_t* sSt = sP + 2 * TILE_BYTES;
+  uint8_t* sDW = sSt + 8192;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDW + 8192);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int n_chunks = T / CHUNK;
+  const int tile = blockIdx.x;
+  const int h = tile % H, n = (tile / H) % n_chunks, b = tile / (H * n_chunks);
+  const int row0 = b * T + n * CHUNK;
+
+  if (tid == 0) {
+    for (int i = 0; i < 5; ++i) mbar_init(&bars[i], 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t t_s = tmem;          // S, later dP            (128 cols)
+  const uint32_t t_o = tmem + 128;    // O, later dtK           (64)
+  const uint32_t t_m = tmem + 192;    // Mem, later dtU         (64)
+  const uint32_t t_dv = tmem + 256;   // dV                     (64)
+  const uint32_t t_dq = tmem + 320;   // dQr                    (64)
+  const uint32_t t_dk = tmem + 384;   // dKr (attention part)   (64)
+  const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+
+  if (tid == 0) {
+    mbar_expect_tx(&bars[0], 6 * TILE_BYTES + 2 * 8192);
+    tma_load_2d(sQ, &tm_qkvgu, &bars[0], 0 * d + h * HD, row0);
+    tma_load_2d(sK, &tm_qkvgu, &bars[0], 1 * d + h * HD, row0);
+    tma_load_2d(sV, &tm_qkvgu, &bars[0], 2 * d + h * HD, row0);
+    tma_load_2d(sTK, &tm_qkvgu, &bars[0], 1 * d + h * HD, row0);
+    tma_load_2d(sTU, &tm_qkvgu, &bars[0], 4 * d + h * HD, row0);
+    tma_load_2d(sDL, &tm_dy, &bars[0], h * HD, row0);
+    tma_load_2d(sSt, &tm_state, &bars[0], 0, tile * HD);
+    tma_load_2d(sDW, &tm_dw, &bars[0], 0, tile * HD);
+  }
+  bool ok = mbar_wait(&bars[0], 0, abort_flag);
+  if (ok) {
+    rope_tanh_row(sQ, tid, rope, true, false);
+    rope_tanh_row(sK, tid, rope, true, false);
+    rope_tanh_row(sTK, tid, rope, true, true);
+    rope_tanh_row(sTU, tid, rope, false, true);
+  }
+  fence_proxy_async_smem();
+  __syncthreads();
+  // ---- MMA 1: S = Qr Kr^T, Mem = Qr State
+  if (tid == 0 && ok) {
+    constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
+    constexpr uint32_t idesc_m = make_idesc_bf16(128, 64, false, true);
+#pragma unroll
+    for (int k = 0; k < HD / 16; ++k)
+      umma_bf16(t_s, make_smem_desc_sw128(smem_u32(sQ) + k * 32, 0, 1024),
+                make_smem_desc_sw128(smem_u32(sK) + k * 32, 0, 1024), idesc_s, k > 0);
+#pragma unroll
+    for (int k = 0; k < HD / 16; ++k)
+      umma_bf16(t_m, make_smem_desc_sw128(smem_u32(sQ) + k * 32, 0, 1024),
+                make_smem_desc_sw128(smem_u32(sSt) + k * 2048, 0, 1024), idesc_m, k > 0);
+    umma_commit(&bars[1]);
+  }
+  ok = ok && mbar_wait(&bars[1], 0, abort_flag);
+  tc_fence_after_sync();
+
+  // ---- softmax (unnormalised P~ to smem, 1/l kept in a register)
+  const float kScale = 0.125f * 1.4426950408889634f;
+  const int last_chunk = warp;
+  float row_max = -INFINITY;
+  for (int cc = 0; cc <= last_chunk; ++cc) {
+    uint32_t r[32];
+    tmem_ld_32x32b_x32(t_s + lane_base + cc * 32, r);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (cc * 32 + j <= tid) row_max = fmaxf(row_max, __uint_as_float(r[j]));
+  }
+  float row_sum = 0.f;
+  for (int cc = 0; cc < 4; ++cc) {
+    uint32_t pk[16];
+    if (cc <= last_chunk) {
+      uint32_t r[32];
+      tmem_ld_32x32b_x32(t_s + lane_base + cc * 32, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        const float p0 = (cc * 32 + j <= tid) ? exp2f((__uint_as_float(r[j]) - row_max) * kScale) : 0.f;
+        const float p1 = (cc * 32 + j + 1 <= tid) ? exp2f((__uint_as_float(r[j + 1]) - row_max) * kScale) : 0.f;
+        const __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
+        const float2 back = __bfloat1622float2(v);
+        row_sum += back.x + back.y;
+        pk[j >> 1] = *reinterpret_cast<const uint32_t*>(&v);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) pk[j] = 0u;
+    }
+    store_row_chunk32(sP, tid, cc * 32, pk);
+  }
+  const float inv_l = 1.f / row_sum;
+  tc_fence_before_sync();
+  fence_proxy_async_smem();
+  __syncthreads();
+  // ---- MMA 2: O~ = P~ V
+  if (tid == 0 && ok) {
+    tc_fence_after_sync();
+    constexpr uint32_t idesc_o = make_idesc_bf16(128, 64, false, true);
+#pragma unroll
+    for (int k = 0; k < CHUNK / 16; ++k)
+      umma_bf16(t_o, make_smem_desc_sw128(smem_u32(sP) + (k >> 2) * TILE_BYTES + (k & 3) * 32, 0, 1024),
+                make_smem_desc_sw128(smem_u32(sV) + k * 2048, 0, 1024), idesc_o, k > 0);
+    umma_commit(&bars[2]);
+  }
+  ok = ok && mbar_wait(&bars[2], 0, abort_flag);
+  tc_fence_after_sync();
+
+  // ---- element-wise stage 1: gate, dlocal, dmem, dGate, D = sum(dlocal * local)
+  const size_t grow = static_cast<size_t>(row0 + tid);
+  const __nv_bfloat16* gate = qkvgu + grow * (5 * static_cast<size_t>(d)) + 3 * d + h * HD;
+  __nv_bfloat16* dout = dqkvgu + grow * (5 * static_cast<size_t>(d)) + h * HD;
+  float Drow = 0.f;
+#pragma unroll
+  for (int c = 0; c < HD; c += 16) {
+    uint32_t ro[16], rm[16];
+    tmem_ld_32x32b_x16(t_o + lane_base + c, ro);
+    tmem_ld_32x32b_x16(t_m + lane_base + c, rm);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 16; j += 8) {
+      const int chunk = (c + j) >> 3;
+      uint4* pdl = reinterpret_cast<uint4*>(tile_chunk(sDL, tid, chunk));
+      const uint4 dyq = *pdl;
+      const uint4 gq = *reinterpret_cast<const uint4*>(gate + c + j);
+      const __nv_bfloat162* dyb = reinterpret_cast<const __nv_bfloat162*>(&dyq);
+      const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&gq);
+      uint4 o_dl, o_dls, o_dm, o_dg;
+      uint32_t* w_dl = reinterpret_cast<uint32_t*>(&o_dl);
+      uint32_t* w_dls = reinterpret_cast<uint32_t*>(&o_dls);
+      uint32_t* w_dm = reinterpret_cast<uint32_t*>(&o_dm);
+      uint32_t* w_dg = reinterpret_cast<uint32_t*>(&o_dg);
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float2 dyv = __bfloat1622float2(dyb[t]);
+        const float2 gf = __bfloat1622float2(gb[t]);
+        const float g0 = sigmoid_f(gf.x), g1 = sigmoid_f(gf.y);
+        const float l0 = __uint_as_float(ro[j + 2 * t]) * inv_l, l1 = __uint_as_float(ro[j + 2 * t + 1]) * inv_l;
+        const float m0 = __uint_as_float(rm[j + 2 * t]) * 0.125f, m1 = __uint_as_float(rm[j + 2 * t + 1]) * 0.125f;
+        const float dl0 = dyv.x * g0, dl1 = dyv.y * g1;
+        Drow += dl0 * l0 + dl1 * l1;
+        w_dl[t] = pack_bf16x2(dl0, dl1);
+        w_dls[t] = pack_bf16x2(dl0 * inv_l, dl1 * inv_l);
+        w_dm[t] = pack_bf16x2(dyv.x * (1.f - g0) * 0.125f, dyv.y * (1.f - g1) * 0.125f);
+        w_dg[t] = pack_bf16x2(dyv.x * (l0 - m0) * g0 * (1.f - g0), dyv.y * (l1 - m1) * g1 * (1.f - g1));
+      }
+      *pdl = o_dl;
+      *reinterpret_cast<uint4*>(tile_chunk(sDLs, tid, chunk)) = o_dls;
+      *reinterpret_cast<uint4*>(tile_chunk(sDM, tid, chunk)) = o_dm;
+      if (ok) *reinterpret_cast<uint4*>(dout + 3 * d + c + j) = o_dg;
+    }
+  }
+  tc_fence_before_sync();
+  fence_proxy_async_smem();
+  __syncthreads();
+  // ---- MMA 3: dP, dV, dQr(memory part), dtK, dtU
+  if (tid == 0 && ok) {
+    tc_fence_after_sync();
+    constexpr uint32_t idesc_kk128 = make_idesc_bf16(128, 128, false, false);
+    constexpr uint32_t idesc_kk64 = make_idesc_bf16(128, 64, false, false);
+    constexpr uint32_t idesc_kmn64 = make_idesc_bf16(128, 64, false, true);
+    constexpr uint32_t idesc_mnmn64 = make_idesc_bf16(128, 64, true, true);
+#pragma unroll
+    for (int k = 0; k < HD / 16; ++k)  // dP = dlocal V^T
+      umma_bf16(t_s, make_smem_desc_sw128(smem_u32(sDL) + k * 32, 0, 1024),
+                make_smem_desc_sw128(smem_u32(sV) + k * 32, 0, 1024), idesc_kk128, k > 0);
+#pragma unroll
+    for (int k = 0; k < CHUNK / 16; ++k)  // dV = P~^T (dlocal / l)
+      umma_bf16(t_dv, make_smem_desc_sw128(smem_u32(sP) + k * 2048, TILE_BYTES, 1024),
+                make_smem_desc_sw128(smem_u32(sDLs) + k * 2048, 0, 1024), idesc_mnmn64, k > 0);
+#pragma unroll
+    for (int k = 0; k < HD / 16; ++k)  // dQr = (dmem/8) State^T
+      umma_bf16(t_dq, make_smem_desc_sw128(smem_u32(sDM) + k * 32, 0, 1024),
+                make_smem_desc_sw128(smem_u32(sSt) + k * 32, 0, 1024), idesc_kk64, k > 0);
+#pragma unroll
+    for (int k = 0; k < HD / 16; ++k)  // dtK = tU dW^T
+      umma_bf16(t_o, make_smem_desc_sw128(smem_u32(sTU) + k * 32, 0, 1024),
+                make_smem_desc_sw128(smem_u32(sDW) + k * 32, 0, 1024), idesc_kk64, k > 0);
+#pragma unroll
+    for (int k = 0; k < HD / 16; ++k)  // dtU = tK dW
+      umma_bf16(t_m, make_smem_desc_sw128(smem_u32(sTK) + k * 32, 0, 1024),
+                make_smem_desc_sw128(smem_u32(sDW) + k * 2048, 0, 1024), idesc_kmn64, k > 0);
+    umma_commit(&bars[3]);
+  }
+  ok = ok && mbar_wait(&bars[3], 0, abort_flag);
+  tc_fence_after_sync();
+
+  // ---- dS = P~/l * (dP - D) / 8, written over P~
+  for (int cc = 0; cc <= last_chunk; ++cc) {
+    uint32_t r[32], pk[16];
+    tmem_ld_32x32b_x32(t_s + lane_base + cc * 32, r);
+    load_row_chunk32(sP, tid, cc * 32, pk);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float2 p = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pk[j]));
+      const float s0 = p.x * inv_l * (__uint_as_float(r[2 * j]) - Drow) * 0.125f;
+      const float s1 = p.y * inv_l * (__uint_as_float(r[2 * j + 1]) - Drow) * 0.125f;
+      pk[j] = pack_bf16x2(s0, s1);
+    }
+    store_row_chunk32(sP, tid, cc * 32, pk);
+  }
+  tc_fence_before_sync();
+  fence_proxy_async_smem();
+  __syncthreads();
+  // ---- MMA 4: dQr += dS Kr, dKr = dS^T Qr
+  if (tid == 0 && ok) {
+    tc_fence_after_sync();
+    constexpr uint32_t idesc_kmn64 = make_idesc_bf16(128, 64, false, true);
+    constexpr uint32_t idesc_mnmn64 = make_idesc_bf16(128, 64, true, true);
+#pragma unroll
+    for (int k = 0; k < CHUNK / 16; ++k)
+      umma_bf16(t_dq, make_smem_desc_sw128(smem_u32(sP) + (k >> 2) * TILE_BYTES + (k & 3) * 32, 0, 1024),
+                make_smem_desc_sw128(smem_u32(sK) + k * 2048, 0, 1024), idesc_kmn64, 1u);
+#pragma unroll
+    for (int k = 0; k < CHUNK / 16; ++k)
+      umma_bf16(t_dk, make_smem_desc_sw128(smem_u32(sP) + k * 2048, TILE_BYTES, 1024),
+                make_smem_desc_sw128(smem_u32(sQ) + k * 2048, 0, 1024), idesc_mnmn64, k > 0);
+    umma_commit(&bars[4]);
+  }
+  ok = ok && mbar_wait(&bars[4], 0, abort_flag);
+  tc_fence_after_sync();
+
+  // ---- final: dQ, dK (RoPE transpose), dV, dU
+#pragma unroll
+  for (int c = 0; c < HD; c += 16) {
+    uint32_t rq[16], rk[16], rv[16], rtk[16], rtu[16];
+    tmem_ld_32x32b_x16(t_dq + lane_base + c, rq);
+    tmem_ld_32x32b_x16(t_dk + lane_base + c, rk);
+    tmem_ld_32x32b_x16(t_dv + lane_base + c, rv);
+    tmem_ld_32x32b_x16(t_o + lane_base + c, rtk);
+    tmem_ld_32x32b_x16(t_m + lane_base + c, rtu);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 16; j += 8) {
+      const int chunk = (c + j) >> 3;
+      const uint4 tkq = *reinterpret_cast<const uint4*>(tile_chunk(sTK, tid, chunk));
+      const uint4 tuq = *reinterpret_cast<const uint4*>(tile_chunk(sTU, tid, chunk));
+      const __nv_bfloat162* tkb = reinterpret_cast<const __nv_bfloat162*>(&tkq);
+      const __nv_bfloat162* tub = reinterpret_cast<const __nv_bfloat162*>(&tuq);
+      uint4 o_q, o_k, o_v, o_u;
+      uint32_t* w_q = reinterpret_cast<uint32_t*>(&o_q);
+      uint32_t* w_k = reinterpret_cast<uint32_t*>(&o_k);
+      uint32_t* w_v = reinterpret_cast<uint32_t*>(&o_v);
+      uint32_t* w_u = reinterpret_cast<uint32_t*>(&o_u);
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const int e0 = j + 2 * t, e1 = e0 + 1;
+        const float2 cs = rope[tid * 32 + ((c + e0) >> 1)];
+        const float2 tk = __bfloat1622float2(tkb[t]);
+        const float2 tu = __bfloat1622float2(tub[t]);
+        // y0 = x0 c - x1 s ; y1 = x1 c + x0 s   =>   dx0 = dy0 c + dy1 s ; dx1 = dy1 c - dy0 s
+        const float q0 = __uint_as_float(rq[e0]), q1 = __uint_as_float(rq[e1]);
+        w_q[t] = pack_bf16x2(q0 * cs.x + q1 * cs.y, q1 * cs.x - q0 * cs.y);
+        const float k0 = __uint_as_float(rk[e0]) + __uint_as_float(rtk[e0]) * (1.f / CHUNK) * (1.f - tk.x * tk.x);
+        const float k1 = __uint_as_float(rk[e1]) + __uint_as_float(rtk[e1]) * (1.f / CHUNK) * (1.f - tk.y * tk.y);
+        w_k[t] = pack_bf16x2(k0 * cs.x + k1 * cs.y, k1 * cs.x - k0 * cs.y);
+        w_v[t] = pack_bf16x2(__uint_as_float(rv[e0]), __uint_as_float(rv[e1]));
+        w_u[t] = pack_bf16x2(__uint_as_float(rtu[e0]) * (1.f / CHUNK) * (1.f - tu.x * tu.x),
+                             __uint_as_float(rtu[e1]) * (1.f / CHUNK) * (1.f - tu.y * tu.y));
+      }
+      if (ok) {
+        *reinterpret_cast<uint4*>(dout + 0 * d + c + j) = o_q;
+        *reinterpret_cast<uint4*>(dout + 1 * d + c + j) = o_k;
+        *reinterpret_cast<uint4*>(dout + 2 * d + c + j) = o_v;
+        *reinterpret_cast<uint4*>(dout + 4 * d + c + j) = o_u;
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (tid == 0 && *abort_flag != 0 && error_flag != nullptr) atomicExch(error_flag, 5);
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+}  // namespace ws
+
+using namespace ws;
+
+extern "C" int ws_attn_dstate(const void* qkvgu, const void* dy, const float* rope, float* dstate, int B, int T,
+                              int H, int d, int* error_flag, cudaStream_t stream) {
+  if (T % CHUNK != 0 || d != H * HD) return -1;
+  CUtensorMap tm, td;
+  int rc = make_tile_map(&tm, qkvgu, 5 * (uint64_t)d, (uint64_t)B * T, 5 * (uint64_t)d, HD, CHUNK);
+  if (rc) return rc;
+  rc = make_tile_map(&td, dy, (uint64_t)d, (uint64_t)B * T, (uint64_t)d, HD, CHUNK);
+  if (rc) return rc;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(dstate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DS_SMEM) != cudaSuccess)
+      return -20;
+    configured = true;
+  }
+  const int tiles = B * (T / CHUNK) * H;
+  dstate_kernel<<<tiles, 128, DS_SMEM, stream>>>(tm, td, (const __nv_bfloat16*)qkvgu,
+                                                 reinterpret_cast<const float2*>(rope), dstate, T, H, d, error_flag);
+  ws_count_launch();
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+extern "C" int ws_memory_scan_bwd(const float* dstate, const float* writes, const float* fast_logit,
+                                  const float* slow_logit, const float* mix_logit, void* dwrites, float* partials,
+                                  int B, int N, int H, cudaStream_t stream) {
+  if (N > SCAN_MAX_CHUNKS) return -1;
+  const size_t total = (size_t)B * H * 4096;
+  memory_scan_bwd_kernel<<<(unsigned)(total / 256), 256, 0, stream>>>(dstate, writes, fast_logit, slow_logit,
+                                                                      mix_logit, (__nv_bfloat16*)dwrites, partials,
+                                                                      B, N, H);
+  ws_count_launch();
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+extern "C" int ws_attn_bwd(const void* qkvgu, const void* states, const void* dy, const void* dwrites,
+                           const float* rope, void* dqkvgu, int B, int T, int H, int d, int* error_flag,
+                           cudaStream_t stream) {
+  if (T % CHUNK != 0 || d != H * HD) return -1;
+  const int tiles = B * (T / CHUNK) * H;
+  CUtensorMap tm, ts, td, tw;
+  int rc = make_tile_map(&tm, qkvgu, 5 * (uint64_t)d, (uint64_t)B * T, 5 * (uint64_t)d, HD, CHUNK);
+  if (rc) return rc;
+  rc = make_tile_map(&ts, states, HD, (uint64_t)tiles * HD, HD, HD, HD);
+  if (rc) return rc;
+  rc = make_tile_map(&td, dy, (uint64_t)d, (uint64_t)B * T, (uint64_t)d, HD, CHUNK);
+  if (rc) return rc;
+  rc = make_tile_map(&tw, dwrites, HD, (uint64_t)tiles * HD, HD, HD, HD);
+  if (rc) return rc;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AB_SMEM) != cudaSuccess)
+      return -20;
+    configured = true;
+  }
+  attn_bwd_kernel<<<tiles, 128, AB_SMEM, stream>>>(tm, ts, td, tw, (const __nv_bfloat16*)qkvgu,
+                                                   reinterpret_cast<const float2*>(rope), (__nv_bfloat16*)dqkvgu, T,
+                                                   H, d, error_flag);
+  ws_count_launch();
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}

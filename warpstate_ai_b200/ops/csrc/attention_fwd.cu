@@ -1,0 +1,356 @@
+// Forward kernels of the middle of a WarpState core (everything between in_proj and out_proj;
+// reference math: warpstate/model.py:124-176), for chunk_size 128 and head_dim 64.
+//
+// The packed projection qkvgu [tokens, 5d] (Q,K,V,gate,U) is read in place with TMA: a tile of
+// one (batch, chunk, head) is the box rows [b*T + n*128, +128) x cols [sel*d + h*64, +64) -- the
+// reference's chunkify/permute/contiguous copies do not exist here.
+//
+//   chunk_writes_kernel : W[b,n,h] = tanh(rope(K))^T tanh(U) / 128            (tcgen05, 64x64 out)
+//   memory_scan_kernel  : state seen by chunk n = mix*F_n + (1-mix)*S_n with
+//                         F_n = d_f F_{n-1} + (1-d_f) W_{n-1}, F_0 = 0 (FP32, O(N) scan)
+//   attn_fwd_kernel     : S = rope(Q) rope(K)^T (tcgen05 -> TMEM), causal softmax by one thread
+//                         per row straight out of TMEM, O = P V and Mem = rope(Q) state (tcgen05),
+//                         y = sigmoid(g) * O/l + (1 - sigmoid(g)) * Mem/8, stored token-major.
+//
+// One thread owns one token row (= one TMEM lane): no cross-thread reductions anywhere.
+#include "ws_ptx.cuh"
+#include "ws_api.h"
+#include "attention_common.cuh"
+
+namespace ws {
+
+extern "C" void ws_count_launch(void);
+
+// =============================================================================== writes
+// smem: sK 16K | sU 16K | bars
+constexpr int WR_SMEM = 2 * TILE_BYTES + 1024 + 128;
+
+__global__ void __launch_bounds__(128, 3)
+chunk_writes_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const float2* __restrict__ rope,
+                    float* __restrict__ writes, int T, int H, int d, int* error_flag) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  uint8_t* sK = smem;
+  uint8_t* sU = smem + TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * TILE_BYTES);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int n_chunks = T / CHUNK;
+  const int tile = blockIdx.x;
+  const int h = tile % H, n = (tile / H) % n_chunks, b = tile / (H * n_chunks);
+  const int row0 = b * T + n * CHUNK;
+
+  if (tid == 0) {
+    mbar_init(&bars[0], 1);
+    mbar_init(&bars[1], 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, 64);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+
+  if (tid == 0) {
+    mbar_expect_tx(&bars[0], 2 * TILE_BYTES);
+    tma_load_2d(sK, &tm_qkvgu, &bars[0], 1 * d + h * HD, row0);
+    tma_load_2d(sU, &tm_qkvgu, &bars[0], 4 * d + h * HD, row0);
+  }
+  bool ok = mbar_wait(&bars[0], 0, abort_flag);
+  if (ok) {
+    rope_tanh_row(sK, tid, rope, true, true);    // K -> tanh(rope(K))
+    rope_tanh_row(sU, tid, rope, false, true);   // U -> tanh(U)
+  }
+  fence_proxy_async_smem();
+  __syncthreads();
+  if (tid == 0 && ok) {
+    // D[128 x 64]: rows 0..63 = tK^T tU.  A is read MN-major with a zero stride between its two
+    // 64-wide atoms, so rows 64..127 repeat rows 0..63 and are ignored.
+    constexpr uint32_t idesc = make_idesc_bf16(128, 64, true, true);
+#pragma unroll
+    for (int k = 0; k < CHUNK / 16; ++k) {
+      const uint64_t da = make_smem_desc_sw128(smem_u32(sK) + k * 2048, 0, 1024);
+      const uint64_t db = make_smem_desc_sw128(smem_u32(sU) + k * 2048, 0, 1024);
+      umma_bf16(tmem, da, db, idesc, k > 0);
+    }
+    umma_commit(&bars[1]);
+  }
+  ok = ok && mbar_wait(&bars[1], 0, abort_flag);
+  tc_fence_after_sync();
+  if (warp < 2) {  // lanes 0..63 hold the result rows
+    float* out = writes + (static_cast<size_t>(tile) * HD + tid) * HD;
+#pragma unroll
+    for (int c = 0; c < HD; c += 16) {
+      uint32_t r[16];
+      tmem_ld_32x32b_x16(tmem + (static_cast<uint32_t>(warp * 32) << 16) + c, r);
+      tmem_ld_wait();
+      if (ok) {
+#pragma unroll
+        for (int j = 0; j < 16; j += 4)
+          *reinterpret_cast<float4*>(out + c + j) =
+              make_float4(__uint_as_float(r[j]) * (1.f / CHUNK), __uint_as_float(r[j + 1]) * (1.f / CHUNK),
+                          __uint_as_float(r[j + 2]) * (1.f / CHUNK), __uint_as_float(r[j + 3]) * (1.f / CHUNK));
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (tid == 0 && *abort_flag != 0 && error_flag != nullptr) atomicExch(error_flag, 2);
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, 64);
+  }
+}
+
+// =============================================================================== scan
+// writes [B,N,H,4096] FP32 -> states [B,N,H,4096] BF16 (mixed state read by chunk n), and
+// optionally the fast / slow states after the last chunk [B,H,4096] FP32 (prefill).
+__global__ void __launch_bounds__(256)
+memory_scan_kernel(const float* __restrict__ writes, const float* __restrict__ fast_logit,
+                   const float* __restrict__ slow_logit, const float* __restrict__ mix_logit,
+                   __nv_bfloat16* __restrict__ states, float* __restrict__ final_fast,
+                   float* __restrict__ final_slow, const float* __restrict__ init_fast,
+                   const float* __restrict__ init_slow, int B, int N, int H) {
+  const size_t idx = blockIdx.x * static_cast<size_t>(256) + threadIdx.x;  // over B*H*4096
+  const size_t total = static_cast<size_t>(B) * H * 4096;
+  if (idx >= total) return;
+  const int e = idx % 4096;
+  const int h = (idx / 4096) % H;
+  const int b = idx / (4096 * static_cast<size_t>(H));
+  const float df = 1.f / (1.f + expf(-fast_logit[h]));
+  const float ds = 1.f / (1.f + expf(-slow_logit[h]));
+  const float mix = 1.f / (1.f + expf(-mix_logit[h]));
+  float f = init_fast != nullptr ? init_fast[idx] : 0.f;
+  float s = init_slow != nullptr ? init_slow[idx] : 0.f;
+  for (int n = 0; n < N; ++n) {
+    const size_t off = ((static_cast<size_t>(b) * N + n) * H + h) * 4096 + e;
+    if (states != nullptr) states[off] = __float2bfloat16_rn(mix * f + (1.f - mix) * s);
+    const float w = writes[off];
+    f = df * f + (1.f - df) * w;
+    s = ds * s + (1.f - ds) * w;
+  }
+  if (final_fast != nullptr) {
+    final_fast[idx] = f;
+    final_slow[idx] = s;
+  }
+}
+
+// =============================================================================== attention
+// smem: sQ 16K | sK 16K | sV 16K | sSt 8K | sP 32K | bars
+constexpr int AF_SMEM = 3 * TILE_BYTES + 8192 + 2 * TILE_BYTES + 1024 + 128;
+
+__global__ void __launch_bounds__(128, 2)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_constant__ CUtensorMap tm_state,
+                const __nv_bfloat16* __restrict__ qkvgu, const float2* __restrict__ rope,
+                __nv_bfloat16* __restrict__ y, int T, int H, int d, int* error_flag) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  uint8_t* sQ = smem;
+  uint8_t* sK = smem + TILE_BYTES;
+  uint8_t* sV = smem + 2 * TILE_BYTES;
+  uint8_t* sSt = smem + 3 * TILE_BYTES;
+  uint8_t* sP = smem + 3 * TILE_BYTES + 8192;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * TILE_BYTES);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int n_chunks = T / CHUNK;
+  const int tile = blockIdx.x;
+  const int h = tile % H, n = (tile / H) % n_chunks, b = tile / (H * n_chunks);
+  const int row0 = b * T + n * CHUNK;
+
+  if (tid == 0) {
+    mbar_init(&bars[0], 1);
+    mbar_init(&bars[1], 1);
+    mbar_init(&bars[2], 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t t_s = tmem, t_o = tmem + 128, t_m = tmem + 192;
+  const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+
+  if (tid == 0) {
+    mbar_expect_tx(&bars[0], 3 * TILE_BYTES + 8192);
+    tma_load_2d(sQ, &tm_qkvgu, &bars[0], 0 * d + h * HD, row0);
+    tma_load_2d(sK, &tm_qkvgu, &bars[0], 1 * d + h * HD, row0);
+    tma_load_2d(sV, &tm_qkvgu, &bars[0], 2 * d + h * HD, row0);
+    tma_load_2d(sSt, &tm_state, &bars[0], 0, tile * HD);
+  }
+  bool ok = mbar_wait(&bars[0], 0, abort_flag);
+  if (ok) {
+    rope_tanh_row(sQ, tid, rope, true, false);
+    rope_tanh_row(sK, tid, rope, true, false);
+  }
+  fence_proxy_async_smem();
+  __syncthreads();
+  if (tid == 0 && ok) {
+    constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
+    constexpr uint32_t idesc_m = make_idesc_bf16(128, 64, false, true);
+#pragma unroll
+    for (int k = 0; k < HD / 16; ++k)
+      umma_bf16(t_s, make_smem_desc_sw128(smem_u32(sQ) + k * 32, 0, 1024),
+                make_smem_desc_sw128(smem_u32(sK) + k * 32, 0, 1024), idesc_s, k > 0);
+#pragma unroll
+    for (int k = 0; k < HD / 16; ++k)
+      umma_bf16(t_m, make_smem_desc_sw128(smem_u32(sQ) + k * 32, 0, 1024),
+                make_smem_desc_sw128(smem_u32(sSt) + k * 2048, 0, 1024), idesc_m, k > 0);
+    umma_commit(&bars[1]);
+  }
+  ok = ok && mbar_wait(&bars[1], 0, abort_flag);
+  tc_fence_after_sync();
+
+  // ---- causal softmax of row `tid` (scores scaled by 1/8); P stays unnormalised
+  const float kScale = 0.125f * 1.4426950408889634f;  // fold log2(e)
+  float row_max = -INFINITY;
+  const int last_chunk = warp;  // columns beyond 32*warp+31 are masked for the whole warp
+  for (int cc = 0; cc <= last_chunk; ++cc) {
+    uint32_t r[32];
+    tmem_ld_32x32b_x32(t_s + lane_base + cc * 32, r);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (cc * 32 + j <= tid) row_max = fmaxf(row_max, __uint_as_float(r[j]));
+  }
+  float row_sum = 0.f;
+  for (int cc = 0; cc < 4; ++cc) {
+    uint32_t pk[16];
+    if (cc <= last_chunk) {
+      uint32_t r[32];
+      tmem_ld_32x32b_x32(t_s + lane_base + cc * 32, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        const float p0 = (cc * 32 + j <= tid) ? exp2f((__uint_as_float(r[j]) - row_max) * kScale) : 0.f;
+        const float p1 = (cc * 32 + j + 1 <= tid) ? exp2f((__uint_as_float(r[j + 1]) - row_max) * kScale) : 0.f;
+        const __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
+        const float2 back = __bfloat1622float2(v);
+        row_sum += back.x + back.y;  // normalise by what the MMA will actually sum
+        pk[j >> 1] = *reinterpret_cast<const uint32_t*>(&v);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) pk[j] = 0u;
+    }
+    store_row_chunk32(sP, tid, cc * 32, pk);
+  }
+  fence_proxy_async_smem();
+  __syncthreads();
+  if (tid == 0 && ok) {
+    constexpr uint32_t idesc_o = make_idesc_bf16(128, 64, false, true);
+#pragma unroll
+    for (int k = 0; k < CHUNK / 16; ++k)
+      umma_bf16(t_o, make_smem_desc_sw128(smem_u32(sP) + (k >> 2) * TILE_BYTES + (k & 3) * 32, 0, 1024),
+                make_smem_desc_sw128(smem_u32(sV) + k * 2048, 0, 1024), idesc_o, k > 0);
+    umma_commit(&bars[2]);
+  }
+  ok = ok && mbar_wait(&bars[2], 0, abort_flag);
+  tc_fence_after_sync();
+
+  // ---- gate blend and token-major store
+  const float inv_l = 1.f / row_sum;
+  const size_t grow = static_cast<size_t>(row0 + tid);
+  const __nv_bfloat16* gate = qkvgu + grow * (5 * static_cast<size_t>(d)) + 3 * d + h * HD;
+  __nv_bfloat16* yout = y + grow * d + h * HD;
+#pragma unroll
+  for (int c = 0; c < HD; c += 16) {
+    uint32_t ro[16], rm[16];
+    tmem_ld_32x32b_x16(t_o + lane_base + c, ro);
+    tmem_ld_32x32b_x16(t_m + lane_base + c, rm);
+    tmem_ld_wait();
+    if (ok) {
+#pragma unroll
+      for (int j = 0; j < 16; j += 8) {
+        const uint4 gq = *reinterpret_cast<const uint4*>(gate + c + j);
+        const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&gq);
+        uint4 out;
+        uint32_t* ow = reinterpret_cast<uint32_t*>(&out);
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float2 gf = __bfloat1622float2(gb[t]);
+          const float g0 = sigmoid_f(gf.x), g1 = sigmoid_f(gf.y);
+          const float o0 = __uint_as_float(ro[j + 2 * t]) * inv_l, o1 = __uint_as_float(ro[j + 2 * t + 1]) * inv_l;
+          const float m0 = __uint_as_float(rm[j + 2 * t]) * 0.125f, m1 = __uint_as_float(rm[j + 2 * t + 1]) * 0.125f;
+          ow[t] = pack_bf16x2(g0 * o0 + (1.f - g0) * m0, g1 * o1 + (1.f - g1) * m1);
+        }
+        *reinterpret_cast<uint4*>(yout + c + j) = out;
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (tid == 0 && *abort_flag != 0 && error_flag != nullptr) atomicExch(error_flag, 3);
+  if (warp == 0) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, 256);
+  }
+}
+
+}  // namespace ws
+
+using namespace ws;
+
+extern "C" int ws_chunk_writes(const void* qkvgu, const float* rope, float* writes, int B, int T, int H, int d,
+                               int* error_flag, cudaStream_t stream) {
+  if (T % CHUNK != 0 || d != H * HD) return -1;
+  CUtensorMap tm;
+  int rc = make_tile_map(&tm, qkvgu, 5 * (uint64_t)d, (uint64_t)B * T, 5 * (uint64_t)d, HD, CHUNK);
+  if (rc) return rc;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(chunk_writes_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WR_SMEM) != cudaSuccess)
+      return -20;
+    configured = true;
+  }
+  const int tiles = B * (T / CHUNK) * H;
+  chunk_writes_kernel<<<tiles, 128, WR_SMEM, stream>>>(tm, reinterpret_cast<const float2*>(rope), writes, T, H, d,
+                                                       error_flag);
+  ws_count_launch();
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+extern "C" int ws_memory_scan(const float* writes, const float* fast_logit, const float* slow_logit,
+                              const float* mix_logit, void* states, float* final_fast, float* final_slow,
+                              const float* init_fast, const float* init_slow, int B, int N, int H,
+                              cudaStream_t stream) {
+  const size_t total = (size_t)B * H * 4096;
+  memory_scan_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
+      writes, fast_logit, slow_logit, mix_logit, (__nv_bfloat16*)states, final_fast, final_slow, init_fast,
+      init_slow, B, N, H);
+  ws_count_launch();
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+extern "C" int ws_attn_fwd(const void* qkvgu, const void* states, const float* rope, void* y, int B, int T, int H,
+                           int d, int* error_flag, cudaStream_t stream) {
+  if (T % CHUNK != 0 || d != H * HD) return -1;
+  const int tiles = B * (T / CHUNK) * H;
+  CUtensorMap tm, ts;
+  int rc = make_tile_map(&tm, qkvgu, 5 * (uint64_t)d, (uint64_t)B * T, 5 * (uint64_t)d, HD, CHUNK);
+  if (rc) return rc;
+  rc = make_tile_map(&ts, states, HD, (uint64_t)tiles * HD, HD, HD, HD);
+  if (rc) return rc;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AF_SMEM) != cudaSuccess)
+      return -20;
+    configured = true;
+  }
+  attn_fwd_kernel<<<tiles, 128, AF_SMEM, stream>>>(tm, ts, (const __nv_bfloat16*)qkvgu,
+                                                   reinterpret_cast<const float2*>(rope), (__nv_bfloat16*)y, T, H, d,
+                                                   error_flag);
+  ws_count_launch();
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}

@@ -201,6 +201,93 @@ void embed_bwd(const at::Tensor& dx, const at::Tensor& ids, at::Tensor grad_tabl
                         n_seg, rows, d, grad_table.data_ptr<float>(), cur_stream()), "embed_bwd");
 }
 
+// ----------------------------------------------------------------------------- attention / memory
+void check_qkvgu(const at::Tensor& qkvgu, int64_t B, int64_t T, int64_t H) {
+  TORCH_CHECK(qkvgu.is_cuda() && qkvgu.scalar_type() == at::kBFloat16 && qkvgu.is_contiguous() && qkvgu.dim() == 2,
+              "attention: qkvgu must be contiguous BF16 [B*T, 5d]");
+  TORCH_CHECK(qkvgu.size(0) == B * T && qkvgu.size(1) == 5 * H * 64 && T % 128 == 0,
+              "attention: shape mismatch (chunk 128, head_dim 64)");
+}
+
+at::Tensor chunk_writes(const at::Tensor& qkvgu, const at::Tensor& rope, int64_t B, int64_t T, int64_t H,
+                        const c10::optional<at::Tensor>& error_flag) {
+  check_qkvgu(qkvgu, B, T, H);
+  TORCH_CHECK(rope.scalar_type() == at::kFloat && rope.is_contiguous() && rope.numel() == 128 * 64, "rope table");
+  c10::cuda::CUDAGuard guard(qkvgu.device());
+  at::Tensor writes = at::empty({B, T / 128, H, 64, 64}, qkvgu.options().dtype(at::kFloat));
+  check_rc(ws_chunk_writes(qkvgu.data_ptr(), rope.data_ptr<float>(), writes.data_ptr<float>(), (int)B, (int)T,
+                           (int)H, (int)(H * 64), reinterpret_cast<int*>(const_cast<void*>(opt_ptr(error_flag))),
+                           cur_stream()), "chunk_writes");
+  return writes;
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor> memory_scan(const at::Tensor& writes, const at::Tensor& fast_logit,
+                                                           const at::Tensor& slow_logit, const at::Tensor& mix_logit,
+                                                           bool want_states, bool want_final,
+                                                           const c10::optional<at::Tensor>& init_fast,
+                                                           const c10::optional<at::Tensor>& init_slow) {
+  TORCH_CHECK(writes.is_cuda() && writes.scalar_type() == at::kFloat && writes.is_contiguous() && writes.dim() == 5,
+              "memory_scan: writes must be FP32 [B,N,H,64,64]");
+  const int B = (int)writes.size(0), N = (int)writes.size(1), H = (int)writes.size(2);
+  for (const at::Tensor* t : {&fast_logit, &slow_logit, &mix_logit})
+    TORCH_CHECK(t->scalar_type() == at::kFloat && t->is_contiguous() && t->numel() == H, "memory_scan: logits");
+  c10::cuda::CUDAGuard guard(writes.device());
+  at::Tensor states = want_states ? at::empty(writes.sizes(), writes.options().dtype(at::kBFloat16)) : at::Tensor();
+  at::Tensor ff = want_final ? at::empty({B, H, 64, 64}, writes.options()) : at::Tensor();
+  at::Tensor fs = want_final ? at::empty({B, H, 64, 64}, writes.options()) : at::Tensor();
+  const float* i_f = init_fast.has_value() && init_fast->defined() ? init_fast->data_ptr<float>() : nullptr;
+  const float* i_s = init_slow.has_value() && init_slow->defined() ? init_slow->data_ptr<float>() : nullptr;
+  check_rc(ws_memory_scan(writes.data_ptr<float>(), fast_logit.data_ptr<float>(), slow_logit.data_ptr<float>(),
+                          mix_logit.data_ptr<float>(), want_states ? states.data_ptr() : nullptr,
+                          want_final ? ff.data_ptr<float>() : nullptr, want_final ? fs.data_ptr<float>() : nullptr,
+                          i_f, i_s, B, N, H, cur_stream()), "memory_scan");
+  return {states, ff, fs};
+}
+
+at::Tensor attn_fwd(const at::Tensor& qkvgu, const at::Tensor& states, const at::Tensor& rope, int64_t B, int64_t T,
+                    int64_t H, const c10::optional<at::Tensor>& error_flag) {
+  check_qkvgu(qkvgu, B, T, H);
+  TORCH_CHECK(states.scalar_type() == at::kBFloat16 && states.is_contiguous() &&
+              states.numel() == B * (T / 128) * H * 4096, "attn_fwd: states");
+  c10::cuda::CUDAGuard guard(qkvgu.device());
+  at::Tensor y = at::empty({B * T, H * 64}, qkvgu.options());
+  check_rc(ws_attn_fwd(qkvgu.data_ptr(), states.data_ptr(), rope.data_ptr<float>(), y.data_ptr(), (int)B, (int)T,
+                       (int)H, (int)(H * 64), reinterpret_cast<int*>(const_cast<void*>(opt_ptr(error_flag))),
+                       cur_stream()), "attn_fwd");
+  return y;
+}
+
+// returns (dqkvgu [M,5d] BF16, partials [B*H*16,3] FP32)
+std::tuple<at::Tensor, at::Tensor> attn_bwd(const at::Tensor& qkvgu, const at::Tensor& dy, const at::Tensor& states,
+                                            const at::Tensor& writes, const at::Tensor& rope,
+                                            const at::Tensor& fast_logit, const at::Tensor& slow_logit,
+                                            const at::Tensor& mix_logit, int64_t B, int64_t T, int64_t H,
+                                            const c10::optional<at::Tensor>& error_flag) {
+  check_qkvgu(qkvgu, B, T, H);
+  const int64_t d = H * 64, N = T / 128;
+  TORCH_CHECK(dy.is_cuda() && dy.scalar_type() == at::kBFloat16 && dy.is_contiguous() && dy.numel() == B * T * d,
+              "attn_bwd: dy must be contiguous BF16 [B*T, d]");
+  TORCH_CHECK(states.scalar_type() == at::kBFloat16 && states.is_contiguous() && states.numel() == B * N * H * 4096,
+              "attn_bwd: states");
+  TORCH_CHECK(writes.scalar_type() == at::kFloat && writes.is_contiguous() && writes.numel() == B * N * H * 4096,
+              "attn_bwd: writes");
+  TORCH_CHECK(N <= 64, "attn_bwd: at most 64 chunks per sequence");
+  c10::cuda::CUDAGuard guard(qkvgu.device());
+  int* err = reinterpret_cast<int*>(const_cast<void*>(opt_ptr(error_flag)));
+  at::Tensor dstate = at::empty({B, N, H, 64, 64}, qkvgu.options().dtype(at::kFloat));
+  check_rc(ws_attn_dstate(qkvgu.data_ptr(), dy.data_ptr(), rope.data_ptr<float>(), dstate.data_ptr<float>(), (int)B,
+                          (int)T, (int)H, (int)d, err, cur_stream()), "attn_dstate");
+  at::Tensor dwrites = at::empty({B, N, H, 64, 64}, qkvgu.options());
+  at::Tensor partials = at::empty({B * H * 16, 3}, qkvgu.options().dtype(at::kFloat));
+  check_rc(ws_memory_scan_bwd(dstate.data_ptr<float>(), writes.data_ptr<float>(), fast_logit.data_ptr<float>(),
+                              slow_logit.data_ptr<float>(), mix_logit.data_ptr<float>(), dwrites.data_ptr(),
+                              partials.data_ptr<float>(), (int)B, (int)N, (int)H, cur_stream()), "memory_scan_bwd");
+  at::Tensor dqkvgu = at::empty_like(qkvgu);
+  check_rc(ws_attn_bwd(qkvgu.data_ptr(), states.data_ptr(), dy.data_ptr(), dwrites.data_ptr(), rope.data_ptr<float>(),
+                       dqkvgu.data_ptr(), (int)B, (int)T, (int)H, (int)d, err, cur_stream()), "attn_bwd");
+  return {dqkvgu, partials};
+}
+
 // ----------------------------------------------------------------------------- optimizer
 at::Tensor grad_norm_clip(const at::Tensor& g, double max_norm, const c10::optional<at::Tensor>& extra_sumsq) {
   TORCH_CHECK(g.is_cuda() && g.scalar_type() == at::kFloat && g.is_contiguous() && g.numel() % 4 == 0,
@@ -246,6 +333,12 @@ TORCH_LIBRARY(ws_b200, m) {
   m.def("embed_fwd(Tensor ids, Tensor table, bool out_bf16) -> Tensor");
   m.def("embed_bwd(Tensor dx, Tensor ids, Tensor(a!) grad_table) -> ()");
   m.def("launch_count() -> int");
+  m.def("attn_bwd(Tensor qkvgu, Tensor dy, Tensor states, Tensor writes, Tensor rope, Tensor fast_logit, "
+        "Tensor slow_logit, Tensor mix_logit, int B, int T, int H, Tensor(a!)? error_flag) -> (Tensor, Tensor)");
+  m.def("chunk_writes(Tensor qkvgu, Tensor rope, int B, int T, int H, Tensor(a!)? error_flag) -> Tensor");
+  m.def("memory_scan(Tensor writes, Tensor fast_logit, Tensor slow_logit, Tensor mix_logit, bool want_states, "
+        "bool want_final, Tensor? init_fast, Tensor? init_slow) -> (Tensor, Tensor, Tensor)");
+  m.def("attn_fwd(Tensor qkvgu, Tensor states, Tensor rope, int B, int T, int H, Tensor(a!)? error_flag) -> Tensor");
   m.def("grad_norm_clip(Tensor g, float max_norm, Tensor? extra_sumsq) -> Tensor");
   m.def("adamw_step(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, Tensor(d!)? p_bf16, float lr, float beta1, "
         "float beta2, float eps, float wd, int step, Tensor? grad_scale, float grad_scale_const) -> ()");
@@ -267,5 +360,9 @@ TORCH_LIBRARY_IMPL(ws_b200, CUDA, m) {
   m.impl("embed_fwd", &embed_fwd);
   m.impl("embed_bwd", &embed_bwd);
   m.impl("grad_norm_clip", &grad_norm_clip);
+  m.impl("attn_bwd", &attn_bwd);
+  m.impl("chunk_writes", &chunk_writes);
+  m.impl("memory_scan", &memory_scan);
+  m.impl("attn_fwd", &attn_fwd);
   m.impl("adamw_step", &adamw_step);
 }

@@ -21,6 +21,7 @@
 // the BF16->FP32 gradient accumulation of autograd's AccumulateGrad).
 #include "ws_ptx.cuh"
 #include "ws_api.h"
+#include "ws_tma_host.h"
 
 #include <atomic>
 #include <mutex>
@@ -399,42 +400,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
 }
 
 // =============================================================================== host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
-            cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  });
-  return fn;
-}
-
-// 2-D BF16 tensor map with 128-byte swizzle: `inner` contiguous elements per row, `outer` rows,
-// row pitch `ld` elements, box = box_inner x box_outer.
-static int make_map_bf16(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer,
-                         uint64_t ld, uint32_t box_inner, uint32_t box_outer) {
-  EncodeTiledFn fn = get_encode_fn();
-  if (fn == nullptr) return -10;
-  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (ld * 2) % 16 != 0) return -11;
-  cuuint64_t dims[2] = {inner, outer};
-  cuuint64_t strides[1] = {ld * 2};
-  cuuint32_t box[2] = {box_inner, box_outer};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
-                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -12;
-}
-
 static std::atomic<long long> g_launches{0};
 static std::atomic<int> g_sm_limit{0};
 

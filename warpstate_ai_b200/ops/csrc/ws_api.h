@@ -81,6 +81,33 @@ int ws_embed_bwd(const void* dx, int dx_bf16, const long long* sorted_ids, const
                  const int* seg_start, int n_seg, int rows, int d, float* grad_table,
                  cudaStream_t stream);
 
+// ----------------------------------------------------------------------------- attention / memory
+// qkvgu: BF16 [B*T, 5d] (Q,K,V,gate,U); chunk 128, head_dim 64, d = H*64.  rope: float2 [128][32].
+// writes: FP32 [B, T/128, H, 64, 64] = tanh(rope(K))^T tanh(U) / 128.
+int ws_chunk_writes(const void* qkvgu, const float* rope, float* writes, int B, int T, int H, int d,
+                    int* error_flag, cudaStream_t stream);
+// states (BF16, may be NULL): mixed state read by each chunk; final_* (FP32 [B,H,64,64], may be NULL);
+// init_* (may be NULL) start the scan from given states.
+int ws_memory_scan(const float* writes, const float* fast_logit, const float* slow_logit,
+                   const float* mix_logit, void* states, float* final_fast, float* final_slow,
+                   const float* init_fast, const float* init_slow, int B, int N, int H,
+                   cudaStream_t stream);
+// y: BF16 [B*T, d] token-major.
+int ws_attn_fwd(const void* qkvgu, const void* states, const float* rope, void* y, int B, int T, int H,
+                int d, int* error_flag, cudaStream_t stream);
+
+// Backward of the same block.  dy: BF16 [B*T, d].  dstate: FP32 [B,N,H,64,64].
+int ws_attn_dstate(const void* qkvgu, const void* dy, const float* rope, float* dstate, int B, int T, int H,
+                   int d, int* error_flag, cudaStream_t stream);
+// dwrites: BF16 [B,N,H,64,64]; partials: FP32 [B*H*16][3] (d fast decay, d slow decay, d mix); N <= 64.
+int ws_memory_scan_bwd(const float* dstate, const float* writes, const float* fast_logit,
+                       const float* slow_logit, const float* mix_logit, void* dwrites, float* partials,
+                       int B, int N, int H, cudaStream_t stream);
+// dqkvgu: BF16 [B*T, 5d], fully written.
+int ws_attn_bwd(const void* qkvgu, const void* states, const void* dy, const void* dwrites,
+                const float* rope, void* dqkvgu, int B, int T, int H, int d, int* error_flag,
+                cudaStream_t stream);
+
 // ----------------------------------------------------------------------------- optimizer
 int ws_sumsq_parts(void);
 // stats[0] = ||g||_2, stats[1] = min(1, max_norm / (||g|| + 1e-6)), stats[2] = ||g||^2 (+ *extra_sumsq)
