@@ -1,0 +1,91 @@
+"""Kernel-level profile of one optimizer update (torch.profiler, CUDA activities).
+
+Equivalent of the reference's ``ops/benchmark_training.py --profile`` (kernel table + name-based
+categories, ops/benchmark_training.py:199-255): prints per-kernel total device time and the
+share of each category for one measured update after warm-up.  Numbers taken under the profiler
+are for *shares* only; throughput is measured by bench.py.
+
+    python -m warpstate_ai_b200.bench.profile_step --model 2b --micro-batch 8 --grad-accum 1
+"""
+from __future__ import annotations
+
+import argparse
+import json
+from collections import defaultdict
+
+import torch
+
+CATEGORIES = [
+    ("gemm", ("gemm_kernel",)),
+    ("attention", ("attn_fwd_kernel", "attn_bwd_kernel", "chunk_writes_kernel", "dstate_kernel", "memory_scan")),
+    ("lm_head", ("lmhead", "ce_")),
+    ("norm", ("rmsnorm", "colsum")),
+    ("optimizer", ("adamw_kernel", "sumsq_kernel", "clip_coef")),
+    ("embedding", ("embed_",)),
+    ("cast", ("cast_f32_bf16",)),
+    ("communication", ("nccl", "grad_reduce", "allreduce", "allgather")),
+    ("copies", ("Memcpy", "memcpy", "Memset", "memset")),
+]
+
+
+def category(name: str) -> str:
+    for cat, keys in CATEGORIES:
+        if any(k in name for k in keys):
+            return cat
+    return "other (library / eager PyTorch)"
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="2b", choices=["2b", "smoke"])
+    ap.add_argument("--micro-batch", type=int, default=8)
+    ap.add_argument("--grad-accum", type=int, default=1)
+    ap.add_argument("--seq-len", type=int, default=2048)
+    ap.add_argument("--top", type=int, default=40)
+    ap.add_argument("--out", default=None)
+    args = ap.parse_args()
+    from .. import WarpStateLM, warpstate_2b, warpstate_smoke
+    from ..data.tokens import SyntheticTokens
+    from ..train.engine import Trainer
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    cfg = warpstate_2b() if args.model == "2b" else warpstate_smoke()
+    cfg.gradient_checkpointing = False
+    torch.manual_seed(0)
+    with torch.device(device):
+        model = WarpStateLM(cfg)
+    trainer = Trainer(model, device=device)
+    tokens = args.micro_batch * args.seq_len * args.grad_accum
+    data = SyntheticTokens(tokens * 2 + 1, cfg.vocab_size)
+    for _ in range(2):
+        trainer.pretrain_update(data, 0, tokens, args.micro_batch, args.seq_len, 1e-4)
+    torch.cuda.synchronize()
+    with torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CUDA,
+                                            torch.profiler.ProfilerActivity.CPU]) as prof:
+        trainer.pretrain_update(data, 0, tokens, args.micro_batch, args.seq_len, 1e-4)
+        torch.cuda.synchronize()
+    per_kernel = defaultdict(lambda: [0.0, 0])
+    for event in prof.events():
+        if event.device_type == torch.autograd.DeviceType.CUDA:
+            per_kernel[event.name][0] += event.device_time
+            per_kernel[event.name][1] += 1
+    total = sum(v[0] for v in per_kernel.values())
+    cats = defaultdict(float)
+    for name, (us, _count) in per_kernel.items():
+        cats[category(name)] += us
+    rows = sorted(per_kernel.items(), key=lambda kv: -kv[1][0])
+    print(f"total device time {total / 1e3:.2f} ms over {sum(v[1] for v in per_kernel.values())} kernels")
+    for cat, us in sorted(cats.items(), key=lambda kv: -kv[1]):
+        print(f"  {cat:36s} {us / 1e3:9.2f} ms  {100 * us / total:5.1f} %")
+    print("top kernels:")
+    for name, (us, count) in rows[:args.top]:
+        print(f"  {us / 1e3:9.3f} ms  x{count:5d}  {name[:110]}")
+    if args.out:
+        with open(args.out, "w") as f:
+            json.dump({"total_ms": total / 1e3, "categories": {k: v / 1e3 for k, v in cats.items()},
+                       "kernels": [{"name": n, "ms": v[0] / 1e3, "count": v[1]} for n, v in rows]}, f, indent=1)
+
+
+if __name__ == "__main__":
+    main()

@@ -14,7 +14,7 @@ constexpr int TILE_BYTES = CHUNK * HD * 2;  // one [128 x 64] BF16 tile, 16 KiB
 __device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
   return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~static_cast<uintptr_t>(1023));
 }
-__device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + __expf(-x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return sigmoid_fast(x); }
 
 // Address of the 16-byte chunk `j` (8 BF16 columns) of row `r` in a [rows x 64] swizzled tile.
 __device__ __forceinline__ uint8_t* tile_chunk(uint8_t* tile, int r, int j) {
@@ -41,8 +41,8 @@ __device__ __forceinline__ void rope_tanh_row(uint8_t* tile, int r, const float2
         x.y = b;
       }
       if (do_tanh) {
-        x.x = tanhf(x.x);
-        x.y = tanhf(x.y);
+        x.x = tanh_fast(x.x);
+        x.y = tanh_fast(x.y);
       }
       w[t] = pack_bf16x2(x.x, x.y);
     }

@@ -69,7 +69,7 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int&
   nb = r / gsz;
 }
 
-__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + __expf(-x)); }
+__device__ __forceinline__ float sigmoidf_(float x) { return sigmoid_fast(x); }
 
 template <bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)

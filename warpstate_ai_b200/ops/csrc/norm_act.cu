@@ -280,7 +280,7 @@ extern "C" int ws_rmsnorm_fwd(const void* x, int x_bf16, const float* col_scale,
 // Number of partial rows ws_rmsnorm_bwd writes (the caller sizes dw_partial as parts*d floats).
 extern "C" int ws_rmsnorm_bwd_parts(int rows) {
   int blocks = (rows + ROW_WARPS - 1) / ROW_WARPS;
-  const int cap = 148 * 2;
+  const int cap = 148 * 4;
   return blocks < cap ? (blocks > 0 ? blocks : 1) : cap;
 }
 
