@@ -368,3 +368,70 @@ extern "C" int ws_embed_bwd(const void* dx, int dx_bf16, const long long* sorted
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
+
+// =============================================================================== no-allocation entry
+// RMSNorm backward whose partial-sum scratch is part of the library image (see
+// ws_static_scratch.h for who needs this and for the sharing rules).
+#include "ws_static_scratch.h"
+#include <mutex>
+
+// Lives in every GPU that loads this library until the process exits.  In host code this name is
+// only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) float g_static_scratch[WS_STATIC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_scratch_addr[kMaxDevices] = {};
+std::mutex g_scratch_mutex;
+
+// Device address of the scratch array on the current device, looked up once per device.
+int static_scratch_for_current_device(float** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return WS_STATIC_ERR_SYMBOL;
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (g_scratch_addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || ptr == nullptr) return WS_STATIC_ERR_SYMBOL;
+    g_scratch_addr[dev] = static_cast<float*>(ptr);
+  }
+  *out = g_scratch_addr[dev];
+  return 0;
+}
+}  // namespace
+
+extern "C" const char* ws_static_scratch_strerror(int code) {
+  switch (code) {
+    case 0: return "success";
+    case WS_STATIC_ERR_BAD_SHAPE: return "rows must be positive and d a multiple of 128 not above 2048";
+    case WS_STATIC_ERR_LAUNCH: return "kernel launch failed";
+    case WS_STATIC_ERR_TOO_LARGE: return "problem needs more partial sums than the built-in scratch array holds "
+                                         "(blocks(rows) * d > WS_STATIC_SCRATCH_FLOATS)";
+    case WS_STATIC_ERR_SYMBOL: return "could not resolve the device address of the built-in scratch array";
+    default: return "unknown error";
+  }
+}
+
+extern "C" int ws_rmsnorm_bwd_static(const void* dz, const void* x, int x_bf16, const float* rstd, const float* w,
+                                     const void* dres, const float* out_scale, int rows, int d, void* dx_out,
+                                     void* dx_bf16, float* dw_out, cudaStream_t stream) {
+  if (d % 128 != 0 || d > 128 * MAX_CHUNKS || rows <= 0) return WS_STATIC_ERR_BAD_SHAPE;
+  const int parts = ws_rmsnorm_bwd_parts(rows);
+  if (static_cast<long long>(parts) * d > static_cast<long long>(WS_STATIC_SCRATCH_FLOATS)) return WS_STATIC_ERR_TOO_LARGE;
+  float* scratch = nullptr;
+  const int rc = static_scratch_for_current_device(&scratch);
+  if (rc != 0) return rc;
+  // Every partial row that the reduction reads below is written by the kernel first, so the
+  // previous call's contents never leak into this result.
+  if (x_bf16)
+    rmsnorm_bwd_kernel<__nv_bfloat16><<<parts, ROW_THREADS, 0, stream>>>(
+        (const __nv_bfloat16*)dz, (const __nv_bfloat16*)x, rstd, w, (const __nv_bfloat16*)dres, out_scale,
+        rows, d, (__nv_bfloat16*)dx_out, (__nv_bfloat16*)dx_bf16, scratch);
+  else
+    rmsnorm_bwd_kernel<float><<<parts, ROW_THREADS, 0, stream>>>(
+        (const __nv_bfloat16*)dz, (const float*)x, rstd, w, (const float*)dres, out_scale, rows, d,
+        (float*)dx_out, (__nv_bfloat16*)dx_bf16, scratch);
+  ws_count_launch();
+  colsum_finalize_kernel<<<(d + 255) / 256, 256, 0, stream>>>(scratch, parts, d, nullptr, 0.f, dw_out);
+  ws_count_launch();
+  return cudaGetLastError() == cudaSuccess ? 0 : WS_STATIC_ERR_LAUNCH;
+}
