@@ -1,0 +1,186 @@
+"""Data-parallel gradient synchronisation.
+
+The file doubles as the worker (the reference's pattern, test_distributed_execution.py:78-177):
+the test spawns ranks as child processes with a file-store rendezvous, each rank writes a JSON
+report, the parent asserts on the reports.
+
+* CPU (gloo, 2 ranks): two-rank training with `CollectiveGradSync` equals single-process
+  training on the concatenated batch (the global token-mean objective), including an update in
+  which one rank has no valid tokens.
+* GPU (2 ranks, needs two devices): the in-kernel all-reduce over symmetric memory equals
+  NCCL all_reduce / world on random buffers (peer-load path and, when offered, the multimem
+  path), and two-rank training with the fused synchroniser equals the NCCL synchroniser.
+"""
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def spawn(mode: str, world: int, tmp_path: Path, env_extra=None, timeout=240):
+    env = dict(os.environ)
+    env.update(env_extra or {})
+    env["PYTHONPATH"] = str(ROOT) + os.pathsep + env.get("PYTHONPATH", "")
+    procs = []
+    for rank in range(world):
+        procs.append(subprocess.Popen([sys.executable, __file__, mode, str(rank), str(world), str(tmp_path)],
+                                      env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    outputs = []
+    for p in procs:
+        try:
+            out, _ = p.communicate(timeout=timeout)
+        except subprocess.TimeoutExpired:
+            for q in procs:
+                q.kill()
+            raise
+        outputs.append(out)
+    for rank, p in enumerate(procs):
+        assert p.returncode == 0, f"rank {rank} failed:\n{outputs[rank][-3000:]}"
+    return [json.loads((tmp_path / f"report-{rank}.json").read_text()) for rank in range(world)]
+
+
+def tiny_model(device):
+    from warpstate_ai_b200 import WarpStateConfig, WarpStateLM
+    torch.manual_seed(0)
+    cfg = WarpStateConfig(vocab_size=128, d_model=256 if device.type == "cuda" else 32, n_heads=4, n_cores=2,
+                          logical_depth=2, ffn_hidden=256 if device.type == "cuda" else 48,
+                          chunk_size=128 if device.type == "cuda" else 8, gradient_checkpointing=False,
+                          parallel_memory=True)
+    return WarpStateLM(cfg).to(device), cfg
+
+
+def run_updates(trainer, cfg, world, rank, seq, micro_batch, targets):
+    from warpstate_ai_b200.data.tokens import SyntheticTokens
+    data = SyntheticTokens(4096, cfg.vocab_size, seed=3)
+    losses = []
+    cursor = 0
+    for target in targets:
+        result = trainer.pretrain_update(data, cursor, target, micro_batch, seq, 1e-3)
+        losses.append(result.loss)
+        cursor += target
+    return losses
+
+
+def worker(mode: str, rank: int, world: int, out_dir: Path) -> None:
+    import torch.distributed as dist
+    from warpstate_ai_b200.train.engine import Trainer
+    cuda = mode.startswith("gpu")
+    if cuda:
+        torch.cuda.set_device(rank)
+        device = torch.device("cuda", rank)
+    else:
+        device = torch.device("cpu")
+    dist.init_process_group("nccl" if cuda else "gloo", init_method=(out_dir / "rendezvous").as_uri(),
+                            rank=rank, world_size=world, **({"device_id": device} if cuda else {}))
+    report = {}
+    seq = 256 if cuda else 16
+    mb = 2
+    if mode in ("cpu_train", "gpu_train"):
+        from warpstate_ai_b200.parallel.grad_sync import CollectiveGradSync, FusedGradSync
+        kinds = ["collective", "fused"] if cuda else ["collective"]
+        # 2 full updates, then one where the second rank's slice is empty
+        targets = [world * mb * seq * 2, world * mb * seq * 2, mb * seq]
+        for kind in kinds:
+            model, cfg = tiny_model(device)
+            sync = (FusedGradSync(device, world, rank, budget_seconds=20.0) if kind == "fused"
+                    else CollectiveGradSync(device, world, rank))
+            trainer = Trainer(model, device=device, rank=rank, world_size=world, lr=1e-3, weight_decay=0.1,
+                              grad_sync=sync)
+            losses = run_updates(trainer, cfg, world, rank, seq, mb, targets)
+            flat = trainer.arena.master.detach().float().cpu()
+            report[kind] = {"losses": losses, "checksum": float(flat.double().sum()), "norm": float(flat.norm()),
+                            "sync": sync.kind}
+            torch.save(flat, out_dir / f"params-{kind}-{rank}.pt")
+            dist.barrier()
+    elif mode == "gpu_kernel":
+        from warpstate_ai_b200.ops import _ext
+        from warpstate_ai_b200.parallel import symm
+        _ext.require()
+        n = 3 * 1024 * 1024 + 256
+        torch.manual_seed(100 + rank)
+        for use_nvls in (False, True):
+            buf = symm.allocate(n, torch.float32, device)
+            flags = symm.allocate(64, torch.int32, device)
+            mc = buf.multicast_ptr if use_nvls else 0
+            if use_nvls and not mc:
+                report["nvls"] = "unavailable"
+                continue
+            status = torch.zeros(8, dtype=torch.int32, device=device)
+            worst = 0.0
+            for seq_no in (1, 2):
+                src = torch.randn(n, device=device)
+                buf.tensor.copy_(src)
+                want = src.clone()
+                dist.all_reduce(want)
+                want /= world
+                torch.cuda.synchronize()
+                dist.barrier()
+                torch.ops.ws_b200.grad_allreduce(buf.peer_ptrs, flags.peer_ptrs, mc, rank, world, 256, n - 256, 0,
+                                                 seq_no, 1.0 / world, True, 16, None, status, 20.0)
+                torch.cuda.synchronize()
+                dist.barrier()
+                assert int(status[0]) == 0, status.tolist()
+                assert torch.equal(buf.tensor[:256], src[:256])  # outside the bucket: untouched
+                err = float((buf.tensor[256:] - want[256:]).abs().max())
+                worst = max(worst, err)
+                gathered = [torch.empty_like(buf.tensor) for _ in range(world)]
+                dist.all_gather(gathered, buf.tensor)
+                assert all(torch.equal(gathered[0][256:], g[256:]) for g in gathered)  # bit-identical on every rank
+            report["nvls" if use_nvls else "p2p"] = worst
+    (out_dir / f"report-{rank}.json").write_text(json.dumps(report))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+# ----------------------------------------------------------------------------------- tests
+def test_two_cpu_ranks_match_single_process(tmp_path):
+    reports = spawn("cpu_train", 2, tmp_path, env_extra={"CUDA_VISIBLE_DEVICES": ""})
+    a = torch.load(tmp_path / "params-collective-0.pt")
+    b = torch.load(tmp_path / "params-collective-1.pt")
+    assert torch.equal(a, b)
+    assert reports[0]["collective"]["losses"] == pytest.approx(reports[1]["collective"]["losses"], rel=1e-6)
+    # single process over the same global batches
+    from warpstate_ai_b200.train.engine import Trainer
+    device = torch.device("cpu")
+    model, cfg = tiny_model(device)
+    trainer = Trainer(model, device=device, lr=1e-3, weight_decay=0.1)
+    losses = run_updates(trainer, cfg, 1, 0, 16, 2, [2 * 2 * 16 * 2, 2 * 2 * 16 * 2, 2 * 16])
+    assert losses == pytest.approx(reports[0]["collective"]["losses"], rel=2e-5, abs=2e-6)
+    assert torch.allclose(trainer.arena.master.detach().cpu(), a, rtol=1e-4, atol=2e-6)
+
+
+needs_two_gpus = pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2,
+                                    reason="needs two CUDA devices")
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+@needs_two_gpus
+def test_fused_allreduce_kernel_matches_nccl(tmp_path):
+    reports = spawn("gpu_kernel", 2, tmp_path)
+    for r in reports:
+        assert r["p2p"] < 1e-6
+        assert r["nvls"] == "unavailable" or r["nvls"] < 1e-5
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+@needs_two_gpus
+def test_fused_sync_training_matches_nccl_sync(tmp_path):
+    reports = spawn("gpu_train", 2, tmp_path)
+    for kind in ("collective", "fused"):
+        assert torch.equal(torch.load(tmp_path / f"params-{kind}-0.pt"), torch.load(tmp_path / f"params-{kind}-1.pt"))
+    a = torch.load(tmp_path / "params-collective-0.pt")
+    b = torch.load(tmp_path / "params-fused-0.pt")
+    assert torch.allclose(a, b, rtol=1e-3, atol=2e-5)
+    assert reports[0]["fused"]["losses"] == pytest.approx(reports[0]["collective"]["losses"], rel=1e-3)
+
+
+if __name__ == "__main__":
+    worker(sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), Path(sys.argv[4]))

@@ -323,6 +323,55 @@ void adamw_step(at::Tensor p, const at::Tensor& g, at::Tensor m, at::Tensor v, c
 
 int64_t launch_count() { return (int64_t)ws_launch_count(); }
 
+// ----------------------------------------------------------------------------- communication
+std::vector<unsigned long long> ptr_table(at::IntArrayRef v) {
+  std::vector<unsigned long long> out;
+  for (int64_t p : v) out.push_back(static_cast<unsigned long long>(p));
+  return out;
+}
+
+void grad_allreduce(at::IntArrayRef grad_ptrs, at::IntArrayRef flag_ptrs, int64_t mc_grad, int64_t rank,
+                    int64_t world, int64_t start, int64_t count, int64_t bucket, int64_t seq, double scale, bool push,
+                    int64_t ctas, c10::optional<at::Tensor> sumsq_out, at::Tensor status, double budget_seconds) {
+  TORCH_CHECK((int64_t)grad_ptrs.size() == world && (int64_t)flag_ptrs.size() == world, "grad_allreduce: peer tables");
+  TORCH_CHECK(status.is_cuda() && status.scalar_type() == at::kInt && status.numel() >= 8, "grad_allreduce: status");
+  c10::cuda::CUDAGuard guard(status.device());
+  float* ss = nullptr;
+  if (sumsq_out.has_value() && sumsq_out->defined()) {
+    TORCH_CHECK(sumsq_out->scalar_type() == at::kFloat && sumsq_out->numel() >= ctas, "grad_allreduce: sumsq_out");
+    ss = sumsq_out->data_ptr<float>();
+  }
+  auto g = ptr_table(grad_ptrs), f = ptr_table(flag_ptrs);
+  check_rc(ws_grad_allreduce(g.data(), f.data(), (unsigned long long)mc_grad, (int)rank, (int)world, (size_t)start,
+                             (size_t)count, (int)bucket, (unsigned)seq, (float)scale, push ? 1 : 0, (int)ctas, ss,
+                             status.data_ptr<int>(), budget_seconds, cur_stream()), "grad_allreduce");
+}
+
+void wait_probe(const at::Tensor& flag, int64_t expected, at::Tensor status, double budget_seconds) {
+  TORCH_CHECK(flag.is_cuda() && flag.scalar_type() == at::kInt && status.scalar_type() == at::kInt &&
+              status.numel() >= 8, "wait_probe: int32 CUDA tensors required");
+  c10::cuda::CUDAGuard guard(flag.device());
+  check_rc(ws_wait_probe(reinterpret_cast<const unsigned*>(flag.data_ptr<int>()), (unsigned)expected,
+                         status.data_ptr<int>(), budget_seconds, cur_stream()), "wait_probe");
+}
+
+void adamw_shard_push(at::IntArrayRef master_ptrs, at::IntArrayRef bf16_ptrs, int64_t rank, int64_t world,
+                      const at::Tensor& g, at::Tensor m, at::Tensor v, int64_t lo, int64_t n, double lr, double beta1,
+                      double beta2, double eps, double wd, int64_t step, const c10::optional<at::Tensor>& grad_scale,
+                      bool push_master) {
+  TORCH_CHECK((int64_t)master_ptrs.size() == world && (int64_t)bf16_ptrs.size() == world, "adamw_shard_push: tables");
+  TORCH_CHECK(g.is_cuda() && g.scalar_type() == at::kFloat && g.is_contiguous() && g.numel() >= lo + n, "adamw_shard_push: g");
+  TORCH_CHECK(m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat && m.numel() == n && v.numel() == n &&
+              m.is_contiguous() && v.is_contiguous(), "adamw_shard_push: moments");
+  c10::cuda::CUDAGuard guard(g.device());
+  auto mp = ptr_table(master_ptrs), bp = ptr_table(bf16_ptrs);
+  const float* gs = grad_scale.has_value() && grad_scale->defined() ? grad_scale->data_ptr<float>() : nullptr;
+  check_rc(ws_adamw_shard_push(mp.data(), bp.data(), (int)rank, (int)world, g.data_ptr<float>(), m.data_ptr<float>(),
+                               v.data_ptr<float>(), (size_t)lo, (size_t)n, (float)lr, (float)beta1, (float)beta2,
+                               (float)eps, (float)wd, (int)step, gs, push_master ? 1 : 0, cur_stream()),
+           "adamw_shard_push");
+}
+
 }  // namespace
 
 TORCH_LIBRARY(ws_b200, m) {
@@ -333,6 +382,13 @@ TORCH_LIBRARY(ws_b200, m) {
   m.def("embed_fwd(Tensor ids, Tensor table, bool out_bf16) -> Tensor");
   m.def("embed_bwd(Tensor dx, Tensor ids, Tensor(a!) grad_table) -> ()");
   m.def("launch_count() -> int");
+  m.def("grad_allreduce(int[] grad_ptrs, int[] flag_ptrs, int mc_grad, int rank, int world, int start, int count, "
+        "int bucket, int seq, float scale, bool push, int ctas, Tensor(a!)? sumsq_out, Tensor(b!) status, "
+        "float budget_seconds) -> ()");
+  m.def("wait_probe(Tensor flag, int expected, Tensor(a!) status, float budget_seconds) -> ()");
+  m.def("adamw_shard_push(int[] master_ptrs, int[] bf16_ptrs, int rank, int world, Tensor g, Tensor(a!) m, "
+        "Tensor(b!) v, int lo, int n, float lr, float beta1, float beta2, float eps, float wd, int step, "
+        "Tensor? grad_scale, bool push_master) -> ()");
   m.def("attn_bwd(Tensor qkvgu, Tensor dy, Tensor states, Tensor writes, Tensor rope, Tensor fast_logit, "
         "Tensor slow_logit, Tensor mix_logit, int B, int T, int H, Tensor(a!)? error_flag) -> (Tensor, Tensor)");
   m.def("chunk_writes(Tensor qkvgu, Tensor rope, int B, int T, int H, Tensor(a!)? error_flag) -> Tensor");
@@ -365,4 +421,7 @@ TORCH_LIBRARY_IMPL(ws_b200, CUDA, m) {
   m.impl("memory_scan", &memory_scan);
   m.impl("attn_fwd", &attn_fwd);
   m.impl("adamw_step", &adamw_step);
+  m.impl("grad_allreduce", &grad_allreduce);
+  m.impl("wait_probe", &wait_probe);
+  m.impl("adamw_shard_push", &adamw_shard_push);
 }

@@ -119,6 +119,29 @@ int ws_adamw(float* p, const float* g, float* m, float* v, void* p_bf16, size_t 
              float beta2, float eps, float wd, int step, const float* grad_scale_ptr,
              float grad_scale_const, cudaStream_t stream);
 
+// ----------------------------------------------------------------------------- communication
+// Peer tables are arrays of `world` (<= 8) device addresses valid in THIS process: its mappings
+// of every rank's buffer, own rank included.  Flag buffers hold ws_comm_flag_words(buckets)
+// zero-initialised 32-bit words per rank.  status: 8 ints on the device, 0 = no error.
+int ws_comm_flag_words(int buckets);
+int ws_comm_max_ctas(void);
+// In-place all-reduce (push = 1) or reduce-scatter (push = 0) of grad[start, start+count) with
+// the result scaled by `scale`; mc_grad is the multimem address of the arena or 0.
+// sumsq_out (may be NULL) receives `ctas` partial sums of squares of this rank's reduced slice.
+int ws_grad_allreduce(const unsigned long long* grad_ptrs, const unsigned long long* flag_ptrs,
+                      unsigned long long mc_grad, int rank, int world, size_t start, size_t count, int bucket,
+                      unsigned seq, float scale, int push, int ctas, float* sumsq_out, int* status,
+                      double budget_seconds, cudaStream_t stream);
+// Waits (bounded) for *flag >= expected and reports expiry through `status` like the kernels do.
+int ws_wait_probe(const unsigned* flag, unsigned expected, int* status, double budget_seconds,
+                  cudaStream_t stream);
+// AdamW on arena elements [lo, lo+n) owned by this rank; m, v are the rank's shard-local moments;
+// updated BF16 weights (and FP32 masters when push_master) are stored to every rank.
+int ws_adamw_shard_push(const unsigned long long* master_ptrs, const unsigned long long* bf16_ptrs, int rank,
+                        int world, const float* g, float* m, float* v, size_t lo, size_t n, float lr,
+                        float beta1, float beta2, float eps, float wd, int step, const float* grad_scale_ptr,
+                        int push_master, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -64,6 +64,16 @@ def _ops():
     return torch.ops.ws_b200
 
 
+_core_grad_hook = None
+
+
+def set_core_grad_hook(fn) -> None:
+    """``fn(core)`` is called when a core's weight gradients are final for this backward pass
+    (used by the gradient synchroniser to start reducing that core's bucket early)."""
+    global _core_grad_hook
+    _core_grad_hook = fn
+
+
 # --------------------------------------------------------------------------- BF16 weight views
 def bf16_weight(p: torch.Tensor) -> torch.Tensor:
     """BF16 copy of an FP32 master weight.
@@ -128,7 +138,7 @@ def _attention_backward(dy: torch.Tensor, qkvgu: torch.Tensor, saved, core, batc
 class CoreFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, depth_scale, depth_bias, n1w, w_in, w_out, n2w, w_ug, w_down, fast_logit,
-                slow_logit, mix_logit, core):
+                slow_logit, mix_logit, core, notify=True):
         ops = _ops()
         batch, seq, d = x.shape
         m = batch * seq
@@ -146,6 +156,7 @@ class CoreFn(torch.autograd.Function):
         packed, act = G.linear_swiglu(z2, bf16_weight(w_ug))
         x3 = G.linear_residual(act, bf16_weight(w_down), x2)
         ctx.core = core
+        ctx.notify = notify
         ctx.dims = (batch, seq, d)
         ctx.has_mod = has_mod
         ctx.attn_saved = attn_saved
@@ -187,17 +198,35 @@ class CoreFn(torch.autograd.Function):
         if ctx.has_mod:
             # d bias = colsum(d x_mod), d scale = colsum(d x_mod * x_in), with d x_mod = dx_in / (1+scale)
             g_bias, g_scale = ops.colsum2(dx_in, x_in, scale)
+        if ctx.notify and _core_grad_hook is not None:
+            _attach_small_grads(core, g_n1, g_n2, g_fast, g_slow, g_mix)
+            _core_grad_hook(core)
+            g_n1 = g_n2 = g_fast = g_slow = g_mix = None
         return (dx_in.view(batch, seq, d), g_scale, g_bias, g_n1, g_in, g_out, g_n2, g_ug, g_down,
-                g_fast, g_slow, g_mix, None)
+                g_fast, g_slow, g_mix, None, None)
 
 
-def core_forward(core, x: torch.Tensor, depth_scale=None, depth_bias=None) -> torch.Tensor:
+def _attach_small_grads(core, g_n1, g_n2, g_fast, g_slow, g_mix) -> None:
+    """Add the core's small-parameter gradients to the arena now (instead of letting autograd do
+    it after this node returns) so that the whole bucket is final when the hook fires."""
+    pairs = ((core.norm1.weight, g_n1), (core.norm2.weight, g_n2), (core.fast_decay_logit, g_fast),
+             (core.slow_decay_logit, g_slow), (core.memory_mix_logit, g_mix))
+    for p, g in pairs:
+        if g is None:
+            continue
+        main = getattr(p, "main_grad", None)
+        if main is None:
+            raise RuntimeError("core gradient hook requires parameters bound to a ParamArena")
+        main.add_(g.to(main.dtype))
+
+
+def core_forward(core, x: torch.Tensor, depth_scale=None, depth_bias=None, notify: bool = True) -> torch.Tensor:
     if x.dtype not in (torch.float32, torch.bfloat16):
         x = x.float()
     return CoreFn.apply(x, depth_scale, depth_bias, core.norm1.weight, core.in_proj.weight,
                         core.out_proj.weight, core.norm2.weight, core.ffn.up_gate.weight,
                         core.ffn.down.weight, core.fast_decay_logit, core.slow_decay_logit,
-                        core.memory_mix_logit, core)
+                        core.memory_mix_logit, core, notify)
 
 
 # --------------------------------------------------------------------------- embedding / final norm
@@ -252,7 +281,8 @@ def trunk_forward(model, input_ids: torch.Tensor) -> torch.Tensor:
     x = EmbedFn.apply(input_ids, model.embed.weight)
     for depth in range(cfg.logical_depth):
         core = model.cores[depth % cfg.n_cores]
-        x = core_forward(core, x, model.depth_scale[depth], model.depth_bias[depth])
+        # the first forward use of a (possibly shared) core is its last use in backward
+        x = core_forward(core, x, model.depth_scale[depth], model.depth_bias[depth], notify=depth < cfg.n_cores)
     return NormFn.apply(x, model.final_norm.weight, cfg.rms_eps)
 
 

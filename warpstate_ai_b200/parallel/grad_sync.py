@@ -1,0 +1,186 @@
+"""Gradient synchronisation for replicated data parallelism.
+
+Contract (what the reference gets from DistributedDataParallel with ``no_sync`` on all but the
+last micro-batch, FP32 buckets averaged over ranks; reference run_40b.py:601-603,742 and
+ops/distributed_execution.py:16-79): after `finish_update()` every rank's gradient arena holds
+the rank-average of the accumulated FP32 gradients, bit-identical on all ranks.
+
+Two implementations:
+
+* `FusedGradSync`   -- the product path.  The gradient arena lives in symmetric memory; each
+  bucket (one per core, plus a tail bucket with embedding / depth modulation / final norm) is
+  reduced by ONE kernel (`grad_allreduce_kernel`, ops/csrc/comm.cu) that pulls the rank's slice
+  from all peers over NVLink (or reduces it in the switch with multimem), applies the 1/world
+  scale and pushes the result to all peers.  Buckets are launched on a side stream as soon as the
+  last micro-batch's backward has finished the corresponding core, so the transfer overlaps the
+  remaining backward GEMMs.
+* `CollectiveGradSync` -- the baseline and oracle: `torch.distributed.all_reduce` per bucket
+  (NCCL on CUDA, gloo on CPU).
+"""
+from __future__ import annotations
+
+import contextlib
+import os
+
+import torch
+import torch.distributed as dist
+
+
+class GradSyncBase:
+    kind = "none"
+
+    def __init__(self, device: torch.device, world: int, rank: int, group=None):
+        self.device, self.world, self.rank, self.group = device, world, rank, group
+        self.arena = None
+        self.core_bucket: dict[int, int] = {}
+        self.reduced: set[int] = set()
+        self.seq = 0
+
+    # ---- hooks used by the trainer
+    def alloc_grad_buffer(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        return torch.zeros(numel, dtype=dtype, device=self.device)
+
+    def attach(self, arena, model) -> None:
+        self.arena = arena
+        self.model = model
+        for bucket in arena.buckets:
+            cores = {int(n.split(".")[1]) for n in bucket.names if n.startswith("cores.")}
+            if len(cores) == 1 and all(n.startswith("cores.") for n in bucket.names):
+                self.core_bucket[cores.pop()] = bucket.index
+        self.core_index = {id(core): i for i, core in enumerate(getattr(model, "cores", []))}
+
+    def begin_update(self) -> None:
+        self.seq += 1
+        self.reduced.clear()
+
+    @contextlib.contextmanager
+    def last_micro_batch(self):
+        from ..ops import fused
+        fused.set_core_grad_hook(self._core_done)
+        try:
+            yield
+        finally:
+            fused.set_core_grad_hook(None)
+
+    def _core_done(self, core) -> None:
+        index = self.core_index.get(id(core))
+        bucket = self.core_bucket.get(index)
+        if bucket is not None and bucket not in self.reduced:
+            self.reduce_bucket(bucket)
+
+    def finish_update(self):
+        for bucket in reversed(range(len(self.arena.buckets))):
+            if bucket not in self.reduced:
+                self.reduce_bucket(bucket)
+        self.wait()
+        return None
+
+    def reduce_scalar(self, t: torch.Tensor) -> None:
+        if self.world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+
+    def status_word(self):
+        return None
+
+    # ---- implemented by subclasses
+    def reduce_bucket(self, bucket: int) -> None:
+        raise NotImplementedError
+
+    def wait(self) -> None:
+        pass
+
+
+class CollectiveGradSync(GradSyncBase):
+    """all_reduce(SUM) / world per bucket through torch.distributed (NCCL or gloo)."""
+
+    def __init__(self, device, world, rank, group=None):
+        super().__init__(device, world, rank, group)
+        self.kind = "nccl" if device.type == "cuda" else "gloo"
+        self.stream = torch.cuda.Stream(device=device) if device.type == "cuda" else None
+        self.pending = []
+
+    def reduce_bucket(self, bucket: int) -> None:
+        b = self.arena.buckets[bucket]
+        view = self.arena.grad[b.start:b.stop]
+        self.reduced.add(bucket)
+        if self.stream is None:
+            dist.all_reduce(view, op=dist.ReduceOp.SUM, group=self.group)
+            view.mul_(1.0 / self.world)
+            return
+        self.stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(self.stream):
+            dist.all_reduce(view, op=dist.ReduceOp.SUM, group=self.group)
+            view.mul_(1.0 / self.world)
+
+    def wait(self) -> None:
+        if self.stream is not None:
+            torch.cuda.current_stream(self.device).wait_stream(self.stream)
+
+
+class FusedGradSync(GradSyncBase):
+    """One in-kernel all-reduce per bucket over symmetric memory (NVLink peer access / NVLS)."""
+
+    kind = "fused"
+
+    def __init__(self, device, world, rank, group=None, ctas: int | None = None, budget_seconds: float | None = None,
+                 use_nvls: bool | None = None):
+        super().__init__(device, world, rank, group)
+        from ..ops import _ext
+        _ext.require()
+        self.ctas = int(ctas or os.environ.get("WARPSTATE_COMM_CTAS", 32))
+        self.budget = float(budget_seconds or os.environ.get("WARPSTATE_COMM_WAIT_SECONDS", 20.0))
+        self.use_nvls = use_nvls
+        self.stream = torch.cuda.Stream(device=device)
+        self.grad_sym = None
+        self.flag_sym = None
+        self.status = torch.zeros(8, dtype=torch.int32, device=device)
+
+    def alloc_grad_buffer(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        from . import symm
+        self.grad_sym = symm.allocate(numel, dtype, self.device, self.group)
+        return self.grad_sym.tensor
+
+    def attach(self, arena, model) -> None:
+        super().attach(arena, model)
+        from . import symm
+        words = 2 * 8 * len(arena.buckets)
+        self.flag_sym = symm.allocate(max(words, 64), torch.int32, self.device, self.group)
+        mc = self.grad_sym.multicast_ptr
+        if self.use_nvls is False:
+            mc = 0
+        self.mc_ptr = mc
+        self.kind = "fused-nvls" if mc else "fused-p2p"
+        self.flag_sym.barrier()
+
+    def reduce_bucket(self, bucket: int) -> None:
+        b = self.arena.buckets[bucket]
+        self.reduced.add(bucket)
+        self.stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(self.stream):
+            torch.ops.ws_b200.grad_allreduce(self.grad_sym.peer_ptrs, self.flag_sym.peer_ptrs, self.mc_ptr, self.rank,
+                                             self.world, b.start, b.stop - b.start, bucket, self.seq,
+                                             1.0 / self.world, True, self.ctas, None, self.status, self.budget)
+
+    def wait(self) -> None:
+        torch.cuda.current_stream(self.device).wait_stream(self.stream)
+
+    def status_word(self):
+        return self.status[0]
+
+    def describe_error(self) -> str:
+        code, bucket, src, expected, seen = self.status[:5].tolist()
+        what = {1: "waiting for a peer's gradients to be ready", 2: "waiting for peers to finish writing"}.get(code, "?")
+        return (f"rank {self.rank}: gradient all-reduce gave up {what}: bucket {bucket}, peer {src}, "
+                f"expected {expected}, saw {seen}")
+
+
+def make_grad_sync(device: torch.device, world: int, rank: int, group=None, kind: str = "auto"):
+    if world <= 1:
+        return None
+    if kind == "auto":
+        kind = "fused" if device.type == "cuda" else "collective"
+    if kind == "fused":
+        return FusedGradSync(device, world, rank, group)
+    if kind in ("collective", "nccl", "gloo"):
+        return CollectiveGradSync(device, world, rank, group)
+    raise ValueError(f"unknown gradient synchronisation kind: {kind}")

@@ -97,6 +97,18 @@ class Trainer:
             self.sync.reduce_scalar(self.loss_sum)
         return stats
 
+    def read_update_scalars(self, stats: torch.Tensor):
+        """One device->host read per update: loss, gradient norm, clip coefficient and, with a
+        fused gradient synchroniser, its error word."""
+        items = [self.loss_sum, stats[0], stats[1]]
+        word = self.sync.status_word() if self.sync is not None else None
+        if word is not None:
+            items.append(word.float())
+        host = torch.stack(items).tolist()
+        if word is not None and host[3] != 0:
+            raise RuntimeError(self.sync.describe_error())
+        return host[0], host[1], host[2]
+
     # ------------------------------------------------------------------ pretraining update
     def pretrain_update(self, data, cursor: int, target_tokens: int, micro_batch: int, seq_len: int,
                         lr: float, batcher: HostBatcher | None = None) -> UpdateResult:
@@ -120,8 +132,7 @@ class Trainer:
             self.micro_step(loss_fn, last=index == len(slices) - 1)
             batcher.release(current)
         stats = self.finish_update(lr)
-        host = torch.stack([self.loss_sum, stats[0], stats[1]]).tolist()  # the one host sync
-        loss, norm, coef = host
+        loss, norm, coef = self.read_update_scalars(stats)  # the one host sync
         if not math.isfinite(norm):
             raise RuntimeError(f"non-finite gradient norm {norm}")
         return UpdateResult(loss=loss, grad_norm=norm, tokens=target_tokens,
