@@ -151,3 +151,31 @@ def test_trainer_update_runs_and_learns():
     data = SyntheticTokens(4 * 256 * 2 + 1, 512, seed=0)
     losses = [trainer.pretrain_update(data, 0, 4 * 256 * 2, 4, 256, 3e-3).loss for _ in range(8)]
     assert losses[-1] < losses[0] - 0.3, losses
+
+
+@pytest.mark.parametrize("rows,d,vocab", [(300, 256, 1000), (2048, 512, 32768), (9000, 256, 4224)])
+def test_lm_head_cross_entropy_matches_reference(ops, rows, d, vocab):
+    from warpstate_ai_b200.ops import lmhead, reference as R
+    from warpstate_ai_b200.ops.gemm import check_device_errors
+    torch.manual_seed(0)
+    hidden = torch.randn(rows, d, device="cuda").bfloat16().requires_grad_(True)
+    weight = (torch.randn(vocab, d, device="cuda") * 0.05).requires_grad_(True)
+    labels = torch.randint(0, vocab, (rows,), device="cuda")
+    labels[::7] = -100
+    assert lmhead.kernels_ready(hidden, weight)
+    logp = lmhead.token_logps(hidden, weight, labels)
+    weights = torch.randn(rows, device="cuda")
+    (logp * weights).sum().backward()
+    check_device_errors()
+    h32 = hidden.detach().float().requires_grad_(True)
+    w32 = weight.detach().bfloat16().float().requires_grad_(True)
+    ref = R.lm_head_token_logps(h32, w32, labels)
+    (ref * weights).sum().backward()
+    assert float(logp[::7].abs().max()) == 0.0
+    assert torch.allclose(logp, ref, rtol=2e-2, atol=2e-2)
+    assert rel_l2(logp, ref) < 5e-3
+    assert rel_l2(hidden.grad, h32.grad) < 0.02
+    assert rel_l2(weight.grad, w32.grad) < 0.02
+    total = lmhead.loss_sum(hidden.detach(), weight.detach(), labels)
+    want = R.lm_head_loss_sum(h32.detach(), w32.detach(), labels)
+    assert abs(float(total) - float(want)) < 2e-3 * abs(float(want))

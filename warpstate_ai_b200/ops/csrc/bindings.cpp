@@ -74,6 +74,7 @@ void gemm(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool b_mn, int64_
   g.out2 = const_cast<void*>(opt_ptr(out2)); g.ldo2 = (int)opt_ld(out2);
   g.aux = opt_ptr(aux); g.ldaux = (int)opt_ld(aux);
   g.row_scale = reinterpret_cast<const float*>(opt_ptr(row_scale));
+  g.row_vec = nullptr;
   g.alpha = (float)alpha; g.beta = (float)beta;
   g.error_flag = reinterpret_cast<int*>(const_cast<void*>(opt_ptr(error_flag)));
   check_rc(ws_gemm(&g, cur_stream()), "gemm");
@@ -323,6 +324,71 @@ void adamw_step(at::Tensor p, const at::Tensor& g, at::Tensor m, at::Tensor v, c
 
 int64_t launch_count() { return (int64_t)ws_launch_count(); }
 
+// ----------------------------------------------------------------------------- LM head
+// (lse [rows], logp [rows]) of hidden @ weight.T against labels; logits stay on chip.
+std::tuple<at::Tensor, at::Tensor> lm_head_fwd(const at::Tensor& hidden, const at::Tensor& weight,
+                                               const at::Tensor& labels, int64_t ignore_index,
+                                               const c10::optional<at::Tensor>& error_flag) {
+  TORCH_CHECK(hidden.is_cuda() && hidden.scalar_type() == at::kBFloat16 && hidden.dim() == 2 && hidden.stride(1) == 1,
+              "lm_head_fwd: hidden must be BF16 [rows, d]");
+  TORCH_CHECK(weight.scalar_type() == at::kBFloat16 && weight.dim() == 2 && weight.is_contiguous() &&
+              weight.size(1) == hidden.size(1), "lm_head_fwd: weight must be BF16 [vocab, d]");
+  TORCH_CHECK(labels.scalar_type() == at::kLong && labels.is_contiguous() && labels.numel() == hidden.size(0),
+              "lm_head_fwd: labels must be int64 [rows]");
+  c10::cuda::CUDAGuard guard(hidden.device());
+  const int rows = (int)hidden.size(0), d = (int)hidden.size(1), vocab = (int)weight.size(0);
+  const int nparts = 2 * ((vocab + 255) / 256) - (((vocab % 256) != 0 && (vocab % 256) <= 128) ? 1 : 0);
+  const int ld = 2 * ((vocab + 255) / 256);
+  at::Tensor parts = at::empty({rows, ld, 2}, hidden.options().dtype(at::kFloat));
+  at::Tensor label_logit = at::zeros({rows}, hidden.options().dtype(at::kFloat));
+  WsGemm g;
+  g.a = hidden.data_ptr(); g.b = weight.data_ptr();
+  g.m = rows; g.n = vocab; g.k = d;
+  g.lda = (int)hidden.stride(0); g.ldb = (int)weight.stride(0);
+  g.a_mn = 0; g.b_mn = 0; g.epilogue = WS_EPI_CE_FWD;
+  g.out = parts.data_ptr(); g.ldo = ld;
+  g.out2 = label_logit.data_ptr(); g.ldo2 = 0;
+  g.aux = labels.data_ptr(); g.ldaux = 0;
+  g.row_scale = nullptr; g.row_vec = nullptr; g.alpha = 1.f; g.beta = 0.f;
+  g.error_flag = reinterpret_cast<int*>(const_cast<void*>(opt_ptr(error_flag)));
+  check_rc(ws_gemm(&g, cur_stream()), "lm_head_fwd gemm");
+  at::Tensor lse = at::empty({rows}, hidden.options().dtype(at::kFloat));
+  at::Tensor logp = at::empty({rows}, hidden.options().dtype(at::kFloat));
+  check_rc(ws_ce_combine(parts.data_ptr(), ld, nparts, label_logit.data_ptr<float>(),
+                         reinterpret_cast<const long long*>(labels.data_ptr<int64_t>()), (long long)ignore_index, rows,
+                         lse.data_ptr<float>(), logp.data_ptr<float>(), cur_stream()), "ce_combine");
+  return {lse, logp};
+}
+
+// dlogits [rows, vocab] BF16 = (softmax(hidden @ weight.T) - onehot(labels)) * row_weight
+at::Tensor lm_head_dlogits(const at::Tensor& hidden, const at::Tensor& weight, const at::Tensor& labels,
+                           const at::Tensor& lse, const at::Tensor& row_weight,
+                           const c10::optional<at::Tensor>& error_flag) {
+  TORCH_CHECK(hidden.is_cuda() && hidden.scalar_type() == at::kBFloat16 && hidden.dim() == 2 && hidden.stride(1) == 1,
+              "lm_head_dlogits: hidden");
+  TORCH_CHECK(weight.scalar_type() == at::kBFloat16 && weight.is_contiguous() && weight.size(1) == hidden.size(1) &&
+              weight.size(0) % 8 == 0, "lm_head_dlogits: weight must be BF16 [vocab, d] with vocab % 8 == 0");
+  const int rows = (int)hidden.size(0), d = (int)hidden.size(1), vocab = (int)weight.size(0);
+  TORCH_CHECK(labels.scalar_type() == at::kLong && labels.is_contiguous() && labels.numel() == rows &&
+              lse.scalar_type() == at::kFloat && lse.is_contiguous() && lse.numel() == rows &&
+              row_weight.scalar_type() == at::kFloat && row_weight.is_contiguous() && row_weight.numel() == rows,
+              "lm_head_dlogits: per-row vectors");
+  c10::cuda::CUDAGuard guard(hidden.device());
+  at::Tensor out = at::empty({rows, vocab}, hidden.options());
+  WsGemm g;
+  g.a = hidden.data_ptr(); g.b = weight.data_ptr();
+  g.m = rows; g.n = vocab; g.k = d;
+  g.lda = (int)hidden.stride(0); g.ldb = (int)weight.stride(0);
+  g.a_mn = 0; g.b_mn = 0; g.epilogue = WS_EPI_CE_BWD;
+  g.out = out.data_ptr(); g.ldo = vocab;
+  g.out2 = nullptr; g.ldo2 = 0;
+  g.aux = labels.data_ptr(); g.ldaux = 0;
+  g.row_scale = row_weight.data_ptr<float>(); g.row_vec = lse.data_ptr<float>(); g.alpha = 1.f; g.beta = 0.f;
+  g.error_flag = reinterpret_cast<int*>(const_cast<void*>(opt_ptr(error_flag)));
+  check_rc(ws_gemm(&g, cur_stream()), "lm_head_dlogits gemm");
+  return out;
+}
+
 // ----------------------------------------------------------------------------- communication
 std::vector<unsigned long long> ptr_table(at::IntArrayRef v) {
   std::vector<unsigned long long> out;
@@ -382,6 +448,8 @@ TORCH_LIBRARY(ws_b200, m) {
   m.def("embed_fwd(Tensor ids, Tensor table, bool out_bf16) -> Tensor");
   m.def("embed_bwd(Tensor dx, Tensor ids, Tensor(a!) grad_table) -> ()");
   m.def("launch_count() -> int");
+  m.def("lm_head_fwd(Tensor hidden, Tensor weight, Tensor labels, int ignore_index, Tensor(a!)? error_flag) -> (Tensor, Tensor)");
+  m.def("lm_head_dlogits(Tensor hidden, Tensor weight, Tensor labels, Tensor lse, Tensor row_weight, Tensor(a!)? error_flag) -> Tensor");
   m.def("grad_allreduce(int[] grad_ptrs, int[] flag_ptrs, int mc_grad, int rank, int world, int start, int count, "
         "int bucket, int seq, float scale, bool push, int ctas, Tensor(a!)? sumsq_out, Tensor(b!) status, "
         "float budget_seconds) -> ()");
@@ -421,6 +489,8 @@ TORCH_LIBRARY_IMPL(ws_b200, CUDA, m) {
   m.impl("memory_scan", &memory_scan);
   m.impl("attn_fwd", &attn_fwd);
   m.impl("adamw_step", &adamw_step);
+  m.impl("lm_head_fwd", &lm_head_fwd);
+  m.impl("lm_head_dlogits", &lm_head_dlogits);
   m.impl("grad_allreduce", &grad_allreduce);
   m.impl("wait_probe", &wait_probe);
   m.impl("adamw_shard_push", &adamw_shard_push);

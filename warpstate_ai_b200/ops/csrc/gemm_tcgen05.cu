@@ -5,7 +5,8 @@
 //   warp 1      : TMEM owner + MMA issuer (one lane) - tcgen05.mma 128x256x16, FP32 accumulators
 //                 in TMEM, two accumulator buffers (2 x 256 columns) so that the epilogue of
 //                 tile i overlaps the main loop of tile i+1.
-//   warps 2..5  : epilogue - tcgen05.ld of the warp's 32-lane quarter, fused epilogue math,
+//   warps 2..9  : epilogue (two groups of four, each group drains half of the tile columns) -
+//                 tcgen05.ld of the warp's 32-lane quarter, fused epilogue math,
 //                 vectorised global stores.
 //
 // Operand layouts: each operand is either K-major (contraction contiguous, the nn.Linear
@@ -39,7 +40,7 @@ constexpr int STAGES = 4;
 constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
 constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 320;  // producer warp, MMA warp, 2 groups of 4 epilogue warps
 constexpr int TMEM_COLS = 512;
 constexpr int GROUP_M = 8;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
@@ -55,6 +56,7 @@ struct GemmParams {
   const void* aux;
   int ldaux;
   const float* row_scale;
+  const float* row_vec;
   float alpha, beta;
   int* error_flag;
 };
@@ -98,7 +100,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull[b], 1);
-      mbar_init(&tempty[b], 4);
+      mbar_init(&tempty[b], 8);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -201,6 +203,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
   } else {
     // ------------------------------------------------------------------ epilogue warps
     const int quarter = warp & 3;
+    const int egroup = (warp - 2) >> 2;  // which half of the tile columns this warp drains
     int tcount = 0;
     for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++tcount) {
       int mb, nb;
@@ -218,7 +221,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(row) * p.ldo;
         const int n0 = nb * BN;
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
+        for (int c = egroup * 128; c < egroup * 128 + 128; c += 32) {
           if (n0 + c >= p.n) break;
           uint32_t r[32];
           tmem_ld_32x32b_x32(taddr + c, r);
@@ -242,7 +245,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         const float* res = reinterpret_cast<const float*>(p.aux) + static_cast<size_t>(row) * p.ldaux;
         const int n0 = nb * BN;
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
+        for (int c = egroup * 128; c < egroup * 128 + 128; c += 32) {
           if (n0 + c >= p.n) break;
           uint32_t r[32];
           tmem_ld_32x32b_x32(taddr + c, r);
@@ -277,7 +280,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
             reinterpret_cast<const __nv_bfloat16*>(p.aux) + static_cast<size_t>(row) * p.ldaux;
         const int n0 = nb * BN;
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
+        for (int c = egroup * 128; c < egroup * 128 + 128; c += 32) {
           if (n0 + c >= p.n) break;
           uint32_t r[32];
           tmem_ld_32x32b_x32(taddr + c, r);
@@ -309,7 +312,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         __nv_bfloat16* act = reinterpret_cast<__nv_bfloat16*>(p.out2) + static_cast<size_t>(row) * p.ldo2;
         const int n0 = nb * 128;
 #pragma unroll 1
-        for (int c = 0; c < 128; c += 16) {
+        for (int c = egroup * 64; c < egroup * 64 + 64; c += 16) {
           if (n0 + c >= p.h) break;
           uint32_t ru[16], rg[16];
           tmem_ld_32x32b_x16(taddr + c, ru);
@@ -349,7 +352,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
             reinterpret_cast<const __nv_bfloat16*>(p.aux) + static_cast<size_t>(row) * p.ldaux;
         const int n0 = nb * BN;
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 16) {
+        for (int c = egroup * 128; c < egroup * 128 + 128; c += 16) {
           if (n0 + c >= p.n) break;
           uint32_t r[16];
           tmem_ld_32x32b_x16(taddr + c, r);
@@ -378,6 +381,73 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
                 }
                 *reinterpret_cast<uint4*>(dpk + n0 + c + j) = vu;
                 *reinterpret_cast<uint4*>(dpk + p.n + n0 + c + j) = vg;
+              }
+            }
+          }
+        }
+      } else if constexpr (EPI == WS_EPI_CE_FWD) {
+        // LM head forward: the logits tile never leaves the SM.  Each thread folds its 128
+        // columns of one row into (max, sum exp) and the owner of the label column records the
+        // label's logit.  Logits are rounded to BF16 first, as a BF16 head GEMM would return them.
+        const long long* labels = reinterpret_cast<const long long*>(p.aux);
+        const long long lab = row_ok ? labels[row] : -1;
+        const int n0 = nb * BN;
+        float mx = -INFINITY, sm = 0.f;
+#pragma unroll 1
+        for (int c = egroup * 128; c < egroup * 128 + 128; c += 32) {
+          if (n0 + c >= p.n) break;
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + c, r);
+          tmem_ld_wait();
+          float cm = -INFINITY;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float v = (n0 + c + j < p.n) ? bf16_round(__uint_as_float(r[j])) : -INFINITY;
+            r[j] = __float_as_uint(v);
+            cm = fmaxf(cm, v);
+            if (n0 + c + j == lab) reinterpret_cast<float*>(p.out2)[row] = v;
+          }
+          const float nm = fmaxf(mx, cm);
+          float cs = 0.f;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) cs += __expf(__uint_as_float(r[j]) - nm);
+          sm = sm * __expf(mx - nm) + cs;
+          mx = nm;
+        }
+        if (row_ok && n0 + egroup * 128 < p.n) {
+          float2* part = reinterpret_cast<float2*>(p.out) + static_cast<size_t>(row) * p.ldo + (nb * 2 + egroup);
+          *part = make_float2(mx, sm);
+        }
+      } else if constexpr (EPI == WS_EPI_CE_BWD) {
+        // LM head backward: recompute the logits tile and emit
+        // dlogits = (softmax - onehot(label)) * row_weight in BF16.
+        const long long* labels = reinterpret_cast<const long long*>(p.aux);
+        const long long lab = row_ok ? labels[row] : -1;
+        const float lse = row_ok ? p.row_vec[row] : 0.f;
+        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(row) * p.ldo;
+        const int n0 = nb * BN;
+#pragma unroll 1
+        for (int c = egroup * 128; c < egroup * 128 + 128; c += 32) {
+          if (n0 + c >= p.n) break;
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + c, r);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              if (n0 + c + j < p.n) {
+                uint4 v;
+                uint32_t* vw = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                  const int col = n0 + c + j + 2 * t;
+                  float d0 = __expf(bf16_round(__uint_as_float(r[j + 2 * t])) - lse);
+                  float d1 = __expf(bf16_round(__uint_as_float(r[j + 2 * t + 1])) - lse);
+                  if (col == lab) d0 -= 1.f;
+                  if (col + 1 == lab) d1 -= 1.f;
+                  vw[t] = pack_bf16x2(d0 * rs, d1 * rs);
+                }
+                *reinterpret_cast<uint4*>(out + n0 + c + j) = v;
               }
             }
           }
@@ -460,6 +530,7 @@ extern "C" int ws_gemm(const WsGemm* g, cudaStream_t stream) {
   p.out2 = g->out2; p.ldo2 = g->ldo2;
   p.aux = g->aux; p.ldaux = g->ldaux;
   p.row_scale = g->row_scale;
+  p.row_vec = g->row_vec;
   p.alpha = g->alpha; p.beta = g->beta;
   p.error_flag = g->error_flag;
 
@@ -467,7 +538,12 @@ extern "C" int ws_gemm(const WsGemm* g, cudaStream_t stream) {
   const bool f32_out = g->epilogue == WS_EPI_RESID_F32 || g->epilogue == WS_EPI_ACC_F32 ||
                        g->epilogue == WS_EPI_F32;
   const int vec = f32_out ? 4 : 8;
-  if (g->n % vec != 0 || g->ldo % vec != 0) return -2;
+  if (g->epilogue == WS_EPI_CE_FWD) {
+    if (g->aux == nullptr || g->out2 == nullptr || g->ldo < 2 * ((g->n + BN - 1) / BN)) return -7;
+  } else if (g->n % vec != 0 || g->ldo % vec != 0) {
+    return -2;
+  }
+  if (g->epilogue == WS_EPI_CE_BWD && (g->aux == nullptr || g->row_vec == nullptr || g->row_scale == nullptr)) return -8;
   if ((g->epilogue == WS_EPI_RESID_F32 || g->epilogue == WS_EPI_RESID_BF16) &&
       (g->aux == nullptr || g->ldaux % vec != 0)) return -3;
   if (swiglu && (g->out2 == nullptr || g->ldo2 % 8 != 0)) return -4;
@@ -491,6 +567,8 @@ extern "C" int ws_gemm(const WsGemm* g, cudaStream_t stream) {
     case (3 | (WS_EPI_ACC_F32 << 2)): return launch<true, true, WS_EPI_ACC_F32>(ta, tb, p, grid, stream);
     case (3 | (WS_EPI_BF16 << 2)): return launch<true, true, WS_EPI_BF16>(ta, tb, p, grid, stream);
     case (2 | (WS_EPI_SWIGLU_BWD << 2)): return launch<false, true, WS_EPI_SWIGLU_BWD>(ta, tb, p, grid, stream);
+    case (0 | (WS_EPI_CE_FWD << 2)): return launch<false, false, WS_EPI_CE_FWD>(ta, tb, p, grid, stream);
+    case (0 | (WS_EPI_CE_BWD << 2)): return launch<false, false, WS_EPI_CE_BWD>(ta, tb, p, grid, stream);
     default: return -6;
   }
 }

@@ -24,6 +24,8 @@ enum WsEpilogue {
   WS_EPI_SWIGLU_BWD = 4,  // acc = dAct[M,h]; aux_bf16[M,2h] = (up|gate); out_bf16[M,2h] = (dUp|dGate)
   WS_EPI_F32 = 5,         // out_f32[M,N]  = acc
   WS_EPI_RESID_BF16 = 6,  // out_bf16[M,N] = resid_bf16[M,N] + acc   (BF16 residual stream)
+  WS_EPI_CE_FWD = 7,      // LM head: out = float2 parts[M, ldo] of (max, sum exp) per 128 columns, out2 = label logit[M]; aux = labels (int64)
+  WS_EPI_CE_BWD = 8,      // LM head: out_bf16[M,N] = (exp(logit - row_vec[m]) - onehot(label)) * row_scale[m]; aux = labels
 };
 
 typedef struct WsGemm {
@@ -40,6 +42,7 @@ typedef struct WsGemm {
   const void* aux;  // RESID: residual; SWIGLU_BWD: packed (up|gate)
   int ldaux;
   const float* row_scale;  // optional per-row multiplier applied to acc (may be NULL)
+  const float* row_vec;    // CE_BWD: per-row log-sum-exp (otherwise NULL)
   float alpha;
   float beta;
   int* error_flag;  // device int; set non-zero if a bounded wait ran out (may be NULL)
@@ -118,6 +121,12 @@ int ws_grad_norm_clip(const float* g, size_t n, float* partial, const float* ext
 int ws_adamw(float* p, const float* g, float* m, float* v, void* p_bf16, size_t n, float lr, float beta1,
              float beta2, float eps, float wd, int step, const float* grad_scale_ptr,
              float grad_scale_const, cudaStream_t stream);
+
+// ----------------------------------------------------------------------------- LM head
+// parts: float2 [rows, ld] of (max, sum exp) per 128 vocabulary columns (nparts valid per row),
+// written by the WS_EPI_CE_FWD epilogue.  lse[rows], logp[rows] (0 where label == ignore_index).
+int ws_ce_combine(const void* parts, int ld, int nparts, const float* label_logit, const long long* labels,
+                  long long ignore_index, int rows, float* lse, float* logp, cudaStream_t stream);
 
 // ----------------------------------------------------------------------------- communication
 // Peer tables are arrays of `world` (<= 8) device addresses valid in THIS process: its mappings
