@@ -102,7 +102,10 @@ class WarpStateCore(nn.Module):
         self.fast_decay_logit = nn.Parameter(torch.full((self.h,), math.log(0.90 / 0.10)))
         self.slow_decay_logit = nn.Parameter(torch.full((self.h,), math.log(0.99 / 0.01)))
         self.memory_mix_logit = nn.Parameter(torch.zeros(self.h))
-        cos, sin = R.rope_tables(self.chunk, self.hd, None, torch.float32)
+        # Real tables even when the module is built on the meta device (they are not in the state
+        # dict, so a meta-constructed model could never fill them in).
+        table_device = torch.device("cpu") if torch.get_default_device().type == "meta" else None
+        cos, sin = R.rope_tables(self.chunk, self.hd, table_device, torch.float32)
         self.register_buffer("rope_cos", cos, persistent=False)
         self.register_buffer("rope_sin", sin, persistent=False)
 
