@@ -271,6 +271,29 @@ class WarpStateLM(nn.Module):
                 total = total + R.lm_head_loss_sum(h, self.embed.weight, y)
         return total / count
 
+    def sequence_logps(self, input_ids: torch.Tensor, targets: torch.Tensor, head_chunk_size: int = 256) -> torch.Tensor:
+        """Per-sequence sum of label log-probabilities over positions whose target is not -100
+        (FP32, ``[B]``), without keeping ``[B, T, vocab]`` logits: the scoring head of DPO
+        (reference dpo.py:130-163)."""
+        x = self.hidden_states(input_ids)
+        b, t, d = x.shape
+        if _fused_active(x):
+            from ..ops import lmhead
+            hidden = x.reshape(b * t, d)
+            if hidden.dtype != torch.bfloat16:
+                hidden = hidden.to(torch.bfloat16)
+            if lmhead.kernels_ready(hidden, self.embed.weight):
+                return lmhead.token_logps(hidden, self.embed.weight, targets.reshape(-1)).view(b, t).sum(dim=1)
+
+        def score(h, weight, labels):
+            return R.lm_head_token_logps(h.reshape(-1, h.size(-1)), weight, labels.reshape(-1)).view(labels.shape).sum(dim=1)
+
+        logps = x.new_zeros((b,), dtype=torch.float32)
+        for start in range(0, t, head_chunk_size):
+            args = (x[:, start:start + head_chunk_size], self.embed.weight, targets[:, start:start + head_chunk_size])
+            logps = logps + (checkpoint(score, *args, use_reentrant=False) if torch.is_grad_enabled() else score(*args))
+        return logps
+
     # ------------------------------------------------------------------ decode
     @torch.no_grad()
     def init_generation_cache(self, batch_size: int, device: torch.device, dtype: torch.dtype) -> List[LayerCache]:
