@@ -347,3 +347,30 @@ def lm_head_loss(hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tenso
     if lmhead.kernels_ready(hidden, weight):
         return lmhead.loss_sum(hidden, weight, labels)
     return LMHeadLossFn.apply(hidden, weight, labels)
+
+
+# --------------------------------------------------------------------------- prefill
+@torch.no_grad()
+def core_prefill(core, x: torch.Tensor, depth_scale, depth_bias):
+    """Forward of one core over whole chunks that also returns the fast / slow memory states
+    after the last chunk (FP32 ``[B,H,64,64]``): the chunked prefill of the decode engine."""
+    from . import attention
+    ops = _ops()
+    batch, seq, d = x.shape
+    x_in = x.reshape(batch * seq, d).contiguous()
+    scale = depth_scale.detach().float().contiguous()
+    bias = depth_bias.detach().float().contiguous()
+    z1, _, xmod = ops.rmsnorm_fwd(x_in, scale, bias, core.norm1.weight.detach(), core.cfg.rms_eps, True)
+    qkvgu = G.linear(z1, bf16_weight(core.in_proj.weight))
+    if attention.geometry_ok(core):
+        y, _, _, (fast, slow) = attention.forward_only(qkvgu, core, batch, seq, want_final=True)
+    else:
+        y, (fast, slow) = R.attention_memory(qkvgu.view(batch, seq, -1), core.fast_decay_logit, core.slow_decay_logit,
+                                             core.memory_mix_logit, core.h, core.chunk, core.cfg.parallel_memory,
+                                             core.rope_cos, core.rope_sin, return_state=True)
+        y = y.reshape(batch * seq, -1).contiguous()
+    x2 = G.linear_residual(y, bf16_weight(core.out_proj.weight), xmod)
+    z2, _, _ = ops.rmsnorm_fwd(x2, None, None, core.norm2.weight.detach(), core.cfg.rms_eps, False)
+    _, act = G.linear_swiglu(z2, bf16_weight(core.ffn.up_gate.weight))
+    x3 = G.linear_residual(act, bf16_weight(core.ffn.down.weight), x2)
+    return x3.view(batch, seq, d), fast, slow

@@ -1,0 +1,203 @@
+"""Batched prefill + decode engine.
+
+Decoding carries, per logical depth and per sequence, only the fast and slow matrix memories
+(``[H, 64, 64]`` FP32 each) plus the keys / values / memory-values of the *current* 128-token
+chunk -- there is no growing KV cache (reference model: warpstate/model.py:222-274; its
+training-consistent variant ops/posttrain_chat.py:94-142, whose semantics this follows: the mix
+of fast/slow is applied before the read and a chunk's write is formed as ONE product
+``tanh(K)^T tanh(U) / C`` when the chunk completes).
+
+What is new relative to the reference (whose CLIs prefill token by token at batch 1):
+
+* `prefill` pushes all complete chunks of the prompt through the training forward path (the fused
+  sm_100a kernels on CUDA) and reads the memory states after the last complete chunk from the
+  O(N) scan kernel; only the tokens of a trailing partial chunk are stepped one by one;
+* `step` handles a whole batch in lock-step; on CUDA the step for a fixed batch size is captured
+  once in a CUDA graph and replayed per token (the in-chunk position is a device scalar, the
+  attention over the chunk cache is masked instead of sliced, so one graph serves all positions);
+* the memory update at a chunk boundary runs outside the graph, every 128 tokens.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+
+from ..ops import reference as R
+
+
+@dataclass
+class DepthState:
+    fast: torch.Tensor    # [B,H,Dh,Dh] FP32
+    slow: torch.Tensor    # [B,H,Dh,Dh] FP32
+    mixed: torch.Tensor   # [B,H,Dh,Dh] compute dtype: mix*fast + (1-mix)*slow, what a read uses
+    k: torch.Tensor       # [B,H,C,Dh] roped keys of the current chunk
+    v: torch.Tensor
+    u: torch.Tensor
+
+
+class DecodeEngine:
+    def __init__(self, model, dtype: torch.dtype = torch.bfloat16, use_cuda_graph: bool | None = None):
+        if model.training:
+            raise ValueError("Decode requires model.eval()")
+        self.model = model
+        self.cfg = model.cfg
+        self.device = model.embed.weight.device
+        self.dtype = dtype if self.device.type == "cuda" else torch.float32 if dtype == torch.float32 else dtype
+        self.chunk = self.cfg.chunk_size
+        self.h, self.hd = self.cfg.n_heads, self.cfg.head_dim
+        self.use_graph = (self.device.type == "cuda") if use_cuda_graph is None else use_cuda_graph
+        self.weights = []
+        with torch.no_grad():
+            for depth in range(self.cfg.logical_depth):
+                core = model.cores[depth % self.cfg.n_cores]
+                self.weights.append(dict(
+                    scale=model.depth_scale[depth].detach().float(), bias=model.depth_bias[depth].detach().float(),
+                    n1=core.norm1.weight.detach().float(), n2=core.norm2.weight.detach().float(),
+                    w_in=core.in_proj.weight.detach().to(self.dtype), w_out=core.out_proj.weight.detach().to(self.dtype),
+                    w_ug=core.ffn.up_gate.weight.detach().to(self.dtype), w_down=core.ffn.down.weight.detach().to(self.dtype),
+                    df=torch.sigmoid(core.fast_decay_logit.detach().float()).view(1, self.h, 1, 1),
+                    ds=torch.sigmoid(core.slow_decay_logit.detach().float()).view(1, self.h, 1, 1),
+                    mix=torch.sigmoid(core.memory_mix_logit.detach().float()).view(1, self.h, 1, 1)))
+            self.embed = model.embed.weight.detach()
+            self.head = model.embed.weight.detach().to(self.dtype)
+            self.final_norm = model.final_norm.weight.detach().float()
+        cos, sin = R.rope_tables(self.chunk, self.hd, self.device, torch.float32)
+        self.cos, self.sin = cos, sin
+        self.states: list[DepthState] | None = None
+        self.batch = 0
+        self.pos = 0            # host copy of the in-chunk position
+        self._graph = None
+
+    # ------------------------------------------------------------------ state
+    def new_state(self, batch: int) -> None:
+        z = lambda *shape, dtype: torch.zeros(shape, device=self.device, dtype=dtype)
+        self.states = [DepthState(z(batch, self.h, self.hd, self.hd, dtype=torch.float32),
+                                  z(batch, self.h, self.hd, self.hd, dtype=torch.float32),
+                                  z(batch, self.h, self.hd, self.hd, dtype=self.dtype),
+                                  z(batch, self.h, self.chunk, self.hd, dtype=self.dtype),
+                                  z(batch, self.h, self.chunk, self.hd, dtype=self.dtype),
+                                  z(batch, self.h, self.chunk, self.hd, dtype=self.dtype))
+                       for _ in range(self.cfg.logical_depth)]
+        self.batch = batch
+        self.pos = 0
+        self.pos_dev = torch.zeros((), dtype=torch.long, device=self.device)
+        self.token_buf = torch.zeros(batch, dtype=torch.long, device=self.device)
+        self.logits_buf = None
+        self._graph = None
+
+    def _norm(self, x, w):
+        x32 = x.float()
+        return (x32 * torch.rsqrt(x32.pow(2).mean(-1, keepdim=True) + self.cfg.rms_eps) * w).to(self.dtype)
+
+    # ------------------------------------------------------------------ one token for the whole batch
+    def _step_math(self, token: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
+        b = token.shape[0]
+        x = self.embed[token].float()
+        cos = self.cos.index_select(0, pos.view(1)).view(1, 1, self.hd)
+        sin = self.sin.index_select(0, pos.view(1)).view(1, 1, self.hd)
+        visible = (torch.arange(self.chunk, device=self.device) <= pos).view(1, 1, self.chunk)
+        scale = 1.0 / math.sqrt(self.hd)
+        for w, st in zip(self.weights, self.states):
+            x = x * (1.0 + w["scale"]) + w["bias"]
+            qkvgu = F.linear(self._norm(x, w["n1"]), w["w_in"])
+            q, k, v, g, u = (t.view(b, self.h, self.hd) for t in qkvgu.chunk(5, dim=-1))
+            q = (q.float() * cos + R.rotate_pairs(q.float()) * sin).to(self.dtype)
+            k = (k.float() * cos + R.rotate_pairs(k.float()) * sin).to(self.dtype)
+            index = pos.view(1)
+            st.k.index_copy_(2, index, k.unsqueeze(2))
+            st.v.index_copy_(2, index, v.unsqueeze(2))
+            st.u.index_copy_(2, index, u.unsqueeze(2))
+            scores = torch.einsum("bhd,bhcd->bhc", q.float(), st.k.float()) * scale
+            p = torch.softmax(scores.masked_fill(~visible, -torch.inf), dim=-1)
+            local = torch.einsum("bhc,bhcd->bhd", p, st.v.float())
+            memory = torch.einsum("bhi,bhij->bhj", q.float(), st.mixed.float()) * scale
+            gate = torch.sigmoid(g.float())
+            y = (gate * local + (1.0 - gate) * memory).to(self.dtype).reshape(b, self.h * self.hd)
+            x = x + F.linear(y, w["w_out"]).float()
+            up, gt = F.linear(self._norm(x, w["n2"]), w["w_ug"]).chunk(2, dim=-1)
+            x = x + F.linear(F.silu(gt) * up, w["w_down"]).float()
+        return F.linear(self._norm(x, self.final_norm), self.head).float()
+
+    def _end_of_chunk(self) -> None:
+        for w, st in zip(self.weights, self.states):
+            write = torch.matmul(torch.tanh(st.k).transpose(-2, -1), torch.tanh(st.u)).float() / self.chunk
+            st.fast.mul_(w["df"]).add_(write * (1.0 - w["df"]))
+            st.slow.mul_(w["ds"]).add_(write * (1.0 - w["ds"]))
+            st.mixed.copy_((w["mix"] * st.fast + (1.0 - w["mix"]) * st.slow).to(self.dtype))
+
+    @torch.no_grad()
+    def step(self, token: torch.Tensor) -> torch.Tensor:
+        """``token [B]`` (or ``[B,1]``) -> logits ``[B, V]`` FP32."""
+        token = token.reshape(-1).to(self.device)
+        if self.states is None or token.shape[0] != self.batch:
+            self.new_state(token.shape[0])
+        self.pos_dev.fill_(self.pos)
+        if self.use_graph:
+            self.token_buf.copy_(token)
+            if self._graph is None:
+                self._capture()
+            self._graph.replay()
+            logits = self.logits_buf
+        else:
+            logits = self._step_math(token, self.pos_dev)
+        self.pos += 1
+        if self.pos == self.chunk:
+            self._end_of_chunk()
+            self.pos = 0
+        return logits
+
+    def _capture(self) -> None:
+        # warm up on a side stream (allocator + lazy initialisations), then capture once;
+        # the cache writes of the warm-up land at the current position and are overwritten by the
+        # identical values of the captured replay
+        stream = torch.cuda.Stream(device=self.device)
+        stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(stream):
+            for _ in range(2):
+                self._step_math(self.token_buf, self.pos_dev)
+        torch.cuda.current_stream(self.device).wait_stream(stream)
+        self._graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self._graph):
+            self.logits_buf = self._step_math(self.token_buf, self.pos_dev)
+
+    # ------------------------------------------------------------------ prefill
+    @torch.no_grad()
+    def prefill(self, ids: torch.Tensor) -> torch.Tensor:
+        """``ids [B, T]``: fills the state with the whole prompt; returns the logits after its
+        last token ``[B, V]``."""
+        ids = ids.to(self.device)
+        b, t = ids.shape
+        self.new_state(b)
+        full = (t // self.chunk) * self.chunk
+        logits = None
+        if full:
+            hidden = self._prefill_chunks(ids[:, :full])
+            if full == t:
+                logits = F.linear(self._norm(hidden[:, -1], self.final_norm), self.head).float()
+        for i in range(full, t):
+            logits = self.step(ids[:, i])
+        return logits
+
+    def _prefill_chunks(self, ids: torch.Tensor) -> torch.Tensor:
+        model = self.model
+        use_fused = False
+        if self.device.type == "cuda" and self.dtype == torch.bfloat16:
+            from ..ops import fused
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                use_fused = fused.active(self.embed)
+        x = self.embed[ids].float()
+        for depth, (w, st) in enumerate(zip(self.weights, self.states)):
+            core = model.cores[depth % self.cfg.n_cores]
+            if use_fused:
+                from ..ops import fused
+                x, fast, slow = fused.core_prefill(core, x, model.depth_scale[depth], model.depth_bias[depth])
+            else:
+                x = x * (1.0 + w["scale"]) + w["bias"]
+                x, (fast, slow) = core.forward_with_state(x)
+            st.fast.copy_(fast.float())
+            st.slow.copy_(slow.float())
+            st.mixed.copy_((w["mix"] * st.fast + (1.0 - w["mix"]) * st.slow).to(self.dtype))
+        return x
