@@ -1,0 +1,210 @@
+"""Launcher escalation, sealed archives, the handoff state machine with a fake supervisor and a
+fake launcher, and the preflight gate on CPU (reference test_training_launcher.py:26-86,
+test_posttrain_handoff.py, test_archive_dpo.py, test_posttrain_worker_lock.py)."""
+import json
+import os
+import signal
+import subprocess
+import sys
+import textwrap
+import threading
+import time
+from pathlib import Path
+
+import pytest
+import torch
+
+from warpstate_ai_b200.data import prepare as P
+from warpstate_ai_b200.data.prepare_posttrain import prepare as prepare_posttrain
+from warpstate_ai_b200.orchestration import archive as A
+from warpstate_ai_b200.orchestration import handoff as H
+from warpstate_ai_b200.orchestration import launcher as L
+from warpstate_ai_b200.train import pretrain as T
+from warpstate_ai_b200.utils.io import LockHeld, digest, process_lock
+
+ROOT = Path(__file__).resolve().parents[1]
+TOK = ROOT / "tokenizer.model"
+
+
+@pytest.fixture()
+def ws(tmp_path, monkeypatch):
+    root = tmp_path / "ws"
+    root.mkdir()
+    monkeypatch.setenv("WARPSTATE_WORKSPACE", str(root))
+    return root
+
+
+def worker_script(tmp_path: Path, graceful: bool) -> Path:
+    path = tmp_path / "worker.py"
+    path.write_text(textwrap.dedent(f"""
+        import os, sys, time, subprocess
+        # a grandchild in its own session, like a torchrun worker
+        if len(sys.argv) > 1 and sys.argv[1] == "leaf":
+            stop = os.environ["STOP_FILE"]
+            while True:
+                if {graceful!r} and os.path.exists(stop):
+                    open(os.environ["MARK"], "w").write("saved")
+                    sys.exit(0)
+                time.sleep(0.05)
+        child = subprocess.Popen([sys.executable, __file__, "leaf"], start_new_session=True)
+        open(os.environ["PIDFILE"], "w").write(str(child.pid))
+        import signal
+        signal.signal(signal.SIGTERM, lambda *a: None)
+        sys.exit(child.wait())
+    """))
+    return path
+
+
+@pytest.mark.parametrize("graceful", [True, False])
+def test_launcher_graceful_and_forced_stop(ws, tmp_path, graceful):
+    stop = ws / "control/stop"
+    stop.parent.mkdir()
+    env = dict(os.environ, STOP_FILE=str(stop), MARK=str(tmp_path / "mark"), PIDFILE=str(tmp_path / "pid"))
+    script = worker_script(tmp_path, graceful)
+    result = {}
+
+    def run():
+        result["code"] = L.supervise([sys.executable, str(script)], stop, env, grace_seconds=1.0,
+                                     terminate_seconds=0.5, poll_seconds=0.05, scan_seconds=0.1)
+
+    # signal handlers must be installed from the main thread: run supervise here, trigger from a thread
+    def trigger():
+        for _ in range(100):
+            if (tmp_path / "pid").exists():
+                break
+            time.sleep(0.05)
+        time.sleep(0.3)
+        os.kill(os.getpid(), signal.SIGUSR1)
+
+    threading.Thread(target=trigger, daemon=True).start()
+    run()
+    leaf = int((tmp_path / "pid").read_text())
+    time.sleep(0.2)
+    assert L.process_info(leaf) is None or not Path(f"/proc/{leaf}/cmdline").read_text().count("leaf") \
+        or Path(f"/proc/{leaf}/stat").read_text().split()[2] == "Z"
+    if graceful:
+        assert result["code"] == 0 and (tmp_path / "mark").read_text() == "saved"
+    else:
+        assert result["code"] != 0 and not (tmp_path / "mark").exists()
+    assert stop.exists()
+
+
+def test_lock_is_inherited_by_children(tmp_path):
+    lock = tmp_path / "pipeline.lock"
+    with process_lock(lock) as handle:
+        child = subprocess.Popen([sys.executable, "-c", "import time; time.sleep(30)"], pass_fds=(handle.fileno(),))
+    try:
+        with pytest.raises(LockHeld):  # the parent released its context, the orphan still holds the lock
+            with process_lock(lock):
+                pass
+        with pytest.raises(LockHeld):
+            with process_lock(lock, shared=True):
+                pass
+    finally:
+        child.kill()
+        child.wait()
+    with process_lock(lock):
+        pass
+
+
+def train_base(ws: Path) -> tuple[Path, dict]:
+    cfg = ws / "cfg.json"
+    cfg.write_text(json.dumps(dict(vocab_size=32768, d_model=16, n_heads=2, n_cores=1, logical_depth=2, ffn_hidden=24,
+                                   chunk_size=8, gradient_checkpointing=False, parallel_memory=True)))
+    tok = ws / "tokenizer.model"
+    tok.write_bytes(TOK.read_bytes())
+    base = ws / "base"
+    P.write_synthetic_corpus(base, tok, 73, 64, 32768, seed=2)
+    T.STOP = False
+    T.main(["--from-scratch", "--work-dir", str(base), "--config", str(cfg), "--tokenizer", str(tok), "--stage", "train",
+            "--device", "cpu", "--test-small-gpu", "--train-tokens", "73", "--val-tokens", "64", "--seq-len", "8",
+            "--micro-batch", "2", "--grad-accum", "2", "--warmup-steps", "1", "--eval-batches", "1",
+            "--no-activation-checkpointing", "--dataset", "synthetic/uniform", "--dataset-config", "none",
+            "--revision", "0"])
+    ckpt = torch.load(base / "run/latest.pt", weights_only=False)
+    return tok, {"step": ckpt["step"], "tokens_seen": ckpt["tokens_seen"], "tokenizer_sha256": digest(tok)}
+
+
+def test_archive_seal_verify_and_tamper(ws):
+    tok, boundary = train_base(ws)
+    stage = H.SftStage()
+    plan = {"base": boundary}
+    paths = {"base_work_dir": ws / "base", "tokenizer": tok, "archive_dir": ws / "base/archives/final"}
+    meta = stage.make_archive(paths, plan, "rev")
+    assert meta["step"] == boundary["step"]
+    again = stage.make_archive(paths, plan, "rev")  # idempotent: verifies instead of rewriting
+    assert again["snapshot_sha256"] == meta["snapshot_sha256"]
+    copy = A.independent_copy(paths["archive_dir"], ws / "sft/initialization", boundary, meta["snapshot_sha256"])
+    assert copy.stat().st_ino != (paths["archive_dir"] / "model.pt").stat().st_ino
+    with pytest.raises(ValueError):
+        A.verify_archive(paths["archive_dir"], dict(boundary, step=boundary["step"] + 1))
+    victim = ws / "sft/initialization/ARCHIVE.md"
+    os.chmod(victim.parent, 0o755)
+    os.chmod(victim, 0o644)
+    victim.write_text("tampered")
+    os.chmod(victim, 0o444)
+    with pytest.raises(ValueError, match="checksum mismatch"):
+        A.verify_archive(ws / "sft/initialization", boundary)
+    with pytest.raises(OSError):
+        A.publish_directory(ws / "cfg.json", paths["archive_dir"])  # never replaces an existing archive
+
+
+def test_handoff_state_machine_with_fakes(ws, monkeypatch):
+    tok, boundary = train_base(ws)
+    data = ws / "data"
+    rows = [{"messages": [{"role": "user", "content": f"q{i}"}, {"role": "assistant", "content": f"a{i}"}]} for i in range(8)]
+    prepare_posttrain(data, tok, 64, sft_rows=rows, val_modulus=3)
+    plan = {"format": "warpstate-posttrain-plan-v1", "stage": "sft", "after_completion": "pause_for_evaluation",
+            "base": boundary, "training": {"sequence_length": 64, "micro_batch": 2, "grad_accum": 1, "lr": 1e-3,
+                                           "eval_every": 1, "save_every": 1, "eval_batches": 1, "workers": 1,
+                                           "max_steps": 2},
+            "handoff": {"base_work_dir": "base", "supervisor_socket": "supervisor.sock", "archive_dir": "base/archives/final",
+                        "work_dir": "sft", "data_dir": "data", "tokenizer": "tokenizer.model", "base_program": "train",
+                        "processes": 1, "poll_seconds": 0.01, "preflight": False}}
+    config = ws / "plan.json"
+    config.write_text(json.dumps(plan))
+    monkeypatch.setattr(H, "STOPPED", False)
+    states = iter([{"statename": "RUNNING"}, {"statename": "RUNNING"}] + [{"statename": "EXITED", "exitstatus": 0}] * 10)
+    calls = []
+
+    def fake_supervise(command, stop_path, environment, pass_fds=()):
+        calls.append(command)
+        assert len(pass_fds) == 2
+        # run the real trainer in-process equivalent: a subprocess on CPU, single rank
+        args = command[command.index(str(L.PACKAGE / "posttrain.py")) + 1:]
+        env = dict(environment, PYTHONPATH=str(ROOT), WARPSTATE_WORKSPACE=str(ws))
+        return subprocess.run([sys.executable, str(L.PACKAGE / "posttrain.py"), *args, "--device", "cpu"], env=env).returncode
+
+    assert H.run_handoff(config, stage_name="sft", status_fn=lambda s, p: next(states), supervise_fn=fake_supervise) == 0
+    state = json.loads((ws / "sft/control/handoff.json").read_text())
+    assert state["phase"] == "complete" and state["completion"]["completed"] is True
+    assert len(calls) == 1 and (ws / "sft/run/latest.pt").exists() and (ws / "sft/initialization/model.pt").exists()
+    A.verify_archive(ws / "base/archives/final", boundary, state["archive_sha256"])
+    # a second run is a no-op; a changed plan is refused
+    assert H.run_handoff(config, stage_name="sft", status_fn=lambda s, p: {"statename": "EXITED", "exitstatus": 0},
+                         supervise_fn=fake_supervise) == 0
+    assert len(calls) == 1
+    plan["training"]["lr"] = 2e-3
+    config.write_text(json.dumps(plan))
+    with pytest.raises(ValueError, match="re-arm"):
+        H.run_handoff(config, stage_name="sft", status_fn=lambda s, p: {"statename": "EXITED", "exitstatus": 0},
+                      supervise_fn=fake_supervise)
+
+
+def test_handoff_rejects_wrong_boundary(ws, monkeypatch):
+    tok, boundary = train_base(ws)
+    stage = H.SftStage()
+    ckpt = torch.load(ws / "base/run/latest.pt", weights_only=False)
+    with pytest.raises(ValueError, match="step"):
+        stage.validate_parent(ckpt, {"base": dict(boundary, step=boundary["step"] + 1)}, digest(tok))
+    ckpt["val_step"] = 0
+    with pytest.raises(ValueError, match="final validation"):
+        stage.validate_parent(ckpt, {"base": boundary}, digest(tok))
+
+
+def test_preflight_gate_on_cpu(tmp_path):
+    from warpstate_ai_b200.orchestration import preflight
+    assert preflight.main(["--stage", "dpo", "--work-dir", str(tmp_path / "pf"), "--processes", "1", "--device", "cpu"]) == 0
+    report = json.loads((tmp_path / "pf/report.json").read_text())
+    assert report["accepted"] is True and report["frozen_reference_unchanged"] is True
+    assert abs(report["initial_validation_loss"] - 0.6931) < 1e-3

@@ -82,11 +82,9 @@ def process_lock(path, shared: bool = False, blocking: bool = False):
             fcntl.flock(f, mode)
         except BlockingIOError as error:
             raise LockHeld(f"{path} is locked by another process") from error
-        try:
-            yield f
-        finally:
-            with contextlib.suppress(OSError):
-                fcntl.flock(f, fcntl.LOCK_UN)
+        # No explicit unlock: closing this descriptor drops the lock only when no other process
+        # still holds the same open file description (an inherited descriptor keeps it).
+        yield f
 
 
 def utc_timestamp() -> str:
