@@ -1,0 +1,291 @@
+// CTA-pair BF16 GEMM for sm_100a: two CTAs of a cluster compute one 256x256 tile with
+// tcgen05.mma.cta_group::2.
+//
+// Why pairs: with one CTA per 128x256 tile every k-block moves 48 KiB into shared memory by TMA
+// and 48 KiB out of it into the tensor core, which exceeds what one SM's shared memory can
+// stream at the tensor core's rate (the single-CTA kernel saturates near 70 % tensor-pipe
+// activity).  In a pair each CTA stages only its own 128 rows of A and its own 128 of the 256
+// B rows (32 KiB per k-block) and the hardware feeds both tensor cores from both shared
+// memories, so the same tile costs two thirds of the shared-memory traffic and the ring holds
+// six stages instead of four.
+//
+// Roles per CTA (320 threads): warp 0 = TMA producer (its own halves; plain per-CTA loads whose
+// completion is counted on the LEADER CTA's `full` barrier), warp 1 = TMEM owner and, in the
+// leader CTA only, MMA issuer; warps 2..9 = epilogue of the CTA's own 128 rows.
+// `empty` / `tmem_full` barriers exist in both CTAs and are signalled by two tcgen05.commit
+// (own + peer address); `tmem_empty` lives in the leader and counts the epilogue warps of both.
+// Every wait is bounded; both CTAs always reach the closing cluster barrier.
+#include "ws_ptx.cuh"
+#include "ws_api.h"
+#include "ws_tma_host.h"
+#include "gemm_epilogue.cuh"
+
+#include <cstdlib>
+
+namespace ws {
+
+extern "C" void ws_count_launch(void);
+
+namespace pair {
+constexpr int BM = 128;        // rows per CTA (256 per pair)
+constexpr int BN = 256;        // accumulator columns (128 B rows staged per CTA)
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 6;
+constexpr int A_BYTES = BM * BK * 2;        // 16 KiB
+constexpr int B_BYTES = (BN / 2) * BK * 2;  // 16 KiB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int THREADS = 320;
+constexpr int TMEM_COLS = 512;
+constexpr int GROUP_M = 8;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+}  // namespace pair
+
+__device__ __forceinline__ void pair_tile_coords(int tile, int num_m, int num_n, int& mb, int& nb) {
+  const int group_size = pair::GROUP_M * num_n;
+  const int group = tile / group_size;
+  const int first_m = group * pair::GROUP_M;
+  const int gsz = min(num_m - first_m, pair::GROUP_M);
+  const int r = tile - group * group_size;
+  mb = first_m + (r % gsz);
+  nb = r / gsz;
+}
+
+template <bool A_MN, bool B_MN, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::THREADS, 1)
+gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+             const GemmParams p) {
+  using namespace pair;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full = bars;                    // used in the leader CTA
+  uint64_t* empty = bars + STAGES;          // per CTA
+  uint64_t* tfull = bars + 2 * STAGES;      // per CTA
+  uint64_t* tempty = bars + 2 * STAGES + 2; // used in the leader CTA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 2);   // one expect-tx arrival per CTA of the pair
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tfull[b], 1);
+      mbar_init(&tempty[b], 16);  // 8 epilogue warps x 2 CTAs
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // peer barriers are initialised before anyone signals them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  constexpr bool kSwiglu = (EPI == WS_EPI_SWIGLU);
+  const int n_tile = kSwiglu ? 128 : BN;
+  const int num_m = (p.m + 2 * BM - 1) / (2 * BM);
+  const int num_n = (p.n + n_tile - 1) / n_tile;
+  const int tiles = num_m * num_n;
+  const int num_k = (p.k + BK - 1) / BK;
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int it = 0;
+      bool ok = true;
+      for (int tile = pair_id; tile < tiles && ok; tile += num_pairs) {
+        int mb, nb;
+        pair_tile_coords(tile, num_m, num_n, mb, nb);
+        const int m0 = mb * 2 * BM + rank * BM;  // this CTA's rows
+        for (int kb = 0; kb < num_k; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full_leader = mapa_shared(smem_u32(&full[s]), 0);
+          mbar_expect_tx_cluster(full_leader, STAGE_BYTES);
+          uint8_t* a_dst = sA + s * A_BYTES;
+          uint8_t* b_dst = sB + s * B_BYTES;
+          if (!A_MN) {
+            tma_load_2d_pair(a_dst, &tma_a, full_leader, kb * BK, m0);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BM / 64; ++i)
+              tma_load_2d_pair(a_dst + i * (BK * 128), &tma_a, full_leader, m0 + i * 64, kb * BK);
+          }
+          if (!B_MN) {
+            const int r0 = kSwiglu ? (rank ? p.h + nb * 128 : nb * 128) : nb * BN + rank * 128;
+            tma_load_2d_pair(b_dst, &tma_b, full_leader, kb * BK, r0);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+              tma_load_2d_pair(b_dst + i * (BK * 128), &tma_b, full_leader, nb * BN + rank * 128 + i * 64, kb * BK);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = make_idesc_bf16(2 * BM, BN, A_MN, B_MN);
+      int it = 0;
+      int tcount = 0;
+      bool ok = true;
+      for (int tile = pair_id; tile < tiles && ok; tile += num_pairs, ++tcount) {
+        const int buf = tcount & 1;
+        const uint32_t tph = (tcount >> 1) & 1;
+        if (!mbar_wait(&tempty[buf], tph ^ 1, abort_flag)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < num_k; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&full[s], ph, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_base = smem_u32(sA + s * A_BYTES);
+          const uint32_t b_base = smem_u32(sB + s * B_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t da = A_MN ? make_smem_desc_sw128(a_base + k * UMMA_K * 128, BK * 128, 1024)
+                                     : make_smem_desc_sw128(a_base + k * UMMA_K * 2, 0, 1024);
+            const uint64_t db = B_MN ? make_smem_desc_sw128(b_base + k * UMMA_K * 128, BK * 128, 1024)
+                                     : make_smem_desc_sw128(b_base + k * UMMA_K * 2, 0, 1024);
+            umma_bf16_pair(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          // free the stage in both CTAs once these MMAs have consumed it
+          umma_commit_pair(smem_u32(&empty[s]));
+          umma_commit_pair(mapa_shared(smem_u32(&empty[s]), 1));
+        }
+        if (ok) {
+          umma_commit_pair(smem_u32(&tfull[buf]));
+          umma_commit_pair(mapa_shared(smem_u32(&tfull[buf]), 1));
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps (both CTAs)
+    const int quarter = warp & 3;
+    const int egroup = (warp - 2) >> 2;
+    int tcount = 0;
+    for (int tile = pair_id; tile < tiles; tile += num_pairs, ++tcount) {
+      int mb, nb;
+      pair_tile_coords(tile, num_m, num_n, mb, nb);
+      const int buf = tcount & 1;
+      const uint32_t tph = (tcount >> 1) & 1;
+      if (!mbar_wait(&tfull[buf], tph, abort_flag)) break;
+      tc_fence_after_sync();
+      const int row = mb * 2 * BM + rank * BM + quarter * 32 + lane;
+      const bool row_ok = row < p.m;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+      const float rs = (p.row_scale != nullptr && row_ok) ? p.row_scale[row] : 1.0f;
+      gemm_epilogue<EPI>(p, taddr, row, row_ok, rs, nb, egroup);
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&tempty[buf]), 0));
+    }
+  }
+
+  // ------------------------------------------------------------------ tear-down
+  tc_fence_before_sync();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag != 0 && p.error_flag != nullptr) atomicExch(p.error_flag, 6);
+  cluster_sync_all();  // neither CTA leaves (or frees TMEM) while the peer may still signal it
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+template <bool A_MN, bool B_MN, int EPI>
+static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int pairs,
+                       cudaStream_t stream) {
+  static bool configured = false;
+  auto kern = gemm2_kernel<A_MN, B_MN, EPI>;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::SMEM_BYTES) != cudaSuccess)
+      return -20;
+    configured = true;
+  }
+  kern<<<2 * pairs, pair::THREADS, pair::SMEM_BYTES, stream>>>(ta, tb, p);
+  ws_count_launch();
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+}  // namespace ws
+
+// Same contract as ws_gemm (ws_api.h), whose argument checks have already run; `sms` bounds the
+// number of SMs used.  Returns -6 for a combination this kernel does not build.
+extern "C" int ws_gemm_pair(const WsGemm* g, int sms, cudaStream_t stream) {
+  using namespace ws;
+  if (g->m <= 0 || g->n <= 0 || g->k <= 0) return -1;
+  const bool swiglu = g->epilogue == WS_EPI_SWIGLU;
+  const int b_rows = swiglu ? 2 * g->n : g->n;
+  CUtensorMap ta, tb;
+  int rc;
+  if (!g->a_mn)
+    rc = make_map_bf16(&ta, g->a, g->k, g->m, g->lda, pair::BK, pair::BM);
+  else
+    rc = make_map_bf16(&ta, g->a, g->m, g->k, g->lda, 64, pair::BK);
+  if (rc) return rc;
+  if (!g->b_mn)
+    rc = make_map_bf16(&tb, g->b, g->k, b_rows, g->ldb, pair::BK, 128);
+  else
+    rc = make_map_bf16(&tb, g->b, b_rows, g->k, g->ldb, 64, pair::BK);
+  if (rc) return rc;
+  GemmParams p;
+  p.m = g->m; p.n = g->n; p.k = g->k;
+  p.h = g->n;
+  p.epi_n = swiglu ? 128 : pair::BN;
+  p.out = g->out; p.ldo = g->ldo;
+  p.out2 = g->out2; p.ldo2 = g->ldo2;
+  p.aux = g->aux; p.ldaux = g->ldaux;
+  p.row_scale = g->row_scale;
+  p.row_vec = g->row_vec;
+  p.alpha = g->alpha; p.beta = g->beta;
+  p.error_flag = g->error_flag;
+  p.debug = 0;
+  const int n_tile = swiglu ? 128 : pair::BN;
+  const int tiles = ((g->m + 2 * pair::BM - 1) / (2 * pair::BM)) * ((g->n + n_tile - 1) / n_tile);
+  int pairs = sms / 2;
+  if (pairs < 1) pairs = 1;
+  if (tiles < pairs) pairs = tiles;
+  const int key = (g->a_mn ? 1 : 0) | (g->b_mn ? 2 : 0) | (g->epilogue << 2);
+  switch (key) {
+    case (0 | (WS_EPI_BF16 << 2)): return launch_pair<false, false, WS_EPI_BF16>(ta, tb, p, pairs, stream);
+    case (2 | (WS_EPI_BF16 << 2)): return launch_pair<false, true, WS_EPI_BF16>(ta, tb, p, pairs, stream);
+    case (0 | (WS_EPI_RESID_F32 << 2)): return launch_pair<false, false, WS_EPI_RESID_F32>(ta, tb, p, pairs, stream);
+    case (0 | (WS_EPI_RESID_BF16 << 2)): return launch_pair<false, false, WS_EPI_RESID_BF16>(ta, tb, p, pairs, stream);
+    case (0 | (WS_EPI_SWIGLU << 2)): return launch_pair<false, false, WS_EPI_SWIGLU>(ta, tb, p, pairs, stream);
+    case (0 | (WS_EPI_F32 << 2)): return launch_pair<false, false, WS_EPI_F32>(ta, tb, p, pairs, stream);
+    case (3 | (WS_EPI_ACC_F32 << 2)): return launch_pair<true, true, WS_EPI_ACC_F32>(ta, tb, p, pairs, stream);
+    case (3 | (WS_EPI_BF16 << 2)): return launch_pair<true, true, WS_EPI_BF16>(ta, tb, p, pairs, stream);
+    case (2 | (WS_EPI_SWIGLU_BWD << 2)): return launch_pair<false, true, WS_EPI_SWIGLU_BWD>(ta, tb, p, pairs, stream);
+    case (0 | (WS_EPI_CE_FWD << 2)): return launch_pair<false, false, WS_EPI_CE_FWD>(ta, tb, p, pairs, stream);
+    case (0 | (WS_EPI_CE_BWD << 2)): return launch_pair<false, false, WS_EPI_CE_BWD>(ta, tb, p, pairs, stream);
+    default: return -6;
+  }
+}
