@@ -16,10 +16,15 @@ def rel_rms(a, b):
     return float((a - b).pow(2).mean().sqrt() / b.pow(2).mean().sqrt().clamp_min(1e-12))
 
 
-@pytest.fixture(scope="module")
-def g():
-    from warpstate_ai_b200.ops import gemm
-    return gemm
+@pytest.fixture(scope="module", params=["pair", "single"])
+def g(request):
+    """Every case runs on both kernels: the CTA-pair (cta_group::2) one, taken for problems with at
+    least 256 rows, and the single-CTA one."""
+    from warpstate_ai_b200.ops import _ext, gemm
+    lib = _ext.cdll()
+    lib.ws_gemm_set_pair_mode(1 if request.param == "pair" else 0)
+    yield gemm
+    lib.ws_gemm_set_pair_mode(-1)
 
 
 SHAPES = [(128, 256, 64), (256, 512, 256), (384, 1280, 256), (1000, 1376, 688), (2048, 2048, 2048),

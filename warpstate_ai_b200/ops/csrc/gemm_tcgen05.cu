@@ -254,14 +254,18 @@ extern "C" long long ws_launch_count(void) { return ws::g_launches.load(); }
 extern "C" void ws_count_launch(void) { ws::g_launches.fetch_add(1, std::memory_order_relaxed); }
 extern "C" void ws_gemm_set_sm_limit(int sms) { ws::g_sm_limit.store(sms); }
 
-// CTA-pair kernel (gemm2_tcgen05.cu); chosen by WS_GEMM_PAIR=1/0 in the environment.
+// CTA-pair kernel (gemm2_tcgen05.cu): the default for problems with at least 256 rows;
+// WS_GEMM_PAIR=0 in the environment keeps every GEMM on the single-CTA kernel.
 extern "C" int ws_gemm_pair(const WsGemm* g, int sms, cudaStream_t stream);
+static std::atomic<int> g_pair_override{-1};
+extern "C" void ws_gemm_set_pair_mode(int mode) { g_pair_override.store(mode); }
 static bool pair_mode() {
   static const bool on = [] {
     const char* e = getenv("WS_GEMM_PAIR");
-    return e != nullptr && atoi(e) != 0;
+    return e == nullptr || atoi(e) != 0;
   }();
-  return on;
+  const int forced = g_pair_override.load(std::memory_order_relaxed);
+  return forced < 0 ? on : forced != 0;
 }
 
 extern "C" int ws_gemm(const WsGemm* g, cudaStream_t stream) {
@@ -315,7 +319,7 @@ extern "C" int ws_gemm(const WsGemm* g, cudaStream_t stream) {
   int sms = sm_count();
   const int lim = g_sm_limit.load();
   if (lim > 0 && lim < sms) sms = lim;
-  if (pair_mode()) return ws_gemm_pair(g, sms, stream);
+  if (pair_mode() && g->m >= 256 && sms >= 2) return ws_gemm_pair(g, sms, stream);
   const int grid = tiles < sms ? tiles : sms;
 
   const int key = (g->a_mn ? 1 : 0) | (g->b_mn ? 2 : 0) | (g->epilogue << 2);

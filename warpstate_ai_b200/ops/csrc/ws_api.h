@@ -52,6 +52,9 @@ int ws_gemm(const WsGemm* g, cudaStream_t stream);
 // Number of SMs the GEMM may use on this stream's device (0 = all).  Lets a communication
 // kernel keep a few SMs for itself while persistent GEMM CTAs fill the rest.
 void ws_gemm_set_sm_limit(int sms);
+// Kernel choice for problems with >= 256 rows: 1 = CTA-pair (cta_group::2) kernel, 0 = single-CTA
+// kernel, -1 = the process default (pair unless WS_GEMM_PAIR=0 is in the environment).
+void ws_gemm_set_pair_mode(int mode);
 
 // Number of kernels this library has launched in this process.
 long long ws_launch_count(void);

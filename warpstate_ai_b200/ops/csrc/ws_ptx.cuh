@@ -282,6 +282,12 @@ __device__ __forceinline__ void cluster_sync_all() {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+// Arrival without memory ordering: for signals whose only payload is "my tcgen05.ld / smem reads
+// have completed" (already guaranteed by tcgen05.wait / program order).  A release at cluster
+// scope would first drain the thread's outstanding global stores, which costs microseconds.
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
 __device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t cluster_addr, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr),
                "r"(bytes)
@@ -326,5 +332,13 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t mbar_cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar_cluster_addr)
                : "memory");
 }
-// Bounded wait on a local mbarrier (same contract as mbar_wait).
+// The same arrival delivered to the barrier at this offset in every CTA of `cta_mask` (a signal
+// between the two CTAs of a pair; no data moves).
+__device__ __forceinline__ void umma_commit_pair_mask(uint32_t mbar_addr, uint16_t cta_mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+          mbar_addr),
+      "h"(cta_mask)
+      : "memory");
+}
 }  // namespace ws
