@@ -179,27 +179,39 @@ memory_scan_bwd_kernel(const float* __restrict__ dstate, const float* __restrict
 }
 
 // =============================================================================== attention bwd
-// smem tiles (16 KiB each unless noted):
-//   sQ | sK | sV | sTK | sTU | sDL (dy -> dlocal) | sDLs (dlocal / l) | sDM (dmem/8) | sP (32K: P~ -> dS)
-//   | sSt (8K) | sDW (8K) | bars
-constexpr int AB_SMEM = 8 * TILE_BYTES + 2 * TILE_BYTES + 2 * 8192 + 1024 + 128;
+// One CTA of 128 threads per (batch, chunk, head) tile; thread t owns row t of the chunk.
+// The kernel is a chain of four MMA phases with element-wise work between them, so a single
+// tile cannot keep an SM busy; what matters is how many tiles an SM holds at once.  Shared
+// memory is therefore kept to 112 KiB and TMEM to 256 columns, so that TWO CTAs fit per SM:
+//
+//   smem: B0 Qr | B1 Kr | B2 dy -> dlocal -> tanh(U) | B3 dmem/8 -> V -> tanh(Kr) | sP (32K: P -> dS)
+//         | sSt (8K) | sDW (8K) | barriers
+//   TMEM: [0,128) S -> O (first 64) -> dP -> dKr (first 64) + dtK (last 64)
+//         [128,192) Mem -> dV -> dtU        [192,256) dQr (memory part, later += attention part)
+//
+// V and U are fetched late (into buffers that earlier operands have left), each behind work that
+// hides most of the load latency.  P is stored normalised, so O and dV need no row scaling.
+constexpr int AB_THREADS = 128;
+// No alignment slack: 2 x (114816 + 1024 reserved) = 231680 <= 233472 bytes of an SM.  The dynamic
+// segment is declared 1024-byte aligned (the 128-byte swizzle needs it); the kernel checks.
+constexpr int AB_SMEM = 4 * TILE_BYTES + 2 * TILE_BYTES + 2 * 8192 + 128;
 
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(AB_THREADS, 2)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_constant__ CUtensorMap tm_state,
                 const __grid_constant__ CUtensorMap tm_dy, const __grid_constant__ CUtensorMap tm_dw,
                 const __nv_bfloat16* __restrict__ qkvgu, const float2* __restrict__ rope,
                 __nv_bfloat16* __restrict__ dqkvgu, int T, int H, int d, int* error_flag) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = align1024(smem_raw);
-  uint8_t* sQ = smem;
-  uint8_t* sK = sQ + TILE_BYTES;
-  uint8_t* sV = sK + TILE_BYTES;
-  uint8_t* sTK = sV + TILE_BYTES;
-  uint8_t* sTU = sTK + TILE_BYTES;
-  uint8_t* sDL = sTU + TILE_BYTES;
-  uint8_t* sDLs = sDL + TILE_BYTES;
-  uint8_t* sDM = sDLs + TILE_BYTES;
-  uint8_t* sP = sDM + TILE_BYTES;
+  extern __shared__ __align__(1024) uint8_t smem_ab[];
+  uint8_t* smem = smem_ab;
+  if ((smem_u32(smem) & 1023u) != 0u) {  // uniform over the CTA: nothing has been set up yet
+    if (threadIdx.x == 0 && error_flag != nullptr) atomicExch(error_flag, 7);
+    return;
+  }
+  uint8_t* sQ = smem;                    // B0
+  uint8_t* sK = sQ + TILE_BYTES;         // B1
+  uint8_t* sB2 = sK + TILE_BYTES;        // dy -> dlocal -> tanh(U)
+  uint8_t* sB3 = sB2 + TILE_BYTES;       // dmem/8 -> V -> tanh(Kr)
+  uint8_t* sP = sB3 + TILE_BYTES;
   uint8_t* sSt = sP + 2 * TILE_BYTES;
   uint8_t* sDW = sSt + 8192;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sDW + 8192);
@@ -212,90 +224,118 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_const
   const int row0 = b * T + n * CHUNK;
 
   if (tid == 0) {
-    for (int i = 0; i < 5; ++i) mbar_init(&bars[i], 1);
+    for (int i = 0; i < 7; ++i) mbar_init(&bars[i], 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
   if (warp == 0) {
-    tmem_alloc(tmem_slot, 512);
+    tmem_alloc(tmem_slot, 256);
     tmem_relinquish();
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t t_s = tmem;          // S, later dP            (128 cols)
-  const uint32_t t_o = tmem + 128;    // O, later dtK           (64)
-  const uint32_t t_m = tmem + 192;    // Mem, later dtU         (64)
-  const uint32_t t_dv = tmem + 256;   // dV                     (64)
-  const uint32_t t_dq = tmem + 320;   // dQr                    (64)
-  const uint32_t t_dk = tmem + 384;   // dKr (attention part)   (64)
+  const uint32_t t_lo = tmem;          // S / O / dP / dKr+dtK
+  const uint32_t t_mid = tmem + 128;   // Mem / dV / dtU
+  const uint32_t t_dq = tmem + 192;    // dQr
   const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
 
   if (tid == 0) {
-    mbar_expect_tx(&bars[0], 6 * TILE_BYTES + 2 * 8192);
+    mbar_expect_tx(&bars[0], 3 * TILE_BYTES + 2 * 8192);
     tma_load_2d(sQ, &tm_qkvgu, &bars[0], 0 * d + h * HD, row0);
     tma_load_2d(sK, &tm_qkvgu, &bars[0], 1 * d + h * HD, row0);
-    tma_load_2d(sV, &tm_qkvgu, &bars[0], 2 * d + h * HD, row0);
-    tma_load_2d(sTK, &tm_qkvgu, &bars[0], 1 * d + h * HD, row0);
-    tma_load_2d(sTU, &tm_qkvgu, &bars[0], 4 * d + h * HD, row0);
-    tma_load_2d(sDL, &tm_dy, &bars[0], h * HD, row0);
+    tma_load_2d(sB2, &tm_dy, &bars[0], h * HD, row0);
     tma_load_2d(sSt, &tm_state, &bars[0], 0, tile * HD);
     tma_load_2d(sDW, &tm_dw, &bars[0], 0, tile * HD);
   }
+  const size_t grow = static_cast<size_t>(row0 + tid);
+  const __nv_bfloat16* gate = qkvgu + grow * (5 * static_cast<size_t>(d)) + 3 * d + h * HD;
+  __nv_bfloat16* dout = dqkvgu + grow * (5 * static_cast<size_t>(d)) + h * HD;
+
   bool ok = mbar_wait(&bars[0], 0, abort_flag);
   if (ok) {
     rope_tanh_row(sQ, tid, rope, true, false);
     rope_tanh_row(sK, tid, rope, true, false);
-    rope_tanh_row(sTK, tid, rope, true, true);
-    rope_tanh_row(sTU, tid, rope, false, true);
+    // dmem/8 = dy * (1 - sigmoid(gate)) / 8  -> B3
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint4 dyq = *reinterpret_cast<const uint4*>(tile_chunk(sB2, tid, j));
+      const uint4 gq = *reinterpret_cast<const uint4*>(gate + j * 8);
+      const __nv_bfloat162* dyb = reinterpret_cast<const __nv_bfloat162*>(&dyq);
+      const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&gq);
+      uint4 o;
+      uint32_t* wo = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float2 dyv = __bfloat1622float2(dyb[t]);
+        const float2 gf = __bfloat1622float2(gb[t]);
+        wo[t] = pack_bf16x2(dyv.x * (1.f - sigmoid_f(gf.x)) * 0.125f, dyv.y * (1.f - sigmoid_f(gf.y)) * 0.125f);
+      }
+      *reinterpret_cast<uint4*>(tile_chunk(sB3, tid, j)) = o;
+    }
   }
   fence_proxy_async_smem();
   __syncthreads();
-  // ---- MMA 1: S = Qr Kr^T, Mem = Qr State
+  // ---- MMA A: S = Qr Kr^T, Mem = Qr State, dQr = (dmem/8) State^T
   if (tid == 0 && ok) {
     constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
     constexpr uint32_t idesc_m = make_idesc_bf16(128, 64, false, true);
+    constexpr uint32_t idesc_kk64 = make_idesc_bf16(128, 64, false, false);
 #pragma unroll
     for (int k = 0; k < HD / 16; ++k)
-      umma_bf16(t_s, make_smem_desc_sw128(smem_u32(sQ) + k * 32, 0, 1024),
+      umma_bf16(t_lo, make_smem_desc_sw128(smem_u32(sQ) + k * 32, 0, 1024),
                 make_smem_desc_sw128(smem_u32(sK) + k * 32, 0, 1024), idesc_s, k > 0);
 #pragma unroll
     for (int k = 0; k < HD / 16; ++k)
-      umma_bf16(t_m, make_smem_desc_sw128(smem_u32(sQ) + k * 32, 0, 1024),
+      umma_bf16(t_mid, make_smem_desc_sw128(smem_u32(sQ) + k * 32, 0, 1024),
                 make_smem_desc_sw128(smem_u32(sSt) + k * 2048, 0, 1024), idesc_m, k > 0);
+#pragma unroll
+    for (int k = 0; k < HD / 16; ++k)
+      umma_bf16(t_dq, make_smem_desc_sw128(smem_u32(sB3) + k * 32, 0, 1024),
+                make_smem_desc_sw128(smem_u32(sSt) + k * 32, 0, 1024), idesc_kk64, k > 0);
     umma_commit(&bars[1]);
   }
   ok = ok && mbar_wait(&bars[1], 0, abort_flag);
   tc_fence_after_sync();
+  if (tid == 0 && ok) {  // B3 (dmem) has been consumed: fetch V into it behind the softmax
+    mbar_expect_tx(&bars[2], TILE_BYTES);
+    tma_load_2d(sB3, &tm_qkvgu, &bars[2], 2 * d + h * HD, row0);
+  }
 
-  // ---- softmax (unnormalised P~ to smem, 1/l kept in a register)
+  // ---- softmax: max, sum, then normalised P (BF16) to smem
   const float kScale = 0.125f * 1.4426950408889634f;
   const int last_chunk = warp;
   float row_max = -INFINITY;
   for (int cc = 0; cc <= last_chunk; ++cc) {
     uint32_t r[32];
-    tmem_ld_32x32b_x32(t_s + lane_base + cc * 32, r);
+    tmem_ld_32x32b_x32(t_lo + lane_base + cc * 32, r);
     tmem_ld_wait();
 #pragma unroll
     for (int j = 0; j < 32; ++j)
       if (cc * 32 + j <= tid) row_max = fmaxf(row_max, __uint_as_float(r[j]));
   }
   float row_sum = 0.f;
+  for (int cc = 0; cc <= last_chunk; ++cc) {
+    uint32_t r[32];
+    tmem_ld_32x32b_x32(t_lo + lane_base + cc * 32, r);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (cc * 32 + j <= tid) row_sum += exp2f((__uint_as_float(r[j]) - row_max) * kScale);
+  }
+  const float inv_l = 1.f / row_sum;
   for (int cc = 0; cc < 4; ++cc) {
     uint32_t pk[16];
     if (cc <= last_chunk) {
       uint32_t r[32];
-      tmem_ld_32x32b_x32(t_s + lane_base + cc * 32, r);
+      tmem_ld_32x32b_x32(t_lo + lane_base + cc * 32, r);
       tmem_ld_wait();
 #pragma unroll
       for (int j = 0; j < 32; j += 2) {
-        const float p0 = (cc * 32 + j <= tid) ? exp2f((__uint_as_float(r[j]) - row_max) * kScale) : 0.f;
-        const float p1 = (cc * 32 + j + 1 <= tid) ? exp2f((__uint_as_float(r[j + 1]) - row_max) * kScale) : 0.f;
-        const __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
-        const float2 back = __bfloat1622float2(v);
-        row_sum += back.x + back.y;
-        pk[j >> 1] = *reinterpret_cast<const uint32_t*>(&v);
+        const float p0 = (cc * 32 + j <= tid) ? exp2f((__uint_as_float(r[j]) - row_max) * kScale) * inv_l : 0.f;
+        const float p1 = (cc * 32 + j + 1 <= tid) ? exp2f((__uint_as_float(r[j + 1]) - row_max) * kScale) * inv_l : 0.f;
+        pk[j >> 1] = pack_bf16x2(p0, p1);
       }
     } else {
 #pragma unroll
@@ -303,159 +343,178 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_const
     }
     store_row_chunk32(sP, tid, cc * 32, pk);
   }
-  const float inv_l = 1.f / row_sum;
   tc_fence_before_sync();
   fence_proxy_async_smem();
   __syncthreads();
-  // ---- MMA 2: O~ = P~ V
+  // ---- MMA B: O = P V
   if (tid == 0 && ok) {
-    tc_fence_after_sync();
-    constexpr uint32_t idesc_o = make_idesc_bf16(128, 64, false, true);
+    ok = mbar_wait(&bars[2], 0, abort_flag);  // V has landed
+    if (ok) {
+      tc_fence_after_sync();
+      constexpr uint32_t idesc_o = make_idesc_bf16(128, 64, false, true);
 #pragma unroll
-    for (int k = 0; k < CHUNK / 16; ++k)
-      umma_bf16(t_o, make_smem_desc_sw128(smem_u32(sP) + (k >> 2) * TILE_BYTES + (k & 3) * 32, 0, 1024),
-                make_smem_desc_sw128(smem_u32(sV) + k * 2048, 0, 1024), idesc_o, k > 0);
-    umma_commit(&bars[2]);
+      for (int k = 0; k < CHUNK / 16; ++k)
+        umma_bf16(t_lo, make_smem_desc_sw128(smem_u32(sP) + (k >> 2) * TILE_BYTES + (k & 3) * 32, 0, 1024),
+                  make_smem_desc_sw128(smem_u32(sB3) + k * 2048, 0, 1024), idesc_o, k > 0);
+      umma_commit(&bars[3]);
+    }
   }
-  ok = ok && mbar_wait(&bars[2], 0, abort_flag);
+  ok = mbar_wait(&bars[3], 0, abort_flag) && ok;
   tc_fence_after_sync();
 
-  // ---- element-wise stage 1: gate, dlocal, dmem, dGate, D = sum(dlocal * local)
-  const size_t grow = static_cast<size_t>(row0 + tid);
-  const __nv_bfloat16* gate = qkvgu + grow * (5 * static_cast<size_t>(d)) + 3 * d + h * HD;
-  __nv_bfloat16* dout = dqkvgu + grow * (5 * static_cast<size_t>(d)) + h * HD;
+  // ---- element-wise stage 1: dlocal = dy * g (in place in B2), dGate, D = sum(dlocal * local)
   float Drow = 0.f;
 #pragma unroll
   for (int c = 0; c < HD; c += 16) {
     uint32_t ro[16], rm[16];
-    tmem_ld_32x32b_x16(t_o + lane_base + c, ro);
-    tmem_ld_32x32b_x16(t_m + lane_base + c, rm);
+    tmem_ld_32x32b_x16(t_lo + lane_base + c, ro);
+    tmem_ld_32x32b_x16(t_mid + lane_base + c, rm);
     tmem_ld_wait();
 #pragma unroll
     for (int j = 0; j < 16; j += 8) {
       const int chunk = (c + j) >> 3;
-      uint4* pdl = reinterpret_cast<uint4*>(tile_chunk(sDL, tid, chunk));
+      uint4* pdl = reinterpret_cast<uint4*>(tile_chunk(sB2, tid, chunk));
       const uint4 dyq = *pdl;
       const uint4 gq = *reinterpret_cast<const uint4*>(gate + c + j);
       const __nv_bfloat162* dyb = reinterpret_cast<const __nv_bfloat162*>(&dyq);
       const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&gq);
-      uint4 o_dl, o_dls, o_dm, o_dg;
+      uint4 o_dl, o_dg;
       uint32_t* w_dl = reinterpret_cast<uint32_t*>(&o_dl);
-      uint32_t* w_dls = reinterpret_cast<uint32_t*>(&o_dls);
-      uint32_t* w_dm = reinterpret_cast<uint32_t*>(&o_dm);
       uint32_t* w_dg = reinterpret_cast<uint32_t*>(&o_dg);
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
         const float2 dyv = __bfloat1622float2(dyb[t]);
         const float2 gf = __bfloat1622float2(gb[t]);
         const float g0 = sigmoid_f(gf.x), g1 = sigmoid_f(gf.y);
-        const float l0 = __uint_as_float(ro[j + 2 * t]) * inv_l, l1 = __uint_as_float(ro[j + 2 * t + 1]) * inv_l;
+        const float l0 = __uint_as_float(ro[j + 2 * t]), l1 = __uint_as_float(ro[j + 2 * t + 1]);
         const float m0 = __uint_as_float(rm[j + 2 * t]) * 0.125f, m1 = __uint_as_float(rm[j + 2 * t + 1]) * 0.125f;
         const float dl0 = dyv.x * g0, dl1 = dyv.y * g1;
         Drow += dl0 * l0 + dl1 * l1;
         w_dl[t] = pack_bf16x2(dl0, dl1);
-        w_dls[t] = pack_bf16x2(dl0 * inv_l, dl1 * inv_l);
-        w_dm[t] = pack_bf16x2(dyv.x * (1.f - g0) * 0.125f, dyv.y * (1.f - g1) * 0.125f);
         w_dg[t] = pack_bf16x2(dyv.x * (l0 - m0) * g0 * (1.f - g0), dyv.y * (l1 - m1) * g1 * (1.f - g1));
       }
       *pdl = o_dl;
-      *reinterpret_cast<uint4*>(tile_chunk(sDLs, tid, chunk)) = o_dls;
-      *reinterpret_cast<uint4*>(tile_chunk(sDM, tid, chunk)) = o_dm;
       if (ok) *reinterpret_cast<uint4*>(dout + 3 * d + c + j) = o_dg;
     }
   }
   tc_fence_before_sync();
   fence_proxy_async_smem();
   __syncthreads();
-  // ---- MMA 3: dP, dV, dQr(memory part), dtK, dtU
+  // ---- MMA C: dP = dlocal V^T, dV = P^T dlocal
   if (tid == 0 && ok) {
     tc_fence_after_sync();
     constexpr uint32_t idesc_kk128 = make_idesc_bf16(128, 128, false, false);
-    constexpr uint32_t idesc_kk64 = make_idesc_bf16(128, 64, false, false);
-    constexpr uint32_t idesc_kmn64 = make_idesc_bf16(128, 64, false, true);
     constexpr uint32_t idesc_mnmn64 = make_idesc_bf16(128, 64, true, true);
 #pragma unroll
-    for (int k = 0; k < HD / 16; ++k)  // dP = dlocal V^T
-      umma_bf16(t_s, make_smem_desc_sw128(smem_u32(sDL) + k * 32, 0, 1024),
-                make_smem_desc_sw128(smem_u32(sV) + k * 32, 0, 1024), idesc_kk128, k > 0);
+    for (int k = 0; k < HD / 16; ++k)
+      umma_bf16(t_lo, make_smem_desc_sw128(smem_u32(sB2) + k * 32, 0, 1024),
+                make_smem_desc_sw128(smem_u32(sB3) + k * 32, 0, 1024), idesc_kk128, k > 0);
 #pragma unroll
-    for (int k = 0; k < CHUNK / 16; ++k)  // dV = P~^T (dlocal / l)
-      umma_bf16(t_dv, make_smem_desc_sw128(smem_u32(sP) + k * 2048, TILE_BYTES, 1024),
-                make_smem_desc_sw128(smem_u32(sDLs) + k * 2048, 0, 1024), idesc_mnmn64, k > 0);
-#pragma unroll
-    for (int k = 0; k < HD / 16; ++k)  // dQr = (dmem/8) State^T
-      umma_bf16(t_dq, make_smem_desc_sw128(smem_u32(sDM) + k * 32, 0, 1024),
-                make_smem_desc_sw128(smem_u32(sSt) + k * 32, 0, 1024), idesc_kk64, k > 0);
-#pragma unroll
-    for (int k = 0; k < HD / 16; ++k)  // dtK = tU dW^T
-      umma_bf16(t_o, make_smem_desc_sw128(smem_u32(sTU) + k * 32, 0, 1024),
-                make_smem_desc_sw128(smem_u32(sDW) + k * 32, 0, 1024), idesc_kk64, k > 0);
-#pragma unroll
-    for (int k = 0; k < HD / 16; ++k)  // dtU = tK dW
-      umma_bf16(t_m, make_smem_desc_sw128(smem_u32(sTK) + k * 32, 0, 1024),
-                make_smem_desc_sw128(smem_u32(sDW) + k * 2048, 0, 1024), idesc_kmn64, k > 0);
-    umma_commit(&bars[3]);
+    for (int k = 0; k < CHUNK / 16; ++k)
+      umma_bf16(t_mid, make_smem_desc_sw128(smem_u32(sP) + k * 2048, TILE_BYTES, 1024),
+                make_smem_desc_sw128(smem_u32(sB2) + k * 2048, 0, 1024), idesc_mnmn64, k > 0);
+    umma_commit(&bars[4]);
   }
-  ok = ok && mbar_wait(&bars[3], 0, abort_flag);
+  ok = mbar_wait(&bars[4], 0, abort_flag) && ok;
   tc_fence_after_sync();
+  if (tid == 0 && ok) {  // B2 (dlocal) has been consumed: fetch U into it behind the dS phase
+    mbar_expect_tx(&bars[5], TILE_BYTES);
+    tma_load_2d(sB2, &tm_qkvgu, &bars[5], 4 * d + h * HD, row0);
+  }
 
-  // ---- dS = P~/l * (dP - D) / 8, written over P~
+  // ---- dS = P * (dP - D) / 8 over P; dV out; tanh(Kr) -> B3
   for (int cc = 0; cc <= last_chunk; ++cc) {
     uint32_t r[32], pk[16];
-    tmem_ld_32x32b_x32(t_s + lane_base + cc * 32, r);
+    tmem_ld_32x32b_x32(t_lo + lane_base + cc * 32, r);
     load_row_chunk32(sP, tid, cc * 32, pk);
     tmem_ld_wait();
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
-      const float2 p = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pk[j]));
-      const float s0 = p.x * inv_l * (__uint_as_float(r[2 * j]) - Drow) * 0.125f;
-      const float s1 = p.y * inv_l * (__uint_as_float(r[2 * j + 1]) - Drow) * 0.125f;
+      const float2 pv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pk[j]));
+      const float s0 = pv.x * (__uint_as_float(r[2 * j]) - Drow) * 0.125f;
+      const float s1 = pv.y * (__uint_as_float(r[2 * j + 1]) - Drow) * 0.125f;
       pk[j] = pack_bf16x2(s0, s1);
     }
     store_row_chunk32(sP, tid, cc * 32, pk);
   }
+#pragma unroll
+  for (int c = 0; c < HD; c += 16) {
+    uint32_t rv[16];
+    tmem_ld_32x32b_x16(t_mid + lane_base + c, rv);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 16; j += 8) {
+      const uint4 o_v = make_uint4(pack_bf16x2(__uint_as_float(rv[j]), __uint_as_float(rv[j + 1])),
+                                   pack_bf16x2(__uint_as_float(rv[j + 2]), __uint_as_float(rv[j + 3])),
+                                   pack_bf16x2(__uint_as_float(rv[j + 4]), __uint_as_float(rv[j + 5])),
+                                   pack_bf16x2(__uint_as_float(rv[j + 6]), __uint_as_float(rv[j + 7])));
+      if (ok) *reinterpret_cast<uint4*>(dout + 2 * d + c + j) = o_v;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {  // tanh(Kr) -> B3 (V is no longer needed)
+    const uint4 kq = *reinterpret_cast<const uint4*>(tile_chunk(sK, tid, j));
+    const __nv_bfloat162* kb = reinterpret_cast<const __nv_bfloat162*>(&kq);
+    uint4 o;
+    uint32_t* wo = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const float2 kv = __bfloat1622float2(kb[t]);
+      wo[t] = pack_bf16x2(tanh_fast(kv.x), tanh_fast(kv.y));
+    }
+    *reinterpret_cast<uint4*>(tile_chunk(sB3, tid, j)) = o;
+  }
+  ok = mbar_wait(&bars[5], 0, abort_flag) && ok;  // U has landed
+  if (ok) rope_tanh_row(sB2, tid, rope, false, true);
   tc_fence_before_sync();
   fence_proxy_async_smem();
   __syncthreads();
-  // ---- MMA 4: dQr += dS Kr, dKr = dS^T Qr
+  // ---- MMA D: dQr += dS Kr, dKr = dS^T Qr, dtK = tU dW^T, dtU = tK dW
   if (tid == 0 && ok) {
     tc_fence_after_sync();
     constexpr uint32_t idesc_kmn64 = make_idesc_bf16(128, 64, false, true);
     constexpr uint32_t idesc_mnmn64 = make_idesc_bf16(128, 64, true, true);
+    constexpr uint32_t idesc_kk64 = make_idesc_bf16(128, 64, false, false);
 #pragma unroll
     for (int k = 0; k < CHUNK / 16; ++k)
       umma_bf16(t_dq, make_smem_desc_sw128(smem_u32(sP) + (k >> 2) * TILE_BYTES + (k & 3) * 32, 0, 1024),
                 make_smem_desc_sw128(smem_u32(sK) + k * 2048, 0, 1024), idesc_kmn64, 1u);
 #pragma unroll
     for (int k = 0; k < CHUNK / 16; ++k)
-      umma_bf16(t_dk, make_smem_desc_sw128(smem_u32(sP) + k * 2048, TILE_BYTES, 1024),
+      umma_bf16(t_lo, make_smem_desc_sw128(smem_u32(sP) + k * 2048, TILE_BYTES, 1024),
                 make_smem_desc_sw128(smem_u32(sQ) + k * 2048, 0, 1024), idesc_mnmn64, k > 0);
-    umma_commit(&bars[4]);
+#pragma unroll
+    for (int k = 0; k < HD / 16; ++k)  // dtK = tU dW^T
+      umma_bf16(t_lo + 64, make_smem_desc_sw128(smem_u32(sB2) + k * 32, 0, 1024),
+                make_smem_desc_sw128(smem_u32(sDW) + k * 32, 0, 1024), idesc_kk64, k > 0);
+#pragma unroll
+    for (int k = 0; k < HD / 16; ++k)  // dtU = tK dW
+      umma_bf16(t_mid, make_smem_desc_sw128(smem_u32(sB3) + k * 32, 0, 1024),
+                make_smem_desc_sw128(smem_u32(sDW) + k * 2048, 0, 1024), idesc_kmn64, k > 0);
+    umma_commit(&bars[6]);
   }
-  ok = ok && mbar_wait(&bars[4], 0, abort_flag);
+  ok = mbar_wait(&bars[6], 0, abort_flag) && ok;
   tc_fence_after_sync();
 
-  // ---- final: dQ, dK (RoPE transpose), dV, dU
+  // ---- final: dQ, dK (RoPE transpose), dU
 #pragma unroll
   for (int c = 0; c < HD; c += 16) {
-    uint32_t rq[16], rk[16], rv[16], rtk[16], rtu[16];
+    uint32_t rq[16], rk[16], rtk[16], rtu[16];
     tmem_ld_32x32b_x16(t_dq + lane_base + c, rq);
-    tmem_ld_32x32b_x16(t_dk + lane_base + c, rk);
-    tmem_ld_32x32b_x16(t_dv + lane_base + c, rv);
-    tmem_ld_32x32b_x16(t_o + lane_base + c, rtk);
-    tmem_ld_32x32b_x16(t_m + lane_base + c, rtu);
+    tmem_ld_32x32b_x16(t_lo + lane_base + c, rk);
+    tmem_ld_32x32b_x16(t_lo + 64 + lane_base + c, rtk);
+    tmem_ld_32x32b_x16(t_mid + lane_base + c, rtu);
     tmem_ld_wait();
 #pragma unroll
     for (int j = 0; j < 16; j += 8) {
       const int chunk = (c + j) >> 3;
-      const uint4 tkq = *reinterpret_cast<const uint4*>(tile_chunk(sTK, tid, chunk));
-      const uint4 tuq = *reinterpret_cast<const uint4*>(tile_chunk(sTU, tid, chunk));
+      const uint4 tkq = *reinterpret_cast<const uint4*>(tile_chunk(sB3, tid, chunk));
+      const uint4 tuq = *reinterpret_cast<const uint4*>(tile_chunk(sB2, tid, chunk));
       const __nv_bfloat162* tkb = reinterpret_cast<const __nv_bfloat162*>(&tkq);
       const __nv_bfloat162* tub = reinterpret_cast<const __nv_bfloat162*>(&tuq);
-      uint4 o_q, o_k, o_v, o_u;
+      uint4 o_q, o_k, o_u;
       uint32_t* w_q = reinterpret_cast<uint32_t*>(&o_q);
       uint32_t* w_k = reinterpret_cast<uint32_t*>(&o_k);
-      uint32_t* w_v = reinterpret_cast<uint32_t*>(&o_v);
       uint32_t* w_u = reinterpret_cast<uint32_t*>(&o_u);
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
@@ -469,14 +528,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_const
         const float k0 = __uint_as_float(rk[e0]) + __uint_as_float(rtk[e0]) * (1.f / CHUNK) * (1.f - tk.x * tk.x);
         const float k1 = __uint_as_float(rk[e1]) + __uint_as_float(rtk[e1]) * (1.f / CHUNK) * (1.f - tk.y * tk.y);
         w_k[t] = pack_bf16x2(k0 * cs.x + k1 * cs.y, k1 * cs.x - k0 * cs.y);
-        w_v[t] = pack_bf16x2(__uint_as_float(rv[e0]), __uint_as_float(rv[e1]));
         w_u[t] = pack_bf16x2(__uint_as_float(rtu[e0]) * (1.f / CHUNK) * (1.f - tu.x * tu.x),
                              __uint_as_float(rtu[e1]) * (1.f / CHUNK) * (1.f - tu.y * tu.y));
       }
       if (ok) {
         *reinterpret_cast<uint4*>(dout + 0 * d + c + j) = o_q;
         *reinterpret_cast<uint4*>(dout + 1 * d + c + j) = o_k;
-        *reinterpret_cast<uint4*>(dout + 2 * d + c + j) = o_v;
         *reinterpret_cast<uint4*>(dout + 4 * d + c + j) = o_u;
       }
     }
@@ -486,7 +543,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_const
   if (tid == 0 && *abort_flag != 0 && error_flag != nullptr) atomicExch(error_flag, 5);
   if (warp == 0) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem, 512);
+    tmem_dealloc(tmem, 256);
   }
 }
 
@@ -547,7 +604,7 @@ extern "C" int ws_attn_bwd(const void* qkvgu, const void* states, const void* dy
       return -20;
     configured = true;
   }
-  attn_bwd_kernel<<<tiles, 128, AB_SMEM, stream>>>(tm, ts, td, tw, (const __nv_bfloat16*)qkvgu,
+  attn_bwd_kernel<<<tiles, AB_THREADS, AB_SMEM, stream>>>(tm, ts, td, tw, (const __nv_bfloat16*)qkvgu,
                                                    reinterpret_cast<const float2*>(rope), (__nv_bfloat16*)dqkvgu, T,
                                                    H, d, error_flag);
   ws_count_launch();

@@ -88,78 +88,105 @@ rmsnorm_fwd_kernel(const T* __restrict__ x, const float* __restrict__ col_scale,
 // --------------------------------------------------------------------------- RMSNorm backward
 // dxn = rstd * (dz*w - x_hat * mean(dz*w*x_hat));  out = (dres + dxn) * (1 + out_scale)
 // dw_partial[block] = sum over the block's rows of dz * x_hat.
+//
+// Column-owner layout: thread t owns columns 8t .. 8t+7 (256 threads cover d <= 2048) and the
+// block walks over groups of RB_ROWS rows, so every operand is read from global memory exactly
+// once with 16/32-byte coalesced accesses, the per-row mean needs one block reduction per group
+// (double-buffered, one __syncthreads), and the weight-gradient column sums stay in 8 registers.
+constexpr int RB_ROWS = 4;
+
 template <typename T>
-__global__ void __launch_bounds__(ROW_THREADS)
+__device__ __forceinline__ void ld8(const T* p, float (&v)[8]) {
+  const float4 a = ld4(p), b = ld4(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <typename T>
+__device__ __forceinline__ void st8(T* p, const float (&v)[8]) {
+  st4(p, make_float4(v[0], v[1], v[2], v[3]));
+  st4(p + 4, make_float4(v[4], v[5], v[6], v[7]));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(ROW_THREADS, 2)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dz, const T* __restrict__ x,
                    const float* __restrict__ rstd_in, const float* __restrict__ w,
                    const T* __restrict__ dres, const float* __restrict__ out_scale, int rows, int d,
                    T* __restrict__ dx_out, __nv_bfloat16* __restrict__ dx_bf16,
                    float* __restrict__ dw_partial) {
-  __shared__ float red[ROW_WARPS][128];
+  __shared__ float red[2][RB_ROWS][ROW_WARPS];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nchunk = d / 128;
-  float4 acc[MAX_CHUNKS];
-#pragma unroll
-  for (int i = 0; i < MAX_CHUNKS; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  const int c = threadIdx.x * 8;
+  const bool active = c < d;
   const float inv_d = 1.0f / static_cast<float>(d);
-
-  for (int row = blockIdx.x * ROW_WARPS + warp; row < rows; row += gridDim.x * ROW_WARPS) {
-    const size_t base = static_cast<size_t>(row) * d;
-    const float rstd = rstd_in[row];
-    float dot = 0.f;
+  float wv[8], sv[8], acc[8];
 #pragma unroll
-    for (int i = 0; i < MAX_CHUNKS; ++i) {
-      if (i < nchunk) {
-        const int c = lane * 4 + i * 128;
-        const float4 g = ld4(dz + base + c);
-        const float4 xv = ld4(x + base + c);
-        const float4 ww = ld4(w + c);
-        dot += g.x * ww.x * xv.x + g.y * ww.y * xv.y + g.z * ww.z * xv.z + g.w * ww.w * xv.w;
+  for (int j = 0; j < 8; ++j) { wv[j] = 0.f; sv[j] = 1.f; acc[j] = 0.f; }
+  if (active) {
+    ld8(w + c, wv);
+    if (out_scale != nullptr) {
+      ld8(out_scale + c, sv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sv[j] += 1.f;
+    }
+  }
+  int it = 0;
+  for (int row0 = blockIdx.x * RB_ROWS; row0 < rows; row0 += gridDim.x * RB_ROWS, ++it) {
+    float g[RB_ROWS][8], xh[RB_ROWS][8], rs[RB_ROWS], part[RB_ROWS];
+#pragma unroll
+    for (int r = 0; r < RB_ROWS; ++r) {
+      const int row = row0 + r;
+      part[r] = 0.f;
+      rs[r] = 0.f;
+      if (row < rows && active) {
+        const size_t base = static_cast<size_t>(row) * d + c;
+        ld8(dz + base, g[r]);
+        ld8(x + base, xh[r]);
+        rs[r] = rstd_in[row];
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { g[r][j] = 0.f; xh[r][j] = 0.f; }
       }
     }
-    dot = warp_sum(dot) * rstd * inv_d;  // mean(dz*w*x_hat)
 #pragma unroll
-    for (int i = 0; i < MAX_CHUNKS; ++i) {
-      if (i < nchunk) {
-        const int c = lane * 4 + i * 128;
-        const float4 g = ld4(dz + base + c);
-        const float4 xv = ld4(x + base + c);
-        const float4 ww = ld4(w + c);
-        float4 xh = make_float4(xv.x * rstd, xv.y * rstd, xv.z * rstd, xv.w * rstd);
-        acc[i].x += g.x * xh.x; acc[i].y += g.y * xh.y; acc[i].z += g.z * xh.z; acc[i].w += g.w * xh.w;
-        float4 o;
-        o.x = rstd * (g.x * ww.x - xh.x * dot); o.y = rstd * (g.y * ww.y - xh.y * dot);
-        o.z = rstd * (g.z * ww.z - xh.z * dot); o.w = rstd * (g.w * ww.w - xh.w * dot);
+    for (int r = 0; r < RB_ROWS; ++r) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        xh[r][j] *= rs[r];
+        part[r] += g[r][j] * wv[j] * xh[r][j];
+      }
+      part[r] = warp_sum(part[r]);
+      if (lane == 0) red[it & 1][r][warp] = part[r];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < RB_ROWS; ++r) {
+      const int row = row0 + r;
+      if (row < rows && active) {
+        float dot = 0.f;
+#pragma unroll
+        for (int wi = 0; wi < ROW_WARPS; ++wi) dot += red[it & 1][r][wi];
+        dot *= inv_d;  // mean(dz * w * x_hat)
+        const size_t base = static_cast<size_t>(row) * d + c;
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          acc[j] += g[r][j] * xh[r][j];
+          o[j] = rs[r] * (g[r][j] * wv[j] - xh[r][j] * dot);
+        }
         if (dres != nullptr) {
-          const float4 r = ld4(dres + base + c);
-          o.x += r.x; o.y += r.y; o.z += r.z; o.w += r.w;
+          float rr[8];
+          ld8(dres + base, rr);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += rr[j];
         }
-        if (out_scale != nullptr) {
-          const float4 s = ld4(out_scale + c);
-          o.x *= 1.f + s.x; o.y *= 1.f + s.y; o.z *= 1.f + s.z; o.w *= 1.f + s.w;
-        }
-        st4(dx_out + base + c, o);
-        if (dx_bf16 != nullptr) st4(dx_bf16 + base + c, o);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] *= sv[j];
+        st8(dx_out + base, o);
+        if (dx_bf16 != nullptr) st8(dx_bf16 + base, o);
       }
     }
   }
-  // Block reduction of the column sums, one 128-column chunk at a time.
-  if (dw_partial != nullptr) {
-#pragma unroll
-    for (int i = 0; i < MAX_CHUNKS; ++i) {
-      if (i < nchunk) {
-        __syncthreads();
-        *reinterpret_cast<float4*>(&red[warp][lane * 4]) = acc[i];
-        __syncthreads();
-        if (threadIdx.x < 128) {
-          float s = 0.f;
-#pragma unroll
-          for (int wgt = 0; wgt < ROW_WARPS; ++wgt) s += red[wgt][threadIdx.x];
-          dw_partial[static_cast<size_t>(blockIdx.x) * d + i * 128 + threadIdx.x] = s;
-        }
-      }
-    }
-  }
+  if (dw_partial != nullptr && active) st8(dw_partial + static_cast<size_t>(blockIdx.x) * d + c, acc);
 }
 
 // --------------------------------------------------------------------------- column sums
@@ -187,18 +214,38 @@ colsum2_kernel(const T* __restrict__ a, const T* __restrict__ b, int rows, int d
 }
 
 // out[c] = beta*out[c] + scale(c) * sum_p partial[p][c];  scale(c) = 1/(1+inv_scale[c]) if given
-__global__ void colsum_finalize_kernel(const float* __restrict__ partial, int parts, int d,
-                                       const float* __restrict__ inv_scale, float beta,
-                                       float* __restrict__ out) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= d) return;
-  float s = 0.f;
-  for (int p = 0; p < parts; ++p) s += partial[static_cast<size_t>(p) * d + c];
-  if (inv_scale != nullptr) {
-    const float den = 1.f + inv_scale[c];
-    s = den != 0.f ? s / den : 0.f;
+// One block per 32 columns; warp w sums parts w, w+8, ... (independent 128-byte loads in
+// flight), then the eight warp sums are combined in a fixed order: the result is deterministic.
+constexpr int FIN_COLS = 32;
+__global__ void __launch_bounds__(ROW_THREADS)
+colsum_finalize_kernel(const float* __restrict__ partial, int parts, int d,
+                       const float* __restrict__ inv_scale, float beta, float* __restrict__ out) {
+  __shared__ float red[ROW_WARPS][FIN_COLS];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c = blockIdx.x * FIN_COLS + lane;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  if (c < d) {
+    int p = warp;
+    for (; p + 3 * ROW_WARPS < parts; p += 4 * ROW_WARPS) {
+      s0 += partial[static_cast<size_t>(p) * d + c];
+      s1 += partial[static_cast<size_t>(p + ROW_WARPS) * d + c];
+      s2 += partial[static_cast<size_t>(p + 2 * ROW_WARPS) * d + c];
+      s3 += partial[static_cast<size_t>(p + 3 * ROW_WARPS) * d + c];
+    }
+    for (; p < parts; p += ROW_WARPS) s0 += partial[static_cast<size_t>(p) * d + c];
   }
-  out[c] = (beta != 0.f ? beta * out[c] : 0.f) + s;
+  red[warp][lane] = (s0 + s1) + (s2 + s3);
+  __syncthreads();
+  if (warp == 0 && c < d) {
+    float s = 0.f;
+#pragma unroll
+    for (int wi = 0; wi < ROW_WARPS; ++wi) s += red[wi][lane];
+    if (inv_scale != nullptr) {
+      const float den = 1.f + inv_scale[c];
+      s = den != 0.f ? s / den : 0.f;
+    }
+    out[c] = (beta != 0.f ? beta * out[c] : 0.f) + s;
+  }
 }
 
 // --------------------------------------------------------------------------- casts
@@ -279,15 +326,15 @@ extern "C" int ws_rmsnorm_fwd(const void* x, int x_bf16, const float* col_scale,
 
 // Number of partial rows ws_rmsnorm_bwd writes (the caller sizes dw_partial as parts*d floats).
 extern "C" int ws_rmsnorm_bwd_parts(int rows) {
-  int blocks = (rows + ROW_WARPS - 1) / ROW_WARPS;
-  const int cap = 148 * 4;
+  int blocks = (rows + RB_ROWS - 1) / RB_ROWS;
+  const int cap = 148 * 2;  // two resident blocks per SM
   return blocks < cap ? (blocks > 0 ? blocks : 1) : cap;
 }
 
 extern "C" int ws_rmsnorm_bwd(const void* dz, const void* x, int x_bf16, const float* rstd, const float* w,
                               const void* dres, const float* out_scale, int rows, int d, void* dx_out,
                               void* dx_bf16, float* dw_partial, cudaStream_t stream) {
-  if (d % 128 != 0 || d > 128 * MAX_CHUNKS || rows <= 0) return -1;
+  if (d % 128 != 0 || d > ROW_THREADS * 8 || rows <= 0) return -1;
   const int grid = ws_rmsnorm_bwd_parts(rows);
   if (x_bf16)
     rmsnorm_bwd_kernel<__nv_bfloat16><<<grid, ROW_THREADS, 0, stream>>>(
@@ -319,7 +366,7 @@ extern "C" int ws_colsum2(const void* a, const void* b, int is_bf16, int rows, i
 
 extern "C" int ws_colsum_finalize(const float* partial, int parts, int d, const float* inv_scale, float beta,
                                   float* out, cudaStream_t stream) {
-  colsum_finalize_kernel<<<(d + 255) / 256, 256, 0, stream>>>(partial, parts, d, inv_scale, beta, out);
+  colsum_finalize_kernel<<<(d + FIN_COLS - 1) / FIN_COLS, ROW_THREADS, 0, stream>>>(partial, parts, d, inv_scale, beta, out);
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
@@ -431,7 +478,7 @@ extern "C" int ws_rmsnorm_bwd_static(const void* dz, const void* x, int x_bf16, 
         (const __nv_bfloat16*)dz, (const float*)x, rstd, w, (const float*)dres, out_scale, rows, d,
         (float*)dx_out, (__nv_bfloat16*)dx_bf16, scratch);
   ws_count_launch();
-  colsum_finalize_kernel<<<(d + 255) / 256, 256, 0, stream>>>(scratch, parts, d, nullptr, 0.f, dw_out);
+  colsum_finalize_kernel<<<(d + FIN_COLS - 1) / FIN_COLS, ROW_THREADS, 0, stream>>>(scratch, parts, d, nullptr, 0.f, dw_out);
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : WS_STATIC_ERR_LAUNCH;
 }

@@ -42,7 +42,10 @@ def check_device_errors(device: torch.device | None = None) -> None:
         value = int(flag.item())
         if value != 0:
             flag.zero_()
-            raise RuntimeError(f"ws_b200 kernel on cuda:{index} reported a timed-out wait (code {value})")
+            what = {5: "attention backward: a wait timed out", 6: "CTA-pair GEMM: a wait timed out",
+                    7: "attention backward: dynamic shared memory is not 1024-byte aligned"}.get(
+                        value, "a wait timed out")
+            raise RuntimeError(f"ws_b200 kernel on cuda:{index} reported an error (code {value}: {what})")
 
 
 def _gemm(a, b, a_mn, b_mn, epi, m, n, k, out, out2=None, aux=None, row_scale=None, alpha=1.0, beta=0.0):
