@@ -108,3 +108,34 @@ def test_swiglu_forward_backward(g, m, h, k):
     ref_d = torch.cat([dact * pg * s, dact * pu * s * (1 + pg * (1 - s))], dim=-1)
     assert rel_rms(dpacked, ref_d) < 0.006
     g.check_device_errors()
+
+
+def test_grouped_weight_gradients_match_single_launches(g):
+    """Four dW problems of different shapes in one grouped launch == four separate launches, bit for bit."""
+    torch.manual_seed(7)
+    tokens = 1024
+    shapes = [(512, 256), (256, 768), (1280, 256), (304, 264)]  # ragged last tile in both directions
+    items, refs = [], []
+    for n, k in shapes:
+        dy = torch.randn(tokens, n, device="cuda").bfloat16()
+        x = torch.randn(tokens, k, device="cuda").bfloat16()
+        base = torch.randn(n, k, device="cuda")
+        single = g.grad_weight_accumulate(dy, x, base.clone(), accumulate=True)
+        refs.append(single)
+        items.append((dy, x, base.clone(), True))
+    g.grad_weight_accumulate_group(items)
+    for (dy, x, grad, _), ref in zip(items, refs):
+        assert torch.equal(grad, ref)
+        assert rel_rms(grad - 0, ref) == 0.0
+    fresh = [(dy, x, torch.full_like(grad, float("nan")), False) for dy, x, grad, _ in items]
+    g.grad_weight_accumulate_group(fresh)  # beta = 0 must ignore what was there
+    for (dy, x, grad, _) in fresh:
+        assert rel_rms(grad, dy.float().T @ x.float()) < 1e-3
+    g.check_device_errors()
+
+
+def test_misaligned_row_pitch_is_rejected(g):
+    dy = torch.zeros(64, 300, device="cuda").bfloat16()  # 600-byte pitch: not a legal TMA stride
+    x = torch.zeros(64, 264, device="cuda").bfloat16()
+    with pytest.raises(RuntimeError, match="row pitches"):
+        g.grad_weight_accumulate(dy, x, torch.zeros(300, 264, device="cuda"))

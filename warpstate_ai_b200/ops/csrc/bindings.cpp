@@ -5,6 +5,8 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 
+#include <vector>
+
 #include "ws_api.h"
 
 namespace {
@@ -34,6 +36,10 @@ void gemm(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool b_mn, int64_
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1,
               "gemm: operands must be 2-D with a contiguous last dimension");
   TORCH_CHECK(out.dim() == 2 && out.stride(1) == 1, "gemm: out must be 2-D row-major");
+  // TMA needs 16-byte aligned bases and row pitches (8 BF16 elements).
+  TORCH_CHECK(a.stride(0) % 8 == 0 && b.stride(0) % 8 == 0 &&
+              reinterpret_cast<uintptr_t>(a.data_ptr()) % 16 == 0 && reinterpret_cast<uintptr_t>(b.data_ptr()) % 16 == 0,
+              "gemm: operand row pitches must be multiples of 8 elements and bases 16-byte aligned");
   const int64_t b_rows = epilogue == WS_EPI_SWIGLU ? 2 * n : n;
   if (!a_mn) { TORCH_CHECK(a.size(0) == m && a.size(1) == k, "gemm: A must be [m,k]"); }
   else { TORCH_CHECK(a.size(0) == k && a.size(1) == m, "gemm: A must be [k,m]"); }
@@ -78,6 +84,45 @@ void gemm(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool b_mn, int64_
   g.alpha = (float)alpha; g.beta = (float)beta;
   g.error_flag = reinterpret_cast<int*>(const_cast<void*>(opt_ptr(error_flag)));
   check_rc(ws_gemm(&g, cur_stream()), "gemm");
+}
+
+// grads[i] = beta[i] * grads[i] + dy[i]^T x[i]  (FP32), all problems in one persistent launch
+// when the CTA-pair kernel can take them (up to four with >= 256 output rows each).
+void grad_weight_group(at::TensorList dys, at::TensorList xs, at::TensorList grads,
+                       at::ArrayRef<double> betas, c10::optional<at::Tensor> error_flag) {
+  const size_t count = dys.size();
+  TORCH_CHECK(count > 0 && xs.size() == count && grads.size() == count && betas.size() == count,
+              "grad_weight_group: list lengths differ");
+  std::vector<WsGemm> items(count);
+  for (size_t i = 0; i < count; ++i) {
+    const at::Tensor& dy = dys[i];
+    const at::Tensor& x = xs[i];
+    const at::Tensor& grad = grads[i];
+    TORCH_CHECK(dy.is_cuda() && x.is_cuda() && grad.is_cuda() && dy.device() == dys[0].device(),
+                "grad_weight_group: CUDA tensors on one device required");
+    TORCH_CHECK(dy.scalar_type() == at::kBFloat16 && x.scalar_type() == at::kBFloat16 && grad.scalar_type() == at::kFloat,
+                "grad_weight_group: BF16 operands and FP32 gradients required");
+    TORCH_CHECK(dy.dim() == 2 && x.dim() == 2 && grad.dim() == 2 && dy.stride(1) == 1 && x.stride(1) == 1 &&
+                grad.stride(1) == 1, "grad_weight_group: 2-D tensors with a contiguous last dimension required");
+    TORCH_CHECK(dy.size(0) == x.size(0) && grad.size(0) == dy.size(1) && grad.size(1) == x.size(1),
+                "grad_weight_group: shapes must be dy [T,N], x [T,K], grad [N,K]");
+    TORCH_CHECK(dy.stride(0) % 8 == 0 && x.stride(0) % 8 == 0 &&
+                reinterpret_cast<uintptr_t>(dy.data_ptr()) % 16 == 0 && reinterpret_cast<uintptr_t>(x.data_ptr()) % 16 == 0,
+                "grad_weight_group: operand row pitches must be multiples of 8 elements and bases 16-byte aligned");
+    WsGemm& g = items[i];
+    g.a = dy.data_ptr(); g.b = x.data_ptr();
+    g.m = (int)dy.size(1); g.n = (int)x.size(1); g.k = (int)dy.size(0);
+    g.lda = (int)dy.stride(0); g.ldb = (int)x.stride(0);
+    g.a_mn = true; g.b_mn = true; g.epilogue = WS_EPI_ACC_F32;
+    g.out = grad.data_ptr(); g.ldo = (int)grad.stride(0);
+    g.out2 = nullptr; g.ldo2 = 0;
+    g.aux = nullptr; g.ldaux = 0;
+    g.row_scale = nullptr; g.row_vec = nullptr;
+    g.alpha = 1.0f; g.beta = (float)betas[i];
+    g.error_flag = reinterpret_cast<int*>(const_cast<void*>(opt_ptr(error_flag)));
+  }
+  c10::cuda::CUDAGuard guard(dys[0].device());
+  check_rc(ws_gemm_group(items.data(), (int)count, cur_stream()), "grad_weight_group");
 }
 
 // ----------------------------------------------------------------------------- row kernels
@@ -469,6 +514,7 @@ TORCH_LIBRARY(ws_b200, m) {
   m.def("gemm(Tensor a, Tensor b, bool a_mn, bool b_mn, int epilogue, int m, int n, int k, "
         "Tensor(a!) out, Tensor(b!)? out2, Tensor? aux, Tensor? row_scale, float alpha, float beta, "
         "Tensor(c!)? error_flag) -> ()");
+  m.def("grad_weight_group(Tensor[] dys, Tensor[] xs, Tensor(a!)[] grads, float[] betas, Tensor(b!)? error_flag) -> ()");
 }
 
 TORCH_LIBRARY_IMPL(ws_b200, CompositeExplicitAutograd, m) {
@@ -477,6 +523,7 @@ TORCH_LIBRARY_IMPL(ws_b200, CompositeExplicitAutograd, m) {
 
 TORCH_LIBRARY_IMPL(ws_b200, CUDA, m) {
   m.impl("gemm", &gemm);
+  m.impl("grad_weight_group", &grad_weight_group);
   m.impl("rmsnorm_fwd", &rmsnorm_fwd);
   m.impl("rmsnorm_bwd", &rmsnorm_bwd);
   m.impl("colsum2", &colsum2);

@@ -26,6 +26,7 @@
 #include "gemm_epilogue.cuh"
 
 #include <cstdlib>
+#include <cstring>
 
 namespace ws {
 
@@ -56,10 +57,36 @@ __device__ __forceinline__ void pair_tile_coords(int tile, int num_m, int num_n,
   nb = r / gsz;
 }
 
+// Up to MAX_GROUP independent problems of the same kind share one persistent launch: their
+// tiles form one list, so the last partial wave is paid once per group instead of once per
+// problem (the four weight-gradient GEMMs of a layer: 17 waves of 74 pairs separately, 15 grouped).
+constexpr int MAX_GROUP = 4;
+struct alignas(64) PairGroup {
+  CUtensorMap a[MAX_GROUP];
+  CUtensorMap b[MAX_GROUP];
+  GemmParams p[MAX_GROUP];
+  int tile_start[MAX_GROUP + 1];
+  int count;
+};
+
+struct PairTile {
+  int prob, mb, nb, num_k;
+};
+__device__ __forceinline__ PairTile resolve_tile(const PairGroup& g, int tile, int n_tile) {
+  PairTile t;
+  t.prob = 0;
+  while (t.prob + 1 < g.count && tile >= g.tile_start[t.prob + 1]) ++t.prob;
+  const GemmParams& p = g.p[t.prob];
+  const int num_m = (p.m + 2 * pair::BM - 1) / (2 * pair::BM);
+  const int num_n = (p.n + n_tile - 1) / n_tile;
+  pair_tile_coords(tile - g.tile_start[t.prob], num_m, num_n, t.mb, t.nb);
+  t.num_k = (p.k + pair::BK - 1) / pair::BK;
+  return t;
+}
+
 template <bool A_MN, bool B_MN, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::THREADS, 1)
-gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-             const GemmParams p) {
+gemm2_kernel(const __grid_constant__ PairGroup g) {
   using namespace pair;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -90,8 +117,10 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
     }
     *abort_flag = 0;
     mbar_fence_init();
-    tma_prefetch_desc(&tma_a);
-    tma_prefetch_desc(&tma_b);
+    for (int i = 0; i < g.count; ++i) {
+      tma_prefetch_desc(&g.a[i]);
+      tma_prefetch_desc(&g.b[i]);
+    }
   }
   if (warp == 1) {
     tmem_alloc_pair(tmem_slot, TMEM_COLS);
@@ -105,10 +134,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
 
   constexpr bool kSwiglu = (EPI == WS_EPI_SWIGLU);
   const int n_tile = kSwiglu ? 128 : BN;
-  const int num_m = (p.m + 2 * BM - 1) / (2 * BM);
-  const int num_n = (p.n + n_tile - 1) / n_tile;
-  const int tiles = num_m * num_n;
-  const int num_k = (p.k + BK - 1) / BK;
+  const int tiles = g.tile_start[g.count];
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
 
@@ -118,10 +144,13 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
       int it = 0;
       bool ok = true;
       for (int tile = pair_id; tile < tiles && ok; tile += num_pairs) {
-        int mb, nb;
-        pair_tile_coords(tile, num_m, num_n, mb, nb);
-        const int m0 = mb * 2 * BM + rank * BM;  // this CTA's rows
-        for (int kb = 0; kb < num_k; ++kb, ++it) {
+        const PairTile t = resolve_tile(g, tile, n_tile);
+        const GemmParams& p = g.p[t.prob];
+        const CUtensorMap* tma_a = &g.a[t.prob];
+        const CUtensorMap* tma_b = &g.b[t.prob];
+        const int nb = t.nb;
+        const int m0 = t.mb * 2 * BM + rank * BM;  // this CTA's rows
+        for (int kb = 0; kb < t.num_k; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) {
@@ -136,19 +165,19 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
           uint8_t* a_dst = sA + s * A_BYTES;
           uint8_t* b_dst = sB + s * B_BYTES;
           if (!A_MN) {
-            tma_load_2d_pair(a_dst, &tma_a, bar, kb * BK, m0);
+            tma_load_2d_pair(a_dst, tma_a, bar, kb * BK, m0);
           } else {
 #pragma unroll
             for (int i = 0; i < BM / 64; ++i)
-              tma_load_2d_pair(a_dst + i * (BK * 128), &tma_a, bar, m0 + i * 64, kb * BK);
+              tma_load_2d_pair(a_dst + i * (BK * 128), tma_a, bar, m0 + i * 64, kb * BK);
           }
           if (!B_MN) {
             const int r0 = kSwiglu ? (rank ? p.h + nb * 128 : nb * 128) : nb * BN + rank * 128;
-            tma_load_2d_pair(b_dst, &tma_b, bar, kb * BK, r0);
+            tma_load_2d_pair(b_dst, tma_b, bar, kb * BK, r0);
           } else {
 #pragma unroll
             for (int i = 0; i < 2; ++i)
-              tma_load_2d_pair(b_dst + i * (BK * 128), &tma_b, bar, nb * BN + rank * 128 + i * 64, kb * BK);
+              tma_load_2d_pair(b_dst + i * (BK * 128), tma_b, bar, nb * BN + rank * 128 + i * 64, kb * BK);
           }
         }
       }
@@ -166,6 +195,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
         if (!mbar_wait(&tempty[buf], tph ^ 1, abort_flag)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * BN;
+        const int num_k = resolve_tile(g, tile, n_tile).num_k;
         for (int kb = 0; kb < num_k; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -198,13 +228,14 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
     const int egroup = (warp - 2) >> 2;
     int tcount = 0;
     for (int tile = pair_id; tile < tiles; tile += num_pairs, ++tcount) {
-      int mb, nb;
-      pair_tile_coords(tile, num_m, num_n, mb, nb);
+      const PairTile t = resolve_tile(g, tile, n_tile);
+      const GemmParams& p = g.p[t.prob];
+      const int nb = t.nb;
       const int buf = tcount & 1;
       const uint32_t tph = (tcount >> 1) & 1;
       if (!mbar_wait(&tfull[buf], tph, abort_flag)) break;
       tc_fence_after_sync();
-      const int row = mb * 2 * BM + rank * BM + quarter * 32 + lane;
+      const int row = t.mb * 2 * BM + rank * BM + quarter * 32 + lane;
       const bool row_ok = row < p.m;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
       const float rs = (p.row_scale != nullptr && row_ok) ? p.row_scale[row] : 1.0f;
@@ -218,7 +249,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
   // ------------------------------------------------------------------ tear-down
   tc_fence_before_sync();
   __syncthreads();
-  if (threadIdx.x == 0 && *abort_flag != 0 && p.error_flag != nullptr) atomicExch(p.error_flag, 6);
+  if (threadIdx.x == 0 && *abort_flag != 0 && g.p[0].error_flag != nullptr) atomicExch(g.p[0].error_flag, 6);
   cluster_sync_all();  // neither CTA leaves (or frees TMEM) while the peer may still signal it
   if (warp == 1) {
     tc_fence_after_sync();
@@ -227,8 +258,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ 
 }
 
 template <bool A_MN, bool B_MN, int EPI>
-static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int pairs,
-                       cudaStream_t stream) {
+static int launch_pair(const PairGroup& g, int pairs, cudaStream_t stream) {
   static bool configured = false;
   auto kern = gemm2_kernel<A_MN, B_MN, EPI>;
   if (!configured) {
@@ -236,33 +266,28 @@ static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
       return -20;
     configured = true;
   }
-  kern<<<2 * pairs, pair::THREADS, pair::SMEM_BYTES, stream>>>(ta, tb, p);
+  kern<<<2 * pairs, pair::THREADS, pair::SMEM_BYTES, stream>>>(g);
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 
-}  // namespace ws
-
-// Same contract as ws_gemm (ws_api.h), whose argument checks have already run; `sms` bounds the
-// number of SMs used.  Returns -6 for a combination this kernel does not build.
-extern "C" int ws_gemm_pair(const WsGemm* g, int sms, cudaStream_t stream) {
-  using namespace ws;
+// Tensor maps, kernel parameters and tile count of one problem.
+static int fill_problem(const WsGemm* g, PairGroup& grp, int i, int* tiles_out) {
   if (g->m <= 0 || g->n <= 0 || g->k <= 0) return -1;
   const bool swiglu = g->epilogue == WS_EPI_SWIGLU;
   const int b_rows = swiglu ? 2 * g->n : g->n;
-  CUtensorMap ta, tb;
   int rc;
   if (!g->a_mn)
-    rc = make_map_bf16(&ta, g->a, g->k, g->m, g->lda, pair::BK, pair::BM);
+    rc = make_map_bf16(&grp.a[i], g->a, g->k, g->m, g->lda, pair::BK, pair::BM);
   else
-    rc = make_map_bf16(&ta, g->a, g->m, g->k, g->lda, 64, pair::BK);
+    rc = make_map_bf16(&grp.a[i], g->a, g->m, g->k, g->lda, 64, pair::BK);
   if (rc) return rc;
   if (!g->b_mn)
-    rc = make_map_bf16(&tb, g->b, g->k, b_rows, g->ldb, pair::BK, 128);
+    rc = make_map_bf16(&grp.b[i], g->b, g->k, b_rows, g->ldb, pair::BK, 128);
   else
-    rc = make_map_bf16(&tb, g->b, b_rows, g->k, g->ldb, 64, pair::BK);
+    rc = make_map_bf16(&grp.b[i], g->b, b_rows, g->k, g->ldb, 64, pair::BK);
   if (rc) return rc;
-  GemmParams p;
+  GemmParams& p = grp.p[i];
   p.m = g->m; p.n = g->n; p.k = g->k;
   p.h = g->n;
   p.epi_n = swiglu ? 128 : pair::BN;
@@ -275,23 +300,53 @@ extern "C" int ws_gemm_pair(const WsGemm* g, int sms, cudaStream_t stream) {
   p.error_flag = g->error_flag;
   p.debug = 0;
   const int n_tile = swiglu ? 128 : pair::BN;
-  const int tiles = ((g->m + 2 * pair::BM - 1) / (2 * pair::BM)) * ((g->n + n_tile - 1) / n_tile);
+  *tiles_out = ((g->m + 2 * pair::BM - 1) / (2 * pair::BM)) * ((g->n + n_tile - 1) / n_tile);
+  return 0;
+}
+
+}  // namespace ws
+
+// `count` problems (1..4) of one kind (same operand majors and epilogue) in one launch.  The
+// argument checks of ws_gemm have already run on every item; `sms` bounds the SMs used.
+// Returns -6 for a combination this kernel does not build.
+extern "C" int ws_gemm_pair_group(const WsGemm* items, int count, int sms, cudaStream_t stream) {
+  using namespace ws;
+  if (count < 1 || count > MAX_GROUP) return -9;
+  PairGroup grp;
+  memset(&grp, 0, sizeof(grp));
+  grp.count = count;
+  int total = 0;
+  for (int i = 0; i < count; ++i) {
+    if (items[i].a_mn != items[0].a_mn || items[i].b_mn != items[0].b_mn || items[i].epilogue != items[0].epilogue)
+      return -9;
+    int tiles = 0;
+    const int rc = fill_problem(&items[i], grp, i, &tiles);
+    if (rc) return rc;
+    grp.tile_start[i] = total;
+    total += tiles;
+  }
+  for (int i = count; i <= MAX_GROUP; ++i) grp.tile_start[i] = total;
   int pairs = sms / 2;
   if (pairs < 1) pairs = 1;
-  if (tiles < pairs) pairs = tiles;
+  if (total < pairs) pairs = total;
+  const WsGemm* g = &items[0];
   const int key = (g->a_mn ? 1 : 0) | (g->b_mn ? 2 : 0) | (g->epilogue << 2);
   switch (key) {
-    case (0 | (WS_EPI_BF16 << 2)): return launch_pair<false, false, WS_EPI_BF16>(ta, tb, p, pairs, stream);
-    case (2 | (WS_EPI_BF16 << 2)): return launch_pair<false, true, WS_EPI_BF16>(ta, tb, p, pairs, stream);
-    case (0 | (WS_EPI_RESID_F32 << 2)): return launch_pair<false, false, WS_EPI_RESID_F32>(ta, tb, p, pairs, stream);
-    case (0 | (WS_EPI_RESID_BF16 << 2)): return launch_pair<false, false, WS_EPI_RESID_BF16>(ta, tb, p, pairs, stream);
-    case (0 | (WS_EPI_SWIGLU << 2)): return launch_pair<false, false, WS_EPI_SWIGLU>(ta, tb, p, pairs, stream);
-    case (0 | (WS_EPI_F32 << 2)): return launch_pair<false, false, WS_EPI_F32>(ta, tb, p, pairs, stream);
-    case (3 | (WS_EPI_ACC_F32 << 2)): return launch_pair<true, true, WS_EPI_ACC_F32>(ta, tb, p, pairs, stream);
-    case (3 | (WS_EPI_BF16 << 2)): return launch_pair<true, true, WS_EPI_BF16>(ta, tb, p, pairs, stream);
-    case (2 | (WS_EPI_SWIGLU_BWD << 2)): return launch_pair<false, true, WS_EPI_SWIGLU_BWD>(ta, tb, p, pairs, stream);
-    case (0 | (WS_EPI_CE_FWD << 2)): return launch_pair<false, false, WS_EPI_CE_FWD>(ta, tb, p, pairs, stream);
-    case (0 | (WS_EPI_CE_BWD << 2)): return launch_pair<false, false, WS_EPI_CE_BWD>(ta, tb, p, pairs, stream);
+    case (0 | (WS_EPI_BF16 << 2)): return launch_pair<false, false, WS_EPI_BF16>(grp, pairs, stream);
+    case (2 | (WS_EPI_BF16 << 2)): return launch_pair<false, true, WS_EPI_BF16>(grp, pairs, stream);
+    case (0 | (WS_EPI_RESID_F32 << 2)): return launch_pair<false, false, WS_EPI_RESID_F32>(grp, pairs, stream);
+    case (0 | (WS_EPI_RESID_BF16 << 2)): return launch_pair<false, false, WS_EPI_RESID_BF16>(grp, pairs, stream);
+    case (0 | (WS_EPI_SWIGLU << 2)): return launch_pair<false, false, WS_EPI_SWIGLU>(grp, pairs, stream);
+    case (0 | (WS_EPI_F32 << 2)): return launch_pair<false, false, WS_EPI_F32>(grp, pairs, stream);
+    case (3 | (WS_EPI_ACC_F32 << 2)): return launch_pair<true, true, WS_EPI_ACC_F32>(grp, pairs, stream);
+    case (3 | (WS_EPI_BF16 << 2)): return launch_pair<true, true, WS_EPI_BF16>(grp, pairs, stream);
+    case (2 | (WS_EPI_SWIGLU_BWD << 2)): return launch_pair<false, true, WS_EPI_SWIGLU_BWD>(grp, pairs, stream);
+    case (0 | (WS_EPI_CE_FWD << 2)): return launch_pair<false, false, WS_EPI_CE_FWD>(grp, pairs, stream);
+    case (0 | (WS_EPI_CE_BWD << 2)): return launch_pair<false, false, WS_EPI_CE_BWD>(grp, pairs, stream);
     default: return -6;
   }
+}
+
+extern "C" int ws_gemm_pair(const WsGemm* g, int sms, cudaStream_t stream) {
+  return ws_gemm_pair_group(g, 1, sms, stream);
 }

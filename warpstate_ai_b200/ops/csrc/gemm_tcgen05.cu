@@ -268,9 +268,65 @@ static bool pair_mode() {
   return forced < 0 ? on : forced != 0;
 }
 
-extern "C" int ws_gemm(const WsGemm* g, cudaStream_t stream) {
+// Argument checks shared by every entry point (0 = acceptable).
+static int validate_gemm(const WsGemm* g) {
   using namespace ws;
   if (g->m <= 0 || g->n <= 0 || g->k <= 0) return -1;
+  const bool swiglu = g->epilogue == WS_EPI_SWIGLU;
+  // Vector-store alignment of the epilogues (8 BF16 or 4 FP32 per store).
+  const bool f32_out = g->epilogue == WS_EPI_RESID_F32 || g->epilogue == WS_EPI_ACC_F32 ||
+                       g->epilogue == WS_EPI_F32;
+  const int vec = f32_out ? 4 : 8;
+  if (g->epilogue == WS_EPI_CE_FWD) {
+    if (g->aux == nullptr || g->out2 == nullptr || g->ldo < 2 * ((g->n + BN - 1) / BN)) return -7;
+  } else if (g->n % vec != 0 || g->ldo % vec != 0) {
+    return -2;
+  }
+  if (g->epilogue == WS_EPI_CE_BWD && (g->aux == nullptr || g->row_vec == nullptr || g->row_scale == nullptr)) return -8;
+  if ((g->epilogue == WS_EPI_RESID_F32 || g->epilogue == WS_EPI_RESID_BF16) &&
+      (g->aux == nullptr || g->ldaux % vec != 0)) return -3;
+  if (swiglu && (g->out2 == nullptr || g->ldo2 % 8 != 0)) return -4;
+  if (g->epilogue == WS_EPI_SWIGLU_BWD && (g->aux == nullptr || g->ldaux % 8 != 0)) return -5;
+
+  return 0;
+}
+
+static int usable_sms() {
+  int sms = ws::sm_count();
+  const int lim = ws::g_sm_limit.load();
+  if (lim > 0 && lim < sms) sms = lim;
+  return sms;
+}
+
+extern "C" int ws_gemm_pair_group(const WsGemm* items, int count, int sms, cudaStream_t stream);
+
+// Several problems of one kind in one persistent launch when the CTA-pair kernel can take them
+// (all with >= 256 rows, at most 4); otherwise one launch each, in order.
+extern "C" int ws_gemm_group(const WsGemm* items, int count, cudaStream_t stream) {
+  if (count <= 0) return 0;
+  bool groupable = pair_mode() && count <= 4 && usable_sms() >= 2;
+  for (int i = 0; i < count; ++i) {
+    const int rc = validate_gemm(&items[i]);
+    if (rc) return rc;
+    groupable = groupable && items[i].m >= 256 && items[i].a_mn == items[0].a_mn &&
+                items[i].b_mn == items[0].b_mn && items[i].epilogue == items[0].epilogue;
+  }
+  if (groupable) return ws_gemm_pair_group(items, count, usable_sms(), stream);
+  for (int i = 0; i < count; ++i) {
+    const int rc = ws_gemm(&items[i], stream);
+    if (rc) return rc;
+  }
+  return 0;
+}
+
+extern "C" int ws_gemm(const WsGemm* g, cudaStream_t stream) {
+  {
+    const int vrc = validate_gemm(g);
+    if (vrc) return vrc;
+  }
+  using namespace ws;
+  const int sms = usable_sms();
+  if (pair_mode() && g->m >= 256 && sms >= 2) return ws_gemm_pair(g, sms, stream);
   const bool swiglu = g->epilogue == WS_EPI_SWIGLU;
   const int b_rows = swiglu ? 2 * g->n : g->n;  // output features held by B
   CUtensorMap ta, tb;
@@ -299,27 +355,8 @@ extern "C" int ws_gemm(const WsGemm* g, cudaStream_t stream) {
   p.error_flag = g->error_flag;
   p.debug = 0;
 
-  // Vector-store alignment of the epilogues (8 BF16 or 4 FP32 per store).
-  const bool f32_out = g->epilogue == WS_EPI_RESID_F32 || g->epilogue == WS_EPI_ACC_F32 ||
-                       g->epilogue == WS_EPI_F32;
-  const int vec = f32_out ? 4 : 8;
-  if (g->epilogue == WS_EPI_CE_FWD) {
-    if (g->aux == nullptr || g->out2 == nullptr || g->ldo < 2 * ((g->n + BN - 1) / BN)) return -7;
-  } else if (g->n % vec != 0 || g->ldo % vec != 0) {
-    return -2;
-  }
-  if (g->epilogue == WS_EPI_CE_BWD && (g->aux == nullptr || g->row_vec == nullptr || g->row_scale == nullptr)) return -8;
-  if ((g->epilogue == WS_EPI_RESID_F32 || g->epilogue == WS_EPI_RESID_BF16) &&
-      (g->aux == nullptr || g->ldaux % vec != 0)) return -3;
-  if (swiglu && (g->out2 == nullptr || g->ldo2 % 8 != 0)) return -4;
-  if (g->epilogue == WS_EPI_SWIGLU_BWD && (g->aux == nullptr || g->ldaux % 8 != 0)) return -5;
-
   const int n_tile = swiglu ? 128 : BN;
   const int tiles = ((g->m + BM - 1) / BM) * ((g->n + n_tile - 1) / n_tile);
-  int sms = sm_count();
-  const int lim = g_sm_limit.load();
-  if (lim > 0 && lim < sms) sms = lim;
-  if (pair_mode() && g->m >= 256 && sms >= 2) return ws_gemm_pair(g, sms, stream);
   const int grid = tiles < sms ? tiles : sms;
 
   const int key = (g->a_mn ? 1 : 0) | (g->b_mn ? 2 : 0) | (g->epilogue << 2);

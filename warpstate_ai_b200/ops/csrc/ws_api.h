@@ -51,6 +51,9 @@ typedef struct WsGemm {
 int ws_gemm(const WsGemm* g, cudaStream_t stream);
 // Number of SMs the GEMM may use on this stream's device (0 = all).  Lets a communication
 // kernel keep a few SMs for itself while persistent GEMM CTAs fill the rest.
+// `count` problems in one persistent launch where possible (same operand majors and epilogue, each
+// with >= 256 rows, count <= 4); otherwise equivalent to calling ws_gemm on each item in order.
+int ws_gemm_group(const WsGemm* items, int count, cudaStream_t stream);
 void ws_gemm_set_sm_limit(int sms);
 // Kernel choice for problems with >= 256 rows: 1 = CTA-pair (cta_group::2) kernel, 0 = single-CTA
 // kernel, -1 = the process default (pair unless WS_GEMM_PAIR=0 is in the environment).

@@ -106,6 +106,23 @@ def _wgrad(dy: torch.Tensor, x: torch.Tensor, p: torch.Tensor):
     return grad.to(p.dtype)
 
 
+def _wgrad_group(items):
+    """``items`` = [(dy, x, param), ...] -> list of gradients for autograd (None where the result
+    was accumulated into ``param.main_grad``).  All products run as one grouped launch."""
+    work, results = [], []
+    for dy, x, p in items:
+        main = getattr(p, "main_grad", None)
+        if main is not None:
+            work.append((dy, x, main, True))
+            results.append(None)
+        else:
+            grad = torch.empty(p.shape, dtype=torch.float32, device=p.device)
+            work.append((dy, x, grad, False))
+            results.append((grad, p.dtype))
+    G.grad_weight_accumulate_group(work)
+    return [None if r is None else r[0].to(r[1]) for r in results]
+
+
 # --------------------------------------------------------------------------- attention hook
 def _attention_forward(qkvgu: torch.Tensor, core, batch: int, seq: int):
     """qkvgu [M,5d] BF16 -> (y [M,d] BF16, saved-for-backward)."""
@@ -179,21 +196,19 @@ class CoreFn(torch.autograd.Function):
         # ---- FFN
         dx3b = ops.cast_bf16(dx3, None) if dx3.dtype == torch.float32 else dx3
         dpacked = G.grad_input_swiglu(dx3b, bf16_weight(w_down), packed)
-        g_down = _wgrad(dx3b, act, w_down)
         dz2 = G.grad_input(dpacked, bf16_weight(w_ug))
-        g_ug = _wgrad(dpacked, z2, w_ug)
-        del dpacked
         dx2, dx2b, g_n2 = ops.rmsnorm_bwd(dz2, x2, rstd2, n2w.detach(), dx3, None, True)
         del dz2
         # ---- attention / memory
         dy = G.grad_input(dx2b, bf16_weight(w_out))
-        g_out = _wgrad(dx2b, y, w_out)
         dqkvgu, g_fast, g_slow, g_mix = _attention_backward(dy, qkvgu, ctx.attn_saved, core, batch, seq)
         del dy
         dz1 = G.grad_input(dqkvgu, bf16_weight(w_in))
-        g_in = _wgrad(dqkvgu, z1, w_in)
-        del dqkvgu
         dx_in, _, g_n1 = ops.rmsnorm_bwd(dz1, xmod, rstd1, n1w.detach(), dx2, scale if ctx.has_mod else None, False)
+        # ---- the four weight gradients, deferred to one grouped launch (their tiles share waves)
+        g_down, g_ug, g_out, g_in = _wgrad_group([(dx3b, act, w_down), (dpacked, z2, w_ug), (dx2b, y, w_out),
+                                                  (dqkvgu, z1, w_in)])
+        del dpacked, dqkvgu
         g_scale = g_bias = None
         if ctx.has_mod:
             # d bias = colsum(d x_mod), d scale = colsum(d x_mod * x_in), with d x_mod = dx_in / (1+scale)

@@ -129,6 +129,18 @@ def grad_weight_accumulate(dy: torch.Tensor, x: torch.Tensor, grad: torch.Tensor
                  beta=1.0 if accumulate else 0.0)
 
 
+def grad_weight_accumulate_group(items) -> None:
+    """``items`` = [(dy, x, grad, accumulate), ...]: every ``grad (+)= dy.T @ x`` in ONE persistent
+    launch (up to four problems per launch), so the last partial wave of tiles is paid once for
+    the group instead of once per weight."""
+    _ext.require()
+    items = list(items)
+    for start in range(0, len(items), 4):
+        part = items[start:start + 4]
+        torch.ops.ws_b200.grad_weight_group([i[0] for i in part], [i[1] for i in part], [i[2] for i in part],
+                                            [1.0 if i[3] else 0.0 for i in part], error_flag(part[0][0].device))
+
+
 def grad_weight_bf16(dy: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
     tokens, n = dy.shape
     k = x.shape[1]
