@@ -41,6 +41,8 @@ def parse():
     ap.add_argument("--grad-accum", type=int, default=4)
     ap.add_argument("--seq-len", type=int, default=2048)
     ap.add_argument("--grad-sync", default="auto", help="auto | fused | nccl (multi-GPU gradient path)")
+    ap.add_argument("--shard-optimizer", action="store_true",
+                    help="multi-GPU: sharded AdamW state with the fused update-and-broadcast kernel")
     ap.add_argument("--ref-compile-mode", default=os.environ.get("WARPSTATE_REF_COMPILE_MODE", "default"))
     return ap.parse_args()
 
@@ -135,7 +137,7 @@ def run_ours(args):
         from warpstate_ai_b200.parallel.grad_sync import make_grad_sync
         sync = make_grad_sync(device, world, rank, None, kind=args.grad_sync)
     trainer = Trainer(model, device=device, rank=rank, world_size=world, lr=1.5e-4, weight_decay=0.1,
-                      grad_sync=sync)
+                      grad_sync=sync, shard_optimizer=args.shard_optimizer)
     mb, T, acc = args.micro_batch, args.seq_len, args.grad_accum
     update_tokens = mb * T * acc * world
     data = SyntheticTokens(update_tokens * 3 + 1, cfg.vocab_size, seed=7)
@@ -191,6 +193,7 @@ def run_ours(args):
     h2d = batcher.bytes_per_batch * acc * world
     emit(args, rank, world, tokens / dev_s, dev_s / args.steps * 1e3, tokens / e2e_s, clocks, launches, "ours",
          {"last_loss": result.loss, "last_grad_norm": norm, "grad_sync": getattr(sync, "kind", "none"),
+          "optimizer": "sharded" if (args.shard_optimizer and world > 1) else "replicated",
           "peak_mem_gib": torch.cuda.max_memory_allocated(device) / 2**30}, h2d, 12 * world)
     if world > 1:
         import torch.distributed as dist

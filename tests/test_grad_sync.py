@@ -83,17 +83,25 @@ def worker(mode: str, rank: int, world: int, out_dir: Path) -> None:
     mb = 2
     if mode in ("cpu_train", "gpu_train"):
         from warpstate_ai_b200.parallel.grad_sync import CollectiveGradSync, FusedGradSync
-        kinds = ["collective", "fused"] if cuda else ["collective"]
+        kinds = (["collective", "fused", "collective-sharded", "fused-sharded"] if cuda
+                 else ["collective", "collective-sharded"])
         # 2 full updates, then one where the second rank's slice is empty
         targets = [world * mb * seq * 2, world * mb * seq * 2, mb * seq]
         for kind in kinds:
             model, cfg = tiny_model(device)
-            sync = (FusedGradSync(device, world, rank, budget_seconds=20.0) if kind == "fused"
+            sync = (FusedGradSync(device, world, rank, budget_seconds=20.0) if kind.startswith("fused")
                     else CollectiveGradSync(device, world, rank))
             trainer = Trainer(model, device=device, rank=rank, world_size=world, lr=1e-3, weight_decay=0.1,
-                              grad_sync=sync)
+                              grad_sync=sync, shard_optimizer=kind.endswith("sharded"))
             losses = run_updates(trainer, cfg, world, rank, seq, mb, targets)
+            trainer.gather_for_checkpoint()
             flat = trainer.arena.master.detach().float().cpu()
+            state = trainer.optimizer.state_dict()
+            if rank == 0:
+                torch.save({k: {n: t.cpu() for n, t in v.items()} for k, v in state["state"].items()},
+                           out_dir / f"adam-{kind}.pt")
+            if kind.endswith("sharded"):
+                report[kind + "-moment-bytes"] = trainer.optimizer.memory_bytes()
             report[kind] = {"losses": losses, "checksum": float(flat.double().sum()), "norm": float(flat.norm()),
                             "sync": sync.kind}
             torch.save(flat, out_dir / f"params-{kind}-{rank}.pt")
@@ -153,6 +161,17 @@ def test_two_cpu_ranks_match_single_process(tmp_path):
     losses = run_updates(trainer, cfg, 1, 0, 16, 2, [2 * 2 * 16 * 2, 2 * 2 * 16 * 2, 2 * 16])
     assert losses == pytest.approx(reports[0]["collective"]["losses"], rel=2e-5, abs=2e-6)
     assert torch.allclose(trainer.arena.master.detach().cpu(), a, rtol=1e-4, atol=2e-6)
+    # the sharded optimizer (each rank updates half of every bucket) gives the same bits
+    for rank in (0, 1):
+        assert torch.equal(torch.load(tmp_path / f"params-collective-sharded-{rank}.pt"), a)
+    assert reports[0]["collective-sharded"]["losses"] == reports[0]["collective"]["losses"]
+    whole, sharded = torch.load(tmp_path / "adam-collective.pt"), torch.load(tmp_path / "adam-collective-sharded.pt")
+    assert whole.keys() == sharded.keys()
+    for index in whole:
+        for name in ("step", "exp_avg", "exp_avg_sq"):
+            assert torch.equal(whole[index][name], sharded[index][name]), (index, name)
+    full_bytes = 2 * 4 * trainer.arena.numel
+    assert reports[0]["collective-sharded-moment-bytes"] <= full_bytes // 2 + 64 * len(trainer.arena.buckets)
 
 
 needs_two_gpus = pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2,
@@ -180,6 +199,12 @@ def test_fused_sync_training_matches_nccl_sync(tmp_path):
     b = torch.load(tmp_path / "params-fused-0.pt")
     assert torch.allclose(a, b, rtol=1e-3, atol=2e-5)
     assert reports[0]["fused"]["losses"] == pytest.approx(reports[0]["collective"]["losses"], rel=1e-3)
+    # sharded optimizer: reduce-scatter + update-and-broadcast kernel == all-reduce + replicated AdamW
+    for kind in ("collective-sharded", "fused-sharded"):
+        assert torch.equal(torch.load(tmp_path / f"params-{kind}-0.pt"), torch.load(tmp_path / f"params-{kind}-1.pt"))
+    assert torch.allclose(torch.load(tmp_path / "params-fused-sharded-0.pt"), b, rtol=1e-5, atol=1e-7)
+    assert torch.allclose(torch.load(tmp_path / "params-collective-sharded-0.pt"), a, rtol=1e-5, atol=1e-7)
+    assert reports[0]["fused-sharded"]["losses"] == pytest.approx(reports[0]["fused"]["losses"], rel=1e-5)
 
 
 if __name__ == "__main__":

@@ -122,6 +122,17 @@ class ParamArena:
             if self.bf16 is not None:
                 s.param.bf16_view = self.view(self.bf16, s)
 
+    def adopt_master(self, tensor: torch.Tensor) -> None:
+        """Move the FP32 master weights into ``tensor`` (e.g. symmetric memory) and re-point every
+        parameter at its new storage."""
+        if tensor.numel() != self.numel or tensor.dtype != torch.float32:
+            raise ValueError("replacement master buffer has the wrong size or dtype")
+        with torch.no_grad():
+            tensor.copy_(self.master)
+            self.master = tensor
+            for s in self.slots:
+                s.param.data = self.view(self.master, s)
+
     def zero_grad(self) -> None:
         self.grad.zero_()
 

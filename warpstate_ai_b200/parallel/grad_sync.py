@@ -134,6 +134,7 @@ class FusedGradSync(GradSyncBase):
         self.grad_sym = None
         self.flag_sym = None
         self.status = torch.zeros(8, dtype=torch.int32, device=device)
+        self.push = True  # False: reduce-scatter (the sharded optimizer keeps each slice on its owner)
 
     def alloc_grad_buffer(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
         from . import symm
@@ -159,7 +160,7 @@ class FusedGradSync(GradSyncBase):
         with torch.cuda.stream(self.stream):
             torch.ops.ws_b200.grad_allreduce(self.grad_sym.peer_ptrs, self.flag_sym.peer_ptrs, self.mc_ptr, self.rank,
                                              self.world, b.start, b.stop - b.start, bucket, self.seq,
-                                             1.0 / self.world, True, self.ctas, None, self.status, self.budget)
+                                             1.0 / self.world, self.push, self.ctas, None, self.status, self.budget)
 
     def wait(self) -> None:
         torch.cuda.current_stream(self.device).wait_stream(self.stream)

@@ -51,7 +51,7 @@ class Trainer:
     def __init__(self, model: torch.nn.Module, *, device: torch.device, rank: int = 0, world_size: int = 1,
                  lr: float = 1.5e-4, weight_decay: float = 0.1, betas=(0.9, 0.95), eps: float = 1e-8,
                  max_grad_norm: float | None = 1.0, grad_sync=None, bf16_autocast: bool = True,
-                 process_group=None):
+                 process_group=None, shard_optimizer: bool = False):
         self.model = model
         self.device = device
         self.rank, self.world_size = rank, world_size
@@ -63,10 +63,16 @@ class Trainer:
         self.sync = grad_sync
         alloc = grad_sync.alloc_grad_buffer if grad_sync is not None else None
         self.arena = ParamArena(model, device=device, symmetric_alloc=alloc)
-        self.optimizer = ArenaAdamW(self.arena, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
-                                    max_grad_norm=max_grad_norm)
         if self.sync is not None:
             self.sync.attach(self.arena, model)
+        if shard_optimizer and world_size > 1:
+            from ..parallel.zero import ShardedAdamW
+            self.optimizer = ShardedAdamW(self.arena, rank=rank, world=world_size, group=process_group, sync=self.sync,
+                                          lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
+                                          max_grad_norm=max_grad_norm)
+        else:
+            self.optimizer = ArenaAdamW(self.arena, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay,
+                                        max_grad_norm=max_grad_norm)
         self.loss_sum = torch.zeros((), dtype=torch.float32, device=device)
 
     # ------------------------------------------------------------------ pieces of one update
@@ -96,6 +102,12 @@ class Trainer:
         if self.sync is not None:
             self.sync.reduce_scalar(self.loss_sum)
         return stats
+
+    def gather_for_checkpoint(self) -> None:
+        """With a sharded optimizer: make the FP32 master weights whole on this rank (collective)."""
+        gather = getattr(self.optimizer, "gather_master", None)
+        if gather is not None:
+            gather()
 
     def read_update_scalars(self, stats: torch.Tensor):
         """One device->host read per update: loss, gradient norm, clip coefficient and, with a

@@ -96,6 +96,9 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--device", choices=["cuda", "cpu"], default="cuda", help="cpu runs the plain-PyTorch path (tests)")
     p.add_argument("--grad-sync", choices=["auto", "fused", "nccl"], default="auto",
                    help="multi-GPU gradient path: in-kernel all-reduce over NVLink peer memory, or NCCL")
+    p.add_argument("--shard-optimizer", action="store_true",
+                   help="multi-GPU: each rank keeps AdamW state for 1/world of every bucket and broadcasts its "
+                        "updated BF16 weights from the update kernel (checkpoints stay unsharded)")
     p.add_argument("--kernels", action=argparse.BooleanOptionalAction, default=True,
                    help="use the sm_100a kernel library on CUDA")
     return p
@@ -242,6 +245,16 @@ def preflight(a) -> None:
 
 
 # --------------------------------------------------------------------------- the run
+class _FrozenState:
+    """An already materialised ``state_dict()`` behind the optimizer interface `server_state` expects."""
+
+    def __init__(self, state: dict):
+        self._state = state
+
+    def state_dict(self) -> dict:
+        return self._state
+
+
 class PretrainRun:
     """State of one training process between `setup()` and the end of `loop()`."""
 
@@ -339,7 +352,8 @@ class PretrainRun:
             from ..ops import fused
             fused._enabled = False
         self.trainer = Trainer(model, device=self.device, rank=a.rank, world_size=a.world_size, lr=a.lr,
-                               weight_decay=a.weight_decay, grad_sync=sync)
+                               weight_decay=a.weight_decay, grad_sync=sync,
+                               shard_optimizer=getattr(a, "shard_optimizer", False))
         self.seen, self.step = 0, 0
         if resuming:
             self.trainer.optimizer.load_state_dict(checkpoint["optimizer"])
@@ -446,10 +460,16 @@ class PretrainRun:
             rank_states = [None] * a.world_size
             self.dist.all_gather_object(rank_states, state, group=self.control)
 
+        optimizer = self.trainer.optimizer
+        if hasattr(optimizer, "gather_master"):
+            # sharded optimizer: assembling the unsharded state is collective, so every rank does it now
+            self.trainer.gather_for_checkpoint()
+            optimizer = _FrozenState(optimizer.state_dict())
+
         def build_state():
             print("Staging full CPU checkpoint..." if a.async_checkpoint else "Saving full checkpoint...", flush=True)
             return server_state(signature=self.signature, origin=self.origin, history=self.history, cfg=self.cfg,
-                                model=self.model, optimizer=self.trainer.optimizer, step=self.step,
+                                model=self.model, optimizer=optimizer, step=self.step,
                                 tokens_seen=self.seen, val_loss=validation, val_step=self.last_val_step,
                                 val_tokens=self.last_val_tokens, rng_by_rank=rank_states)
 
