@@ -1,0 +1,127 @@
+"""CPU tests of the benchmark / analysis tools: training benchmark records, run comparison,
+communication-overlap analysis on synthetic traces, loss-curve fits on synthetic curves
+(reference test_analyze_communication_profile.py, test_compare_communication_benchmarks.py)."""
+import json
+import math
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from warpstate_ai_b200.analysis import loss_forecast as LF
+from warpstate_ai_b200.bench import comm_profile as CP
+from warpstate_ai_b200.bench import compare_runs as CR
+from warpstate_ai_b200.bench import train_bench as TB
+
+
+def kernel(name, ts, dur, device=0, **args):
+    return {"ph": "X", "cat": "kernel", "name": name, "ts": ts, "dur": dur, "args": {"device": device, **args}}
+
+
+def test_sweep_separates_exposed_and_hidden_communication():
+    events = [kernel("gemm2_kernel", 0, 100), kernel("attn_bwd_kernel", 150, 50),
+              kernel("ncclDevKernel_AllReduce_Sum_f32", 80, 40, **{"Process Group Name": "0", "Seq": 7,
+                     "Collective name": "allreduce", "In msg nelems": 1024, "dtype": "Float"}),
+              kernel("ncclDevKernel_AllReduce_Sum_f32", 85, 30, **{"Process Group Name": "0", "Seq": 7,
+                     "Collective name": "allreduce", "In msg nelems": 1024, "dtype": "Float"}),
+              kernel("ws::grad_allreduce_kernel(ws::PeerTable, float*)", 190, 30),
+              {"ph": "X", "cat": "gpu_memcpy", "name": "Memcpy HtoD", "ts": 300, "dur": 10, "args": {"device": 0}},
+              {"ph": "X", "cat": "gpu_user_annotation", "name": "range", "ts": 0, "dur": 500, "args": {"device": 0}},
+              {"ph": "X", "cat": "cpu_op", "name": "c10d::allreduce_", "ts": 1, "dur": 1, "args": {"Input Dims": [[1024]]}}]
+    report = CP.summarize_trace({"traceEvents": events, "distributedInfo": {"rank": 1}})
+    d = report["devices"][0]
+    assert report["rank"] == 1 and report["excluded_gpu_annotation_ranges"] == 1
+    # compute: [0,100] [150,200] [300,310]; communication: [80,120] [190,220]
+    assert d["compute_communication_overlap_us"] == pytest.approx(20 + 10)
+    assert d["communication_only_us"] == pytest.approx(20 + 20)
+    assert d["compute_only_us"] == pytest.approx(80 + 40 + 10)
+    assert d["idle_within_activity_span_us"] == pytest.approx(30 + 80)
+    assert d["activity_span_us"] == pytest.approx(310)
+    assert d["communication_overlap_fraction"] == pytest.approx(30 / 70)
+    assert d["collective_call_count"] == 1 and d["logical_input_payload_bytes"] == 4096  # two channel kernels, one call
+    assert d["own_collective_kernels"] == {"ws::grad_allreduce_kernel": 1}
+    assert report["cpu_collective_fingerprint"]["call_count"] == 1
+    with pytest.raises(ValueError):
+        CP.summarize_trace({"traceEvents": [kernel("k", 0, -1)]})
+
+
+def test_comm_profile_cli_refuses_to_overwrite(tmp_path):
+    trace = tmp_path / "profile-rank-3-trace.json"
+    trace.write_text(json.dumps({"traceEvents": [kernel("gemm2_kernel", 0, 5)]}))
+    out = tmp_path / "report.json"
+    assert CP.main([str(trace), "--output", str(out)]) == 0
+    assert json.loads(out.read_text())["ranks"][0]["rank"] == 3
+    with pytest.raises(SystemExit):
+        CP.main([str(trace), "--output", str(out)])
+
+
+@pytest.fixture(scope="module")
+def bench_dirs(tmp_path_factory):
+    root = tmp_path_factory.mktemp("bench")
+    common = ["--model", "smoke", "--device", "cpu", "--micro-batch", "2", "--seq-len", "128",
+              "--global-tokens-per-update", "512", "--warmup-updates", "1", "--measured-updates", "2"]
+    for name in ("a", "b"):
+        assert TB.main(common + ["--output-dir", str(root / name)]) == 0
+    assert TB.main(common + ["--output-dir", str(root / "profiled"), "--profile", "--diagnose-stalls"]) == 0
+    return root
+
+
+def test_train_bench_records(bench_dirs):
+    summary = json.loads((bench_dirs / "a/summary.json").read_text())
+    assert summary["format"] == "warpstate-training-benchmark-v1" and len(summary["updates"]) == 2
+    rows = [json.loads(l) for l in (bench_dirs / "a/rank-0.jsonl").read_text().splitlines()]
+    assert [r["measured"] for r in rows] == [False, True, True]
+    assert all(math.isfinite(r["loss"]) and r["tokens_per_second"] > 0 for r in rows)
+    prof = json.loads((bench_dirs / "profiled/summary.json").read_text())["profile"]
+    assert Path(prof["trace"]).exists() and (bench_dirs / "profiled/profile-rank-0-kernels.tsv").exists()
+    stalls = [json.loads(l) for l in (bench_dirs / "profiled/rank-0.jsonl").read_text().splitlines()][-1]
+    assert {"forward_backward", "sync_clip_step", "read_back"} <= set(stalls["host_stage_seconds"])
+
+
+def test_compare_runs_pairs_updates_and_rejects_mismatches(bench_dirs, tmp_path):
+    out = tmp_path / "cmp.json"
+    assert CR.main(["--control", str(bench_dirs / "a"), "--candidate", str(bench_dirs / "b"), "--output", str(out)]) == 0
+    report = json.loads(out.read_text())["comparisons"][0]
+    assert report["maximum_absolute_loss_difference"] == 0.0  # same seed, same data: same numbers
+    assert report["maximum_relative_grad_norm_difference"] == 0.0
+    assert len(report["paired_updates"]) == 2 and report["throughput_ratio"] > 0
+    with pytest.raises(ValueError, match="unprofiled"):
+        CR.load_run(bench_dirs / "profiled")
+    # a run with another geometry is not comparable
+    other = tmp_path / "other"
+    TB.main(["--model", "smoke", "--device", "cpu", "--micro-batch", "1", "--seq-len", "128",
+             "--global-tokens-per-update", "512", "--warmup-updates", "1", "--measured-updates", "2",
+             "--output-dir", str(other)])
+    with pytest.raises(ValueError, match="geometry"):
+        CR.compare(CR.load_run(bench_dirs / "a"), CR.load_run(other))
+    # tampered throughput is caught
+    bad = tmp_path / "bad"
+    bad.mkdir()
+    (bad / "summary.json").write_text((bench_dirs / "a/summary.json").read_text())
+    rows = [json.loads(l) for l in (bench_dirs / "a/rank-0.jsonl").read_text().splitlines()]
+    rows[1]["tokens_per_second"] *= 2
+    (bad / "rank-0.jsonl").write_text("\n".join(json.dumps(r) for r in rows) + "\n")
+    with pytest.raises(ValueError, match="throughput"):
+        CR.load_run(bad)
+
+
+def test_loss_forecast_recovers_a_power_law():
+    tokens = np.arange(1.0, 8.01, 0.05) * 1e9
+    true = {"floor": 1.7, "amplitude": 1.2, "alpha": 0.35}
+    rows = [{"tokens": int(t), "loss": true["floor"] + true["amplitude"] * (t / 1e9) ** -true["alpha"]} for t in tokens]
+    raw = "\n".join(json.dumps(r) for r in rows).encode()
+    report = LF.analyze(raw)
+    free = next(f for f in report["fits"] if f["start_B"] == 1 and f["parameters"]["model"] == "power_free")
+    # bin means of a convex curve sit slightly above the curve at the mean token count
+    assert free["parameters"]["alpha"] == pytest.approx(true["alpha"], rel=0.05)
+    assert free["parameters"]["floor"] == pytest.approx(true["floor"], abs=0.05)
+    assert free["parameters"]["rmse"] < 1e-3
+    expected_cross = (true["amplitude"] / (2.0 - true["floor"])) ** (1 / true["alpha"])
+    assert free["cross_2_tokens_B"] == pytest.approx(expected_cross, rel=0.15)
+    log = next(f for f in report["fits"] if f["start_B"] == 1 and f["parameters"]["model"] == "log")
+    assert log["parameters"]["slope"] < 0 and log["parameters"]["rmse"] > free["parameters"]["rmse"]
+    assert len(report["holdouts"]) == 3 * 7
+    best = min((h for h in report["holdouts"] if h["train_end_B"] == 6), key=lambda h: h["rmse"])
+    assert best["parameters"]["model"].startswith("power")
+    with pytest.raises(ValueError):
+        LF.analyze(b'{"tokens": 5, "loss": 1}\n{"tokens": 4, "loss": 1}')

@@ -1,0 +1,152 @@
+"""Paired comparison of two `train_bench` output directories (control vs candidate).
+
+Two runs are comparable only if they measured the same thing: same model configuration,
+checkpoint and data identity, geometry (world size, micro-batch, sequence length, tokens per
+update), precision, optimizer-state choice and update counts, none of them profiled.  The tool
+refuses anything else, then pairs update ``i`` of both runs and reports, per update, the
+slowest-rank seconds of each run, the throughput ratio, and the per-rank loss / gradient-norm
+differences (a change of the communication path must not change the numbers), plus timing
+statistics (mean, median, population std, first-five vs last-five drift) and peak memory.
+
+    python -m warpstate_ai_b200.bench.compare_runs --control dir_a --candidate dir_b --output cmp.json
+
+Same checks and report as the reference's ops/compare_communication_benchmarks.py:50-234, over
+this framework's benchmark records (rank-<r>.jsonl + summary.json).
+"""
+from __future__ import annotations
+
+import argparse
+import hashlib
+import json
+import math
+import statistics
+from pathlib import Path
+
+MUST_MATCH = ("world_size", "geometry", "precision", "optimizer_state", "warmup_updates", "measured_updates")
+IDENTITIES = ("checkpoint", "data")
+MAY_DIFFER = ("grad_sync", "optimizer", "source_sha256", "torch", "device")
+
+
+def finite(value, name: str, positive: bool = False) -> float:
+    if isinstance(value, bool) or not isinstance(value, (int, float)) or not math.isfinite(value) or (positive and value <= 0):
+        raise ValueError(f"{name} must be a finite{' positive' if positive else ''} number")
+    return float(value)
+
+
+def load_run(directory: Path) -> dict:
+    directory = Path(directory)
+    inputs = []
+
+    def read(path: Path) -> bytes:
+        data = path.read_bytes()
+        inputs.append({"path": str(path), "sha256": hashlib.sha256(data).hexdigest()})
+        return data
+
+    summary = json.loads(read(directory / "summary.json"))
+    if summary.get("format") != "warpstate-training-benchmark-v1":
+        raise ValueError(f"{directory}: not a training-benchmark summary")
+    world = summary["world_size"]
+    geometry = summary["geometry"]
+    if geometry["global_tokens_per_update"] != world * geometry["grad_accum"] * geometry["micro_batch"] * geometry["seq_len"]:
+        raise ValueError("global batch does not match world size, accumulation, micro-batch and sequence length")
+    if summary.get("profile") is not None:
+        raise ValueError("comparisons need unprofiled runs")
+    ranks = {}
+    total = summary["warmup_updates"] + summary["measured_updates"]
+    for rank in range(world):
+        rows = [json.loads(line) for line in read(directory / f"rank-{rank}.jsonl").splitlines() if line.strip()]
+        if len(rows) != total:
+            raise ValueError(f"rank {rank}: {len(rows)} records, expected {total}")
+        for index, row in enumerate(rows):
+            if row["update"] != index or row["measured"] != (index >= summary["warmup_updates"]):
+                raise ValueError("update records must describe one continuous benchmark")
+            if row.get("profiled"):
+                raise ValueError("profiled updates cannot be compared")
+            finite(row["seconds"], "update seconds", positive=True)
+            finite(row["loss"], "loss")
+            finite(row["grad_norm"], "grad_norm")
+            if row["tokens"] != geometry["global_tokens_per_update"]:
+                raise ValueError("update token count differs from the geometry")
+            if not math.isclose(row["tokens_per_second"], row["tokens"] / row["slowest_rank_seconds"], rel_tol=1e-9):
+                raise ValueError("recorded throughput disagrees with tokens and elapsed time")
+        ranks[rank] = rows
+    return {"directory": str(directory), "summary": summary, "ranks": ranks, "input_files": inputs}
+
+
+def differences(left: dict, right: dict) -> dict:
+    return {k: {"control": left.get(k), "candidate": right.get(k)} for k in sorted(set(left) | set(right))
+            if left.get(k) != right.get(k)}
+
+
+def timing_statistics(seconds: list, tokens: int) -> dict:
+    early, late = statistics.mean(seconds[:5]), statistics.mean(seconds[-5:])
+    return {"updates": len(seconds), "mean_seconds": statistics.mean(seconds), "median_seconds": statistics.median(seconds),
+            "std_seconds": statistics.pstdev(seconds), "std_definition": "population",
+            "tokens_per_second": len(seconds) * tokens / sum(seconds), "first_five_mean_seconds": early,
+            "last_five_mean_seconds": late, "first_to_last_seconds_drift_fraction": late / early - 1,
+            "drift_windows_overlap": len(seconds) < 10}
+
+
+def compare(control: dict, candidate: dict) -> dict:
+    a, b = control["summary"], candidate["summary"]
+    for key in MUST_MATCH:
+        if a.get(key) != b.get(key):
+            raise ValueError(f"incompatible runs: {key} differs ({a.get(key)} vs {b.get(key)})")
+    if a["model"]["config"] != b["model"]["config"]:
+        raise ValueError("incompatible runs: model configuration differs")
+    for key in IDENTITIES:
+        if a.get(key) != b.get(key):
+            raise ValueError(f"incompatible runs: {key} identity differs")
+    start, tokens = a["warmup_updates"], a["geometry"]["global_tokens_per_update"]
+    paired = []
+    for index in range(start, start + a["measured_updates"]):
+        per_rank = []
+        for rank in sorted(control["ranks"]):
+            x, y = control["ranks"][rank][index], candidate["ranks"][rank][index]
+            per_rank.append({"rank": rank, "control_loss": x["loss"], "candidate_loss": y["loss"],
+                             "loss_difference": y["loss"] - x["loss"], "control_grad_norm": x["grad_norm"],
+                             "candidate_grad_norm": y["grad_norm"],
+                             "grad_norm_relative_difference": abs(y["grad_norm"] - x["grad_norm"]) / max(abs(x["grad_norm"]), 1e-30)})
+        cs = max(rows[index]["seconds"] for rows in control["ranks"].values())
+        ds = max(rows[index]["seconds"] for rows in candidate["ranks"].values())
+        paired.append({"update": index, "control_seconds": cs, "candidate_seconds": ds, "throughput_ratio": cs / ds,
+                       "ranks": per_rank})
+    ct = timing_statistics([p["control_seconds"] for p in paired], tokens)
+    dt = timing_statistics([p["candidate_seconds"] for p in paired], tokens)
+    memory = []
+    for rank in sorted(control["ranks"]):
+        row = {"rank": rank}
+        for label, run in (("control", control), ("candidate", candidate)):
+            rows = run["ranks"][rank][start:]
+            row[label] = {k: max((r.get(k) or 0) for r in rows) for k in ("peak_allocated_bytes", "peak_reserved_bytes")}
+        memory.append(row)
+    return {"control_timing": ct, "candidate_timing": dt, "throughput_ratio": dt["tokens_per_second"] / ct["tokens_per_second"],
+            "maximum_absolute_loss_difference": max(abs(r["loss_difference"]) for p in paired for r in p["ranks"]),
+            "maximum_relative_grad_norm_difference": max(r["grad_norm_relative_difference"] for p in paired for r in p["ranks"]),
+            "paired_updates": paired, "rank_peak_memory": memory,
+            "recorded_differences": differences({k: a.get(k) for k in MAY_DIFFER}, {k: b.get(k) for k in MAY_DIFFER})}
+
+
+def main(argv=None) -> int:
+    p = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    p.add_argument("--control", required=True, type=Path)
+    p.add_argument("--candidate", required=True, type=Path, action="append")
+    p.add_argument("--output", required=True, type=Path)
+    a = p.parse_args(argv)
+    if a.output.exists():
+        p.error("output already exists; choose a new report path")
+    control = load_run(a.control)
+    report = {"format": "warpstate-benchmark-comparison-v1", "control": {k: control[k] for k in ("directory", "input_files")},
+              "comparisons": []}
+    for directory in a.candidate:
+        candidate = load_run(directory)
+        report["comparisons"].append({"candidate": {k: candidate[k] for k in ("directory", "input_files")},
+                                      **compare(control, candidate)})
+    a.output.parent.mkdir(parents=True, exist_ok=True)
+    a.output.write_text(json.dumps(report, indent=2, allow_nan=False) + "\n")
+    print(json.dumps({"output": str(a.output), "throughput_ratios": [c["throughput_ratio"] for c in report["comparisons"]]}))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

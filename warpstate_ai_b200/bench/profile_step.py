@@ -16,14 +16,15 @@ from collections import defaultdict
 import torch
 
 CATEGORIES = [
-    ("gemm", ("gemm_kernel",)),
+    ("gemm", ("gemm_kernel", "gemm2_kernel")),
     ("attention", ("attn_fwd_kernel", "attn_bwd_kernel", "chunk_writes_kernel", "dstate_kernel", "memory_scan")),
     ("lm_head", ("lmhead", "ce_")),
     ("norm", ("rmsnorm", "colsum")),
+    ("communication", ("nccl", "grad_allreduce", "adamw_shard_push")),
     ("optimizer", ("adamw_kernel", "sumsq_kernel", "clip_coef")),
     ("embedding", ("embed_",)),
     ("cast", ("cast_f32_bf16",)),
-    ("communication", ("nccl", "grad_reduce", "allreduce", "allgather")),
+    ("communication", ("nccl", "grad_allreduce", "adamw_shard_push", "allreduce", "allgather", "all_gather")),
     ("copies", ("Memcpy", "memcpy", "Memset", "memset")),
 ]
 
