@@ -125,3 +125,30 @@ def test_loss_forecast_recovers_a_power_law():
     assert best["parameters"]["model"].startswith("power")
     with pytest.raises(ValueError):
         LF.analyze(b'{"tokens": 5, "loss": 1}\n{"tokens": 4, "loss": 1}')
+
+
+def test_tuner_pairing_policy_and_loader(tmp_path):
+    from warpstate_ai_b200.bench import tune_gemm as TG
+    from warpstate_ai_b200.ops import gemm as G
+    trials = [{"control_before_ms": 1.00, "candidate_ms": 0.90, "control_after_ms": 1.02},
+              {"control_before_ms": 1.01, "candidate_ms": 0.99, "control_after_ms": 0.99}]
+    m = TG.paired_timing_metrics(trials, minimum_gain=0.02)
+    assert m["minimum_trial_gain"] == pytest.approx(1.0 / 0.99 - 1) and m["timing_eligible"] is False
+    assert TG.paired_timing_metrics(trials, minimum_gain=0.005)["timing_eligible"] is True
+    with pytest.raises(ValueError):
+        TG.paired_timing_metrics([{"control_before_ms": 1.0, "candidate_ms": 0.0, "control_after_ms": 1.0}], 0.01)
+    case = TG.cases(16384, ["fwd", "dw"])[0]
+    rows = [{"case": case, "candidate": {"kernel": "single", "sm_limit": 0}, "status": "ok", "eligible": True,
+             "paired_gain": 0.02, "tflops": 1300.0},
+            {"case": case, "candidate": {"kernel": "pair", "sm_limit": 0}, "status": "ok", "eligible": True,
+             "paired_gain": 0.09, "tflops": 1500.0},
+            {"case": case, "candidate": {"kernel": "pair", "sm_limit": 116}, "status": "ok", "eligible": False,
+             "paired_gain": 0.5, "tflops": 9999.0}]
+    policy = TG.select_policy(rows)
+    assert len(policy["entries"]) == 1 and policy["entries"][0]["kernel"] == "pair" and policy["entries"][0]["sm_limit"] == 0
+    path = tmp_path / "candidate-policy.json"
+    path.write_text(json.dumps(policy))
+    assert G.load_policy(path) == 1
+    assert G._policy_key(False, False, 16384, 10240, 2048) == policy["entries"][0]["key"]
+    G._policy.clear()
+    assert TG.main(["--list-cases", "--output-dir", str(tmp_path / "x")]) == 0

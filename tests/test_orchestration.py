@@ -208,3 +208,30 @@ def test_preflight_gate_on_cpu(tmp_path):
     report = json.loads((tmp_path / "pf/report.json").read_text())
     assert report["accepted"] is True and report["frozen_reference_unchanged"] is True
     assert abs(report["initial_validation_loss"] - 0.6931) < 1e-3
+
+
+def test_launch_scripts_and_supervisor_programs_are_consistent():
+    """Every shell launcher parses, points at modules that exist, and every supervisord program
+    names an existing launcher with the stop protocol's signal and wait time."""
+    import configparser
+    launch = ROOT / "launch"
+    scripts = sorted(launch.glob("*.sh"))
+    assert {"train-b200.sh", "train-8gpu.sh", "benchmark.sh", "posttrain-handoff.sh", "dpo-handoff.sh"} <= {s.name for s in scripts}
+    import re
+    for script in scripts:
+        assert subprocess.run(["bash", "-n", str(script)]).returncode == 0, script
+        for module in re.findall(r"-m (warpstate_ai_b200[\w.]+)", script.read_text()):
+            assert (ROOT / (module.replace(".", "/") + ".py")).exists(), (script.name, module)
+    conf = configparser.RawConfigParser()
+    conf.read(launch / "supervisord.conf")
+    programs = [s for s in conf.sections() if s.startswith("program:")]
+    assert len(programs) >= 4
+    for section in programs:
+        command = conf.get(section, "command").split()[0]
+        assert (launch / Path(command).name).exists(), command
+        assert conf.get(section, "autostart") == "false" and conf.get(section, "autorestart") == "false"
+        if "benchmark" not in section:
+            assert conf.get(section, "stopsignal") == "USR1" and conf.getint(section, "stopwaitsecs") >= 865
+    for plan in ("posttrain_plan.json", "dpo_plan.json"):
+        data = json.loads((ROOT / "configs" / plan).read_text())
+        assert data["after_completion"] == "pause_for_evaluation" and data["handoff"]["processes"] >= 1

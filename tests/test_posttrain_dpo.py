@@ -212,3 +212,23 @@ def test_path_rules(workspace):
     with pytest.raises(ValueError, match="inside"):
         SFT.validate_paths("/tmp/elsewhere", root / "data", base, tok, plan)
     SFT.validate_paths(root / "out", root / "data", base, tok, plan)
+
+
+def test_evaluate_snapshot_on_full_holdout(workspace):
+    from warpstate_ai_b200.train import evaluate_snapshot as ES
+    root, tok = workspace
+    export = make_base_export(root, tok, stage="sft", name="sealed")
+    (root / "sealed/tokenizer.model").write_bytes(tok.read_bytes())
+    data = root / "evaldata"
+    prepare(data, tok, 64, sft_rows=conversations(17), val_modulus=3)
+    out = root / "reports/eval.json"
+    assert ES.main(["--snapshot", str(export), "--data-dir", str(data), "--device", "cpu", "--output", str(out)]) == 0
+    report = json.loads(out.read_text())
+    manifest = json.loads((data / "manifest.json").read_text())
+    assert report["full_holdout"] is True and report["evaluated_samples"] == manifest["outputs"]["sft_val.jsonl"]["rows"]
+    assert report["assistant_target_tokens"] == manifest["outputs"]["sft_val.jsonl"]["supervised_tokens"]
+    assert report["val_perplexity"] == pytest.approx(math.exp(report["val_loss"])) and 5 < report["val_loss"] < 12
+    with pytest.raises(ValueError, match="new report"):
+        ES.run(export, data, out, torch.device("cpu"))
+    with pytest.raises(ValueError, match="new report"):
+        ES.run(export, data, data / "inside.json", torch.device("cpu"))

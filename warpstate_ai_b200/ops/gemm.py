@@ -48,8 +48,38 @@ def check_device_errors(device: torch.device | None = None) -> None:
             raise RuntimeError(f"ws_b200 kernel on cuda:{index} reported an error (code {value}: {what})")
 
 
+_policy: dict[str, dict] = {}
+
+
+def load_policy(path) -> int:
+    """Adopt a ``candidate-policy.json`` written by ``bench.tune_gemm``: per problem
+    (``op:tokens x out x in``) which kernel (``pair`` / ``single``) to use.  Returns the number of
+    entries.  Problems without an entry keep the library default."""
+    import json
+    from pathlib import Path
+    data = json.loads(Path(path).read_text())
+    if data.get("format") != "warpstate-gemm-policy-v1":
+        raise ValueError("not a GEMM policy file")
+    _policy.clear()
+    for entry in data["entries"]:
+        _policy[entry["key"]] = {"kernel": entry["kernel"], "sm_limit": int(entry.get("sm_limit", 0))}
+    return len(_policy)
+
+
+def _policy_key(a_mn, b_mn, m, n, k) -> str:
+    if a_mn and b_mn:
+        return f"dw:{k}x{m}x{n}"
+    if b_mn:
+        return f"dx:{m}x{k}x{n}"
+    return f"fwd:{m}x{n}x{k}"
+
+
 def _gemm(a, b, a_mn, b_mn, epi, m, n, k, out, out2=None, aux=None, row_scale=None, alpha=1.0, beta=0.0):
     _ext.require()
+    if _policy:
+        choice = _policy.get(_policy_key(a_mn, b_mn, m, n, k))
+        lib = _ext.cdll()
+        lib.ws_gemm_set_pair_mode(-1 if choice is None else (1 if choice["kernel"] == "pair" else 0))
     torch.ops.ws_b200.gemm(a, b, a_mn, b_mn, epi, m, n, k, out, out2, aux, row_scale,
                            float(alpha), float(beta), error_flag(a.device))
     return out
