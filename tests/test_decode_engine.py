@@ -75,3 +75,108 @@ def test_cuda_engine_matches_forward_in_bf16():
     for t in range(130, 384):
         last = engine2.step(ids[:, t])
     assert torch.allclose(last, logits, rtol=0.05, atol=0.05)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("batch", [1, 16, 17, 64])
+def test_decode_gemm_against_fp32(batch):
+    """Weight-streaming GEMM: all four epilogues, with and without K splits, ragged batch."""
+    from warpstate_ai_b200.ops import _ext, gemm
+    _ext.require()
+    ops = torch.ops.ws_b200
+    torch.manual_seed(batch)
+    flag = gemm.error_flag(torch.device("cuda"))
+
+    def rel(a, b):
+        return float((a.float() - b).norm() / b.norm().clamp_min(1e-12))
+
+    for n, k in [(1280, 256), (256, 1024), (2048, 2048), (2048, 7168), (1000, 512)]:
+        w = (torch.randn(n, k, device="cuda") * 0.05).bfloat16()
+        x = torch.randn(batch, k, device="cuda").bfloat16()
+        ref = x.float() @ w.float().T
+        out = torch.full((batch, n), float("nan"), device="cuda", dtype=torch.bfloat16)
+        ops.decode_gemm(w, x, n, 0, out, flag)
+        assert rel(out, ref) < 0.004, (n, k, "bf16")
+        out32 = torch.full((batch, n), float("nan"), device="cuda")
+        ops.decode_gemm(w, x, n, 3, out32, flag)
+        assert rel(out32, ref) < 1e-4, (n, k, "f32")
+        splits = ops.decode_gemm_splits(n, k)
+        part = torch.full((splits, batch, n), float("nan"), device="cuda")
+        ops.decode_gemm(w, x, n, 1, part, flag)
+        assert rel(part.sum(0), ref) < 1e-4, (n, k, "split", splits)
+    assert ops.decode_gemm_splits(2048, 2048) > 1 and ops.decode_gemm_splits(10240, 2048) == 1
+    h, k = 512, 256
+    w = (torch.randn(2 * h, k, device="cuda") * 0.05).bfloat16()
+    x = torch.randn(batch, k, device="cuda").bfloat16()
+    both = x.float() @ w.float().T
+    ref = both[:, :h] * torch.nn.functional.silu(both[:, h:])
+    act = torch.full((batch, h), float("nan"), device="cuda", dtype=torch.bfloat16)
+    ops.decode_gemm(w, x, h, 2, act, flag)
+    assert rel(act, ref) < 0.006
+    gemm.check_device_errors()
+
+
+@pytest.mark.gpu
+def test_decode_reduce_norm_and_attention_step_kernels():
+    from warpstate_ai_b200.ops import _ext, attention
+    _ext.require()
+    ops = torch.ops.ws_b200
+    torch.manual_seed(3)
+    b, d, h = 5, 256, 4
+    x = torch.randn(b, d, device="cuda")
+    part = torch.randn(3, b, d, device="cuda")
+    scale, bias, w = (torch.randn(d, device="cuda") * 0.1 for _ in range(3))
+    want = (x + part.sum(0)) * (1 + scale) + bias
+    out = torch.empty(b, d, device="cuda", dtype=torch.bfloat16)
+    xx = x.clone()
+    ops.decode_reduce_norm(xx, part, None, None, scale, bias, w, 1e-5, out)
+    assert torch.allclose(xx, want, rtol=1e-5, atol=1e-5)
+    normed = want * torch.rsqrt(want.pow(2).mean(-1, keepdim=True) + 1e-5) * w
+    assert torch.allclose(out.float(), normed, rtol=0.02, atol=0.02)
+    table = torch.randn(50, d, device="cuda")
+    tok = torch.tensor([0, 49, 7, 7, 3], device="cuda")
+    ops.decode_reduce_norm(xx, None, tok, table, None, None, w, 1e-5, out)
+    assert torch.equal(xx, table[tok])
+    # attention step at several in-chunk positions against the PyTorch formulation
+    from warpstate_ai_b200.ops import reference as R
+    rope = attention.rope_table(torch.device("cuda"))
+    cos, sin = R.rope_tables(128, 64, torch.device("cuda"), torch.float32)
+    kc, vc, uc = (torch.randn(b, h, 128, 64, device="cuda").bfloat16() for _ in range(3))
+    mixed = (torch.randn(b, h, 64, 64, device="cuda") * 0.2).bfloat16()
+    for pos in (0, 1, 63, 127):
+        qkvgu = torch.randn(b, 5 * d, device="cuda").bfloat16()
+        q, k, v, g, u = (t.view(b, h, 64) for t in qkvgu.chunk(5, dim=-1))
+        c, s = cos[pos].view(1, 1, 64), sin[pos].view(1, 1, 64)
+        qr = (q.float() * c + R.rotate_pairs(q.float()) * s).bfloat16()
+        kr = (k.float() * c + R.rotate_pairs(k.float()) * s).bfloat16()
+        k2, v2, u2 = kc.clone(), vc.clone(), uc.clone()
+        k2[:, :, pos], v2[:, :, pos], u2[:, :, pos] = kr, v, u
+        scores = torch.einsum("bhd,bhcd->bhc", qr.float(), k2.float()) * 0.125
+        visible = (torch.arange(128, device="cuda") <= pos).view(1, 1, 128)
+        p = torch.softmax(scores.masked_fill(~visible, -torch.inf), dim=-1)
+        local = torch.einsum("bhc,bhcd->bhd", p, v2.float())
+        memory = torch.einsum("bhi,bhij->bhj", qr.float(), mixed.float()) * 0.125
+        gate = torch.sigmoid(g.float())
+        ref = (gate * local + (1 - gate) * memory).reshape(b, d)
+        y = torch.empty(b, d, device="cuda", dtype=torch.bfloat16)
+        ka, va, ua = kc.clone(), vc.clone(), uc.clone()
+        ops.decode_attn(qkvgu, ka, va, ua, mixed, rope, torch.tensor(pos, device="cuda"), h, y)
+        assert torch.allclose(y.float(), ref, rtol=0.02, atol=0.02), pos
+        assert torch.equal(ka, k2) and torch.equal(va, v2) and torch.equal(ua, u2)
+
+
+@pytest.mark.gpu
+def test_kernel_decode_path_matches_pytorch_path():
+    torch.manual_seed(1)
+    cfg = WarpStateConfig(vocab_size=512, d_model=256, n_heads=4, n_cores=2, logical_depth=3, ffn_hidden=512,
+                          chunk_size=128, gradient_checkpointing=False, parallel_memory=True)
+    model = WarpStateLM(cfg).cuda().eval()
+    ids = torch.randint(0, 512, (3, 200), device="cuda")
+    fast = DecodeEngine(model, dtype=torch.bfloat16)
+    slow = DecodeEngine(model, dtype=torch.bfloat16, use_kernels=False, use_cuda_graph=False)
+    assert fast._kernels_usable(3) and not slow._kernels_usable(3)
+    for t in range(200):   # crosses a chunk boundary at 128
+        a, b = fast.step(ids[:, t]), slow.step(ids[:, t])
+        if t % 37 == 0 or t == 199:
+            assert torch.allclose(a, b, rtol=0.05, atol=0.05), t
+    assert fast._kbufs is not None and slow._kbufs is None

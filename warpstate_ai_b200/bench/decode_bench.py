@@ -23,6 +23,7 @@ def main() -> None:
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--new-tokens", type=int, default=512)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-kernels", action="store_true", help="PyTorch/cuBLAS formulation of the step (the comparison arm)")
     args = ap.parse_args()
     from .. import WarpStateLM, warpstate_2b, warpstate_smoke
     from ..ops import _ext
@@ -36,7 +37,7 @@ def main() -> None:
     with torch.device(device):
         model = WarpStateLM(cfg)
     model.eval().requires_grad_(False)
-    engine = DecodeEngine(model, dtype=torch.bfloat16, use_cuda_graph=not args.no_graph)
+    engine = DecodeEngine(model, dtype=torch.bfloat16, use_cuda_graph=not args.no_graph, use_kernels=not args.no_kernels)
     prompts = torch.randint(0, cfg.vocab_size, (args.batch, args.prompt), device=device)
     generate_batch(engine, prompts[:, :256], 4)  # warm-up (graph capture, lazy initialisation)
     before = _ext.launch_count()

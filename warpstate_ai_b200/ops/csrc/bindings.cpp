@@ -483,9 +483,106 @@ void adamw_shard_push(at::IntArrayRef master_ptrs, at::IntArrayRef bf16_ptrs, in
            "adamw_shard_push");
 }
 
+// ----------------------------------------------------------------------------- decode step
+int64_t decode_gemm_splits(int64_t n, int64_t k) { return ws_decode_gemm_splits((int)n, (int)k); }
+
+void decode_gemm(const at::Tensor& w, const at::Tensor& x, int64_t n, int64_t epilogue, at::Tensor out,
+                 c10::optional<at::Tensor> error_flag) {
+  TORCH_CHECK(w.is_cuda() && x.is_cuda() && out.is_cuda(), "decode_gemm: CUDA tensors required");
+  TORCH_CHECK(w.scalar_type() == at::kBFloat16 && x.scalar_type() == at::kBFloat16 && w.is_contiguous() &&
+              x.is_contiguous() && w.dim() == 2 && x.dim() == 2 && w.size(1) == x.size(1),
+              "decode_gemm: contiguous BF16 W [rows, k] and x [batch, k] required");
+  const int64_t k = x.size(1), batch = x.size(0);
+  TORCH_CHECK(batch >= 1 && batch <= 64 && k % 8 == 0, "decode_gemm: batch must be 1..64 and k a multiple of 8");
+  TORCH_CHECK(w.size(0) == (epilogue == 2 ? 2 * n : n), "decode_gemm: W row count does not match n");
+  TORCH_CHECK(reinterpret_cast<uintptr_t>(w.data_ptr()) % 16 == 0 && reinterpret_cast<uintptr_t>(x.data_ptr()) % 16 == 0,
+              "decode_gemm: 16-byte aligned operands required");
+  TORCH_CHECK(out.is_contiguous(), "decode_gemm: contiguous out required");
+  if (epilogue == 1) {
+    TORCH_CHECK(out.scalar_type() == at::kFloat && out.numel() == decode_gemm_splits(n, k) * batch * n,
+                "decode_gemm: partial buffer must be FP32 [splits, batch, n]");
+  } else {
+    TORCH_CHECK(out.scalar_type() == (epilogue == 3 ? at::kFloat : at::kBFloat16) && out.dim() == 2 &&
+                out.size(0) == batch && out.size(1) == n, "decode_gemm: out must be [batch, n] of the epilogue's dtype");
+  }
+  c10::cuda::CUDAGuard guard(w.device());
+  check_rc(ws_decode_gemm(w.data_ptr(), x.data_ptr(), (int)n, (int)k, (int)batch, (int)epilogue, out.data_ptr(), (int)n,
+                          reinterpret_cast<int*>(const_cast<void*>(opt_ptr(error_flag))), cur_stream()), "decode_gemm");
+}
+
+void decode_reduce_norm(at::Tensor x, const c10::optional<at::Tensor>& partial, const c10::optional<at::Tensor>& token,
+                        const c10::optional<at::Tensor>& table, const c10::optional<at::Tensor>& scale,
+                        const c10::optional<at::Tensor>& bias, const at::Tensor& w, double eps,
+                        c10::optional<at::Tensor> out) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kFloat && x.dim() == 2 && x.is_contiguous(), "decode_reduce_norm: x");
+  const int64_t batch = x.size(0), d = x.size(1);
+  TORCH_CHECK(d % 4 == 0 && w.scalar_type() == at::kFloat && w.numel() == d && w.is_contiguous(), "decode_reduce_norm: w");
+  int splits = 0;
+  const float* pp = nullptr;
+  if (partial.has_value() && partial->defined()) {
+    TORCH_CHECK(partial->scalar_type() == at::kFloat && partial->is_contiguous() && partial->numel() % (batch * d) == 0,
+                "decode_reduce_norm: partial must be FP32 [splits, batch, d]");
+    splits = (int)(partial->numel() / (batch * d));
+    pp = partial->data_ptr<float>();
+  }
+  const long long* tok = nullptr;
+  const float* tab = nullptr;
+  int vocab = 0;
+  if (token.has_value() && token->defined()) {
+    TORCH_CHECK(table.has_value() && token->scalar_type() == at::kLong && token->numel() == batch && token->is_contiguous() &&
+                table->scalar_type() == at::kFloat && table->is_contiguous() && table->size(1) == d && splits == 0,
+                "decode_reduce_norm: token [batch] int64 with an FP32 table [vocab, d], and no partials");
+    tok = reinterpret_cast<const long long*>(token->data_ptr<int64_t>());
+    tab = table->data_ptr<float>();
+    vocab = (int)table->size(0);
+  }
+  const bool mod = scale.has_value() && scale->defined();
+  if (mod) {
+    TORCH_CHECK(bias.has_value() && scale->scalar_type() == at::kFloat && bias->scalar_type() == at::kFloat &&
+                scale->numel() == d && bias->numel() == d && scale->is_contiguous() && bias->is_contiguous(),
+                "decode_reduce_norm: modulation vectors must be FP32 [d]");
+  }
+  void* op = nullptr;
+  if (out.has_value() && out->defined()) {
+    TORCH_CHECK(out->scalar_type() == at::kBFloat16 && out->is_contiguous() && out->numel() == batch * d, "decode_reduce_norm: out");
+    op = out->data_ptr();
+  }
+  c10::cuda::CUDAGuard guard(x.device());
+  check_rc(ws_decode_reduce_norm(x.data_ptr<float>(), pp, splits, tok, tab, vocab, mod ? scale->data_ptr<float>() : nullptr,
+                                 mod ? bias->data_ptr<float>() : nullptr, w.data_ptr<float>(), (float)eps, (int)d,
+                                 (int)batch, op, cur_stream()), "decode_reduce_norm");
+}
+
+void decode_attn(const at::Tensor& qkvgu, at::Tensor kc, at::Tensor vc, at::Tensor uc, const at::Tensor& mixed,
+                 const at::Tensor& rope, const at::Tensor& pos, int64_t H, at::Tensor y) {
+  TORCH_CHECK(qkvgu.is_cuda() && qkvgu.scalar_type() == at::kBFloat16 && qkvgu.dim() == 2 && qkvgu.is_contiguous(),
+              "decode_attn: qkvgu must be contiguous BF16 [batch, 5d]");
+  const int64_t batch = qkvgu.size(0), d = qkvgu.size(1) / 5;
+  TORCH_CHECK(d == H * 64, "decode_attn: head_dim must be 64");
+  for (const at::Tensor* t : {&kc, &vc, &uc}) {
+    TORCH_CHECK(t->scalar_type() == at::kBFloat16 && t->is_contiguous() && t->numel() == batch * H * 128 * 64,
+                "decode_attn: caches must be contiguous BF16 [batch, H, 128, 64]");
+  }
+  TORCH_CHECK(mixed.scalar_type() == at::kBFloat16 && mixed.is_contiguous() && mixed.numel() == batch * H * 64 * 64,
+              "decode_attn: mixed state must be contiguous BF16 [batch, H, 64, 64]");
+  TORCH_CHECK(rope.scalar_type() == at::kFloat && rope.is_contiguous() && rope.numel() == 128 * 32 * 2, "decode_attn: rope table");
+  TORCH_CHECK(pos.scalar_type() == at::kLong && pos.numel() == 1 && pos.is_cuda(), "decode_attn: pos must be a CUDA int64 scalar");
+  TORCH_CHECK(y.scalar_type() == at::kBFloat16 && y.is_contiguous() && y.numel() == batch * d, "decode_attn: y");
+  c10::cuda::CUDAGuard guard(qkvgu.device());
+  check_rc(ws_decode_attn(qkvgu.data_ptr(), kc.data_ptr(), vc.data_ptr(), uc.data_ptr(), mixed.data_ptr(),
+                          rope.data_ptr<float>(), reinterpret_cast<const long long*>(pos.data_ptr<int64_t>()), (int)batch,
+                          (int)H, (int)d, y.data_ptr(), cur_stream()), "decode_attn");
+}
+
 }  // namespace
 
 TORCH_LIBRARY(ws_b200, m) {
+  m.def("decode_gemm_splits(int n, int k) -> int");
+  m.def("decode_gemm(Tensor w, Tensor x, int n, int epilogue, Tensor(a!) out, Tensor(b!)? error_flag) -> ()");
+  m.def("decode_reduce_norm(Tensor(a!) x, Tensor? partial, Tensor? token, Tensor? table, Tensor? scale, Tensor? bias, "
+        "Tensor w, float eps, Tensor(b!)? out) -> ()");
+  m.def("decode_attn(Tensor qkvgu, Tensor(a!) kc, Tensor(b!) vc, Tensor(c!) uc, Tensor mixed, Tensor rope, Tensor pos, "
+        "int H, Tensor(d!) y) -> ()");
   m.def("rmsnorm_fwd(Tensor x, Tensor? col_scale, Tensor? col_bias, Tensor w, float eps, bool want_xmod) -> (Tensor, Tensor, Tensor)");
   m.def("rmsnorm_bwd(Tensor dz, Tensor x, Tensor rstd, Tensor w, Tensor? dres, Tensor? out_scale, bool want_bf16) -> (Tensor, Tensor, Tensor)");
   m.def("colsum2(Tensor a, Tensor b, Tensor? inv_scale) -> (Tensor, Tensor)");
@@ -519,10 +616,14 @@ TORCH_LIBRARY(ws_b200, m) {
 
 TORCH_LIBRARY_IMPL(ws_b200, CompositeExplicitAutograd, m) {
   m.impl("launch_count", &launch_count);
+  m.impl("decode_gemm_splits", &decode_gemm_splits);
 }
 
 TORCH_LIBRARY_IMPL(ws_b200, CUDA, m) {
   m.impl("gemm", &gemm);
+  m.impl("decode_gemm", &decode_gemm);
+  m.impl("decode_reduce_norm", &decode_reduce_norm);
+  m.impl("decode_attn", &decode_attn);
   m.impl("grad_weight_group", &grad_weight_group);
   m.impl("rmsnorm_fwd", &rmsnorm_fwd);
   m.impl("rmsnorm_bwd", &rmsnorm_bwd);

@@ -1,0 +1,458 @@
+// Decode-step kernels: one new token for every sequence of a batch (batch <= 64).
+//
+// A decode step is bound by streaming the weights once (4.0 GB for the 2.005 B model) and the
+// current chunk's K/V cache, so the GEMMs here are weight-streaming kernels, not tile kernels:
+//
+//   decode_gemm_kernel     out[b, n] = sum_k x[b, k] W[n, k].  The roles of the MMA operands are
+//                          swapped with respect to training: 128 weight rows are the M dimension of
+//                          tcgen05.mma, the (padded) batch is its N dimension, so one CTA streams a
+//                          128-row slab of W exactly once through an 8-stage TMA ring while the
+//                          tiny activation block comes from L2.  Slabs x K-splits give >= 128 CTAs
+//                          for every projection of the model; split partials are FP32.
+//                          Epilogues: BF16, FP32 (logits), FP32 split-K partial, SwiGLU (64 up rows
+//                          and their 64 gate rows share a slab).
+//   decode_reduce_norm_kernel  x += sum of split partials (or x = embedding row), optional depth
+//                          modulation of the next layer, RMSNorm -> BF16: everything between two
+//                          GEMMs of the residual stream in one pass, one CTA per sequence.
+//   decode_attn_kernel     one CTA per (sequence, head): RoPE of q/k at the in-chunk position,
+//                          append k/v/u to the chunk cache, causal attention over the cache rows
+//                          <= position, memory read q.M, gate blend.
+//
+// Reference semantics: WarpStateCore.step (reference warpstate/model.py:222-274) in the
+// training-consistent form of ops/posttrain_chat.py:94-142.  The reference runs these as
+// ~40 eager PyTorch ops per layer at batch 1.
+#include "ws_ptx.cuh"
+#include "ws_api.h"
+#include "ws_tma_host.h"
+
+#include <cuda_bf16.h>
+
+namespace ws {
+
+extern "C" void ws_count_launch(void);
+
+namespace dec {
+constexpr int TM = 128;  // weight rows per slab
+constexpr int BK = 64;
+constexpr int THREADS = 192;  // warp 0 TMA, warp 1 MMA + TMEM, warps 2..5 epilogue
+constexpr int W_BYTES = TM * BK * 2;
+}  // namespace dec
+
+struct DecodeGemmParams {
+  int n;        // output features (SwiGLU: hidden size h; W has 2h rows)
+  int k;
+  int batch;
+  int kb_per_split;
+  void* out;    // BF16 [batch, ldo] | FP32 [batch, ldo] | FP32 partial [splits, batch, n]
+  int ldo;
+  int* error_flag;
+};
+
+template <int BPAD>
+struct DecodeCfg {
+  static constexpr int STAGES = 8;
+  static constexpr int X_BYTES = BPAD * dec::BK * 2;
+  static constexpr int STAGE_BYTES = dec::W_BYTES + X_BYTES;
+  static constexpr int EXCHANGE_BYTES = 64 * BPAD * 4;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + EXCHANGE_BYTES + 1024 + 256;
+  static constexpr int TMEM_COLS = BPAD < 32 ? 32 : BPAD;
+};
+
+// EPI: 0 = BF16 out, 1 = FP32 split-K partial, 2 = SwiGLU (BF16 activation), 3 = FP32 out
+template <int BPAD, int EPI>
+__global__ void __launch_bounds__(dec::THREADS, 1)
+decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+                   const DecodeGemmParams p) {
+  using namespace dec;
+  using Cfg = DecodeCfg<BPAD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* sW = smem;
+  uint8_t* sX = smem + Cfg::STAGES * W_BYTES;
+  float* sG = reinterpret_cast<float*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES + Cfg::EXCHANGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + Cfg::STAGES;
+  uint64_t* tfull = bars + 2 * Cfg::STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * Cfg::STAGES + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(tfull, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_w);
+    tma_prefetch_desc(&tm_x);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+
+  const int slab = blockIdx.x;
+  const int total_kb = (p.k + BK - 1) / BK;
+  const int kb0 = blockIdx.y * p.kb_per_split;
+  const int kb1 = min(total_kb, kb0 + p.kb_per_split);
+  const int rows_per_slab = EPI == 2 ? 64 : TM;
+  const int n0 = slab * rows_per_slab;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = kb0, it = 0; kb < kb1; ++kb, ++it) {
+        const int s = it % Cfg::STAGES;
+        const uint32_t ph = (it / Cfg::STAGES) & 1;
+        if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) break;
+        mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
+        if (EPI == 2) {  // 64 up rows + the 64 matching gate rows
+          tma_load_2d(sW + s * W_BYTES, &tm_w, &full[s], kb * BK, n0);
+          tma_load_2d(sW + s * W_BYTES + 64 * 128, &tm_w, &full[s], kb * BK, p.n + n0);
+        } else {
+          tma_load_2d(sW + s * W_BYTES, &tm_w, &full[s], kb * BK, n0);
+        }
+        tma_load_2d(sX + s * Cfg::X_BYTES, &tm_x, &full[s], kb * BK, 0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(TM, BPAD, false, false);
+      bool ok = true;
+      for (int kb = kb0, it = 0; kb < kb1; ++kb, ++it) {
+        const int s = it % Cfg::STAGES;
+        const uint32_t ph = (it / Cfg::STAGES) & 1;
+        if (!mbar_wait(&full[s], ph, abort_flag)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t a = smem_u32(sW + s * W_BYTES), b = smem_u32(sX + s * Cfg::X_BYTES);
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k)
+          umma_bf16(tmem, make_smem_desc_sw128(a + k * 32, 0, 1024), make_smem_desc_sw128(b + k * 32, 0, 1024), idesc,
+                    (it | k) != 0 ? 1u : 0u);
+        umma_commit(&empty[s]);
+      }
+      if (ok) umma_commit(tfull);
+    }
+  } else {
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+    const int row = quarter * 32 + lane;
+    const bool ok = kb1 > kb0 && mbar_wait(tfull, 0, abort_flag);
+    tc_fence_after_sync();
+    const uint32_t taddr = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
+    if (EPI == 2) {
+      // rows 0..63 = up, 64..127 = gate: the gate warps hand silu-ready values over through smem
+      if (row >= 64 && ok) {
+#pragma unroll
+        for (int c0 = 0; c0 < BPAD; c0 += 16) {
+          uint32_t r[16];
+          tmem_ld_32x32b_x16(taddr + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float g = __uint_as_float(r[j]);
+            sG[(c0 + j) * 64 + (row - 64)] = g * sigmoid_fast(g);
+          }
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (row < 64 && ok) {
+        const int hcol = n0 + row;
+        __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
+#pragma unroll
+        for (int c0 = 0; c0 < BPAD; c0 += 16) {
+          uint32_t r[16];
+          tmem_ld_32x32b_x16(taddr + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int b = c0 + j;
+            if (b < p.batch && hcol < p.n)
+              out[static_cast<size_t>(b) * p.ldo + hcol] = __float2bfloat16(__uint_as_float(r[j]) * sG[b * 64 + row]);
+          }
+        }
+      }
+    } else if (ok) {
+      const int n = n0 + row;
+#pragma unroll
+      for (int c0 = 0; c0 < BPAD; c0 += 16) {
+        uint32_t r[16];
+        tmem_ld_32x32b_x16(taddr + c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int b = c0 + j;
+          if (b >= p.batch || n >= p.n) continue;
+          const float v = __uint_as_float(r[j]);
+          if (EPI == 0) {
+            static_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(b) * p.ldo + n] = __float2bfloat16(v);
+          } else if (EPI == 3) {
+            static_cast<float*>(p.out)[static_cast<size_t>(b) * p.ldo + n] = v;
+          } else {
+            static_cast<float*>(p.out)[(static_cast<size_t>(blockIdx.y) * p.batch + b) * p.n + n] = v;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag != 0 && p.error_flag != nullptr) atomicExch(p.error_flag, 8);
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, Cfg::TMEM_COLS);
+  }
+}
+
+// --------------------------------------------------------------------------- residual + norm
+// One CTA per sequence.  x (FP32 residual stream, [batch, d]) is updated in place:
+//   token != null : x = table[token[b]]           (embedding gather)
+//   partial != null: x += sum_s partial[s][b]     (split-K partials of the previous projection)
+//   scale != null : x = x * (1 + scale) + bias    (depth modulation of the layer that follows)
+// then out = BF16(x * rsqrt(mean(x^2) + eps) * w).
+__global__ void __launch_bounds__(256)
+decode_reduce_norm_kernel(float* __restrict__ x, const float* __restrict__ partial, int splits,
+                          const long long* __restrict__ token, const float* __restrict__ table, int vocab,
+                          const float* __restrict__ scale, const float* __restrict__ bias, const float* __restrict__ w,
+                          float eps, int d, int batch, __nv_bfloat16* __restrict__ out) {
+  __shared__ float red[8];
+  const int b = blockIdx.x;
+  float* xr = x + static_cast<size_t>(b) * d;
+  const float* src = xr;
+  if (token != nullptr) {
+    long long id = token[b];
+    if (id < 0) id = 0;
+    if (id >= vocab) id = vocab - 1;
+    src = table + static_cast<size_t>(id) * d;
+  }
+  float ss = 0.f;
+  for (int c = threadIdx.x * 4; c < d; c += 256 * 4) {
+    float4 v = *reinterpret_cast<const float4*>(src + c);
+    for (int s = 0; s < splits; ++s) {
+      const float4 q = *reinterpret_cast<const float4*>(partial + (static_cast<size_t>(s) * batch + b) * d + c);
+      v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
+    }
+    if (scale != nullptr) {
+      const float4 sc = *reinterpret_cast<const float4*>(scale + c), bi = *reinterpret_cast<const float4*>(bias + c);
+      v.x = v.x * (1.f + sc.x) + bi.x; v.y = v.y * (1.f + sc.y) + bi.y;
+      v.z = v.z * (1.f + sc.z) + bi.z; v.w = v.w * (1.f + sc.w) + bi.w;
+    }
+    *reinterpret_cast<float4*>(xr + c) = v;
+    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float total = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) total += red[i];
+  const float rstd = rsqrtf(total / static_cast<float>(d) + eps);
+  if (out == nullptr) return;
+  for (int c = threadIdx.x * 4; c < d; c += 256 * 4) {
+    const float4 v = *reinterpret_cast<const float4*>(xr + c);  // this thread's own stores
+    const float4 ww = *reinterpret_cast<const float4*>(w + c);
+    uint2 o;
+    o.x = pack_bf16x2(v.x * rstd * ww.x, v.y * rstd * ww.y);
+    o.y = pack_bf16x2(v.z * rstd * ww.z, v.w * rstd * ww.w);
+    *reinterpret_cast<uint2*>(out + static_cast<size_t>(b) * d + c) = o;
+  }
+}
+
+// --------------------------------------------------------------------------- attention step
+// One CTA of 128 threads per (sequence, head); head_dim 64, chunk 128.
+// qkvgu: [batch, 5*d] BF16 (q | k | v | gate | u); caches kc/vc/uc: [batch, H, 128, 64] BF16;
+// mixed: [batch, H, 64, 64] BF16 (mix*fast + (1-mix)*slow); rope: [128, 32] (cos, sin);
+// y: [batch, d] BF16.  `pos_ptr` is the in-chunk position (device scalar, so that one captured
+// graph serves every position).
+__global__ void __launch_bounds__(128)
+decode_attn_kernel(const __nv_bfloat16* __restrict__ qkvgu, __nv_bfloat16* __restrict__ kc,
+                   __nv_bfloat16* __restrict__ vc, __nv_bfloat16* __restrict__ uc,
+                   const __nv_bfloat16* __restrict__ mixed, const float2* __restrict__ rope,
+                   const long long* __restrict__ pos_ptr, int H, int d, __nv_bfloat16* __restrict__ y) {
+  constexpr int HD = 64, C = 128;
+  __shared__ float sq[HD], sk[HD], sp[C], sacc[2][HD], sred[4];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int h = blockIdx.x % H, b = blockIdx.x / H;
+  int pos = static_cast<int>(*pos_ptr);
+  pos = pos < 0 ? 0 : (pos >= C ? C - 1 : pos);
+  const __nv_bfloat16* row = qkvgu + static_cast<size_t>(b) * 5 * d + h * HD;
+  const size_t cache = (static_cast<size_t>(b) * H + h) * C * HD;
+  // RoPE (adjacent pairs) of q and k; append k, v, u at `pos`
+  if (tid < 32) {
+    const float2 cs = rope[pos * 32 + tid];
+    const float2 q = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(row + 2 * tid));
+    const float2 k = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(row + d + 2 * tid));
+    // round through BF16 as the cached / batched path does
+    const __nv_bfloat162 qr = __floats2bfloat162_rn(q.x * cs.x - q.y * cs.y, q.y * cs.x + q.x * cs.y);
+    const __nv_bfloat162 kr = __floats2bfloat162_rn(k.x * cs.x - k.y * cs.y, k.y * cs.x + k.x * cs.y);
+    const float2 qf = __bfloat1622float2(qr), kf = __bfloat1622float2(kr);
+    sq[2 * tid] = qf.x; sq[2 * tid + 1] = qf.y;
+    sk[2 * tid] = kf.x; sk[2 * tid + 1] = kf.y;
+    *reinterpret_cast<__nv_bfloat162*>(kc + cache + static_cast<size_t>(pos) * HD + 2 * tid) = kr;
+  } else if (tid < 64) {
+    const int t = tid - 32;
+    *reinterpret_cast<__nv_bfloat162*>(vc + cache + static_cast<size_t>(pos) * HD + 2 * t) =
+        *reinterpret_cast<const __nv_bfloat162*>(row + 2 * d + 2 * t);
+  } else if (tid < 96) {
+    const int t = tid - 64;
+    *reinterpret_cast<__nv_bfloat162*>(uc + cache + static_cast<size_t>(pos) * HD + 2 * t) =
+        *reinterpret_cast<const __nv_bfloat162*>(row + 4 * d + 2 * t);
+  }
+  __syncthreads();
+  // scores: thread c owns key c
+  float score = -INFINITY;
+  if (tid <= pos) {
+    float acc = 0.f;
+    if (tid == pos) {
+#pragma unroll
+      for (int i = 0; i < HD; ++i) acc += sq[i] * sk[i];
+    } else {
+      const uint4* kr = reinterpret_cast<const uint4*>(kc + cache + static_cast<size_t>(tid) * HD);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint4 v = kr[j];
+        const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float2 f = __bfloat1622float2(pb[t]);
+          acc += sq[j * 8 + 2 * t] * f.x + sq[j * 8 + 2 * t + 1] * f.y;
+        }
+      }
+    }
+    score = acc * 0.125f;
+  }
+  float m = score;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if (lane == 0) sred[warp] = m;
+  __syncthreads();
+  m = fmaxf(fmaxf(sred[0], sred[1]), fmaxf(sred[2], sred[3]));
+  const float e = tid <= pos ? __expf(score - m) : 0.f;
+  float s = e;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  __syncthreads();
+  if (lane == 0) sred[warp] = s;
+  sp[tid] = e;
+  __syncthreads();
+  const float inv = 1.f / (sred[0] + sred[1] + sred[2] + sred[3]);
+  // local = sum_c p[c] V[c]: two halves of the key range in parallel, 64 columns each
+  {
+    const int col = tid & 63, half = tid >> 6;
+    const int c_lo = half * 64, c_hi = min(pos + 1, c_lo + 64);
+    float acc = 0.f;
+    for (int c = c_lo; c < c_hi; ++c) {
+      const float v = (c == pos) ? __bfloat162float(row[2 * d + col]) : __bfloat162float(vc[cache + static_cast<size_t>(c) * HD + col]);
+      acc += sp[c] * v;
+    }
+    sacc[half][col] = acc;
+  }
+  __syncthreads();
+  if (tid < HD) {
+    const float local = (sacc[0][tid] + sacc[1][tid]) * inv;
+    // memory read: q . M  (M[i][j], j = this thread's column)
+    const __nv_bfloat16* mrow = mixed + (static_cast<size_t>(b) * H + h) * HD * HD + tid;
+    float mem = 0.f;
+#pragma unroll 8
+    for (int i = 0; i < HD; ++i) mem += sq[i] * __bfloat162float(mrow[i * HD]);
+    mem *= 0.125f;
+    const float g = sigmoid_fast(__bfloat162float(row[3 * d + tid]));
+    y[static_cast<size_t>(b) * d + h * HD + tid] = __float2bfloat16(g * local + (1.f - g) * mem);
+  }
+}
+
+template <int BPAD, int EPI>
+static int launch_decode_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const DecodeGemmParams& p, dim3 grid,
+                              cudaStream_t stream) {
+  static bool configured = false;
+  auto kern = decode_gemm_kernel<BPAD, EPI>;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeCfg<BPAD>::SMEM) != cudaSuccess)
+      return -20;
+    configured = true;
+  }
+  kern<<<grid, dec::THREADS, DecodeCfg<BPAD>::SMEM, stream>>>(tw, tx, p);
+  ws_count_launch();
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+}  // namespace ws
+
+using namespace ws;
+
+// Number of K splits ws_decode_gemm uses for an [n x k] weight (the caller sizes the FP32 partial
+// buffer as splits * batch * n floats when the result is > 1).
+extern "C" int ws_decode_gemm_splits(int n, int k) {
+  const int slabs = (n + dec::TM - 1) / dec::TM;
+  const int total_kb = (k + dec::BK - 1) / dec::BK;
+  int splits = 148 / (slabs > 0 ? slabs : 1);
+  if (splits < 1) splits = 1;
+  while (splits > 1 && total_kb / splits < 4) --splits;
+  const int per = (total_kb + splits - 1) / splits;
+  return (total_kb + per - 1) / per;  // no split is empty
+}
+
+// epilogue: 0 BF16 out [batch, ldo]; 1 FP32 split-K partials [splits, batch, n] (splits from
+// ws_decode_gemm_splits); 2 SwiGLU, W is [2n, k] (up rows then gate rows), BF16 out [batch, ldo];
+// 3 FP32 out [batch, ldo].  batch <= 64; k % 8 == 0.
+extern "C" int ws_decode_gemm(const void* w, const void* x, int n, int k, int batch, int epilogue, void* out, int ldo,
+                              int* error_flag, cudaStream_t stream) {
+  if (n <= 0 || k <= 0 || batch <= 0 || batch > 64 || k % 8 != 0 || epilogue < 0 || epilogue > 3) return -1;
+  if (epilogue == 2 && n % 64 != 0) return -2;
+  CUtensorMap tw, tx;
+  const int w_rows = epilogue == 2 ? 2 * n : n;
+  int rc = make_map_bf16(&tw, w, k, w_rows, k, dec::BK, epilogue == 2 ? 64 : dec::TM);
+  if (rc) return rc;
+  const int bpad = batch <= 16 ? 16 : 64;
+  rc = make_map_bf16(&tx, x, k, batch, k, dec::BK, bpad);
+  if (rc) return rc;
+  DecodeGemmParams p;
+  p.n = n; p.k = k; p.batch = batch; p.out = out; p.ldo = ldo; p.error_flag = error_flag;
+  const int total_kb = (k + dec::BK - 1) / dec::BK;
+  int splits = 1;
+  if (epilogue == 1) splits = ws_decode_gemm_splits(n, k);
+  p.kb_per_split = (total_kb + splits - 1) / splits;
+  const int slabs = epilogue == 2 ? n / 64 : (n + dec::TM - 1) / dec::TM;
+  const dim3 grid(slabs, splits);
+  const int key = (bpad == 16 ? 0 : 4) + epilogue;
+  switch (key) {
+    case 0: return launch_decode_gemm<16, 0>(tw, tx, p, grid, stream);
+    case 1: return launch_decode_gemm<16, 1>(tw, tx, p, grid, stream);
+    case 2: return launch_decode_gemm<16, 2>(tw, tx, p, grid, stream);
+    case 3: return launch_decode_gemm<16, 3>(tw, tx, p, grid, stream);
+    case 4: return launch_decode_gemm<64, 0>(tw, tx, p, grid, stream);
+    case 5: return launch_decode_gemm<64, 1>(tw, tx, p, grid, stream);
+    case 6: return launch_decode_gemm<64, 2>(tw, tx, p, grid, stream);
+    default: return launch_decode_gemm<64, 3>(tw, tx, p, grid, stream);
+  }
+}
+
+extern "C" int ws_decode_reduce_norm(float* x, const float* partial, int splits, const long long* token,
+                                     const float* table, int vocab, const float* scale, const float* bias,
+                                     const float* w, float eps, int d, int batch, void* out, cudaStream_t stream) {
+  if (d % 4 != 0 || batch <= 0 || (splits > 0 && partial == nullptr)) return -1;
+  decode_reduce_norm_kernel<<<batch, 256, 0, stream>>>(x, partial, splits, token, table, vocab, scale, bias, w, eps, d,
+                                                       batch, static_cast<__nv_bfloat16*>(out));
+  ws_count_launch();
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+extern "C" int ws_decode_attn(const void* qkvgu, void* kc, void* vc, void* uc, const void* mixed, const float* rope,
+                              const long long* pos, int batch, int H, int d, void* y, cudaStream_t stream) {
+  if (d != H * 64 || batch <= 0) return -1;
+  decode_attn_kernel<<<batch * H, 128, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(qkvgu), static_cast<__nv_bfloat16*>(kc), static_cast<__nv_bfloat16*>(vc),
+      static_cast<__nv_bfloat16*>(uc), static_cast<const __nv_bfloat16*>(mixed), reinterpret_cast<const float2*>(rope), pos,
+      H, d, static_cast<__nv_bfloat16*>(y));
+  ws_count_launch();
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}

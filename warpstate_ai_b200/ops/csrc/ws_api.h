@@ -55,6 +55,22 @@ int ws_gemm(const WsGemm* g, cudaStream_t stream);
 // with >= 256 rows, count <= 4); otherwise equivalent to calling ws_gemm on each item in order.
 int ws_gemm_group(const WsGemm* items, int count, cudaStream_t stream);
 void ws_gemm_set_sm_limit(int sms);
+// ---- decode step (ops/csrc/decode.cu); batch <= 64
+// out[b, n] = sum_k x[b, k] W[n, k] as a weight-streaming kernel.  epilogue: 0 BF16 [batch, ldo];
+// 1 FP32 split-K partials [ws_decode_gemm_splits(n, k), batch, n]; 2 SwiGLU with W = [2n, k]
+// (up rows, then gate rows), BF16 [batch, ldo]; 3 FP32 [batch, ldo].
+int ws_decode_gemm_splits(int n, int k);
+int ws_decode_gemm(const void* w, const void* x, int n, int k, int batch, int epilogue, void* out, int ldo,
+                   int* error_flag, cudaStream_t stream);
+// x (FP32 [batch, d], in place) = table[token] if token else x + sum of split partials; optional
+// depth modulation x*(1+scale)+bias; out (BF16 [batch, d], may be NULL) = RMSNorm(x) * w.
+int ws_decode_reduce_norm(float* x, const float* partial, int splits, const long long* token, const float* table,
+                          int vocab, const float* scale, const float* bias, const float* w, float eps, int d,
+                          int batch, void* out, cudaStream_t stream);
+// One decode step of the attention block for every (sequence, head); see decode_attn_kernel.
+int ws_decode_attn(const void* qkvgu, void* kc, void* vc, void* uc, const void* mixed, const float* rope,
+                   const long long* pos, int batch, int H, int d, void* y, cudaStream_t stream);
+
 // Kernel choice for problems with >= 256 rows: 1 = CTA-pair (cta_group::2) kernel, 0 = single-CTA
 // kernel, -1 = the process default (pair unless WS_GEMM_PAIR=0 is in the environment).
 void ws_gemm_set_pair_mode(int mode);

@@ -15,7 +15,12 @@ What is new relative to the reference (whose CLIs prefill token by token at batc
 * `step` handles a whole batch in lock-step; on CUDA the step for a fixed batch size is captured
   once in a CUDA graph and replayed per token (the in-chunk position is a device scalar, the
   attention over the chunk cache is masked instead of sliced, so one graph serves all positions);
-* the memory update at a chunk boundary runs outside the graph, every 128 tokens.
+* the memory update at a chunk boundary runs outside the graph, every 128 tokens;
+* on CUDA with the kernel library (BF16, head_dim 64, chunk 128, batch <= 64) the step is seven
+  kernels per layer: weight-streaming tcgen05 GEMMs with swapped operand roles
+  (`decode_gemm_kernel`), a fused residual + depth-modulation + RMSNorm kernel and one attention
+  kernel per (sequence, head) (ops/csrc/decode.cu); the PyTorch formulation below is the
+  reference for it and the fallback elsewhere.
 """
 from __future__ import annotations
 
@@ -39,7 +44,8 @@ class DepthState:
 
 
 class DecodeEngine:
-    def __init__(self, model, dtype: torch.dtype = torch.bfloat16, use_cuda_graph: bool | None = None):
+    def __init__(self, model, dtype: torch.dtype = torch.bfloat16, use_cuda_graph: bool | None = None,
+                 use_kernels: bool = True):
         if model.training:
             raise ValueError("Decode requires model.eval()")
         self.model = model
@@ -49,6 +55,8 @@ class DecodeEngine:
         self.chunk = self.cfg.chunk_size
         self.h, self.hd = self.cfg.n_heads, self.cfg.head_dim
         self.use_graph = (self.device.type == "cuda") if use_cuda_graph is None else use_cuda_graph
+        self.use_kernels = use_kernels
+        self._kbufs = None
         self.weights = []
         with torch.no_grad():
             for depth in range(self.cfg.logical_depth):
@@ -87,6 +95,56 @@ class DecodeEngine:
         self.token_buf = torch.zeros(batch, dtype=torch.long, device=self.device)
         self.logits_buf = None
         self._graph = None
+        self._kbufs = self._kernel_buffers(batch) if self._kernels_usable(batch) else None
+
+    # ------------------------------------------------------------------ kernel path
+    def _kernels_usable(self, batch: int) -> bool:
+        if self.device.type != "cuda" or self.dtype != torch.bfloat16 or self.hd != 64 or self.chunk != 128:
+            return False
+        if batch > 64 or self.cfg.d_model % 8 or self.cfg.ffn_hidden % 64 or not self.use_kernels:
+            return False
+        from ..ops import _ext
+        return _ext.available()
+
+    def _kernel_buffers(self, batch: int) -> dict:
+        ops = torch.ops.ws_b200
+        d, ffn, v = self.cfg.d_model, self.cfg.ffn_hidden, self.cfg.vocab_size
+        dev = self.device
+        from ..ops import attention, gemm
+        return dict(
+            x=torch.zeros(batch, d, device=dev), n=torch.zeros(batch, d, device=dev, dtype=torch.bfloat16),
+            qkvgu=torch.zeros(batch, 5 * d, device=dev, dtype=torch.bfloat16),
+            y=torch.zeros(batch, d, device=dev, dtype=torch.bfloat16),
+            act=torch.zeros(batch, ffn, device=dev, dtype=torch.bfloat16),
+            p_out=torch.zeros(ops.decode_gemm_splits(d, d), batch, d, device=dev),
+            p_down=torch.zeros(ops.decode_gemm_splits(d, ffn), batch, d, device=dev),
+            logits=torch.zeros(batch, v, device=dev), rope=attention.rope_table(dev), flag=gemm.error_flag(dev))
+
+    def _step_kernels(self, token: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
+        ops = torch.ops.ws_b200
+        k = self._kbufs
+        d, ffn, eps = self.cfg.d_model, self.cfg.ffn_hidden, self.cfg.rms_eps
+        first = self.weights[0]
+        ops.decode_reduce_norm(k["x"], None, token, self.embed, first["scale"], first["bias"], first["n1"], eps, k["n"])
+        for index, (w, st) in enumerate(zip(self.weights, self.states)):
+            ops.decode_gemm(w["w_in"], k["n"], 5 * d, 0, k["qkvgu"], k["flag"])
+            ops.decode_attn(k["qkvgu"], st.k, st.v, st.u, st.mixed, k["rope"], pos, self.h, k["y"])
+            ops.decode_gemm(w["w_out"], k["y"], d, 1, k["p_out"], k["flag"])
+            ops.decode_reduce_norm(k["x"], k["p_out"], None, None, None, None, w["n2"], eps, k["n"])
+            ops.decode_gemm(w["w_ug"], k["n"], ffn, 2, k["act"], k["flag"])
+            ops.decode_gemm(w["w_down"], k["act"], d, 1, k["p_down"], k["flag"])
+            if index + 1 < len(self.weights):
+                nxt = self.weights[index + 1]
+                ops.decode_reduce_norm(k["x"], k["p_down"], None, None, nxt["scale"], nxt["bias"], nxt["n1"], eps, k["n"])
+            else:
+                ops.decode_reduce_norm(k["x"], k["p_down"], None, None, None, None, self.final_norm, eps, k["n"])
+        ops.decode_gemm(self.head, k["n"], self.cfg.vocab_size, 3, k["logits"], k["flag"])
+        return k["logits"]
+
+    def _step_fn(self, token: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
+        if self._kbufs is not None:
+            return self._step_kernels(token, pos)
+        return self._step_math(token, pos)
 
     def _norm(self, x, w):
         x32 = x.float()
@@ -131,7 +189,7 @@ class DecodeEngine:
     @torch.no_grad()
     def step(self, token: torch.Tensor) -> torch.Tensor:
         """``token [B]`` (or ``[B,1]``) -> logits ``[B, V]`` FP32."""
-        token = token.reshape(-1).to(self.device)
+        token = token.reshape(-1).to(self.device).contiguous()
         if self.states is None or token.shape[0] != self.batch:
             self.new_state(token.shape[0])
         self.pos_dev.fill_(self.pos)
@@ -142,7 +200,7 @@ class DecodeEngine:
             self._graph.replay()
             logits = self.logits_buf
         else:
-            logits = self._step_math(token, self.pos_dev)
+            logits = self._step_fn(token, self.pos_dev)
         self.pos += 1
         if self.pos == self.chunk:
             self._end_of_chunk()
@@ -157,11 +215,11 @@ class DecodeEngine:
         stream.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(stream):
             for _ in range(2):
-                self._step_math(self.token_buf, self.pos_dev)
+                self._step_fn(self.token_buf, self.pos_dev)
         torch.cuda.current_stream(self.device).wait_stream(stream)
         self._graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self._graph):
-            self.logits_buf = self._step_math(self.token_buf, self.pos_dev)
+            self.logits_buf = self._step_fn(self.token_buf, self.pos_dev)
 
     # ------------------------------------------------------------------ prefill
     @torch.no_grad()
