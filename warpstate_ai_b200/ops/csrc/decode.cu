@@ -279,7 +279,7 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ qkvgu, __nv_bfloat16* __res
                    const __nv_bfloat16* __restrict__ mixed, const float2* __restrict__ rope,
                    const long long* __restrict__ pos_ptr, int H, int d, __nv_bfloat16* __restrict__ y) {
   constexpr int HD = 64, C = 128;
-  __shared__ float sq[HD], sk[HD], sp[C], sacc[2][HD], sred[4];
+  __shared__ float sq[HD], sk[HD], sp[C], sl[16][HD + 1], sm[16][HD + 1], sred[4];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int h = blockIdx.x % H, b = blockIdx.x / H;
   int pos = static_cast<int>(*pos_ptr);
@@ -345,25 +345,59 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ qkvgu, __nv_bfloat16* __res
   sp[tid] = e;
   __syncthreads();
   const float inv = 1.f / (sred[0] + sred[1] + sred[2] + sred[3]);
-  // local = sum_c p[c] V[c]: two halves of the key range in parallel, 64 columns each
+  // local = sum_c p[c] V[c] and memory = q . M in one pass of wide loads: thread (rg, jg) owns
+  // columns 8*jg .. 8*jg+7 and the rows rg, rg+16, ... of V (keys) and of M; the 16 row groups
+  // are then summed through shared memory.
   {
-    const int col = tid & 63, half = tid >> 6;
-    const int c_lo = half * 64, c_hi = min(pos + 1, c_lo + 64);
-    float acc = 0.f;
-    for (int c = c_lo; c < c_hi; ++c) {
-      const float v = (c == pos) ? __bfloat162float(row[2 * d + col]) : __bfloat162float(vc[cache + static_cast<size_t>(c) * HD + col]);
-      acc += sp[c] * v;
+    const int jg = tid & 7, rg = tid >> 3;
+    float accl[8], accm[8];
+#pragma unroll
+    for (int t = 0; t < 8; ++t) { accl[t] = 0.f; accm[t] = 0.f; }
+#pragma unroll
+    for (int it = 0; it < C / 16; ++it) {
+      const int c = rg + it * 16;
+      if (c <= pos) {
+        const uint4 v = (c == pos) ? *reinterpret_cast<const uint4*>(row + 2 * d + jg * 8)
+                                   : *reinterpret_cast<const uint4*>(vc + cache + static_cast<size_t>(c) * HD + jg * 8);
+        const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&v);
+        const float pc = sp[c];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float2 f = __bfloat1622float2(pb[t]);
+          accl[2 * t] += pc * f.x;
+          accl[2 * t + 1] += pc * f.y;
+        }
+      }
     }
-    sacc[half][col] = acc;
+    const __nv_bfloat16* mbase = mixed + (static_cast<size_t>(b) * H + h) * HD * HD;
+#pragma unroll
+    for (int it = 0; it < HD / 16; ++it) {
+      const int i = rg + it * 16;
+      const uint4 v = *reinterpret_cast<const uint4*>(mbase + i * HD + jg * 8);
+      const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&v);
+      const float qi = sq[i];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float2 f = __bfloat1622float2(pb[t]);
+        accm[2 * t] += qi * f.x;
+        accm[2 * t + 1] += qi * f.y;
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+      sl[rg][jg * 8 + t] = accl[t];
+      sm[rg][jg * 8 + t] = accm[t];
+    }
   }
   __syncthreads();
   if (tid < HD) {
-    const float local = (sacc[0][tid] + sacc[1][tid]) * inv;
-    // memory read: q . M  (M[i][j], j = this thread's column)
-    const __nv_bfloat16* mrow = mixed + (static_cast<size_t>(b) * H + h) * HD * HD + tid;
-    float mem = 0.f;
-#pragma unroll 8
-    for (int i = 0; i < HD; ++i) mem += sq[i] * __bfloat162float(mrow[i * HD]);
+    float local = 0.f, mem = 0.f;
+#pragma unroll
+    for (int r = 0; r < 16; ++r) {
+      local += sl[r][tid];
+      mem += sm[r][tid];
+    }
+    local *= inv;
     mem *= 0.125f;
     const float g = sigmoid_fast(__bfloat162float(row[3 * d + tid]));
     y[static_cast<size_t>(b) * d + h * HD + tid] = __float2bfloat16(g * local + (1.f - g) * mem);

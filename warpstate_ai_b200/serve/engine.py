@@ -81,6 +81,14 @@ class DecodeEngine:
 
     # ------------------------------------------------------------------ state
     def new_state(self, batch: int) -> None:
+        if self.states is not None and batch == self.batch:
+            # same shapes: clear in place so that the captured graph and its buffers stay valid
+            for st in self.states:
+                for t in (st.fast, st.slow, st.mixed, st.k, st.v, st.u):
+                    t.zero_()
+            self.pos = 0
+            self.pos_dev.zero_()
+            return
         z = lambda *shape, dtype: torch.zeros(shape, device=self.device, dtype=dtype)
         self.states = [DepthState(z(batch, self.h, self.hd, self.hd, dtype=torch.float32),
                                   z(batch, self.h, self.hd, self.hd, dtype=torch.float32),
