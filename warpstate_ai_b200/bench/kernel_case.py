@@ -22,6 +22,8 @@ def gemm_case(kind: str) -> None:
     w = (torch.randn(n, k, device="cuda") * 0.02).bfloat16()
     dy = torch.randn(m, n, device="cuda").bfloat16()
     grad = torch.zeros(n, k, device="cuda")
+    w_down = (torch.randn(k, n // 2, device="cuda") * 0.02).bfloat16()
+    packed = torch.randn(m, n, device="cuda").bfloat16()
     for _ in range(3):
         if kind == "gemm_fwd":
             G.linear(x, w)
@@ -31,6 +33,9 @@ def gemm_case(kind: str) -> None:
             G.grad_weight_accumulate(dy, x, grad)
         elif kind == "gemm_swiglu":
             G.linear_swiglu(x, w)
+        elif kind == "gemm_swiglu_bwd":
+            # dAct = dy[m, 2048] @ w_down[2048, 5120]; epilogue reads packed (up|gate) [m, 10240]
+            G.grad_input_swiglu(dy[:, :k].contiguous() if False else x, w_down, packed)
     torch.cuda.synchronize()
 
 

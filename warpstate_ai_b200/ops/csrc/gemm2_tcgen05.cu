@@ -41,7 +41,6 @@ constexpr int STAGES = 6;
 constexpr int A_BYTES = BM * BK * 2;        // 16 KiB
 constexpr int B_BYTES = (BN / 2) * BK * 2;  // 16 KiB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int THREADS = 320;
 constexpr int TMEM_COLS = 512;
 constexpr int GROUP_M = 8;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
@@ -84,10 +83,16 @@ __device__ __forceinline__ PairTile resolve_tile(const PairGroup& g, int tile, i
   return t;
 }
 
+template <int EPI>
+constexpr int pair_threads() {
+  return 64 + 128 * epilogue_groups<EPI>();  // TMA warp, MMA warp, GROUPS x 4 epilogue warps
+}
+
 template <bool A_MN, bool B_MN, int EPI>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair::THREADS, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads<EPI>(), 1)
 gemm2_kernel(const __grid_constant__ PairGroup g) {
   using namespace pair;
+  constexpr int GROUPS = epilogue_groups<EPI>();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -113,7 +118,7 @@ gemm2_kernel(const __grid_constant__ PairGroup g) {
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull[b], 1);
-      mbar_init(&tempty[b], 16);  // 8 epilogue warps x 2 CTAs
+      mbar_init(&tempty[b], 8 * GROUPS);  // epilogue warps of both CTAs
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -239,7 +244,7 @@ gemm2_kernel(const __grid_constant__ PairGroup g) {
       const bool row_ok = row < p.m;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
       const float rs = (p.row_scale != nullptr && row_ok) ? p.row_scale[row] : 1.0f;
-      gemm_epilogue<EPI>(p, taddr, row, row_ok, rs, nb, egroup);
+      gemm_epilogue<EPI, GROUPS>(p, taddr, row, row_ok, rs, nb, egroup);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster_relaxed(mapa_shared(smem_u32(&tempty[buf]), 0));
@@ -266,7 +271,7 @@ static int launch_pair(const PairGroup& g, int pairs, cudaStream_t stream) {
       return -20;
     configured = true;
   }
-  kern<<<2 * pairs, pair::THREADS, pair::SMEM_BYTES, stream>>>(g);
+  kern<<<2 * pairs, pair_threads<EPI>(), pair::SMEM_BYTES, stream>>>(g);
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }

@@ -30,10 +30,19 @@ __device__ __forceinline__ float sigmoidf_(float x) { return sigmoid_fast(x); }
 
 // taddr: TMEM address of (this warp's first lane, first column of the accumulator buffer).
 // row: global output row of this thread; nb: N-tile index; egroup: which half of the columns.
+// GROUPS: how many warpgroups of four warps share a tile's columns (egroup in [0, GROUPS)).
+// Two everywhere: four groups on the SwiGLU epilogues measured 5-10 % slower (their
+// row-per-thread global accesses are bound by L1 wavefronts, which more warps do not add).
 template <int EPI>
+constexpr int epilogue_groups() {
+  return 2;
+}
+
+template <int EPI, int GROUPS = 2>
 __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint32_t taddr, int row, bool row_ok, float rs,
                                               int nb, int egroup) {
   constexpr int BN = EPI_BN;
+  static_assert(GROUPS == 2 || EPI == WS_EPI_SWIGLU || EPI == WS_EPI_SWIGLU_BWD, "only the SwiGLU epilogues take 4 groups");
   if constexpr (EPI == WS_EPI_BF16) {
     __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(row) * p.ldo;
     const int n0 = nb * BN;
@@ -128,8 +137,9 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint32_t tadd
     __nv_bfloat16* packed = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(row) * p.ldo;
     __nv_bfloat16* act = reinterpret_cast<__nv_bfloat16*>(p.out2) + static_cast<size_t>(row) * p.ldo2;
     const int n0 = nb * 128;
+    constexpr int GW = 128 / GROUPS;
 #pragma unroll 1
-    for (int c = egroup * 64; c < egroup * 64 + 64; c += 16) {
+    for (int c = egroup * GW; c < egroup * GW + GW; c += 16) {
       if (n0 + c >= p.h) break;
       uint32_t ru[16], rg[16];
       tmem_ld_32x32b_x16(taddr + c, ru);
@@ -164,24 +174,41 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint32_t tadd
     }
   } else if constexpr (EPI == WS_EPI_SWIGLU_BWD) {
     // acc = dAct; aux = packed (up|gate) of the forward; out = packed (dUp|dGate).
+    // The (up, gate) values of the next 16 columns are requested before the current 16 are
+    // processed, so their global-load latency overlaps the TMEM read and the arithmetic.
     __nv_bfloat16* dpk = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(row) * p.ldo;
     const __nv_bfloat16* pk =
         reinterpret_cast<const __nv_bfloat16*>(p.aux) + static_cast<size_t>(row) * p.ldaux;
     const int n0 = nb * BN;
+    constexpr int GWB = BN / GROUPS;
+    const int c_end = egroup * GWB + GWB;
+    uint4 cu[2], cg[2], nu[2], ng[2];
+    auto load_aux = [&](int c, uint4(&u)[2], uint4(&g)[2]) {
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        if (row_ok && n0 + c + q * 8 < p.n) {
+          u[q] = *reinterpret_cast<const uint4*>(pk + n0 + c + q * 8);
+          g[q] = *reinterpret_cast<const uint4*>(pk + p.n + n0 + c + q * 8);
+        } else {
+          u[q] = make_uint4(0u, 0u, 0u, 0u);
+          g[q] = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+    };
+    load_aux(egroup * GWB, cu, cg);
 #pragma unroll 1
-    for (int c = egroup * 128; c < egroup * 128 + 128; c += 16) {
+    for (int c = egroup * GWB; c < c_end; c += 16) {
       if (n0 + c >= p.n) break;
       uint32_t r[16];
       tmem_ld_32x32b_x16(taddr + c, r);
+      if (c + 16 < c_end) load_aux(c + 16, nu, ng);
       tmem_ld_wait();
       if (row_ok) {
 #pragma unroll
         for (int j = 0; j < 16; j += 8) {
           if (n0 + c + j < p.n) {
-            const uint4 qu = *reinterpret_cast<const uint4*>(pk + n0 + c + j);
-            const uint4 qg = *reinterpret_cast<const uint4*>(pk + p.n + n0 + c + j);
-            const __nv_bfloat162* bu = reinterpret_cast<const __nv_bfloat162*>(&qu);
-            const __nv_bfloat162* bg = reinterpret_cast<const __nv_bfloat162*>(&qg);
+            const __nv_bfloat162* bu = reinterpret_cast<const __nv_bfloat162*>(&cu[j >> 3]);
+            const __nv_bfloat162* bg = reinterpret_cast<const __nv_bfloat162*>(&cg[j >> 3]);
             uint4 vu, vg;
             uint32_t* wu = reinterpret_cast<uint32_t*>(&vu);
             uint32_t* wg = reinterpret_cast<uint32_t*>(&vg);
@@ -200,6 +227,11 @@ __device__ __forceinline__ void gemm_epilogue(const GemmParams& p, uint32_t tadd
             *reinterpret_cast<uint4*>(dpk + p.n + n0 + c + j) = vg;
           }
         }
+      }
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        cu[q] = nu[q];
+        cg[q] = ng[q];
       }
     }
   } else if constexpr (EPI == WS_EPI_CE_FWD) {
