@@ -25,6 +25,7 @@
 #include "ws_tma_host.h"
 #include "gemm_epilogue.cuh"
 
+#include <cuda_bf16.h>
 #include <cstdlib>
 #include <cstring>
 
@@ -37,13 +38,13 @@ constexpr int BM = 128;        // rows per CTA (256 per pair)
 constexpr int BN = 256;        // accumulator columns (128 B rows staged per CTA)
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
-constexpr int STAGES = 6;
+constexpr int STAGES = 6;          // staged-epilogue instantiations use one fewer (see pair_stages)
+constexpr int ESTAGE_BYTES = 8 * 8192;  // staged epilogue: 8 warps x 2 buffers x 2 tiles of 32 x 32 BF16
 constexpr int A_BYTES = BM * BK * 2;        // 16 KiB
 constexpr int B_BYTES = (BN / 2) * BK * 2;  // 16 KiB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int TMEM_COLS = 512;
 constexpr int GROUP_M = 8;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 }  // namespace pair
 
 __device__ __forceinline__ void pair_tile_coords(int tile, int num_m, int num_n, int& mb, int& nb) {
@@ -64,9 +65,32 @@ struct alignas(64) PairGroup {
   CUtensorMap a[MAX_GROUP];
   CUtensorMap b[MAX_GROUP];
   GemmParams p[MAX_GROUP];
+  CUtensorMap epi[4];  // staged epilogue of problem 0: aux up, aux gate, out up, out gate (32 x 32 boxes)
   int tile_start[MAX_GROUP + 1];
   int count;
 };
+
+// The SwiGLU-backward epilogue reads and writes 4 bytes of global memory per accumulator element.
+// Done with one thread per row, that is 32 L1 wavefronts per warp instruction and the epilogue
+// takes twice as long as the main loop; staged through shared memory with TMA loads and stores,
+// global memory never goes through L1 and each thread touches only swizzled shared memory.
+template <int EPI>
+constexpr bool staged_epilogue() {
+  return EPI == WS_EPI_SWIGLU_BWD;
+}
+template <int EPI>
+constexpr int pair_stages() {
+  return staged_epilogue<EPI>() ? pair::STAGES - 1 : pair::STAGES;
+}
+template <int EPI>
+constexpr int pair_smem() {
+  return pair_stages<EPI>() * pair::STAGE_BYTES + (staged_epilogue<EPI>() ? pair::ESTAGE_BYTES : 0) + 1024 + 512;
+}
+
+// 16-byte chunk j of row r in a 32-row x 64-byte tile written by TMA with the 64-byte swizzle
+__device__ __forceinline__ uint8_t* tile_chunk64(uint8_t* tile, int r, int j) {
+  return tile + r * 64 + ((j ^ ((r >> 1) & 3)) << 4);
+}
 
 struct PairTile {
   int prob, mb, nb, num_k;
@@ -93,17 +117,21 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads<EPI>(),
 gemm2_kernel(const __grid_constant__ PairGroup g) {
   using namespace pair;
   constexpr int GROUPS = epilogue_groups<EPI>();
+  constexpr int STAGES = pair_stages<EPI>();
+  constexpr bool STAGED = staged_epilogue<EPI>();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES * A_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint8_t* eStage = smem + STAGES * STAGE_BYTES;  // staged epilogue buffers (STAGED only)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(eStage + (STAGED ? ESTAGE_BYTES : 0));
   uint64_t* full = bars;                    // used in the leader CTA
   uint64_t* empty = bars + STAGES;          // per CTA
   uint64_t* tfull = bars + 2 * STAGES;      // per CTA
   uint64_t* tempty = bars + 2 * STAGES + 2; // used in the leader CTA
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  uint64_t* ebar = bars + 2 * STAGES + 4;   // 16: per epilogue warp, per buffer (STAGED only)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4 + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -119,6 +147,10 @@ gemm2_kernel(const __grid_constant__ PairGroup g) {
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull[b], 1);
       mbar_init(&tempty[b], 8 * GROUPS);  // epilogue warps of both CTAs
+    }
+    if (STAGED) {
+      for (int i = 0; i < 16; ++i) mbar_init(&ebar[i], 1);
+      for (int i = 0; i < 4; ++i) tma_prefetch_desc(&g.epi[i]);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -232,22 +264,115 @@ gemm2_kernel(const __grid_constant__ PairGroup g) {
     const int quarter = warp & 3;
     const int egroup = (warp - 2) >> 2;
     int tcount = 0;
-    for (int tile = pair_id; tile < tiles; tile += num_pairs, ++tcount) {
-      const PairTile t = resolve_tile(g, tile, n_tile);
-      const GemmParams& p = g.p[t.prob];
-      const int nb = t.nb;
-      const int buf = tcount & 1;
-      const uint32_t tph = (tcount >> 1) & 1;
-      if (!mbar_wait(&tfull[buf], tph, abort_flag)) break;
-      tc_fence_after_sync();
-      const int row = t.mb * 2 * BM + rank * BM + quarter * 32 + lane;
-      const bool row_ok = row < p.m;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
-      const float rs = (p.row_scale != nullptr && row_ok) ? p.row_scale[row] : 1.0f;
-      gemm_epilogue<EPI, GROUPS>(p, taddr, row, row_ok, rs, nb, egroup);
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster_relaxed(mapa_shared(smem_u32(&tempty[buf]), 0));
+    if constexpr (STAGED) {
+      // SwiGLU backward through shared memory.  Per warp: 32 rows; per step: 32 columns; two
+      // buffers, each holding the (up, gate) tiles that become (dUp, dGate) in place.
+      uint8_t* ebuf = eStage + (warp - 2) * 8192;
+      uint64_t* mybar = ebar + (warp - 2) * 2;
+      constexpr int STEPS = (BN / GROUPS) / 32;
+      const GemmParams& p = g.p[0];
+      auto coords = [&](int tile, int step, int& x, int& y) {
+        const PairTile t = resolve_tile(g, tile, n_tile);
+        x = t.nb * BN + egroup * (BN / GROUPS) + step * 32;
+        y = t.mb * 2 * BM + rank * BM + quarter * 32;
+      };
+      auto issue_load = [&](int tile, int step, int buf) {
+        if (lane == 0) {
+          int x, y;
+          coords(tile, step, x, y);
+          mbar_expect_tx(&mybar[buf], 4096);
+          tma_load_2d(ebuf + buf * 4096, &g.epi[0], &mybar[buf], x, y);
+          tma_load_2d(ebuf + buf * 4096 + 2048, &g.epi[1], &mybar[buf], x, y);
+        }
+      };
+      int q = 0;  // steps done by this warp (buffer = q & 1, barrier phase = (q >> 1) & 1)
+      if (pair_id < tiles) issue_load(pair_id, 0, 0);
+      bool ok = true;
+      for (int tile = pair_id; tile < tiles && ok; tile += num_pairs, ++tcount) {
+        const int buf_t = tcount & 1;
+        const uint32_t tph = (tcount >> 1) & 1;
+        if (!mbar_wait(&tfull[buf_t], tph, abort_flag)) break;
+        tc_fence_after_sync();
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf_t * BN + egroup * (BN / GROUPS);
+#pragma unroll 1
+        for (int step = 0; step < STEPS; ++step, ++q) {
+          const int buf = q & 1;
+          // the store issued from the other buffer one step ago must have read it before it is refilled
+          if (lane == 0) tma_store_wait_read0();
+          if (step + 1 < STEPS) {
+            issue_load(tile, step + 1, buf ^ 1);
+          } else if (tile + num_pairs < tiles) {
+            issue_load(tile + num_pairs, 0, buf ^ 1);
+          }
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + step * 32, r);
+          if (!mbar_wait(&mybar[buf], (q >> 1) & 1, abort_flag)) {
+            ok = false;
+            tmem_ld_wait();
+            break;
+          }
+          tmem_ld_wait();
+          uint8_t* tu = ebuf + buf * 4096;
+          uint8_t* tg = tu + 2048;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4* pu = reinterpret_cast<uint4*>(tile_chunk64(tu, lane, j));
+            uint4* pg = reinterpret_cast<uint4*>(tile_chunk64(tg, lane, j));
+            const uint4 qu = *pu, qg = *pg;
+            const __nv_bfloat162* bu = reinterpret_cast<const __nv_bfloat162*>(&qu);
+            const __nv_bfloat162* bg = reinterpret_cast<const __nv_bfloat162*>(&qg);
+            uint4 vu, vg;
+            uint32_t* wu = reinterpret_cast<uint32_t*>(&vu);
+            uint32_t* wg = reinterpret_cast<uint32_t*>(&vg);
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              const float2 u = __bfloat1622float2(bu[t]);
+              const float2 gg = __bfloat1622float2(bg[t]);
+              const float d0 = bf16_round(__uint_as_float(r[j * 8 + 2 * t]));
+              const float d1 = bf16_round(__uint_as_float(r[j * 8 + 2 * t + 1]));
+              const float s0 = sigmoidf_(gg.x), s1 = sigmoidf_(gg.y);
+              wu[t] = pack_bf16x2(d0 * gg.x * s0, d1 * gg.y * s1);
+              wg[t] = pack_bf16x2(d0 * u.x * s0 * (1.0f + gg.x * (1.0f - s0)),
+                                  d1 * u.y * s1 * (1.0f + gg.y * (1.0f - s1)));
+            }
+            *pu = vu;
+            *pg = vg;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            int x, y;
+            coords(tile, step, x, y);
+            if (x < p.n && y < p.m) {  // a box that lies entirely outside is skipped
+              tma_store_2d(&g.epi[2], tu, x, y);
+              tma_store_2d(&g.epi[3], tg, x, y);
+            }
+            tma_store_commit();
+          }
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster_relaxed(mapa_shared(smem_u32(&tempty[buf_t]), 0));
+      }
+      if (lane == 0) tma_store_wait_all();
+    } else {
+      for (int tile = pair_id; tile < tiles; tile += num_pairs, ++tcount) {
+        const PairTile t = resolve_tile(g, tile, n_tile);
+        const GemmParams& p = g.p[t.prob];
+        const int nb = t.nb;
+        const int buf = tcount & 1;
+        const uint32_t tph = (tcount >> 1) & 1;
+        if (!mbar_wait(&tfull[buf], tph, abort_flag)) break;
+        tc_fence_after_sync();
+        const int row = t.mb * 2 * BM + rank * BM + quarter * 32 + lane;
+        const bool row_ok = row < p.m;
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+        const float rs = (p.row_scale != nullptr && row_ok) ? p.row_scale[row] : 1.0f;
+        gemm_epilogue<EPI, GROUPS>(p, taddr, row, row_ok, rs, nb, egroup);
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster_relaxed(mapa_shared(smem_u32(&tempty[buf]), 0));
+      }
     }
   }
 
@@ -267,11 +392,11 @@ static int launch_pair(const PairGroup& g, int pairs, cudaStream_t stream) {
   static bool configured = false;
   auto kern = gemm2_kernel<A_MN, B_MN, EPI>;
   if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pair::SMEM_BYTES) != cudaSuccess)
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pair_smem<EPI>()) != cudaSuccess)
       return -20;
     configured = true;
   }
-  kern<<<2 * pairs, pair_threads<EPI>(), pair::SMEM_BYTES, stream>>>(g);
+  kern<<<2 * pairs, pair_threads<EPI>(), pair_smem<EPI>(), stream>>>(g);
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
@@ -331,6 +456,18 @@ extern "C" int ws_gemm_pair_group(const WsGemm* items, int count, int sms, cudaS
     total += tiles;
   }
   for (int i = count; i <= MAX_GROUP; ++i) grp.tile_start[i] = total;
+  if (items[0].epilogue == WS_EPI_SWIGLU_BWD) {
+    if (count != 1) return -9;
+    const WsGemm* g0 = &items[0];
+    const __nv_bfloat16* aux = static_cast<const __nv_bfloat16*>(g0->aux);
+    __nv_bfloat16* out = static_cast<__nv_bfloat16*>(g0->out);
+    const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_64B;
+    int rc = make_map_bf16_swz(&grp.epi[0], aux, g0->n, g0->m, g0->ldaux, 32, 32, sw);
+    if (!rc) rc = make_map_bf16_swz(&grp.epi[1], aux + g0->n, g0->n, g0->m, g0->ldaux, 32, 32, sw);
+    if (!rc) rc = make_map_bf16_swz(&grp.epi[2], out, g0->n, g0->m, g0->ldo, 32, 32, sw);
+    if (!rc) rc = make_map_bf16_swz(&grp.epi[3], out + g0->n, g0->n, g0->m, g0->ldo, 32, 32, sw);
+    if (rc) return rc;
+  }
   int pairs = sms / 2;
   if (pairs < 1) pairs = 1;
   if (total < pairs) pairs = total;

@@ -29,8 +29,17 @@ inline EncodeTiledFn get_encode_fn() {
 
 // 2-D BF16 tensor map with 128-byte swizzle: `inner` contiguous elements per row, `outer` rows,
 // row pitch `ld` elements, box = box_inner x box_outer (box_inner * 2 bytes <= 128).
+inline int make_map_bf16_swz(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
+                             uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle);
+
 inline int make_map_bf16(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer,
                          uint64_t ld, uint32_t box_inner, uint32_t box_outer) {
+  return make_map_bf16_swz(map, base, inner, outer, ld, box_inner, box_outer, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+// The same with a chosen swizzle (box_inner * 2 bytes must not exceed the swizzle span).
+inline int make_map_bf16_swz(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
+                             uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swizzle) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return -10;
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (ld * 2) % 16 != 0) return -11;
@@ -39,7 +48,7 @@ inline int make_map_bf16(CUtensorMap* map, const void* base, uint64_t inner, uin
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
-                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -12;
 }
