@@ -65,7 +65,8 @@ struct alignas(64) PairGroup {
   CUtensorMap a[MAX_GROUP];
   CUtensorMap b[MAX_GROUP];
   GemmParams p[MAX_GROUP];
-  CUtensorMap epi[4];  // staged epilogue of problem 0: aux up, aux gate, out up, out gate (32 x 32 boxes)
+  CUtensorMap epi[4];  // staged epilogue of problem 0, 32 x 32 boxes.  SwiGLU backward: aux up, aux gate,
+                       // out up, out gate; SwiGLU forward: packed up, packed gate, activation
   int tile_start[MAX_GROUP + 1];
   int count;
 };
@@ -76,7 +77,7 @@ struct alignas(64) PairGroup {
 // global memory never goes through L1 and each thread touches only swizzled shared memory.
 template <int EPI>
 constexpr bool staged_epilogue() {
-  return EPI == WS_EPI_SWIGLU_BWD;
+  return EPI == WS_EPI_SWIGLU_BWD || EPI == WS_EPI_SWIGLU;
 }
 template <int EPI>
 constexpr int pair_stages() {
@@ -150,7 +151,7 @@ gemm2_kernel(const __grid_constant__ PairGroup g) {
     }
     if (STAGED) {
       for (int i = 0; i < 16; ++i) mbar_init(&ebar[i], 1);
-      for (int i = 0; i < 4; ++i) tma_prefetch_desc(&g.epi[i]);
+      for (int i = 0; i < (EPI == WS_EPI_SWIGLU ? 3 : 4); ++i) tma_prefetch_desc(&g.epi[i]);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -264,7 +265,66 @@ gemm2_kernel(const __grid_constant__ PairGroup g) {
     const int quarter = warp & 3;
     const int egroup = (warp - 2) >> 2;
     int tcount = 0;
-    if constexpr (STAGED) {
+    if constexpr (EPI == WS_EPI_SWIGLU) {
+      // SwiGLU forward through shared memory: per warp 32 rows, per step 32 features; the three
+      // output tiles (up, gate, activation) are written to swizzled shared memory and leave by TMA.
+      uint8_t* ebuf = eStage + (warp - 2) * 8192;  // 3 tiles of 2 KiB used
+      constexpr int STEPS = (128 / GROUPS) / 32;
+      const GemmParams& p = g.p[0];
+      for (int tile = pair_id; tile < tiles; tile += num_pairs, ++tcount) {
+        const PairTile t = resolve_tile(g, tile, n_tile);
+        const int buf_t = tcount & 1;
+        const uint32_t tph = (tcount >> 1) & 1;
+        if (!mbar_wait(&tfull[buf_t], tph, abort_flag)) break;
+        tc_fence_after_sync();
+        const int y = t.mb * 2 * BM + rank * BM + quarter * 32;
+        const int row = y + lane;
+        const float rs = (p.row_scale != nullptr && row < p.m) ? p.row_scale[row] : 1.0f;
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf_t * BN;
+#pragma unroll 1
+        for (int step = 0; step < STEPS; ++step) {
+          const int c = egroup * (128 / GROUPS) + step * 32;
+          const int x = t.nb * 128 + c;
+          uint32_t ru[32], rg[32];
+          tmem_ld_32x32b_x32(taddr + c, ru);
+          tmem_ld_32x32b_x32(taddr + 128 + c, rg);
+          tmem_ld_wait();
+          uint32_t wu[16], wg[16], wa[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float u0 = bf16_round(__uint_as_float(ru[2 * i]) * rs), u1 = bf16_round(__uint_as_float(ru[2 * i + 1]) * rs);
+            const float g0 = bf16_round(__uint_as_float(rg[2 * i]) * rs), g1 = bf16_round(__uint_as_float(rg[2 * i + 1]) * rs);
+            wu[i] = pack_bf16x2(u0, u1);
+            wg[i] = pack_bf16x2(g0, g1);
+            wa[i] = pack_bf16x2(g0 * sigmoidf_(g0) * u0, g1 * sigmoidf_(g1) * u1);
+          }
+          if (lane == 0) tma_store_wait_read0();  // the previous step's stores have read the tiles
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            *reinterpret_cast<uint4*>(tile_chunk64(ebuf, lane, j)) = make_uint4(wu[4 * j], wu[4 * j + 1], wu[4 * j + 2], wu[4 * j + 3]);
+            *reinterpret_cast<uint4*>(tile_chunk64(ebuf + 2048, lane, j)) = make_uint4(wg[4 * j], wg[4 * j + 1], wg[4 * j + 2], wg[4 * j + 3]);
+            *reinterpret_cast<uint4*>(tile_chunk64(ebuf + 4096, lane, j)) = make_uint4(wa[4 * j], wa[4 * j + 1], wa[4 * j + 2], wa[4 * j + 3]);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (x < p.h && y < p.m) {
+              if (p.out != nullptr) {
+                tma_store_2d(&g.epi[0], ebuf, x, y);
+                tma_store_2d(&g.epi[1], ebuf + 2048, x, y);
+              }
+              tma_store_2d(&g.epi[2], ebuf + 4096, x, y);
+            }
+            tma_store_commit();
+          }
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster_relaxed(mapa_shared(smem_u32(&tempty[buf_t]), 0));
+      }
+      if (lane == 0) tma_store_wait_all();
+    } else if constexpr (STAGED) {
       // SwiGLU backward through shared memory.  Per warp: 32 rows; per step: 32 columns; two
       // buffers, each holding the (up, gate) tiles that become (dUp, dGate) in place.
       uint8_t* ebuf = eStage + (warp - 2) * 8192;
@@ -456,6 +516,24 @@ extern "C" int ws_gemm_pair_group(const WsGemm* items, int count, int sms, cudaS
     total += tiles;
   }
   for (int i = count; i <= MAX_GROUP; ++i) grp.tile_start[i] = total;
+  if (items[0].epilogue == WS_EPI_SWIGLU) {
+    if (count != 1) return -9;
+    const WsGemm* g0 = &items[0];
+    __nv_bfloat16* packed = static_cast<__nv_bfloat16*>(g0->out);
+    __nv_bfloat16* act = static_cast<__nv_bfloat16*>(g0->out2);
+    const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_64B;
+    int rc = 0;
+    if (packed != nullptr) {
+      rc = make_map_bf16_swz(&grp.epi[0], packed, g0->n, g0->m, g0->ldo, 32, 32, sw);
+      if (!rc) rc = make_map_bf16_swz(&grp.epi[1], packed + g0->n, g0->n, g0->m, g0->ldo, 32, 32, sw);
+    }
+    if (!rc) rc = make_map_bf16_swz(&grp.epi[2], act, g0->n, g0->m, g0->ldo2, 32, 32, sw);
+    if (rc) return rc;
+    if (packed == nullptr) {
+      grp.epi[0] = grp.epi[2];  // never used for a store; keeps the descriptor prefetch valid
+      grp.epi[1] = grp.epi[2];
+    }
+  }
   if (items[0].epilogue == WS_EPI_SWIGLU_BWD) {
     if (count != 1) return -9;
     const WsGemm* g0 = &items[0];
