@@ -15,8 +15,16 @@ BACKWARD_READY = True
 MAX_CHUNKS = 64
 
 
-def rope_table(device: torch.device) -> torch.Tensor:
-    """(cos, sin) per in-chunk position and rotary pair: float32 [128, 32, 2]."""
+def rope_table(device: torch.device, pair_major: bool = False) -> torch.Tensor:
+    """(cos, sin) per in-chunk position and rotary pair: float32 [128, 32, 2], or with
+    ``pair_major`` [32, 128, 2] (what the chunk kernels read: one thread per position)."""
+    if pair_major:
+        key = (device.type, device.index, "pair-major")
+        table = _rope_cache.get(key)
+        if table is None:
+            table = rope_table(device).transpose(0, 1).contiguous()
+            _rope_cache[key] = table
+        return table
     key = (device.type, device.index)
     table = _rope_cache.get(key)
     if table is None:
@@ -46,7 +54,7 @@ def forward_only(qkvgu: torch.Tensor, core, batch: int, seq: int, want_final: bo
     """y [M,d] (and optionally the final fast/slow states) with the CUDA kernels."""
     _ext.require()
     ops = torch.ops.ws_b200
-    rope = rope_table(qkvgu.device)
+    rope = rope_table(qkvgu.device, pair_major=True)
     flag = error_flag(qkvgu.device)
     writes = ops.chunk_writes(qkvgu, rope, batch, seq, core.h, flag)
     fl = core.fast_decay_logit.detach().float().contiguous()
@@ -68,7 +76,7 @@ def backward(dy, qkvgu, saved, core, batch: int, seq: int):
         raise ValueError(f"the memory-scan backward kernel handles at most {MAX_CHUNKS} chunks per sequence")
     writes, states = saved
     fl, sl, ml = _logits(core)
-    dqkvgu, partials = torch.ops.ws_b200.attn_bwd(qkvgu, dy.contiguous(), states, writes, rope_table(qkvgu.device),
+    dqkvgu, partials = torch.ops.ws_b200.attn_bwd(qkvgu, dy.contiguous(), states, writes, rope_table(qkvgu.device, pair_major=True),
                                                   fl, sl, ml, batch, seq, core.h, error_flag(qkvgu.device))
     g = partials.view(batch, core.h, 16, 3).sum(dim=(0, 2))  # [H, 3] gradients w.r.t. the sigmoids
     df, ds, mix = torch.sigmoid(fl), torch.sigmoid(sl), torch.sigmoid(ml)

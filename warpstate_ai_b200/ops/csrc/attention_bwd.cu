@@ -25,7 +25,7 @@ extern "C" void ws_count_launch(void);
 // =============================================================================== dState
 constexpr int DS_SMEM = 2 * TILE_BYTES + 1024 + 128;
 
-__global__ void __launch_bounds__(128, 3)
+__global__ void __launch_bounds__(128, 6)
 dstate_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_constant__ CUtensorMap tm_dy,
               const __nv_bfloat16* __restrict__ qkvgu, const float2* __restrict__ rope,
               float* __restrict__ dstate, int T, int H, int d, int* error_flag) {
@@ -519,7 +519,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_const
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
         const int e0 = j + 2 * t, e1 = e0 + 1;
-        const float2 cs = rope[tid * 32 + ((c + e0) >> 1)];
+        const float2 cs = rope[((c + e0) >> 1) * CHUNK + tid];
         const float2 tk = __bfloat1622float2(tkb[t]);
         const float2 tu = __bfloat1622float2(tub[t]);
         // y0 = x0 c - x1 s ; y1 = x1 c + x0 s   =>   dx0 = dy0 c + dy1 s ; dx1 = dy1 c - dy0 s

@@ -22,7 +22,8 @@ __device__ __forceinline__ uint8_t* tile_chunk(uint8_t* tile, int r, int j) {
 }
 
 // In place on row `r` of a tile: optional rotary embedding at in-chunk position r (pairs are
-// adjacent elements; rope[r*32 + p] = (cos, sin) of pair p), then optional tanh.
+// adjacent elements; rope[p*128 + r] = (cos, sin) of pair p at position r -- pair-major, so that
+// the 32 rows of a warp read 256 contiguous bytes instead of 32 cache lines), then optional tanh.
 __device__ __forceinline__ void rope_tanh_row(uint8_t* tile, int r, const float2* __restrict__ rope,
                                               bool do_rope, bool do_tanh) {
 #pragma unroll
@@ -34,7 +35,7 @@ __device__ __forceinline__ void rope_tanh_row(uint8_t* tile, int r, const float2
     for (int t = 0; t < 4; ++t) {
       float2 x = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&w[t]));
       if (do_rope) {
-        const float2 cs = rope[r * 32 + j * 4 + t];
+        const float2 cs = rope[(j * 4 + t) * CHUNK + r];
         const float a = x.x * cs.x - x.y * cs.y;
         const float b = x.y * cs.x + x.x * cs.y;
         x.x = a;

@@ -25,7 +25,7 @@ extern "C" void ws_count_launch(void);
 // smem: sK 16K | sU 16K | bars
 constexpr int WR_SMEM = 2 * TILE_BYTES + 1024 + 128;
 
-__global__ void __launch_bounds__(128, 3)
+__global__ void __launch_bounds__(128, 6)
 chunk_writes_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const float2* __restrict__ rope,
                     float* __restrict__ writes, int T, int H, int d, int* error_flag) {
   extern __shared__ uint8_t smem_raw[];
