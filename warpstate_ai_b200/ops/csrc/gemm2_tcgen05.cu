@@ -77,7 +77,7 @@ struct alignas(64) PairGroup {
 // global memory never goes through L1 and each thread touches only swizzled shared memory.
 template <int EPI>
 constexpr bool staged_epilogue() {
-  return EPI == WS_EPI_SWIGLU_BWD || EPI == WS_EPI_SWIGLU;
+  return EPI == WS_EPI_SWIGLU_BWD || EPI == WS_EPI_SWIGLU || EPI == WS_EPI_RESID_F32;
 }
 template <int EPI>
 constexpr int pair_stages() {
@@ -91,6 +91,10 @@ constexpr int pair_smem() {
 // 16-byte chunk j of row r in a 32-row x 64-byte tile written by TMA with the 64-byte swizzle
 __device__ __forceinline__ uint8_t* tile_chunk64(uint8_t* tile, int r, int j) {
   return tile + r * 64 + ((j ^ ((r >> 1) & 3)) << 4);
+}
+// the same for 128-byte rows and the 128-byte swizzle (32 x 32 FP32 tiles)
+__device__ __forceinline__ uint8_t* tile_chunk128(uint8_t* tile, int r, int j) {
+  return tile + r * 128 + ((j ^ (r & 7)) << 4);
 }
 
 struct PairTile {
@@ -151,7 +155,7 @@ gemm2_kernel(const __grid_constant__ PairGroup g) {
     }
     if (STAGED) {
       for (int i = 0; i < 16; ++i) mbar_init(&ebar[i], 1);
-      for (int i = 0; i < (EPI == WS_EPI_SWIGLU ? 3 : 4); ++i) tma_prefetch_desc(&g.epi[i]);
+      for (int i = 0; i < (EPI == WS_EPI_SWIGLU ? 3 : EPI == WS_EPI_RESID_F32 ? 2 : 4); ++i) tma_prefetch_desc(&g.epi[i]);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -316,6 +320,77 @@ gemm2_kernel(const __grid_constant__ PairGroup g) {
               }
               tma_store_2d(&g.epi[2], ebuf + 4096, x, y);
             }
+            tma_store_commit();
+          }
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster_relaxed(mapa_shared(smem_u32(&tempty[buf_t]), 0));
+      }
+      if (lane == 0) tma_store_wait_all();
+    } else if constexpr (EPI == WS_EPI_RESID_F32) {
+      // out = residual + acc through shared memory: per warp 32 rows, per step 32 FP32 columns;
+      // the residual tile is TMA-loaded (double-buffered), updated in place and TMA-stored.
+      uint8_t* ebuf = eStage + (warp - 2) * 8192;  // two buffers of one 4 KiB tile
+      uint64_t* mybar = ebar + (warp - 2) * 2;
+      constexpr int STEPS = (BN / GROUPS) / 32;
+      const GemmParams& p = g.p[0];
+      auto coords = [&](int tile, int step, int& x, int& y) {
+        const PairTile t = resolve_tile(g, tile, n_tile);
+        x = t.nb * BN + egroup * (BN / GROUPS) + step * 32;
+        y = t.mb * 2 * BM + rank * BM + quarter * 32;
+      };
+      auto issue_load = [&](int tile, int step, int buf) {
+        if (lane == 0) {
+          int x, y;
+          coords(tile, step, x, y);
+          mbar_expect_tx(&mybar[buf], 4096);
+          tma_load_2d(ebuf + buf * 4096, &g.epi[0], &mybar[buf], x, y);
+        }
+      };
+      int q = 0;
+      if (pair_id < tiles) issue_load(pair_id, 0, 0);
+      bool ok = true;
+      for (int tile = pair_id; tile < tiles && ok; tile += num_pairs, ++tcount) {
+        const int buf_t = tcount & 1;
+        const uint32_t tph = (tcount >> 1) & 1;
+        if (!mbar_wait(&tfull[buf_t], tph, abort_flag)) break;
+        tc_fence_after_sync();
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf_t * BN + egroup * (BN / GROUPS);
+#pragma unroll 1
+        for (int step = 0; step < STEPS; ++step, ++q) {
+          const int buf = q & 1;
+          if (lane == 0) tma_store_wait_read0();
+          if (step + 1 < STEPS) {
+            issue_load(tile, step + 1, buf ^ 1);
+          } else if (tile + num_pairs < tiles) {
+            issue_load(tile + num_pairs, 0, buf ^ 1);
+          }
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(taddr + step * 32, r);
+          if (!mbar_wait(&mybar[buf], (q >> 1) & 1, abort_flag)) {
+            ok = false;
+            tmem_ld_wait();
+            break;
+          }
+          tmem_ld_wait();
+          uint8_t* tr = ebuf + buf * 4096;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float4* pv = reinterpret_cast<float4*>(tile_chunk128(tr, lane, j));
+            float4 v = *pv;
+            v.x += __uint_as_float(r[4 * j]);
+            v.y += __uint_as_float(r[4 * j + 1]);
+            v.z += __uint_as_float(r[4 * j + 2]);
+            v.w += __uint_as_float(r[4 * j + 3]);
+            *pv = v;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            int x, y;
+            coords(tile, step, x, y);
+            if (x < p.n && y < p.m) tma_store_2d(&g.epi[1], tr, x, y);
             tma_store_commit();
           }
         }
@@ -516,6 +591,13 @@ extern "C" int ws_gemm_pair_group(const WsGemm* items, int count, int sms, cudaS
     total += tiles;
   }
   for (int i = count; i <= MAX_GROUP; ++i) grp.tile_start[i] = total;
+  if (items[0].epilogue == WS_EPI_RESID_F32) {
+    if (count != 1) return -9;
+    const WsGemm* g0 = &items[0];
+    int rc = make_map_f32(&grp.epi[0], g0->aux, g0->n, g0->m, g0->ldaux, 32, 32);
+    if (!rc) rc = make_map_f32(&grp.epi[1], g0->out, g0->n, g0->m, g0->ldo, 32, 32);
+    if (rc) return rc;
+  }
   if (items[0].epilogue == WS_EPI_SWIGLU) {
     if (count != 1) return -9;
     const WsGemm* g0 = &items[0];

@@ -53,4 +53,20 @@ inline int make_map_bf16_swz(CUtensorMap* map, const void* base, uint64_t inner,
   return r == CUDA_SUCCESS ? 0 : -12;
 }
 
+// 2-D FP32 tensor map (128-byte swizzle): for the shared-memory-staged FP32 epilogues.
+inline int make_map_f32(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
+                        uint32_t box_inner, uint32_t box_outer) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return -10;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (ld * 4) % 16 != 0) return -11;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {ld * 4};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -12;
+}
+
 }  // namespace ws
