@@ -232,3 +232,23 @@ def test_evaluate_snapshot_on_full_holdout(workspace):
         ES.run(export, data, out, torch.device("cpu"))
     with pytest.raises(ValueError, match="new report"):
         ES.run(export, data, data / "inside.json", torch.device("cpu"))
+
+
+@pytest.mark.gpu
+def test_bf16_reference_copy_scores_through_the_fused_path():
+    """A frozen BF16 copy of the policy (the resident DPO reference) runs the same fused forward
+    and gives the policy's sequence log-probabilities up to BF16 rounding of the parameters."""
+    import copy
+    torch.manual_seed(0)
+    cfg = WarpStateConfig(vocab_size=1024, d_model=256, n_heads=4, n_cores=2, logical_depth=2, ffn_hidden=512,
+                          chunk_size=128, gradient_checkpointing=False, parallel_memory=True)
+    policy = WarpStateLM(cfg).cuda().eval()
+    frozen = copy.deepcopy(policy).to(torch.bfloat16).requires_grad_(False)
+    x = torch.randint(0, 1024, (4, 256), device="cuda")
+    y = torch.randint(0, 1024, (4, 256), device="cuda")
+    y[:, :100] = -100
+    with torch.no_grad():
+        a = DPO.score_pairs(policy, x, y, torch.device("cuda"), 64)
+        b = DPO.score_pairs(frozen, x, y, torch.device("cuda"), 64)
+    assert torch.isfinite(b).all()
+    assert torch.allclose(a, b, rtol=0.02, atol=0.5), (a, b)

@@ -5,6 +5,7 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 
+#include <string>
 #include <vector>
 
 #include "ws_api.h"
@@ -13,8 +14,13 @@ namespace {
 
 cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
 
+// The message is built as a std::string first: passing the `const char*` and the int straight
+// to TORCH_CHECK's variadic formatter crashed the process (SIGSEGV) instead of throwing.
 void check_rc(int rc, const char* what) {
-  TORCH_CHECK(rc == 0, "ws_b200::", what, " failed with code ", rc);
+  if (rc != 0) {
+    const std::string message = std::string("ws_b200::") + what + " failed with code " + std::to_string(rc);
+    TORCH_CHECK(false, message);
+  }
 }
 
 const void* opt_ptr(const c10::optional<at::Tensor>& t) {
@@ -485,6 +491,12 @@ void adamw_shard_push(at::IntArrayRef master_ptrs, at::IntArrayRef bf16_ptrs, in
 
 // ----------------------------------------------------------------------------- decode step
 int64_t decode_gemm_splits(int64_t n, int64_t k) { return ws_decode_gemm_splits((int)n, (int)k); }
+// Raises the library's error for a non-zero status of a C entry point (what every binding does
+// with the codes it gets back); callable without a GPU, so the error path itself is testable.
+int64_t raise_for_status(int64_t code) {
+  check_rc((int)code, "status");
+  return code;
+}
 
 void decode_gemm(const at::Tensor& w, const at::Tensor& x, int64_t n, int64_t epilogue, at::Tensor out,
                  c10::optional<at::Tensor> error_flag) {
@@ -578,6 +590,7 @@ void decode_attn(const at::Tensor& qkvgu, at::Tensor kc, at::Tensor vc, at::Tens
 
 TORCH_LIBRARY(ws_b200, m) {
   m.def("decode_gemm_splits(int n, int k) -> int");
+  m.def("raise_for_status(int code) -> int");
   m.def("decode_gemm(Tensor w, Tensor x, int n, int epilogue, Tensor(a!) out, Tensor(b!)? error_flag) -> ()");
   m.def("decode_reduce_norm(Tensor(a!) x, Tensor? partial, Tensor? token, Tensor? table, Tensor? scale, Tensor? bias, "
         "Tensor w, float eps, Tensor(b!)? out) -> ()");
@@ -617,6 +630,7 @@ TORCH_LIBRARY(ws_b200, m) {
 TORCH_LIBRARY_IMPL(ws_b200, CompositeExplicitAutograd, m) {
   m.impl("launch_count", &launch_count);
   m.impl("decode_gemm_splits", &decode_gemm_splits);
+  m.impl("raise_for_status", &raise_for_status);
 }
 
 TORCH_LIBRARY_IMPL(ws_b200, CUDA, m) {

@@ -395,6 +395,9 @@ extern "C" int ws_embed_fwd(const long long* ids, const void* table, int table_b
   else if (!table_bf16 && !out_bf16)
     embed_fwd_kernel<float, float><<<grid, ROW_THREADS, 0, stream>>>(ids, (const float*)table, rows, d,
                                                                      vocab, (float*)out);
+  else if (table_bf16 && !out_bf16)  // BF16 table of a frozen model feeding an FP32 residual stream
+    embed_fwd_kernel<__nv_bfloat16, float><<<grid, ROW_THREADS, 0, stream>>>(ids, (const __nv_bfloat16*)table, rows,
+                                                                              d, vocab, (float*)out);
   else
     return -3;
   ws_count_launch();

@@ -165,11 +165,11 @@ class CoreFn(torch.autograd.Function):
         has_mod = depth_scale is not None
         scale = depth_scale.detach().float().contiguous() if has_mod else None
         bias = depth_bias.detach().float().contiguous() if has_mod else None
-        z1, rstd1, xmod = ops.rmsnorm_fwd(x_in, scale, bias, n1w.detach(), core.cfg.rms_eps, True)
+        z1, rstd1, xmod = ops.rmsnorm_fwd(x_in, scale, bias, n1w.detach().float(), core.cfg.rms_eps, True)
         qkvgu = G.linear(z1, bf16_weight(w_in))
         y, attn_saved = _attention_forward(qkvgu, core, batch, seq)
         x2 = G.linear_residual(y, bf16_weight(w_out), xmod)
-        z2, rstd2, _ = ops.rmsnorm_fwd(x2, None, None, n2w.detach(), core.cfg.rms_eps, False)
+        z2, rstd2, _ = ops.rmsnorm_fwd(x2, None, None, n2w.detach().float(), core.cfg.rms_eps, False)
         packed, act = G.linear_swiglu(z2, bf16_weight(w_ug))
         x3 = G.linear_residual(act, bf16_weight(w_down), x2)
         ctx.core = core
@@ -197,14 +197,14 @@ class CoreFn(torch.autograd.Function):
         dx3b = ops.cast_bf16(dx3, None) if dx3.dtype == torch.float32 else dx3
         dpacked = G.grad_input_swiglu(dx3b, bf16_weight(w_down), packed)
         dz2 = G.grad_input(dpacked, bf16_weight(w_ug))
-        dx2, dx2b, g_n2 = ops.rmsnorm_bwd(dz2, x2, rstd2, n2w.detach(), dx3, None, True)
+        dx2, dx2b, g_n2 = ops.rmsnorm_bwd(dz2, x2, rstd2, n2w.detach().float(), dx3, None, True)
         del dz2
         # ---- attention / memory
         dy = G.grad_input(dx2b, bf16_weight(w_out))
         dqkvgu, g_fast, g_slow, g_mix = _attention_backward(dy, qkvgu, ctx.attn_saved, core, batch, seq)
         del dy
         dz1 = G.grad_input(dqkvgu, bf16_weight(w_in))
-        dx_in, _, g_n1 = ops.rmsnorm_bwd(dz1, xmod, rstd1, n1w.detach(), dx2, scale if ctx.has_mod else None, False)
+        dx_in, _, g_n1 = ops.rmsnorm_bwd(dz1, xmod, rstd1, n1w.detach().float(), dx2, scale if ctx.has_mod else None, False)
         # ---- the four weight gradients, deferred to one grouped launch (their tiles share waves)
         g_down, g_ug, g_out, g_in = _wgrad_group([(dx3b, act, w_down), (dpacked, z2, w_ug), (dx2b, y, w_out),
                                                   (dqkvgu, z1, w_in)])
@@ -275,7 +275,7 @@ class NormFn(torch.autograd.Function):
     def forward(ctx, x, w, eps):
         shape = x.shape
         x2 = x.reshape(-1, shape[-1]).contiguous()
-        z, rstd, _ = _ops().rmsnorm_fwd(x2, None, None, w.detach(), eps, False)
+        z, rstd, _ = _ops().rmsnorm_fwd(x2, None, None, w.detach().float(), eps, False)
         ctx.save_for_backward(x2, rstd, w)
         ctx.shape = shape
         return z.view(shape)
@@ -286,7 +286,7 @@ class NormFn(torch.autograd.Function):
         dz = dz.reshape(x2.shape)
         if dz.dtype != torch.bfloat16:
             dz = dz.to(torch.bfloat16)
-        dx, _, dw = _ops().rmsnorm_bwd(dz.contiguous(), x2, rstd, w.detach(), None, None, False)
+        dx, _, dw = _ops().rmsnorm_bwd(dz.contiguous(), x2, rstd, w.detach().float(), None, None, False)
         return dx.view(ctx.shape), dw, None
 
 
@@ -375,7 +375,7 @@ def core_prefill(core, x: torch.Tensor, depth_scale, depth_bias):
     x_in = x.reshape(batch * seq, d).contiguous()
     scale = depth_scale.detach().float().contiguous()
     bias = depth_bias.detach().float().contiguous()
-    z1, _, xmod = ops.rmsnorm_fwd(x_in, scale, bias, core.norm1.weight.detach(), core.cfg.rms_eps, True)
+    z1, _, xmod = ops.rmsnorm_fwd(x_in, scale, bias, core.norm1.weight.detach().float(), core.cfg.rms_eps, True)
     qkvgu = G.linear(z1, bf16_weight(core.in_proj.weight))
     if attention.geometry_ok(core):
         y, _, _, (fast, slow) = attention.forward_only(qkvgu, core, batch, seq, want_final=True)
@@ -385,7 +385,7 @@ def core_prefill(core, x: torch.Tensor, depth_scale, depth_bias):
                                              core.rope_cos, core.rope_sin, return_state=True)
         y = y.reshape(batch * seq, -1).contiguous()
     x2 = G.linear_residual(y, bf16_weight(core.out_proj.weight), xmod)
-    z2, _, _ = ops.rmsnorm_fwd(x2, None, None, core.norm2.weight.detach(), core.cfg.rms_eps, False)
+    z2, _, _ = ops.rmsnorm_fwd(x2, None, None, core.norm2.weight.detach().float(), core.cfg.rms_eps, False)
     _, act = G.linear_swiglu(z2, bf16_weight(core.ffn.up_gate.weight))
     x3 = G.linear_residual(act, bf16_weight(core.ffn.down.weight), x2)
     return x3.view(batch, seq, d), fast, slow
