@@ -235,3 +235,13 @@ def test_launch_scripts_and_supervisor_programs_are_consistent():
     for plan in ("posttrain_plan.json", "dpo_plan.json"):
         data = json.loads((ROOT / "configs" / plan).read_text())
         assert data["after_completion"] == "pause_for_evaluation" and data["handoff"]["processes"] >= 1
+
+
+def test_ops_entry_points_exist_and_parse_help():
+    """The `ops/<name>.py` paths of the original project are thin entry points into the package."""
+    names = sorted(p.name for p in (ROOT / "ops").glob("*.py"))
+    assert {"launch_training.py", "posttrain_handoff.py", "dpo_handoff.py", "transfer_artifacts.py", "benchmark_training.py",
+            "analyze_communication_profile.py", "loss_curve_forecast.py", "archive_dpo.py"} <= set(names)
+    for name in ("loss_curve_forecast.py", "transfer_artifacts.py", "compare_communication_benchmarks.py"):
+        result = subprocess.run([sys.executable, str(ROOT / "ops" / name), "--help"], capture_output=True, text=True)
+        assert result.returncode == 0 and "usage" in result.stdout.lower(), (name, result.stderr[-300:])
