@@ -93,7 +93,7 @@ rmsnorm_fwd_kernel(const T* __restrict__ x, const float* __restrict__ col_scale,
 // block walks over groups of RB_ROWS rows, so every operand is read from global memory exactly
 // once with 16/32-byte coalesced accesses, the per-row mean needs one block reduction per group
 // (double-buffered, one __syncthreads), and the weight-gradient column sums stay in 8 registers.
-constexpr int RB_ROWS = 4;
+constexpr int RB_ROWS = 2;
 
 template <typename T>
 __device__ __forceinline__ void ld8(const T* p, float (&v)[8]) {
@@ -107,7 +107,7 @@ __device__ __forceinline__ void st8(T* p, const float (&v)[8]) {
 }
 
 template <typename T>
-__global__ void __launch_bounds__(ROW_THREADS, 2)
+__global__ void __launch_bounds__(ROW_THREADS, 3)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dz, const T* __restrict__ x,
                    const float* __restrict__ rstd_in, const float* __restrict__ w,
                    const T* __restrict__ dres, const float* __restrict__ out_scale, int rows, int d,
@@ -327,7 +327,7 @@ extern "C" int ws_rmsnorm_fwd(const void* x, int x_bf16, const float* col_scale,
 // Number of partial rows ws_rmsnorm_bwd writes (the caller sizes dw_partial as parts*d floats).
 extern "C" int ws_rmsnorm_bwd_parts(int rows) {
   int blocks = (rows + RB_ROWS - 1) / RB_ROWS;
-  const int cap = 148 * 2;  // two resident blocks per SM
+  const int cap = 148 * 3;  // three resident blocks per SM
   return blocks < cap ? (blocks > 0 ? blocks : 1) : cap;
 }
 
