@@ -106,6 +106,38 @@ def worker(mode: str, rank: int, world: int, out_dir: Path) -> None:
                             "sync": sync.kind}
             torch.save(flat, out_dir / f"params-{kind}-{rank}.pt")
             dist.barrier()
+    elif mode == "gpu_absent_peer":
+        # A peer that never launches its side of a bucket reduction: the surviving rank's kernel
+        # must give up after its time budget, say what it waited for, and leave the GPU usable.
+        # Plain peer loads only (no multimem): NVLS is off for tests in which a rank goes quiet.
+        from warpstate_ai_b200.ops import _ext, gemm
+        from warpstate_ai_b200.parallel import symm
+        _ext.require()
+        n = 1 << 20
+        buf = symm.allocate(n, torch.float32, device)
+        flags = symm.allocate(64, torch.int32, device)
+        status = torch.zeros(8, dtype=torch.int32, device=device)
+        buf.tensor.fill_(float(rank + 1))
+        torch.cuda.synchronize()
+        dist.barrier()
+        # step 1: both ranks take part
+        torch.ops.ws_b200.grad_allreduce(buf.peer_ptrs, flags.peer_ptrs, 0, rank, world, 0, n, 0, 1, 1.0 / world, True, 8,
+                                         None, status, 5.0)
+        torch.cuda.synchronize()
+        assert int(status[0]) == 0 and float(buf.tensor[0]) == 1.5
+        dist.barrier()
+        # step 2: rank 1 stays away (it is idle on the host, nothing of it is in flight)
+        import time
+        if rank == 0:
+            begin = time.perf_counter()
+            torch.ops.ws_b200.grad_allreduce(buf.peer_ptrs, flags.peer_ptrs, 0, rank, world, 0, n, 0, 2, 1.0 / world, True,
+                                             8, None, status, 1.0)
+            torch.cuda.synchronize()
+            report["seconds"] = time.perf_counter() - begin
+            report["status"] = status[:5].tolist()
+            x = torch.randn(256, 256, device=device).bfloat16()
+            report["context_alive"] = bool(torch.isfinite(gemm.linear(x, x).float()).all())
+        dist.barrier()
     elif mode == "gpu_kernel":
         from warpstate_ai_b200.ops import _ext
         from warpstate_ai_b200.parallel import symm
@@ -186,6 +218,17 @@ def test_fused_allreduce_kernel_matches_nccl(tmp_path):
     for r in reports:
         assert r["p2p"] < 1e-6
         assert r["nvls"] == "unavailable" or r["nvls"] < 1e-5
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+@needs_two_gpus
+def test_absent_peer_times_out_with_a_status_and_a_usable_gpu(tmp_path):
+    reports = spawn("gpu_absent_peer", 2, tmp_path, env_extra={"NCCL_NVLS_ENABLE": "0", "WARPSTATE_NVLS": "0"})
+    r = reports[0]
+    code, bucket, peer, expected, seen = r["status"]
+    assert code == 1 and bucket == 0 and peer == 1 and expected == 2 and seen == 1  # waited for rank 1's "ready" of step 2
+    assert 0.9 < r["seconds"] < 10.0 and r["context_alive"] is True
 
 
 @pytest.mark.gpu

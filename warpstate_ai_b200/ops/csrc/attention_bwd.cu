@@ -199,8 +199,8 @@ constexpr int AB_SMEM = 4 * TILE_BYTES + 2 * TILE_BYTES + 2 * 8192 + 128;
 __global__ void __launch_bounds__(AB_THREADS, 2)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_constant__ CUtensorMap tm_state,
                 const __grid_constant__ CUtensorMap tm_dy, const __grid_constant__ CUtensorMap tm_dw,
-                const __nv_bfloat16* __restrict__ qkvgu, const float2* __restrict__ rope,
-                __nv_bfloat16* __restrict__ dqkvgu, int T, int H, int d, int* error_flag) {
+                const __grid_constant__ CUtensorMap tm_dout, const float2* __restrict__ rope, int T, int H, int d,
+                int* error_flag) {
   extern __shared__ __align__(1024) uint8_t smem_ab[];
   uint8_t* smem = smem_ab;
   if ((smem_u32(smem) & 1023u) != 0u) {  // uniform over the CTA: nothing has been set up yet
@@ -242,18 +242,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_const
   const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
 
   if (tid == 0) {
-    mbar_expect_tx(&bars[0], 3 * TILE_BYTES + 2 * 8192);
+    mbar_expect_tx(&bars[0], 4 * TILE_BYTES + 2 * 8192);
     tma_load_2d(sQ, &tm_qkvgu, &bars[0], 0 * d + h * HD, row0);
     tma_load_2d(sK, &tm_qkvgu, &bars[0], 1 * d + h * HD, row0);
     tma_load_2d(sB2, &tm_dy, &bars[0], h * HD, row0);
+    tma_load_2d(sP, &tm_qkvgu, &bars[0], 3 * d + h * HD, row0);  // gate: kept in registers after the first stage
     tma_load_2d(sSt, &tm_state, &bars[0], 0, tile * HD);
     tma_load_2d(sDW, &tm_dw, &bars[0], 0, tile * HD);
   }
-  const size_t grow = static_cast<size_t>(row0 + tid);
-  const __nv_bfloat16* gate = qkvgu + grow * (5 * static_cast<size_t>(d)) + 3 * d + h * HD;
-  __nv_bfloat16* dout = dqkvgu + grow * (5 * static_cast<size_t>(d)) + h * HD;
+  // The thread's gate row, its dGate row and its dV row stay in registers (8 x 16 bytes each) until
+  // the last stage, where all five gradient tiles leave through shared memory and TMA stores.
+  uint4 gate_row[8], dgate_row[8], dv_row[8];
 
   bool ok = mbar_wait(&bars[0], 0, abort_flag);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) gate_row[j] = *reinterpret_cast<const uint4*>(tile_chunk(sP, tid, j));
   if (ok) {
     rope_tanh_row(sQ, tid, rope, true, false);
     rope_tanh_row(sK, tid, rope, true, false);
@@ -261,7 +264,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_const
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const uint4 dyq = *reinterpret_cast<const uint4*>(tile_chunk(sB2, tid, j));
-      const uint4 gq = *reinterpret_cast<const uint4*>(gate + j * 8);
+      const uint4 gq = gate_row[j];
       const __nv_bfloat162* dyb = reinterpret_cast<const __nv_bfloat162*>(&dyq);
       const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&gq);
       uint4 o;
@@ -375,7 +378,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_const
       const int chunk = (c + j) >> 3;
       uint4* pdl = reinterpret_cast<uint4*>(tile_chunk(sB2, tid, chunk));
       const uint4 dyq = *pdl;
-      const uint4 gq = *reinterpret_cast<const uint4*>(gate + c + j);
+      const uint4 gq = gate_row[chunk];
       const __nv_bfloat162* dyb = reinterpret_cast<const __nv_bfloat162*>(&dyq);
       const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&gq);
       uint4 o_dl, o_dg;
@@ -394,7 +397,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_const
         w_dg[t] = pack_bf16x2(dyv.x * (l0 - m0) * g0 * (1.f - g0), dyv.y * (l1 - m1) * g1 * (1.f - g1));
       }
       *pdl = o_dl;
-      if (ok) *reinterpret_cast<uint4*>(dout + 3 * d + c + j) = o_dg;
+      dgate_row[chunk] = o_dg;
     }
   }
   tc_fence_before_sync();
@@ -444,11 +447,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_const
     tmem_ld_wait();
 #pragma unroll
     for (int j = 0; j < 16; j += 8) {
-      const uint4 o_v = make_uint4(pack_bf16x2(__uint_as_float(rv[j]), __uint_as_float(rv[j + 1])),
-                                   pack_bf16x2(__uint_as_float(rv[j + 2]), __uint_as_float(rv[j + 3])),
-                                   pack_bf16x2(__uint_as_float(rv[j + 4]), __uint_as_float(rv[j + 5])),
-                                   pack_bf16x2(__uint_as_float(rv[j + 6]), __uint_as_float(rv[j + 7])));
-      if (ok) *reinterpret_cast<uint4*>(dout + 2 * d + c + j) = o_v;
+      dv_row[(c + j) >> 3] = make_uint4(pack_bf16x2(__uint_as_float(rv[j]), __uint_as_float(rv[j + 1])),
+                                        pack_bf16x2(__uint_as_float(rv[j + 2]), __uint_as_float(rv[j + 3])),
+                                        pack_bf16x2(__uint_as_float(rv[j + 4]), __uint_as_float(rv[j + 5])),
+                                        pack_bf16x2(__uint_as_float(rv[j + 6]), __uint_as_float(rv[j + 7])));
     }
   }
 #pragma unroll
@@ -531,12 +533,27 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_const
         w_u[t] = pack_bf16x2(__uint_as_float(rtu[e0]) * (1.f / CHUNK) * (1.f - tu.x * tu.x),
                              __uint_as_float(rtu[e1]) * (1.f / CHUNK) * (1.f - tu.y * tu.y));
       }
-      if (ok) {
-        *reinterpret_cast<uint4*>(dout + 0 * d + c + j) = o_q;
-        *reinterpret_cast<uint4*>(dout + 1 * d + c + j) = o_k;
-        *reinterpret_cast<uint4*>(dout + 4 * d + c + j) = o_u;
-      }
+      // every operand of the last MMA group has been consumed: Q, K, P, State and dW tiles are free
+      *reinterpret_cast<uint4*>(tile_chunk(sQ, tid, chunk)) = o_q;
+      *reinterpret_cast<uint4*>(tile_chunk(sK, tid, chunk)) = o_k;
+      *reinterpret_cast<uint4*>(tile_chunk(sP, tid, chunk)) = o_u;
+      *reinterpret_cast<uint4*>(tile_chunk(sP + TILE_BYTES, tid, chunk)) = dgate_row[chunk];
+      *reinterpret_cast<uint4*>(tile_chunk(sSt, tid, chunk)) = dv_row[chunk];
     }
+  }
+  fence_proxy_async_smem();
+  __syncwarp();
+  if ((tid & 31) == 0) {  // one store per gradient tile for the warp's 32 token rows
+    if (ok) {
+      const int r = row0 + warp * 32, off = warp * 4096;
+      tma_store_2d(&tm_dout, sQ + off, 0 * d + h * HD, r);
+      tma_store_2d(&tm_dout, sK + off, 1 * d + h * HD, r);
+      tma_store_2d(&tm_dout, sSt + off, 2 * d + h * HD, r);
+      tma_store_2d(&tm_dout, sP + TILE_BYTES + off, 3 * d + h * HD, r);
+      tma_store_2d(&tm_dout, sP + off, 4 * d + h * HD, r);
+      tma_store_commit();
+    }
+    tma_store_wait_read0();
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -589,8 +606,10 @@ extern "C" int ws_attn_bwd(const void* qkvgu, const void* states, const void* dy
                            cudaStream_t stream) {
   if (T % CHUNK != 0 || d != H * HD) return -1;
   const int tiles = B * (T / CHUNK) * H;
-  CUtensorMap tm, ts, td, tw;
+  CUtensorMap tm, ts, td, tw, to;
   int rc = make_tile_map(&tm, qkvgu, 5 * (uint64_t)d, (uint64_t)B * T, 5 * (uint64_t)d, HD, CHUNK);
+  if (rc) return rc;
+  rc = make_tile_map(&to, dqkvgu, 5 * (uint64_t)d, (uint64_t)B * T, 5 * (uint64_t)d, HD, 32);
   if (rc) return rc;
   rc = make_tile_map(&ts, states, HD, (uint64_t)tiles * HD, HD, HD, HD);
   if (rc) return rc;
@@ -604,9 +623,8 @@ extern "C" int ws_attn_bwd(const void* qkvgu, const void* states, const void* dy
       return -20;
     configured = true;
   }
-  attn_bwd_kernel<<<tiles, AB_THREADS, AB_SMEM, stream>>>(tm, ts, td, tw, (const __nv_bfloat16*)qkvgu,
-                                                   reinterpret_cast<const float2*>(rope), (__nv_bfloat16*)dqkvgu, T,
-                                                   H, d, error_flag);
+  attn_bwd_kernel<<<tiles, AB_THREADS, AB_SMEM, stream>>>(tm, ts, td, tw, to, reinterpret_cast<const float2*>(rope),
+                                                          T, H, d, error_flag);
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }

@@ -141,13 +141,16 @@ memory_scan_kernel(const float* __restrict__ writes, const float* __restrict__ f
 }
 
 // =============================================================================== attention
-// smem: sQ 16K | sK 16K | sV 16K | sSt 8K | sP 32K | bars
-constexpr int AF_SMEM = 3 * TILE_BYTES + 8192 + 2 * TILE_BYTES + 1024 + 128;
+// smem: sQ 16K | sK 16K | sV 16K | sSt 8K | sP 32K | sG 16K | bars
+// The gate tile arrives by TMA with the other operands and the blended output leaves by TMA
+// (staged in sQ, one 32-row store per warp): a thread that owns a token row would otherwise
+// touch one 16-byte piece of 32 different cache lines per warp instruction.
+constexpr int AF_SMEM = 3 * TILE_BYTES + 8192 + 2 * TILE_BYTES + TILE_BYTES + 1024 + 128;
 
 __global__ void __launch_bounds__(128, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_constant__ CUtensorMap tm_state,
-                const __nv_bfloat16* __restrict__ qkvgu, const float2* __restrict__ rope,
-                __nv_bfloat16* __restrict__ y, int T, int H, int d, int* error_flag) {
+                const __grid_constant__ CUtensorMap tm_y, const float2* __restrict__ rope, int T, int H, int d,
+                int* error_flag) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
   uint8_t* sQ = smem;
@@ -155,7 +158,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_const
   uint8_t* sV = smem + 2 * TILE_BYTES;
   uint8_t* sSt = smem + 3 * TILE_BYTES;
   uint8_t* sP = smem + 3 * TILE_BYTES + 8192;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * TILE_BYTES);
+  uint8_t* sG = sP + 2 * TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sG + TILE_BYTES);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const int tid = threadIdx.x, warp = tid >> 5;
@@ -183,10 +187,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_const
   const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
 
   if (tid == 0) {
-    mbar_expect_tx(&bars[0], 3 * TILE_BYTES + 8192);
+    mbar_expect_tx(&bars[0], 4 * TILE_BYTES + 8192);
     tma_load_2d(sQ, &tm_qkvgu, &bars[0], 0 * d + h * HD, row0);
     tma_load_2d(sK, &tm_qkvgu, &bars[0], 1 * d + h * HD, row0);
     tma_load_2d(sV, &tm_qkvgu, &bars[0], 2 * d + h * HD, row0);
+    tma_load_2d(sG, &tm_qkvgu, &bars[0], 3 * d + h * HD, row0);
     tma_load_2d(sSt, &tm_state, &bars[0], 0, tile * HD);
   }
   bool ok = mbar_wait(&bars[0], 0, abort_flag);
@@ -259,35 +264,40 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_const
   ok = ok && mbar_wait(&bars[2], 0, abort_flag);
   tc_fence_after_sync();
 
-  // ---- gate blend and token-major store
+  // ---- gate blend into the (now idle) Q tile, then one TMA store of the warp's 32 rows
   const float inv_l = 1.f / row_sum;
-  const size_t grow = static_cast<size_t>(row0 + tid);
-  const __nv_bfloat16* gate = qkvgu + grow * (5 * static_cast<size_t>(d)) + 3 * d + h * HD;
-  __nv_bfloat16* yout = y + grow * d + h * HD;
 #pragma unroll
   for (int c = 0; c < HD; c += 16) {
     uint32_t ro[16], rm[16];
     tmem_ld_32x32b_x16(t_o + lane_base + c, ro);
     tmem_ld_32x32b_x16(t_m + lane_base + c, rm);
     tmem_ld_wait();
-    if (ok) {
 #pragma unroll
-      for (int j = 0; j < 16; j += 8) {
-        const uint4 gq = *reinterpret_cast<const uint4*>(gate + c + j);
-        const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&gq);
-        uint4 out;
-        uint32_t* ow = reinterpret_cast<uint32_t*>(&out);
+    for (int j = 0; j < 16; j += 8) {
+      const int chunk = (c + j) >> 3;
+      const uint4 gq = *reinterpret_cast<const uint4*>(tile_chunk(sG, tid, chunk));
+      const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&gq);
+      uint4 out;
+      uint32_t* ow = reinterpret_cast<uint32_t*>(&out);
 #pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const float2 gf = __bfloat1622float2(gb[t]);
-          const float g0 = sigmoid_f(gf.x), g1 = sigmoid_f(gf.y);
-          const float o0 = __uint_as_float(ro[j + 2 * t]) * inv_l, o1 = __uint_as_float(ro[j + 2 * t + 1]) * inv_l;
-          const float m0 = __uint_as_float(rm[j + 2 * t]) * 0.125f, m1 = __uint_as_float(rm[j + 2 * t + 1]) * 0.125f;
-          ow[t] = pack_bf16x2(g0 * o0 + (1.f - g0) * m0, g1 * o1 + (1.f - g1) * m1);
-        }
-        *reinterpret_cast<uint4*>(yout + c + j) = out;
+      for (int t = 0; t < 4; ++t) {
+        const float2 gf = __bfloat1622float2(gb[t]);
+        const float g0 = sigmoid_f(gf.x), g1 = sigmoid_f(gf.y);
+        const float o0 = __uint_as_float(ro[j + 2 * t]) * inv_l, o1 = __uint_as_float(ro[j + 2 * t + 1]) * inv_l;
+        const float m0 = __uint_as_float(rm[j + 2 * t]) * 0.125f, m1 = __uint_as_float(rm[j + 2 * t + 1]) * 0.125f;
+        ow[t] = pack_bf16x2(g0 * o0 + (1.f - g0) * m0, g1 * o1 + (1.f - g1) * m1);
       }
+      *reinterpret_cast<uint4*>(tile_chunk(sQ, tid, chunk)) = out;
     }
+  }
+  fence_proxy_async_smem();
+  __syncwarp();
+  if ((tid & 31) == 0) {
+    if (ok) {
+      tma_store_2d(&tm_y, sQ + warp * 4096, h * HD, row0 + warp * 32);
+      tma_store_commit();
+    }
+    tma_store_wait_read0();
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -337,10 +347,12 @@ extern "C" int ws_attn_fwd(const void* qkvgu, const void* states, const float* r
                            int d, int* error_flag, cudaStream_t stream) {
   if (T % CHUNK != 0 || d != H * HD) return -1;
   const int tiles = B * (T / CHUNK) * H;
-  CUtensorMap tm, ts;
+  CUtensorMap tm, ts, ty;
   int rc = make_tile_map(&tm, qkvgu, 5 * (uint64_t)d, (uint64_t)B * T, 5 * (uint64_t)d, HD, CHUNK);
   if (rc) return rc;
   rc = make_tile_map(&ts, states, HD, (uint64_t)tiles * HD, HD, HD, HD);
+  if (rc) return rc;
+  rc = make_tile_map(&ty, y, (uint64_t)d, (uint64_t)B * T, (uint64_t)d, HD, 32);
   if (rc) return rc;
   static bool configured = false;
   if (!configured) {
@@ -348,8 +360,7 @@ extern "C" int ws_attn_fwd(const void* qkvgu, const void* states, const float* r
       return -20;
     configured = true;
   }
-  attn_fwd_kernel<<<tiles, 128, AF_SMEM, stream>>>(tm, ts, (const __nv_bfloat16*)qkvgu,
-                                                   reinterpret_cast<const float2*>(rope), (__nv_bfloat16*)y, T, H, d,
+  attn_fwd_kernel<<<tiles, 128, AF_SMEM, stream>>>(tm, ts, ty, reinterpret_cast<const float2*>(rope), T, H, d,
                                                    error_flag);
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
