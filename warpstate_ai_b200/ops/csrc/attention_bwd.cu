@@ -23,17 +23,19 @@ namespace ws {
 extern "C" void ws_count_launch(void);
 
 // =============================================================================== dState
-constexpr int DS_SMEM = 2 * TILE_BYTES + 1024 + 128;
+// smem: Qr 16K | dy -> dmem/8 16K | gate, then the FP32 result 16K | bars
+constexpr int DS_SMEM = 3 * TILE_BYTES + 1024 + 128;
 
-__global__ void __launch_bounds__(128, 6)
+__global__ void __launch_bounds__(128, 4)
 dstate_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_constant__ CUtensorMap tm_dy,
-              const __nv_bfloat16* __restrict__ qkvgu, const float2* __restrict__ rope,
-              float* __restrict__ dstate, int T, int H, int d, int* error_flag) {
+              const __grid_constant__ CUtensorMap tm_out, const float2* __restrict__ rope, int T, int H, int d,
+              int* error_flag) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
   uint8_t* sQ = smem;
   uint8_t* sD = smem + TILE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * TILE_BYTES);
+  uint8_t* sG = smem + 2 * TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 3 * TILE_BYTES);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const int tid = threadIdx.x, warp = tid >> 5;
@@ -58,19 +60,19 @@ dstate_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_constan
   const uint32_t tmem = *tmem_slot;
 
   if (tid == 0) {
-    mbar_expect_tx(&bars[0], 2 * TILE_BYTES);
+    mbar_expect_tx(&bars[0], 3 * TILE_BYTES);
     tma_load_2d(sQ, &tm_qkvgu, &bars[0], h * HD, row0);
     tma_load_2d(sD, &tm_dy, &bars[0], h * HD, row0);
+    tma_load_2d(sG, &tm_qkvgu, &bars[0], 3 * d + h * HD, row0);
   }
   bool ok = mbar_wait(&bars[0], 0, abort_flag);
   if (ok) {
     rope_tanh_row(sQ, tid, rope, true, false);
-    const __nv_bfloat16* gate = qkvgu + static_cast<size_t>(row0 + tid) * (5 * static_cast<size_t>(d)) + 3 * d + h * HD;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       uint4* p = reinterpret_cast<uint4*>(tile_chunk(sD, tid, j));
       uint4 v = *p;
-      const uint4 gq = *reinterpret_cast<const uint4*>(gate + j * 8);
+      const uint4 gq = *reinterpret_cast<const uint4*>(tile_chunk(sG, tid, j));
       uint32_t* w = reinterpret_cast<uint32_t*>(&v);
       const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&gq);
 #pragma unroll
@@ -95,18 +97,30 @@ dstate_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_constan
   ok = ok && mbar_wait(&bars[1], 0, abort_flag);
   tc_fence_after_sync();
   if (warp < 2) {
-    float* out = dstate + (static_cast<size_t>(tile) * HD + tid) * HD;
+    // Row `tid` of the [64 x 64] FP32 result goes to two swizzled [64 x 32] half tiles (the gate tile's
+    // space), and each warp stores its 32 rows of both halves by TMA.
 #pragma unroll
     for (int c = 0; c < HD; c += 16) {
       uint32_t r[16];
       tmem_ld_32x32b_x16(tmem + (static_cast<uint32_t>(warp * 32) << 16) + c, r);
       tmem_ld_wait();
-      if (ok) {
 #pragma unroll
-        for (int j = 0; j < 16; j += 4)
-          *reinterpret_cast<float4*>(out + c + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                                               __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+      for (int j = 0; j < 16; j += 4) {
+        const int col = c + j;
+        uint8_t* dst = sG + (col >> 5) * 8192 + tid * 128 + ((((col & 31) >> 2) ^ (tid & 7)) << 4);
+        *reinterpret_cast<float4*>(dst) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                      __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
       }
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if ((tid & 31) == 0) {
+      if (ok) {
+        tma_store_2d(&tm_out, sG + warp * 4096, 0, tile * HD + warp * 32);
+        tma_store_2d(&tm_out, sG + 8192 + warp * 4096, 32, tile * HD + warp * 32);
+        tma_store_commit();
+      }
+      tma_store_wait_read0();
     }
   }
   tc_fence_before_sync();
@@ -571,10 +585,12 @@ using namespace ws;
 extern "C" int ws_attn_dstate(const void* qkvgu, const void* dy, const float* rope, float* dstate, int B, int T,
                               int H, int d, int* error_flag, cudaStream_t stream) {
   if (T % CHUNK != 0 || d != H * HD) return -1;
-  CUtensorMap tm, td;
+  CUtensorMap tm, td, to;
   int rc = make_tile_map(&tm, qkvgu, 5 * (uint64_t)d, (uint64_t)B * T, 5 * (uint64_t)d, HD, CHUNK);
   if (rc) return rc;
   rc = make_tile_map(&td, dy, (uint64_t)d, (uint64_t)B * T, (uint64_t)d, HD, CHUNK);
+  if (rc) return rc;
+  rc = make_map_f32(&to, dstate, HD, (uint64_t)B * (T / CHUNK) * H * HD, HD, 32, 32);
   if (rc) return rc;
   static bool configured = false;
   if (!configured) {
@@ -583,8 +599,8 @@ extern "C" int ws_attn_dstate(const void* qkvgu, const void* dy, const float* ro
     configured = true;
   }
   const int tiles = B * (T / CHUNK) * H;
-  dstate_kernel<<<tiles, 128, DS_SMEM, stream>>>(tm, td, (const __nv_bfloat16*)qkvgu,
-                                                 reinterpret_cast<const float2*>(rope), dstate, T, H, d, error_flag);
+  dstate_kernel<<<tiles, 128, DS_SMEM, stream>>>(tm, td, to, reinterpret_cast<const float2*>(rope), T, H, d,
+                                                 error_flag);
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }

@@ -26,8 +26,8 @@ extern "C" void ws_count_launch(void);
 constexpr int WR_SMEM = 2 * TILE_BYTES + 1024 + 128;
 
 __global__ void __launch_bounds__(128, 6)
-chunk_writes_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const float2* __restrict__ rope,
-                    float* __restrict__ writes, int T, int H, int d, int* error_flag) {
+chunk_writes_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_constant__ CUtensorMap tm_out,
+                    const float2* __restrict__ rope, int T, int H, int d, int* error_flag) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = align1024(smem_raw);
   uint8_t* sK = smem;
@@ -83,19 +83,31 @@ chunk_writes_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const float2* 
   ok = ok && mbar_wait(&bars[1], 0, abort_flag);
   tc_fence_after_sync();
   if (warp < 2) {  // lanes 0..63 hold the result rows
-    float* out = writes + (static_cast<size_t>(tile) * HD + tid) * HD;
+    // Row `tid` goes to two swizzled [64 x 32] FP32 half tiles in the (consumed) K tile's space; each
+    // warp then stores its 32 rows of both halves by TMA.
 #pragma unroll
     for (int c = 0; c < HD; c += 16) {
       uint32_t r[16];
       tmem_ld_32x32b_x16(tmem + (static_cast<uint32_t>(warp * 32) << 16) + c, r);
       tmem_ld_wait();
-      if (ok) {
 #pragma unroll
-        for (int j = 0; j < 16; j += 4)
-          *reinterpret_cast<float4*>(out + c + j) =
-              make_float4(__uint_as_float(r[j]) * (1.f / CHUNK), __uint_as_float(r[j + 1]) * (1.f / CHUNK),
-                          __uint_as_float(r[j + 2]) * (1.f / CHUNK), __uint_as_float(r[j + 3]) * (1.f / CHUNK));
+      for (int j = 0; j < 16; j += 4) {
+        const int col = c + j;
+        uint8_t* dst = sK + (col >> 5) * 8192 + tid * 128 + ((((col & 31) >> 2) ^ (tid & 7)) << 4);
+        *reinterpret_cast<float4*>(dst) =
+            make_float4(__uint_as_float(r[j]) * (1.f / CHUNK), __uint_as_float(r[j + 1]) * (1.f / CHUNK),
+                        __uint_as_float(r[j + 2]) * (1.f / CHUNK), __uint_as_float(r[j + 3]) * (1.f / CHUNK));
       }
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if ((tid & 31) == 0) {
+      if (ok) {
+        tma_store_2d(&tm_out, sK + warp * 4096, 0, tile * HD + warp * 32);
+        tma_store_2d(&tm_out, sK + 8192 + warp * 4096, 32, tile * HD + warp * 32);
+        tma_store_commit();
+      }
+      tma_store_wait_read0();
     }
   }
   tc_fence_before_sync();
@@ -325,7 +337,10 @@ extern "C" int ws_chunk_writes(const void* qkvgu, const float* rope, float* writ
     configured = true;
   }
   const int tiles = B * (T / CHUNK) * H;
-  chunk_writes_kernel<<<tiles, 128, WR_SMEM, stream>>>(tm, reinterpret_cast<const float2*>(rope), writes, T, H, d,
+  CUtensorMap to;
+  rc = make_map_f32(&to, writes, HD, (uint64_t)tiles * HD, HD, 32, 32);
+  if (rc) return rc;
+  chunk_writes_kernel<<<tiles, 128, WR_SMEM, stream>>>(tm, to, reinterpret_cast<const float2*>(rope), T, H, d,
                                                        error_flag);
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : -21;

@@ -18,6 +18,11 @@
 //                          append k/v/u to the chunk cache, causal attention over the cache rows
 //                          <= position, memory read q.M, gate blend.
 //
+// The ~200 launches of a step form one chain of programmatic dependent launches: every kernel lets
+// its successor start at once, and a GEMM fills its whole TMA ring with weight tiles (which no
+// kernel of the step writes) before it waits for its predecessor, so the weight stream of the
+// next projection runs under the small kernels and the tail of the previous GEMM.
+//
 // Reference semantics: WarpStateCore.step (reference warpstate/model.py:222-274) in the
 // training-consistent form of ops/posttrain_chat.py:94-142.  The reference runs these as
 // ~40 eager PyTorch ops per layer at batch 1.
@@ -26,6 +31,8 @@
 #include "ws_tma_host.h"
 
 #include <cuda_bf16.h>
+
+#include <cstdlib>
 
 namespace ws {
 
@@ -97,6 +104,7 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
+  pdl_launch_dependents();
 
   const int slab = blockIdx.x;
   const int total_kb = (p.k + BK - 1) / BK;
@@ -107,17 +115,23 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int kb = kb0, it = 0; kb < kb1; ++kb, ++it) {
+      auto load_w = [&](int s, int kb) {
+        mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
+        tma_load_2d(sW + s * W_BYTES, &tm_w, &full[s], kb * BK, n0);
+        if (EPI == 2)  // 64 up rows + the 64 matching gate rows
+          tma_load_2d(sW + s * W_BYTES + 64 * 128, &tm_w, &full[s], kb * BK, p.n + n0);
+      };
+      // The weights are constant during a step: the first ring of weight tiles is requested before
+      // the wait for the previous kernel, whose output is this kernel's activation block.
+      const int pre = min(kb1 - kb0, Cfg::STAGES);
+      for (int it = 0; it < pre; ++it) load_w(it, kb0 + it);
+      pdl_wait();
+      for (int it = 0; it < pre; ++it) tma_load_2d(sX + it * Cfg::X_BYTES, &tm_x, &full[it], (kb0 + it) * BK, 0);
+      for (int kb = kb0 + pre, it = pre; kb < kb1; ++kb, ++it) {
         const int s = it % Cfg::STAGES;
         const uint32_t ph = (it / Cfg::STAGES) & 1;
         if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) break;
-        mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
-        if (EPI == 2) {  // 64 up rows + the 64 matching gate rows
-          tma_load_2d(sW + s * W_BYTES, &tm_w, &full[s], kb * BK, n0);
-          tma_load_2d(sW + s * W_BYTES + 64 * 128, &tm_w, &full[s], kb * BK, p.n + n0);
-        } else {
-          tma_load_2d(sW + s * W_BYTES, &tm_w, &full[s], kb * BK, n0);
-        }
+        load_w(s, kb);
         tma_load_2d(sX + s * Cfg::X_BYTES, &tm_x, &full[s], kb * BK, 0);
       }
     }
@@ -224,6 +238,8 @@ decode_reduce_norm_kernel(float* __restrict__ x, const float* __restrict__ parti
                           const float* __restrict__ scale, const float* __restrict__ bias, const float* __restrict__ w,
                           float eps, int d, int batch, __nv_bfloat16* __restrict__ out) {
   __shared__ float red[8];
+  pdl_launch_dependents();
+  pdl_wait();
   const int b = blockIdx.x;
   float* xr = x + static_cast<size_t>(b) * d;
   const float* src = xr;
@@ -282,6 +298,8 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ qkvgu, __nv_bfloat16* __res
   __shared__ float sq[HD], sk[HD], sp[C], sl[16][HD + 1], sm[16][HD + 1], sred[4];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int h = blockIdx.x % H, b = blockIdx.x / H;
+  pdl_launch_dependents();
+  pdl_wait();
   int pos = static_cast<int>(*pos_ptr);
   pos = pos < 0 ? 0 : (pos >= C ? C - 1 : pos);
   const __nv_bfloat16* row = qkvgu + static_cast<size_t>(b) * 5 * d + h * HD;
@@ -404,6 +422,27 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ qkvgu, __nv_bfloat16* __res
   }
 }
 
+// Launch with the programmatic-stream-serialization attribute (WS_DECODE_PDL=0 launches normally).
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_chained(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                  Args... args) {
+  static const bool chained = [] {
+    const char* e = std::getenv("WS_DECODE_PDL");
+    return e == nullptr || e[0] != '0';
+  }();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = chained ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 template <int BPAD, int EPI>
 static int launch_decode_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const DecodeGemmParams& p, dim3 grid,
                               cudaStream_t stream) {
@@ -414,9 +453,9 @@ static int launch_decode_gemm(const CUtensorMap& tw, const CUtensorMap& tx, cons
       return -20;
     configured = true;
   }
-  kern<<<grid, dec::THREADS, DecodeCfg<BPAD>::SMEM, stream>>>(tw, tx, p);
+  const cudaError_t err = launch_chained(kern, grid, dim3(dec::THREADS), DecodeCfg<BPAD>::SMEM, stream, tw, tx, p);
   ws_count_launch();
-  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+  return err == cudaSuccess ? 0 : -21;
 }
 
 }  // namespace ws
@@ -474,19 +513,21 @@ extern "C" int ws_decode_reduce_norm(float* x, const float* partial, int splits,
                                      const float* table, int vocab, const float* scale, const float* bias,
                                      const float* w, float eps, int d, int batch, void* out, cudaStream_t stream) {
   if (d % 4 != 0 || batch <= 0 || (splits > 0 && partial == nullptr)) return -1;
-  decode_reduce_norm_kernel<<<batch, 256, 0, stream>>>(x, partial, splits, token, table, vocab, scale, bias, w, eps, d,
-                                                       batch, static_cast<__nv_bfloat16*>(out));
+  const cudaError_t err = launch_chained(decode_reduce_norm_kernel, dim3(batch), dim3(256), 0, stream, x, partial, splits,
+                                         token, table, vocab, scale, bias, w, eps, d, batch,
+                                         static_cast<__nv_bfloat16*>(out));
   ws_count_launch();
-  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+  return err == cudaSuccess ? 0 : -21;
 }
 
 extern "C" int ws_decode_attn(const void* qkvgu, void* kc, void* vc, void* uc, const void* mixed, const float* rope,
                               const long long* pos, int batch, int H, int d, void* y, cudaStream_t stream) {
   if (d != H * 64 || batch <= 0) return -1;
-  decode_attn_kernel<<<batch * H, 128, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(qkvgu), static_cast<__nv_bfloat16*>(kc), static_cast<__nv_bfloat16*>(vc),
-      static_cast<__nv_bfloat16*>(uc), static_cast<const __nv_bfloat16*>(mixed), reinterpret_cast<const float2*>(rope), pos,
-      H, d, static_cast<__nv_bfloat16*>(y));
+  const cudaError_t err = launch_chained(
+      decode_attn_kernel, dim3(batch * H), dim3(128), 0, stream, static_cast<const __nv_bfloat16*>(qkvgu),
+      static_cast<__nv_bfloat16*>(kc), static_cast<__nv_bfloat16*>(vc), static_cast<__nv_bfloat16*>(uc),
+      static_cast<const __nv_bfloat16*>(mixed), reinterpret_cast<const float2*>(rope), pos, H, d,
+      static_cast<__nv_bfloat16*>(y));
   ws_count_launch();
-  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+  return err == cudaSuccess ? 0 : -21;
 }
