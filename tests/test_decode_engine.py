@@ -82,6 +82,7 @@ def test_cuda_engine_matches_forward_in_bf16():
 def test_decode_gemm_against_fp32(batch):
     """Weight-streaming GEMM: all four epilogues, with and without K splits, ragged batch."""
     from warpstate_ai_b200.ops import _ext, gemm
+    from warpstate_ai_b200.ops.decode import pack_weight
     _ext.require()
     ops = torch.ops.ws_b200
     torch.manual_seed(batch)
@@ -104,6 +105,14 @@ def test_decode_gemm_against_fp32(batch):
         part = torch.full((splits, batch, n), float("nan"), device="cuda")
         ops.decode_gemm(w, x, n, 1, part, flag)
         assert rel(part.sum(0), ref) < 1e-4, (n, k, "split", splits)
+        # the tile-contiguous weight copy gives the same results bit for bit
+        wp = pack_weight(w)
+        out_p = torch.full_like(out, float("nan"))
+        ops.decode_gemm(wp, x, n, 0, out_p, flag, True)
+        assert torch.equal(out_p, out), (n, k, "packed bf16")
+        part_p = torch.full_like(part, float("nan"))
+        ops.decode_gemm(wp, x, n, 1, part_p, flag, True)
+        assert torch.equal(part_p, part), (n, k, "packed split")
     assert ops.decode_gemm_splits(2048, 2048) > 1 and ops.decode_gemm_splits(10240, 2048) == 1
     h, k = 512, 256
     w = (torch.randn(2 * h, k, device="cuda") * 0.05).bfloat16()
@@ -113,6 +122,9 @@ def test_decode_gemm_against_fp32(batch):
     act = torch.full((batch, h), float("nan"), device="cuda", dtype=torch.bfloat16)
     ops.decode_gemm(w, x, h, 2, act, flag)
     assert rel(act, ref) < 0.006
+    act_p = torch.full_like(act, float("nan"))
+    ops.decode_gemm(pack_weight(w, swiglu=True), x, h, 2, act_p, flag, True)
+    assert torch.equal(act_p, act)
     gemm.check_device_errors()
 
 
@@ -180,3 +192,22 @@ def test_kernel_decode_path_matches_pytorch_path():
         if t % 37 == 0 or t == 199:
             assert torch.allclose(a, b, rtol=0.05, atol=0.05), t
     assert fast._kbufs is not None and slow._kbufs is None
+
+
+def test_pack_weight_round_trip_and_tile_order():
+    """CPU: the tile-by-tile copy restores to the original, and a tile is the promised block."""
+    from warpstate_ai_b200.ops.decode import pack_weight, unpack_weight
+    torch.manual_seed(0)
+    w = torch.randn(300, 200).bfloat16()
+    packed = pack_weight(w)
+    assert packed.shape == (3, 4, 128, 64) and packed.is_contiguous()
+    assert torch.equal(unpack_weight(packed, 300, 200), w)
+    assert torch.equal(packed[1, 2, :, :], w[128:256, 128:192])
+    assert float(packed[2, 0, 300 - 256:, :].abs().sum()) == 0.0  # rows past the weight are zero
+    ug = torch.randn(2 * 128, 64).bfloat16()
+    p2 = pack_weight(ug, swiglu=True)
+    assert p2.shape == (2, 1, 128, 64)
+    assert torch.equal(p2[1, 0, :64], ug[64:128]) and torch.equal(p2[1, 0, 64:], ug[128 + 64:256])
+    assert torch.equal(unpack_weight(p2, 256, 64, swiglu=True), ug)
+    with pytest.raises(ValueError):
+        pack_weight(torch.randn(2 * 96, 64), swiglu=True)

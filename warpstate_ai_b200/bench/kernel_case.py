@@ -111,7 +111,8 @@ def scan_case() -> None:
 
 
 def decode_case() -> None:
-    """Decode-step GEMMs at batch 64: in_proj (direct), down (split-K partials), up/gate (SwiGLU)."""
+    """Decode-step GEMMs at batch 64: in_proj (direct), up/gate (SwiGLU), down (split-K partials);
+    each with row-major weights, then with the tile-contiguous copy."""
     ops = torch.ops.ws_b200
     flag = G.error_flag(torch.device("cuda"))
     x = torch.randn(64, 2048, device="cuda").bfloat16()
@@ -122,10 +123,15 @@ def decode_case() -> None:
     out = torch.empty(64, 10240, device="cuda", dtype=torch.bfloat16)
     a = torch.empty(64, 7168, device="cuda", dtype=torch.bfloat16)
     part = torch.empty(ops.decode_gemm_splits(2048, 7168), 64, 2048, device="cuda")
+    from ..ops.decode import pack_weight
+    p_in, p_ug, p_down = pack_weight(w_in), pack_weight(w_ug, swiglu=True), pack_weight(w_down)
     for _ in range(3):
         ops.decode_gemm(w_in, x, 10240, 0, out, flag)
         ops.decode_gemm(w_ug, x, 7168, 2, a, flag)
         ops.decode_gemm(w_down, act, 2048, 1, part, flag)
+        ops.decode_gemm(p_in, x, 10240, 0, out, flag, True)
+        ops.decode_gemm(p_ug, x, 7168, 2, a, flag, True)
+        ops.decode_gemm(p_down, act, 2048, 1, part, flag, True)
     torch.cuda.synchronize()
 
 

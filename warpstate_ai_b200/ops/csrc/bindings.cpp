@@ -499,14 +499,21 @@ int64_t raise_for_status(int64_t code) {
 }
 
 void decode_gemm(const at::Tensor& w, const at::Tensor& x, int64_t n, int64_t epilogue, at::Tensor out,
-                 c10::optional<at::Tensor> error_flag) {
+                 c10::optional<at::Tensor> error_flag, bool packed) {
   TORCH_CHECK(w.is_cuda() && x.is_cuda() && out.is_cuda(), "decode_gemm: CUDA tensors required");
   TORCH_CHECK(w.scalar_type() == at::kBFloat16 && x.scalar_type() == at::kBFloat16 && w.is_contiguous() &&
-              x.is_contiguous() && w.dim() == 2 && x.dim() == 2 && w.size(1) == x.size(1),
-              "decode_gemm: contiguous BF16 W [rows, k] and x [batch, k] required");
+              x.is_contiguous() && x.dim() == 2, "decode_gemm: contiguous BF16 W and x [batch, k] required");
   const int64_t k = x.size(1), batch = x.size(0);
   TORCH_CHECK(batch >= 1 && batch <= 64 && k % 8 == 0, "decode_gemm: batch must be 1..64 and k a multiple of 8");
-  TORCH_CHECK(w.size(0) == (epilogue == 2 ? 2 * n : n), "decode_gemm: W row count does not match n");
+  TORCH_CHECK(epilogue >= 0 && epilogue <= 3 && n > 0, "decode_gemm: epilogue 0..3 and n > 0 required");
+  if (packed) {
+    const int64_t slabs = epilogue == 2 ? n / 64 : (n + 127) / 128;
+    TORCH_CHECK(w.dim() == 4 && w.size(0) == slabs && w.size(1) == (k + 63) / 64 && w.size(2) == 128 && w.size(3) == 64,
+                "decode_gemm: a packed W must be [slabs, ceil(k/64), 128, 64]");
+  } else {
+    TORCH_CHECK(w.dim() == 2 && w.size(1) == k && w.size(0) == (epilogue == 2 ? 2 * n : n),
+                "decode_gemm: W must be [rows, k] with rows matching n");
+  }
   TORCH_CHECK(reinterpret_cast<uintptr_t>(w.data_ptr()) % 16 == 0 && reinterpret_cast<uintptr_t>(x.data_ptr()) % 16 == 0,
               "decode_gemm: 16-byte aligned operands required");
   TORCH_CHECK(out.is_contiguous(), "decode_gemm: contiguous out required");
@@ -519,7 +526,8 @@ void decode_gemm(const at::Tensor& w, const at::Tensor& x, int64_t n, int64_t ep
   }
   c10::cuda::CUDAGuard guard(w.device());
   check_rc(ws_decode_gemm(w.data_ptr(), x.data_ptr(), (int)n, (int)k, (int)batch, (int)epilogue, out.data_ptr(), (int)n,
-                          reinterpret_cast<int*>(const_cast<void*>(opt_ptr(error_flag))), cur_stream()), "decode_gemm");
+                          reinterpret_cast<int*>(const_cast<void*>(opt_ptr(error_flag))), packed ? 1 : 0, cur_stream()),
+           "decode_gemm");
 }
 
 void decode_reduce_norm(at::Tensor x, const c10::optional<at::Tensor>& partial, const c10::optional<at::Tensor>& token,
@@ -591,7 +599,7 @@ void decode_attn(const at::Tensor& qkvgu, at::Tensor kc, at::Tensor vc, at::Tens
 TORCH_LIBRARY(ws_b200, m) {
   m.def("decode_gemm_splits(int n, int k) -> int");
   m.def("raise_for_status(int code) -> int");
-  m.def("decode_gemm(Tensor w, Tensor x, int n, int epilogue, Tensor(a!) out, Tensor(b!)? error_flag) -> ()");
+  m.def("decode_gemm(Tensor w, Tensor x, int n, int epilogue, Tensor(a!) out, Tensor(b!)? error_flag, bool packed=False) -> ()");
   m.def("decode_reduce_norm(Tensor(a!) x, Tensor? partial, Tensor? token, Tensor? table, Tensor? scale, Tensor? bias, "
         "Tensor w, float eps, Tensor(b!)? out) -> ()");
   m.def("decode_attn(Tensor qkvgu, Tensor(a!) kc, Tensor(b!) vc, Tensor(c!) uc, Tensor mixed, Tensor rope, Tensor pos, "

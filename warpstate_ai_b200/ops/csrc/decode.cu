@@ -50,6 +50,7 @@ struct DecodeGemmParams {
   int k;
   int batch;
   int kb_per_split;
+  int packed;   // W is stored tile by tile: [slab][k block][128 rows][64 columns], each tile contiguous
   void* out;    // BF16 [batch, ldo] | FP32 [batch, ldo] | FP32 partial [splits, batch, n]
   int ldo;
   int* error_flag;
@@ -117,6 +118,10 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     if (lane == 0) {
       auto load_w = [&](int s, int kb) {
         mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
+        if (p.packed) {  // one contiguous 16 KiB tile (SwiGLU: the up and gate rows are already paired)
+          tma_load_2d(sW + s * W_BYTES, &tm_w, &full[s], 0, (slab * total_kb + kb) * TM);
+          return;
+        }
         tma_load_2d(sW + s * W_BYTES, &tm_w, &full[s], kb * BK, n0);
         if (EPI == 2)  // 64 up rows + the 64 matching gate rows
           tma_load_2d(sW + s * W_BYTES + 64 * 128, &tm_w, &full[s], kb * BK, p.n + n0);
@@ -477,19 +482,28 @@ extern "C" int ws_decode_gemm_splits(int n, int k) {
 // epilogue: 0 BF16 out [batch, ldo]; 1 FP32 split-K partials [splits, batch, n] (splits from
 // ws_decode_gemm_splits); 2 SwiGLU, W is [2n, k] (up rows then gate rows), BF16 out [batch, ldo];
 // 3 FP32 out [batch, ldo].  batch <= 64; k % 8 == 0.
+// packed != 0: W is the tile-by-tile copy [slabs][ceil(k/64)][128][64] (zero padded; for SwiGLU a tile
+// holds 64 up rows followed by their 64 gate rows), so that every TMA load reads 16 contiguous KiB
+// instead of 128 row pieces of 128 bytes that lie a full weight row apart.
 extern "C" int ws_decode_gemm(const void* w, const void* x, int n, int k, int batch, int epilogue, void* out, int ldo,
-                              int* error_flag, cudaStream_t stream) {
+                              int* error_flag, int packed, cudaStream_t stream) {
   if (n <= 0 || k <= 0 || batch <= 0 || batch > 64 || k % 8 != 0 || epilogue < 0 || epilogue > 3) return -1;
   if (epilogue == 2 && n % 64 != 0) return -2;
   CUtensorMap tw, tx;
   const int w_rows = epilogue == 2 ? 2 * n : n;
-  int rc = make_map_bf16(&tw, w, k, w_rows, k, dec::BK, epilogue == 2 ? 64 : dec::TM);
+  int rc;
+  if (packed) {
+    const uint64_t tiles = (uint64_t)(epilogue == 2 ? n / 64 : (n + dec::TM - 1) / dec::TM) * ((k + dec::BK - 1) / dec::BK);
+    rc = make_map_bf16(&tw, w, dec::BK, tiles * dec::TM, dec::BK, dec::BK, dec::TM);
+  } else {
+    rc = make_map_bf16(&tw, w, k, w_rows, k, dec::BK, epilogue == 2 ? 64 : dec::TM);
+  }
   if (rc) return rc;
   const int bpad = batch <= 16 ? 16 : 64;
   rc = make_map_bf16(&tx, x, k, batch, k, dec::BK, bpad);
   if (rc) return rc;
   DecodeGemmParams p;
-  p.n = n; p.k = k; p.batch = batch; p.out = out; p.ldo = ldo; p.error_flag = error_flag;
+  p.n = n; p.k = k; p.batch = batch; p.packed = packed; p.out = out; p.ldo = ldo; p.error_flag = error_flag;
   const int total_kb = (k + dec::BK - 1) / dec::BK;
   int splits = 1;
   if (epilogue == 1) splits = ws_decode_gemm_splits(n, k);

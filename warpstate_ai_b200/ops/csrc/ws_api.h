@@ -61,7 +61,7 @@ void ws_gemm_set_sm_limit(int sms);
 // (up rows, then gate rows), BF16 [batch, ldo]; 3 FP32 [batch, ldo].
 int ws_decode_gemm_splits(int n, int k);
 int ws_decode_gemm(const void* w, const void* x, int n, int k, int batch, int epilogue, void* out, int ldo,
-                   int* error_flag, cudaStream_t stream);
+                   int* error_flag, int packed, cudaStream_t stream);
 // x (FP32 [batch, d], in place) = table[token] if token else x + sum of split partials; optional
 // depth modulation x*(1+scale)+bias; out (BF16 [batch, d], may be NULL) = RMSNorm(x) * w.
 int ws_decode_reduce_norm(float* x, const float* partial, int splits, const long long* token, const float* table,

@@ -114,11 +114,32 @@ class DecodeEngine:
         from ..ops import _ext
         return _ext.available()
 
+    def _pack_weights(self) -> None:
+        """Tile-contiguous copies of the projection weights for the decode GEMM (made once; depths that
+        share a core share the copy).  The row-major weights stay for prefill."""
+        if getattr(self, "_packed_done", False):
+            return
+        from ..ops.decode import pack_weight
+        cache: dict[int, torch.Tensor] = {}
+
+        def packed(w: torch.Tensor, swiglu: bool = False) -> torch.Tensor:
+            key = w.data_ptr()
+            if key not in cache:
+                cache[key] = pack_weight(w, swiglu)
+            return cache[key]
+
+        for w in self.weights:
+            w["p_in"], w["p_out"] = packed(w["w_in"]), packed(w["w_out"])
+            w["p_ug"], w["p_down"] = packed(w["w_ug"], True), packed(w["w_down"])
+        self.head_packed = packed(self.head)
+        self._packed_done = True
+
     def _kernel_buffers(self, batch: int) -> dict:
         ops = torch.ops.ws_b200
         d, ffn, v = self.cfg.d_model, self.cfg.ffn_hidden, self.cfg.vocab_size
         dev = self.device
         from ..ops import attention, gemm
+        self._pack_weights()
         return dict(
             x=torch.zeros(batch, d, device=dev), n=torch.zeros(batch, d, device=dev, dtype=torch.bfloat16),
             qkvgu=torch.zeros(batch, 5 * d, device=dev, dtype=torch.bfloat16),
@@ -135,18 +156,18 @@ class DecodeEngine:
         first = self.weights[0]
         ops.decode_reduce_norm(k["x"], None, token, self.embed, first["scale"], first["bias"], first["n1"], eps, k["n"])
         for index, (w, st) in enumerate(zip(self.weights, self.states)):
-            ops.decode_gemm(w["w_in"], k["n"], 5 * d, 0, k["qkvgu"], k["flag"])
+            ops.decode_gemm(w["p_in"], k["n"], 5 * d, 0, k["qkvgu"], k["flag"], True)
             ops.decode_attn(k["qkvgu"], st.k, st.v, st.u, st.mixed, k["rope"], pos, self.h, k["y"])
-            ops.decode_gemm(w["w_out"], k["y"], d, 1, k["p_out"], k["flag"])
+            ops.decode_gemm(w["p_out"], k["y"], d, 1, k["p_out"], k["flag"], True)
             ops.decode_reduce_norm(k["x"], k["p_out"], None, None, None, None, w["n2"], eps, k["n"])
-            ops.decode_gemm(w["w_ug"], k["n"], ffn, 2, k["act"], k["flag"])
-            ops.decode_gemm(w["w_down"], k["act"], d, 1, k["p_down"], k["flag"])
+            ops.decode_gemm(w["p_ug"], k["n"], ffn, 2, k["act"], k["flag"], True)
+            ops.decode_gemm(w["p_down"], k["act"], d, 1, k["p_down"], k["flag"], True)
             if index + 1 < len(self.weights):
                 nxt = self.weights[index + 1]
                 ops.decode_reduce_norm(k["x"], k["p_down"], None, None, nxt["scale"], nxt["bias"], nxt["n1"], eps, k["n"])
             else:
                 ops.decode_reduce_norm(k["x"], k["p_down"], None, None, None, None, self.final_norm, eps, k["n"])
-        ops.decode_gemm(self.head, k["n"], self.cfg.vocab_size, 3, k["logits"], k["flag"])
+        ops.decode_gemm(self.head_packed, k["n"], self.cfg.vocab_size, 3, k["logits"], k["flag"], True)
         return k["logits"]
 
     def _step_fn(self, token: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
