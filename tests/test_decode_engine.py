@@ -192,6 +192,11 @@ def test_kernel_decode_path_matches_pytorch_path():
         if t % 37 == 0 or t == 199:
             assert torch.allclose(a, b, rtol=0.05, atol=0.05), t
     assert fast._kbufs is not None and slow._kbufs is None
+    # the engine on tile-contiguous weight copies produces the same logits bit for bit
+    packed = DecodeEngine(model, dtype=torch.bfloat16, pack_weights=True)
+    plain = DecodeEngine(model, dtype=torch.bfloat16, use_cuda_graph=False)
+    for t in range(5):
+        assert torch.equal(packed.step(ids[:, t]), plain.step(ids[:, t])), t
 
 
 def test_pack_weight_round_trip_and_tile_order():

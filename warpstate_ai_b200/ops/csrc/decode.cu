@@ -126,16 +126,26 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         if (EPI == 2)  // 64 up rows + the 64 matching gate rows
           tma_load_2d(sW + s * W_BYTES + 64 * 128, &tm_w, &full[s], kb * BK, p.n + n0);
       };
+      // Every CTA walks its k blocks from a different starting block (wrapping around): all CTAs of a
+      // launch read the same activation tiles, and in lock step they would queue on the few L2
+      // slices that hold the current one.
+      const int nkb = kb1 - kb0;
+      const int rot = nkb > 0 ? static_cast<int>((blockIdx.x * 5u + blockIdx.y * 3u) % static_cast<unsigned>(nkb)) : 0;
+      auto block_of = [&](int it) {
+        const int r = it + rot;
+        return kb0 + (r >= nkb ? r - nkb : r);
+      };
       // The weights are constant during a step: the first ring of weight tiles is requested before
       // the wait for the previous kernel, whose output is this kernel's activation block.
-      const int pre = min(kb1 - kb0, Cfg::STAGES);
-      for (int it = 0; it < pre; ++it) load_w(it, kb0 + it);
+      const int pre = min(nkb, Cfg::STAGES);
+      for (int it = 0; it < pre; ++it) load_w(it, block_of(it));
       pdl_wait();
-      for (int it = 0; it < pre; ++it) tma_load_2d(sX + it * Cfg::X_BYTES, &tm_x, &full[it], (kb0 + it) * BK, 0);
-      for (int kb = kb0 + pre, it = pre; kb < kb1; ++kb, ++it) {
+      for (int it = 0; it < pre; ++it) tma_load_2d(sX + it * Cfg::X_BYTES, &tm_x, &full[it], block_of(it) * BK, 0);
+      for (int it = pre; it < nkb; ++it) {
         const int s = it % Cfg::STAGES;
         const uint32_t ph = (it / Cfg::STAGES) & 1;
         if (!mbar_wait(&empty[s], ph ^ 1, abort_flag)) break;
+        const int kb = block_of(it);
         load_w(s, kb);
         tma_load_2d(sX + s * Cfg::X_BYTES, &tm_x, &full[s], kb * BK, 0);
       }

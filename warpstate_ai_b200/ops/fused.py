@@ -151,6 +151,21 @@ def _attention_backward(dy: torch.Tensor, qkvgu: torch.Tensor, saved, core, batc
     return grads[0].reshape(batch * seq, -1).contiguous(), grads[1], grads[2], grads[3]
 
 
+_SIDE_STREAMS: dict = {}
+
+
+def _side_stream(device: torch.device):
+    """The per-device second stream for small bandwidth-bound kernels that overlap a GEMM
+    (``WARPSTATE_SIDE_STREAM=0`` keeps everything on one stream)."""
+    if device.type != "cuda" or os.environ.get("WARPSTATE_SIDE_STREAM", "1") == "0":
+        return None
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    stream = _SIDE_STREAMS.get(key)
+    if stream is None:
+        stream = _SIDE_STREAMS[key] = torch.cuda.Stream(device=device)
+    return stream
+
+
 # --------------------------------------------------------------------------- one core
 class CoreFn(torch.autograd.Function):
     @staticmethod
@@ -205,14 +220,27 @@ class CoreFn(torch.autograd.Function):
         del dy
         dz1 = G.grad_input(dqkvgu, bf16_weight(w_in))
         dx_in, _, g_n1 = ops.rmsnorm_bwd(dz1, xmod, rstd1, n1w.detach().float(), dx2, scale if ctx.has_mod else None, False)
+        g_scale = g_bias = None
+        side = _side_stream(dx_in.device) if ctx.has_mod else None
+        if ctx.has_mod:
+            # d bias = colsum(d x_mod), d scale = colsum(d x_mod * x_in), with d x_mod = dx_in / (1+scale).
+            # Bandwidth-bound and independent of the weight gradients: it runs on a second stream under
+            # the grouped dW launch below, whose CTAs leave room for it on every SM.
+            if side is not None:
+                main = torch.cuda.current_stream(dx_in.device)
+                side.wait_stream(main)
+                with torch.cuda.stream(side):
+                    g_bias, g_scale = ops.colsum2(dx_in, x_in, scale)
+                for t in (g_bias, g_scale, dx_in, x_in, scale):
+                    t.record_stream(side)
+            else:
+                g_bias, g_scale = ops.colsum2(dx_in, x_in, scale)
         # ---- the four weight gradients, deferred to one grouped launch (their tiles share waves)
         g_down, g_ug, g_out, g_in = _wgrad_group([(dx3b, act, w_down), (dpacked, z2, w_ug), (dx2b, y, w_out),
                                                   (dqkvgu, z1, w_in)])
         del dpacked, dqkvgu
-        g_scale = g_bias = None
-        if ctx.has_mod:
-            # d bias = colsum(d x_mod), d scale = colsum(d x_mod * x_in), with d x_mod = dx_in / (1+scale)
-            g_bias, g_scale = ops.colsum2(dx_in, x_in, scale)
+        if side is not None:
+            torch.cuda.current_stream(dx_in.device).wait_stream(side)
         if ctx.notify and _core_grad_hook is not None:
             _attach_small_grads(core, g_n1, g_n2, g_fast, g_slow, g_mix)
             _core_grad_hook(core)
