@@ -152,3 +152,13 @@ def test_tuner_pairing_policy_and_loader(tmp_path):
     assert G._policy_key(False, False, 16384, 10240, 2048) == policy["entries"][0]["key"]
     G._policy.clear()
     assert TG.main(["--list-cases", "--output-dir", str(tmp_path / "x")]) == 0
+
+
+def test_profile_step_idle_gap_arithmetic():
+    """Interval union: overlapping kernels count once, gaps are reported longest first."""
+    from warpstate_ai_b200.bench.profile_step import idle_gaps
+    out = idle_gaps([(0.0, 10.0, "a"), (5.0, 20.0, "b"), (30.0, 40.0, "c"), (41.0, 42.0, "d"), (12.0, 15.0, "e")])
+    assert abs(out["span_ms"] - 0.042) < 1e-9 and abs(out["busy_ms"] - 0.031) < 1e-9 and abs(out["idle_ms"] - 0.011) < 1e-9
+    assert out["n_gaps"] == 2 and out["gaps"][0]["idle_us"] == 10.0
+    assert out["gaps"][0]["after"] == "b" and out["gaps"][0]["before"] == "c"
+    assert idle_gaps([])["idle_ms"] == 0.0

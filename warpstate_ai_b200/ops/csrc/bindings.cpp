@@ -239,18 +239,15 @@ void embed_bwd(const at::Tensor& dx, const at::Tensor& ids, at::Tensor grad_tabl
   c10::cuda::CUDAGuard guard(dx.device());
   const int rows = (int)dx.size(0), d = (int)dx.size(1);
   at::Tensor flat = ids.reshape({-1});
-  auto sorted = flat.sort();
+  auto sorted = flat.sort(/*stable=*/true, /*dim=*/0, /*descending=*/false);
   at::Tensor sorted_ids = std::get<0>(sorted).contiguous();
   at::Tensor order = std::get<1>(sorted).contiguous();
-  // first position of each run of equal ids
-  at::Tensor is_start = at::ones({rows}, flat.options().dtype(at::kBool));
-  if (rows > 1) is_start.slice(0, 1).copy_(sorted_ids.slice(0, 1).ne(sorted_ids.slice(0, 0, rows - 1)));
-  at::Tensor seg_start = is_start.nonzero().reshape({-1}).to(at::kInt).contiguous();
-  const int n_seg = (int)seg_start.numel();
+  TORCH_CHECK(grad_table.dim() == 2 && grad_table.size(1) == d && flat.numel() == rows, "embed_bwd: shapes");
+  // the runs of equal ids are found by the kernel: no host-side count, no device-to-host read
   check_rc(ws_embed_bwd(dx.data_ptr(), dx.scalar_type() == at::kBFloat16,
                         reinterpret_cast<const long long*>(sorted_ids.data_ptr<int64_t>()),
-                        reinterpret_cast<const long long*>(order.data_ptr<int64_t>()), seg_start.data_ptr<int>(),
-                        n_seg, rows, d, grad_table.data_ptr<float>(), cur_stream()), "embed_bwd");
+                        reinterpret_cast<const long long*>(order.data_ptr<int64_t>()), rows, d,
+                        (int)grad_table.size(0), grad_table.data_ptr<float>(), cur_stream()), "embed_bwd");
 }
 
 // ----------------------------------------------------------------------------- attention / memory

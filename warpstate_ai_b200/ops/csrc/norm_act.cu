@@ -275,17 +275,21 @@ embed_fwd_kernel(const long long* __restrict__ ids, const TT* __restrict__ table
 // Deterministic embedding backward: rows were sorted by token id on the host side of the op
 // (`order` = argsort of ids, `seg_start` = first position of each distinct id in that order).
 // One warp adds all gradient rows of one distinct token in order and accumulates into the
-// FP32 gradient table - no atomics, run-to-run identical.
+// FP32 gradient table - no atomics, run-to-run identical.  The runs of equal ids are found on the
+// device: a warp looks at position p of the sorted ids and works only if a run starts there, so the
+// host needs no count of distinct tokens (which would cost a device-to-host read, and with it a
+// drained launch queue, in every micro-batch).
 template <typename T>
 __global__ void __launch_bounds__(ROW_THREADS)
 embed_bwd_kernel(const T* __restrict__ dx, const long long* __restrict__ sorted_ids,
-                 const long long* __restrict__ order, const int* __restrict__ seg_start, int n_seg,
-                 int rows, int d, float* __restrict__ grad_table) {
+                 const long long* __restrict__ order, int rows, int d, int vocab, float* __restrict__ grad_table) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int seg = blockIdx.x * ROW_WARPS + warp; seg < n_seg; seg += gridDim.x * ROW_WARPS) {
-    const int begin = seg_start[seg];
-    const int end = (seg + 1 < n_seg) ? seg_start[seg + 1] : rows;
+  for (int begin = blockIdx.x * ROW_WARPS + warp; begin < rows; begin += gridDim.x * ROW_WARPS) {
     const long long id = sorted_ids[begin];
+    if (begin > 0 && sorted_ids[begin - 1] == id) continue;  // not the head of a run
+    if (id < 0 || id >= vocab) continue;
+    int end = begin + 1;
+    while (end < rows && sorted_ids[end] == id) ++end;
     float* dst = grad_table + static_cast<size_t>(id) * d;
     for (int c = lane * 4; c < d; c += 128) {
       float4 s = ld4(dst + c);
@@ -404,17 +408,16 @@ extern "C" int ws_embed_fwd(const long long* ids, const void* table, int table_b
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
-extern "C" int ws_embed_bwd(const void* dx, int dx_bf16, const long long* sorted_ids, const long long* order,
-                            const int* seg_start, int n_seg, int rows, int d, float* grad_table,
-                            cudaStream_t stream) {
-  if (d % 4 != 0 || rows <= 0 || n_seg <= 0) return -1;
-  const int grid = row_grid(n_seg);
+extern "C" int ws_embed_bwd(const void* dx, int dx_bf16, const long long* sorted_ids, const long long* order, int rows,
+                            int d, int vocab, float* grad_table, cudaStream_t stream) {
+  if (d % 4 != 0 || rows <= 0 || vocab <= 0) return -1;
+  const int grid = row_grid(rows);
   if (dx_bf16)
-    embed_bwd_kernel<__nv_bfloat16><<<grid, ROW_THREADS, 0, stream>>>(
-        (const __nv_bfloat16*)dx, sorted_ids, order, seg_start, n_seg, rows, d, grad_table);
+    embed_bwd_kernel<__nv_bfloat16><<<grid, ROW_THREADS, 0, stream>>>((const __nv_bfloat16*)dx, sorted_ids, order, rows,
+                                                                      d, vocab, grad_table);
   else
-    embed_bwd_kernel<float><<<grid, ROW_THREADS, 0, stream>>>((const float*)dx, sorted_ids, order,
-                                                              seg_start, n_seg, rows, d, grad_table);
+    embed_bwd_kernel<float><<<grid, ROW_THREADS, 0, stream>>>((const float*)dx, sorted_ids, order, rows, d, vocab,
+                                                              grad_table);
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

@@ -102,9 +102,8 @@ int ws_colsum_finalize(const float* partial, int parts, int d, const float* inv_
 int ws_cast_f32_bf16(const float* in, void* out, size_t n, cudaStream_t stream);
 int ws_embed_fwd(const long long* ids, const void* table, int table_bf16, int rows, int d, int vocab,
                  void* out, int out_bf16, cudaStream_t stream);
-int ws_embed_bwd(const void* dx, int dx_bf16, const long long* sorted_ids, const long long* order,
-                 const int* seg_start, int n_seg, int rows, int d, float* grad_table,
-                 cudaStream_t stream);
+int ws_embed_bwd(const void* dx, int dx_bf16, const long long* sorted_ids, const long long* order, int rows,
+                 int d, int vocab, float* grad_table, cudaStream_t stream);
 
 // ----------------------------------------------------------------------------- attention / memory
 // qkvgu: BF16 [B*T, 5d] (Q,K,V,gate,U); chunk 128, head_dim 64, d = H*64.  rope: float2 [128][32].
