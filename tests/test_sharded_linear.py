@@ -1,0 +1,129 @@
+"""Fused all-gather + FP32->BF16 cast + GEMM over a row-sharded weight (`parallel/sharded_linear.py`).
+
+* CPU: shard sizing.
+* One GPU: the kernel with 1, 3, 4 and 8 emulated shards (all on the device) against a plain
+  PyTorch FP32 product of the BF16-rounded operands; the landing buffer must equal the BF16 cast of
+  the weight bit for bit, and the cached second call (ordinary GEMM on the landing buffer) must
+  equal the fused call bit for bit.  A wait that cannot be satisfied (a flag nobody sets) is not
+  constructible here without a missing peer, so the time-out path is covered by the 2-GPU grad-sync test.
+* Two GPUs (child processes, file-store rendezvous): real peer shards in symmetric memory.
+"""
+import json
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+from warpstate_ai_b200.parallel.sharded_linear import rows_per_shard
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def test_rows_per_shard_covers_and_aligns():
+    for n in (8, 1000, 2048, 10240, 14336, 32768):
+        for world in (1, 2, 3, 4, 8):
+            per = rows_per_shard(n, world)
+            assert per % 8 == 0 and per * world >= n and (per - 8) * world < n + 8 * world
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world", [1, 3, 4, 8])
+def test_fused_gather_cast_gemm_emulated_shards(world):
+    from warpstate_ai_b200.ops import _ext, gemm
+    from warpstate_ai_b200.parallel.sharded_linear import ShardedWeight
+    _ext.require()
+    torch.manual_seed(world)
+    for m, n, k in [(512, 1024, 512), (300, 1000, 256), (4096, 10240, 2048)]:
+        w = torch.randn(n, k, device="cuda") * 0.05
+        x = torch.randn(m, k, device="cuda").bfloat16()
+        sw = ShardedWeight.emulated(w, world)
+        assert torch.equal(sw.full_weight(), w)
+        y = sw.forward(x)
+        assert torch.equal(sw.gathered, w.bfloat16()), (m, n, k, "landing buffer")
+        ref = x.float() @ w.bfloat16().float().T
+        rel = float((y.float() - ref).norm() / ref.norm())
+        assert rel < 0.004, (m, n, k, rel)
+        again = sw.forward_cached(x)
+        assert torch.equal(again, y), (m, n, k, "cached GEMM differs from the fused launch")
+        # a changed shard is picked up by the next fused launch
+        sw._keep[world - 1].mul_(2.0)
+        sw.publish()
+        y2 = sw.forward(x)
+        assert torch.equal(sw.gathered, sw.full_weight().bfloat16())
+        assert not torch.equal(y2, y)
+    gemm.check_device_errors()
+
+
+def worker(rank: int, world: int, out_dir: Path) -> None:
+    import torch.distributed as dist
+    from warpstate_ai_b200.ops import _ext, gemm
+    from warpstate_ai_b200.parallel.sharded_linear import ShardedWeight
+    torch.cuda.set_device(rank)
+    device = torch.device("cuda", rank)
+    dist.init_process_group("nccl", init_method=(out_dir / "rendezvous").as_uri(), rank=rank, world_size=world,
+                            device_id=device)
+    _ext.require()
+    report = {}
+    torch.manual_seed(0)                       # the same full weight on every rank
+    n, k, m = 2048, 1024, 1024
+    w = torch.randn(n, k, device=device) * 0.05
+    torch.manual_seed(100 + rank)              # different activations per rank
+    x = torch.randn(m, k, device=device).bfloat16()
+    sw = ShardedWeight.from_full(w, rank, world)
+    y = sw.forward(x)
+    report["landing_equal"] = bool(torch.equal(sw.gathered, w.bfloat16()))
+    ref = x.float() @ w.bfloat16().float().T
+    report["rel"] = float((y.float() - ref).norm() / ref.norm())
+    report["cached_equal"] = bool(torch.equal(sw.forward_cached(x), y))
+    # every rank scales its own shard; after publish() all ranks see all the new rows
+    sw.shard.mul_(1.0 + 0.5 * (rank + 1))
+    sw.publish()
+    y2 = sw.forward(x)
+    per = sw.rows
+    expect = w.clone()
+    for r in range(world):
+        expect[r * per:(r + 1) * per].mul_(1.0 + 0.5 * (r + 1))
+    report["landing_equal_after_update"] = bool(torch.equal(sw.gathered, expect.bfloat16()))
+    ref2 = x.float() @ expect.bfloat16().float().T
+    report["rel_after_update"] = float((y2.float() - ref2).norm() / ref2.norm())
+    gemm.check_device_errors()
+    torch.cuda.synchronize()
+    dist.barrier()
+    (out_dir / f"report-{rank}.json").write_text(json.dumps(report))
+    dist.destroy_process_group()
+
+
+needs_two_gpus = pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2,
+                                    reason="needs two CUDA devices")
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+@needs_two_gpus
+def test_fused_gather_cast_gemm_two_gpus(tmp_path):
+    import os
+    import subprocess
+    env = dict(os.environ)
+    env["PYTHONPATH"] = str(ROOT) + os.pathsep + env.get("PYTHONPATH", "")
+    procs = [subprocess.Popen([sys.executable, __file__, str(rank), "2", str(tmp_path)], env=env,
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for rank in range(2)]
+    outputs = []
+    for p in procs:
+        try:
+            out, _ = p.communicate(timeout=240)
+        except subprocess.TimeoutExpired:
+            for q in procs:
+                q.kill()
+            raise
+        outputs.append(out)
+    for rank, p in enumerate(procs):
+        assert p.returncode == 0, f"rank {rank} failed:\n{outputs[rank][-3000:]}"
+    for rank in range(2):
+        r = json.loads((tmp_path / f"report-{rank}.json").read_text())
+        assert r["landing_equal"] and r["cached_equal"] and r["landing_equal_after_update"], r
+        assert r["rel"] < 0.004 and r["rel_after_update"] < 0.004, r
+
+
+if __name__ == "__main__":
+    worker(int(sys.argv[1]), int(sys.argv[2]), Path(sys.argv[3]))

@@ -57,6 +57,26 @@ __device__ __forceinline__ void pair_tile_coords(int tile, int num_m, int num_n,
   nb = r / gsz;
 }
 
+// The weight-gather variant (GATHER): B is a weight whose FP32 master rows are sharded over the GPUs
+// of a node.  Four extra warps per CTA pull the shards (plain peer loads over NVLink for the rows other
+// ranks own), cast them to BF16 into a local [n, k] buffer and count finished 8-row chunks per
+// 256-row block in a flag word; the TMA producer takes a B tile only once its block is complete.
+// Tiles are walked N-block by N-block, so block j is needed about j * 12 us into the kernel while
+// the whole gather of in_proj takes ~0.1 ms of link time: all-gather, cast and GEMM are one launch and
+// after the first block the transfer hides under the tensor-core work.  Nothing is multicast.
+struct GatherJob {
+  const float* shard[8];   // rank r owns rows [r * rows_per_shard, (r + 1) * rows_per_shard) of W
+  int world;
+  int rows_per_shard;      // a multiple of GATHER_ROWS
+  int n, k;                // k % 8 == 0
+  __nv_bfloat16* dst;      // local BF16 [n, k]
+  unsigned* flags;         // one word per 256-row block, zero at launch
+  unsigned target;         // chunks per complete block
+  unsigned long long wait_ns;
+};
+constexpr int GATHER_ROWS = 8;
+constexpr int GATHER_THREADS = 128;
+
 // Up to MAX_GROUP independent problems of the same kind share one persistent launch: their
 // tiles form one list, so the last partial wave is paid once per group instead of once per
 // problem (the four weight-gradient GEMMs of a layer: 17 waves of 74 pairs separately, 15 grouped).
@@ -100,14 +120,20 @@ __device__ __forceinline__ uint8_t* tile_chunk128(uint8_t* tile, int r, int j) {
 struct PairTile {
   int prob, mb, nb, num_k;
 };
-__device__ __forceinline__ PairTile resolve_tile(const PairGroup& g, int tile, int n_tile) {
+__device__ __forceinline__ PairTile resolve_tile(const PairGroup& g, int tile, int n_tile, bool n_major = false) {
   PairTile t;
   t.prob = 0;
   while (t.prob + 1 < g.count && tile >= g.tile_start[t.prob + 1]) ++t.prob;
   const GemmParams& p = g.p[t.prob];
   const int num_m = (p.m + 2 * pair::BM - 1) / (2 * pair::BM);
   const int num_n = (p.n + n_tile - 1) / n_tile;
-  pair_tile_coords(tile - g.tile_start[t.prob], num_m, num_n, t.mb, t.nb);
+  if (n_major) {  // every M tile of one N block before the next block (weight-gather variant)
+    const int local = tile - g.tile_start[t.prob];
+    t.mb = local % num_m;
+    t.nb = local / num_m;
+  } else {
+    pair_tile_coords(tile - g.tile_start[t.prob], num_m, num_n, t.mb, t.nb);
+  }
   t.num_k = (p.k + pair::BK - 1) / pair::BK;
   return t;
 }
@@ -117,10 +143,11 @@ constexpr int pair_threads() {
   return 64 + 128 * epilogue_groups<EPI>();  // TMA warp, MMA warp, GROUPS x 4 epilogue warps
 }
 
-template <bool A_MN, bool B_MN, int EPI>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads<EPI>(), 1)
-gemm2_kernel(const __grid_constant__ PairGroup g) {
+template <bool A_MN, bool B_MN, int EPI, bool GATHER = false>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads<EPI>() + (GATHER ? GATHER_THREADS : 0), 1)
+gemm2_kernel(const __grid_constant__ PairGroup g, const __grid_constant__ GatherJob gj) {
   using namespace pair;
+  static_assert(!GATHER || (!A_MN && !B_MN && EPI == WS_EPI_BF16), "the gather variant is the NT forward GEMM");
   constexpr int GROUPS = epilogue_groups<EPI>();
   constexpr int STAGES = pair_stages<EPI>();
   constexpr bool STAGED = staged_epilogue<EPI>();
@@ -185,13 +212,39 @@ gemm2_kernel(const __grid_constant__ PairGroup g) {
     if (lane == 0) {
       int it = 0;
       bool ok = true;
+      [[maybe_unused]] int ready_nb = -1;
       for (int tile = pair_id; tile < tiles && ok; tile += num_pairs) {
-        const PairTile t = resolve_tile(g, tile, n_tile);
+        const PairTile t = resolve_tile(g, tile, n_tile, GATHER);
         const GemmParams& p = g.p[t.prob];
         const CUtensorMap* tma_a = &g.a[t.prob];
         const CUtensorMap* tma_b = &g.b[t.prob];
         const int nb = t.nb;
         const int m0 = t.mb * 2 * BM + rank * BM;  // this CTA's rows
+        if constexpr (GATHER) {
+          if (nb != ready_nb) {  // the 256 weight rows of this N block must have landed in the local buffer
+            const unsigned* flag = gj.flags + nb;
+            const int last_block_rows = gj.n - nb * BN;
+            const unsigned want = last_block_rows >= BN ? gj.target : static_cast<unsigned>((last_block_rows + GATHER_ROWS - 1) / GATHER_ROWS);
+            unsigned seen;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+            if (seen < want) {
+              const uint64_t t0 = globaltimer_ns();
+              uint32_t spins = 0;
+              while (true) {
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+                if (seen >= want) break;
+                if ((++spins & 63u) == 0 && (*abort_flag || globaltimer_ns() - t0 > gj.wait_ns)) {
+                  *abort_flag = 1;
+                  ok = false;
+                  break;
+                }
+              }
+              if (!ok) break;
+            }
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+            ready_nb = nb;
+          }
+        }
         for (int kb = 0; kb < t.num_k; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -237,7 +290,7 @@ gemm2_kernel(const __grid_constant__ PairGroup g) {
         if (!mbar_wait(&tempty[buf], tph ^ 1, abort_flag)) break;
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        const int num_k = resolve_tile(g, tile, n_tile).num_k;
+        const int num_k = resolve_tile(g, tile, n_tile, GATHER).num_k;
         for (int kb = 0; kb < num_k; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -264,7 +317,7 @@ gemm2_kernel(const __grid_constant__ PairGroup g) {
         }
       }
     }
-  } else {
+  } else if (warp < 2 + 4 * GROUPS) {
     // ------------------------------------------------------------------ epilogue warps (both CTAs)
     const int quarter = warp & 3;
     const int egroup = (warp - 2) >> 2;
@@ -276,7 +329,7 @@ gemm2_kernel(const __grid_constant__ PairGroup g) {
       constexpr int STEPS = (128 / GROUPS) / 32;
       const GemmParams& p = g.p[0];
       for (int tile = pair_id; tile < tiles; tile += num_pairs, ++tcount) {
-        const PairTile t = resolve_tile(g, tile, n_tile);
+        const PairTile t = resolve_tile(g, tile, n_tile, GATHER);
         const int buf_t = tcount & 1;
         const uint32_t tph = (tcount >> 1) & 1;
         if (!mbar_wait(&tfull[buf_t], tph, abort_flag)) break;
@@ -336,7 +389,7 @@ gemm2_kernel(const __grid_constant__ PairGroup g) {
       constexpr int STEPS = (BN / GROUPS) / 32;
       const GemmParams& p = g.p[0];
       auto coords = [&](int tile, int step, int& x, int& y) {
-        const PairTile t = resolve_tile(g, tile, n_tile);
+        const PairTile t = resolve_tile(g, tile, n_tile, GATHER);
         x = t.nb * BN + egroup * (BN / GROUPS) + step * 32;
         y = t.mb * 2 * BM + rank * BM + quarter * 32;
       };
@@ -407,7 +460,7 @@ gemm2_kernel(const __grid_constant__ PairGroup g) {
       constexpr int STEPS = (BN / GROUPS) / 32;
       const GemmParams& p = g.p[0];
       auto coords = [&](int tile, int step, int& x, int& y) {
-        const PairTile t = resolve_tile(g, tile, n_tile);
+        const PairTile t = resolve_tile(g, tile, n_tile, GATHER);
         x = t.nb * BN + egroup * (BN / GROUPS) + step * 32;
         y = t.mb * 2 * BM + rank * BM + quarter * 32;
       };
@@ -492,7 +545,7 @@ gemm2_kernel(const __grid_constant__ PairGroup g) {
       if (lane == 0) tma_store_wait_all();
     } else {
       for (int tile = pair_id; tile < tiles; tile += num_pairs, ++tcount) {
-        const PairTile t = resolve_tile(g, tile, n_tile);
+        const PairTile t = resolve_tile(g, tile, n_tile, GATHER);
         const GemmParams& p = g.p[t.prob];
         const int nb = t.nb;
         const int buf = tcount & 1;
@@ -507,6 +560,41 @@ gemm2_kernel(const __grid_constant__ PairGroup g) {
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster_relaxed(mapa_shared(smem_u32(&tempty[buf]), 0));
+      }
+    }
+  }
+
+  if constexpr (GATHER) {
+    if (warp >= 2 + 4 * GROUPS) {
+      // ---------------------------------------------------------------- weight gather (both CTAs)
+      // Chunk c = rows [8c, 8c + 8) of W; chunk c belongs to CTA c % gridDim.x, so the blocks complete
+      // in the order in which the tile loop needs them.  A thread converts 8 consecutive floats
+      // (two 16-byte loads, local or peer) into one 16-byte BF16 store.
+      const int gt = threadIdx.x - (2 + 4 * GROUPS) * 32;
+      const int vec_per_row = gj.k / 8;
+      const int chunks = (gj.n + GATHER_ROWS - 1) / GATHER_ROWS;
+      for (int c = blockIdx.x; c < chunks; c += gridDim.x) {
+        const int row0 = c * GATHER_ROWS;
+        const int rows = min(GATHER_ROWS, gj.n - row0);
+        const int owner = row0 / gj.rows_per_shard;
+        const float* src = gj.shard[owner] + static_cast<size_t>(row0 - owner * gj.rows_per_shard) * gj.k;
+        __nv_bfloat16* dst = gj.dst + static_cast<size_t>(row0) * gj.k;
+        const int vecs = rows * vec_per_row;  // rows are contiguous in both buffers
+#pragma unroll 4
+        for (int v = gt; v < vecs; v += GATHER_THREADS) {
+          const float4 lo = __ldg(reinterpret_cast<const float4*>(src) + 2 * v);
+          const float4 hi = __ldg(reinterpret_cast<const float4*>(src) + 2 * v + 1);
+          uint4 o;
+          o.x = pack_bf16x2(lo.x, lo.y);
+          o.y = pack_bf16x2(lo.z, lo.w);
+          o.z = pack_bf16x2(hi.x, hi.y);
+          o.w = pack_bf16x2(hi.z, hi.w);
+          reinterpret_cast<uint4*>(dst)[v] = o;
+        }
+        __threadfence();
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+        asm volatile("bar.sync 3, %0;" ::"n"(GATHER_THREADS) : "memory");
+        if (gt == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(gj.flags + row0 / BN) : "memory");
       }
     }
   }
@@ -531,7 +619,20 @@ static int launch_pair(const PairGroup& g, int pairs, cudaStream_t stream) {
       return -20;
     configured = true;
   }
-  kern<<<2 * pairs, pair_threads<EPI>(), pair_smem<EPI>(), stream>>>(g);
+  kern<<<2 * pairs, pair_threads<EPI>(), pair_smem<EPI>(), stream>>>(g, GatherJob{});
+  ws_count_launch();
+  return cudaGetLastError() == cudaSuccess ? 0 : -21;
+}
+
+static int launch_pair_gather(const PairGroup& g, const GatherJob& job, int pairs, cudaStream_t stream) {
+  static bool configured = false;
+  auto kern = gemm2_kernel<false, false, WS_EPI_BF16, true>;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pair_smem<WS_EPI_BF16>()) != cudaSuccess)
+      return -20;
+    configured = true;
+  }
+  kern<<<2 * pairs, pair_threads<WS_EPI_BF16>() + GATHER_THREADS, pair_smem<WS_EPI_BF16>(), stream>>>(g, job);
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
@@ -651,4 +752,50 @@ extern "C" int ws_gemm_pair_group(const WsGemm* items, int count, int sms, cudaS
 
 extern "C" int ws_gemm_pair(const WsGemm* g, int sms, cudaStream_t stream) {
   return ws_gemm_pair_group(g, 1, sms, stream);
+}
+
+// y[m, n] = x[m, k] . W[n, k]^T where W is the row-sharded FP32 master weight of `world` ranks
+// (shards[r] = address, in this process, of rank r's [rows_per_shard, k] FP32 block; peers' blocks are
+// symmetric-memory mappings).  `wb` is this rank's BF16 [n, k] landing buffer, `flags` a device array of
+// ceil(n / 256) words (zeroed here).  The caller guarantees that no rank changes its shard while the
+// kernel runs.  A bounded wait that runs out sets *error_flag to 6 and the launch still terminates.
+extern "C" int ws_gather_gemm(const void* x, int m, int n, int k, const void* const* shards, int world,
+                              int rows_per_shard, void* wb, void* flags, void* out, int ldo, int* error_flag,
+                              float budget_seconds, int sms, cudaStream_t stream) {
+  using namespace ws;
+  if (m <= 0 || n <= 0 || k <= 0 || k % 8 != 0 || world < 1 || world > 8) return -1;
+  if (rows_per_shard <= 0 || rows_per_shard % GATHER_ROWS != 0 || (long long)rows_per_shard * world < n) return -1;
+  if (ldo < n || ldo % 8 != 0) return -1;
+  if (((uintptr_t)x | (uintptr_t)wb | (uintptr_t)out) & 15) return -5;
+  for (int r = 0; r < world; ++r)
+    if (shards[r] == nullptr || ((uintptr_t)shards[r] & 15)) return -5;
+  WsGemm item;
+  memset(&item, 0, sizeof(item));
+  item.a = x; item.b = wb; item.m = m; item.n = n; item.k = k; item.lda = k; item.ldb = k;
+  item.epilogue = WS_EPI_BF16; item.out = out; item.ldo = ldo; item.alpha = 1.f; item.error_flag = error_flag;
+  PairGroup grp;
+  memset(&grp, 0, sizeof(grp));
+  grp.count = 1;
+  int tiles = 0;
+  int rc = fill_problem(&item, grp, 0, &tiles);
+  if (rc) return rc;
+  for (int i = 1; i <= MAX_GROUP; ++i) grp.tile_start[i] = tiles;
+  GatherJob job;
+  memset(&job, 0, sizeof(job));
+  for (int r = 0; r < world; ++r) job.shard[r] = static_cast<const float*>(shards[r]);
+  job.world = world;
+  job.rows_per_shard = rows_per_shard;
+  job.n = n; job.k = k;
+  job.dst = static_cast<__nv_bfloat16*>(wb);
+  job.flags = static_cast<unsigned*>(flags);
+  job.target = pair::BN / GATHER_ROWS;
+  job.wait_ns = static_cast<unsigned long long>((budget_seconds > 0.f ? budget_seconds : 2.0f) * 1e9);
+  const int blocks = (n + pair::BN - 1) / pair::BN;
+  if (cudaMemsetAsync(flags, 0, sizeof(unsigned) * blocks, stream) != cudaSuccess) return -21;
+  // Every CTA must be resident at once (producers wait for chunks that other CTAs gather): the grid never
+  // exceeds one CTA per SM, and with fewer tiles than pairs the spare pairs still take gather chunks.
+  int pairs = (sms > 0 ? sms : 148) / 2;
+  if (pairs < 1) pairs = 1;
+  if (pairs > 74) pairs = 74;
+  return launch_pair_gather(grp, job, pairs, stream);
 }

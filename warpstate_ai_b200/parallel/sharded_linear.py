@@ -1,0 +1,122 @@
+"""Linear layer over a weight whose FP32 master rows are sharded across the GPUs of a node.
+
+`ShardedWeight` keeps rank r's rows ``[r * rows_per_shard, (r + 1) * rows_per_shard)`` of a
+``[n, k]`` FP32 weight in symmetric memory.  `forward(x)` is ONE kernel launch
+(`gemm2_kernel<..., GATHER=true>`, `ops/csrc/gemm2_tcgen05.cu`): four warps of every CTA pull the
+shards -- peer loads over NVLink for the rows other ranks own -- cast them to BF16 into a local
+landing buffer and publish per-256-row-block counters, while the TMA/tcgen05 tile loop of the
+same CTAs consumes each block of weight rows as soon as it is complete.  All-gather, cast and
+GEMM overlap tile by tile; the gathered BF16 weight is left in the landing buffer, so the
+backward pass (dX = dY W, dW = dY^T X) and the remaining micro-batches of the update reuse it
+with the ordinary GEMM kernels.
+
+The reference has no parameter sharding (its only strategy is replicated data parallelism,
+reference run_40b.py:601-603); this is the per-core "gather the weights, cast them, feed the first
+GEMM" step of a ZeRO-3 layout, built so that the gather costs link time only for the first block.
+
+Rules the caller keeps:
+
+* every rank calls `forward` with the same sequence of weights (the kernel itself does not
+  synchronise ranks: it only READS peer memory);
+* no rank writes its shard between `publish()` (a barrier) and the last `forward` of any rank
+  that reads it -- `publish()` is called after the optimizer step that changed the shard.
+
+CPU / single-process use: `world == 1`, or several "ranks" emulated by shards that all live on
+one device (`ShardedWeight.emulated`), which exercises the same kernel and index arithmetic.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ops import gemm as G
+
+
+def rows_per_shard(n: int, world: int) -> int:
+    """Rows each rank owns: ceil(n / world) rounded up to the gather granule of 8 rows."""
+    per = (n + world - 1) // world
+    return (per + 7) // 8 * 8
+
+
+class ShardedWeight:
+    """Row-sharded FP32 weight with a fused gather + cast + GEMM forward."""
+
+    def __init__(self, n: int, k: int, rank: int, world: int, shard: torch.Tensor, shard_ptrs: list[int],
+                 barrier=None):
+        if n % 8 or k % 8:
+            raise ValueError("n and k must be multiples of 8")
+        self.n, self.k, self.rank, self.world = n, k, rank, world
+        self.rows = rows_per_shard(n, world)
+        if shard.dtype != torch.float32 or shard.numel() < self.rows * k:
+            raise ValueError("shard must be FP32 with rows_per_shard * k elements")
+        self.shard = shard                      # this rank's rows (FP32 master)
+        self.shard_ptrs = list(shard_ptrs)
+        self._barrier = barrier
+        device = shard.device
+        self.gathered = torch.empty(n, k, device=device, dtype=torch.bfloat16)   # landing buffer
+        self.flags = torch.zeros((n + 255) // 256, device=device, dtype=torch.int32)
+        self.error_flag = G.error_flag(device)
+        self.gathered_valid = False
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def from_full(cls, weight: torch.Tensor, rank: int, world: int, group=None) -> "ShardedWeight":
+        """Shard a full ``[n, k]`` weight (identical on every rank) into symmetric memory."""
+        from . import symm
+        n, k = weight.shape
+        per = rows_per_shard(n, world)
+        buf = symm.allocate(per * k, torch.float32, weight.device, group)
+        lo, hi = rank * per, min(n, (rank + 1) * per)
+        if hi > lo:
+            buf.tensor[:(hi - lo) * k].copy_(weight[lo:hi].reshape(-1).float())
+        self = cls(n, k, rank, world, buf.tensor, buf.peer_ptrs, barrier=buf.barrier)
+        self._sym = buf
+        self.publish()
+        return self
+
+    @classmethod
+    def emulated(cls, weight: torch.Tensor, world: int) -> "ShardedWeight":
+        """All ``world`` shards on one device: the kernel and its index arithmetic without peers."""
+        n, k = weight.shape
+        per = rows_per_shard(n, world)
+        shards = []
+        for r in range(world):
+            t = torch.zeros(per * k, device=weight.device, dtype=torch.float32)
+            lo, hi = r * per, min(n, (r + 1) * per)
+            if hi > lo:
+                t[:(hi - lo) * k].copy_(weight[lo:hi].reshape(-1).float())
+            shards.append(t)
+        self = cls(n, k, 0, world, shards[0], [t.data_ptr() for t in shards])
+        self._keep = shards
+        return self
+
+    # ------------------------------------------------------------------ use
+    def publish(self) -> None:
+        """Make this rank's shard visible to the peers' next `forward` (device barrier over the node)
+        and mark the landing buffer stale."""
+        self.gathered_valid = False
+        if self._barrier is not None:
+            torch.cuda.current_stream(self.shard.device).synchronize()
+            self._barrier()
+
+    def forward(self, x: torch.Tensor, budget_seconds: float = 2.0) -> torch.Tensor:
+        """``x [m, k]`` BF16 -> ``x @ W^T [m, n]`` BF16; gathers and casts W in the same launch."""
+        if x.dtype != torch.bfloat16:
+            x = x.to(torch.bfloat16)
+        y = torch.ops.ws_b200.gather_cast_linear(x.contiguous(), self.shard_ptrs, self.n, self.rows, self.gathered,
+                                                 self.flags, self.error_flag, float(budget_seconds))
+        self.gathered_valid = True
+        return y
+
+    def forward_cached(self, x: torch.Tensor) -> torch.Tensor:
+        """Later micro-batches of the same update: the landing buffer already holds the BF16 weight."""
+        if not self.gathered_valid:
+            return self.forward(x)
+        return G.linear(x, self.gathered)
+
+    def full_weight(self) -> torch.Tensor:
+        """The whole FP32 weight, read shard by shard (emulated shards only; for tests)."""
+        keep = getattr(self, "_keep", None)
+        if keep is None:
+            raise RuntimeError("full_weight() needs emulated shards")
+        rows = torch.cat([t.view(self.rows, self.k) for t in keep], dim=0)
+        return rows[:self.n]
