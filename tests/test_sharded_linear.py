@@ -55,6 +55,35 @@ def test_fused_gather_cast_gemm_emulated_shards(world):
     gemm.check_device_errors()
 
 
+@pytest.mark.gpu
+def test_sharded_linear_module_gradients_single_rank():
+    from warpstate_ai_b200.ops import _ext
+    from warpstate_ai_b200.parallel.sharded_linear import ShardedLinear, ShardedWeight
+    _ext.require()
+    torch.manual_seed(5)
+    n, k = 768, 512
+    w = torch.randn(n, k, device="cuda") * 0.05
+    layer = ShardedLinear(ShardedWeight.emulated(w, 1))
+    grads = []
+    for step in range(2):                      # the second micro-batch reuses the landing buffer
+        x = torch.randn(2, 256, k, device="cuda", requires_grad=True)
+        dy = torch.randn(2, 256, n, device="cuda").bfloat16()
+        y = layer(x)
+        y.backward(dy)
+        xr = x.detach().bfloat16().float().requires_grad_(True)
+        wr = w.bfloat16().float().requires_grad_(True)
+        yr = xr @ wr.T
+        yr.backward(dy.float())
+        assert float((y.float() - yr).norm() / yr.norm()) < 0.004
+        assert float((x.grad - xr.grad).norm() / xr.grad.norm()) < 0.006
+        grads.append(wr.grad)
+    total = grads[0] + grads[1]
+    assert float((layer.weight.shard_grad.view(-1, k)[:n] - total).norm() / total.norm()) < 0.004
+    assert layer.weight.gathered_valid
+    layer.publish()
+    assert not layer.weight.gathered_valid
+
+
 def worker(rank: int, world: int, out_dir: Path) -> None:
     import torch.distributed as dist
     from warpstate_ai_b200.ops import _ext, gemm
@@ -87,6 +116,20 @@ def worker(rank: int, world: int, out_dir: Path) -> None:
     report["landing_equal_after_update"] = bool(torch.equal(sw.gathered, expect.bfloat16()))
     ref2 = x.float() @ expect.bfloat16().float().T
     report["rel_after_update"] = float((y2.float() - ref2).norm() / ref2.norm())
+    # module: dW rows of every owner are the sum over ranks
+    from warpstate_ai_b200.parallel.sharded_linear import ShardedLinear
+    layer = ShardedLinear(sw)
+    xg = x.float().requires_grad_(True)
+    torch.manual_seed(200 + rank)
+    dy = torch.randn(m, n, device=device).bfloat16()
+    layer(xg).backward(dy)
+    dw_local = dy.float().T @ x.float()        # this rank's contribution, all rows
+    dist.all_reduce(dw_local)
+    mine = dw_local[rank * per:(rank + 1) * per]
+    got = sw.shard_grad.view(per, k)[:mine.shape[0]]
+    report["dw_rel"] = float((got - mine).norm() / mine.norm())
+    dxr = dy.float() @ expect.bfloat16().float()
+    report["dx_rel"] = float((xg.grad - dxr).norm() / dxr.norm())
     gemm.check_device_errors()
     torch.cuda.synchronize()
     dist.barrier()
@@ -123,6 +166,7 @@ def test_fused_gather_cast_gemm_two_gpus(tmp_path):
         r = json.loads((tmp_path / f"report-{rank}.json").read_text())
         assert r["landing_equal"] and r["cached_equal"] and r["landing_equal_after_update"], r
         assert r["rel"] < 0.004 and r["rel_after_update"] < 0.004, r
+        assert r["dw_rel"] < 0.004 and r["dx_rel"] < 0.006, r
 
 
 if __name__ == "__main__":

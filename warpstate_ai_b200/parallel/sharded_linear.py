@@ -56,6 +56,7 @@ class ShardedWeight:
         self.flags = torch.zeros((n + 255) // 256, device=device, dtype=torch.int32)
         self.error_flag = G.error_flag(device)
         self.gathered_valid = False
+        self.shard_grad = None                  # FP32 gradient of this rank's rows (set by ShardedLinear)
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -120,3 +121,64 @@ class ShardedWeight:
             raise RuntimeError("full_weight() needs emulated shards")
         rows = torch.cat([t.view(self.rows, self.k) for t in keep], dim=0)
         return rows[:self.n]
+
+
+class _ShardedLinearFn(torch.autograd.Function):
+    """y = x W^T over a `ShardedWeight`; dX from the gathered BF16 weight, dW reduce-scattered to its owners."""
+
+    @staticmethod
+    def forward(ctx, x, anchor, sw: ShardedWeight, fresh: bool, group):
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        x2 = x2 if x2.dtype == torch.bfloat16 else x2.to(torch.bfloat16)
+        x2 = x2.contiguous()
+        y = sw.forward(x2) if fresh else sw.forward_cached(x2)
+        ctx.sw, ctx.group, ctx.shape, ctx.x_dtype = sw, group, shape, x.dtype
+        ctx.save_for_backward(x2)
+        return y.view(*shape[:-1], sw.n)
+
+    @staticmethod
+    def backward(ctx, dy):
+        import torch.distributed as dist
+        sw: ShardedWeight = ctx.sw
+        (x2,) = ctx.saved_tensors
+        dy2 = dy.reshape(-1, sw.n)
+        dy2 = (dy2 if dy2.dtype == torch.bfloat16 else dy2.to(torch.bfloat16)).contiguous()
+        dx = G.grad_input(dy2, sw.gathered).view(ctx.shape).to(ctx.x_dtype)
+        # full dW in FP32 (rows padded to world * rows_per_shard), then each owner keeps the sum of its rows
+        full = torch.zeros(sw.rows * sw.world, sw.k, device=dy2.device, dtype=torch.float32)
+        G.grad_weight_accumulate(dy2, x2, full[:sw.n])
+        if sw.world > 1 and dist.is_initialized():
+            mine = torch.empty(sw.rows, sw.k, device=dy2.device, dtype=torch.float32)
+            dist.reduce_scatter_tensor(mine, full, group=ctx.group)
+        else:
+            mine = full[:sw.rows]
+        if sw.shard_grad is None:
+            sw.shard_grad = mine.clone() if mine.data_ptr() == full.data_ptr() else mine
+        else:
+            sw.shard_grad += mine
+        return dx, None, None, None, None
+
+
+class ShardedLinear(torch.nn.Module):
+    """A bias-free linear layer whose FP32 weight rows live sharded across the ranks of a node.
+
+    ``forward(x)`` runs the fused gather + cast + GEMM the first time after `publish()` and the
+    plain GEMM on the landing buffer afterwards; the weight gradient of this rank's rows is summed
+    over ranks into ``weight.shard_grad`` (FP32, ``[rows_per_shard, k]``).  After the owner has
+    updated ``weight.shard`` it calls ``publish()``.
+    """
+
+    def __init__(self, weight: ShardedWeight, group=None):
+        super().__init__()
+        self.weight = weight
+        self.group = group
+        weight.shard_grad = None
+        # autograd needs one differentiable input even when x comes from a frozen producer
+        self._anchor = torch.nn.Parameter(torch.zeros((), device=weight.shard.device))
+
+    def publish(self) -> None:
+        self.weight.publish()
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return _ShardedLinearFn.apply(x, self._anchor, self.weight, not self.weight.gathered_valid, self.group)
