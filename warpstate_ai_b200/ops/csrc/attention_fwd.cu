@@ -153,13 +153,17 @@ memory_scan_kernel(const float* __restrict__ writes, const float* __restrict__ f
 }
 
 // =============================================================================== attention
-// smem: sQ 16K | sK 16K | sV 16K | sSt 8K | sP 32K | sG 16K | bars
-// The gate tile arrives by TMA with the other operands and the blended output leaves by TMA
-// (staged in sQ, one 32-row store per warp): a thread that owns a token row would otherwise
-// touch one 16-byte piece of 32 different cache lines per warp instruction.
-constexpr int AF_SMEM = 3 * TILE_BYTES + 8192 + 2 * TILE_BYTES + TILE_BYTES + 1024 + 128;
+// smem: sQ 16K | sK 16K | sX 16K | sV 16K | sSt 8K | bars  (73 KiB: three CTAs per SM)
+// The gate tile arrives by TMA with the other operands (into sX; every thread moves its gate row to
+// registers before the softmax) and the blended output leaves by TMA (staged in sQ, one 32-row
+// store per warp): a thread that owns a token row would otherwise touch one 16-byte piece of 32
+// different cache lines per warp instruction.  P (128 x 128 BF16) overlays sK | sX once S = Q K^T
+// is complete.  TMEM: 128 columns; S occupies all of them, and after the softmax has read S, O takes
+// columns 0-63 and Mem = Q State columns 64-127, so three CTAs fit the 512 columns of an SM too.
+// The kernel is bound by the latency of its dependent chain, so tiles in flight are what counts.
+constexpr int AF_SMEM = 4 * TILE_BYTES + 8192 + 1024 + 128;
 
-__global__ void __launch_bounds__(128, 2)
+__global__ void __launch_bounds__(128, 3)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_constant__ CUtensorMap tm_state,
                 const __grid_constant__ CUtensorMap tm_y, const float2* __restrict__ rope, int T, int H, int d,
                 int* error_flag) {
@@ -167,11 +171,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_const
   uint8_t* smem = align1024(smem_raw);
   uint8_t* sQ = smem;
   uint8_t* sK = smem + TILE_BYTES;
-  uint8_t* sV = smem + 2 * TILE_BYTES;
-  uint8_t* sSt = smem + 3 * TILE_BYTES;
-  uint8_t* sP = smem + 3 * TILE_BYTES + 8192;
-  uint8_t* sG = sP + 2 * TILE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sG + TILE_BYTES);
+  uint8_t* sG = smem + 2 * TILE_BYTES;   // gate tile, later the second half of P
+  uint8_t* sV = smem + 3 * TILE_BYTES;
+  uint8_t* sSt = smem + 4 * TILE_BYTES;
+  uint8_t* sP = sK;                      // P overlays K | gate
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sSt + 8192);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const int tid = threadIdx.x, warp = tid >> 5;
@@ -188,14 +192,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_const
     mbar_fence_init();
   }
   if (warp == 0) {
-    tmem_alloc(tmem_slot, 256);
+    tmem_alloc(tmem_slot, 128);
     tmem_relinquish();
   }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t t_s = tmem, t_o = tmem + 128, t_m = tmem + 192;
+  const uint32_t t_s = tmem, t_o = tmem, t_m = tmem + 64;  // O and Mem reuse S's columns after the softmax
   const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
 
   if (tid == 0) {
@@ -207,6 +211,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_const
     tma_load_2d(sSt, &tm_state, &bars[0], 0, tile * HD);
   }
   bool ok = mbar_wait(&bars[0], 0, abort_flag);
+  uint4 gate_row[8];  // this thread's gate row: the tile's space becomes half of P
+#pragma unroll
+  for (int j = 0; j < 8; ++j) gate_row[j] = *reinterpret_cast<const uint4*>(tile_chunk(sG, tid, j));
   if (ok) {
     rope_tanh_row(sQ, tid, rope, true, false);
     rope_tanh_row(sK, tid, rope, true, false);
@@ -215,15 +222,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_const
   __syncthreads();
   if (tid == 0 && ok) {
     constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
-    constexpr uint32_t idesc_m = make_idesc_bf16(128, 64, false, true);
 #pragma unroll
     for (int k = 0; k < HD / 16; ++k)
       umma_bf16(t_s, make_smem_desc_sw128(smem_u32(sQ) + k * 32, 0, 1024),
                 make_smem_desc_sw128(smem_u32(sK) + k * 32, 0, 1024), idesc_s, k > 0);
-#pragma unroll
-    for (int k = 0; k < HD / 16; ++k)
-      umma_bf16(t_m, make_smem_desc_sw128(smem_u32(sQ) + k * 32, 0, 1024),
-                make_smem_desc_sw128(smem_u32(sSt) + k * 2048, 0, 1024), idesc_m, k > 0);
     umma_commit(&bars[1]);
   }
   ok = ok && mbar_wait(&bars[1], 0, abort_flag);
@@ -263,14 +265,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_const
     }
     store_row_chunk32(sP, tid, cc * 32, pk);
   }
+  tc_fence_before_sync();  // every thread's reads of S precede the MMAs that overwrite its columns
   fence_proxy_async_smem();
   __syncthreads();
   if (tid == 0 && ok) {
+    tc_fence_after_sync();
     constexpr uint32_t idesc_o = make_idesc_bf16(128, 64, false, true);
 #pragma unroll
     for (int k = 0; k < CHUNK / 16; ++k)
       umma_bf16(t_o, make_smem_desc_sw128(smem_u32(sP) + (k >> 2) * TILE_BYTES + (k & 3) * 32, 0, 1024),
                 make_smem_desc_sw128(smem_u32(sV) + k * 2048, 0, 1024), idesc_o, k > 0);
+#pragma unroll
+    for (int k = 0; k < HD / 16; ++k)  // Mem = Q State
+      umma_bf16(t_m, make_smem_desc_sw128(smem_u32(sQ) + k * 32, 0, 1024),
+                make_smem_desc_sw128(smem_u32(sSt) + k * 2048, 0, 1024), idesc_o, k > 0);
     umma_commit(&bars[2]);
   }
   ok = ok && mbar_wait(&bars[2], 0, abort_flag);
@@ -287,7 +295,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_const
 #pragma unroll
     for (int j = 0; j < 16; j += 8) {
       const int chunk = (c + j) >> 3;
-      const uint4 gq = *reinterpret_cast<const uint4*>(tile_chunk(sG, tid, chunk));
+      const uint4 gq = gate_row[chunk];
       const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&gq);
       uint4 out;
       uint32_t* ow = reinterpret_cast<uint32_t*>(&out);
@@ -316,7 +324,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_const
   if (tid == 0 && *abort_flag != 0 && error_flag != nullptr) atomicExch(error_flag, 3);
   if (warp == 0) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem, 256);
+    tmem_dealloc(tmem, 128);
   }
 }
 
