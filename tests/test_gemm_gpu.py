@@ -139,3 +139,34 @@ def test_misaligned_row_pitch_is_rejected(g):
     x = torch.zeros(64, 264, device="cuda").bfloat16()
     with pytest.raises(RuntimeError, match="row pitches"):
         g.grad_weight_accumulate(dy, x, torch.zeros(300, 264, device="cuda"))
+
+
+@pytest.mark.gpu
+def test_gemm_from_a_thread_whose_first_cuda_action_is_the_tensor_map():
+    """A tensor-map encode is a driver call that needs a context current on the calling thread.  A fresh
+    thread that only receives already allocated tensors (an autograd worker fed from the caching
+    allocator) has none until the library binds it: the GEMM must work there as well."""
+    import threading
+    from warpstate_ai_b200.ops import gemm as G
+    torch.manual_seed(0)
+    x = torch.randn(512, 256, device="cuda").bfloat16()
+    w = (torch.randn(384, 256, device="cuda") * 0.05).bfloat16()
+    out = torch.empty(512, 384, device="cuda", dtype=torch.bfloat16)
+    G.error_flag(x.device)          # created here, so that the thread allocates nothing
+    torch.cuda.synchronize()
+    result = {}
+
+    def work():
+        try:
+            G.linear(x, w, out=out)
+            torch.cuda.synchronize()
+            result["ok"] = True
+        except Exception as exc:   # reported to the main thread
+            result["error"] = repr(exc)
+
+    t = threading.Thread(target=work)
+    t.start()
+    t.join(60)
+    assert result.get("ok"), result
+    ref = x.float() @ w.float().T
+    assert float((out.float() - ref).norm() / ref.norm()) < 0.004

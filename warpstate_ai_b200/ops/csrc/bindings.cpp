@@ -1,6 +1,6 @@
 // torch.ops.ws_b200.* registrations: argument checking and pointer extraction only; all
 // device work is in the .cu files behind the C ABI of ws_api.h.
-#include <sstream>
+#include <cstdio>
 #include <torch/library.h>
 #include <ATen/ATen.h>
 #include <ATen/cuda/CUDAContext.h>
@@ -92,11 +92,10 @@ void gemm(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool b_mn, int64_
   g.error_flag = reinterpret_cast<int*>(const_cast<void*>(opt_ptr(error_flag)));
   const int rc = ws_gemm(&g, cur_stream());
   if (rc != 0) {  // name the problem: a bare code is of little use for a tensor-map or shape refusal
-    std::ostringstream what;
-    what << "gemm (m=" << m << " n=" << n << " k=" << k << " a_mn=" << a_mn << " b_mn=" << b_mn << " epilogue=" << epilogue
-         << " lda=" << g.lda << " ldb=" << g.ldb << " ldo=" << g.ldo << " a%1024=" << (reinterpret_cast<uintptr_t>(g.a) & 1023)
-         << " b%1024=" << (reinterpret_cast<uintptr_t>(g.b) & 1023) << " a=" << g.a << " b=" << g.b << ")";
-    check_rc(rc, what.str().c_str());
+    char what[256];
+    snprintf(what, sizeof(what), "gemm (m=%lld n=%lld k=%lld a_mn=%d b_mn=%d epilogue=%lld lda=%d ldb=%d ldo=%d)",
+             (long long)m, (long long)n, (long long)k, (int)a_mn, (int)b_mn, (long long)epilogue, g.lda, g.ldb, g.ldo);
+    check_rc(rc, what);
   }
 }
 

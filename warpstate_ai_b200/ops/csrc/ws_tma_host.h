@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 #include <mutex>
 #include <stdint.h>
+#include <stdio.h>
 
 namespace ws {
 
@@ -13,7 +14,20 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+// cuTensorMapEncodeTiled is a driver call and wants a context current on the calling thread; the
+// runtime binds the primary context lazily, on a thread's first runtime call that needs one.  A thread
+// whose first CUDA action is building a tensor map (an autograd worker whose tensors all came out of
+// the caching allocator) otherwise gets CUDA_ERROR_INVALID_CONTEXT.  Once per thread.
+inline void ensure_context_on_this_thread() {
+  static thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
+}
+
 inline EncodeTiledFn get_encode_fn() {
+  ensure_context_on_this_thread();
   static EncodeTiledFn fn = nullptr;
   static std::once_flag once;
   std::call_once(once, [] {
@@ -50,6 +64,10 @@ inline int make_map_bf16_swz(CUtensorMap* map, const void* base, uint64_t inner,
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)  // say what was refused: the bare code cannot be traced back to an operand
+    fprintf(stderr, "ws_b200: tensor-map encode refused (CUresult %d): map %p base %p dims %llu x %llu pitch %llu B box %u x %u swizzle %d\n",
+            (int)r, (void*)map, base, (unsigned long long)inner, (unsigned long long)outer, (unsigned long long)(ld * 2),
+            box_inner, box_outer, (int)swizzle);
   return r == CUDA_SUCCESS ? 0 : -12;
 }
 
