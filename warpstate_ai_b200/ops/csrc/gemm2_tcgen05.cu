@@ -67,14 +67,14 @@ __device__ __forceinline__ void pair_tile_coords(int tile, int num_m, int num_n,
 struct GatherJob {
   const float* shard[8];   // rank r owns rows [r * rows_per_shard, (r + 1) * rows_per_shard) of W
   int world;
-  int rows_per_shard;      // a multiple of GATHER_ROWS
+  int rows_per_shard;      // a multiple of 8 (so a chunk never straddles two shards)
   int n, k;                // k % 8 == 0
   __nv_bfloat16* dst;      // local BF16 [n, k]
   unsigned* flags;         // one word per 256-row block, zero at launch
   unsigned target;         // chunks per complete block
   unsigned long long wait_ns;
 };
-constexpr int GATHER_ROWS = 8;
+constexpr int GATHER_ROWS = 2;   // rows per chunk: small, so that the first block is spread over 128 CTAs
 constexpr int GATHER_THREADS = 128;
 
 // Up to MAX_GROUP independent problems of the same kind share one persistent launch: their
@@ -567,7 +567,7 @@ gemm2_kernel(const __grid_constant__ PairGroup g, const __grid_constant__ Gather
   if constexpr (GATHER) {
     if (warp >= 2 + 4 * GROUPS) {
       // ---------------------------------------------------------------- weight gather (both CTAs)
-      // Chunk c = rows [8c, 8c + 8) of W; chunk c belongs to CTA c % gridDim.x, so the blocks complete
+      // Chunk c = GATHER_ROWS rows of W; chunk c belongs to CTA c % gridDim.x, so the blocks complete
       // in the order in which the tile loop needs them.  A thread converts 8 consecutive floats
       // (two 16-byte loads, local or peer) into one 16-byte BF16 store.
       const int gt = threadIdx.x - (2 + 4 * GROUPS) * 32;
@@ -580,16 +580,30 @@ gemm2_kernel(const __grid_constant__ PairGroup g, const __grid_constant__ Gather
         const float* src = gj.shard[owner] + static_cast<size_t>(row0 - owner * gj.rows_per_shard) * gj.k;
         __nv_bfloat16* dst = gj.dst + static_cast<size_t>(row0) * gj.k;
         const int vecs = rows * vec_per_row;  // rows are contiguous in both buffers
-#pragma unroll 4
-        for (int v = gt; v < vecs; v += GATHER_THREADS) {
-          const float4 lo = __ldg(reinterpret_cast<const float4*>(src) + 2 * v);
-          const float4 hi = __ldg(reinterpret_cast<const float4*>(src) + 2 * v + 1);
-          uint4 o;
-          o.x = pack_bf16x2(lo.x, lo.y);
-          o.y = pack_bf16x2(lo.z, lo.w);
-          o.z = pack_bf16x2(hi.x, hi.y);
-          o.w = pack_bf16x2(hi.z, hi.w);
-          reinterpret_cast<uint4*>(dst)[v] = o;
+        // four 32-byte pieces per thread are requested before the first is converted: a peer load takes
+        // a few microseconds, and a chunk is one such round trip
+        for (int v0 = 0; v0 < vecs; v0 += 4 * GATHER_THREADS) {
+          float4 lo[4], hi[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int v = v0 + u * GATHER_THREADS + gt;
+            if (v < vecs) {
+              lo[u] = __ldg(reinterpret_cast<const float4*>(src) + 2 * v);
+              hi[u] = __ldg(reinterpret_cast<const float4*>(src) + 2 * v + 1);
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int v = v0 + u * GATHER_THREADS + gt;
+            if (v < vecs) {
+              uint4 o;
+              o.x = pack_bf16x2(lo[u].x, lo[u].y);
+              o.y = pack_bf16x2(lo[u].z, lo[u].w);
+              o.z = pack_bf16x2(hi[u].x, hi[u].y);
+              o.w = pack_bf16x2(hi[u].z, hi[u].w);
+              reinterpret_cast<uint4*>(dst)[v] = o;
+            }
+          }
         }
         __threadfence();
         asm volatile("fence.proxy.async.global;" ::: "memory");
@@ -764,7 +778,7 @@ extern "C" int ws_gather_gemm(const void* x, int m, int n, int k, const void* co
                               float budget_seconds, int sms, cudaStream_t stream) {
   using namespace ws;
   if (m <= 0 || n <= 0 || k <= 0 || k % 8 != 0 || world < 1 || world > 8) return -1;
-  if (rows_per_shard <= 0 || rows_per_shard % GATHER_ROWS != 0 || (long long)rows_per_shard * world < n) return -1;
+  if (rows_per_shard <= 0 || rows_per_shard % 8 != 0 || (long long)rows_per_shard * world < n) return -1;
   if (ldo < n || ldo % 8 != 0) return -1;
   if (((uintptr_t)x | (uintptr_t)wb | (uintptr_t)out) & 15) return -5;
   for (int r = 0; r < world; ++r)
