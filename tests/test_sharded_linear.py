@@ -56,6 +56,31 @@ def test_fused_gather_cast_gemm_emulated_shards(world):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("world", [1, 4, 8])
+def test_fused_gather_cast_swiglu_gemm_emulated_shards(world):
+    """Up/gate weight [2h, k]: the launch gathers up and gate rows alternately and applies the SwiGLU epilogue."""
+    from warpstate_ai_b200.ops import _ext, gemm
+    from warpstate_ai_b200.parallel.sharded_linear import ShardedWeight
+    _ext.require()
+    torch.manual_seed(10 + world)
+    for m, h, k in [(512, 256, 512), (300, 384, 256), (2048, 7168, 2048)]:
+        w = torch.randn(2 * h, k, device="cuda") * 0.05
+        x = torch.randn(m, k, device="cuda").bfloat16()
+        sw = ShardedWeight.emulated(w, world, swiglu=True)
+        packed, act = sw.forward(x)
+        assert torch.equal(sw.gathered, w.bfloat16()), (m, h, k, "landing buffer")
+        both = x.float() @ w.bfloat16().float().T
+        assert float((packed.float() - both).norm() / both.norm()) < 0.004, (m, h, k)
+        ref = both[:, :h] * torch.nn.functional.silu(both[:, h:])
+        assert float((act.float() - ref).norm() / ref.norm()) < 0.008, (m, h, k)
+        packed2, act2 = sw.forward_cached(x)
+        assert torch.equal(packed2, packed) and torch.equal(act2, act), (m, h, k, "cached GEMM differs")
+    gemm.check_device_errors()
+    with pytest.raises(ValueError):
+        ShardedWeight.emulated(torch.randn(2 * 96, 64, device="cuda"), 1, swiglu=True)
+
+
+@pytest.mark.gpu
 def test_sharded_linear_module_gradients_single_rank():
     from warpstate_ai_b200.ops import _ext
     from warpstate_ai_b200.parallel.sharded_linear import ShardedLinear, ShardedWeight

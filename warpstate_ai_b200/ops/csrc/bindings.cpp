@@ -497,32 +497,45 @@ void adamw_shard_push(at::IntArrayRef master_ptrs, at::IntArrayRef bf16_ptrs, in
 // y = x @ W^T where W [n, k] is FP32 and row-sharded over `shard_ptrs.size()` ranks (addresses as mapped in
 // this process: the local shard and the peers' symmetric-memory shards).  One launch gathers, casts and
 // multiplies; `wb` receives the BF16 copy of the whole weight as a by-product.
-at::Tensor gather_cast_linear(const at::Tensor& x, std::vector<int64_t> shard_ptrs, int64_t n, int64_t rows_per_shard,
-                              at::Tensor wb, at::Tensor flags, c10::optional<at::Tensor> error_flag,
-                              double budget_seconds) {
+std::tuple<at::Tensor, at::Tensor> gather_cast_linear(const at::Tensor& x, std::vector<int64_t> shard_ptrs, int64_t n,
+                                                      int64_t rows_per_shard, at::Tensor wb, at::Tensor flags,
+                                                      c10::optional<at::Tensor> error_flag, double budget_seconds,
+                                                      bool swiglu, bool want_packed) {
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.is_contiguous(),
               "gather_cast_linear: x must be contiguous BF16 [m, k]");
   const int64_t m = x.size(0), k = x.size(1);
   const int64_t world = (int64_t)shard_ptrs.size();
+  const int64_t w_rows = swiglu ? 2 * n : n;
   TORCH_CHECK(world >= 1 && world <= 8, "gather_cast_linear: 1..8 shards");
   TORCH_CHECK(k % 8 == 0 && n > 0 && n % 8 == 0 && rows_per_shard > 0 && rows_per_shard % 8 == 0 &&
-              rows_per_shard * world >= n, "gather_cast_linear: k, n and rows_per_shard must be multiples of 8 and cover n");
-  TORCH_CHECK(wb.is_cuda() && wb.scalar_type() == at::kBFloat16 && wb.is_contiguous() && wb.numel() == n * k,
-              "gather_cast_linear: wb must be contiguous BF16 [n, k]");
-  TORCH_CHECK(flags.is_cuda() && flags.scalar_type() == at::kInt && flags.is_contiguous() && flags.numel() >= (n + 255) / 256,
-              "gather_cast_linear: flags must be int32 [ceil(n/256)]");
+              rows_per_shard * world >= w_rows,
+              "gather_cast_linear: k, n and rows_per_shard must be multiples of 8 and the shards must cover the weight");
+  TORCH_CHECK(!swiglu || n % 128 == 0, "gather_cast_linear: the SwiGLU form needs a hidden width that is a multiple of 128");
+  TORCH_CHECK(wb.is_cuda() && wb.scalar_type() == at::kBFloat16 && wb.is_contiguous() && wb.numel() == w_rows * k,
+              "gather_cast_linear: wb must be contiguous BF16 with the weight's shape");
+  TORCH_CHECK(flags.is_cuda() && flags.scalar_type() == at::kInt && flags.is_contiguous() && flags.numel() >= (w_rows + 127) / 128,
+              "gather_cast_linear: flags must be int32 with one word per 128 weight rows");
   const void* shards[8] = {};
   for (int64_t r = 0; r < world; ++r) {
     TORCH_CHECK(shard_ptrs[r] != 0 && shard_ptrs[r] % 16 == 0, "gather_cast_linear: null or misaligned shard address");
     shards[r] = reinterpret_cast<const void*>(static_cast<uintptr_t>(shard_ptrs[r]));
   }
   c10::cuda::CUDAGuard guard(x.device());
-  at::Tensor out = at::empty({m, n}, x.options());
+  at::Tensor out, act;
+  if (swiglu) {
+    act = at::empty({m, n}, x.options());
+    if (want_packed) out = at::empty({m, 2 * n}, x.options());
+  } else {
+    out = at::empty({m, n}, x.options());
+  }
   check_rc(ws_gather_gemm(x.data_ptr(), (int)m, (int)n, (int)k, shards, (int)world, (int)rows_per_shard, wb.data_ptr(),
-                          flags.data_ptr(), out.data_ptr(), (int)n,
+                          flags.data_ptr(), swiglu ? WS_EPI_SWIGLU : WS_EPI_BF16, out.defined() ? out.data_ptr() : nullptr,
+                          (int)w_rows, swiglu ? act.data_ptr() : nullptr, (int)n,
                           reinterpret_cast<int*>(const_cast<void*>(opt_ptr(error_flag))), (float)budget_seconds, 0,
                           cur_stream()), "gather_cast_linear");
-  return out;
+  if (!out.defined()) out = at::empty({0}, x.options());
+  if (!act.defined()) act = at::empty({0}, x.options());
+  return std::make_tuple(out, act);
 }
 
 // ----------------------------------------------------------------------------- decode step
@@ -635,7 +648,7 @@ void decode_attn(const at::Tensor& qkvgu, at::Tensor kc, at::Tensor vc, at::Tens
 TORCH_LIBRARY(ws_b200, m) {
   m.def("decode_gemm_splits(int n, int k) -> int");
   m.def("gather_cast_linear(Tensor x, int[] shard_ptrs, int n, int rows_per_shard, Tensor(a!) wb, Tensor(b!) flags, "
-        "Tensor(c!)? error_flag, float budget_seconds) -> Tensor");
+        "Tensor(c!)? error_flag, float budget_seconds, bool swiglu=False, bool want_packed=True) -> (Tensor, Tensor)");
   m.def("raise_for_status(int code) -> int");
   m.def("decode_gemm(Tensor w, Tensor x, int n, int epilogue, Tensor(a!) out, Tensor(b!)? error_flag, bool packed=False) -> ()");
   m.def("decode_reduce_norm(Tensor(a!) x, Tensor? partial, Tensor? token, Tensor? table, Tensor? scale, Tensor? bias, "

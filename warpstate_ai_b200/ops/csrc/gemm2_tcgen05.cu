@@ -70,12 +70,14 @@ struct GatherJob {
   int rows_per_shard;      // a multiple of 8 (so a chunk never straddles two shards)
   int n, k;                // k % 8 == 0
   __nv_bfloat16* dst;      // local BF16 [n, k]
-  unsigned* flags;         // one word per 256-row block, zero at launch
+  unsigned* flags;         // one word per 128-row block of W, zero at launch
   unsigned target;         // chunks per complete block
+  int interleave_h;        // SwiGLU: h (n = 2h rows: up, then gate; h % 128 == 0); otherwise 0
   unsigned long long wait_ns;
 };
 constexpr int GATHER_ROWS = 2;   // rows per chunk: small, so that the first block is spread over 128 CTAs
 constexpr int GATHER_THREADS = 128;
+constexpr int GATHER_BLOCK = 128;  // weight rows per ready flag (the rows one CTA of a pair stages)
 
 // Up to MAX_GROUP independent problems of the same kind share one persistent launch: their
 // tiles form one list, so the last partial wave is paid once per group instead of once per
@@ -147,7 +149,8 @@ template <bool A_MN, bool B_MN, int EPI, bool GATHER = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads<EPI>() + (GATHER ? GATHER_THREADS : 0), 1)
 gemm2_kernel(const __grid_constant__ PairGroup g, const __grid_constant__ GatherJob gj) {
   using namespace pair;
-  static_assert(!GATHER || (!A_MN && !B_MN && EPI == WS_EPI_BF16), "the gather variant is the NT forward GEMM");
+  static_assert(!GATHER || (!A_MN && !B_MN && (EPI == WS_EPI_BF16 || EPI == WS_EPI_SWIGLU)),
+                "the gather variant is the NT forward GEMM (plain or SwiGLU)");
   constexpr int GROUPS = epilogue_groups<EPI>();
   constexpr int STAGES = pair_stages<EPI>();
   constexpr bool STAGED = staged_epilogue<EPI>();
@@ -222,11 +225,14 @@ gemm2_kernel(const __grid_constant__ PairGroup g, const __grid_constant__ Gather
         const int m0 = t.mb * 2 * BM + rank * BM;  // this CTA's rows
         if constexpr (GATHER) {
           if (nb != ready_nb) {  // the 256 weight rows of this N block must have landed in the local buffer
-            const unsigned* flag = gj.flags + nb;
-            const int last_block_rows = gj.n - nb * BN;
-            const unsigned want = last_block_rows >= BN ? gj.target : static_cast<unsigned>((last_block_rows + GATHER_ROWS - 1) / GATHER_ROWS);
-            unsigned seen;
-            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+            // this CTA's 128 weight rows: plain [nb*256 + rank*128, +128); SwiGLU up rows nb*128.. (rank 0)
+            // or gate rows h + nb*128.. (rank 1).  One flag word per 128-row block of W.
+            const int block = kSwiglu ? (rank ? gj.interleave_h / GATHER_BLOCK + nb : nb) : 2 * nb + static_cast<int>(rank);
+            const unsigned* flag = gj.flags + block;
+            const int block_rows = min(GATHER_BLOCK, gj.n - block * GATHER_BLOCK);
+            const unsigned want = block_rows <= 0 ? 0u : static_cast<unsigned>((block_rows + GATHER_ROWS - 1) / GATHER_ROWS);
+            unsigned seen = want;  // a block past the last weight row has nothing to wait for (and no flag word)
+            if (want > 0) asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
             if (seen < want) {
               const uint64_t t0 = globaltimer_ns();
               uint32_t spins = 0;
@@ -574,7 +580,9 @@ gemm2_kernel(const __grid_constant__ PairGroup g, const __grid_constant__ Gather
       const int vec_per_row = gj.k / 8;
       const int chunks = (gj.n + GATHER_ROWS - 1) / GATHER_ROWS;
       for (int c = blockIdx.x; c < chunks; c += gridDim.x) {
-        const int row0 = c * GATHER_ROWS;
+        // SwiGLU (W = h up rows, then h gate rows): even chunks walk the up rows, odd chunks the gate
+        // rows, so that the two 128-row blocks of an N tile complete together
+        const int row0 = gj.interleave_h > 0 ? (c & 1) * gj.interleave_h + (c >> 1) * GATHER_ROWS : c * GATHER_ROWS;
         const int rows = min(GATHER_ROWS, gj.n - row0);
         const int owner = row0 / gj.rows_per_shard;
         const float* src = gj.shard[owner] + static_cast<size_t>(row0 - owner * gj.rows_per_shard) * gj.k;
@@ -608,7 +616,7 @@ gemm2_kernel(const __grid_constant__ PairGroup g, const __grid_constant__ Gather
         __threadfence();
         asm volatile("fence.proxy.async.global;" ::: "memory");
         asm volatile("bar.sync 3, %0;" ::"n"(GATHER_THREADS) : "memory");
-        if (gt == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(gj.flags + row0 / BN) : "memory");
+        if (gt == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(gj.flags + row0 / GATHER_BLOCK) : "memory");
       }
     }
   }
@@ -638,15 +646,16 @@ static int launch_pair(const PairGroup& g, int pairs, cudaStream_t stream) {
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
 
+template <int EPI>
 static int launch_pair_gather(const PairGroup& g, const GatherJob& job, int pairs, cudaStream_t stream) {
   static bool configured = false;
-  auto kern = gemm2_kernel<false, false, WS_EPI_BF16, true>;
+  auto kern = gemm2_kernel<false, false, EPI, true>;
   if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pair_smem<WS_EPI_BF16>()) != cudaSuccess)
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, pair_smem<EPI>()) != cudaSuccess)
       return -20;
     configured = true;
   }
-  kern<<<2 * pairs, pair_threads<WS_EPI_BF16>() + GATHER_THREADS, pair_smem<WS_EPI_BF16>(), stream>>>(g, job);
+  kern<<<2 * pairs, pair_threads<EPI>() + GATHER_THREADS, pair_smem<EPI>(), stream>>>(g, job);
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
@@ -684,6 +693,25 @@ static int fill_problem(const WsGemm* g, PairGroup& grp, int i, int* tiles_out) 
   return 0;
 }
 
+// Staged SwiGLU-forward epilogue: 32 x 32 store boxes over the packed (up | gate) matrix and the activation.
+static int fill_swiglu_maps(const WsGemm* g0, PairGroup& grp) {
+  __nv_bfloat16* packed = static_cast<__nv_bfloat16*>(g0->out);
+  __nv_bfloat16* act = static_cast<__nv_bfloat16*>(g0->out2);
+  const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_64B;
+  int rc = 0;
+  if (packed != nullptr) {
+    rc = make_map_bf16_swz(&grp.epi[0], packed, g0->n, g0->m, g0->ldo, 32, 32, sw);
+    if (!rc) rc = make_map_bf16_swz(&grp.epi[1], packed + g0->n, g0->n, g0->m, g0->ldo, 32, 32, sw);
+  }
+  if (!rc) rc = make_map_bf16_swz(&grp.epi[2], act, g0->n, g0->m, g0->ldo2, 32, 32, sw);
+  if (rc) return rc;
+  if (packed == nullptr) {
+    grp.epi[0] = grp.epi[2];  // never used for a store; keeps the descriptor prefetch valid
+    grp.epi[1] = grp.epi[2];
+  }
+  return 0;
+}
+
 }  // namespace ws
 
 // `count` problems (1..4) of one kind (same operand majors and epilogue) in one launch.  The
@@ -715,21 +743,8 @@ extern "C" int ws_gemm_pair_group(const WsGemm* items, int count, int sms, cudaS
   }
   if (items[0].epilogue == WS_EPI_SWIGLU) {
     if (count != 1) return -9;
-    const WsGemm* g0 = &items[0];
-    __nv_bfloat16* packed = static_cast<__nv_bfloat16*>(g0->out);
-    __nv_bfloat16* act = static_cast<__nv_bfloat16*>(g0->out2);
-    const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_64B;
-    int rc = 0;
-    if (packed != nullptr) {
-      rc = make_map_bf16_swz(&grp.epi[0], packed, g0->n, g0->m, g0->ldo, 32, 32, sw);
-      if (!rc) rc = make_map_bf16_swz(&grp.epi[1], packed + g0->n, g0->n, g0->m, g0->ldo, 32, 32, sw);
-    }
-    if (!rc) rc = make_map_bf16_swz(&grp.epi[2], act, g0->n, g0->m, g0->ldo2, 32, 32, sw);
+    const int rc = fill_swiglu_maps(&items[0], grp);
     if (rc) return rc;
-    if (packed == nullptr) {
-      grp.epi[0] = grp.epi[2];  // never used for a store; keeps the descriptor prefetch valid
-      grp.epi[1] = grp.epi[2];
-    }
   }
   if (items[0].epilogue == WS_EPI_SWIGLU_BWD) {
     if (count != 1) return -9;
@@ -770,23 +785,33 @@ extern "C" int ws_gemm_pair(const WsGemm* g, int sms, cudaStream_t stream) {
 
 // y[m, n] = x[m, k] . W[n, k]^T where W is the row-sharded FP32 master weight of `world` ranks
 // (shards[r] = address, in this process, of rank r's [rows_per_shard, k] FP32 block; peers' blocks are
-// symmetric-memory mappings).  `wb` is this rank's BF16 [n, k] landing buffer, `flags` a device array of
-// ceil(n / 256) words (zeroed here).  The caller guarantees that no rank changes its shard while the
-// kernel runs.  A bounded wait that runs out sets *error_flag to 6 and the launch still terminates.
+// symmetric-memory mappings).  `wb` is this rank's BF16 landing buffer for the whole weight, `flags` a
+// device array of one word per 128 weight rows (zeroed here).  epilogue WS_EPI_BF16: W has n rows, out is
+// BF16 [m, n].  WS_EPI_SWIGLU: W has 2n rows (n up rows, then n gate rows; n % 128 == 0), out is the packed
+// (up | gate) [m, 2n] (may be NULL), out2 the activation silu(gate) * up [m, n].  The caller guarantees that
+// no rank changes its shard while the kernel runs.  A bounded wait that runs out sets *error_flag to 6 and
+// the launch still terminates.
 extern "C" int ws_gather_gemm(const void* x, int m, int n, int k, const void* const* shards, int world,
-                              int rows_per_shard, void* wb, void* flags, void* out, int ldo, int* error_flag,
-                              float budget_seconds, int sms, cudaStream_t stream) {
+                              int rows_per_shard, void* wb, void* flags, int epilogue, void* out, int ldo,
+                              void* out2, int ldo2, int* error_flag, float budget_seconds, int sms,
+                              cudaStream_t stream) {
   using namespace ws;
+  const bool swiglu = epilogue == WS_EPI_SWIGLU;
+  if (epilogue != WS_EPI_BF16 && !swiglu) return -6;
   if (m <= 0 || n <= 0 || k <= 0 || k % 8 != 0 || world < 1 || world > 8) return -1;
-  if (rows_per_shard <= 0 || rows_per_shard % 8 != 0 || (long long)rows_per_shard * world < n) return -1;
-  if (ldo < n || ldo % 8 != 0) return -1;
-  if (((uintptr_t)x | (uintptr_t)wb | (uintptr_t)out) & 15) return -5;
+  const int w_rows = swiglu ? 2 * n : n;
+  if (swiglu && (n % GATHER_BLOCK != 0 || out2 == nullptr || ldo2 < n || ldo2 % 8 != 0)) return -1;
+  if (rows_per_shard <= 0 || rows_per_shard % 8 != 0 || (long long)rows_per_shard * world < w_rows) return -1;
+  if (out != nullptr && (ldo < w_rows || ldo % 8 != 0)) return -1;
+  if (!swiglu && out == nullptr) return -1;
+  if (((uintptr_t)x | (uintptr_t)wb | (uintptr_t)out | (uintptr_t)out2) & 15) return -5;
   for (int r = 0; r < world; ++r)
     if (shards[r] == nullptr || ((uintptr_t)shards[r] & 15)) return -5;
   WsGemm item;
   memset(&item, 0, sizeof(item));
   item.a = x; item.b = wb; item.m = m; item.n = n; item.k = k; item.lda = k; item.ldb = k;
-  item.epilogue = WS_EPI_BF16; item.out = out; item.ldo = ldo; item.alpha = 1.f; item.error_flag = error_flag;
+  item.epilogue = epilogue; item.out = out; item.ldo = ldo; item.out2 = out2; item.ldo2 = ldo2;
+  item.alpha = 1.f; item.error_flag = error_flag;
   PairGroup grp;
   memset(&grp, 0, sizeof(grp));
   grp.count = 1;
@@ -794,22 +819,28 @@ extern "C" int ws_gather_gemm(const void* x, int m, int n, int k, const void* co
   int rc = fill_problem(&item, grp, 0, &tiles);
   if (rc) return rc;
   for (int i = 1; i <= MAX_GROUP; ++i) grp.tile_start[i] = tiles;
+  if (swiglu) {
+    rc = fill_swiglu_maps(&item, grp);
+    if (rc) return rc;
+  }
   GatherJob job;
   memset(&job, 0, sizeof(job));
   for (int r = 0; r < world; ++r) job.shard[r] = static_cast<const float*>(shards[r]);
   job.world = world;
   job.rows_per_shard = rows_per_shard;
-  job.n = n; job.k = k;
+  job.n = w_rows; job.k = k;
   job.dst = static_cast<__nv_bfloat16*>(wb);
   job.flags = static_cast<unsigned*>(flags);
-  job.target = pair::BN / GATHER_ROWS;
+  job.target = GATHER_BLOCK / GATHER_ROWS;
+  job.interleave_h = swiglu ? n : 0;
   job.wait_ns = static_cast<unsigned long long>((budget_seconds > 0.f ? budget_seconds : 2.0f) * 1e9);
-  const int blocks = (n + pair::BN - 1) / pair::BN;
+  const int blocks = (w_rows + GATHER_BLOCK - 1) / GATHER_BLOCK;
   if (cudaMemsetAsync(flags, 0, sizeof(unsigned) * blocks, stream) != cudaSuccess) return -21;
   // Every CTA must be resident at once (producers wait for chunks that other CTAs gather): the grid never
   // exceeds one CTA per SM, and with fewer tiles than pairs the spare pairs still take gather chunks.
   int pairs = (sms > 0 ? sms : 148) / 2;
   if (pairs < 1) pairs = 1;
   if (pairs > 74) pairs = 74;
-  return launch_pair_gather(grp, job, pairs, stream);
+  return swiglu ? launch_pair_gather<WS_EPI_SWIGLU>(grp, job, pairs, stream)
+                : launch_pair_gather<WS_EPI_BF16>(grp, job, pairs, stream);
 }

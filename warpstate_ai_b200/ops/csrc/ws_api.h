@@ -57,10 +57,11 @@ int ws_gemm_group(const WsGemm* items, int count, cudaStream_t stream);
 void ws_gemm_set_sm_limit(int sms);
 // Fused all-gather + FP32->BF16 cast + GEMM for a row-sharded weight (ops/csrc/gemm2_tcgen05.cu):
 // out[m, n] = x[m, k] . W[n, k]^T with W's FP32 rows owned by `world` ranks in blocks of rows_per_shard;
-// shards[r] is rank r's block as mapped in this process.  wb: local BF16 [n, k]; flags: ceil(n/256) words.
+// shards[r] is rank r's block as mapped in this process.  wb: local BF16 copy of W; flags: one word per 128
+// weight rows.  epilogue WS_EPI_BF16 (W [n, k]) or WS_EPI_SWIGLU (W [2n, k]; out packed or NULL, out2 activation).
 int ws_gather_gemm(const void* x, int m, int n, int k, const void* const* shards, int world, int rows_per_shard,
-                   void* wb, void* flags, void* out, int ldo, int* error_flag, float budget_seconds, int sms,
-                   cudaStream_t stream);
+                   void* wb, void* flags, int epilogue, void* out, int ldo, void* out2, int ldo2, int* error_flag,
+                   float budget_seconds, int sms, cudaStream_t stream);
 // ---- decode step (ops/csrc/decode.cu); batch <= 64
 // out[b, n] = sum_k x[b, k] W[n, k] as a weight-streaming kernel.  epilogue: 0 BF16 [batch, ldo];
 // 1 FP32 split-K partials [ws_decode_gemm_splits(n, k), batch, n]; 2 SwiGLU with W = [2n, k]

@@ -4,7 +4,7 @@
 ``[n, k]`` FP32 weight in symmetric memory.  `forward(x)` is ONE kernel launch
 (`gemm2_kernel<..., GATHER=true>`, `ops/csrc/gemm2_tcgen05.cu`): four warps of every CTA pull the
 shards -- peer loads over NVLink for the rows other ranks own -- cast them to BF16 into a local
-landing buffer and publish per-256-row-block counters, while the TMA/tcgen05 tile loop of the
+landing buffer and publish per-128-row-block counters, while the TMA/tcgen05 tile loop of the
 same CTAs consumes each block of weight rows as soon as it is complete.  All-gather, cast and
 GEMM overlap tile by tile; the gathered BF16 weight is left in the landing buffer, so the
 backward pass (dX = dY W, dW = dY^T X) and the remaining micro-batches of the update reuse it
@@ -41,9 +41,12 @@ class ShardedWeight:
     """Row-sharded FP32 weight with a fused gather + cast + GEMM forward."""
 
     def __init__(self, n: int, k: int, rank: int, world: int, shard: torch.Tensor, shard_ptrs: list[int],
-                 barrier=None):
+                 barrier=None, swiglu: bool = False):
         if n % 8 or k % 8:
             raise ValueError("n and k must be multiples of 8")
+        if swiglu and (n % 2 or (n // 2) % 128):
+            raise ValueError("a SwiGLU weight needs 2*h rows (up, then gate) with h a multiple of 128")
+        self.swiglu = swiglu                    # W = [2h, k]: forward returns (packed, silu(gate) * up)
         self.n, self.k, self.rank, self.world = n, k, rank, world
         self.rows = rows_per_shard(n, world)
         if shard.dtype != torch.float32 or shard.numel() < self.rows * k:
@@ -53,14 +56,14 @@ class ShardedWeight:
         self._barrier = barrier
         device = shard.device
         self.gathered = torch.empty(n, k, device=device, dtype=torch.bfloat16)   # landing buffer
-        self.flags = torch.zeros((n + 255) // 256, device=device, dtype=torch.int32)
+        self.flags = torch.zeros((n + 127) // 128, device=device, dtype=torch.int32)   # one word per 128 rows
         self.error_flag = G.error_flag(device)
         self.gathered_valid = False
         self.shard_grad = None                  # FP32 gradient of this rank's rows (set by ShardedLinear)
 
     # ------------------------------------------------------------------ construction
     @classmethod
-    def from_full(cls, weight: torch.Tensor, rank: int, world: int, group=None) -> "ShardedWeight":
+    def from_full(cls, weight: torch.Tensor, rank: int, world: int, group=None, swiglu: bool = False) -> "ShardedWeight":
         """Shard a full ``[n, k]`` weight (identical on every rank) into symmetric memory."""
         from . import symm
         n, k = weight.shape
@@ -69,13 +72,13 @@ class ShardedWeight:
         lo, hi = rank * per, min(n, (rank + 1) * per)
         if hi > lo:
             buf.tensor[:(hi - lo) * k].copy_(weight[lo:hi].reshape(-1).float())
-        self = cls(n, k, rank, world, buf.tensor, buf.peer_ptrs, barrier=buf.barrier)
+        self = cls(n, k, rank, world, buf.tensor, buf.peer_ptrs, barrier=buf.barrier, swiglu=swiglu)
         self._sym = buf
         self.publish()
         return self
 
     @classmethod
-    def emulated(cls, weight: torch.Tensor, world: int) -> "ShardedWeight":
+    def emulated(cls, weight: torch.Tensor, world: int, swiglu: bool = False) -> "ShardedWeight":
         """All ``world`` shards on one device: the kernel and its index arithmetic without peers."""
         n, k = weight.shape
         per = rows_per_shard(n, world)
@@ -86,7 +89,7 @@ class ShardedWeight:
             if hi > lo:
                 t[:(hi - lo) * k].copy_(weight[lo:hi].reshape(-1).float())
             shards.append(t)
-        self = cls(n, k, 0, world, shards[0], [t.data_ptr() for t in shards])
+        self = cls(n, k, 0, world, shards[0], [t.data_ptr() for t in shards], swiglu=swiglu)
         self._keep = shards
         return self
 
@@ -99,20 +102,22 @@ class ShardedWeight:
             torch.cuda.current_stream(self.shard.device).synchronize()
             self._barrier()
 
-    def forward(self, x: torch.Tensor, budget_seconds: float = 2.0) -> torch.Tensor:
-        """``x [m, k]`` BF16 -> ``x @ W^T [m, n]`` BF16; gathers and casts W in the same launch."""
+    def forward(self, x: torch.Tensor, budget_seconds: float = 2.0):
+        """``x [m, k]`` BF16 -> ``x @ W^T [m, n]`` BF16; gathers and casts W in the same launch.
+        A SwiGLU weight returns ``(packed [m, 2h], silu(gate) * up [m, h])`` like `ops.gemm.linear_swiglu`."""
         if x.dtype != torch.bfloat16:
             x = x.to(torch.bfloat16)
-        y = torch.ops.ws_b200.gather_cast_linear(x.contiguous(), self.shard_ptrs, self.n, self.rows, self.gathered,
-                                                 self.flags, self.error_flag, float(budget_seconds))
+        out, act = torch.ops.ws_b200.gather_cast_linear(
+            x.contiguous(), self.shard_ptrs, self.n // 2 if self.swiglu else self.n, self.rows, self.gathered,
+            self.flags, self.error_flag, float(budget_seconds), self.swiglu, True)
         self.gathered_valid = True
-        return y
+        return (out, act) if self.swiglu else out
 
-    def forward_cached(self, x: torch.Tensor) -> torch.Tensor:
+    def forward_cached(self, x: torch.Tensor):
         """Later micro-batches of the same update: the landing buffer already holds the BF16 weight."""
         if not self.gathered_valid:
             return self.forward(x)
-        return G.linear(x, self.gathered)
+        return G.linear_swiglu(x, self.gathered) if self.swiglu else G.linear(x, self.gathered)
 
     def full_weight(self) -> torch.Tensor:
         """The whole FP32 weight, read shard by shard (emulated shards only; for tests)."""
@@ -171,6 +176,8 @@ class ShardedLinear(torch.nn.Module):
 
     def __init__(self, weight: ShardedWeight, group=None):
         super().__init__()
+        if weight.swiglu:
+            raise ValueError("ShardedLinear takes a plain weight; a SwiGLU weight is used through ShardedWeight.forward")
         self.weight = weight
         self.group = group
         weight.shard_grad = None
