@@ -25,12 +25,15 @@ import torch.distributed as dist
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--m", type=int, default=16384)
-    ap.add_argument("--n", type=int, default=10240)
-    ap.add_argument("--k", type=int, default=2048)
+    # long names: under torchrun a bare --n is read as an abbreviation of torchrun's own options
+    ap.add_argument("--m", "--tokens", dest="m", type=int, default=16384)
+    ap.add_argument("--n", "--out-features", dest="n", type=int, default=10240)
+    ap.add_argument("--k", "--in-features", dest="k", type=int, default=2048)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--emulate-world", type=int, default=4, help="shards on one device when run without torchrun")
+    ap.add_argument("--swiglu", action="store_true",
+                    help="up/gate weight [2n, k] with the SwiGLU epilogue (n = hidden width; try --out-features 7168)")
     args = ap.parse_args()
     from ..ops import _ext, gemm as G
     from ..parallel.sharded_linear import ShardedWeight, rows_per_shard
@@ -44,16 +47,18 @@ def main() -> None:
         dist.init_process_group("nccl", device_id=device)
     _ext.require()
     torch.manual_seed(0)
-    w = torch.randn(args.n, args.k, device=device) * 0.02
+    w_rows = 2 * args.n if args.swiglu else args.n
+    w = torch.randn(w_rows, args.k, device=device) * 0.02
     torch.manual_seed(1 + rank)
     x = torch.randn(args.m, args.k, device=device).bfloat16()
     if distributed:
-        sw = ShardedWeight.from_full(w, rank, world)
+        sw = ShardedWeight.from_full(w, rank, world, swiglu=args.swiglu)
         shards = world
     else:
-        sw = ShardedWeight.emulated(w, args.emulate_world)
+        sw = ShardedWeight.emulated(w, args.emulate_world, swiglu=args.swiglu)
         shards = args.emulate_world
-    per = rows_per_shard(args.n, shards)
+    per = rows_per_shard(w_rows, shards)
+    linear = G.linear_swiglu if args.swiglu else G.linear
     gathered32 = torch.empty(per * shards, args.k, device=device)
     wb = w.bfloat16()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
@@ -61,12 +66,12 @@ def main() -> None:
     def unfused():
         if distributed:
             dist.all_gather_into_tensor(gathered32.view(-1), sw.shard.view(-1)[:per * args.k])
-            src = gathered32[:args.n]
+            src = gathered32[:w_rows]
         else:
             src = w
-        return G.linear(x, torch.ops.ws_b200.cast_bf16(src, None))
+        return linear(x, torch.ops.ws_b200.cast_bf16(src, None))
 
-    arms = {"fused": lambda: sw.forward(x), "unfused": unfused, "gemm_only": lambda: G.linear(x, wb)}
+    arms = {"fused": lambda: sw.forward(x), "unfused": unfused, "gemm_only": lambda: linear(x, wb)}
     result = {}
     for name, fn in arms.items():
         times = []
@@ -88,8 +93,8 @@ def main() -> None:
         result[name] = float(t.item())
     G.check_device_errors()
     if rank == 0:
-        flops = 2.0 * args.m * args.n * args.k
-        remote_bytes = 4.0 * args.n * args.k * (world - 1) / world
+        flops = 2.0 * args.m * w_rows * args.k
+        remote_bytes = 4.0 * w_rows * args.k * (world - 1) / world
         peaks = {}
         try:
             with open(os.path.join(os.path.dirname(__file__), "..", "..", "MEASURED_PEAKS.json")) as f:
@@ -98,7 +103,7 @@ def main() -> None:
             pass
         peak_tflops = float(peaks.get("bf16_tflops", 1590.0))
         target_ms = max(flops / (peak_tflops * 1e12), remote_bytes / 770e9) * 1e3
-        print(json.dumps({"shape": [args.m, args.n, args.k], "ranks": world, "shards": shards, "ms": result,
+        print(json.dumps({"shape": [args.m, w_rows, args.k], "swiglu": args.swiglu, "ranks": world, "shards": shards, "ms": result,
                           "fused_tflops": flops / result["fused"] / 1e9, "remote_fp32_mb": remote_bytes / 1e6,
                           "roofline_target_ms": target_ms, "fused_fraction_of_roofline": target_ms / result["fused"],
                           "peak_tflops_used": peak_tflops, "timing": "cuda events, median, max over ranks, L2 flushed"}),
