@@ -1,6 +1,7 @@
 """Fused all-gather + FP32->BF16 cast + GEMM over a row-sharded weight (`parallel/sharded_linear.py`).
 
-* CPU: shard sizing.
+* CPU: shard sizing; two gloo ranks on the collective fallback (ownership, cached re-use, publish, gradient
+  scatter to the row owners, SwiGLU form).
 * One GPU: the kernel with 1, 3, 4 and 8 emulated shards (all on the device) against a plain
   PyTorch FP32 product of the BF16-rounded operands; the landing buffer must equal the BF16 cast of
   the weight bit for bit, and the cached second call (ordinary GEMM on the landing buffer) must
@@ -194,5 +195,83 @@ def test_fused_gather_cast_gemm_two_gpus(tmp_path):
         assert r["dw_rel"] < 0.004 and r["dx_rel"] < 0.006, r
 
 
+def cpu_worker(rank: int, world: int, out_dir: Path) -> None:
+    """gloo ranks on CPU: the collective fallback keeps ownership, publish, re-use and gradient scatter."""
+    import torch.distributed as dist
+    from warpstate_ai_b200.parallel.sharded_linear import ShardedLinear, ShardedWeight
+    dist.init_process_group("gloo", init_method=(out_dir / "rendezvous").as_uri(), rank=rank, world_size=world)
+    torch.manual_seed(0)
+    n, k, m = 40, 16, 24
+    w = torch.randn(n, k)
+    torch.manual_seed(100 + rank)
+    x = torch.randn(m, k).bfloat16()
+    dy = torch.randn(m, n).bfloat16()
+    sw = ShardedWeight.from_full_collective(w, rank, world)
+    layer = ShardedLinear(sw)
+    report = {"rows": sw.rows}
+    xg = x.float().requires_grad_(True)
+    y = layer(xg)
+    ref = x.float() @ w.bfloat16().float().T
+    report["rel"] = float((y.float() - ref).norm() / ref.norm())
+    y.backward(dy)
+    dw = dy.float().T @ x.float()
+    dist.all_reduce(dw)
+    padded = torch.zeros(sw.rows * world, k)
+    padded[:n] = dw
+    mine = padded[rank * sw.rows:(rank + 1) * sw.rows]
+    report["dw_err"] = float((sw.shard_grad.view(sw.rows, k) - mine).abs().max())
+    report["cached"] = bool(sw.gathered_valid)
+    # every owner changes its rows; after publish() the next forward sees all of them
+    sw.shard.mul_(2.0 + rank)
+    layer.publish()
+    report["stale_after_publish"] = not sw.gathered_valid
+    y2 = layer(x.float())
+    expect = torch.zeros(sw.rows * world, k)
+    expect[:n] = w
+    for r in range(world):
+        expect[r * sw.rows:(r + 1) * sw.rows] *= 2.0 + r
+    ref2 = x.float() @ expect[:n].bfloat16().float().T
+    report["rel_after_update"] = float((y2.float() - ref2).norm() / ref2.norm())
+    # SwiGLU form
+    torch.manual_seed(1)
+    wug = torch.randn(2 * 128, k)
+    sg = ShardedWeight.from_full_collective(wug, rank, world, swiglu=True)
+    packed, act = sg.forward(x)
+    both = x.float() @ wug.bfloat16().float().T
+    report["swiglu_rel"] = float((act.float() - both[:, :128] * torch.nn.functional.silu(both[:, 128:])).norm()
+                                 / (both[:, :128] * torch.nn.functional.silu(both[:, 128:])).norm())
+    (out_dir / f"report-{rank}.json").write_text(json.dumps(report))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_collective_fallback_two_cpu_ranks(tmp_path):
+    import os
+    import subprocess
+    env = dict(os.environ)
+    env["PYTHONPATH"] = str(ROOT) + os.pathsep + env.get("PYTHONPATH", "")
+    procs = [subprocess.Popen([sys.executable, __file__, str(rank), "2", str(tmp_path), "cpu"], env=env,
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for rank in range(2)]
+    outputs = []
+    for p in procs:
+        try:
+            out, _ = p.communicate(timeout=180)
+        except subprocess.TimeoutExpired:
+            for q in procs:
+                q.kill()
+            raise
+        outputs.append(out)
+    for rank, p in enumerate(procs):
+        assert p.returncode == 0, f"rank {rank} failed:\n{outputs[rank][-3000:]}"
+    for rank in range(2):
+        r = json.loads((tmp_path / f"report-{rank}.json").read_text())
+        assert r["rows"] == 24 and r["cached"] and r["stale_after_publish"], r
+        assert r["rel"] < 0.01 and r["rel_after_update"] < 0.01 and r["swiglu_rel"] < 0.02, r
+        assert r["dw_err"] < 1e-3, r
+
+
 if __name__ == "__main__":
-    worker(int(sys.argv[1]), int(sys.argv[2]), Path(sys.argv[3]))
+    if len(sys.argv) > 4 and sys.argv[4] == "cpu":
+        cpu_worker(int(sys.argv[1]), int(sys.argv[2]), Path(sys.argv[3]))
+    else:
+        worker(int(sys.argv[1]), int(sys.argv[2]), Path(sys.argv[3]))

@@ -57,7 +57,8 @@ class ShardedWeight:
         device = shard.device
         self.gathered = torch.empty(n, k, device=device, dtype=torch.bfloat16)   # landing buffer
         self.flags = torch.zeros((n + 127) // 128, device=device, dtype=torch.int32)   # one word per 128 rows
-        self.error_flag = G.error_flag(device)
+        self.error_flag = G.error_flag(device) if device.type == "cuda" else None
+        self.group = None                       # process group of the collective fallback
         self.gathered_valid = False
         self.shard_grad = None                  # FP32 gradient of this rank's rows (set by ShardedLinear)
 
@@ -75,6 +76,23 @@ class ShardedWeight:
         self = cls(n, k, rank, world, buf.tensor, buf.peer_ptrs, barrier=buf.barrier, swiglu=swiglu)
         self._sym = buf
         self.publish()
+        return self
+
+    @classmethod
+    def from_full_collective(cls, weight: torch.Tensor, rank: int, world: int, group=None,
+                             swiglu: bool = False) -> "ShardedWeight":
+        """The same ownership without symmetric memory (CPU / gloo, or a GPU job without peer access):
+        `forward` gathers the shards with an ordinary all-gather, then casts and multiplies.  The host-side
+        logic -- ownership, publish, cached re-use, gradient scatter -- is the one of the fused path."""
+        n, k = weight.shape
+        per = rows_per_shard(n, world)
+        shard = torch.zeros(per * k, device=weight.device, dtype=torch.float32)
+        lo, hi = rank * per, min(n, (rank + 1) * per)
+        if hi > lo:
+            shard[:(hi - lo) * k].copy_(weight[lo:hi].reshape(-1).float())
+        self = cls(n, k, rank, world, shard, [], swiglu=swiglu)
+        self.group = group
+        self._collective = True
         return self
 
     @classmethod
@@ -107,6 +125,9 @@ class ShardedWeight:
         A SwiGLU weight returns ``(packed [m, 2h], silu(gate) * up [m, h])`` like `ops.gemm.linear_swiglu`."""
         if x.dtype != torch.bfloat16:
             x = x.to(torch.bfloat16)
+        if getattr(self, "_collective", False):
+            self._gather_collective()
+            return self._math_forward(x)
         out, act = torch.ops.ws_b200.gather_cast_linear(
             x.contiguous(), self.shard_ptrs, self.n // 2 if self.swiglu else self.n, self.rows, self.gathered,
             self.flags, self.error_flag, float(budget_seconds), self.swiglu, True)
@@ -117,7 +138,30 @@ class ShardedWeight:
         """Later micro-batches of the same update: the landing buffer already holds the BF16 weight."""
         if not self.gathered_valid:
             return self.forward(x)
+        if getattr(self, "_collective", False):
+            return self._math_forward(x)
         return G.linear_swiglu(x, self.gathered) if self.swiglu else G.linear(x, self.gathered)
+
+    # ------------------------------------------------------------------ collective fallback
+    def _gather_collective(self) -> None:
+        import torch.distributed as dist
+        if self.world > 1:
+            parts = [torch.empty_like(self.shard) for _ in range(self.world)]
+            dist.all_gather(parts, self.shard, group=self.group)
+        else:
+            parts = [self.shard]
+        rows = torch.cat([p.view(self.rows, self.k) for p in parts], dim=0)[:self.n]
+        self.gathered.copy_(rows)               # FP32 -> BF16, the cast the kernel does on the fly
+        self.gathered_valid = True
+
+    def _math_forward(self, x: torch.Tensor):
+        both = (x.float() @ self.gathered.float().T)
+        if not self.swiglu:
+            return both.to(torch.bfloat16)
+        h = self.n // 2
+        packed = both.to(torch.bfloat16)
+        up, gate = packed[:, :h].float(), packed[:, h:].float()
+        return packed, (torch.nn.functional.silu(gate) * up).to(torch.bfloat16)
 
     def full_weight(self) -> torch.Tensor:
         """The whole FP32 weight, read shard by shard (emulated shards only; for tests)."""
@@ -149,11 +193,19 @@ class _ShardedLinearFn(torch.autograd.Function):
         (x2,) = ctx.saved_tensors
         dy2 = dy.reshape(-1, sw.n)
         dy2 = (dy2 if dy2.dtype == torch.bfloat16 else dy2.to(torch.bfloat16)).contiguous()
-        dx = G.grad_input(dy2, sw.gathered).view(ctx.shape).to(ctx.x_dtype)
+        collective = getattr(sw, "_collective", False)
         # full dW in FP32 (rows padded to world * rows_per_shard), then each owner keeps the sum of its rows
         full = torch.zeros(sw.rows * sw.world, sw.k, device=dy2.device, dtype=torch.float32)
-        G.grad_weight_accumulate(dy2, x2, full[:sw.n])
-        if sw.world > 1 and dist.is_initialized():
+        if collective:
+            dx = (dy2.float() @ sw.gathered.float()).to(torch.bfloat16).view(ctx.shape).to(ctx.x_dtype)
+            full[:sw.n] = dy2.float().T @ x2.float()
+        else:
+            dx = G.grad_input(dy2, sw.gathered).view(ctx.shape).to(ctx.x_dtype)
+            G.grad_weight_accumulate(dy2, x2, full[:sw.n])
+        if collective and sw.world > 1 and dist.is_initialized():
+            dist.all_reduce(full, group=ctx.group if ctx.group is not None else sw.group)  # gloo has no reduce-scatter
+            mine = full[sw.rank * sw.rows:(sw.rank + 1) * sw.rows].clone()
+        elif sw.world > 1 and dist.is_initialized():
             mine = torch.empty(sw.rows, sw.k, device=dy2.device, dtype=torch.float32)
             dist.reduce_scatter_tensor(mine, full, group=ctx.group)
         else:
