@@ -269,6 +269,9 @@ extern "C" int ws_comm_max_ctas(void) { return 64; }
 // grad_ptrs / flag_ptrs: `world` device addresses (this process's mappings of every rank's
 // buffers, own rank included).  mc_grad: multimem address of the gradient arena or NULL.
 // sumsq_out: `ctas` floats (may be NULL).  status: 8 ints on the device.
+// `seq` counts the calls on this bucket from 1, on every rank alike, and `ctas` must be the same in every
+// call on a bucket: its completion counter advances by `ctas` per call and a rank waits for seq * ctas.
+// (A different CTA count needs a bucket of its own; a mismatch ends in a reported time-out, code 2.)
 extern "C" int ws_grad_allreduce(const unsigned long long* grad_ptrs, const unsigned long long* flag_ptrs,
                                  unsigned long long mc_grad, int rank, int world, size_t start, size_t count,
                                  int bucket, unsigned seq, float scale, int push, int ctas, float* sumsq_out,
