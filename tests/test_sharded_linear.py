@@ -232,6 +232,32 @@ def cpu_worker(rank: int, world: int, out_dir: Path) -> None:
         expect[r * sw.rows:(r + 1) * sw.rows] *= 2.0 + r
     ref2 = x.float() @ expect[:n].bfloat16().float().T
     report["rel_after_update"] = float((y2.float() - ref2).norm() / ref2.norm())
+    # two updates of owner-only AdamW equal dense AdamW on the whole weight with the summed gradient
+    from warpstate_ai_b200.parallel.sharded_linear import ShardedRowsAdamW
+    torch.manual_seed(0)
+    w0 = torch.randn(n, k)
+    st = ShardedWeight.from_full_collective(w0, rank, world)
+    lin = ShardedLinear(st)
+    opt = ShardedRowsAdamW([lin], lr=1e-2, weight_decay=0.1)
+    dense = torch.nn.Parameter(w0.clone())
+    ref_opt = torch.optim.AdamW([dense], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    for it in range(2):
+        torch.manual_seed(300 + 10 * it + rank)
+        xi = torch.randn(m, k).bfloat16()
+        gi = torch.randn(m, n).bfloat16()
+        opt.zero_grad()
+        lin(xi.float().requires_grad_(True)).backward(gi)
+        opt.step()
+        grad = gi.float().T @ xi.float()
+        dist.all_reduce(grad)
+        ref_opt.zero_grad()
+        dense.grad = grad
+        ref_opt.step()
+    full = torch.zeros(st.rows * world, k)
+    full[:n] = dense.detach()
+    mine_rows = full[rank * st.rows:(rank + 1) * st.rows]
+    report["adamw_err"] = float((st.shard.view(st.rows, k) - mine_rows).abs().max())
+    report["adamw_moment_bytes"] = opt.memory_bytes()
     # SwiGLU form
     torch.manual_seed(1)
     wug = torch.randn(2 * 128, k)
@@ -268,6 +294,7 @@ def test_collective_fallback_two_cpu_ranks(tmp_path):
         assert r["rows"] == 24 and r["cached"] and r["stale_after_publish"], r
         assert r["rel"] < 0.01 and r["rel_after_update"] < 0.01 and r["swiglu_rel"] < 0.02, r
         assert r["dw_err"] < 1e-3, r
+        assert r["adamw_err"] < 2e-5 and r["adamw_moment_bytes"] == 2 * 4 * 24 * 16, r
 
 
 if __name__ == "__main__":

@@ -241,3 +241,45 @@ class ShardedLinear(torch.nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return _ShardedLinearFn.apply(x, self._anchor, self.weight, not self.weight.gathered_valid, self.group)
+
+
+class ShardedRowsAdamW:
+    """AdamW on the rows each rank owns of one or more `ShardedLinear` layers.
+
+    Only the owner holds the FP32 master rows, their gradient (already summed over ranks by the layer's
+    backward) and their two moments: parameter, gradient and optimizer memory per rank are 1/world of the
+    layer's.  `step()` updates the owned rows in place and publishes them; `zero_grad()` drops the row
+    gradients.  The update is `torch.optim.AdamW`'s (decoupled weight decay, bias-corrected moments), the
+    optimizer the reference uses on every parameter (reference run_40b.py:534-535).
+    """
+
+    def __init__(self, layers, lr: float = 1e-3, betas=(0.9, 0.95), eps: float = 1e-8, weight_decay: float = 0.1):
+        self.layers = list(layers)
+        self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
+        self.steps = 0
+        self.m = [torch.zeros_like(layer.weight.shard) for layer in self.layers]
+        self.v = [torch.zeros_like(layer.weight.shard) for layer in self.layers]
+
+    def zero_grad(self) -> None:
+        for layer in self.layers:
+            layer.weight.shard_grad = None
+
+    @torch.no_grad()
+    def step(self, lr: float | None = None, grad_scale: float = 1.0) -> None:
+        lr = self.lr if lr is None else lr
+        self.steps += 1
+        b1, b2 = self.betas
+        c1, c2 = 1.0 - b1 ** self.steps, 1.0 - b2 ** self.steps
+        for layer, m, v in zip(self.layers, self.m, self.v):
+            sw = layer.weight
+            if sw.shard_grad is not None:
+                g = sw.shard_grad.reshape(-1)[:sw.shard.numel()] * grad_scale
+                p = sw.shard
+                p.mul_(1.0 - lr * self.weight_decay)
+                m.mul_(b1).add_(g, alpha=1.0 - b1)
+                v.mul_(b2).addcmul_(g, g, value=1.0 - b2)
+                p.addcdiv_(m / c1, (v / c2).sqrt_().add_(self.eps), value=-lr)
+            layer.publish()
+
+    def memory_bytes(self) -> int:
+        return sum(4 * (m.numel() + v.numel()) for m, v in zip(self.m, self.v))
