@@ -116,7 +116,9 @@ class WarpStateCore(nn.Module):
         ``x*(1+scale)+bias`` is applied first (the fused path folds it into its first kernel)."""
         if x.shape[1] % self.chunk != 0:
             raise ValueError(f"sequence length {x.shape[1]} must be divisible by chunk_size={self.chunk}")
-        if _fused_active(x):
+        # cores whose projections were replaced by row-sharded layers (parallel/sharded_model.py) take the
+        # module-by-module path: their weights are not whole tensors that the fused layer kernels could read
+        if _fused_active(x) and not getattr(self, "sharded_linears", False):
             from ..ops import fused
             return fused.core_forward(self, x, depth_scale, depth_bias)
         if depth_scale is not None:
@@ -224,7 +226,7 @@ class WarpStateLM(nn.Module):
     # ------------------------------------------------------------------ trunk
     def hidden_states(self, input_ids: torch.Tensor) -> torch.Tensor:
         """Embedding, all logical depths and the final norm: ``[B,T] -> [B,T,d]``."""
-        if _fused_active(self.embed.weight) and input_ids.is_cuda:
+        if _fused_active(self.embed.weight) and input_ids.is_cuda and not getattr(self, "sharded_linears", False):
             from ..ops import fused
             return fused.trunk_forward(self, input_ids)
         x = self.embed(input_ids)
