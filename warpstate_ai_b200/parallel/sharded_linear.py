@@ -283,3 +283,37 @@ class ShardedRowsAdamW:
 
     def memory_bytes(self) -> int:
         return sum(4 * (m.numel() + v.numel()) for m, v in zip(self.m, self.v))
+
+    # ------------------------------------------------------------------ unsharded optimizer state
+    def gather_state(self, group=None) -> dict:
+        """Step count and whole-weight moments (``[n, k]`` per layer), identical on every rank: the form a
+        checkpoint keeps, so that a run can resume on a different number of ranks (collective call)."""
+        import torch.distributed as dist
+
+        def whole(layer, rows_tensor):
+            sw = layer.weight
+            if sw.world > 1:
+                parts = [torch.empty_like(rows_tensor) for _ in range(sw.world)]
+                dist.all_gather(parts, rows_tensor.contiguous(), group=group)
+            else:
+                parts = [rows_tensor]
+            return torch.cat([p.view(sw.rows, sw.k) for p in parts], dim=0)[:sw.n].clone()
+
+        return {"steps": self.steps,
+                "exp_avg": [whole(layer, m) for layer, m in zip(self.layers, self.m)],
+                "exp_avg_sq": [whole(layer, v) for layer, v in zip(self.layers, self.v)]}
+
+    def load_state(self, state: dict) -> None:
+        """Adopt a `gather_state` result: every rank keeps the moments of the rows it owns now."""
+        if len(state["exp_avg"]) != len(self.layers):
+            raise ValueError("optimizer state does not match the number of sharded layers")
+        self.steps = int(state["steps"])
+        for layer, m, v, full_m, full_v in zip(self.layers, self.m, self.v, state["exp_avg"], state["exp_avg_sq"]):
+            sw = layer.weight
+            if tuple(full_m.shape) != (sw.n, sw.k):
+                raise ValueError(f"moment shape {tuple(full_m.shape)} does not match the weight {(sw.n, sw.k)}")
+            lo, hi = sw.rank * sw.rows, min(sw.n, (sw.rank + 1) * sw.rows)
+            for own, full in ((m, full_m), (v, full_v)):
+                own.zero_()
+                if hi > lo:
+                    own[:(hi - lo) * sw.k].copy_(full[lo:hi].reshape(-1).to(own.device, own.dtype))
