@@ -302,3 +302,36 @@ if __name__ == "__main__":
         cpu_worker(int(sys.argv[1]), int(sys.argv[2]), Path(sys.argv[3]))
     else:
         worker(int(sys.argv[1]), int(sys.argv[2]), Path(sys.argv[3]))
+
+
+def test_gather_chunk_and_flag_arithmetic_mirrors_the_kernel():
+    """CPU mirror of the index arithmetic of the gather warps and of the producer's wait in
+    `gemm2_kernel<..., GATHER=true>`: every weight row is copied exactly once, no chunk straddles two
+    shards, and the number of chunks counted into a 128-row block equals what the producer waits for."""
+    import re
+    src = (ROOT / "warpstate_ai_b200" / "ops" / "csrc" / "gemm2_tcgen05.cu").read_text()
+    rows_per_chunk = int(re.search(r"constexpr int GATHER_ROWS = (\d+);", src).group(1))
+    block = int(re.search(r"constexpr int GATHER_BLOCK = (\d+);", src).group(1))
+    assert block % rows_per_chunk == 0 and 8 % rows_per_chunk == 0
+    for total_rows, h in [(1000, 0), (10240, 0), (1024, 0), (2 * 384, 384), (2 * 7168, 7168), (2 * 128, 128)]:
+        for world in (1, 2, 3, 8):
+            per = rows_per_shard(total_rows, world)
+            chunks = (total_rows + rows_per_chunk - 1) // rows_per_chunk
+            covered = [0] * total_rows
+            counted = {}
+            for c in range(chunks):
+                row0 = (c & 1) * h + (c >> 1) * rows_per_chunk if h else c * rows_per_chunk
+                rows = min(rows_per_chunk, total_rows - row0)
+                assert rows > 0 and row0 // per == (row0 + rows - 1) // per, (total_rows, h, world, c)
+                for r in range(row0, row0 + rows):
+                    covered[r] += 1
+                counted[row0 // block] = counted.get(row0 // block, 0) + 1
+            assert all(v == 1 for v in covered), (total_rows, h, world)
+            n_tile = 128 if h else 256
+            out_features = h if h else total_rows
+            for nb in range((out_features + n_tile - 1) // n_tile):
+                for rank in (0, 1):
+                    b = (h // block + nb if rank else nb) if h else 2 * nb + rank
+                    block_rows = min(block, total_rows - b * block)
+                    want = 0 if block_rows <= 0 else (block_rows + rows_per_chunk - 1) // rows_per_chunk
+                    assert counted.get(b, 0) == want, (total_rows, h, world, nb, rank)
