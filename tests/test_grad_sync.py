@@ -252,3 +252,33 @@ def test_fused_sync_training_matches_nccl_sync(tmp_path):
 
 if __name__ == "__main__":
     worker(sys.argv[1], int(sys.argv[2]), int(sys.argv[3]), Path(sys.argv[4]))
+
+
+def test_allreduce_loop_partition_mirrors_the_kernel():
+    """CPU mirror of the element loop of `grad_allreduce_kernel` (four pieces per thread and pass, then a
+    one-piece tail): every 16-byte piece of a rank's slice is handled exactly once, in increasing order per
+    thread, for ragged slice lengths and CTA counts."""
+    import re
+    src = (ROOT / "warpstate_ai_b200" / "ops" / "csrc" / "comm.cu").read_text()
+    unroll = int(re.search(r"constexpr int U = (\d+);", src).group(1))
+    threads = int(re.search(r"constexpr int COMM_THREADS = (\d+);", src).group(1))
+    for count4, world, ctas in [(1, 2, 1), (1000, 2, 3), (4096 + 7, 8, 4), (100000, 3, 16)]:
+        per = (count4 + world - 1) // world
+        seen = [0] * count4
+        for rank in range(world):
+            lo, hi = per * rank, min(count4, per * rank + per)
+            stride = ctas * threads
+            for cta in range(ctas):
+                for tid in range(threads):
+                    order = []
+                    i = lo + cta * threads + tid
+                    while i + (unroll - 1) * stride < hi:
+                        order += [i + u * stride for u in range(unroll)]
+                        i += unroll * stride
+                    while i < hi:
+                        order.append(i)
+                        i += stride
+                    assert order == sorted(order)
+                    for index in order:
+                        seen[index] += 1
+        assert all(v == 1 for v in seen), (count4, world, ctas)
