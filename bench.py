@@ -15,7 +15,11 @@ barrier and a device synchronize, max over ranks:
   * `e2e`: wall-clock time of `Trainer.pretrain_update`, the public call, which every step copies
     its micro-batches from pinned host memory and reads loss and gradient norm back to the host.
 Inputs are larger than L2 by construction (8 GB of gradients, 4 GB of BF16 weights and tens of GB
-of activations stream through every update).
+of activations stream through every update).  Every update (warm-up and timed, both regions, both
+arms) reads the next window of the token stream, so no batch is seen twice.
+
+The JSON line keeps the workload definition in `config` (identical in both arms), what the arm is
+built from in `arm`, and what the run produced (loss, gradient norm, peak memory) in `result`.
 """
 from __future__ import annotations
 
@@ -43,6 +47,11 @@ def parse():
     ap.add_argument("--grad-sync", default="auto", help="auto | fused | nccl (multi-GPU gradient path)")
     ap.add_argument("--shard-optimizer", action="store_true",
                     help="multi-GPU: sharded AdamW state with the fused update-and-broadcast kernel")
+    ap.add_argument("--shard-params", choices=["off", "stream", "resident"], default="off",
+                    help="fully sharded parameters, gradients and optimizer state for the core projections "
+                         "(stream: re-gather every use; resident: keep the gathered BF16 weights for the update)")
+    ap.add_argument("--activation-checkpointing", action="store_true")
+    ap.add_argument("--bf16-residuals", action="store_true")
     ap.add_argument("--ref-compile-mode", default=os.environ.get("WARPSTATE_REF_COMPILE_MODE", "default"))
     return ap.parse_args()
 
@@ -90,7 +99,9 @@ def model_config(name: str):
     return cfg
 
 
-def emit(args, rank, world, metric_value, ms_per_step, e2e_value, clocks, launches, impl, extra_cfg, h2d, d2h):
+def emit(args, rank, world, metric_value, ms_per_step, e2e_value, clocks, launches, impl, arm, result, h2d, d2h):
+    """One JSON line from rank 0.  `config` names the workload and is the same dict in both arms; `arm` says
+    what this arm is built from; `result` is what the run produced."""
     if rank != 0:
         return
     global_batch = args.micro_batch * args.grad_accum * world
@@ -101,18 +112,28 @@ def emit(args, rank, world, metric_value, ms_per_step, e2e_value, clocks, launch
         "vs_baseline": (metric_value / BASELINE_TOKS) if args.model == "2b" else None,
         "dtype": "bf16", "data": "synthetic uniform-random tokens; random-init normal(0,0.02) weights",
         "impl": impl,
-        "config": dict({"model": "warpstate-2.005B" if args.model == "2b" else "warpstate-smoke",
-                        "global_batch": global_batch, "seq_len": args.seq_len,
-                        "micro_batch": args.micro_batch, "grad_accum": args.grad_accum,
-                        "tokens_per_update": global_batch * args.seq_len,
-                        "parallelism": f"dp{world}", "master_dtype": "fp32", "grad_dtype": "fp32",
-                        "l2": "working set per update (weights 4 GB bf16 + grads 8 GB + activations) far exceeds the 126 MB L2"},
-                       **extra_cfg),
+        "config": {"model": "warpstate-2.005B" if args.model == "2b" else "warpstate-smoke",
+                   "global_batch": global_batch, "seq_len": args.seq_len,
+                   "micro_batch": args.micro_batch, "grad_accum": args.grad_accum,
+                   "tokens_per_update": global_batch * args.seq_len,
+                   "parallelism": f"dp{world}", "master_dtype": "fp32", "grad_dtype": "fp32",
+                   "batches": "a fresh window of the token stream every update",
+                   "l2": "working set per update (weights 4 GB bf16 + grads 8 GB + activations) far exceeds the 126 MB L2",
+                   "value_region": "device-timed updates on micro-batches already resident on the device",
+                   "e2e_region": "public update call: pinned-host inputs copied every step, loss and norm read back"},
+        "arm": arm,
+        "result": result,
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches,
     }
     print(json.dumps(line), flush=True)
+
+
+def stream_tokens(args, world: int) -> int:
+    """Length of the synthetic stream: one window per update of either region plus warm-up."""
+    update_tokens = args.micro_batch * args.seq_len * args.grad_accum * world
+    return update_tokens * (args.warmup + 2 * args.steps) + 1
 
 
 # ----------------------------------------------------------------------------------- ours
@@ -128,41 +149,50 @@ def run_ours(args):
 
     _ext.require()
     cfg = model_config(args.model)
+    cfg.gradient_checkpointing = bool(args.activation_checkpointing)
     torch.manual_seed(1337)
     with torch.device(device):
         model = WarpStateLM(cfg)
     model.train()
+    if args.bf16_residuals:
+        model.bf16_residuals = True
     sync = None
     if world > 1:
         from warpstate_ai_b200.parallel.grad_sync import make_grad_sync
         sync = make_grad_sync(device, world, rank, None, kind=args.grad_sync)
     trainer = Trainer(model, device=device, rank=rank, world_size=world, lr=1.5e-4, weight_decay=0.1,
-                      grad_sync=sync, shard_optimizer=args.shard_optimizer)
+                      grad_sync=sync, shard_optimizer=args.shard_optimizer,
+                      shard_params=None if args.shard_params == "off" else args.shard_params)
     mb, T, acc = args.micro_batch, args.seq_len, args.grad_accum
     update_tokens = mb * T * acc * world
-    data = SyntheticTokens(update_tokens * 3 + 1, cfg.vocab_size, seed=7)
+    data = SyntheticTokens(stream_tokens(args, world), cfg.vocab_size, seed=7)
     batcher = HostBatcher(mb, T, device)
     lr = 1.5e-4
-
-    # ---- device-resident inputs for the kernel-timed region
-    resident = []
-    for offset, valid in update_slices(update_tokens, mb * T, world, rank):
-        x, y = host_batch(data, offset, mb, T, valid)
-        resident.append((x.to(device), y.to(device), valid))
-
-    def resident_update():
-        trainer.begin_update()
-        for index, (x, y, valid) in enumerate(resident):
-            def loss_fn(x=x, y=y, valid=valid):
-                _, loss = model(x, y, return_logits=False)
-                return loss, valid * world / update_tokens, valid / update_tokens
-            trainer.micro_step(loss_fn, last=index == len(resident) - 1)
-        return trainer.finish_update(lr)
 
     cursor = 0
     for _ in range(args.warmup):
         trainer.pretrain_update(data, cursor, update_tokens, mb, T, lr, batcher)
         cursor += update_tokens
+
+    # ---- device-resident inputs for the kernel-timed region: a different window for every step
+    resident = []
+    for step in range(args.steps):
+        micro = []
+        for offset, valid in update_slices(update_tokens, mb * T, world, rank):
+            x, y = host_batch(data, cursor + offset, mb, T, valid)
+            micro.append((x.to(device), y.to(device), valid))
+        resident.append(micro)
+        cursor += update_tokens
+
+    def resident_update(micro):
+        trainer.begin_update()
+        for index, (x, y, valid) in enumerate(micro):
+            def loss_fn(x=x, y=y, valid=valid):
+                _, loss = model(x, y, return_logits=False)
+                return loss, valid * world / update_tokens, valid / update_tokens
+            trainer.micro_step(loss_fn, last=index == len(micro) - 1)
+        return trainer.finish_update(lr)
+
     # ---- region 1: device-timed
     barrier_sync(world)
     sampler = ClockSampler()
@@ -172,18 +202,19 @@ def run_ours(args):
     start = torch.cuda.Event(enable_timing=True)
     stop = torch.cuda.Event(enable_timing=True)
     start.record()
-    for _ in range(args.steps):
-        stats = resident_update()
+    for micro in resident:
+        stats = resident_update(micro)
     stop.record()
     barrier_sync(world)
     launches = _ext.launch_count() - launches0
     dev_s = max_over_ranks(start.elapsed_time(stop) / 1e3, world, device)
-    norm = float(stats[0])
+    trainer.read_update_scalars(stats)  # raises if the device reported a communication error
     # ---- region 2: end to end through the public API
     barrier_sync(world)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        result = trainer.pretrain_update(data, cursor % update_tokens, update_tokens, mb, T, lr, batcher)
+        result = trainer.pretrain_update(data, cursor, update_tokens, mb, T, lr, batcher)
+        cursor += update_tokens
     barrier_sync(world)
     e2e_s = max_over_ranks(time.perf_counter() - t0, world, device)
     clocks = sampler.stop(gpu_indices=None) if rank == 0 else {}
@@ -191,9 +222,14 @@ def run_ours(args):
     check_device_errors()
     tokens = update_tokens * args.steps
     h2d = batcher.bytes_per_batch * acc * world
-    emit(args, rank, world, tokens / dev_s, dev_s / args.steps * 1e3, tokens / e2e_s, clocks, launches, "ours",
-         {"last_loss": result.loss, "last_grad_norm": norm, "grad_sync": getattr(sync, "kind", "none"),
-          "optimizer": "sharded" if (args.shard_optimizer and world > 1) else "replicated",
+    sharded = args.shard_params != "off"
+    arm = {"grad_sync": getattr(trainer.sync, "kind", "none"),
+           "optimizer": "sharded" if ((args.shard_optimizer or sharded) and world > 1) else "replicated",
+           "params": f"sharded-{args.shard_params}" if sharded else "replicated",
+           "activation_checkpointing": bool(args.activation_checkpointing),
+           "bf16_residuals": bool(args.bf16_residuals)}
+    emit(args, rank, world, tokens / dev_s, dev_s / args.steps * 1e3, tokens / e2e_s, clocks, launches, "ours", arm,
+         {"last_loss": result.loss, "last_grad_norm": result.grad_norm,
           "peak_mem_gib": torch.cuda.max_memory_allocated(device) / 2**30}, h2d, 12 * world)
     if world > 1:
         import torch.distributed as dist
@@ -254,15 +290,17 @@ def run_reference(args):
     mb, T, acc = args.micro_batch, args.seq_len, args.grad_accum
     update_tokens = mb * T * acc * world
     rng = np.random.default_rng(7)
-    data = rng.integers(0, cfg.vocab_size, size=update_tokens * 3 + 1, dtype=np.uint16)
+    data = rng.integers(0, cfg.vocab_size, size=stream_tokens(args, world), dtype=np.uint16)
+    slices = list(ref_run.update_slices(update_tokens, mb * T, world, rank))
 
-    def update(seen):
+    def update(micro):
+        """``micro``: per accumulation step a callable returning the (x, y) pair on the device, and its
+        number of valid tokens."""
         optimizer.zero_grad(set_to_none=True)
         loss_sum = torch.zeros((), device=device)
-        slices = list(ref_run.update_slices(update_tokens, mb * T, world, rank))
-        for index, (offset, valid) in enumerate(slices):
-            x, y = ref_run.batches(data, seen + offset, mb, T, valid, device)
-            sync = model.no_sync() if world > 1 and index < len(slices) - 1 else contextlib.nullcontext()
+        for index, (fetch, valid) in enumerate(micro):
+            x, y = fetch()
+            sync = model.no_sync() if world > 1 and index < len(micro) - 1 else contextlib.nullcontext()
             with sync:
                 with torch.autocast("cuda", dtype=torch.bfloat16, cache_enabled=True):
                     _, loss = model(x, y, return_logits=False)
@@ -272,11 +310,25 @@ def run_reference(args):
         optimizer.step()
         if world > 1:
             dist.all_reduce(loss_sum, op=dist.ReduceOp.SUM)
-        return float(loss_sum), float(norm)
+        return loss_sum, norm
+
+    def from_host(seen):
+        """The reference's own loader: pinned host window -> device, inside the step."""
+        return [((lambda o=offset, v=valid: ref_run.batches(data, seen + o, mb, T, v, device)), valid)
+                for offset, valid in slices]
 
     seen = 0
     for _ in range(args.warmup):
-        update(seen)
+        update(from_host(seen))
+        seen += update_tokens
+    # device-resident micro-batches for the device-timed region, produced by the reference's loader
+    resident = []
+    for _ in range(args.steps):
+        micro = []
+        for offset, valid in slices:
+            pair = ref_run.batches(data, seen + offset, mb, T, valid, device)
+            micro.append(((lambda p=pair: p), valid))
+        resident.append(micro)
         seen += update_tokens
     barrier_sync(world)
     sampler = ClockSampler()
@@ -284,19 +336,26 @@ def run_reference(args):
         sampler.start()
     start = torch.cuda.Event(enable_timing=True)
     stop = torch.cuda.Event(enable_timing=True)
-    t0 = time.perf_counter()
     start.record()
-    for _ in range(args.steps):
-        loss, norm = update(seen % update_tokens)
+    for micro in resident:
+        update(micro)
     stop.record()
     barrier_sync(world)
-    wall = max_over_ranks(time.perf_counter() - t0, world, device)
     dev_s = max_over_ranks(start.elapsed_time(stop) / 1e3, world, device)
+    barrier_sync(world)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        loss_t, norm_t = update(from_host(seen))
+        loss, norm = float(loss_t), float(norm_t)  # the reference reads both every update (run_40b.py:757-764)
+        seen += update_tokens
+    barrier_sync(world)
+    wall = max_over_ranks(time.perf_counter() - t0, world, device)
     clocks = sampler.stop() if rank == 0 else {}
     tokens = update_tokens * args.steps
     emit(args, rank, world, tokens / dev_s, dev_s / args.steps * 1e3, tokens / wall, clocks, 0, "reference",
-         {"last_loss": loss, "last_grad_norm": norm, "compile_mode": args.ref_compile_mode,
-          "loss_mode": "compiled-full", "ddp_bucket_cap_mb": 128,
+         {"compile_mode": args.ref_compile_mode, "loss_mode": "compiled-full", "ddp_bucket_cap_mb": 128,
+          "optimizer": "torch.optim.AdamW(fused=True)"},
+         {"last_loss": loss, "last_grad_norm": norm,
           "peak_mem_gib": torch.cuda.max_memory_allocated(device) / 2**30},
          2 * mb * T * 8 * acc * world, 8 * world)
     if world > 1:

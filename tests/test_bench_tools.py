@@ -24,7 +24,7 @@ def test_sweep_separates_exposed_and_hidden_communication():
                      "Collective name": "allreduce", "In msg nelems": 1024, "dtype": "Float"}),
               kernel("ncclDevKernel_AllReduce_Sum_f32", 85, 30, **{"Process Group Name": "0", "Seq": 7,
                      "Collective name": "allreduce", "In msg nelems": 1024, "dtype": "Float"}),
-              kernel("ws::grad_allreduce_kernel(ws::PeerTable, float*)", 190, 30),
+              kernel("ws::grad_reduce_kernel(ws::PeerTable, float*)", 190, 30),
               {"ph": "X", "cat": "gpu_memcpy", "name": "Memcpy HtoD", "ts": 300, "dur": 10, "args": {"device": 0}},
               {"ph": "X", "cat": "gpu_user_annotation", "name": "range", "ts": 0, "dur": 500, "args": {"device": 0}},
               {"ph": "X", "cat": "cpu_op", "name": "c10d::allreduce_", "ts": 1, "dur": 1, "args": {"Input Dims": [[1024]]}}]
@@ -39,7 +39,7 @@ def test_sweep_separates_exposed_and_hidden_communication():
     assert d["activity_span_us"] == pytest.approx(310)
     assert d["communication_overlap_fraction"] == pytest.approx(30 / 70)
     assert d["collective_call_count"] == 1 and d["logical_input_payload_bytes"] == 4096  # two channel kernels, one call
-    assert d["own_collective_kernels"] == {"ws::grad_allreduce_kernel": 1}
+    assert d["own_collective_kernels"] == {"ws::grad_reduce_kernel": 1}
     assert report["cpu_collective_fingerprint"]["call_count"] == 1
     with pytest.raises(ValueError):
         CP.summarize_trace({"traceEvents": [kernel("k", 0, -1)]})

@@ -255,7 +255,7 @@ if __name__ == "__main__":
 
 
 def test_allreduce_loop_partition_mirrors_the_kernel():
-    """CPU mirror of the element loop of `grad_allreduce_kernel` (four pieces per thread and pass, then a
+    """CPU mirror of the element loop of `grad_reduce_kernel` (four pieces per thread and pass, then a
     one-piece tail): every 16-byte piece of a rank's slice is handled exactly once, in increasing order per
     thread, for ragged slice lengths and CTA counts."""
     import re

@@ -1,4 +1,4 @@
-"""In-kernel gradient all-reduce (`grad_allreduce_kernel`, ops/csrc/comm.cu) against NCCL all_reduce.
+"""In-kernel gradient all-reduce (`bucket_ready_kernel` + `grad_reduce_kernel`, ops/csrc/comm.cu) against NCCL all_reduce.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port 29561 \
         -m warpstate_ai_b200.bench.allreduce_bench [--mib 128 1024] [--ctas 16 32 64]

@@ -2,7 +2,8 @@
 
 For every rank and device of the given traces (``train_bench --profile`` writes them) the tool
 classifies each device activity as communication -- NCCL kernels and this framework's own
-collective kernels (``grad_allreduce_kernel``, ``adamw_shard_push_kernel``) -- or compute
+collective kernels (``grad_reduce_kernel`` and its ``bucket_ready_kernel``, ``norm_exchange_kernel``, ``gather_cast_kernel``,
+``adamw_shard_push_kernel``) -- or compute
 (every other kernel, copies and fills), and sweeps the interval boundaries once to get, in
 microseconds: time with only compute running, only communication running (the *exposed*
 communication), both, and idle time inside the traced span.  For NCCL kernels the logical
@@ -26,7 +27,8 @@ from collections import Counter
 from pathlib import Path
 
 ACTIVITY = {"kernel", "gpu_memcpy", "gpu_memset"}
-OWN_COLLECTIVES = ("grad_allreduce_kernel", "adamw_shard_push_kernel")
+OWN_COLLECTIVES = ("grad_reduce_kernel", "bucket_ready_kernel", "norm_exchange_kernel", "node_barrier_kernel",
+                   "gather_cast_kernel", "adamw_shard_push_kernel")
 C10D_PREFIX = "c10d::"
 DTYPE_BYTES = {"float": 4, "float32": 4, "double": 8, "float64": 8, "half": 2, "float16": 2, "bfloat16": 2,
                "long": 8, "int64": 8, "int": 4, "int32": 4, "short": 2, "int16": 2, "char": 1, "int8": 1,

@@ -20,11 +20,12 @@ CATEGORIES = [
     ("attention", ("attn_fwd_kernel", "attn_bwd_kernel", "chunk_writes_kernel", "dstate_kernel", "memory_scan")),
     ("lm_head", ("lmhead", "ce_")),
     ("norm", ("rmsnorm", "colsum")),
-    ("communication", ("nccl", "grad_allreduce", "adamw_shard_push")),
+    ("communication", ("nccl", "grad_reduce", "bucket_ready", "norm_exchange", "node_barrier", "gather_cast", "adamw_shard_push")),
     ("optimizer", ("adamw_kernel", "sumsq_kernel", "clip_coef")),
     ("embedding", ("embed_",)),
     ("cast", ("cast_f32_bf16",)),
-    ("communication", ("nccl", "grad_allreduce", "adamw_shard_push", "allreduce", "allgather", "all_gather")),
+    ("communication", ("nccl", "grad_reduce", "bucket_ready", "norm_exchange", "node_barrier", "gather_cast", "adamw_shard_push",
+                       "allreduce", "allgather", "all_gather")),
     ("copies", ("Memcpy", "memcpy", "Memset", "memset")),
 ]
 

@@ -53,9 +53,11 @@ def update_slices(target: int, micro_tokens: int, world_size: int, rank: int) ->
 
 
 class HostBatcher:
-    """Pinned double-buffered staging of micro-batches with a copy stream."""
+    """Pinned staging of micro-batches with a copy stream.  Three slots: the slot that `stage` refills for
+    micro-batch k+1 was last read by micro-batch k-2, so the host never waits for the micro-batch the
+    device is still working on and the launch queue stays ahead of the GPU."""
 
-    def __init__(self, batch: int, length: int, device: torch.device, depth: int = 2):
+    def __init__(self, batch: int, length: int, device: torch.device, depth: int = 3):
         self.batch, self.length, self.device = batch, length, device
         self.cuda = device.type == "cuda"
         self.depth = depth

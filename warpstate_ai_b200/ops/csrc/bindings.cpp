@@ -345,21 +345,47 @@ std::tuple<at::Tensor, at::Tensor> attn_bwd(const at::Tensor& qkvgu, const at::T
 }
 
 // ----------------------------------------------------------------------------- optimizer
-at::Tensor grad_norm_clip(const at::Tensor& g, double max_norm, const c10::optional<at::Tensor>& extra_sumsq) {
+static const int* opt_status(const c10::optional<at::Tensor>& status) {
+  if (!status.has_value() || !status->defined()) return nullptr;
+  TORCH_CHECK(status->is_cuda() && status->scalar_type() == at::kInt && status->numel() >= 1, "status: int32 CUDA tensor");
+  return status->data_ptr<int>();
+}
+static const float* opt_f32(const c10::optional<at::Tensor>& t, const char* what) {
+  if (!t.has_value() || !t->defined()) return nullptr;
+  TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kFloat && t->numel() >= 1, what);
+  return t->data_ptr<float>();
+}
+
+// -> stats [8] FP32: norm, clip coefficient, norm^2, skip flag (the rest is zero)
+at::Tensor grad_norm_clip(const at::Tensor& g, double max_norm, const c10::optional<at::Tensor>& extra_sumsq,
+                          const c10::optional<at::Tensor>& status) {
   TORCH_CHECK(g.is_cuda() && g.scalar_type() == at::kFloat && g.is_contiguous() && g.numel() % 4 == 0,
               "grad_norm_clip: flat float32 buffer with numel % 4 == 0 required");
   c10::cuda::CUDAGuard guard(g.device());
   at::Tensor partial = at::empty({ws_sumsq_parts()}, g.options());
-  at::Tensor stats = at::empty({3}, g.options());
-  const float* extra = extra_sumsq.has_value() && extra_sumsq->defined() ? extra_sumsq->data_ptr<float>() : nullptr;
-  check_rc(ws_grad_norm_clip(g.data_ptr<float>(), (size_t)g.numel(), partial.data_ptr<float>(), extra,
-                             (float)max_norm, stats.data_ptr<float>(), cur_stream()), "grad_norm_clip");
+  at::Tensor stats = at::zeros({8}, g.options());
+  check_rc(ws_grad_norm_clip(g.data_ptr<float>(), (size_t)g.numel(), partial.data_ptr<float>(),
+                             opt_f32(extra_sumsq, "grad_norm_clip: extra_sumsq"), (float)max_norm, opt_status(status),
+                             stats.data_ptr<float>(), cur_stream()), "grad_norm_clip");
+  return stats;
+}
+
+at::Tensor clip_from_partials(const at::Tensor& partial, double max_norm, const c10::optional<at::Tensor>& extra_sumsq,
+                              const c10::optional<at::Tensor>& status) {
+  TORCH_CHECK(partial.is_cuda() && partial.scalar_type() == at::kFloat && partial.is_contiguous() && partial.numel() >= 1,
+              "clip_from_partials: float32 CUDA partial sums required");
+  c10::cuda::CUDAGuard guard(partial.device());
+  at::Tensor stats = at::zeros({8}, partial.options());
+  check_rc(ws_clip_from_partials(partial.data_ptr<float>(), (int)partial.numel(),
+                                 opt_f32(extra_sumsq, "clip_from_partials: extra_sumsq"), (float)max_norm,
+                                 opt_status(status), stats.data_ptr<float>(), cur_stream()), "clip_from_partials");
   return stats;
 }
 
 void adamw_step(at::Tensor p, const at::Tensor& g, at::Tensor m, at::Tensor v, c10::optional<at::Tensor> p_bf16,
                 double lr, double beta1, double beta2, double eps, double wd, int64_t step,
-                const c10::optional<at::Tensor>& grad_scale, double grad_scale_const) {
+                const c10::optional<at::Tensor>& grad_scale, double grad_scale_const,
+                const c10::optional<at::Tensor>& skip) {
   TORCH_CHECK(p.is_cuda() && p.scalar_type() == at::kFloat && p.is_contiguous(), "adamw_step: p");
   TORCH_CHECK(g.numel() == p.numel() && m.numel() == p.numel() && v.numel() == p.numel(), "adamw_step: sizes");
   TORCH_CHECK(g.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat &&
@@ -374,7 +400,7 @@ void adamw_step(at::Tensor p, const at::Tensor& g, at::Tensor m, at::Tensor v, c
   const float* gs = grad_scale.has_value() && grad_scale->defined() ? grad_scale->data_ptr<float>() : nullptr;
   check_rc(ws_adamw(p.data_ptr<float>(), g.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), pb,
                     (size_t)p.numel(), (float)lr, (float)beta1, (float)beta2, (float)eps, (float)wd, (int)step, gs,
-                    (float)grad_scale_const, cur_stream()), "adamw_step");
+                    (float)grad_scale_const, opt_f32(skip, "adamw_step: skip"), cur_stream()), "adamw_step");
 }
 
 int64_t launch_count() { return (int64_t)ws_launch_count(); }
@@ -476,10 +502,78 @@ void wait_probe(const at::Tensor& flag, int64_t expected, at::Tensor status, dou
                          status.data_ptr<int>(), budget_seconds, cur_stream()), "wait_probe");
 }
 
+void grad_reduce_segments(at::IntArrayRef grad_ptrs, at::IntArrayRef flag_ptrs, int64_t mc_grad, int64_t rank,
+                          int64_t world, at::IntArrayRef starts, at::IntArrayRef counts, at::IntArrayRef push,
+                          int64_t bucket, int64_t seq, double scale, int64_t ctas, c10::optional<at::Tensor> sumsq_out,
+                          at::Tensor status, double budget_seconds) {
+  TORCH_CHECK((int64_t)grad_ptrs.size() == world && (int64_t)flag_ptrs.size() == world, "grad_reduce_segments: peer tables");
+  TORCH_CHECK(starts.size() == counts.size() && starts.size() == push.size() && !starts.empty() && starts.size() <= 6,
+              "grad_reduce_segments: 1..6 segments with start, count and push each");
+  TORCH_CHECK(status.is_cuda() && status.scalar_type() == at::kInt && status.numel() >= 8, "grad_reduce_segments: status");
+  c10::cuda::CUDAGuard guard(status.device());
+  float* ss = nullptr;
+  if (sumsq_out.has_value() && sumsq_out->defined()) {
+    TORCH_CHECK(sumsq_out->scalar_type() == at::kFloat && sumsq_out->numel() >= ctas && sumsq_out->is_contiguous(),
+                "grad_reduce_segments: sumsq_out");
+    ss = sumsq_out->data_ptr<float>();
+  }
+  size_t st[6], ct[6];
+  int pu[6];
+  for (size_t i = 0; i < starts.size(); ++i) {
+    TORCH_CHECK(starts[i] >= 0 && counts[i] >= 0, "grad_reduce_segments: negative range");
+    st[i] = (size_t)starts[i]; ct[i] = (size_t)counts[i]; pu[i] = push[i] ? 1 : 0;
+  }
+  auto g = ptr_table(grad_ptrs), f = ptr_table(flag_ptrs);
+  check_rc(ws_grad_reduce_segments(g.data(), f.data(), (unsigned long long)mc_grad, (int)rank, (int)world, st, ct, pu,
+                                   (int)starts.size(), (int)bucket, (unsigned)seq, (float)scale, (int)ctas, ss,
+                                   status.data_ptr<int>(), budget_seconds, cur_stream()), "grad_reduce_segments");
+}
+
+// -> stats [8] FP32: global norm, clip coefficient, norm^2, skip flag, loss summed over ranks
+at::Tensor norm_exchange(at::IntArrayRef flag_ptrs, int64_t rank, int64_t world, int64_t base_word, int64_t seq,
+                         const at::Tensor& partial, const c10::optional<at::Tensor>& local_loss, double max_norm,
+                         at::Tensor status, double budget_seconds) {
+  TORCH_CHECK((int64_t)flag_ptrs.size() == world, "norm_exchange: peer table");
+  TORCH_CHECK(partial.is_cuda() && partial.scalar_type() == at::kFloat && partial.is_contiguous() && partial.numel() >= 1,
+              "norm_exchange: partial");
+  TORCH_CHECK(status.is_cuda() && status.scalar_type() == at::kInt && status.numel() >= 8, "norm_exchange: status");
+  c10::cuda::CUDAGuard guard(partial.device());
+  at::Tensor stats = at::zeros({8}, partial.options());
+  auto f = ptr_table(flag_ptrs);
+  check_rc(ws_norm_exchange(f.data(), (int)rank, (int)world, (int)base_word, (unsigned)seq, partial.data_ptr<float>(),
+                            (int)partial.numel(), opt_f32(local_loss, "norm_exchange: local_loss"), (float)max_norm,
+                            status.data_ptr<int>(), stats.data_ptr<float>(), budget_seconds, cur_stream()),
+           "norm_exchange");
+  return stats;
+}
+
+void node_barrier(at::IntArrayRef flag_ptrs, int64_t rank, int64_t world, int64_t base_word, int64_t seq,
+                  at::Tensor status, double budget_seconds) {
+  TORCH_CHECK((int64_t)flag_ptrs.size() == world, "node_barrier: peer table");
+  TORCH_CHECK(status.is_cuda() && status.scalar_type() == at::kInt && status.numel() >= 8, "node_barrier: status");
+  c10::cuda::CUDAGuard guard(status.device());
+  auto f = ptr_table(flag_ptrs);
+  check_rc(ws_node_barrier(f.data(), (int)rank, (int)world, (int)base_word, (unsigned)seq, status.data_ptr<int>(),
+                           budget_seconds, cur_stream()), "node_barrier");
+}
+
+// wb [n, k] BF16 (local) = cast of the row-sharded FP32 weight (shard addresses as mapped in this process)
+void gather_cast(std::vector<int64_t> shard_ptrs, int64_t rows_per_shard, at::Tensor wb, int64_t ctas) {
+  TORCH_CHECK(wb.is_cuda() && wb.scalar_type() == at::kBFloat16 && wb.is_contiguous() && wb.dim() == 2,
+              "gather_cast: wb must be contiguous BF16 [n, k]");
+  const int64_t world = (int64_t)shard_ptrs.size();
+  TORCH_CHECK(world >= 1 && world <= 8, "gather_cast: 1..8 shards");
+  const void* shards[8] = {};
+  for (int64_t r = 0; r < world; ++r) shards[r] = reinterpret_cast<const void*>(static_cast<uintptr_t>(shard_ptrs[r]));
+  c10::cuda::CUDAGuard guard(wb.device());
+  check_rc(ws_gather_cast(shards, (int)world, (int)rows_per_shard, (int)wb.size(0), (int)wb.size(1), wb.data_ptr(),
+                          (int)ctas, cur_stream()), "gather_cast");
+}
+
 void adamw_shard_push(at::IntArrayRef master_ptrs, at::IntArrayRef bf16_ptrs, int64_t rank, int64_t world,
                       const at::Tensor& g, at::Tensor m, at::Tensor v, int64_t lo, int64_t n, double lr, double beta1,
                       double beta2, double eps, double wd, int64_t step, const c10::optional<at::Tensor>& grad_scale,
-                      bool push_master) {
+                      bool push_master, const c10::optional<at::Tensor>& skip) {
   TORCH_CHECK((int64_t)master_ptrs.size() == world && (int64_t)bf16_ptrs.size() == world, "adamw_shard_push: tables");
   TORCH_CHECK(g.is_cuda() && g.scalar_type() == at::kFloat && g.is_contiguous() && g.numel() >= lo + n, "adamw_shard_push: g");
   TORCH_CHECK(m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat && m.numel() == n && v.numel() == n &&
@@ -489,7 +583,8 @@ void adamw_shard_push(at::IntArrayRef master_ptrs, at::IntArrayRef bf16_ptrs, in
   const float* gs = grad_scale.has_value() && grad_scale->defined() ? grad_scale->data_ptr<float>() : nullptr;
   check_rc(ws_adamw_shard_push(mp.data(), bp.data(), (int)rank, (int)world, g.data_ptr<float>(), m.data_ptr<float>(),
                                v.data_ptr<float>(), (size_t)lo, (size_t)n, (float)lr, (float)beta1, (float)beta2,
-                               (float)eps, (float)wd, (int)step, gs, push_master ? 1 : 0, cur_stream()),
+                               (float)eps, (float)wd, (int)step, gs, push_master ? 1 : 0,
+                               opt_f32(skip, "adamw_shard_push: skip"), cur_stream()),
            "adamw_shard_push");
 }
 
@@ -513,8 +608,8 @@ std::tuple<at::Tensor, at::Tensor> gather_cast_linear(const at::Tensor& x, std::
   TORCH_CHECK(!swiglu || n % 128 == 0, "gather_cast_linear: the SwiGLU form needs a hidden width that is a multiple of 128");
   TORCH_CHECK(wb.is_cuda() && wb.scalar_type() == at::kBFloat16 && wb.is_contiguous() && wb.numel() == w_rows * k,
               "gather_cast_linear: wb must be contiguous BF16 with the weight's shape");
-  TORCH_CHECK(flags.is_cuda() && flags.scalar_type() == at::kInt && flags.is_contiguous() && flags.numel() >= (w_rows + 127) / 128,
-              "gather_cast_linear: flags must be int32 with one word per 128 weight rows");
+  TORCH_CHECK(flags.is_cuda() && flags.scalar_type() == at::kInt && flags.is_contiguous() && flags.numel() >= (w_rows + 127) / 128 + 1,
+              "gather_cast_linear: flags must be int32 with one word per 128 weight rows and one more");
   const void* shards[8] = {};
   for (int64_t r = 0; r < world; ++r) {
     TORCH_CHECK(shard_ptrs[r] != 0 && shard_ptrs[r] % 16 == 0, "gather_cast_linear: null or misaligned shard address");
@@ -670,16 +765,26 @@ TORCH_LIBRARY(ws_b200, m) {
   m.def("wait_probe(Tensor flag, int expected, Tensor(a!) status, float budget_seconds) -> ()");
   m.def("adamw_shard_push(int[] master_ptrs, int[] bf16_ptrs, int rank, int world, Tensor g, Tensor(a!) m, "
         "Tensor(b!) v, int lo, int n, float lr, float beta1, float beta2, float eps, float wd, int step, "
-        "Tensor? grad_scale, bool push_master) -> ()");
+        "Tensor? grad_scale, bool push_master, Tensor? skip=None) -> ()");
   m.def("attn_bwd(Tensor qkvgu, Tensor dy, Tensor states, Tensor writes, Tensor rope, Tensor fast_logit, "
         "Tensor slow_logit, Tensor mix_logit, int B, int T, int H, Tensor(a!)? error_flag) -> (Tensor, Tensor)");
   m.def("chunk_writes(Tensor qkvgu, Tensor rope, int B, int T, int H, Tensor(a!)? error_flag) -> Tensor");
   m.def("memory_scan(Tensor writes, Tensor fast_logit, Tensor slow_logit, Tensor mix_logit, bool want_states, "
         "bool want_final, Tensor? init_fast, Tensor? init_slow) -> (Tensor, Tensor, Tensor)");
   m.def("attn_fwd(Tensor qkvgu, Tensor states, Tensor rope, int B, int T, int H, Tensor(a!)? error_flag) -> Tensor");
-  m.def("grad_norm_clip(Tensor g, float max_norm, Tensor? extra_sumsq) -> Tensor");
+  m.def("grad_norm_clip(Tensor g, float max_norm, Tensor? extra_sumsq, Tensor? status=None) -> Tensor");
+  m.def("clip_from_partials(Tensor partial, float max_norm, Tensor? extra_sumsq=None, Tensor? status=None) -> Tensor");
+  m.def("grad_reduce_segments(int[] grad_ptrs, int[] flag_ptrs, int mc_grad, int rank, int world, int[] starts, "
+        "int[] counts, int[] push, int bucket, int seq, float scale, int ctas, Tensor(a!)? sumsq_out, "
+        "Tensor(b!) status, float budget_seconds) -> ()");
+  m.def("norm_exchange(int[] flag_ptrs, int rank, int world, int base_word, int seq, Tensor partial, "
+        "Tensor? local_loss, float max_norm, Tensor(a!) status, float budget_seconds) -> Tensor");
+  m.def("node_barrier(int[] flag_ptrs, int rank, int world, int base_word, int seq, Tensor(a!) status, "
+        "float budget_seconds) -> ()");
+  m.def("gather_cast(int[] shard_ptrs, int rows_per_shard, Tensor(a!) wb, int ctas) -> ()");
   m.def("adamw_step(Tensor(a!) p, Tensor g, Tensor(b!) m, Tensor(c!) v, Tensor(d!)? p_bf16, float lr, float beta1, "
-        "float beta2, float eps, float wd, int step, Tensor? grad_scale, float grad_scale_const) -> ()");
+        "float beta2, float eps, float wd, int step, Tensor? grad_scale, float grad_scale_const, "
+        "Tensor? skip=None) -> ()");
   m.def("gemm(Tensor a, Tensor b, bool a_mn, bool b_mn, int epilogue, int m, int n, int k, "
         "Tensor(a!) out, Tensor(b!)? out2, Tensor? aux, Tensor? row_scale, float alpha, float beta, "
         "Tensor(c!)? error_flag) -> ()");
@@ -706,6 +811,11 @@ TORCH_LIBRARY_IMPL(ws_b200, CUDA, m) {
   m.impl("embed_fwd", &embed_fwd);
   m.impl("embed_bwd", &embed_bwd);
   m.impl("grad_norm_clip", &grad_norm_clip);
+  m.impl("clip_from_partials", &clip_from_partials);
+  m.impl("grad_reduce_segments", &grad_reduce_segments);
+  m.impl("norm_exchange", &norm_exchange);
+  m.impl("node_barrier", &node_barrier);
+  m.impl("gather_cast", &gather_cast);
   m.impl("attn_bwd", &attn_bwd);
   m.impl("chunk_writes", &chunk_writes);
   m.impl("memory_scan", &memory_scan);

@@ -71,6 +71,7 @@ struct GatherJob {
   int n, k;                // k % 8 == 0
   __nv_bfloat16* dst;      // local BF16 [n, k]
   unsigned* flags;         // one word per 128-row block of W, zero at launch
+  unsigned* counter;       // next unclaimed chunk, zero at launch
   unsigned target;         // chunks per complete block
   int interleave_h;        // SwiGLU: h (n = 2h rows: up, then gate; h % 128 == 0); otherwise 0
   unsigned long long wait_ns;
@@ -573,13 +574,21 @@ gemm2_kernel(const __grid_constant__ PairGroup g, const __grid_constant__ Gather
   if constexpr (GATHER) {
     if (warp >= 2 + 4 * GROUPS) {
       // ---------------------------------------------------------------- weight gather (both CTAs)
-      // Chunk c = GATHER_ROWS rows of W; chunk c belongs to CTA c % gridDim.x, so the blocks complete
-      // in the order in which the tile loop needs them.  A thread converts 8 consecutive floats
-      // (two 16-byte loads, local or peer) into one 16-byte BF16 store.
+      // Chunk c = GATHER_ROWS rows of W.  A thread converts 8 consecutive floats (two 16-byte loads,
+      // local or peer) into one 16-byte BF16 store.
+      // Chunks are claimed from a counter in global memory, in order, by whichever CTAs are running: the
+      // tile loop of a CTA never depends on a CTA that is not resident yet (another kernel may hold SMs),
+      // and the blocks still complete in the order in which the tile loop needs them.
       const int gt = threadIdx.x - (2 + 4 * GROUPS) * 32;
       const int vec_per_row = gj.k / 8;
       const int chunks = (gj.n + GATHER_ROWS - 1) / GATHER_ROWS;
-      for (int c = blockIdx.x; c < chunks; c += gridDim.x) {
+      volatile int* chunk_slot = reinterpret_cast<volatile int*>(tmem_slot + 2);
+      while (true) {
+        if (gt == 0) *chunk_slot = static_cast<int>(atomicAdd(gj.counter, 1u));
+        asm volatile("bar.sync 3, %0;" ::"n"(GATHER_THREADS) : "memory");
+        const int c = *chunk_slot;
+        asm volatile("bar.sync 3, %0;" ::"n"(GATHER_THREADS) : "memory");
+        if (c >= chunks) break;
         // SwiGLU (W = h up rows, then h gate rows): even chunks walk the up rows, odd chunks the gate
         // rows, so that the two 128-row blocks of an N tile complete together
         const int row0 = gj.interleave_h > 0 ? (c & 1) * gj.interleave_h + (c >> 1) * GATHER_ROWS : c * GATHER_ROWS;
@@ -786,7 +795,7 @@ extern "C" int ws_gemm_pair(const WsGemm* g, int sms, cudaStream_t stream) {
 // y[m, n] = x[m, k] . W[n, k]^T where W is the row-sharded FP32 master weight of `world` ranks
 // (shards[r] = address, in this process, of rank r's [rows_per_shard, k] FP32 block; peers' blocks are
 // symmetric-memory mappings).  `wb` is this rank's BF16 landing buffer for the whole weight, `flags` a
-// device array of one word per 128 weight rows (zeroed here).  epilogue WS_EPI_BF16: W has n rows, out is
+// device array of one word per 128 weight rows plus one more (zeroed here).  epilogue WS_EPI_BF16: W has n rows, out is
 // BF16 [m, n].  WS_EPI_SWIGLU: W has 2n rows (n up rows, then n gate rows; n % 128 == 0), out is the packed
 // (up | gate) [m, 2n] (may be NULL), out2 the activation silu(gate) * up [m, n].  The caller guarantees that
 // no rank changes its shard while the kernel runs.  A bounded wait that runs out sets *error_flag to 6 and
@@ -835,12 +844,15 @@ extern "C" int ws_gather_gemm(const void* x, int m, int n, int k, const void* co
   job.interleave_h = swiglu ? n : 0;
   job.wait_ns = static_cast<unsigned long long>((budget_seconds > 0.f ? budget_seconds : 2.0f) * 1e9);
   const int blocks = (w_rows + GATHER_BLOCK - 1) / GATHER_BLOCK;
-  if (cudaMemsetAsync(flags, 0, sizeof(unsigned) * blocks, stream) != cudaSuccess) return -21;
-  // Every CTA must be resident at once (producers wait for chunks that other CTAs gather): the grid never
-  // exceeds one CTA per SM, and with fewer tiles than pairs the spare pairs still take gather chunks.
-  int pairs = (sms > 0 ? sms : 148) / 2;
+  job.counter = job.flags + blocks;  // the word after the block flags
+  if (cudaMemsetAsync(flags, 0, sizeof(unsigned) * (blocks + 1), stream) != cudaSuccess) return -21;
+  // Gather chunks are claimed dynamically by running CTAs, so no CTA waits for one that is not resident;
+  // with fewer tiles than pairs the spare pairs still take gather chunks.
+  int dev = 0, sm_count = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+  int pairs = (sms > 0 ? sms : sm_count) / 2;
   if (pairs < 1) pairs = 1;
-  if (pairs > 74) pairs = 74;
+  if (pairs > sm_count / 2) pairs = sm_count / 2;
   return swiglu ? launch_pair_gather<WS_EPI_SWIGLU>(grp, job, pairs, stream)
                 : launch_pair_gather<WS_EPI_BF16>(grp, job, pairs, stream);
 }

@@ -329,10 +329,10 @@ extern "C" int ws_rmsnorm_fwd(const void* x, int x_bf16, const float* col_scale,
 }
 
 // Number of partial rows ws_rmsnorm_bwd writes (the caller sizes dw_partial as parts*d floats).
+constexpr int kRmsBwdMaxParts = 148 * 3;  // three resident blocks per SM
 extern "C" int ws_rmsnorm_bwd_parts(int rows) {
   int blocks = (rows + RB_ROWS - 1) / RB_ROWS;
-  const int cap = 148 * 3;  // three resident blocks per SM
-  return blocks < cap ? (blocks > 0 ? blocks : 1) : cap;
+  return blocks < kRmsBwdMaxParts ? (blocks > 0 ? blocks : 1) : kRmsBwdMaxParts;
 }
 
 extern "C" int ws_rmsnorm_bwd(const void* dz, const void* x, int x_bf16, const float* rstd, const float* w,
@@ -431,6 +431,10 @@ extern "C" int ws_embed_bwd(const void* dx, int dx_bf16, const long long* sorted
 // Lives in every GPU that loads this library until the process exits.  In host code this name is
 // only a handle for cudaGetSymbolAddress, never a device address.
 static __device__ __align__(256) float g_static_scratch[WS_STATIC_SCRATCH_FLOATS];
+// The array is exactly what the largest accepted problem writes: the most partial rows the kernel ever
+// uses times the widest row it accepts.
+static_assert(WS_STATIC_SCRATCH_FLOATS == kRmsBwdMaxParts * 128 * MAX_CHUNKS,
+              "WS_STATIC_SCRATCH_FLOATS must equal the maximum number of partial rows times the maximum width");
 
 namespace {
 constexpr int kMaxDevices = 64;
@@ -458,7 +462,7 @@ extern "C" const char* ws_static_scratch_strerror(int code) {
     case WS_STATIC_ERR_BAD_SHAPE: return "rows must be positive and d a multiple of 128 not above 2048";
     case WS_STATIC_ERR_LAUNCH: return "kernel launch failed";
     case WS_STATIC_ERR_TOO_LARGE: return "problem needs more partial sums than the built-in scratch array holds "
-                                         "(blocks(rows) * d > WS_STATIC_SCRATCH_FLOATS)";
+                                         "(cannot happen while d <= 2048 is enforced; kept as a guard)";
     case WS_STATIC_ERR_SYMBOL: return "could not resolve the device address of the built-in scratch array";
     default: return "unknown error";
   }

@@ -48,10 +48,16 @@ sumsq_kernel(const float* __restrict__ g, size_t n4, float* __restrict__ partial
   if (threadIdx.x == 0) partial[blockIdx.x] = s;
 }
 
-// stats[0] = ||g||, stats[1] = clip coefficient min(1, max_norm/(||g||+1e-6)), stats[2] = ||g||^2.
+__device__ __forceinline__ bool not_finite(float x) { return (__float_as_uint(x) & 0x7f800000u) == 0x7f800000u; }
+
+// stats[0] = ||g||, stats[1] = clip coefficient min(1, max_norm/(||g||+1e-6)), stats[2] = ||g||^2,
+// stats[3] = skip flag: 1 when the norm is not finite or `status` (optional device word of a
+// communication kernel, 0 = no error) is non-zero.  The update kernels return without touching
+// parameters or moments when the flag is set, so a caller that raises on the host afterwards
+// still holds the state of the previous update.
 // `extra_sumsq` (optional) is added first: other ranks' shares when the gradient is sharded.
 __global__ void clip_coef_kernel(const float* __restrict__ partial, int parts, const float* extra_sumsq,
-                                 float max_norm, float* __restrict__ stats) {
+                                 float max_norm, const int* __restrict__ status, float* __restrict__ stats) {
   __shared__ float red[32];
   float s = 0.f;
   for (int i = threadIdx.x; i < parts; i += blockDim.x) s += partial[i];
@@ -61,9 +67,11 @@ __global__ void clip_coef_kernel(const float* __restrict__ partial, int parts, c
     const float norm = __fsqrt_rn(s);
     float coef = max_norm > 0.f ? __fdiv_rn(max_norm, norm + 1e-6f) : 1.0f;
     if (coef > 1.0f) coef = 1.0f;
+    const bool bad = not_finite(norm) || (status != nullptr && *status != 0);
     stats[0] = norm;
-    stats[1] = coef;
+    stats[1] = bad ? 0.0f : coef;
     stats[2] = s;
+    stats[3] = bad ? 1.0f : 0.0f;
   }
 }
 
@@ -75,7 +83,9 @@ __global__ void __launch_bounds__(OPT_THREADS)
 adamw_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
              float* __restrict__ v, __nv_bfloat16* __restrict__ p_bf16, size_t n4, float lr, float beta1,
              float beta2, float eps, float wd, float bias1, float bias2_sqrt,
-             const float* __restrict__ grad_scale_ptr, float grad_scale_const) {
+             const float* __restrict__ grad_scale_ptr, float grad_scale_const,
+             const float* __restrict__ skip_ptr) {
+  if (skip_ptr != nullptr && *skip_ptr != 0.0f) return;  // non-finite norm or failed gradient exchange
   const float gs = (grad_scale_ptr != nullptr ? *grad_scale_ptr : 1.0f) * grad_scale_const;
   const float decay = 1.0f - lr * wd;
   const float step_size = lr / bias1;
@@ -117,21 +127,30 @@ using namespace ws;
 
 extern "C" int ws_sumsq_parts(void) { return 148 * 8; }
 
-// stats: 3 floats on the device.  partial: ws_sumsq_parts() floats of scratch.
+// stats: 4 floats on the device.  partial: ws_sumsq_parts() floats of scratch.
 extern "C" int ws_grad_norm_clip(const float* g, size_t n, float* partial, const float* extra_sumsq,
-                                 float max_norm, float* stats, cudaStream_t stream) {
+                                 float max_norm, const int* status, float* stats, cudaStream_t stream) {
   if (n % 4 != 0) return -1;
   const int parts = ws_sumsq_parts();
   sumsq_kernel<<<parts, OPT_THREADS, 0, stream>>>(g, n / 4, partial);
   ws_count_launch();
-  clip_coef_kernel<<<1, 256, 0, stream>>>(partial, parts, extra_sumsq, max_norm, stats);
+  clip_coef_kernel<<<1, 256, 0, stream>>>(partial, parts, extra_sumsq, max_norm, status, stats);
+  ws_count_launch();
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// The same statistics from `parts` partial sums of squares that other kernels produced.
+extern "C" int ws_clip_from_partials(const float* partial, int parts, const float* extra_sumsq, float max_norm,
+                                     const int* status, float* stats, cudaStream_t stream) {
+  if (parts < 1) return -1;
+  clip_coef_kernel<<<1, 256, 0, stream>>>(partial, parts, extra_sumsq, max_norm, status, stats);
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
 extern "C" int ws_adamw(float* p, const float* g, float* m, float* v, void* p_bf16, size_t n, float lr,
                         float beta1, float beta2, float eps, float wd, int step, const float* grad_scale_ptr,
-                        float grad_scale_const, cudaStream_t stream) {
+                        float grad_scale_const, const float* skip_ptr, cudaStream_t stream) {
   if (n % 4 != 0 || step < 1) return -1;
   if (n == 0) return 0;
   const double bias1 = 1.0 - pow((double)beta1, (double)step);
@@ -140,7 +159,7 @@ extern "C" int ws_adamw(float* p, const float* g, float* m, float* v, void* p_bf
   if (blocks > 148 * 16) blocks = 148 * 16;
   adamw_kernel<<<(int)blocks, OPT_THREADS, 0, stream>>>(p, g, m, v, (__nv_bfloat16*)p_bf16, n / 4, lr, beta1,
                                                        beta2, eps, wd, (float)bias1, (float)sqrt(bias2),
-                                                       grad_scale_ptr, grad_scale_const);
+                                                       grad_scale_ptr, grad_scale_const, skip_ptr);
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }

@@ -141,14 +141,20 @@ int ws_attn_bwd(const void* qkvgu, const void* states, const void* dy, const voi
 
 // ----------------------------------------------------------------------------- optimizer
 int ws_sumsq_parts(void);
-// stats[0] = ||g||_2, stats[1] = min(1, max_norm / (||g|| + 1e-6)), stats[2] = ||g||^2 (+ *extra_sumsq)
+// stats (4 floats): [0] = ||g||_2, [1] = min(1, max_norm / (||g|| + 1e-6)), [2] = ||g||^2 (+ *extra_sumsq),
+// [3] = skip flag, 1 when the norm is not finite or *status (device int of a communication kernel, may be
+// NULL) is non-zero; the coefficient is 0 then.
 int ws_grad_norm_clip(const float* g, size_t n, float* partial, const float* extra_sumsq, float max_norm,
-                      float* stats, cudaStream_t stream);
+                      const int* status, float* stats, cudaStream_t stream);
+// The same from `parts` partial sums of squares produced elsewhere (summed in index order).
+int ws_clip_from_partials(const float* partial, int parts, const float* extra_sumsq, float max_norm,
+                          const int* status, float* stats, cudaStream_t stream);
 // AdamW over flat FP32 arenas (n % 4 == 0); gradients are multiplied by *grad_scale_ptr (device,
 // may be NULL) times grad_scale_const first; p_bf16 (may be NULL) receives the BF16 copy of p.
+// When *skip_ptr (device, may be NULL) is non-zero the kernel changes nothing.
 int ws_adamw(float* p, const float* g, float* m, float* v, void* p_bf16, size_t n, float lr, float beta1,
              float beta2, float eps, float wd, int step, const float* grad_scale_ptr,
-             float grad_scale_const, cudaStream_t stream);
+             float grad_scale_const, const float* skip_ptr, cudaStream_t stream);
 
 // ----------------------------------------------------------------------------- LM head
 // parts: float2 [rows, ld] of (max, sum exp) per 128 vocabulary columns (nparts valid per row),
@@ -165,10 +171,33 @@ int ws_comm_max_ctas(void);
 // In-place all-reduce (push = 1) or reduce-scatter (push = 0) of grad[start, start+count) with
 // the result scaled by `scale`; mc_grad is the multimem address of the arena or 0.
 // sumsq_out (may be NULL) receives `ctas` partial sums of squares of this rank's reduced slice.
+// Two launches: a one-warp kernel that announces the bucket and waits (bounded) for the peers', then
+// the data kernel, which moves nothing when *status is already non-zero.
 int ws_grad_allreduce(const unsigned long long* grad_ptrs, const unsigned long long* flag_ptrs,
                       unsigned long long mc_grad, int rank, int world, size_t start, size_t count, int bucket,
                       unsigned seq, float scale, int push, int ctas, float* sumsq_out, int* status,
                       double budget_seconds, cudaStream_t stream);
+// The same over up to 6 ranges of the arena with their own push flags, under one bucket's flags.
+int ws_grad_reduce_segments(const unsigned long long* grad_ptrs, const unsigned long long* flag_ptrs,
+                            unsigned long long mc_grad, int rank, int world, const size_t* starts,
+                            const size_t* counts, const int* push, int nseg, int bucket, unsigned seq, float scale,
+                            int ctas, float* sumsq_out, int* status, double budget_seconds, cudaStream_t stream);
+// Words a flag buffer needs after the bucket flags for ws_norm_exchange (3 * 8 words from its base) and
+// ws_node_barrier (8 words from its base).
+int ws_comm_extra_words(void);
+// stats[0..4] = global gradient norm, clip coefficient, norm^2, skip flag, sum over ranks of *local_loss,
+// bit-identical on every rank: each rank sums its `parts` partials, the sums are exchanged through the flag
+// buffers (words [base_word, base_word + 24)) and added in rank order.  `seq` as for the buckets.
+int ws_norm_exchange(const unsigned long long* flag_ptrs, int rank, int world, int base_word, unsigned seq,
+                     const float* partial, int parts, const float* local_loss, float max_norm, int* status,
+                     float* stats, double budget_seconds, cudaStream_t stream);
+// Device-side barrier over the ranks of the node through words [base_word, base_word + 8) of the flag buffers.
+int ws_node_barrier(const unsigned long long* flag_ptrs, int rank, int world, int base_word, unsigned seq,
+                    int* status, double budget_seconds, cudaStream_t stream);
+// dst[n, k] (BF16, local) = the FP32 weight whose rows are sharded over `world` ranks in blocks of
+// rows_per_shard (shards[r]: rank r's block as mapped in this process; plain peer loads).
+int ws_gather_cast(const void* const* shards, int world, int rows_per_shard, int n, int k, void* dst, int ctas,
+                   cudaStream_t stream);
 // Waits (bounded) for *flag >= expected and reports expiry through `status` like the kernels do.
 int ws_wait_probe(const unsigned* flag, unsigned expected, int* status, double budget_seconds,
                   cudaStream_t stream);
@@ -177,7 +206,7 @@ int ws_wait_probe(const unsigned* flag, unsigned expected, int* status, double b
 int ws_adamw_shard_push(const unsigned long long* master_ptrs, const unsigned long long* bf16_ptrs, int rank,
                         int world, const float* g, float* m, float* v, size_t lo, size_t n, float lr,
                         float beta1, float beta2, float eps, float wd, int step, const float* grad_scale_ptr,
-                        int push_master, cudaStream_t stream);
+                        int push_master, const float* skip_ptr, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

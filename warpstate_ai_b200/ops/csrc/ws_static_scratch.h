@@ -11,7 +11,7 @@
 // own.
 //
 // How: the partial sums live in an array that is part of the library image itself (a file-scope
-// device array of WS_STATIC_SCRATCH_FLOATS floats, about 4.6 MiB).  Every GPU that loads the
+// device array of WS_STATIC_SCRATCH_FLOATS floats, about 3.5 MiB).  Every GPU that loads the
 // library holds that memory until the process exits, whether or not this function is ever
 // called.  The function itself calls no cudaMalloc, no cudaFree and no allocating library
 // routine; inputs and outputs are the caller's.
@@ -21,9 +21,12 @@
 // initialisation, before any stream capture begins, with the device you will use current.
 //
 // Limits and sharing:
-//   * d must be a multiple of 128 and at most 2048, and blocks(rows) * d must not exceed
-//     WS_STATIC_SCRATCH_FLOATS; anything larger is rejected with WS_STATIC_ERR_TOO_LARGE before
-//     any work is launched (ws_static_scratch_strerror gives the text).
+//   * d must be a multiple of 128 and at most 2048: that is the limit that binds.  A wider row is
+//     rejected with WS_STATIC_ERR_BAD_SHAPE before any work is launched (ws_static_scratch_strerror
+//     gives the text).  The number of rows is free: the kernel never uses more than 444 partial
+//     rows (three blocks on each of 148 SMs) however many rows there are, and the array holds
+//     exactly 444 rows of 2048 floats.  WS_STATIC_ERR_TOO_LARGE guards the array bound itself and
+//     cannot be returned while the width limit stands.
 //   * All calls on a device share the one array, and it keeps whatever the previous call left
 //     in it.  Each call overwrites every element it later reads, so nothing has to be cleared,
 //     but two calls that overlap in time on the same GPU (different streams, or different
@@ -35,7 +38,7 @@
 extern "C" {
 #endif
 
-#define WS_STATIC_SCRATCH_FLOATS (592 * 2048)
+#define WS_STATIC_SCRATCH_FLOATS (444 * 2048)
 
 #define WS_STATIC_ERR_BAD_SHAPE (-1)
 #define WS_STATIC_ERR_LAUNCH (-2)

@@ -166,12 +166,74 @@ def _side_stream(device: torch.device):
     return stream
 
 
+# --------------------------------------------------------------------------- projection weights
+class LocalWeights:
+    """BF16 compute copies of a core's four projection weights when they are whole on this rank.
+    `parallel.fsdp.CoreWeights` offers the same calls for row-sharded weights (gathers included)."""
+
+    def __init__(self, w_in, w_out, w_ug, w_down):
+        self.w = (w_in, w_out, w_ug, w_down)
+
+    def begin_forward(self) -> None:
+        pass
+
+    def in_proj(self, z):
+        return G.linear(z, bf16_weight(self.w[0]))
+
+    def up_gate(self, z):
+        return G.linear_swiglu(z, bf16_weight(self.w[2]))
+
+    def out_w(self):
+        return bf16_weight(self.w[1])
+
+    def down_w(self):
+        return bf16_weight(self.w[3])
+
+    def end_forward(self) -> None:
+        pass
+
+    def begin_backward(self) -> None:
+        pass
+
+    def backward_weights(self):
+        return tuple(bf16_weight(w) for w in self.w)
+
+    def end_backward(self) -> None:
+        pass
+
+
+def _weights_of(core, params):
+    sharded = getattr(core, "ws_weights", None)
+    return sharded if sharded is not None else LocalWeights(*params)
+
+
 # --------------------------------------------------------------------------- one core
+def _core_kernels(core, weights, x_in, scale, bias, n1w, n2w, batch, seq, want_output=True):
+    """The forward kernel sequence of one core on ``x_in [M, d]`` (FP32 or BF16 residual stream).
+    Returns every tensor the backward pass reads, and ``x3`` (None when ``want_output`` is False: the
+    recomputation inside a checkpointed backward stops before the down projection)."""
+    ops = _ops()
+    has_mod = scale is not None
+    weights.begin_forward()
+    z1, rstd1, xmod = ops.rmsnorm_fwd(x_in, scale, bias, n1w, core.cfg.rms_eps, True)
+    qkvgu = weights.in_proj(z1)
+    y, attn_saved = _attention_forward(qkvgu, core, batch, seq)
+    x2 = G.linear_residual(y, weights.out_w(), xmod)
+    z2, rstd2, _ = ops.rmsnorm_fwd(x2, None, None, n2w, core.cfg.rms_eps, False)
+    packed, act = weights.up_gate(z2)
+    x3 = G.linear_residual(act, weights.down_w(), x2) if want_output else None
+    weights.end_forward()
+    return (xmod if has_mod else x_in, rstd1, z1, qkvgu, y, x2, rstd2, z2, packed, act, attn_saved), x3
+
+
 class CoreFn(torch.autograd.Function):
+    """One core as one autograd node.  ``checkpoint=True`` keeps only the core's input (and the small
+    vectors) for the backward pass and re-runs the forward kernels there -- the fused counterpart of the
+    reference's per-core ``torch.utils.checkpoint`` (warpstate/model.py:310-313)."""
+
     @staticmethod
     def forward(ctx, x, depth_scale, depth_bias, n1w, w_in, w_out, n2w, w_ug, w_down, fast_logit,
-                slow_logit, mix_logit, core, notify=True):
-        ops = _ops()
+                slow_logit, mix_logit, core, notify=True, checkpoint=False):
         batch, seq, d = x.shape
         m = batch * seq
         x_in = x.reshape(m, d)
@@ -180,21 +242,25 @@ class CoreFn(torch.autograd.Function):
         has_mod = depth_scale is not None
         scale = depth_scale.detach().float().contiguous() if has_mod else None
         bias = depth_bias.detach().float().contiguous() if has_mod else None
-        z1, rstd1, xmod = ops.rmsnorm_fwd(x_in, scale, bias, n1w.detach().float(), core.cfg.rms_eps, True)
-        qkvgu = G.linear(z1, bf16_weight(w_in))
-        y, attn_saved = _attention_forward(qkvgu, core, batch, seq)
-        x2 = G.linear_residual(y, bf16_weight(w_out), xmod)
-        z2, rstd2, _ = ops.rmsnorm_fwd(x2, None, None, n2w.detach().float(), core.cfg.rms_eps, False)
-        packed, act = G.linear_swiglu(z2, bf16_weight(w_ug))
-        x3 = G.linear_residual(act, bf16_weight(w_down), x2)
+        n1 = n1w.detach().float()
+        n2 = n2w.detach().float()
+        weights = _weights_of(core, (w_in, w_out, w_ug, w_down))
+        saved, x3 = _core_kernels(core, weights, x_in, scale, bias, n1, n2, batch, seq)
+        xmod, rstd1, z1, qkvgu, y, x2, rstd2, z2, packed, act, attn_saved = saved
         ctx.core = core
         ctx.notify = notify
         ctx.dims = (batch, seq, d)
         ctx.has_mod = has_mod
-        ctx.attn_saved = attn_saved
+        ctx.checkpoint = bool(checkpoint)
         ctx.params = (w_in, w_out, w_ug, w_down)
-        ctx.save_for_backward(x_in if has_mod else xmod, xmod, rstd1, z1, qkvgu, y, x2, rstd2, z2, packed, act,
-                              scale if has_mod else rstd1, n1w, n2w)
+        dummy = rstd1
+        if ctx.checkpoint:
+            ctx.attn_saved = None
+            ctx.save_for_backward(x_in, scale if has_mod else dummy, bias if has_mod else dummy, n1w, n2w)
+        else:
+            ctx.attn_saved = attn_saved
+            ctx.save_for_backward(x_in if has_mod else xmod, xmod, rstd1, z1, qkvgu, y, x2, rstd2, z2, packed, act,
+                                  scale if has_mod else dummy, n1w, n2w)
         return x3.view(batch, seq, d)
 
     @staticmethod
@@ -203,22 +269,37 @@ class CoreFn(torch.autograd.Function):
         core = ctx.core
         batch, seq, d = ctx.dims
         m = batch * seq
-        x_in, xmod, rstd1, z1, qkvgu, y, x2, rstd2, z2, packed, act, scale, n1w, n2w = ctx.saved_tensors
         w_in, w_out, w_ug, w_down = ctx.params
+        weights = _weights_of(core, ctx.params)
+        weights.begin_backward()
+        if ctx.checkpoint:
+            x_in, scale, bias, n1w, n2w = ctx.saved_tensors
+            with torch.no_grad():
+                saved, _ = _core_kernels(core, weights, x_in, scale if ctx.has_mod else None,
+                                         bias if ctx.has_mod else None, n1w.detach().float(), n2w.detach().float(),
+                                         batch, seq, want_output=False)
+            xmod, rstd1, z1, qkvgu, y, x2, rstd2, z2, packed, act, attn_saved = saved
+        else:
+            x_in, xmod, rstd1, z1, qkvgu, y, x2, rstd2, z2, packed, act, scale, n1w, n2w = ctx.saved_tensors
+            attn_saved = ctx.attn_saved
+        bw_in, bw_out, bw_ug, bw_down = weights.backward_weights()
         dx3 = dx3.reshape(m, d)
         if not dx3.is_contiguous():
             dx3 = dx3.contiguous()
+        stream_bf16 = dx3.dtype == torch.bfloat16
         # ---- FFN
-        dx3b = ops.cast_bf16(dx3, None) if dx3.dtype == torch.float32 else dx3
-        dpacked = G.grad_input_swiglu(dx3b, bf16_weight(w_down), packed)
-        dz2 = G.grad_input(dpacked, bf16_weight(w_ug))
-        dx2, dx2b, g_n2 = ops.rmsnorm_bwd(dz2, x2, rstd2, n2w.detach().float(), dx3, None, True)
+        dx3b = dx3 if stream_bf16 else ops.cast_bf16(dx3, None)
+        dpacked = G.grad_input_swiglu(dx3b, bw_down, packed)
+        dz2 = G.grad_input(dpacked, bw_ug)
+        dx2, dx2b, g_n2 = ops.rmsnorm_bwd(dz2, x2, rstd2, n2w.detach().float(), dx3, None, not stream_bf16)
+        if stream_bf16:
+            dx2b = dx2
         del dz2
         # ---- attention / memory
-        dy = G.grad_input(dx2b, bf16_weight(w_out))
-        dqkvgu, g_fast, g_slow, g_mix = _attention_backward(dy, qkvgu, ctx.attn_saved, core, batch, seq)
+        dy = G.grad_input(dx2b, bw_out)
+        dqkvgu, g_fast, g_slow, g_mix = _attention_backward(dy, qkvgu, attn_saved, core, batch, seq)
         del dy
-        dz1 = G.grad_input(dqkvgu, bf16_weight(w_in))
+        dz1 = G.grad_input(dqkvgu, bw_in)
         dx_in, _, g_n1 = ops.rmsnorm_bwd(dz1, xmod, rstd1, n1w.detach().float(), dx2, scale if ctx.has_mod else None, False)
         g_scale = g_bias = None
         side = _side_stream(dx_in.device) if ctx.has_mod else None
@@ -239,6 +320,7 @@ class CoreFn(torch.autograd.Function):
         g_down, g_ug, g_out, g_in = _wgrad_group([(dx3b, act, w_down), (dpacked, z2, w_ug), (dx2b, y, w_out),
                                                   (dqkvgu, z1, w_in)])
         del dpacked, dqkvgu
+        weights.end_backward()
         if side is not None:
             torch.cuda.current_stream(dx_in.device).wait_stream(side)
         if ctx.notify and _core_grad_hook is not None:
@@ -246,7 +328,7 @@ class CoreFn(torch.autograd.Function):
             _core_grad_hook(core)
             g_n1 = g_n2 = g_fast = g_slow = g_mix = None
         return (dx_in.view(batch, seq, d), g_scale, g_bias, g_n1, g_in, g_out, g_n2, g_ug, g_down,
-                g_fast, g_slow, g_mix, None, None)
+                g_fast, g_slow, g_mix, None, None, None)
 
 
 def _attach_small_grads(core, g_n1, g_n2, g_fast, g_slow, g_mix) -> None:
@@ -263,22 +345,27 @@ def _attach_small_grads(core, g_n1, g_n2, g_fast, g_slow, g_mix) -> None:
         main.add_(g.to(main.dtype))
 
 
-def core_forward(core, x: torch.Tensor, depth_scale=None, depth_bias=None, notify: bool = True) -> torch.Tensor:
+def core_forward(core, x: torch.Tensor, depth_scale=None, depth_bias=None, notify: bool = True,
+                 checkpoint: bool = False) -> torch.Tensor:
     if x.dtype not in (torch.float32, torch.bfloat16):
         x = x.float()
     return CoreFn.apply(x, depth_scale, depth_bias, core.norm1.weight, core.in_proj.weight,
                         core.out_proj.weight, core.norm2.weight, core.ffn.up_gate.weight,
                         core.ffn.down.weight, core.fast_decay_logit, core.slow_decay_logit,
-                        core.memory_mix_logit, core, notify)
+                        core.memory_mix_logit, core, notify, checkpoint)
 
 
 # --------------------------------------------------------------------------- embedding / final norm
 class EmbedFn(torch.autograd.Function):
+    """Embedding rows into the residual stream: FP32 by default, BF16 when the model runs with a BF16
+    residual stream (the reference's ``apply_bf16_residuals``, ops/residual_experiment.py:25-58, which
+    casts the embedding and the depth modulation so that every residual add rounds to BF16)."""
+
     @staticmethod
-    def forward(ctx, ids, table):
+    def forward(ctx, ids, table, out_bf16=False):
         ctx.save_for_backward(ids)
         ctx.table = table
-        out = _ops().embed_fwd(ids.reshape(-1).contiguous(), table.detach(), False)
+        out = _ops().embed_fwd(ids.reshape(-1).contiguous(), table.detach(), bool(out_bf16))
         return out.view(*ids.shape, table.shape[1])
 
     @staticmethod
@@ -290,10 +377,10 @@ class EmbedFn(torch.autograd.Function):
         main = getattr(table, "main_grad", None)
         if main is not None:
             _ops().embed_bwd(dx, ids, main)
-            return None, None
+            return None, None, None
         grad = torch.zeros(table.shape, dtype=torch.float32, device=table.device)
         _ops().embed_bwd(dx, ids, grad)
-        return None, grad.to(table.dtype)
+        return None, grad.to(table.dtype), None
 
 
 class NormFn(torch.autograd.Function):
@@ -319,13 +406,18 @@ class NormFn(torch.autograd.Function):
 
 
 def trunk_forward(model, input_ids: torch.Tensor) -> torch.Tensor:
-    """Embedding -> logical depths -> final norm; returns BF16 hidden states ``[B,T,d]``."""
+    """Embedding -> logical depths -> final norm; returns BF16 hidden states ``[B,T,d]``.
+
+    ``model.bf16_residuals`` selects a BF16 residual stream; ``cfg.gradient_checkpointing`` (while training
+    with gradients enabled) keeps only each core's input and recomputes the core in its backward."""
     cfg = model.cfg
-    x = EmbedFn.apply(input_ids, model.embed.weight)
+    x = EmbedFn.apply(input_ids, model.embed.weight, bool(getattr(model, "bf16_residuals", False)))
+    checkpoint = bool(cfg.gradient_checkpointing and model.training and torch.is_grad_enabled())
     for depth in range(cfg.logical_depth):
         core = model.cores[depth % cfg.n_cores]
         # the first forward use of a (possibly shared) core is its last use in backward
-        x = core_forward(core, x, model.depth_scale[depth], model.depth_bias[depth], notify=depth < cfg.n_cores)
+        x = core_forward(core, x, model.depth_scale[depth], model.depth_bias[depth], notify=depth < cfg.n_cores,
+                         checkpoint=checkpoint)
     return NormFn.apply(x, model.final_norm.weight, cfg.rms_eps)
 
 

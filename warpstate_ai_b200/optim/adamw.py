@@ -46,6 +46,27 @@ def linear_warmup_decay_lr(step: int, *, lr: float, warmup_steps: int, total_ste
     return lr * (1.0 - (1.0 - final_ratio) * frac)
 
 
+def host_clip_stats(sumsq: torch.Tensor, max_norm: float, status: torch.Tensor | None = None) -> torch.Tensor:
+    """``[norm, coef, norm^2, skip, 0, 0, 0, 0]`` from a sum of squares, as the kernels lay it out."""
+    sumsq = sumsq.reshape(()).float()
+    norm = sumsq.sqrt()
+    coef = torch.clamp(max_norm / (norm + 1e-6), max=1.0) if max_norm > 0 else torch.ones_like(norm)
+    bad = ~torch.isfinite(norm)
+    if status is not None:
+        bad = bad | (status.reshape(-1)[0] != 0)
+    zero = torch.zeros_like(norm)
+    return torch.stack([norm, torch.where(bad, zero, coef), sumsq, bad.float(), zero, zero, zero, zero])
+
+
+def host_adamw(p, grad, m, v, lr, b1, b2, eps, weight_decay, step) -> None:
+    """torch.optim.AdamW's update on flat tensors (the CPU form of `adamw_kernel`)."""
+    p.mul_(1 - lr * weight_decay)
+    m.lerp_(grad, 1 - b1)
+    v.mul_(b2).addcmul_(grad, grad, value=1 - b2)
+    denom = (v.sqrt() / math.sqrt(1 - b2 ** step)).add_(eps)
+    p.addcdiv_(m, denom, value=-lr / (1 - b1 ** step))
+
+
 class ArenaAdamW:
     def __init__(self, arena: ParamArena, lr: float = 1.5e-4, betas=(0.9, 0.95), eps: float = 1e-8,
                  weight_decay: float = 0.1, max_grad_norm: float | None = 1.0,
@@ -75,24 +96,25 @@ class ArenaAdamW:
     def zero_grad(self, set_to_none: bool = False) -> None:
         self.arena.zero_grad()
 
-    def clip_stats(self, extra_sumsq: torch.Tensor | None = None) -> torch.Tensor:
-        """[||g||, clip coefficient, ||g||^2] over the owned slice (+ ``extra_sumsq``)."""
+    def clip_stats(self, extra_sumsq: torch.Tensor | None = None, status: torch.Tensor | None = None) -> torch.Tensor:
+        """Device statistics of the owned slice (+ ``extra_sumsq``): ``[||g||, clip coefficient, ||g||^2,
+        skip, ...]``.  ``skip`` is 1 when the norm is not finite or the communication ``status`` word is
+        non-zero; `step` then leaves parameters and moments untouched."""
         g = self.arena.grad[self.lo:self.hi]
         max_norm = self.max_grad_norm if self.max_grad_norm is not None else 0.0
         if g.is_cuda and _kernels():
-            return torch.ops.ws_b200.grad_norm_clip(g, float(max_norm), extra_sumsq)
+            return torch.ops.ws_b200.grad_norm_clip(g, float(max_norm), extra_sumsq, status)
         sumsq = g.double().pow(2).sum().float()
         if extra_sumsq is not None:
             sumsq = sumsq + extra_sumsq.reshape(())
-        norm = sumsq.sqrt()
-        coef = torch.clamp(max_norm / (norm + 1e-6), max=1.0) if max_norm > 0 else torch.ones_like(norm)
-        return torch.stack([norm, coef, sumsq])
+        return host_clip_stats(sumsq, max_norm, status)
 
     @torch.no_grad()
     def step(self, lr: float | None = None, stats: torch.Tensor | None = None) -> torch.Tensor:
-        """One update.  Returns the device tensor ``[grad_norm, clip_coef, norm^2]``; callers that
+        """One update.  Returns the device tensor ``[grad_norm, clip_coef, norm^2, skip, ...]``; callers that
         want the reference's ``error_if_nonfinite`` behaviour check ``stats[0]`` when they read
-        the loss (one host sync per step instead of two)."""
+        the loss (one host sync per step instead of two).  When ``stats[3]`` is set nothing is changed on
+        the device and the caller is expected to call `rollback_step()` when it raises."""
         if lr is not None:
             self.lr = lr
         a = self.arena
@@ -106,19 +128,19 @@ class ArenaAdamW:
         if p.is_cuda and _kernels():
             pb = a.bf16[self.lo:self.hi] if a.bf16 is not None else None
             torch.ops.ws_b200.adamw_step(p, g, self.exp_avg, self.exp_avg_sq, pb, float(self.lr), b1, b2,
-                                         self.eps, self.weight_decay, self.step_count, stats[1:2], 1.0)
+                                         self.eps, self.weight_decay, self.step_count, stats[1:2], 1.0, stats[3:4])
             return stats
-        grad = g * stats[1]
-        p.mul_(1 - self.lr * self.weight_decay)
-        self.exp_avg.lerp_(grad, 1 - b1)
-        self.exp_avg_sq.mul_(b2).addcmul_(grad, grad, value=1 - b2)
-        bias1 = 1 - b1 ** self.step_count
-        bias2 = 1 - b2 ** self.step_count
-        denom = (self.exp_avg_sq.sqrt() / math.sqrt(bias2)).add_(self.eps)
-        p.addcdiv_(self.exp_avg, denom, value=-self.lr / bias1)
+        if float(stats[3]) != 0.0:
+            return stats
+        host_adamw(p, g * stats[1], self.exp_avg, self.exp_avg_sq, self.lr, b1, b2, self.eps, self.weight_decay,
+                   self.step_count)
         if a.bf16 is not None:
             a.bf16[self.lo:self.hi].copy_(p)
         return stats
+
+    def rollback_step(self) -> None:
+        """Undo the step count of an update that the device skipped (``stats[3]`` set)."""
+        self.step_count = max(0, self.step_count - 1)
 
     # ------------------------------------------------------------------ torch-compatible state
     def state_dict(self) -> dict:

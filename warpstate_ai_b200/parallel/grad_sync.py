@@ -118,7 +118,18 @@ class CollectiveGradSync(GradSyncBase):
 
 
 class FusedGradSync(GradSyncBase):
-    """One in-kernel all-reduce per bucket over symmetric memory (NVLink peer access / NVLS)."""
+    """One in-kernel all-reduce per bucket over symmetric memory (NVLink peer access / NVLS).
+
+    Per bucket two launches on the side stream: a one-warp kernel that announces the bucket and waits for
+    the peers' announcements, then the data kernel (``ctas`` CTAs), which therefore occupies SMs only
+    while it moves data.  The data kernel also leaves per-CTA sums of squares of the slice it reduced;
+    `exchange_stats` combines them over ranks (and the loss sum with them) in one more launch, so the
+    update needs no library collective at all.
+
+    A bucket may carry ``segments`` -- ``[(start, count, push), ...]`` set by a sharded-parameter
+    layout (`parallel/fsdp.py`): reduce-scatter ranges for row-owned matrices and an all-reduce range
+    for the replicated rest, all under the bucket's one pair of flags.
+    """
 
     kind = "fused"
 
@@ -129,12 +140,16 @@ class FusedGradSync(GradSyncBase):
         _ext.require()
         self.ctas = int(ctas or os.environ.get("WARPSTATE_COMM_CTAS", 32))
         self.budget = float(budget_seconds or os.environ.get("WARPSTATE_COMM_WAIT_SECONDS", 20.0))
+        if use_nvls is None and os.environ.get("WARPSTATE_COMM_PATH") in ("p2p", "nvls"):
+            use_nvls = os.environ["WARPSTATE_COMM_PATH"] == "nvls"
         self.use_nvls = use_nvls
         self.stream = torch.cuda.Stream(device=device)
         self.grad_sym = None
         self.flag_sym = None
         self.status = torch.zeros(8, dtype=torch.int32, device=device)
         self.push = True  # False: reduce-scatter (the sharded optimizer keeps each slice on its owner)
+        self.segments: dict[int, list[tuple[int, int, bool]]] = {}
+        self.barrier_seq = 0
 
     def alloc_grad_buffer(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
         from . import symm
@@ -144,8 +159,12 @@ class FusedGradSync(GradSyncBase):
     def attach(self, arena, model) -> None:
         super().attach(arena, model)
         from . import symm
-        words = 2 * 8 * len(arena.buckets)
+        n_buckets = len(arena.buckets)
+        self.exchange_base = 2 * 8 * n_buckets        # words after the bucket flags: norm exchange ...
+        self.barrier_base = self.exchange_base + 24   # ... and the node barrier
+        words = self.barrier_base + 8
         self.flag_sym = symm.allocate(max(words, 64), torch.int32, self.device, self.group)
+        self.partials = torch.zeros(n_buckets * self.ctas, dtype=torch.float32, device=self.device)
         mc = self.grad_sym.multicast_ptr
         if self.use_nvls is False:
             mc = 0
@@ -156,22 +175,44 @@ class FusedGradSync(GradSyncBase):
     def reduce_bucket(self, bucket: int) -> None:
         b = self.arena.buckets[bucket]
         self.reduced.add(bucket)
+        segs = self.segments.get(bucket) or [(b.start, b.stop - b.start, self.push)]
         self.stream.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(self.stream):
-            torch.ops.ws_b200.grad_allreduce(self.grad_sym.peer_ptrs, self.flag_sym.peer_ptrs, self.mc_ptr, self.rank,
-                                             self.world, b.start, b.stop - b.start, bucket, self.seq,
-                                             1.0 / self.world, self.push, self.ctas, None, self.status, self.budget)
+            torch.ops.ws_b200.grad_reduce_segments(
+                self.grad_sym.peer_ptrs, self.flag_sym.peer_ptrs, self.mc_ptr, self.rank, self.world,
+                [s[0] for s in segs], [s[1] for s in segs], [int(bool(s[2])) for s in segs], bucket, self.seq,
+                1.0 / self.world, self.ctas, self.partials[bucket * self.ctas:(bucket + 1) * self.ctas], self.status,
+                self.budget)
 
     def wait(self) -> None:
         torch.cuda.current_stream(self.device).wait_stream(self.stream)
+
+    def finish_update(self):
+        """Reduce what is left, join the side stream; returns this rank's partial sums of squares."""
+        super().finish_update()
+        return self.partials
+
+    def exchange_stats(self, partials: torch.Tensor, max_norm: float, local_loss: torch.Tensor | None) -> torch.Tensor:
+        """``[norm, coef, norm^2, skip, loss summed over ranks, ...]`` of the averaged gradient, bit-identical
+        on every rank (one launch; slots in the flag buffers, added in rank order)."""
+        return torch.ops.ws_b200.norm_exchange(self.flag_sym.peer_ptrs, self.rank, self.world, self.exchange_base,
+                                               self.seq, partials, local_loss, float(max_norm), self.status,
+                                               self.budget)
+
+    def node_barrier(self) -> None:
+        """Device-side barrier over the node on the current stream (bounded; failure lands in the status word)."""
+        self.barrier_seq += 1
+        torch.ops.ws_b200.node_barrier(self.flag_sym.peer_ptrs, self.rank, self.world, self.barrier_base,
+                                       self.barrier_seq, self.status, self.budget)
 
     def status_word(self):
         return self.status[0]
 
     def describe_error(self) -> str:
         code, bucket, src, expected, seen = self.status[:5].tolist()
-        what = {1: "waiting for a peer's gradients to be ready", 2: "waiting for peers to finish writing"}.get(code, "?")
-        return (f"rank {self.rank}: gradient all-reduce gave up {what}: bucket {bucket}, peer {src}, "
+        what = {1: "waiting for a peer's gradients to be ready", 2: "waiting for peers to finish writing",
+                3: "waiting for a peer's share of the gradient norm", 4: "in the node barrier"}.get(code, "?")
+        return (f"rank {self.rank}: gradient synchronisation gave up {what}: bucket {bucket}, peer {src}, "
                 f"expected {expected}, saw {seen}")
 
 

@@ -56,7 +56,7 @@ class ShardedWeight:
         self._barrier = barrier
         device = shard.device
         self.gathered = torch.empty(n, k, device=device, dtype=torch.bfloat16)   # landing buffer
-        self.flags = torch.zeros((n + 127) // 128, device=device, dtype=torch.int32)   # one word per 128 rows
+        self.flags = torch.zeros((n + 127) // 128 + 1, device=device, dtype=torch.int32)   # one word per 128 rows + chunk counter
         self.error_flag = G.error_flag(device) if device.type == "cuda" else None
         self.group = None                       # process group of the collective fallback
         self.gathered_valid = False

@@ -3,7 +3,7 @@
 The reference has replicated data parallelism only (DDP, run_40b.py:601-603): every rank keeps
 all of AdamW's state and repeats the whole update.  Here each rank owns, inside every gradient
 bucket of the `ParamArena`, the slice that the in-kernel reduce-scatter leaves on it
-(`grad_allreduce_kernel` with ``push = 0``, ops/csrc/comm.cu: slice ``r`` of a bucket of ``n4``
+(`grad_reduce_kernel` with ``push = 0``, ops/csrc/comm.cu: slice ``r`` of a bucket of ``n4``
 float4 words is ``[ceil(n4/world)*r, min(ceil(n4/world)*(r+1), n4))``).  A rank
 
 * receives only its slice of the averaged gradients (half the NVLink bytes of an all-reduce),
@@ -90,18 +90,29 @@ class ShardedAdamW:
     def zero_grad(self, set_to_none: bool = False) -> None:
         self.arena.zero_grad()
 
-    def clip_stats(self, extra_sumsq: torch.Tensor | None = None) -> torch.Tensor:
-        """[||g||, clip coefficient, ||g||^2] of the global (all ranks' slices) gradient."""
-        parts = [g.double().pow(2).sum() for g in self.owned(self.arena.grad) if g.numel()]
+    def clip_stats(self, extra_sumsq: torch.Tensor | None = None, status: torch.Tensor | None = None) -> torch.Tensor:
+        """``[||g||, clip coefficient, ||g||^2, skip, ...]`` of the global gradient.
+
+        With the fused synchroniser the trainer does not come here: the reduce-scatter kernel has already
+        left per-CTA sums of squares of the slices this rank owns and `FusedGradSync.exchange_stats`
+        combines them over ranks.  With a collective synchroniser every rank holds the whole averaged
+        gradient after the all-reduce, so on CUDA the norm is the deterministic two-stage kernel over the
+        arena, as in the replicated optimizer; on CPU the owned slices are summed in FP64 and all-reduced."""
+        from ..optim.adamw import host_clip_stats
+        max_norm = self.max_grad_norm if self.max_grad_norm is not None else 0.0
+        grad = self.arena.grad
+        if grad.is_cuda and not self.fused:
+            from ..ops import _ext
+            if _ext.available():
+                return torch.ops.ws_b200.grad_norm_clip(grad, float(max_norm), extra_sumsq, status)
+        parts = [g.double().pow(2).sum() for g in self.owned(grad) if g.numel()]
         sumsq = torch.stack(parts).sum().float() if parts else torch.zeros((), device=self.arena.device)
         sumsq = sumsq.reshape(1)
         if self.world > 1:
             dist.all_reduce(sumsq, op=dist.ReduceOp.SUM, group=self.group)
-        sumsq = sumsq.reshape(())
-        norm = sumsq.sqrt()
-        max_norm = self.max_grad_norm if self.max_grad_norm is not None else 0.0
-        coef = torch.clamp(max_norm / (norm + 1e-6), max=1.0) if max_norm > 0 else torch.ones_like(norm)
-        return torch.stack([norm, coef, sumsq])
+        if extra_sumsq is not None:
+            sumsq = sumsq + extra_sumsq.reshape(1)
+        return host_clip_stats(sumsq, max_norm, status)
 
     @torch.no_grad()
     def step(self, lr: float | None = None, stats: torch.Tensor | None = None) -> torch.Tensor:
@@ -130,8 +141,8 @@ class ShardedAdamW:
             torch.ops.ws_b200.adamw_shard_push(master_ptrs, self.mirror_sym.peer_ptrs, self.rank, self.world, a.grad,
                                                self.exp_avg[o0:o1], self.exp_avg_sq[o0:o1], lo, hi - lo,
                                                float(self.lr), b1, b2, self.eps, self.weight_decay, self.step_count,
-                                               stats[1:2], self.push_master)
-        self.mirror_sym.barrier()  # every rank's stores have landed before anyone's next forward
+                                               stats[1:2], self.push_master, stats[3:4])
+        self.sync.node_barrier()  # every rank's stores have landed before anyone's next forward
 
     def _step_collective(self, stats: torch.Tensor) -> None:
         a = self.arena
@@ -148,8 +159,10 @@ class ShardedAdamW:
                 from ..ops import _ext
                 if _ext.available():
                     torch.ops.ws_b200.adamw_step(p, g, m, v, None, float(self.lr), b1, b2, self.eps,
-                                                 self.weight_decay, self.step_count, stats[1:2], 1.0)
+                                                 self.weight_decay, self.step_count, stats[1:2], 1.0, stats[3:4])
                     continue
+            if float(stats[3]) != 0.0:
+                continue
             grad = g * stats[1]
             p.mul_(1 - self.lr * self.weight_decay)
             m.lerp_(grad, 1 - b1)
@@ -158,6 +171,10 @@ class ShardedAdamW:
             p.addcdiv_(m, denom, value=-self.lr / bias1)
         self.gather_into(a.master)
         a.refresh_bf16()
+
+    def rollback_step(self) -> None:
+        """Undo the step count of an update that the device skipped (``stats[3]`` set)."""
+        self.step_count = max(0, self.step_count - 1)
 
     # ------------------------------------------------------------------ gathers
     def gather_into(self, full: torch.Tensor) -> None:
