@@ -14,17 +14,15 @@ file (`renderer_sha256`), so a change to the renderer invalidates prepared data 
 from __future__ import annotations
 
 import hashlib
-import json
 import random
 from functools import lru_cache
 from pathlib import Path
 
 import torch
 
-from ..utils.io import digest
 
 RENDER_FORMAT = "warpstate-segmented-roles-v1"
-DATA_FORMAT = "warpstate-posttrain-data-v1"
+from .prepared import DATA_FORMAT  # noqa: E402  (the directory format lives with its reader)
 IGNORE_INDEX = -100
 ROLES = frozenset({"system", "user", "assistant", "tool"})
 
@@ -137,40 +135,19 @@ def rank_microbatches(indices, records, micro_batch: int, grad_accum: int, world
 
 
 def load_data(data_dir, tokenizer, tokenizer_hash: str, sequence_length: int):
-    """Load and re-encode prepared SFT data, refusing anything partial or inconsistent."""
-    directory = Path(data_dir)
-    manifest_path = directory / "manifest.json"
-    manifest = json.loads(manifest_path.read_text())
-    if manifest.get("format") != DATA_FORMAT or manifest.get("complete") is not True:
-        raise ValueError("Posttraining data is not complete")
-    if manifest.get("tokenizer_sha256") != tokenizer_hash:
-        raise ValueError("Prepared data tokenizer hash differs")
-    if manifest.get("renderer_sha256") != renderer_sha256():
-        raise ValueError("Prepared data renderer hash differs")
-    if manifest.get("max_length") != sequence_length:
-        raise ValueError("Prepared data max_length differs from sequence_length")
-    splits = []
-    for filename in ("sft_train.jsonl", "sft_val.jsonl"):
-        info = manifest.get("outputs", {}).get(filename)
-        path = directory / filename
-        if not info or not path.is_file() or digest(path) != info.get("sha256"):
-            raise ValueError(f"Missing or changed prepared file: {filename}")
-        records, tokens_total, targets_total = [], 0, 0
-        with path.open() as stream:
-            for number, line in enumerate(stream, 1):
-                row = json.loads(line)
-                if row.get("tools"):
-                    raise ValueError(f"{filename}:{number}: tools must be injected into messages")
-                encoded = encode_messages(row["messages"], tokenizer, max_length=sequence_length)
-                tokens, targets = len(encoded["input_ids"]), supervised_count(encoded)
-                if row.get("tokens") != tokens or row.get("supervised_tokens") != targets:
-                    raise ValueError(f"{filename}:{number}: token metadata differs from exact encoding")
-                records.append(encoded)
-                tokens_total += tokens
-                targets_total += targets
-        if not records or len(records) != info.get("rows"):
-            raise ValueError(f"{filename}: empty data or row count mismatch")
-        if tokens_total != info.get("tokens") or targets_total != info.get("supervised_tokens"):
-            raise ValueError(f"{filename}: manifest token totals differ")
-        splits.append(records)
-    return splits[0], splits[1], manifest, digest(manifest_path)
+    """Load and re-encode prepared SFT data, refusing anything partial or inconsistent:
+    -> (train records, validation records, manifest, SHA-256 of the manifest file)."""
+    from .prepared import PreparedDirectory
+    prepared = PreparedDirectory(data_dir, tokenizer_hash, renderer_sha256(), sequence_length)
+
+    def encode(row, number):
+        if row.get("tools"):
+            raise ValueError(f"row {number}: tool definitions must already be part of the messages")
+        return encode_messages(row["messages"], tokenizer, max_length=sequence_length)
+
+    def measure(row, record):
+        counts = len(record["input_ids"]), supervised_count(record)
+        return counts if (row.get("tokens"), row.get("supervised_tokens")) == counts else None
+
+    train, val = (prepared.split(name, encode, measure) for name in ("sft_train.jsonl", "sft_val.jsonl"))
+    return train, val, prepared.manifest, prepared.manifest_digest()

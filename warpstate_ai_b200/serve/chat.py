@@ -1,271 +1,250 @@
-"""Interactive / one-shot text generation from a sealed inference snapshot.
+"""Text generation from a sealed inference snapshot: one-shot prompt or interactive session.
 
-Snapshot handling follows the reference probe (chat.py:37-151): a training checkpoint
-(``warpstate-server-v1``) is never loaded directly; `capture_latest` pins the published file by
-file descriptor (the trainer replaces ``latest.pt`` by rename, so an open descriptor keeps one
-complete version), exports the model-only ``warpstate-chat-v1`` snapshot read-only with a
-``snapshot.json`` carrying its SHA-256, and `load_model` verifies snapshot hash, tokenizer hash
-and a strict meta-device load before any generation.
+The entry point of the reference's base-model probe (reference chat.py: snapshot capture and
+verification :37-151, sampling :154-193, generation :196-255, REPL :258-352), rebuilt on this
+framework's serving pieces:
 
-Generation differs: the prompt is prefilled in whole chunks through the training forward path
-and decoded with the batched `DecodeEngine` (CUDA graph replay per token on a GPU); ``--device
-cpu`` keeps the reference's FP32 probe behaviour.
+* snapshots are exported, verified and loaded by `serve.snapshots.SnapshotStore`;
+* the prompt is prefilled in whole 128-token chunks through the training kernels and decoded by
+  the batched `DecodeEngine` (CUDA-graph replay per token on a GPU; ``--device cpu`` runs the
+  FP32 PyTorch definition, like the reference's probe), where the reference feeds the prompt
+  token by token through ``model.step``;
+* token choice is `serve.sampling.Sampler` with a `ReplyHistory` per reply;
+* the interactive loop is a `ChatSession` with a table of slash commands.
+
+`capture_latest`, `resolve_snapshot`, `load_model` and `generate` keep the reference's call
+signatures for code that imports them.
 """
 from __future__ import annotations
 
 import argparse
-import gc
 import json
-import math
-import os
-import stat
-import tempfile
 import time
 from pathlib import Path
 
 import torch
 
-from ..ckpt.formats import CHAT_FORMAT, SERVER_FORMAT
-from ..config import WarpStateConfig
-from ..models.warpstate import WarpStateLM
-from ..utils.io import digest, fsync_dir, utc_timestamp
+from ..ckpt.formats import CHAT_FORMAT
 from .engine import DecodeEngine
-from .sampling import banned_ngram_tokens, sample_token
+from .sampling import ReplyHistory, Sampler, SamplingSettings
+from .snapshots import SnapshotStore
 
 ROOT = Path(__file__).resolve().parents[2]
 FORMAT = CHAT_FORMAT
 
 
+# ----------------------------------------------------------------------------------- snapshot helpers
 def capture_latest(source, tokenizer, snapshot_root) -> Path:
-    source, tokenizer, snapshot_root = Path(source), Path(tokenizer), Path(snapshot_root)
-    if source.suffix != ".pt" or source.is_symlink():
-        raise ValueError("Select a completed regular .pt checkpoint, not a temporary file")
-    tokenizer_sha = digest(tokenizer)
-    fd = os.open(source, os.O_RDONLY | os.O_NOFOLLOW)
-    try:
-        before = os.fstat(fd)
-        if not stat.S_ISREG(before.st_mode):
-            raise ValueError("Checkpoint must be a regular file")
-        checkpoint = torch.load(f"/proc/self/fd/{fd}", map_location="cpu", weights_only=False, mmap=True)
-        if checkpoint.get("format") == FORMAT:
-            raise ValueError(f"Chat snapshot requires its original snapshot.json beside {source}. "
-                             "Restore that metadata or export a fresh snapshot from a training checkpoint.")
-        if checkpoint.get("format") != SERVER_FORMAT:
-            raise ValueError("Expected a full warpstate-server-v1 training checkpoint")
-        if checkpoint["signature"]["data"]["signature"]["tokenizer_sha256"] != tokenizer_sha:
-            raise ValueError("Tokenizer SHA256 differs from training checkpoint")
-        snapshot_root.mkdir(parents=True, exist_ok=True)
-        folder = Path(tempfile.mkdtemp(prefix=f"step-{checkpoint['step']}-", dir=snapshot_root))
-        destination, temporary = folder / "model.pt", folder / "model.pt.tmp"
-        identity = (before.st_dev, before.st_ino, before.st_size, before.st_mtime_ns)
-        metadata = dict(format=FORMAT, inference_only=True, config=checkpoint["config"], step=checkpoint["step"],
-                        tokens_seen=checkpoint["tokens_seen"], val_loss=checkpoint.get("val_loss"),
-                        tokenizer_sha256=tokenizer_sha, captured_at_utc=utc_timestamp(),
-                        source=dict(path=str(source.resolve()), device=before.st_dev, inode=before.st_ino,
-                                    size=before.st_size, mtime_ns=before.st_mtime_ns))
-        print(f"Capturing completed step {metadata['step']:,} / {metadata['tokens_seen']:,} tokens; "
-              "model weights only...", flush=True)
-        with temporary.open("xb") as stream:
-            torch.save(dict(metadata, model=checkpoint["model"]), stream)
-            stream.flush()
-            os.fsync(stream.fileno())
-        after = os.fstat(fd)
-        if identity != (after.st_dev, after.st_ino, after.st_size, after.st_mtime_ns):
-            raise RuntimeError("Pinned checkpoint contents changed; snapshot not published")
-        os.chmod(temporary, 0o444)
-        os.replace(temporary, destination)
-        metadata["snapshot_sha256"] = digest(destination)
-        metadata["snapshot_bytes"] = destination.stat().st_size
-        with (folder / "snapshot.json").open("x") as stream:
-            json.dump(metadata, stream, indent=2)
-            stream.write("\n")
-            stream.flush()
-            os.fsync(stream.fileno())
-        fsync_dir(folder)
-        return destination
-    finally:
-        os.close(fd)
+    return SnapshotStore(snapshot_root, tokenizer).export(source)
 
 
 def resolve_snapshot(source, tokenizer, snapshot_root) -> Path:
-    source = Path(source)
-    if not source.is_file():
-        raise ValueError(f"Checkpoint file does not exist or is not a regular file: {source}")
-    if source.with_name("snapshot.json").exists():
-        return source
-    return capture_latest(source, tokenizer, snapshot_root)
+    return SnapshotStore(snapshot_root, tokenizer).resolve(source)
 
 
 def load_model(snapshot, tokenizer, device: str = "cpu"):
-    import sentencepiece as spm
-    snapshot, tokenizer = Path(snapshot), Path(tokenizer)
-    proof_path = snapshot.with_name("snapshot.json")
-    try:
-        proof = json.loads(proof_path.read_text())
-    except FileNotFoundError as exc:
-        raise ValueError(f"Missing snapshot metadata: {proof_path}. Use --checkpoint to export training weights, "
-                         "or restore the original metadata.") from exc
-    if not isinstance(proof, dict) or not isinstance(proof.get("snapshot_sha256"), str):
-        raise ValueError(f"Invalid snapshot metadata: {proof_path}")
-    if proof["snapshot_sha256"] != digest(snapshot):
-        raise ValueError("Inference snapshot SHA256 mismatch")
-    checkpoint = torch.load(snapshot, map_location="cpu", weights_only=False, mmap=True)
-    if checkpoint.get("format") != FORMAT or not checkpoint.get("inference_only"):
-        raise ValueError("Use the independent inference snapshot, not live latest.pt")
-    if checkpoint["tokenizer_sha256"] != digest(tokenizer):
-        raise ValueError("Tokenizer SHA256 mismatch")
-    config = WarpStateConfig(**checkpoint["config"])
-    sp = spm.SentencePieceProcessor(model_file=str(tokenizer))
-    if sp.vocab_size() != config.vocab_size:
-        raise ValueError("Tokenizer vocabulary differs from model")
-    with torch.device("meta"):
-        model = WarpStateLM(config)
-    model.load_state_dict(checkpoint["model"], strict=True, assign=True)
-    model.eval().requires_grad_(False)
-    if any(p.dtype != torch.float32 for p in model.parameters()):
-        raise ValueError("Snapshots hold the original FP32 model parameters")
-    model = model.to(device)
-    metadata = {k: v for k, v in checkpoint.items() if k != "model"}
-    del checkpoint
-    gc.collect()
-    return model, sp, metadata
+    return SnapshotStore(Path(snapshot).parent.parent, tokenizer).load(snapshot, device)
+
+
+# ----------------------------------------------------------------------------------- generation
+def _context_window(ids: list, max_new_tokens: int, max_context: int) -> list:
+    if not 0 < max_new_tokens < max_context:
+        raise ValueError("need 0 < max-new-tokens < max-context")
+    if not ids:
+        raise ValueError("the prompt encodes to no tokens")
+    return ids[-(max_context - max_new_tokens):]
 
 
 @torch.inference_mode()
 def generate(model, sp, prompt: str, *, max_new_tokens=256, temperature=0.8, top_k=40, top_p=0.9, seed=1337,
              max_context=2048, repetition_penalty=1.2, no_repeat_ngram_size=4, engine: DecodeEngine | None = None):
-    """Yields token ids of the reply."""
-    if max_new_tokens < 1 or max_context <= max_new_tokens:
-        raise ValueError("Require 0 < max-new-tokens < max-context")
-    if not math.isfinite(repetition_penalty) or repetition_penalty < 1:
-        raise ValueError("Require a finite repetition-penalty >= 1")
-    if not isinstance(no_repeat_ngram_size, int) or no_repeat_ngram_size < 0:
-        raise ValueError("Require an integer no-repeat-ngram-size >= 0")
-    ids = sp.encode(prompt, out_type=int)
-    if not ids:
-        raise ValueError("Prompt contains no tokens")
-    ids = ids[-(max_context - max_new_tokens):]
+    """Yields the reply's token ids one by one (stops at end-of-sequence, at the length limit or when
+    the sampling rules leave no candidate)."""
+    settings = SamplingSettings(temperature=temperature, top_k=top_k, top_p=top_p,
+                                repetition_penalty=repetition_penalty, no_repeat_ngram=no_repeat_ngram_size)
+    ids = _context_window(sp.encode(prompt, out_type=int), max_new_tokens, max_context)
     device = model.embed.weight.device
-    engine = engine or DecodeEngine(model, dtype=torch.bfloat16 if device.type == "cuda" else torch.float32)
+    if engine is None:
+        engine = DecodeEngine(model, dtype=torch.bfloat16 if device.type == "cuda" else torch.float32)
+    sampler = Sampler(settings, torch.Generator(device="cpu").manual_seed(seed))
+    history = ReplyHistory(settings.no_repeat_ngram)
     logits = engine.prefill(torch.tensor([ids], dtype=torch.long, device=device))[0]
-    generator = torch.Generator(device="cpu").manual_seed(seed)
-    generated = []
-    for index in range(max_new_tokens):
-        value = sample_token(logits.cpu(), temperature, top_k, top_p, generator, previous_tokens=generated,
-                             repetition_penalty=repetition_penalty,
-                             banned_tokens=banned_ngram_tokens(generated, no_repeat_ngram_size))
-        if value is None or value == sp.eos_id():
-            break
-        generated.append(value)
-        yield value
-        if index + 1 < max_new_tokens:
-            logits = engine.step(torch.tensor([value], device=device))[0]
+    stop = sp.eos_id()
+    while len(history.tokens) < max_new_tokens:
+        token = sampler.next(logits.cpu(), history)
+        if token is None or token == stop:
+            return
+        history.push(token)
+        yield token
+        if len(history.tokens) < max_new_tokens:
+            logits = engine.step(torch.tensor([token], device=device))[0]
+
+
+class ReplyPrinter:
+    """Streams a reply to the terminal as it decodes.  SentencePiece may emit a multi-byte character over
+    several byte-fallback tokens; text after the first replacement character is held back until complete."""
+
+    def __init__(self, sp):
+        self.sp, self.ids, self.shown = sp, [], ""
+        self.started = time.perf_counter()
+        self.first_token_at = None
+
+    def _emit(self, text: str) -> None:
+        if text.startswith(self.shown):
+            print(text[len(self.shown):], end="", flush=True)
+            self.shown = text
+
+    def feed(self, token: int) -> None:
+        if self.first_token_at is None:
+            self.first_token_at = time.perf_counter()
+        self.ids.append(token)
+        self._emit(self.sp.decode(self.ids).partition("�")[0])
+
+    def finish(self) -> str:
+        text = self.sp.decode(self.ids)
+        self._emit(text)
+        took = time.perf_counter() - self.started
+        first = "-" if self.first_token_at is None else f"{self.first_token_at - self.started:.2f}s"
+        rate = len(self.ids) / max(took, 1e-9)
+        print(f"\n[{len(self.ids)} tokens; {took:.1f}s total; TTFT {first}; {rate:.1f} tok/s]", flush=True)
+        return text
 
 
 def reply(model, sp, prompt, args, engine=None) -> str:
-    ids, emitted = [], ""
-    begin, first = time.perf_counter(), None
-    for value in generate(model, sp, prompt, max_new_tokens=args.max_new_tokens, temperature=args.temperature,
+    printer = ReplyPrinter(sp)
+    for token in generate(model, sp, prompt, max_new_tokens=args.max_new_tokens, temperature=args.temperature,
                           top_k=args.top_k, top_p=args.top_p, seed=args.seed, max_context=args.max_context,
-                          repetition_penalty=args.repetition_penalty,
-                          no_repeat_ngram_size=args.no_repeat_ngram_size, engine=engine):
-        if first is None:
-            first = time.perf_counter()
-        ids.append(value)
-        safe = sp.decode(ids).split("�", 1)[0]  # hold back incomplete byte-fallback characters
-        if safe.startswith(emitted):
-            print(safe[len(emitted):], end="", flush=True)
-            emitted = safe
-    text = sp.decode(ids)
-    if text.startswith(emitted):
-        print(text[len(emitted):], end="", flush=True)
-    elapsed = time.perf_counter() - begin
-    ttft = "-" if first is None else f"{first - begin:.2f}s"
-    print(f"\n[{len(ids)} tokens; {elapsed:.1f}s total; TTFT {ttft}; {len(ids) / max(elapsed, 1e-9):.1f} tok/s]", flush=True)
-    return text
+                          repetition_penalty=args.repetition_penalty, no_repeat_ngram_size=args.no_repeat_ngram_size,
+                          engine=engine):
+        printer.feed(token)
+    return printer.finish()
 
 
+# ----------------------------------------------------------------------------------- interactive session
+class ChatSession:
+    """Conversation state plus the slash commands.  In Q/A mode a turn is framed as
+    ``Question: ...\\nAnswer:`` (the reference's probe format); raw mode continues plain text."""
+
+    def __init__(self, model, sp, metadata: dict, args):
+        self.model, self.sp, self.metadata, self.args = model, sp, metadata, args
+        self.raw = bool(args.raw)
+        self.transcript = ""
+        self.commands = {"/new": self._new, "/raw": self._raw, "/chat": self._qa, "/info": self._info,
+                         "/help": self._help}
+
+    def _mode(self) -> str:
+        return "raw completion" if self.raw else "Q/A probe"
+
+    def _new(self) -> None:
+        self.transcript = ""
+        print(f"Context cleared. Mode: {self._mode()}")
+
+    def _raw(self) -> None:
+        self.raw = True
+        self._new()
+
+    def _qa(self) -> None:
+        self.raw = False
+        self._new()
+
+    def _info(self) -> None:
+        print(json.dumps(self.metadata, indent=2, default=str))
+
+    def _help(self) -> None:
+        print("/new forget the conversation; /raw plain completion; /chat question/answer framing; "
+              "/info snapshot metadata; /exit leave")
+
+    def ask(self, text: str) -> str:
+        prompt = self.transcript + (text if self.raw else f"Question: {text}\nAnswer:")
+        print("Model: ", end="", flush=True)
+        answer = reply(self.model, self.sp, prompt, self.args)
+        self.transcript = prompt + ("" if self.raw else " ") + answer + "\n\n"
+        return answer
+
+    def banner(self) -> None:
+        meta = self.metadata
+        print(f"WarpState {self.model.num_parameters() / 1e9:.3f}B | {self.args.device} | step {meta['step']:,} | "
+              f"{meta['tokens_seen']:,} training tokens", flush=True)
+        print("This is a pretrained base model without instruction tuning; the Q/A framing is a probe only.\n"
+              "Commands: " + ", ".join(self.commands) + ", /exit. Ctrl-C cancels the current reply.", flush=True)
+
+    def loop(self) -> None:
+        while True:
+            try:
+                line = input("\nYou: ").strip()
+            except EOFError:
+                return
+            if line in ("/exit", "/quit"):
+                return
+            if not line:
+                continue
+            command = self.commands.get(line)
+            try:
+                command() if command else self.ask(line)
+            except KeyboardInterrupt:
+                print("\nReply cancelled (a running training job is not touched by this).", flush=True)
+
+
+# ----------------------------------------------------------------------------------- command line
 def build_parser() -> argparse.ArgumentParser:
     p = argparse.ArgumentParser(description="WarpState base-model probe")
-    p.add_argument("--checkpoint", type=Path, default=ROOT / "work/run/latest.pt")
-    p.add_argument("--snapshot", type=Path, help="reuse a sealed model-only snapshot, or export a training checkpoint")
-    p.add_argument("--snapshot-root", type=Path, default=ROOT / "work/chat")
-    p.add_argument("--tokenizer", type=Path, default=ROOT / "tokenizer.model")
-    p.add_argument("--capture-only", action="store_true")
-    p.add_argument("--prompt", help="one-shot probe instead of interactive input")
-    p.add_argument("--raw", action="store_true", help="plain text completion instead of Q/A labels")
-    p.add_argument("--threads", type=int, default=16)
-    p.add_argument("--max-new-tokens", type=int, default=256)
-    p.add_argument("--max-context", type=int, default=2048)
-    p.add_argument("--temperature", type=float, default=0.8, help="0 = greedy")
-    p.add_argument("--top-k", type=int, default=40)
-    p.add_argument("--top-p", type=float, default=0.9)
-    p.add_argument("--repetition-penalty", type=float, default=1.2)
-    p.add_argument("--no-repeat-ngram-size", type=int, default=4)
-    p.add_argument("--seed", type=int, default=1337)
-    p.add_argument("--device", choices=["cpu", "cuda"], default="cpu")
+    where = p.add_argument_group("snapshot")
+    where.add_argument("--checkpoint", type=Path, default=ROOT / "work/run/latest.pt")
+    where.add_argument("--snapshot", type=Path, help="a sealed export to reuse, or a training checkpoint to export first")
+    where.add_argument("--snapshot-root", type=Path, default=ROOT / "work/chat")
+    where.add_argument("--tokenizer", type=Path, default=ROOT / "tokenizer.model")
+    where.add_argument("--capture-only", action="store_true", help="export and stop")
+    run = p.add_argument_group("generation")
+    run.add_argument("--prompt", help="answer this one prompt and exit")
+    run.add_argument("--raw", action="store_true", help="continue plain text instead of the Q/A framing")
+    run.add_argument("--device", choices=["cpu", "cuda"], default="cpu")
+    run.add_argument("--threads", type=int, default=16)
+    run.add_argument("--seed", type=int, default=1337)
+    for flag, kind, default, note in (("--max-new-tokens", int, 256, None), ("--max-context", int, 2048, None),
+                                      ("--temperature", float, 0.8, "0 selects the most likely token"),
+                                      ("--top-k", int, 40, None), ("--top-p", float, 0.9, None),
+                                      ("--repetition-penalty", float, 1.2, None),
+                                      ("--no-repeat-ngram-size", int, 4, None)):
+        run.add_argument(flag, type=kind, default=default, help=note)
     return p
+
+
+def _check_args(parser, args) -> None:
+    if args.threads < 1:
+        parser.error("--threads must be at least 1")
+    if not 0 < args.max_new_tokens < args.max_context:
+        parser.error("need 0 < --max-new-tokens < --max-context")
+    try:
+        SamplingSettings(args.temperature, args.top_k, args.top_p, args.repetition_penalty, args.no_repeat_ngram_size)
+    except ValueError as problem:
+        parser.error(str(problem))
+    if args.prompt is not None and not args.prompt.strip():
+        parser.error("--prompt is empty")
 
 
 def main(argv=None) -> None:
     parser = build_parser()
     args = parser.parse_args(argv)
-    if args.threads < 1 or not 0 < args.max_new_tokens < args.max_context:
-        parser.error("Require threads >= 1 and 0 < max-new-tokens < max-context")
-    if not math.isfinite(args.temperature) or args.temperature < 0 or args.top_k < 0 or not 0 < args.top_p <= 1:
-        parser.error("Invalid temperature / top-k / top-p")
-    if not math.isfinite(args.repetition_penalty) or args.repetition_penalty < 1 or args.no_repeat_ngram_size < 0:
-        parser.error("Require finite repetition-penalty >= 1 and no-repeat-ngram-size >= 0")
-    if args.prompt is not None and not args.prompt.strip():
-        parser.error("A one-shot prompt must not be empty")
+    _check_args(parser, args)
     torch.set_num_threads(args.threads)
+    store = SnapshotStore(args.snapshot_root, args.tokenizer)
     try:
-        if args.snapshot is not None:
-            snapshot = resolve_snapshot(args.snapshot, args.tokenizer, args.snapshot_root)
-        else:
-            snapshot = capture_latest(args.checkpoint, args.tokenizer, args.snapshot_root)
+        snapshot = store.resolve(args.snapshot) if args.snapshot is not None else store.export(args.checkpoint)
         print(f"Snapshot: {snapshot}", flush=True)
         if args.capture_only:
             return
-        model, sp, metadata = load_model(snapshot, args.tokenizer, args.device)
-    except (OSError, ValueError) as exc:
-        parser.error(str(exc))
-    print(f"WarpState {model.num_parameters() / 1e9:.3f}B | {args.device} | step {metadata['step']:,} | "
-          f"{metadata['tokens_seen']:,} training tokens", flush=True)
-    print("Base pretrained model, not instruction-tuned. Q/A labels are only a probe.\n"
-          "Commands: /new, /raw, /chat, /info, /help, /exit. Ctrl-C cancels a reply.", flush=True)
-    history = ""
-    while True:
+        model, sp, metadata = store.load(snapshot, args.device)
+    except (OSError, ValueError) as problem:
+        parser.error(str(problem))
+    session = ChatSession(model, sp, metadata, args)
+    session.banner()
+    if args.prompt is not None:
         try:
-            user = args.prompt if args.prompt is not None else input("\nYou: ").strip()
-            if user is None or (args.prompt is None and user in ("/exit", "/quit")):
-                break
-            if not user:
-                continue
-            if args.prompt is None and user in ("/new", "/raw", "/chat"):
-                history = ""
-                if user != "/new":
-                    args.raw = user == "/raw"
-                print("Context cleared. Mode: " + ("raw completion" if args.raw else "Q/A probe"))
-                continue
-            if args.prompt is None and user == "/info":
-                print(json.dumps(metadata, indent=2, default=str))
-                continue
-            if args.prompt is None and user == "/help":
-                print("/new clears context; /raw plain completion; /chat Q/A; /info snapshot; /exit quit")
-                continue
-            prompt = history + (user if args.raw else f"Question: {user}\nAnswer:")
-            print("Model: ", end="", flush=True)
-            answer = reply(model, sp, prompt, args)
-            history = prompt + ("" if args.raw else " ") + answer + "\n\n"
-            if args.prompt is not None:
-                break
-        except EOFError:
-            break
+            session.ask(args.prompt)
         except KeyboardInterrupt:
-            print("\nReply cancelled; training was not affected.", flush=True)
-            if args.prompt is not None:
-                break
+            print("\nReply cancelled.", flush=True)
+        return
+    session.loop()
 
 
 if __name__ == "__main__":
