@@ -57,6 +57,7 @@ def arguments(argv=None):
     p.add_argument("--device", choices=["cuda", "cpu"], default="cuda" if torch.cuda.is_available() else "cpu")
     p.add_argument("--grad-sync", choices=["auto", "fused", "nccl"], default="auto")
     p.add_argument("--shard-optimizer", action="store_true")
+    p.add_argument("--shard-params", choices=["off", "stream", "resident"], default="off")
     return p.parse_args(argv)
 
 
@@ -232,7 +233,8 @@ def benchmark(a) -> dict:
         sync = make_grad_sync(device, world, rank, None,
                               kind={"auto": "auto", "fused": "fused", "nccl": "collective"}[a.grad_sync])
     trainer = Trainer(model, device=device, rank=rank, world_size=world, grad_sync=sync,
-                      shard_optimizer=a.shard_optimizer)
+                      shard_optimizer=a.shard_optimizer,
+                      shard_params=None if a.shard_params == "off" else a.shard_params)
     if checkpoint is not None and a.optimizer_state == "resume":
         trainer.optimizer.load_state_dict(checkpoint["optimizer"])
     del checkpoint
