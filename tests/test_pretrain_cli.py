@@ -126,14 +126,83 @@ def test_signature_rules():
 
 
 @pytest.mark.parametrize("flags", [
-    ["--compile", "--compile-core"], ["--compile-mode", "reduce-overhead"], ["--overlap-swap-collectives"],
-    ["--gradient-mode", "compiled-autograd", "--ddp-batched-grad-copy"], ["--backward-layout", "paired"],
-    ["--cache-core-weight-casts"], ["--min-lr", "1"], ["--micro-batch", "0"], ["--overlap-memory-budget", "0.5"],
-    ["--gradient-mode", "compiled-autograd", "--activation-mode", "swiglu"], ["--ddp-bucket-cap-mb", "0"],
+    ["--min-lr", "1"], ["--micro-batch", "0"], ["--ddp-bucket-cap-mb", "-1"], ["--val-tokens", "100"],
+    ["--shard-params", "stream", "--shard-optimizer"], ["--bootstrap", "--no-bootstrap"], ["--vram-limit-gib", "0"],
+    ["--stage", "sometimes"],
 ])
-def test_incompatible_flags_are_rejected(flags):
+def test_invalid_settings_are_rejected(flags):
     with pytest.raises(SystemExit):
         T.arguments(["--from-scratch", *flags])
+
+
+def test_reference_execution_flags_are_accepted_recorded_and_reported(capsys):
+    """The reference's execution experiments have no counterpart to switch here: any combination parses, the
+    values reach the resume signature, and rank 0 says once per flag that it changes nothing and why."""
+    from warpstate_ai_b200.train.signature import train_signature
+    a = T.arguments(["--from-scratch", "--compile", "--compile-core", "--compile-mode", "reduce-overhead",
+                     "--gradient-mode", "compiled-autograd", "--ddp-batched-grad-copy", "--backward-layout", "paired",
+                     "--cache-core-weight-casts", "--activation-mode", "swiglu", "--overlap-swap-collectives"])
+    out = capsys.readouterr().out
+    for flag in ("--compile-mode reduce-overhead", "--backward-layout paired", "--gradient-mode compiled-autograd"):
+        assert f"note: {flag} has no effect here" in out
+    settings = train_signature(a, {"x": 1})["settings"]
+    assert settings["gradient_mode"] == "compiled-autograd" and settings["compile_mode"] == "reduce-overhead"
+    assert settings["cache_core_weight_casts"] is True and settings["ddp_batched_grad_copy"] is True
+    quiet = T.arguments(["--from-scratch"])
+    assert "no effect" not in capsys.readouterr().out and quiet.ddp_bucket_cap_mb == 0.0
+
+
+def test_bucket_cap_merges_small_cores_and_splits_large_buckets():
+    import torch
+    from warpstate_ai_b200 import WarpStateConfig, WarpStateLM
+    from warpstate_ai_b200.optim.arena import ParamArena
+    from warpstate_ai_b200.parallel.grad_sync import CollectiveGradSync
+    cfg = WarpStateConfig(vocab_size=64, d_model=32, n_heads=2, n_cores=4, logical_depth=4, ffn_hidden=48, chunk_size=8,
+                          gradient_checkpointing=False)
+    per_core = ParamArena(WarpStateLM(cfg), device=torch.device("cpu"))
+    assert len(per_core.buckets) == 5                                      # tail + one per core
+    core_bytes = 4 * (per_core.buckets[1].stop - per_core.buckets[1].start)
+    merged = ParamArena(WarpStateLM(cfg), device=torch.device("cpu"), bucket_cap_bytes=2 * core_bytes)
+    assert len(merged.buckets) == 3                                        # tail + two pairs of cores
+    sync = CollectiveGradSync(torch.device("cpu"), 2, 0, bucket_cap_bytes=4 * 1024)
+    sync.attach(merged, WarpStateLM(cfg))
+    assert sync.core_bucket == {0: 1, 2: 2}                                # the lowest core of a bucket completes it
+    for b in merged.buckets:
+        pieces = sync.pieces_of(b.index)
+        assert pieces[0][0] == b.start and sum(c for _, c in pieces) == b.stop - b.start
+        assert all(c <= 1024 and c % 4 == 0 for _, c in pieces)
+        assert all(pieces[i][0] + pieces[i][1] == pieces[i + 1][0] for i in range(len(pieces) - 1))
+
+
+def test_bootstrap_builds_an_environment_and_re_executes(monkeypatch, tmp_path):
+    """--bootstrap with pip, venv and exec replaced by recorders: the sequence of commands, and the command line
+    that is re-executed inside the environment."""
+    import subprocess
+    calls = []
+    monkeypatch.setattr(T, "ROOT", tmp_path)
+    (tmp_path / "launch").mkdir()
+    (tmp_path / "launch/requirements-training.txt").write_text("torch\n")
+
+    def fake_run(cmd, check=True):
+        calls.append(cmd)
+        if cmd[1:3] == ["-m", "venv"]:
+            (tmp_path / ".server-venv/bin").mkdir(parents=True)
+            (tmp_path / ".server-venv/bin/python").write_text("")
+
+    monkeypatch.setattr(subprocess, "run", fake_run)
+    monkeypatch.setattr(subprocess, "check_output", lambda cmd, text=True: "torch==0\n")
+    executed = {}
+    monkeypatch.setattr(T.os, "execv", lambda path, argv: executed.update(path=path, argv=argv))
+    monkeypatch.setattr(sys, "argv", ["run_40b.py", "--from-scratch", "--bootstrap", "--seq-len", "256"])
+    a = T.arguments(["--from-scratch", "--bootstrap", "--seq-len", "256"])
+    T.bootstrap(a)
+    assert [c[1:4] for c in calls][:2] == [["-m", "venv", str(tmp_path / ".server-venv")], ["-m", "pip", "install"]]
+    assert (tmp_path / ".server-venv/warpstate-deps-v1.json").exists()
+    assert executed["argv"][-1] == "--no-bootstrap" and "--bootstrap" not in executed["argv"]
+    assert executed["argv"][3:6] == ["--from-scratch", "--seq-len", "256"]
+    calls.clear()
+    T.bootstrap(T.arguments(["--from-scratch"]))      # off by default: nothing happens
+    assert calls == []
 
 
 def test_accepted_flag_combinations():

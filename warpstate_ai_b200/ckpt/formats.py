@@ -88,10 +88,12 @@ def model_from_checkpoint(checkpoint: dict, device: torch.device, dtype=torch.fl
 
 
 def server_state(*, signature, origin, history, cfg, model, optimizer, step, tokens_seen, val_loss, val_step,
-                 val_tokens, rng_by_rank) -> dict:
+                 val_tokens, rng_by_rank, model_state=None) -> dict:
+    """``model_state``: an already assembled unsharded state dict (sharded parameters), else ``model``'s own."""
     own = rng_by_rank[0]
+    weights = model_state if model_state is not None else clean_state_dict(model)
     return {"format": SERVER_FORMAT, "signature": signature, "origin": origin, "execution_history": history,
-            "config": vars(cfg).copy(), "model": clean_state_dict(model), "optimizer": optimizer.state_dict(),
+            "config": vars(cfg).copy(), "model": weights, "optimizer": optimizer.state_dict(),
             "step": step, "tokens_seen": tokens_seen, "val_loss": val_loss, "val_step": val_step,
             "val_tokens": val_tokens, "rng_by_rank": rng_by_rank, "rng_torch": own["torch"],
             "rng_cuda": [own["cuda"]], "rng_numpy": own["numpy"], "rng_python": own["python"]}

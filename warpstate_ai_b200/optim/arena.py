@@ -51,8 +51,11 @@ def _round_up(x: int, a: int) -> int:
     return (x + a - 1) // a * a
 
 
-def default_groups(model: torch.nn.Module) -> list[list[tuple[str, torch.nn.Parameter]]]:
-    """Group named parameters by gradient-readiness: tail group first, then one group per core."""
+def default_groups(model: torch.nn.Module, bucket_cap_bytes: int = 0) -> list[list[tuple[str, torch.nn.Parameter]]]:
+    """Group named parameters by gradient-readiness: tail group first, then one group per core.  With a
+    positive ``bucket_cap_bytes`` consecutive cores share a group while their FP32 gradients fit the cap
+    (what a DDP bucket cap does for small models, reference ops/distributed_execution.py:16-79); a core
+    larger than the cap stays one group and is split at reduction time by the synchroniser."""
     named = list(model.named_parameters())
     cores: dict[int, list] = {}
     tail = []
@@ -62,20 +65,27 @@ def default_groups(model: torch.nn.Module) -> list[list[tuple[str, torch.nn.Para
         else:
             tail.append((name, p))
     groups = [tail] if tail else []
+    open_group, open_bytes = None, 0
     for index in sorted(cores):
-        groups.append(cores[index])
+        size = 4 * sum(_round_up(p.numel(), ALIGN) for _, p in cores[index])
+        if open_group is not None and bucket_cap_bytes > 0 and open_bytes + size <= bucket_cap_bytes:
+            open_group.extend(cores[index])
+            open_bytes += size
+        else:
+            open_group, open_bytes = list(cores[index]), size
+            groups.append(open_group)
     return groups
 
 
 class ParamArena:
     def __init__(self, model: torch.nn.Module, device: torch.device | None = None,
-                 bf16_mirror: bool | None = None, groups=None, symmetric_alloc=None):
+                 bf16_mirror: bool | None = None, groups=None, symmetric_alloc=None, bucket_cap_bytes: int = 0):
         params = list(model.parameters())
         if not params:
             raise ValueError("model has no parameters")
         self.device = device or params[0].device
         self.order = list(model.named_parameters())
-        groups = groups if groups is not None else default_groups(model)
+        groups = groups if groups is not None else default_groups(model, bucket_cap_bytes)
         self.slots: list[Slot] = []
         self.buckets: list[Bucket] = []
         offset = 0

@@ -29,8 +29,9 @@ import torch.distributed as dist
 class GradSyncBase:
     kind = "none"
 
-    def __init__(self, device: torch.device, world: int, rank: int, group=None):
+    def __init__(self, device: torch.device, world: int, rank: int, group=None, bucket_cap_bytes: int = 0):
         self.device, self.world, self.rank, self.group = device, world, rank, group
+        self.bucket_cap_bytes = int(bucket_cap_bytes)   # largest range one reduction handles (0: whole buckets)
         self.arena = None
         self.core_bucket: dict[int, int] = {}
         self.reduced: set[int] = set()
@@ -45,8 +46,9 @@ class GradSyncBase:
         self.model = model
         for bucket in arena.buckets:
             cores = {int(n.split(".")[1]) for n in bucket.names if n.startswith("cores.")}
-            if len(cores) == 1 and all(n.startswith("cores.") for n in bucket.names):
-                self.core_bucket[cores.pop()] = bucket.index
+            if cores and all(n.startswith("cores.") for n in bucket.names):
+                # backward finishes the cores of a bucket from the highest index down: the lowest one completes it
+                self.core_bucket[min(cores)] = bucket.index
         self.core_index = {id(core): i for i, core in enumerate(getattr(model, "cores", []))}
 
     def begin_update(self) -> None:
@@ -82,6 +84,15 @@ class GradSyncBase:
     def status_word(self):
         return None
 
+    def pieces_of(self, bucket: int) -> list[tuple[int, int]]:
+        """``(start, count)`` ranges of a bucket, none larger than the cap (whole bucket without a cap)."""
+        b = self.arena.buckets[bucket]
+        total = b.stop - b.start
+        cap = (self.bucket_cap_bytes // 4) // 1024 * 1024
+        if cap <= 0 or total <= cap:
+            return [(b.start, total)]
+        return [(b.start + off, min(cap, total - off)) for off in range(0, total, cap)]
+
     # ---- implemented by subclasses
     def reduce_bucket(self, bucket: int) -> None:
         raise NotImplementedError
@@ -93,24 +104,25 @@ class GradSyncBase:
 class CollectiveGradSync(GradSyncBase):
     """all_reduce(SUM) / world per bucket through torch.distributed (NCCL or gloo)."""
 
-    def __init__(self, device, world, rank, group=None):
-        super().__init__(device, world, rank, group)
+    def __init__(self, device, world, rank, group=None, bucket_cap_bytes: int = 0):
+        super().__init__(device, world, rank, group, bucket_cap_bytes)
         self.kind = "nccl" if device.type == "cuda" else "gloo"
         self.stream = torch.cuda.Stream(device=device) if device.type == "cuda" else None
         self.pending = []
 
     def reduce_bucket(self, bucket: int) -> None:
-        b = self.arena.buckets[bucket]
-        view = self.arena.grad[b.start:b.stop]
+        views = [self.arena.grad[start:start + count] for start, count in self.pieces_of(bucket)]
         self.reduced.add(bucket)
         if self.stream is None:
-            dist.all_reduce(view, op=dist.ReduceOp.SUM, group=self.group)
-            view.mul_(1.0 / self.world)
+            for view in views:
+                dist.all_reduce(view, op=dist.ReduceOp.SUM, group=self.group)
+                view.mul_(1.0 / self.world)
             return
         self.stream.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(self.stream):
-            dist.all_reduce(view, op=dist.ReduceOp.SUM, group=self.group)
-            view.mul_(1.0 / self.world)
+            for view in views:
+                dist.all_reduce(view, op=dist.ReduceOp.SUM, group=self.group)
+                view.mul_(1.0 / self.world)
 
     def wait(self) -> None:
         if self.stream is not None:
@@ -134,8 +146,8 @@ class FusedGradSync(GradSyncBase):
     kind = "fused"
 
     def __init__(self, device, world, rank, group=None, ctas: int | None = None, budget_seconds: float | None = None,
-                 use_nvls: bool | None = None):
-        super().__init__(device, world, rank, group)
+                 use_nvls: bool | None = None, bucket_cap_bytes: int = 0):
+        super().__init__(device, world, rank, group, bucket_cap_bytes)
         from ..ops import _ext
         _ext.require()
         self.ctas = int(ctas or os.environ.get("WARPSTATE_COMM_CTAS", 32))
@@ -159,12 +171,18 @@ class FusedGradSync(GradSyncBase):
     def attach(self, arena, model) -> None:
         super().attach(arena, model)
         from . import symm
-        n_buckets = len(arena.buckets)
-        self.exchange_base = 2 * 8 * n_buckets        # words after the bucket flags: norm exchange ...
+        # one pair of flags (and one row of norm partials) per launch: a bucket above the cap is several launches
+        self.launch_ids: dict[int, list[int]] = {}
+        launches = 0
+        for b in arena.buckets:
+            count = 1 if getattr(arena, "segments", None) else len(self.pieces_of(b.index))
+            self.launch_ids[b.index] = list(range(launches, launches + count))
+            launches += count
+        self.exchange_base = 2 * 8 * launches         # words after the launch flags: norm exchange ...
         self.barrier_base = self.exchange_base + 24   # ... and the node barrier
         words = self.barrier_base + 8
         self.flag_sym = symm.allocate(max(words, 64), torch.int32, self.device, self.group)
-        self.partials = torch.zeros(n_buckets * self.ctas, dtype=torch.float32, device=self.device)
+        self.partials = torch.zeros(launches * self.ctas, dtype=torch.float32, device=self.device)
         mc = self.grad_sym.multicast_ptr
         if self.use_nvls is False:
             mc = 0
@@ -173,16 +191,20 @@ class FusedGradSync(GradSyncBase):
         self.flag_sym.barrier()
 
     def reduce_bucket(self, bucket: int) -> None:
-        b = self.arena.buckets[bucket]
         self.reduced.add(bucket)
-        segs = self.segments.get(bucket) or [(b.start, b.stop - b.start, self.push)]
+        segmented = self.segments.get(bucket)
+        if segmented:
+            work = [segmented]
+        else:
+            work = [[(start, count, self.push)] for start, count in self.pieces_of(bucket)]
         self.stream.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(self.stream):
-            torch.ops.ws_b200.grad_reduce_segments(
-                self.grad_sym.peer_ptrs, self.flag_sym.peer_ptrs, self.mc_ptr, self.rank, self.world,
-                [s[0] for s in segs], [s[1] for s in segs], [int(bool(s[2])) for s in segs], bucket, self.seq,
-                1.0 / self.world, self.ctas, self.partials[bucket * self.ctas:(bucket + 1) * self.ctas], self.status,
-                self.budget)
+            for launch, segs in zip(self.launch_ids[bucket], work):
+                torch.ops.ws_b200.grad_reduce_segments(
+                    self.grad_sym.peer_ptrs, self.flag_sym.peer_ptrs, self.mc_ptr, self.rank, self.world,
+                    [s[0] for s in segs], [s[1] for s in segs], [int(bool(s[2])) for s in segs], launch, self.seq,
+                    1.0 / self.world, self.ctas, self.partials[launch * self.ctas:(launch + 1) * self.ctas],
+                    self.status, self.budget)
 
     def wait(self) -> None:
         torch.cuda.current_stream(self.device).wait_stream(self.stream)
@@ -216,13 +238,14 @@ class FusedGradSync(GradSyncBase):
                 f"expected {expected}, saw {seen}")
 
 
-def make_grad_sync(device: torch.device, world: int, rank: int, group=None, kind: str = "auto"):
+def make_grad_sync(device: torch.device, world: int, rank: int, group=None, kind: str = "auto",
+                   bucket_cap_bytes: int = 0):
     if world <= 1:
         return None
     if kind == "auto":
         kind = "fused" if device.type == "cuda" else "collective"
     if kind == "fused":
-        return FusedGradSync(device, world, rank, group)
+        return FusedGradSync(device, world, rank, group, bucket_cap_bytes=bucket_cap_bytes)
     if kind in ("collective", "nccl", "gloo"):
-        return CollectiveGradSync(device, world, rank, group)
+        return CollectiveGradSync(device, world, rank, group, bucket_cap_bytes=bucket_cap_bytes)
     raise ValueError(f"unknown gradient synchronisation kind: {kind}")

@@ -52,7 +52,13 @@ class ShardedAdamW:
         self.max_grad_norm = max_grad_norm
         self.step_count = 0
         self.push_master = push_master
-        self.ranges = [bucket_slice(b.start, b.stop, rank, world) for b in arena.buckets]
+        # the ranges one reduction launch handles (whole buckets, or pieces under a bucket cap): ownership follows
+        # the kernel's split of each of them
+        if sync is not None and hasattr(sync, "pieces_of") and getattr(sync, "arena", None) is arena:
+            self.pieces = [(start, start + count) for b in arena.buckets for start, count in sync.pieces_of(b.index)]
+        else:
+            self.pieces = [(b.start, b.stop) for b in arena.buckets]
+        self.ranges = [bucket_slice(start, stop, rank, world) for start, stop in self.pieces]
         self.offsets = [0]
         for lo, hi in self.ranges:
             self.offsets.append(self.offsets[-1] + (hi - lo))
@@ -181,18 +187,18 @@ class ShardedAdamW:
         """Make ``full`` (arena-sized) whole on every rank from each rank's owned slices."""
         if self.world == 1:
             return
-        for b in self.arena.buckets:
-            n4 = (b.stop - b.start) // 4
+        for start, stop in self.pieces:
+            n4 = (stop - start) // 4
             per = 4 * ((n4 + self.world - 1) // self.world)
             if per == 0:
                 continue
-            lo, hi = bucket_slice(b.start, b.stop, self.rank, self.world)
+            lo, hi = bucket_slice(start, stop, self.rank, self.world)
             mine = torch.zeros(per, dtype=full.dtype, device=full.device)
             mine[:hi - lo].copy_(full[lo:hi])
             parts = [torch.empty_like(mine) for _ in range(self.world)]
             dist.all_gather(parts, mine, group=self.group)
             for r, part in enumerate(parts):
-                rlo, rhi = bucket_slice(b.start, b.stop, r, self.world)
+                rlo, rhi = bucket_slice(start, stop, r, self.world)
                 if r != self.rank and rhi > rlo:
                     full[rlo:rhi].copy_(part[:rhi - rlo])
 

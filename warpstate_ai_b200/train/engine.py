@@ -51,7 +51,8 @@ class Trainer:
     def __init__(self, model: torch.nn.Module, *, device: torch.device, rank: int = 0, world_size: int = 1,
                  lr: float = 1.5e-4, weight_decay: float = 0.1, betas=(0.9, 0.95), eps: float = 1e-8,
                  max_grad_norm: float | None = 1.0, grad_sync=None, bf16_autocast: bool = True,
-                 process_group=None, shard_optimizer: bool = False, shard_params: str | None = None):
+                 process_group=None, shard_optimizer: bool = False, shard_params: str | None = None,
+                 bucket_cap_bytes: int = 0):
         """``shard_params``: None (replicated parameters), ``"stream"`` or ``"resident"`` -- parameters,
         gradients and optimizer state of the core projections sharded over the ranks
         (`parallel.fsdp.ShardedParamState`)."""
@@ -62,7 +63,7 @@ class Trainer:
         self.process_group = process_group
         if grad_sync is None and world_size > 1:
             from ..parallel.grad_sync import make_grad_sync
-            grad_sync = make_grad_sync(device, world_size, rank, process_group)
+            grad_sync = make_grad_sync(device, world_size, rank, process_group, bucket_cap_bytes=bucket_cap_bytes)
         self.sync = grad_sync
         self.sharded = None
         if shard_params:
@@ -73,7 +74,7 @@ class Trainer:
             self.arena, self.optimizer = self.sharded.arena, self.sharded.optimizer
         else:
             alloc = grad_sync.alloc_grad_buffer if grad_sync is not None else None
-            self.arena = ParamArena(model, device=device, symmetric_alloc=alloc)
+            self.arena = ParamArena(model, device=device, symmetric_alloc=alloc, bucket_cap_bytes=bucket_cap_bytes)
             if self.sync is not None:
                 self.sync.attach(self.arena, model)
             if shard_optimizer and world_size > 1:
