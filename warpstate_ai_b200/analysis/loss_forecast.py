@@ -25,124 +25,175 @@ import hashlib
 import json
 import math
 import platform
+from dataclasses import dataclass
 from pathlib import Path
 
 import numpy as np
 from scipy.optimize import minimize_scalar
 
 ALPHA_RANGE = (1e-4, 3.0)
+MIN_BINS = 3
 
 
-def linear_for_alpha(x, y, alpha: float, fixed_floor):
-    """Closed-form (floor, amplitude, mse) of L = f + A x^-alpha for one alpha."""
-    z = x ** (-alpha)
-    if fixed_floor is None:
-        zc = z - z.mean()
-        denom = float(zc @ zc)
-        amplitude = float(zc @ (y - y.mean()) / denom) if denom > 0 else 0.0
-        floor = float(np.clip(y.mean() - amplitude * z.mean(), 0.0, y.min()))
-    else:
-        floor = float(fixed_floor)
-    amplitude = max(0.0, float(z @ (y - floor) / (z @ z)))
-    return floor, amplitude, float(np.mean((floor + amplitude * z - y) ** 2))
+# ----------------------------------------------------------------------------------- curve families
+class LogCurve:
+    """L = a + b ln t"""
+    name = "log"
+
+    def fit(self, t, loss) -> "Fitted":
+        design = np.stack([np.ones_like(t), np.log(t)], axis=1)
+        (a, b), *_ = np.linalg.lstsq(design, loss, rcond=None)
+        residual = design @ np.array([a, b]) - loss
+        return Fitted(self, {"model": self.name, "intercept": float(a), "slope": float(b),
+                             "rmse": float(np.sqrt(np.mean(residual ** 2)))})
+
+    def evaluate(self, p: dict, t):
+        return p["intercept"] + p["slope"] * np.log(t)
+
+    def log_crossing(self, p: dict, target: float):
+        return (target - p["intercept"]) / p["slope"] if p["slope"] < 0 else None
+
+
+class PowerCurve:
+    """L = f + A t^-alpha with A >= 0; the floor f is fitted in [0, min loss] or fixed by assumption.
+    For a given alpha the curve is linear in (f, A), so alpha is the only searched parameter."""
+
+    def __init__(self, floor: float | None = None):
+        self.floor = floor
+        self.name = "power_free" if floor is None else f"power_fixed:{floor}"
+
+    def _given_alpha(self, t, loss, alpha: float):
+        basis = t ** (-alpha)
+        if self.floor is None:
+            centred = basis - basis.mean()
+            spread = float(centred @ centred)
+            slope = float(centred @ (loss - loss.mean())) / spread if spread > 0 else 0.0
+            floor = float(min(max(loss.mean() - slope * basis.mean(), 0.0), loss.min()))
+        else:
+            floor = float(self.floor)
+        amplitude = max(float(basis @ (loss - floor)) / float(basis @ basis), 0.0)
+        return floor, amplitude, float(np.mean((floor + amplitude * basis - loss) ** 2))
+
+    def fit(self, t, loss) -> "Fitted":
+        def error(log_alpha):
+            return self._given_alpha(t, loss, math.exp(log_alpha))[2]
+
+        # the error can be flat on one side of its minimum: locate the best of a coarse grid, refine around it
+        grid = np.linspace(math.log(ALPHA_RANGE[0]), math.log(ALPHA_RANGE[1]), 200)
+        at = int(np.argmin([error(v) for v in grid]))
+        around = (grid[max(at - 1, 0)], grid[min(at + 1, grid.size - 1)])
+        refined = minimize_scalar(error, bounds=around, method="bounded", options={"xatol": 1e-10})
+        alpha = math.exp(float(refined.x))
+        floor, amplitude, mse = self._given_alpha(t, loss, alpha)
+        return Fitted(self, {"model": self.name, "floor": floor, "amplitude": amplitude, "alpha": alpha,
+                             "rmse": math.sqrt(mse), "alpha_at_search_boundary": at in (0, grid.size - 1)})
+
+    def evaluate(self, p: dict, t):
+        return p["floor"] + p["amplitude"] * t ** (-p["alpha"])
+
+    def log_crossing(self, p: dict, target: float):
+        if p["amplitude"] <= 0 or target <= p["floor"]:
+            return None
+        return math.log(p["amplitude"] / (target - p["floor"])) / p["alpha"]
+
+
+@dataclass
+class Fitted:
+    family: object
+    parameters: dict
+
+    def predict(self, tokens_b):
+        return self.family.evaluate(self.parameters, np.asarray(tokens_b, dtype=np.float64))
+
+    def crossing(self, target: float):
+        """Tokens (billions) at which the curve reaches ``target``; None if never (or beyond e^700)."""
+        where = self.family.log_crossing(self.parameters, target)
+        return math.exp(where) if where is not None and where < 700 else None
+
+
+def family_of(model: str):
+    if model == "log":
+        return LogCurve()
+    if model == "power_free":
+        return PowerCurve()
+    return PowerCurve(float(model.split(":", 1)[1]))
 
 
 def fit(x, y, model: str) -> dict:
-    if len(x) < 3:
-        raise ValueError("each fitting window needs at least three complete bins")
-    if model == "log":
-        slope, intercept = np.polyfit(np.log(x), y, 1)
-        mse = float(np.mean((intercept + slope * np.log(x) - y) ** 2))
-        return {"model": model, "intercept": float(intercept), "slope": float(slope), "rmse": math.sqrt(mse)}
-    fixed = None if model == "power_free" else float(model.split(":", 1)[1])
-    lo, hi = math.log(ALPHA_RANGE[0]), math.log(ALPHA_RANGE[1])
-    coarse = np.linspace(lo, hi, 200)  # the objective can have a flat shoulder: bracket the best coarse point
-    errors = [linear_for_alpha(x, y, math.exp(v), fixed)[2] for v in coarse]
-    best = int(np.argmin(errors))
-    bracket = (coarse[max(best - 1, 0)], coarse[min(best + 1, len(coarse) - 1)])
-    result = minimize_scalar(lambda v: linear_for_alpha(x, y, math.exp(v), fixed)[2], bounds=bracket, method="bounded",
-                             options={"xatol": 1e-10})
-    alpha = math.exp(float(result.x))
-    floor, amplitude, mse = linear_for_alpha(x, y, alpha, fixed)
-    return {"model": model, "floor": floor, "amplitude": amplitude, "alpha": alpha, "rmse": math.sqrt(mse),
-            "alpha_at_search_boundary": best in (0, len(coarse) - 1)}
+    if len(x) < MIN_BINS:
+        raise ValueError(f"a fitting window needs at least {MIN_BINS} complete bins")
+    return family_of(model).fit(np.asarray(x, dtype=np.float64), np.asarray(y, dtype=np.float64)).parameters
 
 
 def predict(parameters: dict, tokens_b):
-    t = np.asarray(tokens_b, dtype=np.float64)
-    if parameters["model"] == "log":
-        return parameters["intercept"] + parameters["slope"] * np.log(t)
-    return parameters["floor"] + parameters["amplitude"] * t ** (-parameters["alpha"])
+    return Fitted(family_of(parameters["model"]), parameters).predict(tokens_b)
 
 
 def crossing(parameters: dict, target: float):
-    """Tokens (billions) at which the fitted curve reaches ``target``; None if it never does."""
-    if parameters["model"] == "log":
-        if parameters["slope"] >= 0:
-            return None
-        exponent = (target - parameters["intercept"]) / parameters["slope"]
-    else:
-        if parameters["floor"] >= target or parameters["amplitude"] <= 0:
-            return None
-        exponent = math.log(parameters["amplitude"] / (target - parameters["floor"])) / parameters["alpha"]
-    return math.exp(exponent) if exponent < 700 else None
+    return Fitted(family_of(parameters["model"]), parameters).crossing(target)
 
 
+# ----------------------------------------------------------------------------------- binning
 def bin_rows(rows, width_b: float, first_b: float):
-    if not rows or any(b["tokens"] <= a["tokens"] for a, b in zip(rows, rows[1:])):
-        raise ValueError("validation snapshot must have strictly increasing token counts")
-    right = math.floor(rows[-1]["tokens"] / 1e9 / width_b) * width_b
-    bins = []
-    left = first_b
-    while left < right - 1e-12:
-        chosen = [r for r in rows if left <= r["tokens"] / 1e9 < left + width_b]
-        if not chosen:
-            raise ValueError(f"missing validation data in the bin starting at {left} B tokens")
-        bins.append({"left_B": left, "right_B": left + width_b,
-                     "tokens_B": float(np.mean([r["tokens"] / 1e9 for r in chosen])),
-                     "loss": float(np.mean([r["loss"] for r in chosen])), "count": len(chosen)})
+    """Mean token count and mean loss per complete bin ``[left, left + width)`` (billions of tokens), from
+    ``first_b`` to the last bin boundary the data reaches.  -> (bins, that boundary)"""
+    tokens_b = np.array([row["tokens"] for row in rows], dtype=np.float64) / 1e9
+    losses = np.array([row["loss"] for row in rows], dtype=np.float64)
+    if tokens_b.size == 0 or np.any(np.diff(tokens_b) <= 0):
+        raise ValueError("the validation rows must have strictly increasing token counts")
+    end = math.floor(tokens_b[-1] / width_b) * width_b
+    bins, left = [], first_b
+    while left < end - 1e-12:
+        inside = (tokens_b >= left) & (tokens_b < left + width_b)
+        if not inside.any():
+            raise ValueError(f"no validation row falls in the bin that starts at {left} B tokens")
+        bins.append({"left_B": left, "right_B": left + width_b, "tokens_B": float(tokens_b[inside].mean()),
+                     "loss": float(losses[inside].mean()), "count": int(inside.sum())})
         left = round(left + width_b, 12)
-    return bins, right
+    return bins, end
+
+
+CAVEATS = ["Illustrative extrapolations, not confidence intervals or ETAs.",
+           "Short hold-outs do not validate an extrapolation over orders of magnitude.",
+           "Learning-rate schedule, data repetition and distribution changes are not modelled.",
+           "Fixed floors are assumptions; a fitted floor above the target proves no architectural limit."]
+METHOD = ("equal-weight least squares in loss space on complete token bins; x is each bin's mean token count in "
+          "billions; power-law alpha minimised on [1e-4, 3] with closed-form floor/amplitude")
 
 
 def analyze(raw: bytes, *, bin_width_b: float = 0.25, first_bin_b: float = 1.0, window_starts=(1, 2, 3, 4, 5),
             fixed_floors=(1.5, 1.8, 1.9, 2.0, 2.1), budgets_b=(40.0, 268.435456, 1073.741824), target: float = 2.0,
             holdout_ends=(4, 5, 6)) -> dict:
     rows = [json.loads(line) for line in raw.splitlines() if line.strip()]
-    bins, right = bin_rows(rows, bin_width_b, first_bin_b)
-    x = np.array([b["tokens_B"] for b in bins])
-    y = np.array([b["loss"] for b in bins])
-    models = ("log", "power_free") + tuple(f"power_fixed:{f}" for f in fixed_floors)
+    bins, end = bin_rows(rows, bin_width_b, first_bin_b)
+    t = np.array([b["tokens_B"] for b in bins])
+    loss = np.array([b["loss"] for b in bins])
+    families = [LogCurve(), PowerCurve(), *(PowerCurve(f) for f in fixed_floors)]
     fits = []
     for start in window_starts:
-        chosen = x >= start
-        if chosen.sum() < 3:
+        window = t >= start
+        if window.sum() < MIN_BINS:
             continue
-        for model in models:
-            parameters = fit(x[chosen], y[chosen], model)
-            fits.append({"start_B": start, "end_B": right, "bins": int(chosen.sum()), "parameters": parameters,
-                         f"cross_{target:g}_tokens_B": crossing(parameters, target),
-                         "endpoint_losses": {f"{b:g}B": float(predict(parameters, b)) for b in budgets_b}})
+        for family in families:
+            curve = family.fit(t[window], loss[window])
+            fits.append({"start_B": start, "end_B": end, "bins": int(window.sum()), "parameters": curve.parameters,
+                         f"cross_{target:g}_tokens_B": curve.crossing(target),
+                         "endpoint_losses": {f"{b:g}B": float(curve.predict(b)) for b in budgets_b}})
     holdouts = []
-    for end in holdout_ends:
-        train, test = (x >= 2) & (x < end), (x >= end) & (x < end + 1)
-        if right < end + 1 or not test.any() or train.sum() < 3:
+    for stop in holdout_ends:
+        known, unseen = (t >= 2) & (t < stop), (t >= stop) & (t < stop + 1)
+        if end < stop + 1 or known.sum() < MIN_BINS or not unseen.any():
             continue
-        for model in models:
-            parameters = fit(x[train], y[train], model)
-            error = predict(parameters, x[test]) - y[test]
-            holdouts.append({"train_start_B": 2, "train_end_B": end, "test_end_B": end + 1, "parameters": parameters,
-                             "actual_mean_loss": float(y[test].mean()),
-                             "predicted_mean_loss": float(predict(parameters, x[test]).mean()),
-                             "mean_bias": float(error.mean()), "rmse": float(np.sqrt(np.mean(error ** 2)))})
-    return {"method": "equal-weight least squares in loss space on complete token bins; x is each bin's mean token "
-                      "count in billions; power-law alpha minimised on [1e-4, 3] with closed-form floor/amplitude",
-            "caveats": ["Illustrative extrapolations, not confidence intervals or ETAs.",
-                        "Short hold-outs do not validate an extrapolation over orders of magnitude.",
-                        "Learning-rate schedule, data repetition and distribution changes are not modelled.",
-                        "Fixed floors are assumptions; a fitted floor above the target proves no architectural limit."],
-            "source_sha256": hashlib.sha256(raw).hexdigest(), "source_rows": len(rows), "latest_validation": rows[-1],
-            "complete_bins_end_B": right, "bins": bins, "fits": fits, "holdouts": holdouts}
+        for family in families:
+            curve = family.fit(t[known], loss[known])
+            guess = curve.predict(t[unseen])
+            holdouts.append({"train_start_B": 2, "train_end_B": stop, "test_end_B": stop + 1,
+                             "parameters": curve.parameters, "actual_mean_loss": float(loss[unseen].mean()),
+                             "predicted_mean_loss": float(guess.mean()), "mean_bias": float((guess - loss[unseen]).mean()),
+                             "rmse": float(np.sqrt(np.mean((guess - loss[unseen]) ** 2)))})
+    return {"method": METHOD, "caveats": CAVEATS, "source_sha256": hashlib.sha256(raw).hexdigest(),
+            "source_rows": len(rows), "latest_validation": rows[-1], "complete_bins_end_B": end, "bins": bins,
+            "fits": fits, "holdouts": holdouts}
 
 
 def main(argv=None) -> int:

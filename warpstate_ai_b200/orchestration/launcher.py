@@ -86,127 +86,162 @@ class ProcessTree:
                     pass
 
 
+class Supervisor:
+    """Runs one child command and walks it through the stop protocol.
+
+    Phases: ``running`` -> (stop signal) ``draining``: the stop file exists, workers finish their update and
+    save -> (grace period over) ``terminating``: the child got SIGTERM -> (second deadline over) ``killing``:
+    every descendant ever seen is SIGKILLed.  Each phase has one entry action and one deadline."""
+
+    SIGNALS = (signal.SIGTERM, signal.SIGINT, signal.SIGUSR1)
+
+    def __init__(self, stop_path: Path, grace_seconds: float, terminate_seconds: float):
+        self.stop_path = stop_path
+        self.deadlines = {"draining": grace_seconds, "terminating": terminate_seconds}
+        self.phase = "running"
+        self.phase_began = None
+        self.stop_seen_at = None         # set by the signal handler; the loop does the phase change
+        self.child = None
+        self.tree = None
+
+    # ---- signal side: only record and touch the file (async-signal-simple)
+    def _on_signal(self, signum, frame) -> None:
+        if self.stop_seen_at is None:
+            self.stop_seen_at = time.monotonic()
+        os.close(os.open(self.stop_path, os.O_WRONLY | os.O_CREAT, 0o600))
+
+    def _enter(self, phase: str, now: float) -> None:
+        self.phase, self.phase_began = phase, now
+        self.tree.scan()
+        if phase == "draining":
+            print("Stop requested: letting the workers finish their update and checkpoint.", flush=True)
+        elif phase == "terminating":
+            print("The grace period is over: sending SIGTERM to the launcher process.", flush=True)
+            with _ignore_missing():
+                self.child.send_signal(signal.SIGTERM)
+        elif phase == "killing":
+            print("The termination deadline is over: killing every process of the job.", flush=True)
+            self.tree.kill_all()
+            self.child.kill()
+
+    def _advance(self, now: float) -> None:
+        if self.phase == "running" and self.stop_seen_at is not None:
+            self._enter("draining", self.stop_seen_at)
+        following = {"draining": "terminating", "terminating": "killing"}.get(self.phase)
+        if following and now - self.phase_began >= self.deadlines[self.phase]:
+            self._enter(following, now)
+
+    def run(self, command, environment, pass_fds=(), poll_seconds: float = 0.2, scan_seconds: float = 2.0) -> int:
+        saved = {sig: signal.signal(sig, self._on_signal) for sig in self.SIGNALS}
+        try:
+            if self.stop_seen_at is not None or self.stop_path.exists():
+                return 0                                   # a stop request was already pending: start nothing
+            self.child = subprocess.Popen(command, env=environment, start_new_session=True, pass_fds=pass_fds)
+            self.tree = ProcessTree(self.child.pid)
+            print(f"Started PID {self.child.pid}; a stop request creates {self.stop_path}", flush=True)
+            next_scan = 0.0
+            while self.child.poll() is None and self.phase != "killing":
+                now = time.monotonic()
+                if now >= next_scan:
+                    self.tree.scan()
+                    next_scan = now + scan_seconds
+                self._advance(now)
+                with _ignore_timeout():
+                    self.child.wait(timeout=poll_seconds)
+            if self.phase == "killing":
+                self.child.wait(timeout=5)
+            return self.child.returncode
+        finally:
+            if self.child is not None:
+                self.tree.scan()
+                if self.child.poll() is None:
+                    self.tree.kill_all()
+                    self.child.kill()
+                    self.child.wait(timeout=5)
+                self.tree.kill_all()                       # orphans of a child that exited on its own
+            for sig, handler in saved.items():
+                signal.signal(sig, handler)
+
+
+class _ignore_missing:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, kind, value, trace):
+        return kind is not None and issubclass(kind, ProcessLookupError)
+
+
+class _ignore_timeout:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, kind, value, trace):
+        return kind is not None and issubclass(kind, subprocess.TimeoutExpired)
+
+
 def supervise(command, stop_path, environment, *, grace_seconds: float = 820, terminate_seconds: float = 45,
               pass_fds=(), poll_seconds: float = 0.2, scan_seconds: float = 2.0) -> int:
-    stop_path = workspace_path(stop_path)
-    state = {"stopped_at": None}
-    previous = {}
+    """Run ``command`` under the stop protocol; returns its exit status (negative: killed by that signal)."""
+    supervisor = Supervisor(workspace_path(stop_path), grace_seconds, terminate_seconds)
+    return supervisor.run(command, environment, pass_fds, poll_seconds, scan_seconds)
 
-    def request_stop(signum, frame):
-        if state["stopped_at"] is None:
-            state["stopped_at"] = time.monotonic()
-        os.close(os.open(stop_path, os.O_CREAT | os.O_WRONLY, 0o600))
 
-    for sig in (signal.SIGTERM, signal.SIGINT, signal.SIGUSR1):
-        previous[sig] = signal.signal(sig, request_stop)
-    child = None
-    tree = None
-    try:
-        if state["stopped_at"] is not None or stop_path.exists():
-            return 0
-        child = subprocess.Popen(command, env=environment, start_new_session=True, pass_fds=pass_fds)
-        tree = ProcessTree(child.pid)
-        print(f"Training launcher started PID {child.pid}; stop requests use {stop_path}", flush=True)
-        last_scan = 0.0
-        announced = False
-        terminated_at = None
-        while child.poll() is None:
-            now = time.monotonic()
-            if now - last_scan >= scan_seconds:
-                tree.scan()
-                last_scan = now
-            stopped_at = state["stopped_at"]
-            if stopped_at is not None:
-                if not announced:
-                    print("Stop requested; waiting for the current update and checkpoint.", flush=True)
-                    announced = True
-                if terminated_at is None and now - stopped_at >= grace_seconds:
-                    tree.scan()
-                    print("Graceful-stop deadline exceeded; asking torchrun to terminate its workers.", flush=True)
-                    try:
-                        child.send_signal(signal.SIGTERM)
-                    except ProcessLookupError:
-                        pass
-                    terminated_at = now
-                elif terminated_at is not None and now - terminated_at >= terminate_seconds:
-                    tree.scan()
-                    print("Termination deadline exceeded; killing remaining training processes.", flush=True)
-                    tree.kill_all()
-                    child.kill()
-                    child.wait(timeout=5)
-                    break
-            try:
-                child.wait(timeout=poll_seconds)
-            except subprocess.TimeoutExpired:
-                pass
-        return child.returncode
-    finally:
-        if child is not None and tree is not None:
-            tree.scan()
-            if child.poll() is None:
-                tree.kill_all()
-                child.kill()
-                child.wait(timeout=5)
-            tree.kill_all()
-        for sig, handler in previous.items():
-            signal.signal(sig, handler)
+CACHE_VARIABLES = {"XDG_CACHE_HOME": "", "PIP_CACHE_DIR": "pip", "TORCH_HOME": "torch", "CUDA_CACHE_PATH": "cuda",
+                   "TORCH_EXTENSIONS_DIR": "torch-extensions"}
 
 
 def training_environment(work: Path) -> dict:
+    """The child's environment: every cache and temporary directory inside the workspace, no bytecode files,
+    and the stop file the workers poll."""
     root = workspace_root()
-    cache = workspace_path(root / ".cache")
-    hf = workspace_path(work / "hf-cache")
-    locations = {"TMPDIR": root / "tmp", "XDG_CACHE_HOME": cache, "PIP_CACHE_DIR": cache / "pip",
-                 "TORCH_HOME": cache / "torch", "CUDA_CACHE_PATH": cache / "cuda",
-                 "TORCH_EXTENSIONS_DIR": cache / "torch-extensions", "HF_HOME": hf, "HF_DATASETS_CACHE": hf / "datasets"}
-    environment = os.environ.copy()
-    for key, value in locations.items():
-        path = workspace_path(value)
-        path.mkdir(parents=True, exist_ok=True)
-        environment[key] = str(path)
-    environment["PYTHONDONTWRITEBYTECODE"] = "1"
+    places = {"TMPDIR": root / "tmp", "HF_HOME": work / "hf-cache", "HF_DATASETS_CACHE": work / "hf-cache/datasets"}
+    places.update({name: root / ".cache" / sub for name, sub in CACHE_VARIABLES.items()})
+    environment = dict(os.environ, PYTHONDONTWRITEBYTECODE="1")
+    for name, place in places.items():
+        place = workspace_path(place)
+        place.mkdir(parents=True, exist_ok=True)
+        environment[name] = str(place)
     environment["WARPSTATE_STOP_FILE"] = str(workspace_path(work / "control/training-stop-request"))
     return environment
 
 
 def build_command(processes: int, runner: Path, work: Path, logs: Path, extra) -> list[str]:
-    command = [sys.executable]
+    """One interpreter for a single process, otherwise a standalone ``torch.distributed.run`` on the loopback."""
+    prefix = [sys.executable]
     if processes > 1:
-        command += ["-m", "torch.distributed.run", "--standalone", "--local-addr", "127.0.0.1", "--nnodes", "1",
-                    "--nproc-per-node", str(processes), "--log-dir", str(logs)]
-    return command + [str(runner), "--work-dir", str(work), *extra]
+        prefix += ["-m", "torch.distributed.run", "--standalone", "--local-addr", "127.0.0.1", "--nnodes", "1",
+                   "--nproc-per-node", str(processes), "--log-dir", str(logs)]
+    return [*prefix, str(runner), "--work-dir", str(work), *extra]
 
 
 def main(argv=None) -> int:
-    parser = argparse.ArgumentParser(description=__doc__)
-    parser.add_argument("--processes", type=int, default=8)
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--processes", type=int, default=8, help="worker processes (one per GPU)")
     parser.add_argument("--work-dir", type=Path, default=PACKAGE / "work")
     parser.add_argument("--runner", type=Path, default=PACKAGE / "run_40b.py")
-    parser.add_argument("--grace-seconds", type=float, default=820)
-    parser.add_argument("--terminate-seconds", type=float, default=45)
-    parser.add_argument("runner_args", nargs=argparse.REMAINDER)
+    parser.add_argument("--grace-seconds", type=float, default=820, help="time the workers get to stop by themselves")
+    parser.add_argument("--terminate-seconds", type=float, default=45, help="time between SIGTERM and SIGKILL")
+    parser.add_argument("runner_args", nargs=argparse.REMAINDER, help="after --: arguments of the runner")
     args = parser.parse_args(argv)
     if args.processes < 1:
-        parser.error("--processes must be positive")
-    extra = args.runner_args[1:] if args.runner_args[:1] == ["--"] else args.runner_args
-    if any(v == "--work-dir" or v.startswith("--work-dir=") for v in extra):
-        parser.error("Pass --work-dir to the launcher, before the -- separator")
+        parser.error("--processes must be at least 1")
+    forwarded = args.runner_args[1:] if args.runner_args[:1] == ["--"] else args.runner_args
+    if any(item.split("=", 1)[0] == "--work-dir" for item in forwarded):
+        parser.error("--work-dir belongs to the launcher (before the -- separator), which passes it on")
     try:
         work = workspace_path(args.work_dir)
-        control = workspace_path(work / "control")
-        logs = workspace_path(work / "logs/torchrun-training")
-        stop_path = workspace_path(control / "training-stop-request")
-        lock_path = workspace_path(control / "training-launcher.lock")
-    except ValueError as error:
-        parser.error(str(error))
+        control, logs = workspace_path(work / "control"), workspace_path(work / "logs/torchrun-training")
+    except ValueError as problem:
+        parser.error(str(problem))
     control.mkdir(parents=True, exist_ok=True)
-    with process_lock(lock_path):
-        stop_path.unlink(missing_ok=True)
+    stop_file = control / "training-stop-request"
+    with process_lock(control / "training-launcher.lock"):
+        stop_file.unlink(missing_ok=True)
         logs.mkdir(parents=True, exist_ok=True)
-        result = supervise(build_command(args.processes, args.runner, work, logs, extra), stop_path,
+        status = supervise(build_command(args.processes, args.runner, work, logs, forwarded), stop_file,
                            training_environment(work), grace_seconds=args.grace_seconds,
                            terminate_seconds=args.terminate_seconds)
-    return 128 - result if result < 0 else result
+    return 128 - status if status < 0 else status
 
 
 if __name__ == "__main__":
