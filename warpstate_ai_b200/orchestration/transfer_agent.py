@@ -31,30 +31,30 @@ from pathlib import Path
 BLOCK = 1 << 20
 
 
+# ------------------------------------------------------------------------------------ confinement and file helpers
 def root() -> Path:
     return Path(os.environ.get("WARPSTATE_WORKSPACE", "/workspace/WarpState")).resolve()
 
 
 def confined(value) -> Path:
-    """Absolute path below the workspace root with no symlink in any component."""
-    path = Path(os.path.abspath(value))
-    base = root()
-    if path == base or not path.is_relative_to(base):
-        raise ValueError(f"Path must be below {base}: {path}")
-    current = base
-    for part in path.relative_to(base).parts:
-        current = current / part
-        if current.is_symlink():
-            raise ValueError(f"Symlink is not allowed: {current}")
+    """``value`` as an absolute path strictly below the workspace root, with no symlink on the way down."""
+    base, path = root(), Path(os.path.abspath(value))
+    if base not in path.parents:
+        raise ValueError(f"{path} is not below {base}")
+    for ancestor in [path, *path.parents]:
+        if ancestor == base:
+            break
+        if ancestor.is_symlink():
+            raise ValueError(f"{ancestor} is a symlink; transfers follow none")
     return path
 
 
 def open_regular(path, flags, mode=0o600) -> int:
     fd = os.open(confined(path), flags | os.O_NOFOLLOW, mode)
-    if not stat.S_ISREG(os.fstat(fd).st_mode):
-        os.close(fd)
-        raise ValueError(f"Not a regular file: {path}")
-    return fd
+    if stat.S_ISREG(os.fstat(fd).st_mode):
+        return fd
+    os.close(fd)
+    raise ValueError(f"{path} is not a regular file")
 
 
 def sync_dir(path) -> None:
@@ -66,101 +66,120 @@ def sync_dir(path) -> None:
 
 
 def write_json(path: Path, value) -> None:
-    temporary = confined(f"{path}.{uuid.uuid4().hex}.tmp")
-    fd = open_regular(temporary, os.O_WRONLY | os.O_CREAT | os.O_EXCL)
+    """Replace ``path`` with ``value`` (sorted keys) through a uniquely named sibling."""
+    sibling = confined(f"{path}.{uuid.uuid4().hex}.tmp")
     try:
-        with os.fdopen(fd, "w") as stream:
-            stream.write(json.dumps(value, sort_keys=True) + "\n")
-            stream.flush()
-            os.fsync(stream.fileno())
-        os.replace(temporary, path)
+        with os.fdopen(open_regular(sibling, os.O_WRONLY | os.O_CREAT | os.O_EXCL), "w") as out:
+            out.write(json.dumps(value, sort_keys=True) + "\n")
+            out.flush()
+            os.fsync(out.fileno())
+        os.replace(sibling, path)
         sync_dir(path.parent)
     finally:
-        if temporary.exists():
-            temporary.unlink()
+        if sibling.exists():
+            sibling.unlink()
 
 
 def read_json(path):
-    with os.fdopen(open_regular(path, os.O_RDONLY), "r") as stream:
-        return json.load(stream)
+    with os.fdopen(open_regular(path, os.O_RDONLY), "r") as source:
+        return json.load(source)
+
+
+def blocks(stream, count=None, exact=True):
+    """``count`` bytes of ``stream`` (all of it when None) in pieces of at most BLOCK bytes.  With ``exact`` an
+    early end of the stream is an error, otherwise the pieces simply stop."""
+    left = count
+    while left is None or left > 0:
+        piece = stream.read(BLOCK if left is None else min(BLOCK, left))
+        if not piece:
+            if left and exact:
+                raise ValueError("the file ended before the expected number of bytes")
+            return
+        yield piece
+        if left is not None:
+            left -= len(piece)
 
 
 def sha_range(path, offset=0, count=None) -> str:
-    h = hashlib.sha256()
+    digest = hashlib.sha256()
     with os.fdopen(open_regular(path, os.O_RDONLY), "rb") as stream:
         stream.seek(offset)
-        while count is None or count > 0:
-            data = stream.read(BLOCK if count is None else min(BLOCK, count))
-            if not data:
-                if count:
-                    raise ValueError("Unexpected end of file during verification")
-                break
-            h.update(data)
-            if count is not None:
-                count -= len(data)
-    return h.hexdigest()
+        for piece in blocks(stream, count):
+            digest.update(piece)
+    return digest.hexdigest()
 
 
 def file_identity(info) -> list:
     if not stat.S_ISREG(info.st_mode):
-        raise ValueError("Source is not a regular file")
+        raise ValueError("the source is not a regular file")
     return [info.st_dev, info.st_ino, info.st_size, info.st_mtime_ns, info.st_ctime_ns]
 
 
 def chunk_manifest(stream, chunk_size: int) -> dict:
-    whole, chunks, size = hashlib.sha256(), [], 0
+    """Size, whole-file SHA-256 and one SHA-256 per ``chunk_size`` bytes of ``stream``."""
+    whole, per_chunk, size = hashlib.sha256(), [], 0
     while True:
-        part, used = hashlib.sha256(), 0
-        while used < chunk_size:
-            data = stream.read(min(BLOCK, chunk_size - used))
-            if not data:
-                break
-            whole.update(data)
-            part.update(data)
-            used += len(data)
-        if not used:
+        one, got = hashlib.sha256(), 0
+        for piece in blocks(stream, chunk_size, exact=False):
+            one.update(piece)
+            whole.update(piece)
+            got += len(piece)
+        if got == 0:
             break
-        chunks.append(part.hexdigest())
-        size += used
-    return {"version": 1, "size": size, "sha256": whole.hexdigest(), "chunk_size": chunk_size, "chunk_sha256": chunks}
+        per_chunk.append(one.hexdigest())
+        size += got
+        if got < chunk_size:
+            break
+    return {"version": 1, "size": size, "sha256": whole.hexdigest(), "chunk_size": chunk_size, "chunk_sha256": per_chunk}
 
 
 # ------------------------------------------------------------------------------------ source side
+class SourceFile:
+    """The file being sent, held open; every action ends by checking that it is still the same file."""
+
+    def __init__(self, path):
+        self.path = confined(path)
+        self.stream = os.fdopen(os.open(self.path, os.O_RDONLY | os.O_NOFOLLOW), "rb")
+        self.identity = file_identity(os.fstat(self.stream.fileno()))
+
+    def require_unchanged(self) -> None:
+        now = (file_identity(os.fstat(self.stream.fileno())), file_identity(os.stat(self.path, follow_symlinks=False)))
+        if now != (self.identity, self.identity):
+            raise ValueError("the source file changed during the transfer")
+
+    def require_identity(self, expected) -> None:
+        if self.identity != expected:
+            raise ValueError("the source file changed during the transfer")
+
+    def manifest(self, chunk_size: int) -> dict:
+        if chunk_size < 1:
+            raise ValueError("the chunk size must be at least one byte")
+        described = chunk_manifest(self.stream, chunk_size)
+        self.require_unchanged()
+        return {"manifest": described, "identity": self.identity}
+
+    def send(self, offset: int, length: int, out) -> None:
+        if offset < 0 or length < 0 or offset + length > self.identity[2]:
+            raise ValueError("the requested range lies outside the source file")
+        self.stream.seek(offset)
+        for piece in blocks(self.stream, length):
+            out.write(piece)
+        out.flush()
+        self.require_unchanged()
+
+
 def source_action(action: str, argv: list) -> None:
-    path = confined(argv[0])
-    with os.fdopen(os.open(path, os.O_RDONLY | os.O_NOFOLLOW), "rb") as stream:
-        before = file_identity(os.fstat(stream.fileno()))
-
-        def unchanged():
-            if file_identity(os.fstat(stream.fileno())) != before or file_identity(os.stat(path, follow_symlinks=False)) != before:
-                raise ValueError("Source changed during transfer")
-
+    source = SourceFile(argv[0])
+    with source.stream:
         if action == "manifest":
-            chunk = int(argv[1])
-            if chunk < 1:
-                raise ValueError("Chunk size must be positive")
-            manifest = chunk_manifest(stream, chunk)
-            unchanged()
-            print(json.dumps({"manifest": manifest, "identity": before}))
+            print(json.dumps(source.manifest(int(argv[1]))))
             return
-        if before != json.loads(argv[1]):
-            raise ValueError("Source changed during transfer")
+        source.require_identity(json.loads(argv[1]))
         if action == "identity":
-            unchanged()
-            print(json.dumps({"identity": before}))
-            return
-        offset, remaining = int(argv[2]), int(argv[3])
-        if offset < 0 or remaining < 0 or offset + remaining > before[2]:
-            raise ValueError("Invalid source chunk range")
-        stream.seek(offset)
-        while remaining:
-            data = stream.read(min(BLOCK, remaining))
-            if not data:
-                raise ValueError("Source ended early")
-            sys.stdout.buffer.write(data)
-            remaining -= len(data)
-        sys.stdout.buffer.flush()
-        unchanged()
+            source.require_unchanged()
+            print(json.dumps({"identity": source.identity}))
+        else:
+            source.send(int(argv[2]), int(argv[3]), sys.stdout.buffer)
 
 
 # ---------------------------------------------------------------------------------- receiver side
@@ -169,122 +188,144 @@ def chunk_extent(state: dict, index: int):
     return offset, min(state["chunk_size"], state["size"] - offset)
 
 
-def receiver_action(action: str, argv: list) -> None:
-    target, expected = confined(argv[0]), argv[1]
-    target.parent.mkdir(parents=True, exist_ok=True)
-    confined(target.parent)
-    partial = confined(f"{target}.uploading")
-    state_path = confined(f"{target}.upload-state.json")
-    receipts = confined(f"{target}.upload-chunks")
-    lock = open_regular(f"{target}.upload.lock", os.O_RDWR | os.O_CREAT)
-    fcntl.flock(lock, fcntl.LOCK_SH if action == "write" else fcntl.LOCK_EX)
+def publish_noreplace(source: Path, target: Path) -> None:
+    rename = ctypes.CDLL(None, use_errno=True).renameat2
+    rename.restype = ctypes.c_int
+    rename.argtypes = [ctypes.c_int, ctypes.c_char_p, ctypes.c_int, ctypes.c_char_p, ctypes.c_uint]
+    if rename(-100, os.fsencode(source), -100, os.fsencode(target), 1) != 0:      # AT_FDCWD, RENAME_NOREPLACE
+        number = ctypes.get_errno()
+        raise OSError(number, os.strerror(number), str(target))
+    sync_dir(target.parent)
 
-    def already_published(size: int) -> bool:
-        if not target.exists():
+
+class Upload:
+    """Receiver state of one destination file: the partial file, its manifest and the chunk receipts."""
+
+    def __init__(self, target, expected_sha: str, exclusive: bool):
+        self.target, self.expected = confined(target), expected_sha
+        self.target.parent.mkdir(parents=True, exist_ok=True)
+        confined(self.target.parent)
+        self.partial = confined(f"{self.target}.uploading")
+        self.state_path = confined(f"{self.target}.upload-state.json")
+        self.receipts = confined(f"{self.target}.upload-chunks")
+        self.lock = open_regular(f"{self.target}.upload.lock", os.O_RDWR | os.O_CREAT)
+        fcntl.flock(self.lock, fcntl.LOCK_EX if exclusive else fcntl.LOCK_SH)   # chunk writers share, the rest exclude
+        self.state = None
+
+    def receipt(self, index: int) -> Path:
+        return confined(self.receipts / f"{index:08d}.json")
+
+    def published(self, size: int) -> bool:
+        """True when the destination already holds exactly this file; raises when it holds another."""
+        if not self.target.exists():
             return False
-        if target.stat().st_size != size or sha_range(target) != expected:
-            raise ValueError(f"Existing destination differs; refusing overwrite: {target}")
-        return True
+        if self.target.stat().st_size == size and sha_range(self.target) == self.expected:
+            return True
+        raise ValueError(f"{self.target} exists with other contents; it is never overwritten")
 
-    if action == "prepare":
-        incoming = json.load(sys.stdin)
-        if incoming["sha256"] != expected:
-            raise ValueError("Source identity mismatch")
-        if already_published(incoming["size"]):
-            print(json.dumps({"complete": True, "sha256": expected}))
-            return
-        if state_path.exists():
-            state = read_json(state_path)
-            if state != incoming:
-                raise ValueError("Partial upload belongs to a different source or chunk size")
+    def load_state(self) -> None:
+        self.state = read_json(self.state_path)
+        if self.state["sha256"] != self.expected:
+            raise ValueError("the partial upload belongs to another source file")
+
+    # ---- prepare
+    def prepare(self, incoming: dict) -> dict:
+        if incoming["sha256"] != self.expected:
+            raise ValueError("the manifest does not describe the announced source file")
+        if self.published(incoming["size"]):
+            return {"complete": True, "sha256": self.expected}
+        if self.state_path.exists():
+            if read_json(self.state_path) != incoming:
+                raise ValueError("a partial upload of another source or chunk size is in the way")
+        elif self.partial.exists() or self.receipts.exists():
+            raise ValueError("upload sidecars without a manifest are in the way; not touching them")
         else:
-            if partial.exists() or receipts.exists():
-                raise ValueError("Unclaimed upload sidecar exists; refusing to replace it")
-            write_json(state_path, incoming)  # identity first: an interruption here can resume
-            state = incoming
-        if not partial.exists():
-            fd = open_regular(partial, os.O_WRONLY | os.O_CREAT | os.O_EXCL)
+            write_json(self.state_path, incoming)     # the manifest comes first: any later interruption can resume
+        self.state = incoming
+        if not self.partial.exists():
+            fd = open_regular(self.partial, os.O_WRONLY | os.O_CREAT | os.O_EXCL)
             try:
-                os.ftruncate(fd, state["size"])
+                os.ftruncate(fd, incoming["size"])
                 os.fsync(fd)
             finally:
                 os.close(fd)
-        if partial.stat().st_size != state["size"]:
-            raise ValueError("Partial upload has an unexpected size")
-        receipts.mkdir(exist_ok=True)
-        done = []
-        for index, want in enumerate(state["chunk_sha256"]):
-            receipt = confined(receipts / f"{index:08d}.json")
-            if not receipt.exists():
-                continue
-            offset, length = chunk_extent(state, index)
-            try:
-                good = read_json(receipt) == {"sha256": want, "size": length} and sha_range(partial, offset, length) == want
-            except (ValueError, OSError):
-                good = False
-            if good:
-                done.append(index)
-            else:
-                receipt.unlink()
-        sync_dir(receipts)
-        print(json.dumps({"complete": False, "completed": done}))
-        return
+        if self.partial.stat().st_size != incoming["size"]:
+            raise ValueError("the partial file does not have the size its manifest states")
+        self.receipts.mkdir(exist_ok=True)
+        kept = [index for index in range(len(incoming["chunk_sha256"])) if self._receipt_holds(index)]
+        sync_dir(self.receipts)
+        return {"complete": False, "completed": kept}
 
-    state = read_json(state_path)
-    if state["sha256"] != expected:
-        raise ValueError("Upload source identity mismatch")
-    if action == "write":
-        index = int(argv[2])
-        if not 0 <= index < len(state["chunk_sha256"]):
-            raise ValueError("Invalid chunk index")
-        offset, length = chunk_extent(state, index)
-        h = hashlib.sha256()
-        fd = open_regular(partial, os.O_WRONLY)
+    def _receipt_holds(self, index: int) -> bool:
+        """Re-hash a receipted chunk; a receipt that no longer matches is dropped."""
+        note = self.receipt(index)
+        if not note.exists():
+            return False
+        offset, length = chunk_extent(self.state, index)
+        want = self.state["chunk_sha256"][index]
         try:
-            remaining, position = length, offset
-            while remaining:
-                data = sys.stdin.buffer.read(min(BLOCK, remaining))
-                if not data:
-                    raise ValueError("Upload stream ended early")
-                h.update(data)
-                view = memoryview(data)
-                while view:
-                    wrote = os.pwrite(fd, view, position)
-                    if wrote <= 0:
-                        raise OSError("pwrite made no progress")
-                    view = view[wrote:]
-                    position += wrote
-                remaining -= len(data)
-            if sys.stdin.buffer.read(1):
-                raise ValueError("Upload stream exceeded its chunk length")
-            if h.hexdigest() != state["chunk_sha256"][index]:
-                raise ValueError("Chunk SHA256 mismatch")
+            good = read_json(note) == {"sha256": want, "size": length} and sha_range(self.partial, offset, length) == want
+        except (OSError, ValueError):
+            good = False
+        if not good:
+            note.unlink()
+        return good
+
+    # ---- write
+    def write(self, index: int, incoming) -> dict:
+        self.load_state()
+        if not 0 <= index < len(self.state["chunk_sha256"]):
+            raise ValueError("no such chunk")
+        offset, length = chunk_extent(self.state, index)
+        digest = hashlib.sha256()
+        fd = open_regular(self.partial, os.O_WRONLY)
+        try:
+            at = offset
+            for piece in blocks(incoming, length):
+                digest.update(piece)
+                rest = memoryview(piece)
+                while rest:
+                    done = os.pwrite(fd, rest, at)
+                    if done <= 0:
+                        raise OSError("pwrite wrote nothing")
+                    rest, at = rest[done:], at + done
+            if incoming.read(1):
+                raise ValueError("more bytes arrived than the chunk holds")
+            if digest.hexdigest() != self.state["chunk_sha256"][index]:
+                raise ValueError("chunk SHA256 mismatch")
             os.fsync(fd)
         finally:
             os.close(fd)
-        write_json(confined(receipts / f"{index:08d}.json"), {"sha256": h.hexdigest(), "size": length})
-        print(json.dumps({"index": index, "sha256": h.hexdigest(), "bytes": length}))
-        return
-    if action != "finalize":
-        raise ValueError("Unknown receiver action")
-    if already_published(state["size"]):
-        print(json.dumps({"complete": True, "sha256": expected, "bytes": state["size"]}))
-        return
-    for index, want in enumerate(state["chunk_sha256"]):
-        _, length = chunk_extent(state, index)
-        receipt = confined(receipts / f"{index:08d}.json")
-        if not receipt.exists() or read_json(receipt) != {"sha256": want, "size": length}:
-            raise ValueError(f"Missing or invalid receipt for chunk {index}")
-    if partial.stat().st_size != state["size"] or sha_range(partial) != expected:
-        raise ValueError("Full destination SHA256 mismatch; partial upload retained")
-    libc = ctypes.CDLL(None, use_errno=True)
-    libc.renameat2.argtypes = [ctypes.c_int, ctypes.c_char_p, ctypes.c_int, ctypes.c_char_p, ctypes.c_uint]
-    libc.renameat2.restype = ctypes.c_int
-    if libc.renameat2(-100, os.fsencode(partial), -100, os.fsencode(target), 1):
-        code = ctypes.get_errno()
-        raise OSError(code, os.strerror(code), str(target))
-    sync_dir(target.parent)
-    print(json.dumps({"complete": True, "sha256": expected, "bytes": state["size"]}))
+        write_json(self.receipt(index), {"sha256": digest.hexdigest(), "size": length})
+        return {"index": index, "sha256": digest.hexdigest(), "bytes": length}
+
+    # ---- finalize
+    def finalize(self) -> dict:
+        self.load_state()
+        outcome = {"complete": True, "sha256": self.expected, "bytes": self.state["size"]}
+        if self.published(self.state["size"]):
+            return outcome
+        for index, want in enumerate(self.state["chunk_sha256"]):
+            note = self.receipt(index)
+            if not note.exists() or read_json(note) != {"sha256": want, "size": chunk_extent(self.state, index)[1]}:
+                raise ValueError(f"chunk {index} has no valid receipt")
+        if self.partial.stat().st_size != self.state["size"] or sha_range(self.partial) != self.expected:
+            raise ValueError("the assembled file does not hash to the source's SHA256; the partial upload is kept")
+        publish_noreplace(self.partial, self.target)
+        return outcome
+
+
+def receiver_action(action: str, argv: list) -> None:
+    upload = Upload(argv[0], argv[1], exclusive=action != "write")
+    if action == "prepare":
+        result = upload.prepare(json.load(sys.stdin))
+    elif action == "write":
+        result = upload.write(int(argv[2]), sys.stdin.buffer)
+    elif action == "finalize":
+        result = upload.finalize()
+    else:
+        raise ValueError(f"unknown receiver action {action}")
+    print(json.dumps(result))
 
 
 def agent_main(argv: list) -> None:
@@ -294,7 +335,7 @@ def agent_main(argv: list) -> None:
     elif action in ("prepare", "write", "finalize"):
         receiver_action(action, argv[1:])
     else:
-        raise ValueError(f"Unknown action {action}")
+        raise ValueError(f"unknown action {action}")
 
 
 if __name__ == "__main__":
