@@ -192,11 +192,34 @@ def test_kernel_decode_path_matches_pytorch_path():
         if t % 37 == 0 or t == 199:
             assert torch.allclose(a, b, rtol=0.05, atol=0.05), t
     assert fast._kbufs is not None and slow._kbufs is None
+    # capture / replay evidence: one capture, every step a replay; the eager engine replays nothing
+    assert fast.graph_counters.as_dict() == {"capture_calls": 1, "replay_calls": 200, "eager_steps": 0, "invalidations": 0,
+                                             "kernels_per_replay": 7 * 3 + 2, "replay_calls_by_batch": {"3": 200}}
+    assert slow.graph_counters.replay_calls == 0 and slow.graph_counters.eager_steps == 200
+    from warpstate_ai_b200.serve.graph_stats import collect_graph_diagnostics
+    with collect_graph_diagnostics(fast) as diagnostics:
+        fast.step(ids[:, 0])
+        fast.step(ids[:2, 0])        # another batch size: the captured graph is dropped and a new one recorded
+    assert diagnostics.snapshot() == {"capture_calls": 1, "replay_calls": 2, "eager_steps": 0, "invalidations": 1,
+                                      "kernels_per_replay": 7 * 3 + 2, "replay_calls_by_batch": {"3": 1, "2": 1}}
     # the engine on tile-contiguous weight copies produces the same logits bit for bit
     packed = DecodeEngine(model, dtype=torch.bfloat16, pack_weights=True)
     plain = DecodeEngine(model, dtype=torch.bfloat16, use_cuda_graph=False)
     for t in range(5):
         assert torch.equal(packed.step(ids[:, t]), plain.step(ids[:, t])), t
+
+
+def test_graph_counters_on_cpu_count_eager_steps():
+    from warpstate_ai_b200.serve.graph_stats import collect_graph_diagnostics
+    torch.manual_seed(0)
+    cfg = WarpStateConfig(vocab_size=64, d_model=32, n_heads=2, n_cores=1, logical_depth=2, ffn_hidden=48, chunk_size=8,
+                          gradient_checkpointing=False)
+    engine = DecodeEngine(WarpStateLM(cfg).eval(), dtype=torch.float32)
+    with collect_graph_diagnostics(engine) as diagnostics:
+        for token in range(5):
+            engine.step(torch.tensor([token, token + 1]))
+    assert diagnostics.snapshot() == {"capture_calls": 0, "replay_calls": 0, "eager_steps": 5, "invalidations": 0,
+                                      "kernels_per_replay": 0, "replay_calls_by_batch": {}}
 
 
 def test_pack_weight_round_trip_and_tile_order():

@@ -139,7 +139,10 @@ def main() -> None:
         if world > 1:
             torch.cuda.synchronize()
             dist.barrier()            # the replicas run at the same time, as they would in service
-        result = generate_batch(engine, prompts, args.new_tokens)
+        from ..serve.graph_stats import collect_graph_diagnostics
+        with collect_graph_diagnostics(engine) as diagnostics:
+            result = generate_batch(engine, prompts, args.new_tokens)
+        graph_report = diagnostics.snapshot()
     mine = {"tokens_per_second": result["tokens_per_second"], "p50_latency_seconds": result["p50_latency_seconds"],
             "prefill_tokens_per_second": args.batch * args.prompt / result["prefill_seconds"],
             "prefill_seconds": result["prefill_seconds"],
@@ -161,7 +164,8 @@ def main() -> None:
             "p50_token_latency_ms": total["p50_latency_seconds"] * 1e3,
             "prefill_tokens_per_second": total["prefill_tokens_per_second"],
             "prefill_seconds": total["prefill_seconds"], "cuda_graph": not args.no_graph,
-            "own_kernel_launches": launches, "model": args.model, "dtype": "bf16", "impl": args.impl,
+            "own_kernel_launches": launches, "cuda_graph_diagnostics": graph_report if args.impl == "ours" else None,
+            "model": args.model, "dtype": "bf16", "impl": args.impl,
             "peak_mem_gib": total["peak_mem_gib"]}
     print(json.dumps(line), flush=True)
     if world > 1:

@@ -79,6 +79,8 @@ class DecodeEngine:
         self.batch = 0
         self.pos = 0            # host copy of the in-chunk position
         self._graph = None
+        from .graph_stats import GraphCounters
+        self.graph_counters = GraphCounters()
 
     # ------------------------------------------------------------------ state
     def new_state(self, batch: int) -> None:
@@ -103,6 +105,8 @@ class DecodeEngine:
         self.pos_dev = torch.zeros((), dtype=torch.long, device=self.device)
         self.token_buf = torch.zeros(batch, dtype=torch.long, device=self.device)
         self.logits_buf = None
+        if self._graph is not None:
+            self.graph_counters.invalidations += 1
         self._graph = None
         self._kbufs = self._kernel_buffers(batch) if self._kernels_usable(batch) else None
 
@@ -233,9 +237,12 @@ class DecodeEngine:
             if self._graph is None:
                 self._capture()
             self._graph.replay()
+            self.graph_counters.replay_calls += 1
+            self.graph_counters.replay_calls_by_batch[self.batch] += 1
             logits = self.logits_buf
         else:
             logits = self._step_fn(token, self.pos_dev)
+            self.graph_counters.eager_steps += 1
         self.pos += 1
         if self.pos == self.chunk:
             self._end_of_chunk()
@@ -252,9 +259,13 @@ class DecodeEngine:
             for _ in range(2):
                 self._step_fn(self.token_buf, self.pos_dev)
         torch.cuda.current_stream(self.device).wait_stream(stream)
+        from ..ops import _ext
         self._graph = torch.cuda.CUDAGraph()
+        launched = _ext.launch_count()
         with torch.cuda.graph(self._graph):
             self.logits_buf = self._step_fn(self.token_buf, self.pos_dev)
+        self.graph_counters.capture_calls += 1
+        self.graph_counters.kernels_per_replay = _ext.launch_count() - launched
 
     # ------------------------------------------------------------------ prefill
     @torch.no_grad()

@@ -19,68 +19,83 @@ import json
 import math
 import sys
 import time
+from dataclasses import dataclass
 from pathlib import Path
-from types import SimpleNamespace
 
 import torch
 
 from ..data import sft as D
 from ..utils.io import digest, utc_timestamp
 
+REPORT_FORMAT = "warpstate-sft-snapshot-evaluation-v1"
+SUMMARY_KEYS = ("evaluated_samples", "assistant_target_tokens", "val_loss", "val_perplexity", "evaluation_seconds")
+
+
+@dataclass
+class _Evaluator:
+    """The two attributes `train.sft.evaluate` reads from a trainer."""
+    model: torch.nn.Module
+    device: torch.device
+
+
+def _write_once(path: Path, report: dict) -> None:
+    path.parent.mkdir(parents=True, exist_ok=True)
+    with path.open("x") as out:
+        out.write(json.dumps(report, indent=2, allow_nan=False, default=str) + "\n")
+
 
 def run(snapshot: Path, data_dir: Path, output: Path, device: torch.device, micro_batch: int = 4) -> dict:
-    from ..serve.chat import load_model
+    from ..serve.snapshots import SnapshotStore
     from .sft import evaluate
-    snapshot, data_dir, output = snapshot.resolve(), data_dir.resolve(), output.resolve()
-    if output.exists() or output.is_relative_to(snapshot.parent) or output.is_relative_to(data_dir):
-        raise ValueError("Select a new report outside the snapshot and dataset directories")
-    started = time.perf_counter()
-    tokenizer = snapshot.with_name("tokenizer.model")
-    model, sp, metadata = load_model(snapshot, tokenizer, device=str(device))
-    manifest = json.loads((data_dir / "manifest.json").read_text())
-    _, records, manifest, data_hash = D.load_data(data_dir, sp, metadata["tokenizer_sha256"], manifest["max_length"])
-    print(f"Validated {len(records):,} SFT holdout conversations; evaluating on {device}", flush=True)
-    settings = dict(sequence_length=manifest["max_length"], micro_batch=micro_batch, eval_batches=32)
-    pad_id = sp.pad_id() if sp.pad_id() >= 0 else sp.eos_id()
-    if device.type == "cuda":
+    snapshot, data_dir, output = (Path(p).resolve() for p in (snapshot, data_dir, output))
+    if output.exists() or any(output.is_relative_to(place) for place in (snapshot.parent, data_dir)):
+        raise ValueError(f"{output}: write the new report to a fresh file outside the snapshot and data directories")
+    clock = time.perf_counter
+    began = clock()
+    store = SnapshotStore(snapshot.parent.parent, snapshot.with_name("tokenizer.model"))
+    model, tokenizer, metadata = store.load(snapshot, str(device))
+    max_length = json.loads((data_dir / "manifest.json").read_text())["max_length"]
+    _, holdout, manifest, data_hash = D.load_data(data_dir, tokenizer, metadata["tokenizer_sha256"], max_length)
+    print(f"Validated {len(holdout):,} SFT holdout conversations; evaluating on {device}", flush=True)
+    on_gpu = device.type == "cuda"
+    if on_gpu:
         torch.cuda.reset_peak_memory_stats(device)
-    evaluation_started = time.perf_counter()
-    loss, targets = evaluate(SimpleNamespace(model=model, device=device), records, settings, pad_id, full=True)
-    if device.type == "cuda":
+    settings = {"sequence_length": max_length, "micro_batch": micro_batch, "eval_batches": 32}
+    pad = tokenizer.pad_id() if tokenizer.pad_id() >= 0 else tokenizer.eos_id()
+    measured_from = clock()
+    loss, tokens = evaluate(_Evaluator(model, device), holdout, settings, pad, full=True)
+    if on_gpu:
         torch.cuda.synchronize(device)
-    report = dict(
-        format="warpstate-sft-snapshot-evaluation-v1", timestamp_utc=utc_timestamp(), snapshot=str(snapshot),
-        snapshot_sha256=digest(snapshot), snapshot_metadata=metadata, data_sha256=data_hash,
-        holdout_sha256=manifest["outputs"]["sft_val.jsonl"]["sha256"], renderer_sha256=D.renderer_sha256(),
-        full_holdout=True, evaluated_samples=len(records), assistant_target_tokens=targets, val_loss=loss,
-        val_perplexity=math.exp(loss), objective="assistant-token-mean", settings=settings,
-        execution=dict(device=str(device),
-                       device_name=torch.cuda.get_device_name(device) if device.type == "cuda" else "cpu",
-                       torch_version=torch.__version__, compute_dtype="bfloat16" if device.type == "cuda" else "float32",
-                       parameter_dtype="float32"),
-        evaluation_seconds=time.perf_counter() - evaluation_started, total_seconds=time.perf_counter() - started,
-        peak_allocated_bytes=torch.cuda.max_memory_allocated(device) if device.type == "cuda" else None)
-    output.parent.mkdir(parents=True, exist_ok=True)
-    with output.open("x") as stream:
-        json.dump(report, stream, indent=2, allow_nan=False, default=str)
-        stream.write("\n")
+    finished = clock()
+    report = {
+        "format": REPORT_FORMAT, "timestamp_utc": utc_timestamp(), "snapshot": str(snapshot),
+        "snapshot_sha256": digest(snapshot), "snapshot_metadata": metadata, "data_sha256": data_hash,
+        "holdout_sha256": manifest["outputs"]["sft_val.jsonl"]["sha256"], "renderer_sha256": D.renderer_sha256(),
+        "full_holdout": True, "evaluated_samples": len(holdout), "assistant_target_tokens": tokens, "val_loss": loss,
+        "val_perplexity": math.exp(loss), "objective": "assistant-token-mean", "settings": settings,
+        "execution": {"device": str(device), "device_name": torch.cuda.get_device_name(device) if on_gpu else "cpu",
+                      "torch_version": torch.__version__, "compute_dtype": "bfloat16" if on_gpu else "float32",
+                      "parameter_dtype": "float32"},
+        "evaluation_seconds": finished - measured_from, "total_seconds": finished - began,
+        "peak_allocated_bytes": torch.cuda.max_memory_allocated(device) if on_gpu else None}
+    _write_once(output, report)
     return report
 
 
 def main(argv=None) -> int:
-    p = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    p.add_argument("--snapshot", type=Path, required=True)
-    p.add_argument("--data-dir", type=Path, required=True)
-    p.add_argument("--device", default="cuda:0" if torch.cuda.is_available() else "cpu")
-    p.add_argument("--micro-batch", type=int, default=4)
-    p.add_argument("--output", type=Path, required=True)
-    a = p.parse_args(argv)
-    device = torch.device(a.device)
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--snapshot", type=Path, required=True, help="model.pt of a sealed export")
+    parser.add_argument("--data-dir", type=Path, required=True, help="prepared post-training data")
+    parser.add_argument("--output", type=Path, required=True, help="report file (must not exist)")
+    parser.add_argument("--device", default="cuda:0" if torch.cuda.is_available() else "cpu")
+    parser.add_argument("--micro-batch", type=int, default=4)
+    args = parser.parse_args(argv)
+    device = torch.device(args.device)
     if device.type == "cuda":
         torch.cuda.set_device(device)
-    report = run(a.snapshot, a.data_dir, a.output, device, a.micro_batch)
-    print(json.dumps({k: report[k] for k in ("evaluated_samples", "assistant_target_tokens", "val_loss",
-                                             "val_perplexity", "evaluation_seconds")}) + f"\nReport: {a.output}", flush=True)
+    report = run(args.snapshot, args.data_dir, args.output, device, args.micro_batch)
+    print(json.dumps({key: report[key] for key in SUMMARY_KEYS}), flush=True)
+    print(f"Report: {args.output}", flush=True)
     return 0
 
 
