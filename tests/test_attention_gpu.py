@@ -47,7 +47,9 @@ def test_forward_matches_composite(batch, seq, h):
     assert rel_l2(y, ref.reshape(batch * seq, d)) < 0.01
 
 
-@pytest.mark.parametrize("batch,seq,h", [(1, 128, 1), (2, 512, 4), (2, 2048, 8)])
+# 17 chunks: two groups of the reverse scan, the second with one chunk; 70 chunks: beyond the 64 of the
+# earlier register-array kernel, five groups, the last one partial
+@pytest.mark.parametrize("batch,seq,h", [(1, 128, 1), (2, 512, 4), (2, 2048, 8), (2, 128 * 17, 2), (1, 128 * 70, 1)])
 def test_backward_matches_autograd_of_composite(batch, seq, h):
     from warpstate_ai_b200.ops import attention, reference as R
     from warpstate_ai_b200.ops.gemm import check_device_errors

@@ -12,7 +12,7 @@ from .gemm import error_flag
 
 _rope_cache: dict = {}
 BACKWARD_READY = True
-MAX_CHUNKS = 64
+MAX_CHUNKS = 256
 
 
 def rope_table(device: torch.device, pair_major: bool = False) -> torch.Tensor:

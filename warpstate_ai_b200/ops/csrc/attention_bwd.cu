@@ -16,6 +16,7 @@
 // one token row in every element-wise stage.
 #include "ws_ptx.cuh"
 #include "ws_api.h"
+#include "ws_launch.h"
 #include "attention_common.cuh"
 
 namespace ws {
@@ -58,6 +59,8 @@ dstate_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_constan
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (tid == 0) {
     mbar_expect_tx(&bars[0], 3 * TILE_BYTES);
@@ -133,7 +136,13 @@ dstate_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_constan
 }
 
 // =============================================================================== reverse scan
-constexpr int SCAN_MAX_CHUNKS = 64;
+// The reverse scan needs the state every chunk saw.  Those are recomputed from the writes in groups of
+// SCAN_GROUP chunks: a first pass keeps the state at every group boundary, then the groups are walked
+// from the last to the first, each re-running its forward recurrence into registers before its reverse
+// part.  One group (sequences up to 2048 tokens) skips the first pass.
+constexpr int SCAN_GROUP = 16;
+constexpr int SCAN_MAX_GROUPS = 16;
+constexpr int SCAN_MAX_CHUNKS = SCAN_GROUP * SCAN_MAX_GROUPS;  // 32768 tokens per sequence
 
 // dstate [B,N,H,4096] FP32 (gradient of the mixed state read by chunk n), writes [B,N,H,4096] FP32
 // -> dwrites [B,N,H,4096] BF16 and partial sums [B*H*16][3] of d(fast decay), d(slow decay), d(mix).
@@ -142,6 +151,8 @@ memory_scan_bwd_kernel(const float* __restrict__ dstate, const float* __restrict
                        const float* __restrict__ fast_logit, const float* __restrict__ slow_logit,
                        const float* __restrict__ mix_logit, __nv_bfloat16* __restrict__ dwrites,
                        float* __restrict__ partials, int B, int N, int H) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float red[3][8];
   const size_t idx = blockIdx.x * static_cast<size_t>(256) + threadIdx.x;  // over B*H*4096 (exact multiple)
   const int e = idx % 4096;
@@ -150,27 +161,57 @@ memory_scan_bwd_kernel(const float* __restrict__ dstate, const float* __restrict
   const float df = 1.f / (1.f + expf(-fast_logit[h]));
   const float ds = 1.f / (1.f + expf(-slow_logit[h]));
   const float mix = 1.f / (1.f + expf(-mix_logit[h]));
-  float F[SCAN_MAX_CHUNKS], S[SCAN_MAX_CHUNKS];
-  float f = 0.f, s = 0.f;
-  for (int n = 0; n < N; ++n) {  // forward: state seen by chunk n
-    F[n] = f;
-    S[n] = s;
-    const float w = writes[((static_cast<size_t>(b) * N + n) * H + h) * 4096 + e];
-    f = df * f + (1.f - df) * w;
-    s = ds * s + (1.f - ds) * w;
+  const size_t chunk_stride = static_cast<size_t>(H) * 4096;
+  const size_t base = (static_cast<size_t>(b) * N * H + h) * 4096 + e;  // chunk 0 of this element
+  const int groups = (N + SCAN_GROUP - 1) / SCAN_GROUP;
+  float start_f[SCAN_MAX_GROUPS], start_s[SCAN_MAX_GROUPS];
+  {
+    float f = 0.f, s = 0.f;
+#pragma unroll 1
+    for (int g = 0; g < groups; ++g) {
+      start_f[g] = f;
+      start_s[g] = s;
+      if (g + 1 < groups) {
+#pragma unroll
+        for (int i = 0; i < SCAN_GROUP; ++i) {
+          const float w = writes[base + (g * SCAN_GROUP + i) * chunk_stride];
+          f = df * f + (1.f - df) * w;
+          s = ds * s + (1.f - ds) * w;
+        }
+      }
+    }
   }
+  // a, bb: gradients of the fast and slow state AFTER the chunk being visited (F_{n+1}, S_{n+1})
   float a = 0.f, bb = 0.f, g_df = 0.f, g_ds = 0.f, g_mix = 0.f;
-  for (int n = N - 1; n >= 0; --n) {
-    const size_t off = ((static_cast<size_t>(b) * N + n) * H + h) * 4096 + e;
-    dwrites[off] = __float2bfloat16_rn((1.f - df) * a + (1.f - ds) * bb);  // a, bb = grads of F_{n+1}, S_{n+1}
-    const float g = dstate[off];
-    g_mix += g * (F[n] - S[n]);
-    a = mix * g + df * a;         // gradient of F_n
-    bb = (1.f - mix) * g + ds * bb;
-    if (n > 0) {
-      const float w_prev = writes[off - static_cast<size_t>(H) * 4096];
-      g_df += a * (F[n - 1] - w_prev);
-      g_ds += bb * (S[n - 1] - w_prev);
+#pragma unroll 1
+  for (int g = groups - 1; g >= 0; --g) {
+    const int n0 = g * SCAN_GROUP;
+    const int count = min(SCAN_GROUP, N - n0);
+    float F[SCAN_GROUP], S[SCAN_GROUP], W[SCAN_GROUP];
+    float f = start_f[g], s = start_s[g];
+#pragma unroll
+    for (int i = 0; i < SCAN_GROUP; ++i) {  // forward: state seen by chunk n0 + i
+      if (i < count) {
+        F[i] = f;
+        S[i] = s;
+        const float w = writes[base + (n0 + i) * chunk_stride];
+        W[i] = w;
+        f = df * f + (1.f - df) * w;
+        s = ds * s + (1.f - ds) * w;
+      }
+    }
+#pragma unroll
+    for (int i = SCAN_GROUP - 1; i >= 0; --i) {
+      if (i < count) {
+        const size_t off = base + (n0 + i) * chunk_stride;
+        dwrites[off] = __float2bfloat16_rn((1.f - df) * a + (1.f - ds) * bb);
+        g_df += a * (F[i] - W[i]);    // F_{n+1} = df F_n + (1 - df) w_n
+        g_ds += bb * (S[i] - W[i]);
+        const float gr = dstate[off];
+        g_mix += gr * (F[i] - S[i]);
+        a = mix * gr + df * a;        // gradient of F_n
+        bb = (1.f - mix) * gr + ds * bb;
+      }
     }
   }
   // block reduction (fixed order)
@@ -250,6 +291,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_const
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
+  pdl_launch_dependents();
+  pdl_wait();
   const uint32_t t_lo = tmem;          // S / O / dP / dKr+dtK
   const uint32_t t_mid = tmem + 128;   // Mem / dV / dtU
   const uint32_t t_dq = tmem + 192;    // dQr
@@ -599,7 +642,7 @@ extern "C" int ws_attn_dstate(const void* qkvgu, const void* dy, const float* ro
     configured = true;
   }
   const int tiles = B * (T / CHUNK) * H;
-  dstate_kernel<<<tiles, 128, DS_SMEM, stream>>>(tm, td, to, reinterpret_cast<const float2*>(rope), T, H, d,
+  launch_dependent(dstate_kernel, dim3(tiles), dim3(128), DS_SMEM, stream, tm, td, to, reinterpret_cast<const float2*>(rope), T, H, d,
                                                  error_flag);
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
@@ -610,7 +653,7 @@ extern "C" int ws_memory_scan_bwd(const float* dstate, const float* writes, cons
                                   int B, int N, int H, cudaStream_t stream) {
   if (N > SCAN_MAX_CHUNKS) return -1;
   const size_t total = (size_t)B * H * 4096;
-  memory_scan_bwd_kernel<<<(unsigned)(total / 256), 256, 0, stream>>>(dstate, writes, fast_logit, slow_logit,
+  launch_dependent(memory_scan_bwd_kernel, dim3((unsigned)(total / 256)), dim3(256), 0, stream, dstate, writes, fast_logit, slow_logit,
                                                                       mix_logit, (__nv_bfloat16*)dwrites, partials,
                                                                       B, N, H);
   ws_count_launch();
@@ -639,7 +682,7 @@ extern "C" int ws_attn_bwd(const void* qkvgu, const void* states, const void* dy
       return -20;
     configured = true;
   }
-  attn_bwd_kernel<<<tiles, AB_THREADS, AB_SMEM, stream>>>(tm, ts, td, tw, to, reinterpret_cast<const float2*>(rope),
+  launch_dependent(attn_bwd_kernel, dim3(tiles), dim3(AB_THREADS), AB_SMEM, stream, tm, ts, td, tw, to, reinterpret_cast<const float2*>(rope),
                                                           T, H, d, error_flag);
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : -21;

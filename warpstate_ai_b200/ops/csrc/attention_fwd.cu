@@ -15,6 +15,7 @@
 // One thread owns one token row (= one TMEM lane): no cross-thread reductions anywhere.
 #include "ws_ptx.cuh"
 #include "ws_api.h"
+#include "ws_launch.h"
 #include "attention_common.cuh"
 
 namespace ws {
@@ -55,6 +56,8 @@ chunk_writes_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_c
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (tid == 0) {
     mbar_expect_tx(&bars[0], 2 * TILE_BYTES);
@@ -128,6 +131,8 @@ memory_scan_kernel(const float* __restrict__ writes, const float* __restrict__ f
                    __nv_bfloat16* __restrict__ states, float* __restrict__ final_fast,
                    float* __restrict__ final_slow, const float* __restrict__ init_fast,
                    const float* __restrict__ init_slow, int B, int N, int H) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t idx = blockIdx.x * static_cast<size_t>(256) + threadIdx.x;  // over B*H*4096
   const size_t total = static_cast<size_t>(B) * H * 4096;
   if (idx >= total) return;
@@ -199,6 +204,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_const
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
+  pdl_launch_dependents();
+  pdl_wait();
   const uint32_t t_s = tmem, t_o = tmem, t_m = tmem + 64;  // O and Mem reuse S's columns after the softmax
   const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
 
@@ -348,7 +355,7 @@ extern "C" int ws_chunk_writes(const void* qkvgu, const float* rope, float* writ
   CUtensorMap to;
   rc = make_map_f32(&to, writes, HD, (uint64_t)tiles * HD, HD, 32, 32);
   if (rc) return rc;
-  chunk_writes_kernel<<<tiles, 128, WR_SMEM, stream>>>(tm, to, reinterpret_cast<const float2*>(rope), T, H, d,
+  launch_dependent(chunk_writes_kernel, dim3(tiles), dim3(128), WR_SMEM, stream, tm, to, reinterpret_cast<const float2*>(rope), T, H, d,
                                                        error_flag);
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
@@ -359,8 +366,7 @@ extern "C" int ws_memory_scan(const float* writes, const float* fast_logit, cons
                               const float* init_fast, const float* init_slow, int B, int N, int H,
                               cudaStream_t stream) {
   const size_t total = (size_t)B * H * 4096;
-  memory_scan_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
-      writes, fast_logit, slow_logit, mix_logit, (__nv_bfloat16*)states, final_fast, final_slow, init_fast,
+  launch_dependent(memory_scan_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, writes, fast_logit, slow_logit, mix_logit, (__nv_bfloat16*)states, final_fast, final_slow, init_fast,
       init_slow, B, N, H);
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
@@ -383,7 +389,7 @@ extern "C" int ws_attn_fwd(const void* qkvgu, const void* states, const float* r
       return -20;
     configured = true;
   }
-  attn_fwd_kernel<<<tiles, 128, AF_SMEM, stream>>>(tm, ts, ty, reinterpret_cast<const float2*>(rope), T, H, d,
+  launch_dependent(attn_fwd_kernel, dim3(tiles), dim3(128), AF_SMEM, stream, tm, ts, ty, reinterpret_cast<const float2*>(rope), T, H, d,
                                                    error_flag);
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : -21;

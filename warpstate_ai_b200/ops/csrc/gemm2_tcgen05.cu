@@ -24,6 +24,7 @@
 #include "ws_api.h"
 #include "ws_tma_host.h"
 #include "gemm_epilogue.cuh"
+#include "ws_launch.h"
 
 #include <cuda_bf16.h>
 #include <cstdlib>
@@ -204,6 +205,9 @@ gemm2_kernel(const __grid_constant__ PairGroup g, const __grid_constant__ Gather
   cluster_sync_all();  // peer barriers are initialised before anyone signals them
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  // set-up is done: let the next kernel of the stream be scheduled, then wait for the previous one's results
+  pdl_launch_dependents();
+  pdl_wait();
 
   constexpr bool kSwiglu = (EPI == WS_EPI_SWIGLU);
   const int n_tile = kSwiglu ? 128 : BN;
@@ -650,7 +654,7 @@ static int launch_pair(const PairGroup& g, int pairs, cudaStream_t stream) {
       return -20;
     configured = true;
   }
-  kern<<<2 * pairs, pair_threads<EPI>(), pair_smem<EPI>(), stream>>>(g, GatherJob{});
+  launch_dependent(kern, dim3(2 * pairs), dim3(pair_threads<EPI>()), pair_smem<EPI>(), stream, g, GatherJob{});
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
@@ -664,7 +668,7 @@ static int launch_pair_gather(const PairGroup& g, const GatherJob& job, int pair
       return -20;
     configured = true;
   }
-  kern<<<2 * pairs, pair_threads<EPI>() + GATHER_THREADS, pair_smem<EPI>(), stream>>>(g, job);
+  launch_dependent(kern, dim3(2 * pairs), dim3(pair_threads<EPI>() + GATHER_THREADS), pair_smem<EPI>(), stream, g, job);
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }

@@ -24,6 +24,7 @@
 #include "ws_api.h"
 #include "ws_tma_host.h"
 #include "gemm_epilogue.cuh"
+#include "ws_launch.h"
 
 #include <atomic>
 #include <mutex>
@@ -100,6 +101,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_launch_dependents();
+  pdl_wait();
 
   constexpr bool kSwiglu = (EPI == WS_EPI_SWIGLU);
   const int n_tile = kSwiglu ? 128 : BN;  // logical output columns per tile
@@ -233,7 +236,7 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
     if (e != cudaSuccess) return -20;
     configured = true;
   }
-  kern<<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ta, tb, p);
+  launch_dependent(kern, dim3(grid), dim3(GEMM_THREADS), SMEM_BYTES, stream, ta, tb, p);
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }

@@ -8,6 +8,7 @@
 // the per-sequence log-probability head of DPO (dpo.py:150-161).
 #include "ws_ptx.cuh"
 #include "ws_api.h"
+#include "ws_launch.h"
 
 namespace ws {
 
@@ -19,6 +20,8 @@ __global__ void __launch_bounds__(256)
 ce_combine_kernel(const float2* __restrict__ parts, int ld, int nparts, const float* __restrict__ label_logit,
                   const long long* __restrict__ labels, long long ignore_index, int rows,
                   float* __restrict__ lse_out, float* __restrict__ logp_out) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * 8 + warp;
   if (row >= rows) return;
@@ -50,7 +53,7 @@ extern "C" int ws_ce_combine(const void* parts, int ld, int nparts, const float*
                              const long long* labels, long long ignore_index, int rows, float* lse,
                              float* logp, cudaStream_t stream) {
   if (rows <= 0 || nparts <= 0) return -1;
-  ce_combine_kernel<<<(rows + 7) / 8, 256, 0, stream>>>(reinterpret_cast<const float2*>(parts), ld, nparts,
+  launch_dependent(ce_combine_kernel, dim3((rows + 7) / 8), dim3(256), 0, stream, reinterpret_cast<const float2*>(parts), ld, nparts,
                                                          label_logit, labels, ignore_index, rows, lse, logp);
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : -2;

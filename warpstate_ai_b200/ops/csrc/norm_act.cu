@@ -8,6 +8,7 @@
 // partial rows in a fixed order, so the result does not depend on scheduling.
 #include "ws_ptx.cuh"
 #include "ws_api.h"
+#include "ws_launch.h"
 
 namespace ws {
 
@@ -46,6 +47,8 @@ rmsnorm_fwd_kernel(const T* __restrict__ x, const float* __restrict__ col_scale,
                    const float* __restrict__ col_bias, const float* __restrict__ w, float eps, int rows,
                    int d, T* __restrict__ xmod_out, __nv_bfloat16* __restrict__ z,
                    float* __restrict__ rstd_out) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int row = blockIdx.x * ROW_WARPS + warp; row < rows; row += gridDim.x * ROW_WARPS) {
     const T* xr = x + static_cast<size_t>(row) * d;
@@ -113,6 +116,8 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dz, const T* __restrict__ x
                    const T* __restrict__ dres, const float* __restrict__ out_scale, int rows, int d,
                    T* __restrict__ dx_out, __nv_bfloat16* __restrict__ dx_bf16,
                    float* __restrict__ dw_partial) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float red[2][RB_ROWS][ROW_WARPS];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int c = threadIdx.x * 8;
@@ -195,6 +200,8 @@ template <typename T>
 __global__ void __launch_bounds__(ROW_THREADS)
 colsum2_kernel(const T* __restrict__ a, const T* __restrict__ b, int rows, int d,
                float* __restrict__ partial_a, float* __restrict__ partial_ab) {
+  pdl_launch_dependents();
+  pdl_wait();
   // thread t owns columns t*4 .. t*4+3 of a 1024-wide panel; rows strided over blocks
   for (int c0 = 0; c0 < d; c0 += ROW_THREADS * 4) {
     const int c = c0 + threadIdx.x * 4;
@@ -220,6 +227,8 @@ constexpr int FIN_COLS = 32;
 __global__ void __launch_bounds__(ROW_THREADS)
 colsum_finalize_kernel(const float* __restrict__ partial, int parts, int d,
                        const float* __restrict__ inv_scale, float beta, float* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float red[ROW_WARPS][FIN_COLS];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int c = blockIdx.x * FIN_COLS + lane;
@@ -251,6 +260,8 @@ colsum_finalize_kernel(const float* __restrict__ partial, int parts, int d,
 // --------------------------------------------------------------------------- casts
 __global__ void cast_f32_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out,
                                      size_t n4) {
+  pdl_launch_dependents();
+  pdl_wait();
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n4;
        i += static_cast<size_t>(gridDim.x) * blockDim.x) {
     st4(out + i * 4, ld4(in + i * 4));
@@ -318,12 +329,10 @@ extern "C" int ws_rmsnorm_fwd(const void* x, int x_bf16, const float* col_scale,
   if (d % 128 != 0 || rows <= 0) return -1;
   const int grid = row_grid(rows);
   if (x_bf16)
-    rmsnorm_fwd_kernel<__nv_bfloat16><<<grid, ROW_THREADS, 0, stream>>>(
-        (const __nv_bfloat16*)x, col_scale, col_bias, w, eps, rows, d, (__nv_bfloat16*)xmod_out,
+    launch_dependent(rmsnorm_fwd_kernel<__nv_bfloat16>, dim3(grid), dim3(ROW_THREADS), 0, stream, (const __nv_bfloat16*)x, col_scale, col_bias, w, eps, rows, d, (__nv_bfloat16*)xmod_out,
         (__nv_bfloat16*)z, rstd);
   else
-    rmsnorm_fwd_kernel<float><<<grid, ROW_THREADS, 0, stream>>>(
-        (const float*)x, col_scale, col_bias, w, eps, rows, d, (float*)xmod_out, (__nv_bfloat16*)z, rstd);
+    launch_dependent(rmsnorm_fwd_kernel<float>, dim3(grid), dim3(ROW_THREADS), 0, stream, (const float*)x, col_scale, col_bias, w, eps, rows, d, (float*)xmod_out, (__nv_bfloat16*)z, rstd);
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
@@ -341,12 +350,10 @@ extern "C" int ws_rmsnorm_bwd(const void* dz, const void* x, int x_bf16, const f
   if (d % 128 != 0 || d > ROW_THREADS * 8 || rows <= 0) return -1;
   const int grid = ws_rmsnorm_bwd_parts(rows);
   if (x_bf16)
-    rmsnorm_bwd_kernel<__nv_bfloat16><<<grid, ROW_THREADS, 0, stream>>>(
-        (const __nv_bfloat16*)dz, (const __nv_bfloat16*)x, rstd, w, (const __nv_bfloat16*)dres, out_scale,
+    launch_dependent(rmsnorm_bwd_kernel<__nv_bfloat16>, dim3(grid), dim3(ROW_THREADS), 0, stream, (const __nv_bfloat16*)dz, (const __nv_bfloat16*)x, rstd, w, (const __nv_bfloat16*)dres, out_scale,
         rows, d, (__nv_bfloat16*)dx_out, (__nv_bfloat16*)dx_bf16, dw_partial);
   else
-    rmsnorm_bwd_kernel<float><<<grid, ROW_THREADS, 0, stream>>>(
-        (const __nv_bfloat16*)dz, (const float*)x, rstd, w, (const float*)dres, out_scale, rows, d,
+    launch_dependent(rmsnorm_bwd_kernel<float>, dim3(grid), dim3(ROW_THREADS), 0, stream, (const __nv_bfloat16*)dz, (const float*)x, rstd, w, (const float*)dres, out_scale, rows, d,
         (float*)dx_out, (__nv_bfloat16*)dx_bf16, dw_partial);
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
@@ -359,10 +366,9 @@ extern "C" int ws_colsum2(const void* a, const void* b, int is_bf16, int rows, i
   if (d % 4 != 0 || rows <= 0) return -1;
   const int grid = ws_colsum_parts(rows);
   if (is_bf16)
-    colsum2_kernel<__nv_bfloat16><<<grid, ROW_THREADS, 0, stream>>>(
-        (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, rows, d, partial_a, partial_ab);
+    launch_dependent(colsum2_kernel<__nv_bfloat16>, dim3(grid), dim3(ROW_THREADS), 0, stream, (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, rows, d, partial_a, partial_ab);
   else
-    colsum2_kernel<float><<<grid, ROW_THREADS, 0, stream>>>((const float*)a, (const float*)b, rows, d,
+    launch_dependent(colsum2_kernel<float>, dim3(grid), dim3(ROW_THREADS), 0, stream, (const float*)a, (const float*)b, rows, d,
                                                             partial_a, partial_ab);
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
@@ -370,7 +376,7 @@ extern "C" int ws_colsum2(const void* a, const void* b, int is_bf16, int rows, i
 
 extern "C" int ws_colsum_finalize(const float* partial, int parts, int d, const float* inv_scale, float beta,
                                   float* out, cudaStream_t stream) {
-  colsum_finalize_kernel<<<(d + FIN_COLS - 1) / FIN_COLS, ROW_THREADS, 0, stream>>>(partial, parts, d, inv_scale, beta, out);
+  launch_dependent(colsum_finalize_kernel, dim3((d + FIN_COLS - 1) / FIN_COLS), dim3(ROW_THREADS), 0, stream, partial, parts, d, inv_scale, beta, out);
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
@@ -381,7 +387,7 @@ extern "C" int ws_cast_f32_bf16(const float* in, void* out, size_t n, cudaStream
   const size_t n4 = n / 4;
   size_t blocks = (n4 + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  cast_f32_bf16_kernel<<<(int)blocks, 256, 0, stream>>>(in, (__nv_bfloat16*)out, n4);
+  launch_dependent(cast_f32_bf16_kernel, dim3((int)blocks), dim3(256), 0, stream, in, (__nv_bfloat16*)out, n4);
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
@@ -480,15 +486,13 @@ extern "C" int ws_rmsnorm_bwd_static(const void* dz, const void* x, int x_bf16, 
   // Every partial row that the reduction reads below is written by the kernel first, so the
   // previous call's contents never leak into this result.
   if (x_bf16)
-    rmsnorm_bwd_kernel<__nv_bfloat16><<<parts, ROW_THREADS, 0, stream>>>(
-        (const __nv_bfloat16*)dz, (const __nv_bfloat16*)x, rstd, w, (const __nv_bfloat16*)dres, out_scale,
+    launch_dependent(rmsnorm_bwd_kernel<__nv_bfloat16>, dim3(parts), dim3(ROW_THREADS), 0, stream, (const __nv_bfloat16*)dz, (const __nv_bfloat16*)x, rstd, w, (const __nv_bfloat16*)dres, out_scale,
         rows, d, (__nv_bfloat16*)dx_out, (__nv_bfloat16*)dx_bf16, scratch);
   else
-    rmsnorm_bwd_kernel<float><<<parts, ROW_THREADS, 0, stream>>>(
-        (const __nv_bfloat16*)dz, (const float*)x, rstd, w, (const float*)dres, out_scale, rows, d,
+    launch_dependent(rmsnorm_bwd_kernel<float>, dim3(parts), dim3(ROW_THREADS), 0, stream, (const __nv_bfloat16*)dz, (const float*)x, rstd, w, (const float*)dres, out_scale, rows, d,
         (float*)dx_out, (__nv_bfloat16*)dx_bf16, scratch);
   ws_count_launch();
-  colsum_finalize_kernel<<<(d + FIN_COLS - 1) / FIN_COLS, ROW_THREADS, 0, stream>>>(scratch, parts, d, nullptr, 0.f, dw_out);
+  launch_dependent(colsum_finalize_kernel, dim3((d + FIN_COLS - 1) / FIN_COLS), dim3(ROW_THREADS), 0, stream, scratch, parts, d, nullptr, 0.f, dw_out);
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : WS_STATIC_ERR_LAUNCH;
 }
