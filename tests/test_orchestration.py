@@ -153,7 +153,10 @@ def test_handoff_state_machine_with_fakes(ws, monkeypatch):
     tok, boundary = train_base(ws)
     data = ws / "data"
     rows = [{"messages": [{"role": "user", "content": f"q{i}"}, {"role": "assistant", "content": f"a{i}"}]} for i in range(8)]
-    prepare_posttrain(data, tok, 64, sft_rows=rows, val_modulus=3)
+    preference = [{"prompt": [{"role": "user", "content": f"Say the number {i}."}],
+                   "chosen": [{"role": "assistant", "content": f"{i}"}],
+                   "rejected": [{"role": "assistant", "content": f"I will not say {i + 7} today."}]} for i in range(8)]
+    prepare_posttrain(data, tok, 64, sft_rows=rows, dpo_rows=preference, val_modulus=3)
     plan = {"format": "warpstate-posttrain-plan-v1", "stage": "sft", "after_completion": "pause_for_evaluation",
             "base": boundary, "training": {"sequence_length": 64, "micro_batch": 2, "grad_accum": 1, "lr": 1e-3,
                                            "eval_every": 1, "save_every": 1, "eval_batches": 1, "workers": 1,
@@ -171,9 +174,9 @@ def test_handoff_state_machine_with_fakes(ws, monkeypatch):
         calls.append(command)
         assert len(pass_fds) == 2
         # run the real trainer in-process equivalent: a subprocess on CPU, single rank
-        args = command[command.index(str(L.PACKAGE / "posttrain.py")) + 1:]
+        script = next(i for i, word in enumerate(command) if word in (str(L.PACKAGE / "posttrain.py"), str(L.PACKAGE / "dpo.py")))
         env = dict(environment, PYTHONPATH=str(ROOT), WARPSTATE_WORKSPACE=str(ws))
-        return subprocess.run([sys.executable, str(L.PACKAGE / "posttrain.py"), *args, "--device", "cpu"], env=env).returncode
+        return subprocess.run([sys.executable, *command[script:], "--device", "cpu"], env=env).returncode
 
     assert H.run_handoff(config, stage_name="sft", status_fn=lambda s, p: next(states), supervise_fn=fake_supervise) == 0
     state = json.loads((ws / "sft/control/handoff.json").read_text())
@@ -189,6 +192,30 @@ def test_handoff_state_machine_with_fakes(ws, monkeypatch):
     with pytest.raises(ValueError, match="re-arm"):
         H.run_handoff(config, stage_name="sft", status_fn=lambda s, p: {"statename": "EXITED", "exitstatus": 0},
                       supervise_fn=fake_supervise)
+    # ---- the second guardian: the completed SFT run is sealed, copied and handed to the DPO trainer
+    finished = torch.load(ws / "sft/run/latest.pt", weights_only=False)
+    dpo_plan = {"format": "warpstate-dpo-plan-v1", "stage": "dpo", "after_completion": "pause_for_evaluation",
+                "sft": {"step": finished["step"], "tokens_seen": finished["tokens_seen"], "tokenizer_sha256": digest(tok)},
+                "training": {"sequence_length": 64, "micro_batch": 2, "grad_accum": 1, "lr": 1e-3, "eval_every": 1,
+                             "save_every": 1, "eval_batches": 1, "workers": 1, "max_steps": 2, "beta": 0.5,
+                             "head_chunk_size": 16},
+                "handoff": {"base_work_dir": "base", "sft_work_dir": "sft", "supervisor_socket": "supervisor.sock",
+                            "archive_dir": "archives/sft-final", "work_dir": "dpo", "data_dir": "data",
+                            "tokenizer": "tokenizer.model", "base_program": "sft-handoff", "processes": 1,
+                            "poll_seconds": 0.01, "preflight": False}}
+    dpo_config = ws / "dpo-plan.json"
+    dpo_config.write_text(json.dumps(dpo_plan))
+    assert H.run_handoff(dpo_config, stage_name="dpo", status_fn=lambda s, p: {"statename": "EXITED", "exitstatus": 0},
+                         supervise_fn=fake_supervise) == 0
+    state = json.loads((ws / "dpo/control/handoff.json").read_text())
+    assert state["phase"] == "complete" and state["format"] == "warpstate-dpo-handoff-v1"
+    assert "--reference-cache-dir" in calls[-1] and str(ws / "dpo/reference-cache") in calls[-1]
+    sealed = torch.load(ws / "archives/sft-final/model.pt", weights_only=False)
+    assert sealed["stage"] == "sft" and all(torch.equal(sealed["model"][k], v) for k, v in finished["model"].items())
+    assert torch.load(ws / "dpo/run/latest.pt", weights_only=False)["format"] == "warpstate-dpo-v1"
+    # a parent that stopped one step short is refused by the rule table
+    with pytest.raises(ValueError, match="exact planned run"):
+        H.DpoStage().validate_parent(dict(finished, step=finished["step"] - 1), dpo_plan, digest(tok))
 
 
 def test_handoff_rejects_wrong_boundary(ws, monkeypatch):
@@ -245,3 +272,36 @@ def test_ops_entry_points_exist_and_parse_help():
     for name in ("loss_curve_forecast.py", "transfer_artifacts.py", "compare_communication_benchmarks.py"):
         result = subprocess.run([sys.executable, str(ROOT / "ops" / name), "--help"], capture_output=True, text=True)
         assert result.returncode == 0 and "usage" in result.stdout.lower(), (name, result.stderr[-300:])
+
+
+def test_process_status_speaks_xmlrpc_over_a_unix_socket(tmp_path):
+    """The guardian's supervisord client against a stand-in server on a unix socket: one HTTP/1.0 exchange per
+    question, the answer a struct; a non-200 answer is an error, not a status."""
+    import socketserver
+    import threading
+    import xmlrpc.client
+
+    class Handler(socketserver.StreamRequestHandler):
+        def handle(self):
+            head = b""
+            while not head.endswith(b"\r\n\r\n"):
+                head += self.rfile.read(1)
+            length = int([l.split(b":")[1] for l in head.split(b"\r\n") if l.lower().startswith(b"content-length")][0])
+            (program,), method = xmlrpc.client.loads(self.rfile.read(length))
+            assert head.startswith(b"POST /RPC2 HTTP/1.0") and method == "supervisor.getProcessInfo"
+            if program == "missing":
+                self.wfile.write(b"HTTP/1.0 500 Internal Server Error\r\n\r\n")
+                return
+            body = xmlrpc.client.dumps(({"name": program, "statename": "EXITED", "exitstatus": 0},), methodresponse=True).encode()
+            self.wfile.write(b"HTTP/1.0 200 OK\r\nContent-Type: text/xml\r\nContent-Length: %d\r\n\r\n" % len(body) + body)
+
+    path = tmp_path / "supervisor.sock"
+    with socketserver.UnixStreamServer(str(path), Handler) as server:
+        thread = threading.Thread(target=server.serve_forever, daemon=True)
+        thread.start()
+        info = H.process_status(path, "train")
+        assert info == {"name": "train", "statename": "EXITED", "exitstatus": 0} and H.clean_exit(info)
+        with pytest.raises(ConnectionError):
+            H.process_status(path, "missing")
+        server.shutdown()
+    assert not H.clean_exit({"statename": "EXITED", "exitstatus": 1}) and not H.clean_exit({"statename": "RUNNING"})

@@ -72,12 +72,17 @@ def worker(mode: str, rank: int, world: int, out_dir: Path) -> None:
         report["multicast"] = bool(buf.multicast_ptr)
         buf.tensor.fill_(float(rank + 1))
         buf.barrier()
-        # a view of the peer's mapping in THIS process: read what the peer wrote, then write into it
+        # the peer's mapping in THIS process: read what the peer wrote, then write into it (driver copies: no
+        # library kernel is handed a peer address)
         peer = (rank + 1) % world
-        peer_view = torch.as_tensor(symm._DeviceMemory(buf.peer_ptrs[peer], 4 * n), device=device).view(torch.float32)
-        report["peer_read"] = float(peer_view[123])
+        scratch = torch.zeros(1, dtype=torch.float32, device=device)
+        torch.cuda.synchronize()
+        symm.copy_bytes(scratch.data_ptr(), buf.peer_ptrs[peer] + 4 * 123, 4)
+        report["peer_read"] = float(scratch[0])
         buf.barrier()
-        peer_view[7] = 100.0 + rank
+        scratch.fill_(100.0 + rank)
+        torch.cuda.synchronize()
+        symm.copy_bytes(buf.peer_ptrs[peer] + 4 * 7, scratch.data_ptr(), 4)
         buf.barrier()
         report["peer_wrote_here"] = float(buf.tensor[7])
         # the in-kernel all-reduce on the own allocator (peer loads, and multimem when there is an address)
@@ -100,7 +105,7 @@ def worker(mode: str, rank: int, world: int, out_dir: Path) -> None:
             report[label] = float((buf.tensor - want).abs().max())
         report["status"] = int(status[0])
         before = torch.cuda.mem_get_info(device)[0]
-        del peer_view, buf, flags
+        del buf, flags
         import gc
         gc.collect()
         torch.cuda.synchronize()

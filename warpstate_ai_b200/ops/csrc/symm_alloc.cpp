@@ -305,6 +305,18 @@ int ws_symm_release(unsigned long long handle, unsigned long long ptr, long long
   return 0;
 }
 
+// A synchronous copy between any two mapped ranges (this GPU's or a peer's) by the driver's copy path --
+// no kernel of any library touches the peer mapping.  For tests and one-off transfers.
+int ws_symm_copy(unsigned long long dst, unsigned long long src, long long bytes) {
+  const cudaError_t e = cudaMemcpy(reinterpret_cast<void*>(dst), reinterpret_cast<const void*>(src),
+                                   static_cast<size_t>(bytes), cudaMemcpyDefault);
+  if (e != cudaSuccess) {
+    g_error = std::string("cudaMemcpy failed: ") + cudaGetErrorString(e);
+    return -48;
+  }
+  return 0;
+}
+
 void ws_symm_close_fd(int fd) {
   if (fd >= 0) close(fd);
 }

@@ -16,31 +16,35 @@ A guardian is an explicitly armed, CUDA-free process (run under supervisord) tha
 7. records every phase in ``control/handoff.json`` and refuses to continue if any source file or
    the plan changed after arming.
 
-Reference behaviour: ops/posttrain_handoff.py:378-531, ops/dpo_handoff.py:366-488.  One state
-machine serves both stages here; what differs per stage is a small strategy object.
+Reference behaviour: ops/posttrain_handoff.py:378-531, ops/dpo_handoff.py:366-488.  Here one `Guardian`
+serves both stages.  What a stage demands of its parent checkpoint and of its own completion is a table of
+`Rule`s (message, predicate) that `enforce` walks; the journal file, the lock ladder and the child launches are
+methods of the guardian, one per phase, and a phase that cannot proceed yet returns `RETRY`.
 """
 from __future__ import annotations
 
 import argparse
 import contextlib
-import http.client
 import json
 import math
 import signal
 import socket
 import subprocess
 import sys
+import tempfile
 import time
 import xmlrpc.client
 from pathlib import Path
+from typing import Callable, NamedTuple
 
 import torch
 
-from ..utils.io import atomic_json, digest, process_lock, utc_timestamp
+from ..utils.io import LockHeld, atomic_json, digest, process_lock, utc_timestamp
 from . import archive as A
 from .launcher import PACKAGE, supervise, training_environment, workspace_path, workspace_root
 
 STOPPED = False
+RETRY = object()          # a phase's answer when the world is not ready: sleep one poll interval, start over
 
 
 def request_stop(signum=None, frame=None) -> None:
@@ -49,40 +53,69 @@ def request_stop(signum=None, frame=None) -> None:
 
 
 # --------------------------------------------------------------------------- supervisord status
-class _UnixConnection(http.client.HTTPConnection):
-    def __init__(self, path):
-        super().__init__("localhost", timeout=10)
-        self._path = str(path)
-
-    def connect(self):
-        self.sock = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
-        self.sock.settimeout(self.timeout)
-        self.sock.connect(self._path)
-
-
-class _UnixTransport(xmlrpc.client.Transport):
-    def __init__(self, path):
-        super().__init__()
-        self._path = path
-
-    def make_connection(self, host):
-        return _UnixConnection(self._path)
-
-
 def process_status(socket_path, program: str) -> dict:
-    with xmlrpc.client.ServerProxy("http://localhost/RPC2", transport=_UnixTransport(socket_path)) as rpc:
-        return rpc.supervisor.getProcessInfo(program)
+    """``supervisor.getProcessInfo(program)`` as one HTTP/1.0 exchange over supervisord's unix socket."""
+    call = xmlrpc.client.dumps((program,), "supervisor.getProcessInfo").encode()
+    request = (b"POST /RPC2 HTTP/1.0\r\nHost: localhost\r\nContent-Type: text/xml\r\nContent-Length: "
+               + str(len(call)).encode() + b"\r\n\r\n" + call)
+    with socket.socket(socket.AF_UNIX, socket.SOCK_STREAM) as link:
+        link.settimeout(10)
+        link.connect(str(socket_path))
+        link.sendall(request)
+        answer = b"".join(iter(lambda: link.recv(1 << 16), b""))
+    head, separator, body = answer.partition(b"\r\n\r\n")
+    status_line = head.split(b"\r\n", 1)[0].split()
+    if not separator or len(status_line) < 2 or status_line[1] != b"200":
+        raise ConnectionError(f"supervisord answered {head[:80]!r}")
+    (info,), _ = xmlrpc.client.loads(body)
+    return info
 
 
 def clean_exit(info: dict) -> bool:
-    return info.get("statename") == "EXITED" and info.get("exitstatus") == 0
+    return (info.get("statename"), info.get("exitstatus")) == ("EXITED", 0)
 
 
 def read_json(path):
-    return json.loads(Path(path).read_text())
+    with open(path, encoding="utf-8") as handle:
+        return json.load(handle)
 
 
-# --------------------------------------------------------------------------- stage strategies
+def load_checkpoint(path):
+    return torch.load(path, map_location="cpu", weights_only=False, mmap=True)
+
+
+# --------------------------------------------------------------------------- rules
+class Rule(NamedTuple):
+    message: str
+    holds: Callable[[], bool]
+
+
+def enforce(rules) -> None:
+    """Raise the message of the first rule that does not hold (a rule that cannot even be evaluated -- a missing
+    key -- does not hold)."""
+    for rule in rules:
+        try:
+            fine = bool(rule.holds())
+        except (KeyError, TypeError):
+            fine = False
+        if not fine:
+            raise ValueError(rule.message)
+
+
+def finite(value) -> bool:
+    return isinstance(value, (int, float)) and math.isfinite(value)
+
+
+def fp32_weights(model: dict, what: str):
+    return [Rule(f"Expected {what} FP32 model weights: {name}: {tensor.dtype}",
+                 lambda t=tensor: not t.is_floating_point() or t.dtype == torch.float32) for name, tensor in model.items()]
+
+
+def overlaps(a: Path, b: Path) -> bool:
+    return a.is_relative_to(b) or b.is_relative_to(a)
+
+
+# --------------------------------------------------------------------------- stages
 BASE_NOTE = """# KEEP: historical WarpState step {step} weights
 
 Raw model archive created {created} before supervised fine-tuning.
@@ -97,412 +130,443 @@ Preserve this directory during cleanup and chat refreshes.
 """
 
 
-class SftStage:
+class Stage:
+    """What differs between the two hand-offs.  Subclasses fill the class attributes and the rule tables."""
+    name = plan_format = handoff_format = preflight_format = trainer = checkpoint_format = completion_format = ""
+    parent_key = parent_dir_key = ""
+    data_files: tuple = ()
+    path_keys: tuple = ()
+    trainer_extras: tuple = ()
+
+    def check_paths(self, plan, paths) -> None:
+        raise NotImplementedError
+
+    def parent_rules(self, checkpoint, plan, tokenizer_hash) -> list:
+        raise NotImplementedError
+
+    def make_archive(self, paths, plan, revision) -> dict:
+        raise NotImplementedError
+
+    def completion_rules(self, checkpoint, completion, report, plan, model_hash) -> list:
+        raise NotImplementedError
+
+    # ---- shared behaviour
+    def boundary(self, plan) -> dict:
+        parent = plan[self.parent_key]
+        return {key: parent[key] for key in ("step", "tokens_seen", "tokenizer_sha256")}
+
+    def tokenizer_hash(self, plan) -> str:
+        return plan[self.parent_key]["tokenizer_sha256"]
+
+    def parent_checkpoint(self, paths) -> Path:
+        return paths[self.parent_dir_key] / "run/latest.pt"
+
+    def validate_parent(self, checkpoint, plan, tokenizer_hash) -> None:
+        enforce(self.parent_rules(checkpoint, plan, tokenizer_hash))
+
+    def verify_completion(self, run: Path, plan, model_hash) -> dict:
+        completion, report = read_json(run / "completion.json"), read_json(run / "evaluation.json")
+        enforce(self.completion_rules(load_checkpoint(run / "latest.pt"), completion, report, plan, model_hash))
+        return completion
+
+    def torchrun(self, paths, processes: int) -> list:
+        return [sys.executable, "-B", "-m", "torch.distributed.run", "--standalone", "--local-addr", "127.0.0.1",
+                "--nnodes", "1", "--nproc-per-node", str(processes), "--log-dir", str(paths["work_dir"] / "logs/torchrun")]
+
+    def trainer_command(self, config, paths, weights, stop_path, processes) -> list:
+        work = paths["work_dir"]
+        flags = {"--config": config, "--work-dir": work / "run", "--data-dir": paths["data_dir"], "--weights": weights,
+                 "--tokenizer": paths["tokenizer"]}
+        flags.update({flag: work / leaf for flag, leaf in self.trainer_extras})
+        flags["--stop-file"] = stop_path
+        return [*self.torchrun(paths, processes), str(PACKAGE / self.trainer),
+                *(text for flag, value in flags.items() for text in (flag, str(value)))]
+
+    def preflight_command(self, paths, processes) -> list:
+        return [sys.executable, "-B", "-m", "warpstate_ai_b200.orchestration.preflight", "--stage", self.name,
+                "--work-dir", str(paths["work_dir"] / "preflight"), "--processes", str(processes)]
+
+
+class SftStage(Stage):
     """base pretraining -> SFT."""
-    name = "sft"
-    plan_format = "warpstate-posttrain-plan-v1"
-    handoff_format = "warpstate-posttrain-handoff-v1"
+    name, trainer = "sft", "posttrain.py"
+    plan_format, handoff_format = "warpstate-posttrain-plan-v1", "warpstate-posttrain-handoff-v1"
+    preflight_format = "warpstate-posttrain-preflight-v1"
+    checkpoint_format, completion_format = "warpstate-posttrain-v1", "warpstate-posttrain-completion-v1"
+    parent_key, parent_dir_key = "base", "base_work_dir"
     data_files = ("sft_train.jsonl", "sft_val.jsonl")
     path_keys = ("base_work_dir", "supervisor_socket", "archive_dir", "work_dir", "data_dir", "tokenizer")
 
     def check_paths(self, plan, paths):
-        base, work, archive, data = paths["base_work_dir"], paths["work_dir"], paths["archive_dir"], paths["data_dir"]
-        if work == base or work.is_relative_to(base / "run") or work.is_relative_to(base / "archives") \
-                or work.is_relative_to(archive):
-            raise ValueError("Posttraining must have a separate run directory outside the base run/archive")
-        if archive.is_relative_to(work) or data.is_relative_to(work) or work.is_relative_to(data):
-            raise ValueError("Archive and prepared data must stay outside the mutable posttraining run")
+        work, base = paths["work_dir"], paths["base_work_dir"]
+        inside = [base / "run", base / "archives", paths["archive_dir"]]
+        enforce([Rule("Posttraining must have a separate run directory outside the base run/archive",
+                      lambda: work != base and not any(work.is_relative_to(p) for p in inside)),
+                 Rule("Archive and prepared data must stay outside the mutable posttraining run",
+                      lambda: not paths["archive_dir"].is_relative_to(work) and not overlaps(paths["data_dir"], work))])
 
-    def boundary(self, plan):
-        return plan["base"]
-
-    def parent_checkpoint(self, paths):
-        return paths["base_work_dir"] / "run/latest.pt"
-
-    def validate_parent(self, checkpoint, plan, tokenizer_hash):
-        base = plan["base"]
-        if checkpoint.get("format") != "warpstate-server-v1":
-            raise ValueError("Expected a full base training checkpoint")
-        for key in ("step", "tokens_seen"):
-            if checkpoint.get(key) != base[key]:
-                raise ValueError(f"Base {key} must equal {base[key]}, got {checkpoint.get(key)}")
-        if checkpoint.get("val_step") != base["step"] or checkpoint.get("val_tokens") != base["tokens_seen"]:
-            raise ValueError("Base checkpoint must contain final validation at the exact stop boundary")
-        if not math.isfinite(checkpoint.get("val_loss", float("nan"))):
-            raise ValueError("Base validation loss is not finite")
-        actual = checkpoint["signature"]["data"]["signature"]["tokenizer_sha256"]
-        if actual != tokenizer_hash or actual != base["tokenizer_sha256"]:
-            raise ValueError("Base tokenizer identity differs from the pinned posttraining plan")
-        if not checkpoint.get("model"):
-            raise ValueError("Base checkpoint contains no model tensors")
-        for name, tensor in checkpoint["model"].items():
-            if tensor.is_floating_point() and tensor.dtype != torch.float32:
-                raise ValueError(f"Expected original FP32 model weights: {name}: {tensor.dtype}")
+    def parent_rules(self, checkpoint, plan, tokenizer_hash):
+        want = plan["base"]
+        recorded = lambda: checkpoint["signature"]["data"]["signature"]["tokenizer_sha256"]   # noqa: E731
+        return [Rule("Expected a full base training checkpoint", lambda: checkpoint["format"] == "warpstate-server-v1"),
+                *(Rule(f"Base {key} must equal {want[key]}, got {checkpoint.get(key)}",
+                       lambda key=key: checkpoint[key] == want[key]) for key in ("step", "tokens_seen")),
+                Rule("Base checkpoint must contain final validation at the exact stop boundary",
+                     lambda: (checkpoint["val_step"], checkpoint["val_tokens"]) == (want["step"], want["tokens_seen"])),
+                Rule("Base validation loss is not finite", lambda: finite(checkpoint["val_loss"])),
+                Rule("Base tokenizer identity differs from the pinned posttraining plan",
+                     lambda: recorded() == tokenizer_hash == want["tokenizer_sha256"]),
+                Rule("Base checkpoint contains no model tensors", lambda: len(checkpoint["model"]) > 0),
+                *fp32_weights(checkpoint.get("model") or {}, "original")]
 
     def make_archive(self, paths, plan, revision):
-        base = plan["base"]
-        return A.archive_training_checkpoint(
-            self.parent_checkpoint(paths), paths["tokenizer"], paths["archive_dir"], base, BASE_NOTE,
-            lambda ckpt: self.validate_parent(ckpt, plan, digest(paths["tokenizer"])))
+        identity = digest(paths["tokenizer"])
+        return A.archive_training_checkpoint(self.parent_checkpoint(paths), paths["tokenizer"], paths["archive_dir"],
+                                             plan["base"], BASE_NOTE,
+                                             lambda loaded: self.validate_parent(loaded, plan, identity))
 
-    def trainer_command(self, config, paths, weights, stop_path, processes):
-        return [sys.executable, "-B", "-m", "torch.distributed.run", "--standalone", "--local-addr", "127.0.0.1",
-                "--nnodes", "1", "--nproc-per-node", str(processes), "--log-dir", str(paths["work_dir"] / "logs/torchrun"),
-                str(PACKAGE / "posttrain.py"), "--config", str(config), "--work-dir", str(paths["work_dir"] / "run"),
-                "--data-dir", str(paths["data_dir"]), "--weights", str(weights), "--tokenizer", str(paths["tokenizer"]),
-                "--stop-file", str(stop_path)]
-
-    def preflight_command(self, paths, processes):
-        return [sys.executable, "-B", "-m", "warpstate_ai_b200.orchestration.preflight", "--stage", "sft",
-                "--work-dir", str(paths["work_dir"] / "preflight"), "--processes", str(processes)]
-
-    def verify_completion(self, run, plan, model_hash):
-        completion = read_json(run / "completion.json")
-        checkpoint = torch.load(run / "latest.pt", map_location="cpu", weights_only=False, mmap=True)
-        report = read_json(run / "evaluation.json")
-        step, total = checkpoint["step"], checkpoint["total_steps"]
-        if (checkpoint.get("format") != "warpstate-posttrain-v1" or checkpoint.get("completed") is not True
-                or step != total or total < 1 or checkpoint.get("val_step") != step
-                or not math.isfinite(checkpoint["val_loss"])):
-            raise ValueError("SFT completion does not have a durable, fully evaluated final checkpoint")
-        if (checkpoint["signature"]["plan"] != plan or checkpoint["signature"]["base_sha256"] != model_hash
-                or checkpoint["origin"]["step"] != plan["base"]["step"]):
-            raise ValueError("SFT completion belongs to a different plan or initialization")
-        if (completion.get("format") != "warpstate-posttrain-completion-v1" or completion.get("stage") != "sft"
-                or completion.get("completed") is not True or completion.get("step") != step
-                or completion.get("total_steps") != total or completion.get("base_step") != plan["base"]["step"]):
-            raise ValueError("SFT completion report differs from its checkpoint")
-        if (report.get("stage") != "sft" or report.get("step") != step or report.get("base_sha256") != model_hash
-                or report.get("val_loss") != checkpoint["val_loss"]):
-            raise ValueError("SFT evaluation report differs from its completed checkpoint")
-        return completion
-
-    def tokenizer_hash(self, plan):
-        return plan["base"]["tokenizer_sha256"]
+    def completion_rules(self, checkpoint, completion, report, plan, model_hash):
+        step, origin = checkpoint["step"], plan["base"]["step"]
+        return [Rule("SFT completion does not have a durable, fully evaluated final checkpoint",
+                     lambda: (checkpoint["format"] == self.checkpoint_format and checkpoint["completed"] is True
+                              and 1 <= checkpoint["total_steps"] == step == checkpoint["val_step"]
+                              and finite(checkpoint["val_loss"]))),
+                Rule("SFT completion belongs to a different plan or initialization",
+                     lambda: (checkpoint["signature"]["plan"] == plan and checkpoint["signature"]["base_sha256"] == model_hash
+                              and checkpoint["origin"]["step"] == origin)),
+                Rule("SFT completion report differs from its checkpoint",
+                     lambda: ({k: completion[k] for k in ("format", "stage", "completed", "step", "total_steps", "base_step")}
+                              == {"format": self.completion_format, "stage": "sft", "completed": True, "step": step,
+                                  "total_steps": checkpoint["total_steps"], "base_step": origin})),
+                Rule("SFT evaluation report differs from its completed checkpoint",
+                     lambda: ({k: report[k] for k in ("stage", "step", "base_sha256", "val_loss")}
+                              == {"stage": "sft", "step": step, "base_sha256": model_hash, "val_loss": checkpoint["val_loss"]}))]
 
 
-class DpoStage(SftStage):
+class DpoStage(Stage):
     """SFT -> DPO: the parent is a completed SFT run; its model is exported with ``stage='sft'``."""
-    name = "dpo"
-    plan_format = "warpstate-dpo-plan-v1"
-    handoff_format = "warpstate-dpo-handoff-v1"
+    name, trainer = "dpo", "dpo.py"
+    plan_format, handoff_format = "warpstate-dpo-plan-v1", "warpstate-dpo-handoff-v1"
+    preflight_format = "warpstate-dpo-preflight-v1"
+    checkpoint_format, completion_format = "warpstate-dpo-v1", "warpstate-dpo-completion-v1"
+    parent_key, parent_dir_key = "sft", "sft_work_dir"
     data_files = ("dpo_train.jsonl", "dpo_val.jsonl")
     path_keys = ("base_work_dir", "sft_work_dir", "supervisor_socket", "archive_dir", "work_dir", "data_dir", "tokenizer")
+    trainer_extras = (("--reference-cache-dir", "reference-cache"),)
 
     def check_paths(self, plan, paths):
-        work, base, sft, archive, data = (paths[k] for k in ("work_dir", "base_work_dir", "sft_work_dir",
-                                                             "archive_dir", "data_dir"))
-        for protected in (base / "run", sft, archive, data):
-            if work.is_relative_to(protected) or protected.is_relative_to(work):
-                raise ValueError(f"DPO outputs overlap protected inputs: {protected}")
+        work = paths["work_dir"]
+        protected = [paths["base_work_dir"] / "run", paths["sft_work_dir"], paths["archive_dir"], paths["data_dir"]]
+        enforce(Rule(f"DPO outputs overlap protected inputs: {p}", lambda p=p: not overlaps(work, p)) for p in protected)
 
-    def boundary(self, plan):
-        s = plan["sft"]
-        return {"step": s["step"], "tokens_seen": s["tokens_seen"], "tokenizer_sha256": s["tokenizer_sha256"]}
-
-    def parent_checkpoint(self, paths):
-        return paths["sft_work_dir"] / "run/latest.pt"
-
-    def validate_parent(self, checkpoint, plan, tokenizer_hash):
-        expected = plan["sft"]
-        if (checkpoint.get("format") != "warpstate-posttrain-v1" or checkpoint.get("completed") is not True
-                or checkpoint.get("step") != expected["step"] or checkpoint.get("total_steps") != expected["step"]
-                or checkpoint.get("tokens_seen") != expected["tokens_seen"]
-                or checkpoint.get("val_step") != expected["step"]):
-            raise ValueError("SFT must complete the exact planned run and final validation before DPO")
-        if not math.isfinite(checkpoint.get("val_loss", float("nan"))):
-            raise ValueError("SFT final validation loss is not finite")
-        if checkpoint["signature"]["tokenizer_sha256"] != expected["tokenizer_sha256"] or tokenizer_hash != expected["tokenizer_sha256"]:
-            raise ValueError("Completed SFT checkpoint belongs to a different tokenizer")
-        if not checkpoint.get("optimizer") or not checkpoint.get("rng_by_rank"):
-            raise ValueError("Full SFT optimizer or per-rank resume state is missing")
-        for name, tensor in checkpoint["model"].items():
-            if tensor.is_floating_point() and tensor.dtype != torch.float32:
-                raise ValueError(f"Expected untouched FP32 SFT weights: {name}")
+    def parent_rules(self, checkpoint, plan, tokenizer_hash):
+        want = plan["sft"]
+        return [Rule("SFT must complete the exact planned run and final validation before DPO",
+                     lambda: (checkpoint["format"] == "warpstate-posttrain-v1" and checkpoint["completed"] is True
+                              and checkpoint["step"] == checkpoint["total_steps"] == checkpoint["val_step"] == want["step"]
+                              and checkpoint["tokens_seen"] == want["tokens_seen"])),
+                Rule("SFT final validation loss is not finite", lambda: finite(checkpoint["val_loss"])),
+                Rule("Completed SFT checkpoint belongs to a different tokenizer",
+                     lambda: checkpoint["signature"]["tokenizer_sha256"] == tokenizer_hash == want["tokenizer_sha256"]),
+                Rule("Full SFT optimizer or per-rank resume state is missing",
+                     lambda: bool(checkpoint["optimizer"]) and bool(checkpoint["rng_by_rank"])),
+                *fp32_weights(checkpoint.get("model") or {}, "untouched SFT")]
 
     def make_archive(self, paths, plan, revision):
-        """Sealed SFT archive: tensor-exact ``stage='sft'`` model export + tokenizer + the run's
-        reports; the complete SFT checkpoint is referenced by hash (it stays in the SFT run)."""
+        """Sealed SFT archive: tensor-exact ``stage='sft'`` model export + tokenizer + a note; the complete SFT
+        checkpoint is referenced by hash (it stays in the SFT run).  An existing archive is verified instead."""
         from ..ckpt.formats import export_chat_snapshot
-        import tempfile
-        destination = paths["archive_dir"]
-        boundary = self.boundary(plan)
-        source = self.parent_checkpoint(paths)
-        checkpoint = torch.load(source, map_location="cpu", weights_only=False, mmap=True)
+        destination, boundary, source = paths["archive_dir"], self.boundary(plan), self.parent_checkpoint(paths)
+        checkpoint = load_checkpoint(source)
         self.validate_parent(checkpoint, plan, digest(paths["tokenizer"]))
+
+        def same_tensors(folder):
+            A.tensors_equal(checkpoint["model"], load_checkpoint(folder / "model.pt")["model"])
+
         if destination.exists():
             metadata = A.verify_archive(destination, boundary)
-            exported = torch.load(destination / "model.pt", map_location="cpu", weights_only=False, mmap=True)
-            A.tensors_equal(checkpoint["model"], exported["model"])
+            same_tensors(destination)
             return metadata
         destination.parent.mkdir(parents=True, exist_ok=True)
         staging = Path(tempfile.mkdtemp(prefix=".sft-final-", dir=destination.parent))
-        full_hash = digest(source)
-        export_chat_snapshot(checkpoint, staging, paths["tokenizer"], {"path": str(source), "sha256": full_hash},
-                             stage="sft")
-        exported = torch.load(staging / "model.pt", map_location="cpu", weights_only=False, mmap=True)
-        A.tensors_equal(checkpoint["model"], exported["model"])
+        whole = {"path": str(source), "sha256": digest(source)}
+        export_chat_snapshot(checkpoint, staging, paths["tokenizer"], whole, stage="sft")
+        same_tensors(staging)
         A.copy_regular(paths["tokenizer"], staging / "tokenizer.model")
-        A.write_new(staging / "ARCHIVE.md",
-                    f"# KEEP: completed SFT at step {checkpoint['step']}\n\nCreated {utc_timestamp()}.\n"
-                    f"Full SFT checkpoint SHA256: `{full_hash}` ({source}).\nFinal full-holdout loss: "
-                    f"{checkpoint['val_loss']}.\nRepository revision: `{revision}`.\n")
+        A.write_new(staging / "ARCHIVE.md", "\n".join([
+            f"# KEEP: completed SFT at step {checkpoint['step']}", "", f"Created {utc_timestamp()}.",
+            f"Full SFT checkpoint SHA256: `{whole['sha256']}` ({source}).",
+            f"Final full-holdout loss: {checkpoint['val_loss']}.", f"Repository revision: `{revision}`.", ""]))
         A.seal(staging)
         metadata = A.verify_archive(staging, boundary)
         A.publish_directory(staging, destination)
         return metadata
 
-    def trainer_command(self, config, paths, weights, stop_path, processes):
-        return [sys.executable, "-B", "-m", "torch.distributed.run", "--standalone", "--local-addr", "127.0.0.1",
-                "--nnodes", "1", "--nproc-per-node", str(processes), "--log-dir", str(paths["work_dir"] / "logs/torchrun"),
-                str(PACKAGE / "dpo.py"), "--config", str(config), "--work-dir", str(paths["work_dir"] / "run"),
-                "--data-dir", str(paths["data_dir"]), "--weights", str(weights), "--tokenizer", str(paths["tokenizer"]),
-                "--reference-cache-dir", str(paths["work_dir"] / "reference-cache"), "--stop-file", str(stop_path)]
-
-    def preflight_command(self, paths, processes):
-        return [sys.executable, "-B", "-m", "warpstate_ai_b200.orchestration.preflight", "--stage", "dpo",
-                "--work-dir", str(paths["work_dir"] / "preflight"), "--processes", str(processes)]
-
-    def verify_completion(self, run, plan, model_hash):
-        completion = read_json(run / "completion.json")
-        checkpoint = torch.load(run / "latest.pt", map_location="cpu", weights_only=False, mmap=True)
-        report = read_json(run / "evaluation.json")
-        step, total = checkpoint["step"], checkpoint["total_steps"]
-        if (checkpoint.get("format") != "warpstate-dpo-v1" or checkpoint.get("completed") is not True or step != total
-                or checkpoint.get("val_step") != step or not math.isfinite(checkpoint["val_loss"])):
-            raise ValueError("DPO completion does not have a durable, fully evaluated final checkpoint")
-        if checkpoint["signature"]["plan"] != plan or checkpoint["signature"]["base_sha256"] != model_hash:
-            raise ValueError("DPO completion belongs to a different plan or initialization")
-        if (completion.get("format") != "warpstate-dpo-completion-v1" or completion.get("completed") is not True
-                or completion.get("step") != step or report.get("step") != step
-                or report.get("val_loss") != checkpoint["val_loss"]):
-            raise ValueError("DPO completion/evaluation reports differ from the checkpoint")
-        return completion
-
-    def tokenizer_hash(self, plan):
-        return plan["sft"]["tokenizer_sha256"]
+    def completion_rules(self, checkpoint, completion, report, plan, model_hash):
+        step = checkpoint["step"]
+        return [Rule("DPO completion does not have a durable, fully evaluated final checkpoint",
+                     lambda: (checkpoint["format"] == self.checkpoint_format and checkpoint["completed"] is True
+                              and checkpoint["total_steps"] == step == checkpoint["val_step"]
+                              and finite(checkpoint["val_loss"]))),
+                Rule("DPO completion belongs to a different plan or initialization",
+                     lambda: checkpoint["signature"]["plan"] == plan and checkpoint["signature"]["base_sha256"] == model_hash),
+                Rule("DPO completion/evaluation reports differ from the checkpoint",
+                     lambda: (completion["format"] == self.completion_format and completion["completed"] is True
+                              and completion["step"] == step == report["step"]
+                              and report["val_loss"] == checkpoint["val_loss"]))]
 
 
 STAGES = {"sft": SftStage(), "dpo": DpoStage()}
 
 
-# --------------------------------------------------------------------------- plan / data
+# --------------------------------------------------------------------------- plan / data / identity
 def load_plan(path, stage):
     plan = read_json(path)
-    if (plan.get("format") != stage.plan_format or plan.get("stage") != stage.name
-            or plan.get("after_completion") != "pause_for_evaluation"):
-        raise ValueError(f"This handoff supports {stage.name} followed by an evaluation pause only")
-    options = plan["handoff"]
-    root = workspace_root()
+    enforce([Rule(f"This handoff supports {stage.name} followed by an evaluation pause only",
+                  lambda: (plan["format"], plan["stage"], plan["after_completion"])
+                  == (stage.plan_format, stage.name, "pause_for_evaluation"))])
+    options, root = plan["handoff"], workspace_root()
     paths = {key: workspace_path(root / options[key]) for key in stage.path_keys}
     stage.check_paths(plan, paths)
-    if not 1 <= options["processes"] <= 8 or not 0.01 <= options["poll_seconds"] <= 60:
-        raise ValueError("Invalid process count or polling interval")
+    enforce([Rule("Invalid process count or polling interval",
+                  lambda: 1 <= options["processes"] <= 8 and 0.01 <= options["poll_seconds"] <= 60)])
     return plan, paths
 
 
 def data_readiness(folder: Path, plan, stage, *, verify: bool = False):
-    path = folder / "manifest.json"
-    if not path.is_file():
+    """(ready, why).  Not ready is an answer; prepared data that contradicts the plan is an error."""
+    listing = folder / "manifest.json"
+    if not listing.is_file():
         return False, "waiting for data manifest"
-    manifest = read_json(path)
-    if manifest.get("format") != "warpstate-posttrain-data-v1" or not manifest.get("complete"):
+    manifest = read_json(listing)
+    if (manifest.get("format"), bool(manifest.get("complete"))) != ("warpstate-posttrain-data-v1", True):
         return False, "data preparation is incomplete"
-    if manifest.get("tokenizer_sha256") != stage.tokenizer_hash(plan):
-        raise ValueError("Prepared data uses a different tokenizer")
-    if manifest.get("max_length") != plan["training"]["sequence_length"]:
-        raise ValueError("Prepared data context length differs from the plan")
-    expected_manifest = plan["handoff"].get("data_manifest_sha256")
-    if expected_manifest is not None and digest(path) != expected_manifest:
-        raise ValueError("Prepared data differs from the authorized plan")
-    for name in stage.data_files:
-        entry = manifest["outputs"].get(name, {})
-        if entry.get("rows", 0) < 1 or not (folder / name).is_file():
-            raise ValueError(f"Prepared split is empty or missing: {name}")
-        if verify and digest(folder / name) != entry.get("sha256"):
-            raise ValueError(f"Prepared file checksum mismatch: {name}")
-    return True, "data manifest complete" if not verify else "data hashes verified"
+    pinned = plan["handoff"].get("data_manifest_sha256")
+    outputs = manifest.get("outputs", {})
+    enforce([Rule("Prepared data uses a different tokenizer", lambda: manifest["tokenizer_sha256"] == stage.tokenizer_hash(plan)),
+             Rule("Prepared data context length differs from the plan",
+                  lambda: manifest["max_length"] == plan["training"]["sequence_length"]),
+             Rule("Prepared data differs from the authorized plan", lambda: pinned is None or digest(listing) == pinned),
+             *(Rule(f"Prepared split is empty or missing: {name}",
+                    lambda name=name: outputs[name]["rows"] >= 1 and (folder / name).is_file()) for name in stage.data_files)])
+    if not verify:
+        return True, "data manifest complete"
+    enforce(Rule(f"Prepared file checksum mismatch: {name}", lambda name=name: digest(folder / name) == outputs[name]["sha256"])
+            for name in stage.data_files)
+    return True, "data hashes verified"
 
 
 def source_identity(config: Path) -> dict:
     """Hashes of the plan and of every source file that defines what the child stage runs."""
     package = PACKAGE / "warpstate_ai_b200"
-    files = [config, PACKAGE / "posttrain.py", PACKAGE / "dpo.py", PACKAGE / "run_40b.py", PACKAGE / "chat.py",
-             *sorted((package / "train").glob("*.py")), *sorted((package / "data").glob("*.py")),
-             *sorted((package / "orchestration").glob("*.py")), package / "models/warpstate.py", package / "config.py",
-             package / "ckpt/writer.py", package / "ckpt/formats.py"]
-    return {str(p): digest(p) for p in files if p.is_file()}
+    entry_points = [PACKAGE / name for name in ("posttrain.py", "dpo.py", "run_40b.py", "chat.py")]
+    folders = [sorted((package / sub).glob("*.py")) for sub in ("train", "data", "orchestration")]
+    single = [package / leaf for leaf in ("models/warpstate.py", "config.py", "ckpt/writer.py", "ckpt/formats.py")]
+    return {str(p): digest(p) for p in (config, *entry_points, *(f for group in folders for f in group), *single) if p.is_file()}
 
 
 def git_revision() -> str:
-    try:
-        return subprocess.check_output(["git", "rev-parse", "HEAD"], cwd=PACKAGE, text=True,
-                                       stderr=subprocess.DEVNULL).strip()
-    except (OSError, subprocess.CalledProcessError):
-        return "unknown"
+    done = subprocess.run(["git", "rev-parse", "HEAD"], cwd=PACKAGE, text=True, capture_output=True, check=False)
+    return done.stdout.strip() if done.returncode == 0 and done.stdout.strip() else "unknown"
 
 
 def verify_preflight(path: Path, stage, processes: int) -> dict:
     report = read_json(path)
-    if (report.get("format") != f"warpstate-{'posttrain' if stage.name == 'sft' else 'dpo'}-preflight-v1"
-            or report.get("accepted") is not True or report.get("processes") != processes
-            or report.get("bf16_compute") is not True or report.get("fp32_parameters_and_adam") is not True):
-        raise ValueError("GPU preflight report is missing, failed, or belongs to different sources")
+    wanted = {"format": stage.preflight_format, "accepted": True, "processes": processes, "bf16_compute": True,
+              "fp32_parameters_and_adam": True}
+    enforce([Rule("GPU preflight report is missing, failed, or belongs to different sources",
+                  lambda: {key: report[key] for key in wanted} == wanted)])
     return report
 
 
-# --------------------------------------------------------------------------- the state machine
+# --------------------------------------------------------------------------- the guardian
+class Journal:
+    """``control/handoff.json``: who armed the hand-off against which sources, and the phase it is in."""
+
+    def __init__(self, path: Path, stage, identity: dict, boundary: dict, paths: dict):
+        self.path = path
+        if path.exists():
+            self.state = read_json(path)
+            if self.state["source_sha256"] != identity:
+                raise ValueError("Armed handoff source/config changed; inspect and explicitly re-arm")
+        else:
+            self.state = {"format": stage.handoff_format, "armed_at": utc_timestamp(), "source_sha256": identity,
+                          "git_revision": git_revision(), "target": boundary, "archive_dir": str(paths["archive_dir"]),
+                          "work_dir": str(paths["work_dir"])}
+
+    @property
+    def complete(self) -> bool:
+        return self.state.get("phase") == "complete"
+
+    def note(self, phase: str, message: str, **extra) -> None:
+        fresh = (self.state.get("phase"), self.state.get("message")) != (phase, message)
+        self.state.update(extra, phase=phase, message=message, updated_at=utc_timestamp())
+        atomic_json(self.path, self.state)
+        if fresh:
+            print(f"[{utc_timestamp()}] {phase}: {message}", flush=True)
+
+
+class Guardian:
+    def __init__(self, config: Path, stage, status_fn, supervise_fn):
+        self.config, self.stage, self.supervise_fn = Path(config), stage, supervise_fn
+        self.plan, self.paths = load_plan(self.config, stage)
+        self.options = self.plan["handoff"]
+        self.boundary = stage.boundary(self.plan)
+        self.work, self.base_work = self.paths["work_dir"], self.paths["base_work_dir"]
+        self.state_path = self.work / "control/handoff.json"
+        self.stop_path = self.work / "control/training-stop-request"
+        program = self.options["parent_program"] if "parent_program" in self.options else self.options["base_program"]
+        self.parent_status = lambda: status_fn(self.paths["supervisor_socket"], program)
+
+    # ---- read-only report
+    def describe(self) -> dict:
+        ready, reason = data_readiness(self.paths["data_dir"], self.plan, self.stage)
+        return {"parent_process": self.parent_status(), "target": self.boundary, "data_ready": ready, "data_status": reason,
+                "state_path": str(self.state_path),
+                "handoff": read_json(self.state_path) if self.state_path.exists() else None}
+
+    # ---- helpers
+    def nap(self):
+        time.sleep(self.options["poll_seconds"])
+
+    def unchanged(self, when: str) -> None:
+        if source_identity(self.config) != self.identity:
+            raise ValueError(f"Armed source/config changed before {when}")
+
+    # ---- phases (each returns RETRY when it has to wait)
+    def parent_finished(self):
+        info = self.parent_status()
+        if clean_exit(info):
+            return True
+        ready, reason = data_readiness(self.paths["data_dir"], self.plan, self.stage)
+        self.journal.note("waiting_for_parent", f"Parent {info.get('statename')}; {reason}", data_ready=ready)
+        return RETRY
+
+    def seal_and_stage(self):
+        """Under the exclusive pipeline lock: validate, archive, copy, wait for data, write execution.json.
+        -> (weights path, archive hash), RETRY, or None when a stop arrived while waiting for data."""
+        if not clean_exit(self.parent_status()):
+            return RETRY
+        reached = load_checkpoint(self.stage.parent_checkpoint(self.paths))
+        if reached.get("step", -1) < self.boundary["step"]:
+            self.journal.note("waiting_for_parent", f"Parent exited early at step {reached.get('step')}")
+            return RETRY
+        self.stage.validate_parent(reached, self.plan, digest(self.paths["tokenizer"]))
+        del reached
+        self.unchanged("handoff")
+        self.journal.note("archiving", "Sealing the parent's original FP32 weights at the exact final step")
+        model_hash = self.stage.make_archive(self.paths, self.plan, self.journal.state["git_revision"])["snapshot_sha256"]
+        self.journal.note("copying_initialization", "Creating/verifying the independent initialization",
+                          archive_sha256=model_hash)
+        weights = A.independent_copy(self.paths["archive_dir"], self.work / "initialization", self.boundary, model_hash)
+        while True:
+            if STOPPED:
+                return None
+            ready, reason = data_readiness(self.paths["data_dir"], self.plan, self.stage)
+            if ready:
+                break
+            self.journal.note("waiting_for_data", reason)
+            self.nap()
+        data_readiness(self.paths["data_dir"], self.plan, self.stage, verify=True)
+        self.unchanged("launch")
+        self.stop_path.unlink(missing_ok=True)        # no surviving worker can still need it
+        atomic_json(self.work / "control/execution.json", {
+            "plan": self.plan, "source_sha256": self.identity, "git_revision": self.journal.state["git_revision"],
+            "archive_sha256": model_hash, "data_manifest_sha256": digest(self.paths["data_dir"] / "manifest.json")})
+        return weights, model_hash
+
+    def run_children(self, weights: Path, model_hash: str, descriptors: tuple) -> None:
+        """Preflight, then the trainer; both inherit the guardian's lock descriptors so that its death cannot lead to
+        a duplicate launch."""
+        environment, processes = training_environment(self.work), self.options["processes"]
+        if self.options.get("preflight", True):
+            self.journal.note("gpu_preflight", "Checking BF16 training, masked tails and checkpoint resume")
+            code = self.supervise_fn(self.stage.preflight_command(self.paths, processes), self.stop_path, environment,
+                                     pass_fds=descriptors)
+            if code:
+                raise RuntimeError(f"GPU preflight exited with status {code}; training was not started")
+            if STOPPED or self.stop_path.exists():
+                self.journal.note("paused", "Handoff stopped during GPU preflight; training was not started")
+                return
+            self.journal.state["preflight"] = verify_preflight(self.work / "preflight/report.json", self.stage, processes)
+        command = self.stage.trainer_command(self.config, self.paths, weights, self.stop_path, processes)
+        name = self.stage.name
+        self.journal.note(name, f"Starting/resuming {name}; fresh optimizer on first start", command=command)
+        code = self.supervise_fn(command, self.stop_path, environment, pass_fds=descriptors)
+        if code:
+            raise RuntimeError(f"{name} child exited with status {code}; checkpoints preserved")
+        if not (self.work / "run/completion.json").is_file():
+            self.journal.note("paused", f"{name} stopped before completion; its resume checkpoint is retained")
+            return
+        completion = self.stage.verify_completion(self.work / "run", self.plan, model_hash)
+        A.verify_archive(self.paths["archive_dir"], self.boundary, model_hash)
+        if digest(weights) != model_hash:
+            raise ValueError("Initialization changed during training")
+        self.journal.note("complete", f"{name} finished; paused for evaluation.", completion=completion)
+
+    def attempt(self, handoff_file):
+        """One pass down the lock ladder.  True when the hand-off has run its course (completed or paused)."""
+        if self.parent_finished() is RETRY:
+            return RETRY
+        with contextlib.ExitStack() as held:
+            # outer -> inner order of the base launcher; surviving child ranks hold the pipeline lock shared, so a
+            # retry while they live fails closed
+            try:
+                launcher_file = held.enter_context(process_lock(self.base_work / "control/training-launcher.lock"))
+            except LockHeld:
+                self.journal.note("waiting_for_locks", "Base launcher is still occupied")
+                return RETRY
+            with process_lock(self.base_work / "pipeline.lock"):
+                staged = self.seal_and_stage()
+            # the exclusive pipeline lock is released; the launcher and hand-off locks stay held
+            if staged is RETRY:
+                return RETRY
+            if staged is None or STOPPED:
+                return None
+            self.run_children(*staged, (handoff_file.fileno(), launcher_file.fileno()))
+            return True
+
+    def run(self) -> int:
+        self.state_path.parent.mkdir(parents=True, exist_ok=True)
+        with process_lock(self.work / "control/handoff.lock") as handoff_file:
+            self.identity = source_identity(self.config)
+            self.journal = Journal(self.state_path, self.stage, self.identity, self.boundary, self.paths)
+            if self.journal.complete:
+                print(f"{self.stage.name} already completed; remaining paused for evaluation.", flush=True)
+                return 0
+            for number in (signal.SIGINT, signal.SIGTERM, signal.SIGUSR1):
+                with contextlib.suppress(ValueError):      # not the main thread (tests)
+                    signal.signal(number, request_stop)
+            try:
+                while not STOPPED:
+                    outcome = self.attempt(handoff_file)
+                    if outcome is True:
+                        return 0
+                    if outcome is RETRY:
+                        self.nap()
+                self.journal.note("paused", "Handoff paused by request; no further training will start automatically")
+                return 0
+            except BaseException as error:
+                self.journal.note("failed", f"{type(error).__name__}: {error}")
+                raise
+
+
 def run_handoff(config, *, stage_name: str = "sft", check: bool = False, status_fn=process_status,
                 supervise_fn=supervise) -> int:
-    global STOPPED
-    stage = STAGES[stage_name]
-    config = Path(config)
-    plan, paths = load_plan(config, stage)
-    options = plan["handoff"]
-    boundary = stage.boundary(plan)
-    work, base_work = paths["work_dir"], paths["base_work_dir"]
-    state_path = work / "control/handoff.json"
-
-    def status():
-        return status_fn(paths["supervisor_socket"], options["parent_program"] if "parent_program" in options
-                         else options["base_program"])
-
+    guardian = Guardian(config, STAGES[stage_name], status_fn, supervise_fn)
     if check:
-        ready, reason = data_readiness(paths["data_dir"], plan, stage)
-        print(json.dumps(dict(parent_process=status(), target=boundary, data_ready=ready, data_status=reason,
-                              state_path=str(state_path),
-                              handoff=read_json(state_path) if state_path.exists() else None), indent=2))
+        print(json.dumps(guardian.describe(), indent=2))
         return 0
-    state_path.parent.mkdir(parents=True, exist_ok=True)
-    with process_lock(work / "control/handoff.lock") as handoff_file:
-        identity = source_identity(config)
-        if state_path.exists():
-            state = read_json(state_path)
-            if state["source_sha256"] != identity:
-                raise ValueError("Armed handoff source/config changed; inspect and explicitly re-arm")
-            if state.get("phase") == "complete":
-                print(f"{stage.name} already completed; remaining paused for evaluation.", flush=True)
-                return 0
-        else:
-            state = dict(format=stage.handoff_format, armed_at=utc_timestamp(), source_sha256=identity,
-                         git_revision=git_revision(), target=boundary, archive_dir=str(paths["archive_dir"]),
-                         work_dir=str(work))
-
-        def record(phase, message, **extra):
-            changed = state.get("phase") != phase or state.get("message") != message
-            state.update(phase=phase, message=message, updated_at=utc_timestamp(), **extra)
-            atomic_json(state_path, state)
-            if changed:
-                print(f"[{utc_timestamp()}] {phase}: {message}", flush=True)
-
-        stop_path = work / "control/training-stop-request"
-        for sig in (signal.SIGINT, signal.SIGTERM, signal.SIGUSR1):
-            with contextlib.suppress(ValueError):
-                signal.signal(sig, request_stop)
-        try:
-            while not STOPPED:
-                info = status()
-                ready, reason = data_readiness(paths["data_dir"], plan, stage)
-                if not clean_exit(info):
-                    record("waiting_for_parent", f"Parent {info.get('statename')}; {reason}", data_ready=ready)
-                    time.sleep(options["poll_seconds"])
-                    continue
-                # outer -> inner lock order of the base launcher; surviving child ranks hold the
-                # pipeline lock shared, so a retry while they live fails closed
-                launcher_ctx = process_lock(base_work / "control/training-launcher.lock")
-                try:
-                    launcher_file = launcher_ctx.__enter__()
-                except Exception as error:
-                    if type(error).__name__ != "LockHeld":
-                        raise
-                    record("waiting_for_locks", "Base launcher is still occupied")
-                    time.sleep(options["poll_seconds"])
-                    continue
-                try:
-                    with process_lock(base_work / "pipeline.lock"):
-                        if not clean_exit(status()):
-                            continue
-                        parent_path = stage.parent_checkpoint(paths)
-                        raw = torch.load(parent_path, map_location="cpu", weights_only=False, mmap=True)
-                        if raw.get("step", -1) < boundary["step"]:
-                            record("waiting_for_parent", f"Parent exited early at step {raw.get('step')}")
-                            del raw
-                            time.sleep(options["poll_seconds"])
-                            continue
-                        stage.validate_parent(raw, plan, digest(paths["tokenizer"]))
-                        del raw
-                        if source_identity(config) != identity:
-                            raise ValueError("Armed source/config changed before handoff")
-                        record("archiving", "Sealing the parent's original FP32 weights at the exact final step")
-                        metadata = stage.make_archive(paths, plan, state["git_revision"])
-                        model_hash = metadata["snapshot_sha256"]
-                        record("copying_initialization", "Creating/verifying the independent initialization",
-                               archive_sha256=model_hash)
-                        weights = A.independent_copy(paths["archive_dir"], work / "initialization", boundary, model_hash)
-                        while not STOPPED:
-                            ready, reason = data_readiness(paths["data_dir"], plan, stage)
-                            if ready:
-                                break
-                            record("waiting_for_data", reason)
-                            time.sleep(options["poll_seconds"])
-                        if STOPPED:
-                            break
-                        data_readiness(paths["data_dir"], plan, stage, verify=True)
-                        if source_identity(config) != identity:
-                            raise ValueError("Armed source/config changed before launch")
-                        stop_path.unlink(missing_ok=True)  # no surviving worker can still need it
-                        atomic_json(work / "control/execution.json", dict(
-                            plan=plan, source_sha256=identity, git_revision=state["git_revision"],
-                            archive_sha256=model_hash,
-                            data_manifest_sha256=digest(paths["data_dir"] / "manifest.json")))
-                    if STOPPED:
-                        break
-                    # pipeline.lock (exclusive) is released here; launcher lock + handoff lock stay
-                    # held and are passed to the children so that the guardian's death cannot
-                    # lead to a duplicate launch
-                    environment = training_environment(work)
-                    fds = (handoff_file.fileno(), launcher_file.fileno())
-                    processes = options["processes"]
-                    if options.get("preflight", True):
-                        record("gpu_preflight", "Checking BF16 training, masked tails and checkpoint resume")
-                        result = supervise_fn(stage.preflight_command(paths, processes), stop_path, environment,
-                                              pass_fds=fds)
-                        if result:
-                            raise RuntimeError(f"GPU preflight exited with status {result}; training was not started")
-                        if stop_path.exists() or STOPPED:
-                            record("paused", "Handoff stopped during GPU preflight; training was not started")
-                            return 0
-                        state["preflight"] = verify_preflight(work / "preflight/report.json", stage, processes)
-                    command = stage.trainer_command(config, paths, weights, stop_path, processes)
-                    record(stage.name, f"Starting/resuming {stage.name}; fresh optimizer on first start", command=command)
-                    result = supervise_fn(command, stop_path, environment, pass_fds=fds)
-                    if result:
-                        raise RuntimeError(f"{stage.name} child exited with status {result}; checkpoints preserved")
-                    if (work / "run/completion.json").is_file():
-                        completed = stage.verify_completion(work / "run", plan, model_hash)
-                        A.verify_archive(paths["archive_dir"], boundary, model_hash)
-                        if digest(weights) != model_hash:
-                            raise ValueError("Initialization changed during training")
-                        record("complete", f"{stage.name} finished; paused for evaluation.", completion=completed)
-                    else:
-                        record("paused", f"{stage.name} stopped before completion; its resume checkpoint is retained")
-                    return 0
-                finally:
-                    launcher_ctx.__exit__(None, None, None)
-            record("paused", "Handoff paused by request; no further training will start automatically")
-            return 0
-        except BaseException as error:
-            record("failed", f"{type(error).__name__}: {error}")
-            raise
+    return guardian.run()
 
 
 def main(argv=None) -> int:
-    parser = argparse.ArgumentParser(description=__doc__)
-    parser.add_argument("--config", type=Path, required=True)
-    parser.add_argument("--stage", choices=sorted(STAGES), default="sft")
-    parser.add_argument("--check", action="store_true", help="read-only status; do not arm or launch")
-    args = parser.parse_args(argv)
-    return run_handoff(workspace_path(args.config), stage_name=args.stage, check=args.check)
+    parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    parser.add_argument("--config", required=True, type=Path, help="the stage's plan file")
+    parser.add_argument("--stage", default="sft", choices=sorted(STAGES))
+    parser.add_argument("--check", action="store_true", help="print the read-only status; do not arm or launch")
+    options = parser.parse_args(argv)
+    return run_handoff(workspace_path(options.config), stage_name=options.stage, check=options.check)
 
 
 if __name__ == "__main__":

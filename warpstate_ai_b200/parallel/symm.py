@@ -81,6 +81,7 @@ class _Library:
                                                   ctypes.c_int]
         lib.ws_symm_release.argtypes = [ctypes.c_ulonglong, ctypes.c_ulonglong, ctypes.c_longlong]
         lib.ws_symm_multicast_supported.argtypes = [ctypes.c_int]
+        lib.ws_symm_copy.argtypes = [ctypes.c_ulonglong, ctypes.c_ulonglong, ctypes.c_longlong]
         self.lib = lib
 
     def check(self, code: int, what: str) -> None:
@@ -96,6 +97,13 @@ def _lib() -> _Library:
     if _library is None:
         _library = _Library()
     return _library
+
+
+def copy_bytes(dst_ptr: int, src_ptr: int, nbytes: int) -> None:
+    """Synchronous copy between mapped device ranges, peers' included, by the driver (no library kernel is handed
+    a peer address)."""
+    api = _lib()
+    api.check(api.lib.ws_symm_copy(dst_ptr, src_ptr, nbytes), "copy")
 
 
 class _DeviceMemory:
