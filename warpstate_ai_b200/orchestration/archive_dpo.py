@@ -29,96 +29,104 @@ import torch
 
 from ..ckpt.formats import export_chat_snapshot
 from ..train.dpo import DEFAULTS, identity_digest
-from ..utils.io import digest, utc_timestamp
+from ..utils.io import digest, process_lock, utc_timestamp
+from ..utils.rules import Rule, enforce, finite, fp32_tensors, matches
 from . import archive as A
 
 REPORTS = ("settings.json", "evaluation.json", "completion.json", "metrics.jsonl")
+# archive file name <- where it comes from: (root, leaf) with root one of run / data / cache / tokenizer / plan
+COPIED = {"checkpoint.pt": ("run", "latest.pt"), "tokenizer.model": ("tokenizer", ""), "plan.json": ("plan", ""),
+          **{name: ("run", name) for name in REPORTS}, "data-manifest.json": ("data", "manifest.json"),
+          "reference-manifest.json": ("cache", "manifest.json"), "reference-train.npy": ("cache", "train.npy"),
+          "reference-val.npy": ("cache", "val.npy")}
 FILES = ("checkpoint.pt", "model.pt", "snapshot.json", "tokenizer.model", "plan.json", *REPORTS, "data-manifest.json",
          "reference-manifest.json", "reference-train.npy", "reference-val.npy", "PROVENANCE.json", "ARCHIVE.md")
 CHAT_FILES = ("model.pt", "snapshot.json", "tokenizer.model", "ARCHIVE.md")
+SCORES = ("val_loss", "reward_margin", "reward_accuracy", "chosen_nll")
+IDENTITIES = ("base_sha256", "data_sha256", "tokenizer_sha256", "reference_sha256")
 
 
 def read_json(path):
-    return json.loads(Path(path).read_text())
+    with open(path, encoding="utf-8") as handle:
+        return json.load(handle)
+
+
+def load_tensors(path):
+    return torch.load(path, map_location="cpu", weights_only=False, mmap=True)
 
 
 def expected_counters(plan: dict, data: dict) -> dict:
-    settings = DEFAULTS | plan["training"]
-    world = plan["handoff"]["processes"]
-    train = data["outputs"]["dpo_train.jsonl"]
+    """Where a whole run over the prepared pairs must end, from the plan and the data manifest alone."""
+    settings, ranks = DEFAULTS | plan["training"], plan["handoff"]["processes"]
     if settings["max_steps"] is not None:
         raise ValueError("Archive requires a completed whole DPO run, without a plan step cap")
-    steps = math.ceil(train["rows"] / (settings["micro_batch"] * settings["grad_accum"] * world)) * settings["epochs"]
-    return dict(step=steps, total_steps=steps, sample_cursor=train["rows"] * settings["epochs"],
-                tokens_seen=(train["tokens"] - 2 * train["rows"]) * settings["epochs"],
-                response_tokens_seen=train["supervised_tokens"] * settings["epochs"], val_step=steps)
+    pairs, epochs = data["outputs"]["dpo_train.jsonl"], settings["epochs"]
+    per_update = settings["micro_batch"] * settings["grad_accum"] * ranks
+    updates = epochs * -(-pairs["rows"] // per_update)
+    return {"step": updates, "total_steps": updates, "val_step": updates, "sample_cursor": epochs * pairs["rows"],
+            "tokens_seen": epochs * (pairs["tokens"] - 2 * pairs["rows"]),       # each branch loses its shifted token
+            "response_tokens_seen": epochs * pairs["supervised_tokens"]}
 
 
 def validate_state(checkpoint, evaluation, completion, settings_report, data, reference, plan) -> dict:
-    """Consistency of a finished DPO run, judged from its preserved records only."""
-    settings = DEFAULTS | plan["training"]
-    world = plan["handoff"]["processes"]
-    val = data["outputs"]["dpo_val.jsonl"]
-    train = data["outputs"]["dpo_train.jsonl"]
+    """Consistency of a finished DPO run, judged from its preserved records only.  Returns the expected counters."""
+    settings, ranks = DEFAULTS | plan["training"], plan["handoff"]["processes"]
+    train_rows, val_rows = (data["outputs"][f"dpo_{split}.jsonl"]["rows"] for split in ("train", "val"))
     want = expected_counters(plan, data)
-    if (checkpoint.get("format") != "warpstate-dpo-v1" or checkpoint.get("completed") is not True
-            or any(checkpoint.get(k) != v for k, v in want.items())
-            or not math.isfinite(checkpoint.get("val_loss", float("nan")))):
-        raise ValueError("DPO checkpoint is not the fully completed, finally evaluated state")
-    sig = checkpoint["signature"]
-    if (sig.get("plan") != plan or sig.get("settings") != settings or sig.get("world_size") != world
-            or settings_report.get("signature") != sig or settings_report.get("total_steps") != want["step"]
-            or settings_report.get("train_rows") != train["rows"] or settings_report.get("val_rows") != val["rows"]):
-        raise ValueError("DPO checkpoint/settings signatures or dataset counts differ")
-    if (data.get("format") != "warpstate-posttrain-data-v1" or data.get("complete") is not True
-            or data.get("tokenizer_sha256") != sig["tokenizer_sha256"]
-            or data.get("max_length") != settings["sequence_length"]):
-        raise ValueError("DPO data provenance differs from its signature")
-    origin = checkpoint["origin"]
-    parent = plan.get("sft")
-    if origin.get("stage") != "sft" or origin.get("weights_sha256") != sig["base_sha256"]:
-        raise ValueError("DPO did not start from a sealed SFT export")
-    if parent is not None and (origin.get("step") != parent["step"] or origin.get("tokens_seen") != parent["tokens_seen"]):
-        raise ValueError("DPO SFT ancestry differs from the authorized plan")
-    states = checkpoint.get("optimizer", {}).get("state")
-    rng = checkpoint.get("rng_by_rank", [])
-    if not states or len(rng) != world or any("torch" not in r for r in rng):
-        raise ValueError("DPO optimizer or per-rank RNG state is missing")
-    for entry in states.values():
-        if float(entry["step"]) != want["step"]:
-            raise ValueError("DPO Adam step differs from the final checkpoint")
-        if entry["exp_avg"].dtype != torch.float32 or entry["exp_avg_sq"].dtype != torch.float32:
-            raise ValueError("DPO Adam state must retain its original FP32 tensors")
-    if not checkpoint.get("model"):
-        raise ValueError("DPO model tensors are missing")
-    for name, tensor in checkpoint["model"].items():
-        if tensor.is_floating_point() and tensor.dtype != torch.float32:
-            raise ValueError(f"DPO model tensor is not original FP32: {name}")
-    counters = ("step", "total_steps", "sample_cursor", "tokens_seen", "response_tokens_seen", "val_loss")
-    if (completion.get("format") != "warpstate-dpo-completion-v1" or completion.get("completed") is not True
-            or completion.get("paused_for_evaluation") is not True
-            or any(completion.get(k) != checkpoint[k] for k in counters)
-            or completion.get("reference_sha256") != sig["reference_sha256"]):
-        raise ValueError("DPO completion report differs from its checkpoint")
-    scores = ("val_loss", "reward_margin", "reward_accuracy", "chosen_nll")
-    if (evaluation.get("stage") != "dpo" or evaluation.get("step") != want["step"] or evaluation.get("full_holdout") is not True
-            or evaluation.get("evaluated_samples") != val["rows"]
-            or evaluation.get("available_validation_samples") != val["rows"]
-            or evaluation.get("objective") != settings["objective"]
-            or any(evaluation.get(k) != checkpoint["validation"].get(k) for k in (*scores, "evaluated_samples"))
-            or any(evaluation.get(k) != sig[k] for k in ("base_sha256", "data_sha256", "tokenizer_sha256", "reference_sha256"))
-            or not all(math.isfinite(evaluation.get(k, float("nan"))) for k in scores)):
-        raise ValueError("DPO final full-holdout evaluation differs from its checkpoint")
-    if not 0 <= evaluation["reward_accuracy"] <= 1 or evaluation["chosen_nll"] < 0:
-        raise ValueError("DPO evaluation contains impossible accuracy/NLL")
-    ident = reference.get("identity", {})
-    if (reference.get("format") != "warpstate-dpo-reference-v1" or reference.get("complete") is not True
-            or reference.get("identity_sha256") != identity_digest(ident) or ident.get("weights_sha256") != sig["base_sha256"]
-            or ident.get("data_sha256") != sig["data_sha256"] or ident.get("tokenizer_sha256") != sig["tokenizer_sha256"]
-            or ident.get("world_size") != world
-            or any(v != settings.get(k) for k, v in ident.get("settings", {}).items())):
-        raise ValueError("DPO fixed-reference identity differs from its final checkpoint")
+    signature = checkpoint.get("signature") or {}
+    origin, ancestor = checkpoint.get("origin") or {}, plan.get("sft")
+    moments = (checkpoint.get("optimizer") or {}).get("state") or {}
+    identity = reference.get("identity") or {}
+    enforce([
+        Rule("DPO checkpoint is not the fully completed, finally evaluated state",
+             lambda: matches(checkpoint, {"format": "warpstate-dpo-v1", "completed": True, **want}) and finite(checkpoint["val_loss"])),
+        Rule("DPO checkpoint/settings signatures or dataset counts differ",
+             lambda: matches(signature, {"plan": plan, "settings": settings, "world_size": ranks})
+             and matches(settings_report, {"signature": signature, "total_steps": want["step"], "train_rows": train_rows,
+                                           "val_rows": val_rows})),
+        Rule("DPO data provenance differs from its signature",
+             lambda: matches(data, {"format": "warpstate-posttrain-data-v1", "complete": True,
+                                    "tokenizer_sha256": signature["tokenizer_sha256"],
+                                    "max_length": settings["sequence_length"]})),
+        Rule("DPO did not start from a sealed SFT export",
+             lambda: matches(origin, {"stage": "sft", "weights_sha256": signature["base_sha256"]})),
+        Rule("DPO SFT ancestry differs from the authorized plan",
+             lambda: ancestor is None or matches(origin, {"step": ancestor["step"], "tokens_seen": ancestor["tokens_seen"]})),
+        Rule("DPO optimizer or per-rank RNG state is missing",
+             lambda: len(moments) > 0 and len(checkpoint["rng_by_rank"]) == ranks
+             and all("torch" in stream for stream in checkpoint["rng_by_rank"])),
+        Rule("DPO Adam step differs from the final checkpoint",
+             lambda: all(float(entry["step"]) == want["step"] for entry in moments.values())),
+        Rule("DPO Adam state must retain its original FP32 tensors",
+             lambda: all(entry[key].dtype == torch.float32 for entry in moments.values() for key in ("exp_avg", "exp_avg_sq"))),
+        Rule("DPO model tensors are missing", lambda: len(checkpoint["model"]) > 0),
+        *fp32_tensors(checkpoint.get("model") or {}, "DPO model tensor is not original FP32: {name}"),
+        Rule("DPO completion report differs from its checkpoint",
+             lambda: matches(completion, {"format": "warpstate-dpo-completion-v1", "completed": True, "paused_for_evaluation": True,
+                                          "reference_sha256": signature["reference_sha256"],
+                                          **{key: checkpoint[key] for key in ("step", "total_steps", "sample_cursor", "tokens_seen",
+                                                                              "response_tokens_seen", "val_loss")}})),
+        Rule("DPO final full-holdout evaluation differs from its checkpoint",
+             lambda: matches(evaluation, {"stage": "dpo", "step": want["step"], "full_holdout": True, "evaluated_samples": val_rows,
+                                          "available_validation_samples": val_rows, "objective": settings["objective"],
+                                          **{key: signature[key] for key in IDENTITIES},
+                                          **{key: checkpoint["validation"].get(key) for key in (*SCORES, "evaluated_samples")}})
+             and all(finite(evaluation[key]) for key in SCORES)),
+        Rule("DPO evaluation contains impossible accuracy/NLL",
+             lambda: 0 <= evaluation["reward_accuracy"] <= 1 and evaluation["chosen_nll"] >= 0),
+        Rule("DPO fixed-reference identity differs from its final checkpoint",
+             lambda: matches(reference, {"format": "warpstate-dpo-reference-v1", "complete": True,
+                                         "identity_sha256": identity_digest(identity)})
+             and matches(identity, {"weights_sha256": signature["base_sha256"], "data_sha256": signature["data_sha256"],
+                                    "tokenizer_sha256": signature["tokenizer_sha256"], "world_size": ranks})
+             and matches(settings, identity.get("settings", {}))),
+    ])
     return want
+
+
+def _plain_read_only_file(path: Path) -> bool:
+    mode = path.lstat().st_mode if path.exists() or path.is_symlink() else 0
+    return stat.S_ISREG(mode) and not stat.S_IMODE(mode) & 0o222
 
 
 def verify_dpo_archive(folder, *, expected_checkpoint_hash: str | None = None):
@@ -127,42 +135,41 @@ def verify_dpo_archive(folder, *, expected_checkpoint_hash: str | None = None):
     if folder.is_symlink() or not folder.is_dir():
         raise ValueError(f"Archive is not a regular directory: {folder}")
     entries = A.read_checksums(folder, FILES)
-    if stat.S_IMODE(folder.stat().st_mode) & 0o222 or {p.name for p in folder.iterdir()} != set(FILES) | {"SHA256SUMS"}:
-        raise ValueError("DPO archive directory is not sealed or contains unexpected files")
-    for name in (*FILES, "SHA256SUMS"):
-        path = folder / name
-        if path.is_symlink() or not path.is_file() or stat.S_IMODE(path.stat().st_mode) & 0o222:
-            raise ValueError(f"Archive file missing, not regular or writable: {name}")
-        if name in entries and digest(path) != entries[name]:
-            raise ValueError(f"Archive checksum mismatch: {name}")
-    if expected_checkpoint_hash and entries["checkpoint.pt"] != expected_checkpoint_hash:
-        raise ValueError("Archived DPO state differs from the source checkpoint")
-    checkpoint = torch.load(folder / "checkpoint.pt", map_location="cpu", weights_only=False, mmap=True)
-    plan, data, reference = (read_json(folder / n) for n in ("plan.json", "data-manifest.json", "reference-manifest.json"))
-    validate_state(checkpoint, read_json(folder / "evaluation.json"), read_json(folder / "completion.json"),
-                   read_json(folder / "settings.json"), data, reference, plan)
-    sig = checkpoint["signature"]
-    if (entries["data-manifest.json"] != sig["data_sha256"] or entries["reference-manifest.json"] != sig["reference_sha256"]
-            or entries["tokenizer.model"] != sig["tokenizer_sha256"]):
-        raise ValueError("Archived data/reference/tokenizer hashes differ from checkpoint signatures")
-    for split in ("train", "val"):
-        info = reference["files"][f"{split}.npy"]
-        rows = data["outputs"][f"dpo_{split}.jsonl"]["rows"]
+    members = (*FILES, "SHA256SUMS")
+    enforce([Rule("DPO archive directory is not sealed or contains unexpected files",
+                  lambda: not stat.S_IMODE(folder.stat().st_mode) & 0o222 and sorted(p.name for p in folder.iterdir()) == sorted(members)),
+             *(Rule(f"Archive file missing, not regular or writable: {name}", lambda name=name: _plain_read_only_file(folder / name))
+               for name in members),
+             *(Rule(f"Archive checksum mismatch: {name}", lambda name=name: digest(folder / name) == entries[name]) for name in FILES),
+             Rule("Archived DPO state differs from the source checkpoint",
+                  lambda: not expected_checkpoint_hash or entries["checkpoint.pt"] == expected_checkpoint_hash)])
+    checkpoint = load_tensors(folder / "checkpoint.pt")
+    records = {name: read_json(folder / f"{name}.json") for name in ("plan", "data-manifest", "reference-manifest", "evaluation",
+                                                                      "completion", "settings", "snapshot")}
+    data, reference, metadata = records["data-manifest"], records["reference-manifest"], records["snapshot"]
+    validate_state(checkpoint, records["evaluation"], records["completion"], records["settings"], data, reference, records["plan"])
+    signature = checkpoint["signature"]
+
+    def scores_intact(split: str) -> bool:
+        listed, rows = reference["files"][f"{split}.npy"], data["outputs"][f"dpo_{split}.jsonl"]["rows"]
         values = np.load(folder / f"reference-{split}.npy", allow_pickle=False, mmap_mode="r")
-        if (entries[f"reference-{split}.npy"] != info["sha256"] or info["rows"] != rows or values.shape != (rows, 2)
-                or values.dtype != np.float64 or not np.isfinite(values).all() or not (values <= 0).all()):
-            raise ValueError("Archived fixed-reference score array differs")
-    metadata = read_json(folder / "snapshot.json")
-    if (metadata.get("format") != "warpstate-chat-v1" or metadata.get("stage") != "dpo"
-            or any(metadata.get(k) != checkpoint[k] for k in ("step", "tokens_seen", "val_loss"))
-            or metadata.get("tokenizer_sha256") != entries["tokenizer.model"]
-            or metadata.get("snapshot_sha256") != entries["model.pt"]
-            or metadata.get("snapshot_bytes") != (folder / "model.pt").stat().st_size
-            or metadata.get("source", {}).get("sha256") != entries["checkpoint.pt"]):
-        raise ValueError("DPO model export metadata differs from the full archive")
-    exported = torch.load(folder / "model.pt", map_location="cpu", weights_only=False, mmap=True)
-    if exported.get("inference_only") is not True or exported.get("config") != checkpoint["config"]:
-        raise ValueError("DPO exported model is not an inference snapshot of this run")
+        return (listed["sha256"] == entries[f"reference-{split}.npy"] and listed["rows"] == rows
+                and (values.shape, values.dtype) == ((rows, 2), np.float64)
+                and bool(np.isfinite(values).all()) and bool((values <= 0).all()))      # log-probabilities
+
+    exported = load_tensors(folder / "model.pt")
+    enforce([Rule("Archived data/reference/tokenizer hashes differ from checkpoint signatures",
+                  lambda: (entries["data-manifest.json"], entries["reference-manifest.json"], entries["tokenizer.model"])
+                  == (signature["data_sha256"], signature["reference_sha256"], signature["tokenizer_sha256"])),
+             *(Rule("Archived fixed-reference score array differs", lambda split=split: scores_intact(split)) for split in ("train", "val")),
+             Rule("DPO model export metadata differs from the full archive",
+                  lambda: matches(metadata, {"format": "warpstate-chat-v1", "stage": "dpo", "tokenizer_sha256": entries["tokenizer.model"],
+                                             "snapshot_sha256": entries["model.pt"],
+                                             "snapshot_bytes": (folder / "model.pt").stat().st_size,
+                                             **{key: checkpoint[key] for key in ("step", "tokens_seen", "val_loss")}})
+                  and metadata["source"]["sha256"] == entries["checkpoint.pt"]),
+             Rule("DPO exported model is not an inference snapshot of this run",
+                  lambda: exported["inference_only"] is True and exported["config"] == checkpoint["config"])])
     A.tensors_equal(checkpoint["model"], exported["model"])
     return metadata, entries
 
@@ -183,42 +190,37 @@ Do not modify; copy to continue training or to chat.
 def archive_dpo(run_dir, data_dir, cache_dir, tokenizer, plan_path, destination, revision: str = "") -> dict:
     """Build and publish the sealed archive of a finished DPO run.  The caller holds the locks that
     exclude training; nothing under ``run_dir`` is modified.  Idempotent."""
-    run_dir, data_dir, cache_dir, tokenizer, destination = map(Path, (run_dir, data_dir, cache_dir, tokenizer, destination))
-    source = run_dir / "latest.pt"
+    roots = {"run": Path(run_dir), "data": Path(data_dir), "cache": Path(cache_dir), "tokenizer": Path(tokenizer),
+             "plan": Path(plan_path)}
+    destination, source = Path(destination), Path(run_dir) / "latest.pt"
     if source.is_symlink():
         raise ValueError("The checkpoint must not be a symlink")
     if destination.exists() or destination.is_symlink():
         return verify_dpo_archive(destination, expected_checkpoint_hash=digest(source))[0]
-    before = source.stat()
-    checkpoint = torch.load(source, map_location="cpu", weights_only=False, mmap=True)
-    plan = read_json(plan_path)
-    validate_state(checkpoint, read_json(run_dir / "evaluation.json"), read_json(run_dir / "completion.json"),
-                   read_json(run_dir / "settings.json"), read_json(data_dir / "manifest.json"),
-                   read_json(cache_dir / "manifest.json"), plan)
-    full_hash = digest(source)
+
+    def fingerprint():
+        seen = source.stat()
+        return seen.st_ino, seen.st_size, seen.st_mtime_ns
+
+    first_seen = fingerprint()
+    checkpoint = load_tensors(source)
+    validate_state(checkpoint, *(read_json(roots["run"] / f"{name}.json") for name in ("evaluation", "completion", "settings")),
+                   read_json(roots["data"] / "manifest.json"), read_json(roots["cache"] / "manifest.json"), read_json(plan_path))
+    whole = digest(source)
     destination.parent.mkdir(parents=True, exist_ok=True)
     staging = Path(tempfile.mkdtemp(prefix=".dpo-final-", dir=destination.parent))
-    export_chat_snapshot(checkpoint, staging, tokenizer, {"path": str(source), "sha256": full_hash}, stage="dpo")
-    A.copy_regular(source, staging / "checkpoint.pt")
-    A.copy_regular(tokenizer, staging / "tokenizer.model")
-    A.copy_regular(Path(plan_path), staging / "plan.json")
-    for name in REPORTS:
-        A.copy_regular(run_dir / name, staging / name)
-    A.copy_regular(data_dir / "manifest.json", staging / "data-manifest.json")
-    A.copy_regular(cache_dir / "manifest.json", staging / "reference-manifest.json")
-    for split in ("train", "val"):
-        A.copy_regular(cache_dir / f"{split}.npy", staging / f"reference-{split}.npy")
-    A.write_new(staging / "PROVENANCE.json", json.dumps(dict(
-        created_utc=utc_timestamp(), revision=revision, source=str(source), source_sha256=full_hash,
-        torch_version=torch.__version__, python=sys.version.split()[0], signature=checkpoint["signature"]),
-        indent=2, default=str) + "\n")
-    A.write_new(staging / "ARCHIVE.md", NOTE.format(created=utc_timestamp(), step=checkpoint["step"],
-                                                    val_loss=checkpoint["val_loss"], source=source, sha=full_hash))
-    after = source.stat()
-    if (before.st_ino, before.st_size, before.st_mtime_ns) != (after.st_ino, after.st_size, after.st_mtime_ns):
+    export_chat_snapshot(checkpoint, staging, roots["tokenizer"], {"path": str(source), "sha256": whole}, stage="dpo")
+    for name, (root, leaf) in COPIED.items():
+        A.copy_regular(roots[root] / leaf if leaf else roots[root], staging / name)
+    provenance = {"created_utc": utc_timestamp(), "revision": revision, "source": str(source), "source_sha256": whole,
+                  "torch_version": torch.__version__, "python": sys.version.split()[0], "signature": checkpoint["signature"]}
+    A.write_new(staging / "PROVENANCE.json", json.dumps(provenance, indent=2, default=str) + "\n")
+    A.write_new(staging / "ARCHIVE.md", NOTE.format(created=provenance["created_utc"], step=checkpoint["step"],
+                                                    val_loss=checkpoint["val_loss"], source=source, sha=whole))
+    if fingerprint() != first_seen:
         raise RuntimeError("Checkpoint changed while it was being archived")
     A.seal(staging, FILES)
-    metadata, _ = verify_dpo_archive(staging, expected_checkpoint_hash=full_hash)
+    metadata, _ = verify_dpo_archive(staging, expected_checkpoint_hash=whole)
     A.publish_directory(staging, destination)
     return metadata
 
@@ -226,7 +228,7 @@ def archive_dpo(run_dir, data_dir, cache_dir, tokenizer, plan_path, destination,
 def chat_copy(archive, destination) -> Path:
     """Verified, sealed, physically independent copy of the archive's inference files."""
     archive, destination = Path(archive), Path(destination)
-    metadata, entries = verify_dpo_archive(archive)
+    _, entries = verify_dpo_archive(archive)
     if not destination.exists():
         destination.parent.mkdir(parents=True, exist_ok=True)
         staging = Path(tempfile.mkdtemp(prefix=".chat-", dir=destination.parent))
@@ -234,41 +236,41 @@ def chat_copy(archive, destination) -> Path:
             A.copy_regular(archive / name, staging / name)
         A.seal(staging, CHAT_FILES)
         A.publish_directory(staging, destination)
-    copied = A.read_checksums(destination, CHAT_FILES)
-    for name in CHAT_FILES:
-        if copied[name] != entries[name] or digest(destination / name) != entries[name]:
-            raise ValueError(f"Chat copy differs from its archive: {name}")
-        a, b = (archive / name).stat(), (destination / name).stat()
-        if (a.st_dev, a.st_ino) == (b.st_dev, b.st_ino):
-            raise ValueError(f"Chat copy must not hardlink its archive: {name}")
+    listed = A.read_checksums(destination, CHAT_FILES)
+
+    def separate_file(name: str) -> bool:
+        original, copy = (archive / name).stat(), (destination / name).stat()
+        return (original.st_dev, original.st_ino) != (copy.st_dev, copy.st_ino)
+
+    enforce([*(Rule(f"Chat copy differs from its archive: {name}",
+                    lambda name=name: listed[name] == entries[name] == digest(destination / name)) for name in CHAT_FILES),
+             *(Rule(f"Chat copy must not hardlink its archive: {name}", lambda name=name: separate_file(name)) for name in CHAT_FILES)])
     return destination / "model.pt"
 
 
 def main(argv=None) -> int:
-    p = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    p.add_argument("--config", type=Path, help="DPO plan (with a handoff section naming work/data directories)")
-    p.add_argument("--destination", type=Path)
-    p.add_argument("--archive", type=Path)
-    p.add_argument("--chat-copy", type=Path)
-    p.add_argument("--verify-only", action="store_true")
-    p.add_argument("--revision", default="")
-    a = p.parse_args(argv)
-    if a.chat_copy is not None:
-        model = chat_copy(a.archive, a.chat_copy)
-        print(json.dumps({"snapshot": str(model), "archive": str(a.archive), "independent_copy": True}, indent=2))
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--config", type=Path, help="DPO plan (its handoff section names the work and data directories)")
+    parser.add_argument("--destination", type=Path, help="archive directory (default: <work_dir>-final-archive)")
+    parser.add_argument("--archive", type=Path, help="with --chat-copy: the sealed archive to copy from")
+    parser.add_argument("--chat-copy", type=Path, help="make a sealed chat copy here instead of archiving")
+    parser.add_argument("--verify-only", action="store_true")
+    parser.add_argument("--revision", default="")
+    options = parser.parse_args(argv)
+    if options.chat_copy is not None:
+        model = chat_copy(options.archive, options.chat_copy)
+        print(json.dumps({"snapshot": str(model), "archive": str(options.archive), "independent_copy": True}, indent=2))
         return 0
-    workspace = Path(os.environ.get("WARPSTATE_WORKSPACE", "/workspace/WarpState"))
-    plan = read_json(a.config)
-    handoff = plan["handoff"]
-    work = workspace / handoff["work_dir"]
-    destination = a.destination or (workspace / handoff.get("final_archive_dir", f"{handoff['work_dir']}-final-archive"))
-    if a.verify_only:
+    from .launcher import workspace_root
+    root, section = workspace_root(), read_json(options.config)["handoff"]
+    work = root / section["work_dir"]
+    destination = options.destination or root / section.get("final_archive_dir", section["work_dir"] + "-final-archive")
+    if options.verify_only:
         metadata, _ = verify_dpo_archive(destination)
     else:
-        from ..utils.io import process_lock
-        with process_lock(work / "control/launcher.lock"), process_lock(workspace / "pipeline.lock", shared=True):
-            metadata = archive_dpo(work / "run", workspace / handoff["data_dir"], work / "reference-cache",
-                                   workspace / handoff["tokenizer"], a.config, destination, a.revision)
+        with process_lock(work / "control/launcher.lock"), process_lock(root / "pipeline.lock", shared=True):
+            metadata = archive_dpo(work / "run", root / section["data_dir"], work / "reference-cache", root / section["tokenizer"],
+                                   options.config, destination, options.revision)
     print(json.dumps({"archive": str(destination), "step": metadata["step"], "model_sha256": metadata["snapshot_sha256"]}))
     return 0
 

@@ -26,7 +26,6 @@ from __future__ import annotations
 import argparse
 import contextlib
 import json
-import math
 import signal
 import socket
 import subprocess
@@ -35,11 +34,11 @@ import tempfile
 import time
 import xmlrpc.client
 from pathlib import Path
-from typing import Callable, NamedTuple
 
 import torch
 
 from ..utils.io import LockHeld, atomic_json, digest, process_lock, utc_timestamp
+from ..utils.rules import Rule, enforce, finite, fp32_tensors
 from . import archive as A
 from .launcher import PACKAGE, supervise, training_environment, workspace_path, workspace_root
 
@@ -84,31 +83,8 @@ def load_checkpoint(path):
     return torch.load(path, map_location="cpu", weights_only=False, mmap=True)
 
 
-# --------------------------------------------------------------------------- rules
-class Rule(NamedTuple):
-    message: str
-    holds: Callable[[], bool]
-
-
-def enforce(rules) -> None:
-    """Raise the message of the first rule that does not hold (a rule that cannot even be evaluated -- a missing
-    key -- does not hold)."""
-    for rule in rules:
-        try:
-            fine = bool(rule.holds())
-        except (KeyError, TypeError):
-            fine = False
-        if not fine:
-            raise ValueError(rule.message)
-
-
-def finite(value) -> bool:
-    return isinstance(value, (int, float)) and math.isfinite(value)
-
-
 def fp32_weights(model: dict, what: str):
-    return [Rule(f"Expected {what} FP32 model weights: {name}: {tensor.dtype}",
-                 lambda t=tensor: not t.is_floating_point() or t.dtype == torch.float32) for name, tensor in model.items()]
+    return fp32_tensors(model, "Expected " + what + " FP32 model weights: {name}: {dtype}")
 
 
 def overlaps(a: Path, b: Path) -> bool:
