@@ -327,7 +327,7 @@ std::tuple<at::Tensor, at::Tensor> attn_bwd(const at::Tensor& qkvgu, const at::T
               "attn_bwd: states");
   TORCH_CHECK(writes.scalar_type() == at::kFloat && writes.is_contiguous() && writes.numel() == B * N * H * 4096,
               "attn_bwd: writes");
-  TORCH_CHECK(N <= 64, "attn_bwd: at most 64 chunks per sequence");
+  TORCH_CHECK(N <= 256, "attn_bwd: at most 256 chunks (32768 tokens) per sequence");
   c10::cuda::CUDAGuard guard(qkvgu.device());
   int* err = reinterpret_cast<int*>(const_cast<void*>(opt_ptr(error_flag)));
   at::Tensor dstate = at::empty({B, N, H, 64, 64}, qkvgu.options().dtype(at::kFloat));
