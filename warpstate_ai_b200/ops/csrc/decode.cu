@@ -56,29 +56,35 @@ struct DecodeGemmParams {
   int* error_flag;
 };
 
-template <int BPAD>
+// DEPTH = stages of the TMA ring.  8: one CTA per SM with 192 KiB of tiles in flight.  4: half the ring, so that
+// two CTAs fit on an SM -- the successor of a launch in the dependent chain can then become resident, set up and
+// request its first ring of weights while its predecessor still occupies every SM.  The SwiGLU exchange buffer
+// overlays the first ring stages (the ring is idle once the last MMA has completed).
+template <int BPAD, int DEPTH>
 struct DecodeCfg {
-  static constexpr int STAGES = 8;
+  static constexpr int STAGES = DEPTH;
   static constexpr int X_BYTES = BPAD * dec::BK * 2;
   static constexpr int STAGE_BYTES = dec::W_BYTES + X_BYTES;
   static constexpr int EXCHANGE_BYTES = 64 * BPAD * 4;
-  static constexpr int SMEM = STAGES * STAGE_BYTES + EXCHANGE_BYTES + 1024 + 256;
+  static_assert(EXCHANGE_BYTES <= STAGES * dec::W_BYTES, "the exchange buffer overlays the weight stages");
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256;
   static constexpr int TMEM_COLS = BPAD < 32 ? 32 : BPAD;
+  static constexpr int CTAS_PER_SM = 2 * (SMEM + 1024) <= 233472 ? 2 : 1;
 };
 
 // EPI: 0 = BF16 out, 1 = FP32 split-K partial, 2 = SwiGLU (BF16 activation), 3 = FP32 out
-template <int BPAD, int EPI>
-__global__ void __launch_bounds__(dec::THREADS, 1)
+template <int BPAD, int EPI, int DEPTH>
+__global__ void __launch_bounds__(dec::THREADS, DecodeCfg<BPAD, DEPTH>::CTAS_PER_SM)
 decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                    const DecodeGemmParams p) {
   using namespace dec;
-  using Cfg = DecodeCfg<BPAD>;
+  using Cfg = DecodeCfg<BPAD, DEPTH>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* sW = smem;
   uint8_t* sX = smem + Cfg::STAGES * W_BYTES;
-  float* sG = reinterpret_cast<float*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES + Cfg::EXCHANGE_BYTES);
+  float* sG = reinterpret_cast<float*>(sW);  // written only after the last MMA has read the ring
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
   uint64_t* full = bars;
   uint64_t* empty = bars + Cfg::STAGES;
   uint64_t* tfull = bars + 2 * Cfg::STAGES;
@@ -458,19 +464,35 @@ static cudaError_t launch_chained(void (*kern)(KArgs...), dim3 grid, dim3 block,
   return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 
+template <int BPAD, int EPI, int DEPTH>
+static int launch_decode_gemm_depth(const CUtensorMap& tw, const CUtensorMap& tx, const DecodeGemmParams& p, dim3 grid,
+                                    cudaStream_t stream) {
+  static bool configured = false;
+  auto kern = decode_gemm_kernel<BPAD, EPI, DEPTH>;
+  using Cfg = DecodeCfg<BPAD, DEPTH>;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess) return -20;
+    configured = true;
+  }
+  const cudaError_t err = launch_chained(kern, grid, dim3(dec::THREADS), Cfg::SMEM, stream, tw, tx, p);
+  ws_count_launch();
+  return err == cudaSuccess ? 0 : -21;
+}
+
+// WS_DECODE_STAGES=8 selects the deep ring (one CTA per SM); the default is 4 (two CTAs per SM).
+static int decode_ring_depth() {
+  static const int depth = [] {
+    const char* e = std::getenv("WS_DECODE_STAGES");
+    return e != nullptr && e[0] == '8' ? 8 : 4;
+  }();
+  return depth;
+}
+
 template <int BPAD, int EPI>
 static int launch_decode_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const DecodeGemmParams& p, dim3 grid,
                               cudaStream_t stream) {
-  static bool configured = false;
-  auto kern = decode_gemm_kernel<BPAD, EPI>;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DecodeCfg<BPAD>::SMEM) != cudaSuccess)
-      return -20;
-    configured = true;
-  }
-  const cudaError_t err = launch_chained(kern, grid, dim3(dec::THREADS), DecodeCfg<BPAD>::SMEM, stream, tw, tx, p);
-  ws_count_launch();
-  return err == cudaSuccess ? 0 : -21;
+  return decode_ring_depth() == 8 ? launch_decode_gemm_depth<BPAD, EPI, 8>(tw, tx, p, grid, stream)
+                                  : launch_decode_gemm_depth<BPAD, EPI, 4>(tw, tx, p, grid, stream);
 }
 
 }  // namespace ws
@@ -480,9 +502,16 @@ using namespace ws;
 // Number of K splits ws_decode_gemm uses for an [n x k] weight (the caller sizes the FP32 partial
 // buffer as splits * batch * n floats when the result is > 1).
 extern "C" int ws_decode_gemm_splits(int n, int k) {
+  // CTAs a split-K launch aims for: one per SM by default; WS_DECODE_SPLIT_CTAS overrides (two CTAs fit per SM
+  // with the 4-stage ring)
+  static const int target = [] {
+    const char* e = std::getenv("WS_DECODE_SPLIT_CTAS");
+    const int v = e != nullptr ? std::atoi(e) : 0;
+    return v >= 16 && v <= 1184 ? v : 148;
+  }();
   const int slabs = (n + dec::TM - 1) / dec::TM;
   const int total_kb = (k + dec::BK - 1) / dec::BK;
-  int splits = 148 / (slabs > 0 ? slabs : 1);
+  int splits = target / (slabs > 0 ? slabs : 1);
   if (splits < 1) splits = 1;
   while (splits > 1 && total_kb / splits < 4) --splits;
   const int per = (total_kb + splits - 1) / splits;

@@ -88,6 +88,56 @@ rmsnorm_fwd_kernel(const T* __restrict__ x, const float* __restrict__ col_scale,
   }
 }
 
+// The same with the row held in registers between the two passes (d = 128 * CHUNKS known at compile time):
+// x is read from memory once, and all CHUNKS loads of a lane are in flight together.
+template <typename T, int CHUNKS>
+__global__ void __launch_bounds__(ROW_THREADS)
+rmsnorm_fwd_rows_kernel(const T* __restrict__ x, const float* __restrict__ col_scale,
+                        const float* __restrict__ col_bias, const float* __restrict__ w, float eps, int rows,
+                        T* __restrict__ xmod_out, __nv_bfloat16* __restrict__ z, float* __restrict__ rstd_out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int d = 128 * CHUNKS;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int row = blockIdx.x * ROW_WARPS + warp; row < rows; row += gridDim.x * ROW_WARPS) {
+    const T* xr = x + static_cast<size_t>(row) * d;
+    float4 v[CHUNKS];
+#pragma unroll
+    for (int i = 0; i < CHUNKS; ++i) v[i] = ld4(xr + i * 128 + lane * 4);
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < CHUNKS; ++i) {
+      if (col_scale != nullptr) {
+        const int c = i * 128 + lane * 4;
+        const float4 s = ld4(col_scale + c), b = ld4(col_bias + c);
+        v[i].x = v[i].x * (1.f + s.x) + b.x; v[i].y = v[i].y * (1.f + s.y) + b.y;
+        v[i].z = v[i].z * (1.f + s.z) + b.z; v[i].w = v[i].w * (1.f + s.w) + b.w;
+        if (sizeof(T) == 2) {
+          v[i].x = bf16_round(v[i].x); v[i].y = bf16_round(v[i].y); v[i].z = bf16_round(v[i].z); v[i].w = bf16_round(v[i].w);
+        }
+      }
+      ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / static_cast<float>(d) + eps);
+    if (lane == 0 && rstd_out != nullptr) rstd_out[row] = rstd;
+#pragma unroll
+    for (int i = 0; i < CHUNKS; ++i) {
+      const int c = i * 128 + lane * 4;
+      if (xmod_out != nullptr) st4(xmod_out + static_cast<size_t>(row) * d + c, v[i]);
+      const float4 ww = ld4(w + c);
+      float4 o;
+      if (sizeof(T) == 2) {  // BF16 stream: round x_hat and w first, as an eager BF16 norm does
+        o.x = bf16_round(v[i].x * rstd) * bf16_round(ww.x); o.y = bf16_round(v[i].y * rstd) * bf16_round(ww.y);
+        o.z = bf16_round(v[i].z * rstd) * bf16_round(ww.z); o.w = bf16_round(v[i].w * rstd) * bf16_round(ww.w);
+      } else {
+        o.x = v[i].x * rstd * ww.x; o.y = v[i].y * rstd * ww.y; o.z = v[i].z * rstd * ww.z; o.w = v[i].w * rstd * ww.w;
+      }
+      st4(z + static_cast<size_t>(row) * d + c, o);
+    }
+  }
+}
+
 // --------------------------------------------------------------------------- RMSNorm backward
 // dxn = rstd * (dz*w - x_hat * mean(dz*w*x_hat));  out = (dres + dxn) * (1 + out_scale)
 // dw_partial[block] = sum over the block's rows of dz * x_hat.
@@ -328,6 +378,16 @@ extern "C" int ws_rmsnorm_fwd(const void* x, int x_bf16, const float* col_scale,
                               float* rstd, cudaStream_t stream) {
   if (d % 128 != 0 || rows <= 0) return -1;
   const int grid = row_grid(rows);
+  if (d == 2048) {  // the model's width: the row stays in registers
+    if (x_bf16)
+      launch_dependent(rmsnorm_fwd_rows_kernel<__nv_bfloat16, 16>, dim3(grid), dim3(ROW_THREADS), 0, stream, (const __nv_bfloat16*)x,
+                       col_scale, col_bias, w, eps, rows, (__nv_bfloat16*)xmod_out, (__nv_bfloat16*)z, rstd);
+    else
+      launch_dependent(rmsnorm_fwd_rows_kernel<float, 16>, dim3(grid), dim3(ROW_THREADS), 0, stream, (const float*)x, col_scale,
+                       col_bias, w, eps, rows, (float*)xmod_out, (__nv_bfloat16*)z, rstd);
+    ws_count_launch();
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  }
   if (x_bf16)
     launch_dependent(rmsnorm_fwd_kernel<__nv_bfloat16>, dim3(grid), dim3(ROW_THREADS), 0, stream, (const __nv_bfloat16*)x, col_scale, col_bias, w, eps, rows, d, (__nv_bfloat16*)xmod_out,
         (__nv_bfloat16*)z, rstd);
