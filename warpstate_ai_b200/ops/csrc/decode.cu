@@ -479,11 +479,13 @@ static int launch_decode_gemm_depth(const CUtensorMap& tw, const CUtensorMap& tx
   return err == cudaSuccess ? 0 : -21;
 }
 
-// WS_DECODE_STAGES=8 selects the deep ring (one CTA per SM); the default is 4 (two CTAs per SM).
+// WS_DECODE_STAGES=9 is the deepest ring that fits (217 KiB at batch 64).  WS_DECODE_STAGES=4 selects the shallow ring (two CTAs per SM); the default is 8 (one CTA per SM): measured at
+// batch 64, 2.14 ms per token with 8 stages against 2.42 with 4 (2.21 with twice the K splits) -- the bytes a CTA
+// keeps in flight matter more than letting the next launch become resident early.
 static int decode_ring_depth() {
   static const int depth = [] {
     const char* e = std::getenv("WS_DECODE_STAGES");
-    return e != nullptr && e[0] == '8' ? 8 : 4;
+    return e != nullptr && e[0] == '4' ? 4 : e != nullptr && e[0] == '9' ? 9 : 8;
   }();
   return depth;
 }
@@ -491,8 +493,11 @@ static int decode_ring_depth() {
 template <int BPAD, int EPI>
 static int launch_decode_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const DecodeGemmParams& p, dim3 grid,
                               cudaStream_t stream) {
-  return decode_ring_depth() == 8 ? launch_decode_gemm_depth<BPAD, EPI, 8>(tw, tx, p, grid, stream)
-                                  : launch_decode_gemm_depth<BPAD, EPI, 4>(tw, tx, p, grid, stream);
+  switch (decode_ring_depth()) {
+    case 4: return launch_decode_gemm_depth<BPAD, EPI, 4>(tw, tx, p, grid, stream);
+    case 9: return launch_decode_gemm_depth<BPAD, EPI, 9>(tw, tx, p, grid, stream);
+    default: return launch_decode_gemm_depth<BPAD, EPI, 8>(tw, tx, p, grid, stream);
+  }
 }
 
 }  // namespace ws
