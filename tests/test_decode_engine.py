@@ -239,3 +239,43 @@ def test_pack_weight_round_trip_and_tile_order():
     assert torch.equal(unpack_weight(p2, 256, 64, swiglu=True), ug)
     with pytest.raises(ValueError):
         pack_weight(torch.randn(2 * 96, 64), swiglu=True)
+
+
+@pytest.mark.gpu
+def test_greedy_decode_without_the_host_matches_the_host_driven_loop():
+    """`decode_greedy` (token pick, hand-back and position counter inside the step graph; steps queued without any
+    synchronisation) against arg-max on the host after every `step`, across a chunk boundary and across a read-out of
+    the history buffer: the same tokens, and the engines end in the same state."""
+    from warpstate_ai_b200 import WarpStateConfig, WarpStateLM
+    from warpstate_ai_b200.serve.engine import DecodeEngine
+    torch.manual_seed(3)
+    cfg = WarpStateConfig(vocab_size=512, d_model=128, n_heads=2, n_cores=2, logical_depth=3, ffn_hidden=256, chunk_size=128,
+                          gradient_checkpointing=False, parallel_memory=True)
+    with torch.device("cuda"):
+        model = WarpStateLM(cfg)
+    model.eval().requires_grad_(False)
+    prompt = torch.randint(0, 512, (5, 100), device="cuda")
+    steps = 70                                  # positions 100 .. 169: crosses the chunk boundary at 128
+    host = DecodeEngine(model, dtype=torch.bfloat16)
+    token = torch.argmax(host.prefill(prompt), dim=-1)
+    first = token.clone()
+    want = []
+    for _ in range(steps):
+        token = torch.argmax(host.step(token), dim=-1)
+        want.append(token)
+    want = torch.stack(want, dim=1)
+    device_side = DecodeEngine(model, dtype=torch.bfloat16)
+    device_side.GREEDY_CAPACITY = 32            # three read-outs of the history buffer
+    assert torch.equal(torch.argmax(device_side.prefill(prompt), dim=-1), first)
+    events = []
+    got = device_side.decode_greedy(first, steps, events)
+    torch.cuda.synchronize()
+    assert got.shape == (5, steps) and torch.equal(got, want)
+    assert len(events) == steps + 1 and all(a.elapsed_time(b) > 0 for a, b in zip(events, events[1:]))
+    assert device_side.pos == host.pos == (100 + steps) % 128 and int(device_side.pos_dev) == device_side.pos
+    for mine, theirs in zip(device_side.states, host.states):
+        assert torch.equal(mine.fast, theirs.fast) and torch.equal(mine.k, theirs.k)
+    counters = device_side.graph_counters.as_dict()
+    assert counters["replay_calls"] >= steps and counters["eager_steps"] == 0
+    # a host-driven step after the device-driven run continues from the same position
+    assert torch.equal(torch.argmax(device_side.step(got[:, -1]), dim=-1), torch.argmax(host.step(want[:, -1]), dim=-1))

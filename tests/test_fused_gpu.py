@@ -69,6 +69,26 @@ def test_embedding_forward_backward_deterministic(ops):
     assert torch.allclose(g1, ref, rtol=1e-4, atol=1e-4)
 
 
+def test_embedding_backward_with_a_run_of_thousands_of_equal_ids(ops):
+    """A fine-tuning batch is mostly padding: one token id thousands of times.  The run is shared by the column
+    chunks' warps; the sum keeps the row order (bitwise repeatable) and matches an FP64 scatter-add."""
+    torch.manual_seed(1)
+    table_rows, d = 512, 2048
+    ids = torch.randint(0, table_rows, (8192,), device="cuda")
+    ids[1000:7000] = 3                               # 6000 padding-like positions, 2192 scattered ones
+    ids[-1] = 511
+    dx = torch.randn(8192, d, device="cuda")
+    g1 = torch.randn(table_rows, d, device="cuda")   # accumulates into what is there
+    g2 = g1.clone()
+    start = g1.clone()
+    ops.embed_bwd(dx, ids, g1)
+    ops.embed_bwd(dx, ids, g2)
+    assert torch.equal(g1, g2)
+    ref = start.double().index_add_(0, ids, dx.double())
+    assert torch.allclose(g1.double(), ref, rtol=1e-5, atol=2e-3)      # 6000 FP32 additions in sequence
+    assert float((g1.double() - ref)[torch.arange(table_rows, device="cuda") != 3].abs().max()) < 1e-4
+
+
 def test_adamw_matches_torch(ops):
     from warpstate_ai_b200.optim import ArenaAdamW, ParamArena
     torch.manual_seed(0)

@@ -31,7 +31,8 @@ def combine_ranks(per_rank: list[dict]) -> dict:
             "prefill_tokens_per_second": sum(r["prefill_tokens_per_second"] for r in per_rank),
             "p50_latency_seconds": max(r["p50_latency_seconds"] for r in per_rank),
             "prefill_seconds": max(r["prefill_seconds"] for r in per_rank),
-            "peak_mem_gib": max(r["peak_mem_gib"] for r in per_rank)}
+            "peak_mem_gib": max(r["peak_mem_gib"] for r in per_rank),
+            "host_driven_p50_seconds": max(r["host_driven_p50_seconds"] for r in per_rank)}
 
 
 def reference_generate_batch(model, prompts: torch.Tensor, new_tokens: int) -> dict:
@@ -143,10 +144,14 @@ def main() -> None:
         with collect_graph_diagnostics(engine) as diagnostics:
             result = generate_batch(engine, prompts, args.new_tokens)
         graph_report = diagnostics.snapshot()
+        # the same engine driven token by token from the host (arg-max on the host stream, one synchronisation per
+        # token, wall clock): what a caller that inspects every token before asking for the next one sees
+        host_driven = generate_batch(engine, prompts[:, :256], 64, synchronous=True)["p50_latency_seconds"]
     mine = {"tokens_per_second": result["tokens_per_second"], "p50_latency_seconds": result["p50_latency_seconds"],
             "prefill_tokens_per_second": args.batch * args.prompt / result["prefill_seconds"],
             "prefill_seconds": result["prefill_seconds"],
-            "peak_mem_gib": torch.cuda.max_memory_allocated(device) / 2 ** 30}
+            "peak_mem_gib": torch.cuda.max_memory_allocated(device) / 2 ** 30,
+            "host_driven_p50_seconds": host_driven if args.impl == "ours" else result["p50_latency_seconds"]}
     launches = _ext.launch_count() - before
     if world > 1:
         gathered = [None] * world
@@ -162,6 +167,8 @@ def main() -> None:
             "unit": "tokens/s", "n_gpus": world, "batch_per_gpu": args.batch, "batch": args.batch * world,
             "prompt_tokens": args.prompt, "new_tokens": args.new_tokens,
             "p50_token_latency_ms": total["p50_latency_seconds"] * 1e3,
+            "latency_timing": result.get("timing", "host clock, one synchronisation per token"),
+            "p50_token_latency_ms_host_driven": total["host_driven_p50_seconds"] * 1e3,
             "prefill_tokens_per_second": total["prefill_tokens_per_second"],
             "prefill_seconds": total["prefill_seconds"], "cuda_graph": not args.no_graph,
             "own_kernel_launches": launches, "cuda_graph_diagnostics": graph_report if args.impl == "ours" else None,

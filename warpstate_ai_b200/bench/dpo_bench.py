@@ -127,6 +127,9 @@ def main(argv=None) -> int:
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--beta", type=float, default=0.1)
     ap.add_argument("--device", choices=["cuda", "cpu"], default="cuda" if torch.cuda.is_available() else "cpu")
+    ap.add_argument("--profile", action="store_true",
+                    help="ours: after the timed updates, run one more under torch.profiler and print the kernels that "
+                         "carry its device time (rank 0)")
     a = ap.parse_args(argv)
     import torch.distributed as dist
     from .. import WarpStateLM, warpstate_2b, warpstate_smoke
@@ -203,6 +206,17 @@ def main(argv=None) -> int:
     if world > 1:
         dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
     seconds = float(elapsed) / a.steps
+    if a.profile and a.device == "cuda":
+        from torch.profiler import ProfilerActivity, profile
+        with profile(activities=[ProfilerActivity.CUDA]) as trace:
+            DPO.training_update(trainer, micro, global_pairs, settings, 5e-7, resident=reference)
+            torch.cuda.synchronize(device)
+        if rank == 0:
+            rows = sorted(trace.key_averages(), key=lambda e: -e.device_time_total)
+            busy = sum(e.device_time_total for e in rows)
+            print(json.dumps({"profiled_update_device_ms": busy / 1e3,
+                              "kernels": [{"name": e.key[:90], "calls": e.count, "ms": round(e.device_time_total / 1e3, 2)}
+                                          for e in rows[:25]]}), flush=True)
     if rank == 0:
         what = "policy + resident BF16 reference" if a.reference == "resident" else "policy update, cached reference scores"
         print(json.dumps({"metric": f"DPO pairs/sec ({what})", "impl": "ours", "value": global_pairs / seconds,

@@ -738,6 +738,31 @@ void decode_attn(const at::Tensor& qkvgu, at::Tensor kc, at::Tensor vc, at::Tens
                           (int)H, (int)d, y.data_ptr(), cur_stream()), "decode_attn");
 }
 
+void decode_pick(const at::Tensor& logits, at::Tensor token, const c10::optional<at::Tensor>& history, at::Tensor cursor,
+                 at::Tensor pos) {
+  TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.dim() == 2 && logits.is_contiguous() &&
+              logits.size(1) % 4 == 0, "decode_pick: logits must be contiguous FP32 [batch, vocab], vocab a multiple of 4");
+  const int64_t batch = logits.size(0);
+  TORCH_CHECK(token.is_cuda() && token.scalar_type() == at::kLong && token.is_contiguous() && token.numel() == batch,
+              "decode_pick: token must be int64 [batch]");
+  TORCH_CHECK(cursor.is_cuda() && cursor.scalar_type() == at::kLong && cursor.is_contiguous() && cursor.numel() == 2,
+              "decode_pick: cursor must be two int64 words");
+  TORCH_CHECK(pos.is_cuda() && pos.scalar_type() == at::kLong && pos.numel() == 1, "decode_pick: pos must be an int64 scalar");
+  long long* hist = nullptr;
+  int capacity = 0;
+  if (history.has_value()) {
+    TORCH_CHECK(history->is_cuda() && history->scalar_type() == at::kLong && history->is_contiguous() && history->dim() == 2 &&
+                history->size(0) == batch, "decode_pick: history must be contiguous int64 [batch, capacity]");
+    hist = reinterpret_cast<long long*>(history->data_ptr<int64_t>());
+    capacity = (int)history->size(1);
+  }
+  c10::cuda::CUDAGuard guard(logits.device());
+  check_rc(ws_decode_pick(logits.data_ptr<float>(), (int)batch, (int)logits.size(1),
+                          reinterpret_cast<long long*>(token.data_ptr<int64_t>()), hist, capacity,
+                          reinterpret_cast<long long*>(cursor.data_ptr<int64_t>()),
+                          reinterpret_cast<long long*>(pos.data_ptr<int64_t>()), cur_stream()), "decode_pick");
+}
+
 }  // namespace
 
 TORCH_LIBRARY(ws_b200, m) {
@@ -748,6 +773,7 @@ TORCH_LIBRARY(ws_b200, m) {
   m.def("decode_gemm(Tensor w, Tensor x, int n, int epilogue, Tensor(a!) out, Tensor(b!)? error_flag, bool packed=False) -> ()");
   m.def("decode_reduce_norm(Tensor(a!) x, Tensor? partial, Tensor? token, Tensor? table, Tensor? scale, Tensor? bias, "
         "Tensor w, float eps, Tensor(b!)? out) -> ()");
+  m.def("decode_pick(Tensor logits, Tensor(a!) token, Tensor(b!)? history, Tensor(c!) cursor, Tensor(d!) pos) -> ()");
   m.def("decode_attn(Tensor qkvgu, Tensor(a!) kc, Tensor(b!) vc, Tensor(c!) uc, Tensor mixed, Tensor rope, Tensor pos, "
         "int H, Tensor(d!) y) -> ()");
   m.def("rmsnorm_fwd(Tensor x, Tensor? col_scale, Tensor? col_bias, Tensor w, float eps, bool want_xmod) -> (Tensor, Tensor, Tensor)");
@@ -803,6 +829,7 @@ TORCH_LIBRARY_IMPL(ws_b200, CUDA, m) {
   m.impl("gather_cast_linear", &gather_cast_linear);
   m.impl("decode_reduce_norm", &decode_reduce_norm);
   m.impl("decode_attn", &decode_attn);
+  m.impl("decode_pick", &decode_pick);
   m.impl("grad_weight_group", &grad_weight_group);
   m.impl("rmsnorm_fwd", &rmsnorm_fwd);
   m.impl("rmsnorm_bwd", &rmsnorm_bwd);

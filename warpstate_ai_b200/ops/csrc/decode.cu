@@ -325,6 +325,24 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ qkvgu, __nv_bfloat16* __res
   pos = pos < 0 ? 0 : (pos >= C ? C - 1 : pos);
   const __nv_bfloat16* row = qkvgu + static_cast<size_t>(b) * 5 * d + h * HD;
   const size_t cache = (static_cast<size_t>(b) * H + h) * C * HD;
+  // Thread (rg, jg) owns columns 8*jg .. 8*jg+7 of the rows rg, rg+16, ... of the K and V caches and of M: a warp
+  // instruction reads four whole 128-byte rows.  Every load the step needs from the caches is issued here, before
+  // the RoPE of the new token, so that the three dependent phases below (scores, softmax, P.V) wait for memory once.
+  const int jg = tid & 7, rg = tid >> 3;
+  uint4 kreg[C / 16], vreg[C / 16], mreg[HD / 16];
+#pragma unroll
+  for (int it = 0; it < C / 16; ++it) {
+    const int c = rg + it * 16;
+    if (c < pos) {
+      kreg[it] = *reinterpret_cast<const uint4*>(kc + cache + static_cast<size_t>(c) * HD + jg * 8);
+      vreg[it] = *reinterpret_cast<const uint4*>(vc + cache + static_cast<size_t>(c) * HD + jg * 8);
+    } else if (c == pos) {
+      vreg[it] = *reinterpret_cast<const uint4*>(row + 2 * d + jg * 8);  // the new token's own value row
+    }
+  }
+  const __nv_bfloat16* mbase = mixed + (static_cast<size_t>(b) * H + h) * HD * HD;
+#pragma unroll
+  for (int it = 0; it < HD / 16; ++it) mreg[it] = *reinterpret_cast<const uint4*>(mbase + (rg + it * 16) * HD + jg * 8);
   // RoPE (adjacent pairs) of q and k; append k, v, u at `pos`
   if (tid < 32) {
     const float2 cs = rope[pos * 32 + tid];
@@ -347,28 +365,34 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ qkvgu, __nv_bfloat16* __res
         *reinterpret_cast<const __nv_bfloat162*>(row + 4 * d + 2 * t);
   }
   __syncthreads();
-  // scores: thread c owns key c
-  float score = -INFINITY;
-  if (tid <= pos) {
-    float acc = 0.f;
-    if (tid == pos) {
+  // scores: the eight lanes of a row group each hold an eighth of q . k[c]; key `pos` is the new token's own
+  {
+    float qv[8];
 #pragma unroll
-      for (int i = 0; i < HD; ++i) acc += sq[i] * sk[i];
-    } else {
-      const uint4* kr = reinterpret_cast<const uint4*>(kc + cache + static_cast<size_t>(tid) * HD);
+    for (int t = 0; t < 8; ++t) qv[t] = sq[jg * 8 + t];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const uint4 v = kr[j];
-        const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&v);
+    for (int it = 0; it < C / 16; ++it) {
+      const int c = rg + it * 16;
+      float acc = 0.f;
+      if (c < pos) {
+        const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&kreg[it]);
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
           const float2 f = __bfloat1622float2(pb[t]);
-          acc += sq[j * 8 + 2 * t] * f.x + sq[j * 8 + 2 * t + 1] * f.y;
+          acc += qv[2 * t] * f.x + qv[2 * t + 1] * f.y;
         }
+      } else if (c == pos) {
+#pragma unroll
+        for (int t = 0; t < 8; ++t) acc += qv[t] * sk[jg * 8 + t];
       }
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+      if (jg == 0) sp[c] = acc * 0.125f;
     }
-    score = acc * 0.125f;
   }
+  __syncthreads();
+  const float score = tid <= pos ? sp[tid] : -INFINITY;
   float m = score;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
@@ -384,11 +408,9 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ qkvgu, __nv_bfloat16* __res
   sp[tid] = e;
   __syncthreads();
   const float inv = 1.f / (sred[0] + sred[1] + sred[2] + sred[3]);
-  // local = sum_c p[c] V[c] and memory = q . M in one pass of wide loads: thread (rg, jg) owns
-  // columns 8*jg .. 8*jg+7 and the rows rg, rg+16, ... of V (keys) and of M; the 16 row groups
-  // are then summed through shared memory.
+  // local = sum_c p[c] V[c] and memory = q . M from the rows already in registers; the 16 row groups are then
+  // summed through shared memory.
   {
-    const int jg = tid & 7, rg = tid >> 3;
     float accl[8], accm[8];
 #pragma unroll
     for (int t = 0; t < 8; ++t) { accl[t] = 0.f; accm[t] = 0.f; }
@@ -396,9 +418,7 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ qkvgu, __nv_bfloat16* __res
     for (int it = 0; it < C / 16; ++it) {
       const int c = rg + it * 16;
       if (c <= pos) {
-        const uint4 v = (c == pos) ? *reinterpret_cast<const uint4*>(row + 2 * d + jg * 8)
-                                   : *reinterpret_cast<const uint4*>(vc + cache + static_cast<size_t>(c) * HD + jg * 8);
-        const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&v);
+        const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&vreg[it]);
         const float pc = sp[c];
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
@@ -408,13 +428,10 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ qkvgu, __nv_bfloat16* __res
         }
       }
     }
-    const __nv_bfloat16* mbase = mixed + (static_cast<size_t>(b) * H + h) * HD * HD;
 #pragma unroll
     for (int it = 0; it < HD / 16; ++it) {
-      const int i = rg + it * 16;
-      const uint4 v = *reinterpret_cast<const uint4*>(mbase + i * HD + jg * 8);
-      const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&v);
-      const float qi = sq[i];
+      const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&mreg[it]);
+      const float qi = sq[rg + it * 16];
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
         const float2 f = __bfloat1622float2(pb[t]);
@@ -440,6 +457,70 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ qkvgu, __nv_bfloat16* __res
     mem *= 0.125f;
     const float g = sigmoid_fast(__bfloat162float(row[3 * d + tid]));
     y[static_cast<size_t>(b) * d + h * HD + tid] = __float2bfloat16(g * local + (1.f - g) * mem);
+  }
+}
+
+// --------------------------------------------------------------------------- greedy pick
+// One CTA per sequence: token[b] = argmax of logits[b, :] (the lowest index among equal maxima, as torch.argmax
+// picks), written where the next step's embedding gather reads it and into column `*cursor` of the history
+// [batch, capacity]; CTA 0 then advances the in-chunk position and the cursor.  With this kernel as the last node of
+// the step graph a greedy decode needs nothing from the host between steps.
+__global__ void __launch_bounds__(256)
+decode_pick_kernel(const float* __restrict__ logits, int vocab, long long* __restrict__ token,
+                   long long* __restrict__ history, int capacity, long long* __restrict__ cursor,
+                   long long* __restrict__ pos) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float best_v[8];
+  __shared__ int best_i[8];
+  const int b = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const float* row = logits + static_cast<size_t>(b) * vocab;
+  float v = -INFINITY;
+  int at = 0x7fffffff;
+  for (int c = threadIdx.x * 4; c < vocab; c += 256 * 4) {  // vocab % 4 == 0 (checked by the caller)
+    const float4 q = *reinterpret_cast<const float4*>(row + c);
+    const float e[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (e[j] > v || (e[j] == v && c + j < at)) {
+        v = e[j];
+        at = c + j;
+      }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, at, o);
+    if (ov > v || (ov == v && oi < at)) {
+      v = ov;
+      at = oi;
+    }
+  }
+  if (lane == 0) {
+    best_v[warp] = v;
+    best_i[warp] = at;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w)
+      if (best_v[w] > v || (best_v[w] == v && best_i[w] < at)) {
+        v = best_v[w];
+        at = best_i[w];
+      }
+    if (at == 0x7fffffff) at = 0;  // a row of NaNs: any token, as long as it is a valid one
+    const long long column = *cursor;
+    token[b] = at;
+    if (history != nullptr && column < capacity) history[static_cast<size_t>(b) * capacity + column] = at;
+  }
+  // every CTA has read the cursor before CTA 0 may advance it: CTA 0 waits for the others' arrival count
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned arrived = atomicAdd(reinterpret_cast<unsigned*>(cursor + 1), 1u) + 1u;
+    if (arrived == gridDim.x) {
+      *reinterpret_cast<unsigned*>(cursor + 1) = 0u;
+      *cursor += 1;
+      *pos += 1;
+    }
   }
 }
 
@@ -586,6 +667,17 @@ extern "C" int ws_decode_attn(const void* qkvgu, void* kc, void* vc, void* uc, c
       static_cast<__nv_bfloat16*>(kc), static_cast<__nv_bfloat16*>(vc), static_cast<__nv_bfloat16*>(uc),
       static_cast<const __nv_bfloat16*>(mixed), reinterpret_cast<const float2*>(rope), pos, H, d,
       static_cast<__nv_bfloat16*>(y));
+  ws_count_launch();
+  return err == cudaSuccess ? 0 : -21;
+}
+
+// token [batch] int64 = argmax(logits [batch, vocab] FP32); also stored in history[:, cursor[0]] (history may be
+// NULL); then pos[0] += 1 and cursor[0] += 1.  cursor is two int64 words: the column, and a word of scratch (zero).
+extern "C" int ws_decode_pick(const float* logits, int batch, int vocab, long long* token, long long* history,
+                              int capacity, long long* cursor, long long* pos, cudaStream_t stream) {
+  if (batch <= 0 || vocab <= 0 || vocab % 4 != 0) return -1;
+  const cudaError_t err = launch_chained(decode_pick_kernel, dim3(batch), dim3(256), 0, stream, logits, vocab, token, history,
+                                         capacity, cursor, pos);
   ws_count_launch();
   return err == cudaSuccess ? 0 : -21;
 }

@@ -334,32 +334,56 @@ embed_fwd_kernel(const long long* __restrict__ ids, const TT* __restrict__ table
 }
 
 // Deterministic embedding backward: rows were sorted by token id on the host side of the op
-// (`order` = argsort of ids, `seg_start` = first position of each distinct id in that order).
-// One warp adds all gradient rows of one distinct token in order and accumulates into the
-// FP32 gradient table - no atomics, run-to-run identical.  The runs of equal ids are found on the
-// device: a warp looks at position p of the sorted ids and works only if a run starts there, so the
-// host needs no count of distinct tokens (which would cost a device-to-host read, and with it a
-// drained launch queue, in every micro-batch).
+// (`order` = argsort of ids).  The unit of work is (position p of the sorted ids, 128-column chunk): a warp
+// works only if a run of equal ids starts at p, and then adds that chunk of all gradient rows of the run, in
+// order, into the FP32 gradient table - no atomics, run-to-run identical.  A run is therefore shared by d / 128
+// warps, which keeps a run of thousands of equal ids (the padding of a fine-tuning batch) from being one
+// warp's serial work.  The runs are found on the device, so the host needs no count of distinct tokens (which
+// would cost a device-to-host read, and with it a drained launch queue, in every micro-batch).
 template <typename T>
 __global__ void __launch_bounds__(ROW_THREADS)
 embed_bwd_kernel(const T* __restrict__ dx, const long long* __restrict__ sorted_ids,
                  const long long* __restrict__ order, int rows, int d, int vocab, float* __restrict__ grad_table) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int begin = blockIdx.x * ROW_WARPS + warp; begin < rows; begin += gridDim.x * ROW_WARPS) {
+  const int chunks = d / 128;
+  const long long units = static_cast<long long>(rows) * chunks;
+  for (long long unit = blockIdx.x * ROW_WARPS + warp; unit < units; unit += static_cast<long long>(gridDim.x) * ROW_WARPS) {
+    const int begin = static_cast<int>(unit / chunks);
+    const int c = static_cast<int>(unit % chunks) * 128 + lane * 4;
     const long long id = sorted_ids[begin];
     if (begin > 0 && sorted_ids[begin - 1] == id) continue;  // not the head of a run
     if (id < 0 || id >= vocab) continue;
+    // the end of the run, 32 positions per step
     int end = begin + 1;
-    while (end < rows && sorted_ids[end] == id) ++end;
-    float* dst = grad_table + static_cast<size_t>(id) * d;
-    for (int c = lane * 4; c < d; c += 128) {
-      float4 s = ld4(dst + c);
-      for (int j = begin; j < end; ++j) {
-        const float4 v = ld4(dx + static_cast<size_t>(order[j]) * d + c);
-        s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    for (;;) {
+      const int at = end + lane;
+      const bool same = at < rows && sorted_ids[at] == id;
+      const unsigned mask = __ballot_sync(0xffffffffu, same);
+      if (mask == 0xffffffffu) {
+        end += 32;
+        continue;
       }
-      st4(dst + c, s);
+      end += __ffs(~mask) - 1;
+      break;
     }
+    float* dst = grad_table + static_cast<size_t>(id) * d + c;
+    float4 s = ld4(dst);
+    int j = begin;
+    for (; j + 4 <= end; j += 4) {  // four independent loads in flight; the sum keeps the row order
+      const float4 v0 = ld4(dx + static_cast<size_t>(order[j]) * d + c);
+      const float4 v1 = ld4(dx + static_cast<size_t>(order[j + 1]) * d + c);
+      const float4 v2 = ld4(dx + static_cast<size_t>(order[j + 2]) * d + c);
+      const float4 v3 = ld4(dx + static_cast<size_t>(order[j + 3]) * d + c);
+      s.x += v0.x; s.y += v0.y; s.z += v0.z; s.w += v0.w;
+      s.x += v1.x; s.y += v1.y; s.z += v1.z; s.w += v1.w;
+      s.x += v2.x; s.y += v2.y; s.z += v2.z; s.w += v2.w;
+      s.x += v3.x; s.y += v3.y; s.z += v3.z; s.w += v3.w;
+    }
+    for (; j < end; ++j) {
+      const float4 v = ld4(dx + static_cast<size_t>(order[j]) * d + c);
+      s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    }
+    st4(dst, s);
   }
 }
 
@@ -476,8 +500,8 @@ extern "C" int ws_embed_fwd(const long long* ids, const void* table, int table_b
 
 extern "C" int ws_embed_bwd(const void* dx, int dx_bf16, const long long* sorted_ids, const long long* order, int rows,
                             int d, int vocab, float* grad_table, cudaStream_t stream) {
-  if (d % 4 != 0 || rows <= 0 || vocab <= 0) return -1;
-  const int grid = row_grid(rows);
+  if (d % 128 != 0 || rows <= 0 || vocab <= 0) return -1;
+  const int grid = 148 * 8;
   if (dx_bf16)
     embed_bwd_kernel<__nv_bfloat16><<<grid, ROW_THREADS, 0, stream>>>((const __nv_bfloat16*)dx, sorted_ids, order, rows,
                                                                       d, vocab, grad_table);

@@ -78,6 +78,12 @@ int ws_decode_reduce_norm(float* x, const float* partial, int splits, const long
 int ws_decode_attn(const void* qkvgu, void* kc, void* vc, void* uc, const void* mixed, const float* rope,
                    const long long* pos, int batch, int H, int d, void* y, cudaStream_t stream);
 
+// Greedy pick at the end of a decode step: token[b] = argmax(logits[b, :]), also written to history[b, cursor[0]]
+// (history [batch, capacity] int64, may be NULL); then pos[0] += 1 and cursor[0] += 1.  cursor: two int64 words
+// (column, zeroed scratch).  vocab % 4 == 0.
+int ws_decode_pick(const float* logits, int batch, int vocab, long long* token, long long* history, int capacity,
+                   long long* cursor, long long* pos, cudaStream_t stream);
+
 // Kernel choice for problems with >= 256 rows: 1 = CTA-pair (cta_group::2) kernel, 0 = single-CTA
 // kernel, -1 = the process default (pair unless WS_GEMM_PAIR=0 is in the environment).
 void ws_gemm_set_pair_mode(int mode);

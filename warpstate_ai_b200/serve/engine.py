@@ -44,6 +44,8 @@ class DepthState:
 
 
 class DecodeEngine:
+    GREEDY_CAPACITY = 1024    # tokens per sequence the history buffer of `decode_greedy` holds between read-outs
+
     def __init__(self, model, dtype: torch.dtype = torch.bfloat16, use_cuda_graph: bool | None = None,
                  use_kernels: bool = True, pack_weights: bool = False):
         if model.training:
@@ -79,6 +81,7 @@ class DecodeEngine:
         self.batch = 0
         self.pos = 0            # host copy of the in-chunk position
         self._graph = None
+        self._greedy_graph = None
         from .graph_stats import GraphCounters
         self.graph_counters = GraphCounters()
 
@@ -105,10 +108,12 @@ class DecodeEngine:
         self.pos_dev = torch.zeros((), dtype=torch.long, device=self.device)
         self.token_buf = torch.zeros(batch, dtype=torch.long, device=self.device)
         self.logits_buf = None
-        if self._graph is not None:
-            self.graph_counters.invalidations += 1
-        self._graph = None
+        self.graph_counters.invalidations += (self._graph is not None) + (self._greedy_graph is not None)
+        self._graph = self._greedy_graph = None
         self._kbufs = self._kernel_buffers(batch) if self._kernels_usable(batch) else None
+        # greedy run-ahead decode: chosen tokens land in `history[:, cursor[0]]`; cursor[1] is kernel scratch
+        self.history = torch.zeros(batch, self.GREEDY_CAPACITY, dtype=torch.long, device=self.device)
+        self.cursor = torch.zeros(2, dtype=torch.long, device=self.device)
 
     # ------------------------------------------------------------------ kernel path
     def _kernels_usable(self, batch: int) -> bool:
@@ -248,6 +253,65 @@ class DecodeEngine:
             self._end_of_chunk()
             self.pos = 0
         return logits
+
+    # ------------------------------------------------------------------ greedy decode without the host
+    @torch.no_grad()
+    def decode_greedy(self, token: torch.Tensor, steps: int, events: list | None = None) -> torch.Tensor:
+        """Feed ``token [B]``, then ``steps`` times pick the arg-max token and feed it back: ``[B, steps]``.
+
+        On the kernel path the pick, the hand-back of the token, the history write and the position counter are the
+        last node of the step graph (`decode_pick_kernel`), so consecutive steps are queued without any host
+        synchronisation; the host only counts positions to run the chunk-boundary state update in stream order.
+        ``events``, when given, receives one CUDA event before the first step and one after every step.
+        Elsewhere (CPU, kernels or graphs off) it is the plain loop over `step`."""
+        token = token.reshape(-1).to(self.device).contiguous()
+        if self.states is None or token.shape[0] != self.batch:
+            self.new_state(token.shape[0])
+        if self._kbufs is None or not self.use_graph:
+            columns = []
+            for _ in range(steps):
+                token = torch.argmax(self.step(token), dim=-1)
+                columns.append(token)
+            return torch.stack(columns, dim=1) if columns else token.new_zeros(token.shape[0], 0)
+        stream = torch.cuda.current_stream(self.device)
+        self.token_buf.copy_(token)
+        self.pos_dev.fill_(self.pos)
+        if events is not None:
+            events.append(torch.cuda.Event(enable_timing=True))
+            events[-1].record(stream)
+        pieces, done = [], 0
+        while done < steps:
+            run = min(steps - done, self.GREEDY_CAPACITY)
+            self.cursor.zero_()
+            for _ in range(run):
+                if self._greedy_graph is None:
+                    self._capture_greedy()
+                self._greedy_graph.replay()
+                self.graph_counters.replay_calls += 1
+                self.graph_counters.replay_calls_by_batch[self.batch] += 1
+                self.pos += 1
+                if self.pos == self.chunk:      # the graph left pos_dev at `chunk`: fold the chunk, start the next
+                    self._end_of_chunk()
+                    self.pos = 0
+                    self.pos_dev.zero_()
+                if events is not None:
+                    events.append(torch.cuda.Event(enable_timing=True))
+                    events[-1].record(stream)
+            pieces.append(self.history[:, :run].clone())
+            done += run
+        return torch.cat(pieces, dim=1) if len(pieces) != 1 else pieces[0]
+
+    def _capture_greedy(self) -> None:
+        if self._graph is None:
+            self._capture()                     # warms the step's kernels up on a side stream
+        from ..ops import _ext
+        self._greedy_graph = torch.cuda.CUDAGraph()
+        launched = _ext.launch_count()
+        with torch.cuda.graph(self._greedy_graph):
+            logits = self._step_fn(self.token_buf, self.pos_dev)
+            torch.ops.ws_b200.decode_pick(logits, self.token_buf, self.history, self.cursor, self.pos_dev)
+        self.graph_counters.capture_calls += 1
+        self.graph_counters.kernels_per_replay = _ext.launch_count() - launched
 
     def _capture(self) -> None:
         # warm up on a side stream (allocator + lazy initialisations), then capture once;

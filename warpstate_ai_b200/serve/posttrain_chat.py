@@ -138,28 +138,43 @@ def generate(engine: DecodeEngine, tokenizer, messages, *, max_new_tokens=256, m
 
 
 @torch.inference_mode()
-def generate_batch(engine: DecodeEngine, prompts: torch.Tensor, max_new_tokens: int, eos_id: int | None = None) -> dict:
+def generate_batch(engine: DecodeEngine, prompts: torch.Tensor, max_new_tokens: int, eos_id: int | None = None,
+                   synchronous: bool = False) -> dict:
     """Greedy lock-step decode of equal-length prompts ``[B, T]``: token ids ``[B, n]``, tokens/s over the
-    decode phase, per-token latencies in seconds and their median."""
+    decode phase, per-token latencies in seconds and their median.
+
+    On a CUDA device the steps are queued back to back (`DecodeEngine.decode_greedy`: the token pick is part of the
+    step graph) and the latencies are the device times between consecutive steps, from CUDA events.
+    ``synchronous=True`` is the host-driven loop -- arg-max on the host stream, one synchronisation per token, wall
+    clock -- which is also what runs on the CPU."""
     device = engine.device
     _sync(device)
     mark = time.perf_counter()
     logits = engine.prefill(prompts)
     _sync(device)
     prefill_seconds = time.perf_counter() - mark
-    columns, latencies = [], []
     token = torch.argmax(logits, dim=-1)
-    for _ in range(max_new_tokens):
-        columns.append(token)
-        mark = time.perf_counter()
-        token = torch.argmax(engine.step(token), dim=-1)
+    if device.type == "cuda" and not synchronous and max_new_tokens > 1:
+        events: list = []
+        chosen = engine.decode_greedy(token, max_new_tokens - 1, events)
         _sync(device)
-        latencies.append(time.perf_counter() - mark)
-    tokens = torch.stack(columns, dim=1)
+        tokens = torch.cat([token.unsqueeze(1), chosen], dim=1)
+        latencies = [a.elapsed_time(b) / 1e3 for a, b in zip(events, events[1:])]
+        timing = "device events between queued steps"
+    else:
+        columns, latencies = [], []
+        for _ in range(max_new_tokens):
+            columns.append(token)
+            mark = time.perf_counter()
+            token = torch.argmax(engine.step(token), dim=-1)
+            _sync(device)
+            latencies.append(time.perf_counter() - mark)
+        tokens = torch.stack(columns, dim=1)
+        timing = "host clock, one synchronisation per token"
     total = math.fsum(latencies)
     return {"tokens": tokens, "prefill_seconds": prefill_seconds, "decode_seconds": total,
-            "tokens_per_second": tokens.numel() / total, "latencies": latencies,
-            "p50_latency_seconds": sorted(latencies)[len(latencies) // 2]}
+            "tokens_per_second": tokens.shape[0] * len(latencies) / total, "latencies": latencies,
+            "p50_latency_seconds": sorted(latencies)[len(latencies) // 2], "timing": timing}
 
 
 # ----------------------------------------------------------------------------------- prompt suites
