@@ -131,6 +131,8 @@ def main(argv=None) -> int:
                     help="ours: after the timed updates, run one more under torch.profiler and print the kernels that "
                          "carry its device time (rank 0)")
     a = ap.parse_args(argv)
+    if a.profile:
+        os.environ.setdefault("WS_TRAIN_PDL", "0")   # dependents would book their in-kernel wait as their own time
     import torch.distributed as dist
     from .. import WarpStateLM, warpstate_2b, warpstate_smoke
     from ..train import dpo as DPO

@@ -10,6 +10,7 @@ are for *shares* only; throughput is measured by bench.py.
 from __future__ import annotations
 
 import argparse
+import os
 import json
 from collections import defaultdict
 
@@ -76,6 +77,10 @@ def main() -> None:
     ap.add_argument("--top", type=int, default=40)
     ap.add_argument("--out", default=None)
     args = ap.parse_args()
+    # A programmatic dependent launch starts before its predecessor ends and waits inside the kernel, so a
+    # profiler would book that wait as the kernel's own time: profile with plain launches (read once, at the
+    # library's first launch).
+    os.environ.setdefault("WS_TRAIN_PDL", "0")
     from .. import WarpStateLM, warpstate_2b, warpstate_smoke
     from ..data.tokens import SyntheticTokens
     from ..train.engine import Trainer

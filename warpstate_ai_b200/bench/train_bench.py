@@ -222,6 +222,10 @@ def benchmark(a) -> dict:
     else:
         cfg = warpstate_2b() if a.model == "2b" else warpstate_smoke()
     cfg.gradient_checkpointing = a.activation_checkpointing
+    if a.profile:
+        # kernels launched as programmatic dependents wait for their predecessor inside the kernel, which a
+        # profiler books as their own time: the profiled run uses plain launches
+        os.environ.setdefault("WS_TRAIN_PDL", "0")
     with torch.device(device):
         model = WarpStateLM(cfg)
     if checkpoint is not None:
