@@ -279,3 +279,39 @@ def test_greedy_decode_without_the_host_matches_the_host_driven_loop():
     assert counters["replay_calls"] >= steps and counters["eager_steps"] == 0
     # a host-driven step after the device-driven run continues from the same position
     assert torch.equal(torch.argmax(device_side.step(got[:, -1]), dim=-1), torch.argmax(host.step(want[:, -1]), dim=-1))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("batch,d,heads,ffn", [(5, 128, 2, 256), (64, 512, 8, 1024), (33, 2048, 32, 7168)])
+def test_persistent_layer_tail_is_bit_identical_to_the_launch_per_projection_step(monkeypatch, batch, d, heads, ffn):
+    """One cooperative launch per layer for out_proj .. next in_proj (grid barriers in place of kernel boundaries)
+    against the seven launches it replaces: the same k-block order and the same reduction order, so the logits of
+    every step must be equal bit for bit -- which also checks every barrier, since a phase that ran early would read
+    stale activations.  The last shape is the production layer (144 work items on 148 SMs)."""
+    from warpstate_ai_b200 import WarpStateConfig, WarpStateLM
+    from warpstate_ai_b200.ops.gemm import check_device_errors
+    from warpstate_ai_b200.serve.engine import DecodeEngine
+    torch.manual_seed(11)
+    cfg = WarpStateConfig(vocab_size=1024, d_model=d, n_heads=heads, n_cores=2, logical_depth=3, ffn_hidden=ffn,
+                          chunk_size=128, gradient_checkpointing=False, parallel_memory=True)
+    with torch.device("cuda"):
+        model = WarpStateLM(cfg)
+    model.eval().requires_grad_(False)
+    prompt = torch.randint(0, 1024, (batch, 40), device="cuda")
+    monkeypatch.setenv("WS_DECODE_LAYER_TAIL", "0")
+    plain = DecodeEngine(model, dtype=torch.bfloat16)
+    token = torch.argmax(plain.prefill(prompt), dim=-1)
+    assert plain._kbufs is not None and not plain._layer_tail
+    monkeypatch.setenv("WS_DECODE_LAYER_TAIL", "1")
+    fused = DecodeEngine(model, dtype=torch.bfloat16)
+    assert torch.equal(torch.argmax(fused.prefill(prompt), dim=-1), token)
+    assert fused._layer_tail
+    for step in range(6):
+        want = plain.step(token).clone()
+        got = fused.step(token).clone()
+        check_device_errors()
+        assert torch.equal(got, want), (step, float((got - want).abs().max()))
+        token = torch.argmax(want, dim=-1)
+    # 2 + 2 launches per layer + 3: embedding norm, first in_proj, head
+    assert fused.graph_counters.kernels_per_replay == 2 * 3 + 3
+    assert plain.graph_counters.kernels_per_replay == 7 * 3 + 2

@@ -738,6 +738,54 @@ void decode_attn(const at::Tensor& qkvgu, at::Tensor kc, at::Tensor vc, at::Tens
                           (int)H, (int)d, y.data_ptr(), cur_stream()), "decode_attn");
 }
 
+void decode_layer_tail(const at::Tensor& w_out, const at::Tensor& w_ug, const at::Tensor& w_down,
+                       const c10::optional<at::Tensor>& w_in_next, const at::Tensor& y, at::Tensor x, at::Tensor part_out,
+                       at::Tensor part_down, at::Tensor n, at::Tensor act, at::Tensor qkvgu, const at::Tensor& w_norm2,
+                       const c10::optional<at::Tensor>& next_scale, const c10::optional<at::Tensor>& next_bias,
+                       const at::Tensor& w_norm_next, double eps, at::Tensor barrier, const c10::optional<at::Tensor>& error_flag) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kFloat && x.dim() == 2 && x.is_contiguous(), "decode_layer_tail: x");
+  const int64_t batch = x.size(0), d = x.size(1);
+  TORCH_CHECK(w_down.dim() == 2 && w_down.size(0) == d, "decode_layer_tail: w_down must be [d, ffn]");
+  const int64_t ffn = w_down.size(1);
+  auto bf16 = [](const at::Tensor& t, int64_t rows, int64_t cols, const char* what) {
+    TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16 && t.is_contiguous() && t.dim() == 2 && t.size(0) == rows &&
+                t.size(1) == cols && reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0, what);
+  };
+  bf16(w_out, d, d, "decode_layer_tail: w_out must be contiguous BF16 [d, d]");
+  bf16(w_ug, 2 * ffn, d, "decode_layer_tail: w_ug must be contiguous BF16 [2 ffn, d]");
+  bf16(w_down, d, ffn, "decode_layer_tail: w_down must be contiguous BF16 [d, ffn]");
+  if (w_in_next.has_value()) bf16(*w_in_next, 5 * d, d, "decode_layer_tail: w_in_next must be contiguous BF16 [5 d, d]");
+  bf16(y, batch, d, "decode_layer_tail: y must be contiguous BF16 [batch, d]");
+  bf16(n, batch, d, "decode_layer_tail: n must be contiguous BF16 [batch, d]");
+  bf16(act, batch, ffn, "decode_layer_tail: act must be contiguous BF16 [batch, ffn]");
+  bf16(qkvgu, batch, 5 * d, "decode_layer_tail: qkvgu must be contiguous BF16 [batch, 5 d]");
+  TORCH_CHECK(part_out.scalar_type() == at::kFloat && part_out.is_contiguous() &&
+              part_out.numel() == decode_gemm_splits(d, d) * batch * d, "decode_layer_tail: part_out [splits, batch, d] FP32");
+  TORCH_CHECK(part_down.scalar_type() == at::kFloat && part_down.is_contiguous() &&
+              part_down.numel() == decode_gemm_splits(d, ffn) * batch * d, "decode_layer_tail: part_down [splits, batch, d] FP32");
+  for (const at::Tensor* t : {&w_norm2, &w_norm_next}) {
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kFloat && t->is_contiguous() && t->numel() == d,
+                "decode_layer_tail: norm weights must be FP32 [d]");
+  }
+  TORCH_CHECK(next_scale.has_value() == next_bias.has_value(), "decode_layer_tail: modulation needs scale and bias");
+  if (next_scale.has_value()) {
+    TORCH_CHECK(next_scale->scalar_type() == at::kFloat && next_scale->numel() == d && next_scale->is_contiguous() &&
+                next_bias->scalar_type() == at::kFloat && next_bias->numel() == d && next_bias->is_contiguous(),
+                "decode_layer_tail: modulation vectors must be FP32 [d]");
+  }
+  TORCH_CHECK(barrier.is_cuda() && barrier.scalar_type() == at::kInt && barrier.is_contiguous() && barrier.numel() >= 2,
+              "decode_layer_tail: barrier must hold two int32 words");
+  c10::cuda::CUDAGuard guard(x.device());
+  check_rc(ws_decode_layer_tail(w_out.data_ptr(), w_ug.data_ptr(), w_down.data_ptr(),
+                                w_in_next.has_value() ? w_in_next->data_ptr() : nullptr, y.data_ptr(), x.data_ptr<float>(),
+                                part_out.data_ptr<float>(), part_down.data_ptr<float>(), n.data_ptr(), act.data_ptr(),
+                                qkvgu.data_ptr(), w_norm2.data_ptr<float>(),
+                                next_scale.has_value() ? next_scale->data_ptr<float>() : nullptr,
+                                next_bias.has_value() ? next_bias->data_ptr<float>() : nullptr, w_norm_next.data_ptr<float>(),
+                                (float)eps, (int)batch, (int)d, (int)ffn, reinterpret_cast<unsigned*>(barrier.data_ptr<int>()),
+                                reinterpret_cast<int*>(const_cast<void*>(opt_ptr(error_flag))), cur_stream()), "decode_layer_tail");
+}
+
 void decode_pick(const at::Tensor& logits, at::Tensor token, const c10::optional<at::Tensor>& history, at::Tensor cursor,
                  at::Tensor pos) {
   TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.dim() == 2 && logits.is_contiguous() &&
@@ -773,6 +821,9 @@ TORCH_LIBRARY(ws_b200, m) {
   m.def("decode_gemm(Tensor w, Tensor x, int n, int epilogue, Tensor(a!) out, Tensor(b!)? error_flag, bool packed=False) -> ()");
   m.def("decode_reduce_norm(Tensor(a!) x, Tensor? partial, Tensor? token, Tensor? table, Tensor? scale, Tensor? bias, "
         "Tensor w, float eps, Tensor(b!)? out) -> ()");
+  m.def("decode_layer_tail(Tensor w_out, Tensor w_ug, Tensor w_down, Tensor? w_in_next, Tensor y, Tensor(a!) x, "
+        "Tensor(b!) part_out, Tensor(c!) part_down, Tensor(d!) n, Tensor(e!) act, Tensor(f!) qkvgu, Tensor w_norm2, "
+        "Tensor? next_scale, Tensor? next_bias, Tensor w_norm_next, float eps, Tensor(g!) barrier, Tensor(h!)? error_flag) -> ()");
   m.def("decode_pick(Tensor logits, Tensor(a!) token, Tensor(b!)? history, Tensor(c!) cursor, Tensor(d!) pos) -> ()");
   m.def("decode_attn(Tensor qkvgu, Tensor(a!) kc, Tensor(b!) vc, Tensor(c!) uc, Tensor mixed, Tensor rope, Tensor pos, "
         "int H, Tensor(d!) y) -> ()");
@@ -830,6 +881,7 @@ TORCH_LIBRARY_IMPL(ws_b200, CUDA, m) {
   m.impl("decode_reduce_norm", &decode_reduce_norm);
   m.impl("decode_attn", &decode_attn);
   m.impl("decode_pick", &decode_pick);
+  m.impl("decode_layer_tail", &decode_layer_tail);
   m.impl("grad_weight_group", &grad_weight_group);
   m.impl("rmsnorm_fwd", &rmsnorm_fwd);
   m.impl("rmsnorm_bwd", &rmsnorm_bwd);

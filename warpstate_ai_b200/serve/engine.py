@@ -60,6 +60,7 @@ class DecodeEngine:
         self.use_kernels = use_kernels
         self.pack_weights = pack_weights
         self._kbufs = None
+        self._layer_tail = False
         self.weights = []
         with torch.no_grad():
             for depth in range(self.cfg.logical_depth):
@@ -111,6 +112,7 @@ class DecodeEngine:
         self.graph_counters.invalidations += (self._graph is not None) + (self._greedy_graph is not None)
         self._graph = self._greedy_graph = None
         self._kbufs = self._kernel_buffers(batch) if self._kernels_usable(batch) else None
+        self._layer_tail = self._kbufs is not None and self._tail_kernel_usable()
         # greedy run-ahead decode: chosen tokens land in `history[:, cursor[0]]`; cursor[1] is kernel scratch
         self.history = torch.zeros(batch, self.GREEDY_CAPACITY, dtype=torch.long, device=self.device)
         self.cursor = torch.zeros(2, dtype=torch.long, device=self.device)
@@ -162,9 +164,45 @@ class DecodeEngine:
             act=torch.zeros(batch, ffn, device=dev, dtype=torch.bfloat16),
             p_out=torch.zeros(ops.decode_gemm_splits(d, d), batch, d, device=dev),
             p_down=torch.zeros(ops.decode_gemm_splits(d, ffn), batch, d, device=dev),
-            logits=torch.zeros(batch, v, device=dev), rope=attention.rope_table(dev), flag=gemm.error_flag(dev))
+            logits=torch.zeros(batch, v, device=dev), rope=attention.rope_table(dev), flag=gemm.error_flag(dev),
+            barrier=torch.zeros(2, dtype=torch.int32, device=dev))
+
+    def _tail_kernel_usable(self) -> bool:
+        """The persistent layer-tail launch gives every CTA at most one work item per phase, one CTA per SM."""
+        import os
+        if os.environ.get("WS_DECODE_LAYER_TAIL", "1") == "0" or self.pack_weights:
+            return False
+        ops = torch.ops.ws_b200
+        d, ffn = self.cfg.d_model, self.cfg.ffn_hidden
+        if d % 128 or ffn % 64:
+            return False
+        slabs = (d + 127) // 128
+        items = max(slabs * ops.decode_gemm_splits(d, d), slabs * ops.decode_gemm_splits(d, ffn), ffn // 64,
+                    (5 * d + 127) // 128, self.batch)
+        return items <= torch.cuda.get_device_properties(self.device).multi_processor_count
+
+    def _step_kernels_tail(self, token: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
+        """The step with one persistent launch per layer for everything after the attention (and the next layer's
+        in_proj): 2 launches per layer instead of 7.  Bit-identical to `_step_kernels`."""
+        ops = torch.ops.ws_b200
+        k = self._kbufs
+        d, eps = self.cfg.d_model, self.cfg.rms_eps
+        first = self.weights[0]
+        ops.decode_reduce_norm(k["x"], None, token, self.embed, first["scale"], first["bias"], first["n1"], eps, k["n"])
+        ops.decode_gemm(first["w_in"], k["n"], 5 * d, 0, k["qkvgu"], k["flag"], False)
+        for index, (w, st) in enumerate(zip(self.weights, self.states)):
+            ops.decode_attn(k["qkvgu"], st.k, st.v, st.u, st.mixed, k["rope"], pos, self.h, k["y"])
+            nxt = self.weights[index + 1] if index + 1 < len(self.weights) else None
+            ops.decode_layer_tail(w["w_out"], w["w_ug"], w["w_down"], nxt["w_in"] if nxt else None, k["y"], k["x"],
+                                  k["p_out"], k["p_down"], k["n"], k["act"], k["qkvgu"], w["n2"],
+                                  nxt["scale"] if nxt else None, nxt["bias"] if nxt else None,
+                                  nxt["n1"] if nxt else self.final_norm, eps, k["barrier"], k["flag"])
+        ops.decode_gemm(self.head, k["n"], self.cfg.vocab_size, 3, k["logits"], k["flag"], False)
+        return k["logits"]
 
     def _step_kernels(self, token: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
+        if self._layer_tail:
+            return self._step_kernels_tail(token, pos)
         ops = torch.ops.ws_b200
         k = self._kbufs
         d, ffn, eps = self.cfg.d_model, self.cfg.ffn_hidden, self.cfg.rms_eps
