@@ -742,7 +742,8 @@ void decode_layer_tail(const at::Tensor& w_out, const at::Tensor& w_ug, const at
                        const c10::optional<at::Tensor>& w_in_next, const at::Tensor& y, at::Tensor x, at::Tensor part_out,
                        at::Tensor part_down, at::Tensor n, at::Tensor act, at::Tensor qkvgu, const at::Tensor& w_norm2,
                        const c10::optional<at::Tensor>& next_scale, const c10::optional<at::Tensor>& next_bias,
-                       const at::Tensor& w_norm_next, double eps, at::Tensor barrier, const c10::optional<at::Tensor>& error_flag) {
+                       const at::Tensor& w_norm_next, double eps, at::Tensor barrier, const c10::optional<at::Tensor>& error_flag,
+                       const c10::optional<at::Tensor>& trace) {
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kFloat && x.dim() == 2 && x.is_contiguous(), "decode_layer_tail: x");
   const int64_t batch = x.size(0), d = x.size(1);
   TORCH_CHECK(w_down.dim() == 2 && w_down.size(0) == d, "decode_layer_tail: w_down must be [d, ffn]");
@@ -775,6 +776,13 @@ void decode_layer_tail(const at::Tensor& w_out, const at::Tensor& w_ug, const at
   }
   TORCH_CHECK(barrier.is_cuda() && barrier.scalar_type() == at::kInt && barrier.is_contiguous() && barrier.numel() >= 2,
               "decode_layer_tail: barrier must hold two int32 words");
+  long long* stamps = nullptr;
+  if (trace.has_value()) {
+    const int sms = at::cuda::getDeviceProperties(x.device().index())->multiProcessorCount;
+    TORCH_CHECK(trace->is_cuda() && trace->scalar_type() == at::kLong && trace->is_contiguous() && trace->numel() >= 16 * sms,
+                "decode_layer_tail: trace must be int64 [SMs, 16]");
+    stamps = reinterpret_cast<long long*>(trace->data_ptr<int64_t>());
+  }
   c10::cuda::CUDAGuard guard(x.device());
   check_rc(ws_decode_layer_tail(w_out.data_ptr(), w_ug.data_ptr(), w_down.data_ptr(),
                                 w_in_next.has_value() ? w_in_next->data_ptr() : nullptr, y.data_ptr(), x.data_ptr<float>(),
@@ -783,7 +791,7 @@ void decode_layer_tail(const at::Tensor& w_out, const at::Tensor& w_ug, const at
                                 next_scale.has_value() ? next_scale->data_ptr<float>() : nullptr,
                                 next_bias.has_value() ? next_bias->data_ptr<float>() : nullptr, w_norm_next.data_ptr<float>(),
                                 (float)eps, (int)batch, (int)d, (int)ffn, reinterpret_cast<unsigned*>(barrier.data_ptr<int>()),
-                                reinterpret_cast<int*>(const_cast<void*>(opt_ptr(error_flag))), cur_stream()), "decode_layer_tail");
+                                reinterpret_cast<int*>(const_cast<void*>(opt_ptr(error_flag))), stamps, cur_stream()), "decode_layer_tail");
 }
 
 void decode_pick(const at::Tensor& logits, at::Tensor token, const c10::optional<at::Tensor>& history, at::Tensor cursor,
@@ -823,7 +831,8 @@ TORCH_LIBRARY(ws_b200, m) {
         "Tensor w, float eps, Tensor(b!)? out) -> ()");
   m.def("decode_layer_tail(Tensor w_out, Tensor w_ug, Tensor w_down, Tensor? w_in_next, Tensor y, Tensor(a!) x, "
         "Tensor(b!) part_out, Tensor(c!) part_down, Tensor(d!) n, Tensor(e!) act, Tensor(f!) qkvgu, Tensor w_norm2, "
-        "Tensor? next_scale, Tensor? next_bias, Tensor w_norm_next, float eps, Tensor(g!) barrier, Tensor(h!)? error_flag) -> ()");
+        "Tensor? next_scale, Tensor? next_bias, Tensor w_norm_next, float eps, Tensor(g!) barrier, Tensor(h!)? error_flag, "
+        "Tensor(i!)? trace=None) -> ()");
   m.def("decode_pick(Tensor logits, Tensor(a!) token, Tensor(b!)? history, Tensor(c!) cursor, Tensor(d!) pos) -> ()");
   m.def("decode_attn(Tensor qkvgu, Tensor(a!) kc, Tensor(b!) vc, Tensor(c!) uc, Tensor mixed, Tensor rope, Tensor pos, "
         "int H, Tensor(d!) y) -> ()");

@@ -58,6 +58,7 @@ struct LayerTailParams {
   const float* w_norm_next;             // next layer's first norm, or the final norm
   unsigned* barrier;                    // [0] arrivals, [1] exits; both zero between launches
   int* error_flag;
+  long long* trace;                     // optional [grid, 16]: %globaltimer of every CTA at its phase boundaries
 };
 
 struct TailCta {
@@ -380,25 +381,42 @@ decode_layer_tail_kernel(const __grid_constant__ CUtensorMap tm_wout, const __gr
     }
   } else {
     const int et = threadIdx.x - 64;
+    int stamp_index = 0;
+    auto stamp = [&]() {
+      if (p.trace != nullptr && et == 0) p.trace[static_cast<size_t>(me) * 16 + stamp_index] = static_cast<long long>(globaltimer_ns());
+      ++stamp_index;
+    };
+    stamp();                                                                                   // 0 start
     uint32_t worked = 0;  // GEMM phases in which this CTA had an item: the parity of its accumulator barrier
     tail_epilogue<1>(c, w_out, p.d, p.batch, p.part_out, 0, worked & 1, warp, lane);
     worked += w_out.valid ? 1u : 0u;
+    stamp();                                                                                   // 1 out_proj stored
     tail_grid_barrier(c, p.barrier, 1u, p.error_flag, et);
+    stamp();                                                                                   // 2 barrier 1
     if (me < p.batch)
       tail_norm_row(p.x, p.part_out, p.splits_out, p.batch, me, p.d, nullptr, nullptr, p.w_norm2, p.eps, p.n, red, et);
+    stamp();                                                                                   // 3 norm 1
     tail_grid_barrier(c, p.barrier, 2u, p.error_flag, et);
+    stamp();                                                                                   // 4 barrier 2
     tail_epilogue<2>(c, w_ug, p.ffn, p.batch, p.act, p.ffn, worked & 1, warp, lane);
     worked += w_ug.valid ? 1u : 0u;
+    stamp();                                                                                   // 5 up/gate stored
     tail_grid_barrier(c, p.barrier, 3u, p.error_flag, et);
+    stamp();                                                                                   // 6 barrier 3
     tail_epilogue<1>(c, w_down, p.d, p.batch, p.part_down, 0, worked & 1, warp, lane);
     worked += w_down.valid ? 1u : 0u;
+    stamp();                                                                                   // 7 down stored
     tail_grid_barrier(c, p.barrier, 4u, p.error_flag, et);
+    stamp();                                                                                   // 8 barrier 4
     if (me < p.batch)
       tail_norm_row(p.x, p.part_down, p.splits_down, p.batch, me, p.d, p.next_scale, p.next_bias, p.w_norm_next, p.eps,
                     p.n, red, et);
+    stamp();                                                                                   // 9 norm 2
     if (p.has_in) {
       tail_grid_barrier(c, p.barrier, 5u, p.error_flag, et);
+      stamp();                                                                                 // 10 barrier 5
       tail_epilogue<0>(c, w_in, 5 * p.d, p.batch, p.qkvgu, 5 * p.d, worked & 1, warp, lane);
+      stamp();                                                                                 // 11 in_proj stored
     }
   }
   tc_fence_before_sync();
@@ -427,12 +445,14 @@ using namespace ws;
 // w_out [d, d], w_ug [2 ffn, d] (up rows, then gate rows), w_down [d, ffn], w_in_next [5 d, d] (NULL after the last
 // layer): row-major BF16.  y [batch, d] BF16 is the attention output.  x, part_out, part_down, n, act, qkvgu as in
 // LayerTailParams; part_* are sized with ws_decode_gemm_splits.  barrier: two zeroed 32-bit words, shared by all
-// launches of a stream.  Returns -30 when the device has fewer SMs than the largest phase has work items.
+// launches of a stream.  trace (optional): [SMs, 16] int64, receives %globaltimer at every CTA's phase boundaries
+// (start, out stored, barrier 1, norm 1, barrier 2, up/gate stored, barrier 3, down stored, barrier 4, norm 2,
+// barrier 5, in_proj stored).  Returns -30 when the device has fewer SMs than the largest phase has work items.
 extern "C" int ws_decode_layer_tail(const void* w_out, const void* w_ug, const void* w_down, const void* w_in_next,
                                     const void* y, float* x, float* part_out, float* part_down, void* n, void* act,
                                     void* qkvgu, const float* w_norm2, const float* next_scale, const float* next_bias,
                                     const float* w_norm_next, float eps, int batch, int d, int ffn, unsigned* barrier,
-                                    int* error_flag, cudaStream_t stream) {
+                                    int* error_flag, long long* trace, cudaStream_t stream) {
   using namespace tail;
   if (batch <= 0 || batch > BPAD || d % 128 != 0 || ffn % 64 != 0 || d % 8 != 0 || ffn % 8 != 0) return -1;
   static int sms = 0;
@@ -462,7 +482,7 @@ extern "C" int ws_decode_layer_tail(const void* w_out, const void* w_ug, const v
   p.n = static_cast<__nv_bfloat16*>(n); p.act = static_cast<__nv_bfloat16*>(act);
   p.qkvgu = static_cast<__nv_bfloat16*>(qkvgu);
   p.w_norm2 = w_norm2; p.next_scale = next_scale; p.next_bias = next_bias; p.w_norm_next = w_norm_next;
-  p.barrier = barrier; p.error_flag = error_flag;
+  p.barrier = barrier; p.error_flag = error_flag; p.trace = trace;
   CUtensorMap t_wout, t_wug, t_wdown, t_win, t_y, t_n, t_act;
   int rc;
   if ((rc = make_map_bf16(&t_wout, w_out, d, d, d, BK, TM))) return rc;

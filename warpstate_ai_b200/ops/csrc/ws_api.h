@@ -83,12 +83,13 @@ int ws_decode_attn(const void* qkvgu, void* kc, void* vc, void* uc, const void* 
 // Weights row-major BF16: w_out [d, d], w_ug [2 ffn, d], w_down [d, ffn], w_in_next [5 d, d] or NULL after the last
 // layer.  y [batch, d] BF16 attention output; x [batch, d] FP32 residual (in place); part_out / part_down FP32
 // [ws_decode_gemm_splits(d, d) | (d, ffn), batch, d]; n [batch, d], act [batch, ffn], qkvgu [batch, 5 d] BF16.
-// barrier: two zeroed 32-bit words.  batch <= 64.  -30: fewer SMs than the largest phase has work items.
+// barrier: two zeroed 32-bit words.  trace: NULL, or [SMs, 16] int64 receiving %globaltimer at phase boundaries.
+// batch <= 64.  -30: fewer SMs than the largest phase has work items.
 int ws_decode_layer_tail(const void* w_out, const void* w_ug, const void* w_down, const void* w_in_next,
                          const void* y, float* x, float* part_out, float* part_down, void* n, void* act, void* qkvgu,
                          const float* w_norm2, const float* next_scale, const float* next_bias,
                          const float* w_norm_next, float eps, int batch, int d, int ffn, unsigned* barrier,
-                         int* error_flag, cudaStream_t stream);
+                         int* error_flag, long long* trace, cudaStream_t stream);
 
 // Greedy pick at the end of a decode step: token[b] = argmax(logits[b, :]), also written to history[b, cursor[0]]
 // (history [batch, capacity] int64, may be NULL); then pos[0] += 1 and cursor[0] += 1.  cursor: two int64 words
