@@ -168,9 +168,10 @@ def test_decode_bench_combines_replicas():
     """Independent decode replicas: throughputs add, latencies take the slowest rank."""
     from warpstate_ai_b200.bench.decode_bench import combine_ranks
     a = {"tokens_per_second": 100.0, "prefill_tokens_per_second": 1000.0, "p50_latency_seconds": 0.002,
-         "prefill_seconds": 0.5, "peak_mem_gib": 30.0}
+         "prefill_seconds": 0.5, "peak_mem_gib": 30.0, "host_driven_p50_seconds": 0.0021}
     b = {"tokens_per_second": 90.0, "prefill_tokens_per_second": 900.0, "p50_latency_seconds": 0.003,
-         "prefill_seconds": 0.6, "peak_mem_gib": 31.0}
+         "prefill_seconds": 0.6, "peak_mem_gib": 31.0, "host_driven_p50_seconds": 0.0032}
     out = combine_ranks([a, b])
     assert out["tokens_per_second"] == 190.0 and out["prefill_tokens_per_second"] == 1900.0
     assert out["p50_latency_seconds"] == 0.003 and out["prefill_seconds"] == 0.6 and out["peak_mem_gib"] == 31.0
+    assert out["host_driven_p50_seconds"] == 0.0032
