@@ -120,6 +120,31 @@ def test_adamw_matches_torch(ops):
         assert torch.allclose(sd["state"][k]["exp_avg"].cuda(), tsd["state"][k]["exp_avg"], rtol=1e-5, atol=1e-8)
 
 
+def test_adamw_with_gradients_whose_squares_are_denormal(ops):
+    """The library is built with flush-to-zero: for |g| ~ 1e-20 the second moment g^2 ~ 1e-40 is a denormal and
+    becomes 0 here while torch's fused AdamW keeps it.  Both denominators are then eps to within 1e-13, so the
+    parameters must still agree; the moments differ by the flushed denormals only.  Pins the accepted deviation."""
+    from warpstate_ai_b200.optim import ArenaAdamW, ParamArena
+    torch.manual_seed(0)
+    net = torch.nn.Linear(512, 256, bias=False).cuda()
+    ref = torch.nn.Linear(512, 256, bias=False).cuda()
+    ref.load_state_dict(net.state_dict())
+    arena = ParamArena(net)
+    opt = ArenaAdamW(arena, lr=1e-3, weight_decay=0.0, max_grad_norm=None)
+    topt = torch.optim.AdamW(ref.parameters(), lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.0, fused=True)
+    for step in range(3):
+        g = torch.randn(256, 512, device="cuda") * 1e-20
+        arena.zero_grad()
+        net.weight.main_grad.copy_(g)
+        ref.weight.grad = g.clone()
+        opt.step()
+        topt.step()
+        assert torch.allclose(net.weight, ref.weight, rtol=0, atol=1e-12)
+    mine, theirs = opt.state_dict()["state"][0], topt.state_dict()["state"][0]
+    assert torch.allclose(mine["exp_avg"].cuda(), theirs["exp_avg"], rtol=1e-5, atol=1e-30)
+    assert float(mine["exp_avg_sq"].abs().max()) == 0.0 and float(theirs["exp_avg_sq"].max()) < 1e-38
+
+
 @pytest.mark.parametrize("parallel", [True, False])
 def test_whole_model_matches_torch_path(parallel):
     from warpstate_ai_b200 import WarpStateConfig, WarpStateLM

@@ -184,7 +184,10 @@ class FusedGradSync(GradSyncBase):
         self.flag_sym = symm.allocate(max(words, 64), torch.int32, self.device, self.group)
         self.partials = torch.zeros(launches * self.ctas, dtype=torch.float32, device=self.device)
         mc = self.grad_sym.multicast_ptr
-        if self.use_nvls is False:
+        # Measured on 256 MiB FP32 (bus GB/s): two ranks -- peer loads 566-617, multimem 388; four ranks -- peer loads
+        # 470-582, multimem 645 at any CTA count.  With one peer the switch has nothing to reduce; from four ranks on
+        # its traffic per rank stays constant while peer loads grow with the peer count.
+        if self.use_nvls is False or (self.use_nvls is None and self.world <= 2):
             mc = 0
         self.mc_ptr = mc
         self.kind = "fused-nvls" if mc else "fused-p2p"
