@@ -187,30 +187,34 @@ memory_scan_bwd_kernel(const float* __restrict__ dstate, const float* __restrict
   for (int g = groups - 1; g >= 0; --g) {
     const int n0 = g * SCAN_GROUP;
     const int count = min(SCAN_GROUP, N - n0);
-    float F[SCAN_GROUP], S[SCAN_GROUP], W[SCAN_GROUP];
+    // every load of the group is requested before its recurrences run: 2 x SCAN_GROUP independent loads in flight
+    float F[SCAN_GROUP], S[SCAN_GROUP], W[SCAN_GROUP], G[SCAN_GROUP];
+#pragma unroll
+    for (int i = 0; i < SCAN_GROUP; ++i) {
+      if (i < count) {
+        W[i] = writes[base + (n0 + i) * chunk_stride];
+        G[i] = dstate[base + (n0 + i) * chunk_stride];
+      }
+    }
     float f = start_f[g], s = start_s[g];
 #pragma unroll
     for (int i = 0; i < SCAN_GROUP; ++i) {  // forward: state seen by chunk n0 + i
       if (i < count) {
         F[i] = f;
         S[i] = s;
-        const float w = writes[base + (n0 + i) * chunk_stride];
-        W[i] = w;
-        f = df * f + (1.f - df) * w;
-        s = ds * s + (1.f - ds) * w;
+        f = df * f + (1.f - df) * W[i];
+        s = ds * s + (1.f - ds) * W[i];
       }
     }
 #pragma unroll
     for (int i = SCAN_GROUP - 1; i >= 0; --i) {
       if (i < count) {
-        const size_t off = base + (n0 + i) * chunk_stride;
-        dwrites[off] = __float2bfloat16_rn((1.f - df) * a + (1.f - ds) * bb);
+        dwrites[base + (n0 + i) * chunk_stride] = __float2bfloat16_rn((1.f - df) * a + (1.f - ds) * bb);
         g_df += a * (F[i] - W[i]);    // F_{n+1} = df F_n + (1 - df) w_n
         g_ds += bb * (S[i] - W[i]);
-        const float gr = dstate[off];
-        g_mix += gr * (F[i] - S[i]);
-        a = mix * gr + df * a;        // gradient of F_n
-        bb = (1.f - mix) * gr + ds * bb;
+        g_mix += G[i] * (F[i] - S[i]);
+        a = mix * G[i] + df * a;      // gradient of F_n
+        bb = (1.f - mix) * G[i] + ds * bb;
       }
     }
   }

@@ -125,7 +125,11 @@ chunk_writes_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_c
 // =============================================================================== scan
 // writes [B,N,H,4096] FP32 -> states [B,N,H,4096] BF16 (mixed state read by chunk n), and
 // optionally the fast / slow states after the last chunk [B,H,4096] FP32 (prefill).
-__global__ void __launch_bounds__(256)
+// One thread owns four consecutive state elements (16-byte loads, 8-byte stores) and requests the writes of
+// SCAN_AHEAD chunks before it runs their recurrence, so a thread keeps 128 bytes in flight instead of 4.
+constexpr int SCAN_AHEAD = 8;
+
+__global__ void __launch_bounds__(128)
 memory_scan_kernel(const float* __restrict__ writes, const float* __restrict__ fast_logit,
                    const float* __restrict__ slow_logit, const float* __restrict__ mix_logit,
                    __nv_bfloat16* __restrict__ states, float* __restrict__ final_fast,
@@ -133,27 +137,43 @@ memory_scan_kernel(const float* __restrict__ writes, const float* __restrict__ f
                    const float* __restrict__ init_slow, int B, int N, int H) {
   pdl_launch_dependents();
   pdl_wait();
-  const size_t idx = blockIdx.x * static_cast<size_t>(256) + threadIdx.x;  // over B*H*4096
-  const size_t total = static_cast<size_t>(B) * H * 4096;
-  if (idx >= total) return;
-  const int e = idx % 4096;
-  const int h = (idx / 4096) % H;
-  const int b = idx / (4096 * static_cast<size_t>(H));
+  const size_t quad = blockIdx.x * static_cast<size_t>(128) + threadIdx.x;  // over B*H*1024 groups of four
+  const size_t total = static_cast<size_t>(B) * H * 1024;
+  if (quad >= total) return;
+  const int e = static_cast<int>(quad % 1024) * 4;
+  const int h = (quad / 1024) % H;
+  const int b = quad / (1024 * static_cast<size_t>(H));
   const float df = 1.f / (1.f + expf(-fast_logit[h]));
   const float ds = 1.f / (1.f + expf(-slow_logit[h]));
   const float mix = 1.f / (1.f + expf(-mix_logit[h]));
-  float f = init_fast != nullptr ? init_fast[idx] : 0.f;
-  float s = init_slow != nullptr ? init_slow[idx] : 0.f;
-  for (int n = 0; n < N; ++n) {
-    const size_t off = ((static_cast<size_t>(b) * N + n) * H + h) * 4096 + e;
-    if (states != nullptr) states[off] = __float2bfloat16_rn(mix * f + (1.f - mix) * s);
-    const float w = writes[off];
-    f = df * f + (1.f - df) * w;
-    s = ds * s + (1.f - ds) * w;
+  const size_t flat = quad * 4;
+  float4 f = init_fast != nullptr ? *reinterpret_cast<const float4*>(init_fast + flat) : make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 s = init_slow != nullptr ? *reinterpret_cast<const float4*>(init_slow + flat) : make_float4(0.f, 0.f, 0.f, 0.f);
+  const size_t chunk_stride = static_cast<size_t>(H) * 4096;
+  const size_t base = (static_cast<size_t>(b) * N * H + h) * 4096 + e;
+  for (int n0 = 0; n0 < N; n0 += SCAN_AHEAD) {
+    float4 w[SCAN_AHEAD];
+#pragma unroll
+    for (int j = 0; j < SCAN_AHEAD; ++j)
+      if (n0 + j < N) w[j] = *reinterpret_cast<const float4*>(writes + base + (n0 + j) * chunk_stride);
+#pragma unroll
+    for (int j = 0; j < SCAN_AHEAD; ++j) {
+      if (n0 + j >= N) break;
+      if (states != nullptr) {
+        uint2 o;
+        o.x = pack_bf16x2(mix * f.x + (1.f - mix) * s.x, mix * f.y + (1.f - mix) * s.y);
+        o.y = pack_bf16x2(mix * f.z + (1.f - mix) * s.z, mix * f.w + (1.f - mix) * s.w);
+        *reinterpret_cast<uint2*>(states + base + (n0 + j) * chunk_stride) = o;
+      }
+      f.x = df * f.x + (1.f - df) * w[j].x; f.y = df * f.y + (1.f - df) * w[j].y;
+      f.z = df * f.z + (1.f - df) * w[j].z; f.w = df * f.w + (1.f - df) * w[j].w;
+      s.x = ds * s.x + (1.f - ds) * w[j].x; s.y = ds * s.y + (1.f - ds) * w[j].y;
+      s.z = ds * s.z + (1.f - ds) * w[j].z; s.w = ds * s.w + (1.f - ds) * w[j].w;
+    }
   }
   if (final_fast != nullptr) {
-    final_fast[idx] = f;
-    final_slow[idx] = s;
+    *reinterpret_cast<float4*>(final_fast + flat) = f;
+    *reinterpret_cast<float4*>(final_slow + flat) = s;
   }
 }
 
@@ -366,7 +386,7 @@ extern "C" int ws_memory_scan(const float* writes, const float* fast_logit, cons
                               const float* init_fast, const float* init_slow, int B, int N, int H,
                               cudaStream_t stream) {
   const size_t total = (size_t)B * H * 4096;
-  launch_dependent(memory_scan_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, writes, fast_logit, slow_logit, mix_logit, (__nv_bfloat16*)states, final_fast, final_slow, init_fast,
+  launch_dependent(memory_scan_kernel, dim3((unsigned)((total / 4 + 127) / 128)), dim3(128), 0, stream, writes, fast_logit, slow_logit, mix_logit, (__nv_bfloat16*)states, final_fast, final_slow, init_fast,
       init_slow, B, N, H);
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
