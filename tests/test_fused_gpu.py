@@ -142,8 +142,7 @@ def test_adamw_with_gradients_whose_squares_are_denormal(ops):
         assert torch.allclose(net.weight, ref.weight, rtol=0, atol=1e-12)
     mine, theirs = opt.state_dict()["state"][0], topt.state_dict()["state"][0]
     a, b = mine["exp_avg"].cuda().double(), theirs["exp_avg"].double()
-    worst = float(((a - b).abs() / b.abs().clamp_min(1e-26)).max())
-    assert worst < 1e-4, (worst, float((a - b).abs().max()), float(b.abs().max()))
+    assert float((a - b).abs().max()) < 1e-6 * float(b.abs().max())      # FP32 rounding of the same lerp
     assert float(mine["exp_avg_sq"].abs().max()) == 0.0 and float(theirs["exp_avg_sq"].max()) < 1e-38
 
 
