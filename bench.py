@@ -52,7 +52,9 @@ def parse():
                          "(stream: re-gather every use; resident: keep the gathered BF16 weights for the update)")
     ap.add_argument("--activation-checkpointing", action="store_true")
     ap.add_argument("--bf16-residuals", action="store_true")
-    ap.add_argument("--ref-compile-mode", default=os.environ.get("WARPSTATE_REF_COMPILE_MODE", "default"))
+    ap.add_argument("--ref-compile-mode", default=os.environ.get("WARPSTATE_REF_COMPILE_MODE", "max-autotune-no-cudagraphs"),
+                    help="torch.compile mode of the reference arm's cores; the default is the reference's own B200 preset "
+                         "(its ops/train-b200.sh), whose compilation takes about a minute here")
     return ap.parse_args()
 
 
