@@ -77,3 +77,45 @@ def test_backward_matches_autograd_of_composite(batch, seq, h):
         assert rel_l2(g_mix, grads[3]) < 0.03, ("mix", g_mix, grads[3])
     else:
         assert float(g_fast.abs().max()) == 0.0 and float(g_mix.abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("batch,seq,h", [(1, 128, 1), (2, 640, 4), (4, 2048, 32)])
+def test_streaming_tile_kernels_equal_the_one_tile_per_cta_kernels(batch, seq, h):
+    """The persistent, warp-specialised form of the chunk-writes kernel (TMA ring, worker warps, MMA issue, epilogue
+    warps with a double-buffered accumulator) against the one-tile-per-CTA form: the same arithmetic in the same
+    order, so the results must be equal bit for bit -- fewer tiles than SMs, a ragged last round, and the
+    production count (2048 tiles on 148 SMs)."""
+    from warpstate_ai_b200.ops import _ext, attention
+    from warpstate_ai_b200.ops.gemm import check_device_errors, error_flag
+    ops = torch.ops.ws_b200
+    lib = _ext.cdll()
+    torch.manual_seed(5)
+    d = 64 * h
+    qkvgu = (torch.randn(batch * seq, 5 * d, device="cuda") * 1.5).bfloat16()
+    rope = attention.rope_table(qkvgu.device, pair_major=True)
+    try:
+        lib.ws_attn_set_stream_mode(0)
+        tile_form = ops.chunk_writes(qkvgu, rope, batch, seq, h, error_flag(qkvgu.device))
+        lib.ws_attn_set_stream_mode(1)
+        stream_form = ops.chunk_writes(qkvgu, rope, batch, seq, h, error_flag(qkvgu.device))
+        again = ops.chunk_writes(qkvgu, rope, batch, seq, h, error_flag(qkvgu.device))
+    finally:
+        lib.ws_attn_set_stream_mode(-1)
+    check_device_errors()
+    assert torch.equal(stream_form, tile_form) and torch.equal(again, tile_form)
+    assert float(tile_form.abs().max()) > 0
+    # the state-gradient kernel has the same two forms; it feeds the reverse scan and the backward kernel, so the
+    # packed gradient and the decay / mix gradients of the whole backward must be equal bit for bit as well
+    core = make_core(h)
+    dy = torch.randn(batch * seq, d, device="cuda").bfloat16()
+    results = {}
+    try:
+        for mode in (0, 1):
+            lib.ws_attn_set_stream_mode(mode)
+            y, saved = attention.forward(qkvgu, core, batch, seq)
+            results[mode] = (y, *attention.backward(dy, qkvgu, saved, core, batch, seq))
+    finally:
+        lib.ws_attn_set_stream_mode(-1)
+    check_device_errors()
+    for mine, theirs in zip(results[1], results[0]):
+        assert torch.equal(mine, theirs)

@@ -135,6 +135,186 @@ dstate_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_constan
   }
 }
 
+// =============================================================================== dState, streaming form
+// dstate_kernel as one persistent CTA per SM with specialised warps, exactly as chunk_writes_stream_kernel
+// (attention_fwd.cu): producer warp with a 3-stage ring of (Q, dy, gate) tiles, 256 workers that turn Q into rope(Q)
+// and dy into dy (1 - sigmoid(gate)) / 8 in place, MMA issue into a double-buffered accumulator, two epilogue warps
+// that store the FP32 [64 x 64] result by TMA.  Bit-identical to dstate_kernel.
+constexpr int DSS_STAGES = 3;
+constexpr int DSS_THREADS = 352;
+constexpr int DSS_SMEM = DSS_STAGES * 3 * TILE_BYTES + 2 * 16384 + 1024 + 256;
+
+__global__ void __launch_bounds__(DSS_THREADS, 1)
+dstate_stream_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_constant__ CUtensorMap tm_dy,
+                     const __grid_constant__ CUtensorMap tm_out, const float2* __restrict__ rope, int T, int H, int d,
+                     int tiles, int* error_flag) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  uint8_t* ring = smem;                                   // stage s: Q, dy, gate at s * 48 KiB
+  uint8_t* staging = smem + DSS_STAGES * 3 * TILE_BYTES;  // two FP32 [64 x 64] tiles
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + 2 * 16384);
+  uint64_t* full = bars;                    // [4] tile landed
+  uint64_t* empty = bars + DSS_STAGES;       // [4] MMAs have read the stage
+  uint64_t* tfull = bars + 2 * DSS_STAGES;   // [2] accumulator complete
+  uint64_t* tempty = tfull + 2;             // [2] accumulator read by both epilogue warps
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_chunks = T / CHUNK;
+
+  if (tid == 0) {
+    for (int s = 0; s < DSS_STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tfull[b], 1);
+      mbar_init(&tempty[b], 2);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_qkvgu);
+    tma_prefetch_desc(&tm_dy);
+    tma_prefetch_desc(&tm_out);
+  }
+  if (warp == 8) {
+    tmem_alloc(tmem_slot, 128);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  pdl_launch_dependents();
+  pdl_wait();
+
+  const int first = blockIdx.x, step = gridDim.x;
+  if (warp == 10) {
+    if (lane == 0) {
+      int i = 0;
+      for (int tile = first; tile < tiles; tile += step, ++i) {
+        const int s = i % DSS_STAGES;
+        if (!mbar_wait(&empty[s], ((i / DSS_STAGES) & 1) ^ 1, abort_flag)) break;
+        const int h = tile % H, n = (tile / H) % n_chunks, b = tile / (H * n_chunks);
+        const int row0 = b * T + n * CHUNK;
+        mbar_expect_tx(&full[s], 3 * TILE_BYTES);
+        tma_load_2d(ring + s * 3 * TILE_BYTES, &tm_qkvgu, &full[s], h * HD, row0);
+        tma_load_2d(ring + s * 3 * TILE_BYTES + TILE_BYTES, &tm_dy, &full[s], h * HD, row0);
+        tma_load_2d(ring + s * 3 * TILE_BYTES + 2 * TILE_BYTES, &tm_qkvgu, &full[s], 3 * d + h * HD, row0);
+      }
+    }
+  } else if (warp < 8) {
+    const int r = tid & 127, q = tid >> 7;   // row, and which four of its eight pieces
+    float2 cs[16];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int t = 0; t < 4; ++t) cs[j * 4 + t] = rope[((q * 4 + j) * 4 + t) * CHUNK + r];
+    int i = 0;
+    for (int tile = first; tile < tiles; tile += step, ++i) {
+      const int s = i % DSS_STAGES;
+      uint8_t* sQ = ring + s * 3 * TILE_BYTES;
+      uint8_t* sD = sQ + TILE_BYTES;
+      uint8_t* sGate = sD + TILE_BYTES;
+      const bool ok = mbar_wait(&full[s], (i / DSS_STAGES) & 1, abort_flag);
+      if (ok) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4* pq = reinterpret_cast<uint4*>(tile_chunk(sQ, r, q * 4 + j));
+          uint4* pd = reinterpret_cast<uint4*>(tile_chunk(sD, r, q * 4 + j));
+          uint4 qv = *pq, dv = *pd;
+          const uint4 gv = *reinterpret_cast<const uint4*>(tile_chunk(sGate, r, q * 4 + j));
+          uint32_t* qw = reinterpret_cast<uint32_t*>(&qv);
+          uint32_t* dw = reinterpret_cast<uint32_t*>(&dv);
+          const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&gv);
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const float2 x = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&qw[t]));
+            const float2 c = cs[j * 4 + t];
+            qw[t] = pack_bf16x2(x.x * c.x - x.y * c.y, x.y * c.x + x.x * c.y);
+            const float2 dyv = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&dw[t]));
+            const float2 gf = __bfloat1622float2(gb[t]);
+            dw[t] = pack_bf16x2(dyv.x * (1.f - sigmoid_f(gf.x)) * 0.125f, dyv.y * (1.f - sigmoid_f(gf.y)) * 0.125f);
+          }
+          *pq = qv;
+          *pd = dv;
+        }
+      }
+      fence_proxy_async_smem();
+      // the workers' barrier doubles as their vote: if any of them gave up on the tile, all leave together
+      uint32_t any_bad;
+      asm volatile(
+          "{\n"
+          ".reg .pred p, q;\n"
+          "setp.ne.u32 q, %1, 0;\n"
+          "bar.red.or.pred p, 2, 256, q;\n"
+          "selp.u32 %0, 1, 0, p;\n"
+          "}\n"
+          : "=r"(any_bad)
+          : "r"(ok ? 0u : 1u)
+          : "memory");
+      if (any_bad) break;
+      if (tid == 0) {
+        const int buf = i & 1;
+        if (mbar_wait(&tempty[buf], ((i >> 1) & 1) ^ 1, abort_flag)) {
+          tc_fence_after_sync();
+          // D[128 x 64]: rows 0..63 = Qr^T (dmem / 8); rows 64..127 repeat them (zero stride between A's atoms)
+          constexpr uint32_t idesc = make_idesc_bf16(128, 64, true, true);
+#pragma unroll
+          for (int k = 0; k < CHUNK / 16; ++k)
+            umma_bf16(tmem + buf * 64, make_smem_desc_sw128(smem_u32(sQ) + k * 2048, 0, 1024),
+                      make_smem_desc_sw128(smem_u32(sD) + k * 2048, 0, 1024), idesc, k > 0);
+          umma_commit(&empty[s]);
+          umma_commit(&tfull[buf]);
+        }
+      }
+    }
+  } else {  // warps 8, 9: accumulator lanes 0..31 and 32..63
+    const int ew = warp - 8, row = ew * 32 + lane;
+    int i = 0;
+    for (int tile = first; tile < tiles; tile += step, ++i) {
+      const int buf = i & 1;
+      uint32_t landed = 0;
+      if (lane == 0) landed = mbar_wait(&tfull[buf], (i >> 1) & 1, abort_flag) ? 1u : 0u;
+      if (__shfl_sync(0xffffffffu, landed, 0) == 0u) break;   // the whole warp leaves together
+      tc_fence_after_sync();
+      uint8_t* st = staging + buf * 16384;
+      if (lane == 0) tma_store_wait_read0();   // the store issued two tiles ago from this buffer has read it
+      __syncwarp();
+#pragma unroll
+      for (int c = 0; c < HD; c += 16) {
+        uint32_t v[16];
+        tmem_ld_32x32b_x16(tmem + buf * 64 + (static_cast<uint32_t>(ew * 32) << 16) + c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; j += 4) {
+          const int col = c + j;
+          uint8_t* dst = st + (col >> 5) * 8192 + row * 128 + ((((col & 31) >> 2) ^ (row & 7)) << 4);
+          *reinterpret_cast<float4*>(dst) =
+              make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+        }
+      }
+      tc_fence_before_sync();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&tempty[buf]);   // this warp's 32 lanes of the accumulator have been read
+        tma_store_2d(&tm_out, st + ew * 4096, 0, tile * HD + ew * 32);
+        tma_store_2d(&tm_out, st + 8192 + ew * 4096, 32, tile * HD + ew * 32);
+        tma_store_commit();
+      }
+    }
+    if (lane == 0) tma_store_wait_all();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (tid == 0 && *abort_flag != 0 && error_flag != nullptr) atomicExch(error_flag, 4);
+  if (warp == 8) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, 128);
+  }
+}
+
 // =============================================================================== reverse scan
 // The reverse scan needs the state every chunk saw.  Those are recomputed from the writes in groups of
 // SCAN_GROUP chunks: a first pass keeps the state at every group boundary, then the groups are walked
@@ -646,8 +826,20 @@ extern "C" int ws_attn_dstate(const void* qkvgu, const void* dy, const float* ro
     configured = true;
   }
   const int tiles = B * (T / CHUNK) * H;
-  launch_dependent(dstate_kernel, dim3(tiles), dim3(128), DS_SMEM, stream, tm, td, to, reinterpret_cast<const float2*>(rope), T, H, d,
-                                                 error_flag);
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        cudaFuncSetAttribute(dstate_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DSS_SMEM) != cudaSuccess)
+      return -20;
+  }
+  if (ws_attn_stream_form() != 0)
+    launch_dependent(dstate_stream_kernel, dim3(tiles < sms ? tiles : sms), dim3(DSS_THREADS), DSS_SMEM, stream, tm, td, to,
+                     reinterpret_cast<const float2*>(rope), T, H, d, tiles, error_flag);
+  else
+    launch_dependent(dstate_kernel, dim3(tiles), dim3(128), DS_SMEM, stream, tm, td, to, reinterpret_cast<const float2*>(rope), T, H, d,
+                     error_flag);
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }

@@ -18,6 +18,8 @@
 #include "ws_launch.h"
 #include "attention_common.cuh"
 
+#include <cstdlib>
+
 namespace ws {
 
 extern "C" void ws_count_launch(void);
@@ -119,6 +121,189 @@ chunk_writes_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_c
   if (warp == 0) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, 64);
+  }
+}
+
+// =============================================================================== writes, streaming form
+// The same product as chunk_writes_kernel, as one persistent CTA per SM with specialised warps:
+//
+//   warp 10      producer: TMA loads of the K and U tiles of tile i into stage i % 4 of a ring (4 x 32 KiB)
+//   warps 0..7   workers (256 threads): thread (row r, half q) turns four of the eight 16-byte pieces of row r of K
+//                into tanh(rope(K)) and of U into tanh(U), in place; its 16 (cos, sin) pairs are loaded once, since
+//                they depend on the row and the column only.  Worker thread 0 then issues the tile's eight MMAs into
+//                TMEM buffer i % 2; their completion frees the ring stage and hands the buffer to the epilogue.
+//   warps 8, 9   epilogue (accumulator lanes 0..63): TMEM -> x 1/128 -> swizzled FP32 staging tile -> TMA store
+//
+// so the loads of the next three tiles, the element-wise work of the current one and the store of the previous
+// one overlap; chunk_writes_kernel gets its overlap from six independent CTAs per SM instead, each of which walks
+// the chain load -> element-wise -> MMA -> store alone.  Results are bit-identical (same arithmetic, same MMA order).
+constexpr int WS_STAGES = 4;
+constexpr int WS_THREADS = 352;
+constexpr int WS_SMEM = WS_STAGES * 2 * TILE_BYTES + 2 * 16384 + 1024 + 256;
+
+__global__ void __launch_bounds__(WS_THREADS, 1)
+chunk_writes_stream_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_constant__ CUtensorMap tm_out,
+                           const float2* __restrict__ rope, int T, int H, int d, int tiles, int* error_flag) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  uint8_t* ring = smem;                                   // stage s: K at s * 32 KiB, U 16 KiB behind it
+  uint8_t* staging = smem + WS_STAGES * 2 * TILE_BYTES;   // two FP32 [64 x 64] tiles
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + 2 * 16384);
+  uint64_t* full = bars;                    // [4] tile landed
+  uint64_t* empty = bars + WS_STAGES;       // [4] MMAs have read the stage
+  uint64_t* tfull = bars + 2 * WS_STAGES;   // [2] accumulator complete
+  uint64_t* tempty = tfull + 2;             // [2] accumulator read by both epilogue warps
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_chunks = T / CHUNK;
+
+  if (tid == 0) {
+    for (int s = 0; s < WS_STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tfull[b], 1);
+      mbar_init(&tempty[b], 2);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_qkvgu);
+    tma_prefetch_desc(&tm_out);
+  }
+  if (warp == 8) {
+    tmem_alloc(tmem_slot, 128);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  pdl_launch_dependents();
+  pdl_wait();
+
+  const int first = blockIdx.x, step = gridDim.x;
+  if (warp == 10) {
+    if (lane == 0) {
+      int i = 0;
+      for (int tile = first; tile < tiles; tile += step, ++i) {
+        const int s = i % WS_STAGES;
+        if (!mbar_wait(&empty[s], ((i / WS_STAGES) & 1) ^ 1, abort_flag)) break;
+        const int h = tile % H, n = (tile / H) % n_chunks, b = tile / (H * n_chunks);
+        const int row0 = b * T + n * CHUNK;
+        mbar_expect_tx(&full[s], 2 * TILE_BYTES);
+        tma_load_2d(ring + s * 2 * TILE_BYTES, &tm_qkvgu, &full[s], 1 * d + h * HD, row0);
+        tma_load_2d(ring + s * 2 * TILE_BYTES + TILE_BYTES, &tm_qkvgu, &full[s], 4 * d + h * HD, row0);
+      }
+    }
+  } else if (warp < 8) {
+    const int r = tid & 127, q = tid >> 7;   // row, and which four of its eight pieces
+    float2 cs[16];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int t = 0; t < 4; ++t) cs[j * 4 + t] = rope[((q * 4 + j) * 4 + t) * CHUNK + r];
+    int i = 0;
+    for (int tile = first; tile < tiles; tile += step, ++i) {
+      const int s = i % WS_STAGES;
+      uint8_t* sK = ring + s * 2 * TILE_BYTES;
+      uint8_t* sU = sK + TILE_BYTES;
+      const bool ok = mbar_wait(&full[s], (i / WS_STAGES) & 1, abort_flag);
+      if (ok) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4* pk = reinterpret_cast<uint4*>(tile_chunk(sK, r, q * 4 + j));
+          uint4* pu = reinterpret_cast<uint4*>(tile_chunk(sU, r, q * 4 + j));
+          uint4 kv = *pk, uv = *pu;
+          uint32_t* kw = reinterpret_cast<uint32_t*>(&kv);
+          uint32_t* uw = reinterpret_cast<uint32_t*>(&uv);
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const float2 x = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&kw[t]));
+            const float2 c = cs[j * 4 + t];
+            kw[t] = pack_bf16x2(tanh_fast(x.x * c.x - x.y * c.y), tanh_fast(x.y * c.x + x.x * c.y));
+            const float2 u = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&uw[t]));
+            uw[t] = pack_bf16x2(tanh_fast(u.x), tanh_fast(u.y));
+          }
+          *pk = kv;
+          *pu = uv;
+        }
+      }
+      fence_proxy_async_smem();
+      // the workers' barrier doubles as their vote: if any of them gave up on the tile, all leave together
+      uint32_t any_bad;
+      asm volatile(
+          "{\n"
+          ".reg .pred p, q;\n"
+          "setp.ne.u32 q, %1, 0;\n"
+          "bar.red.or.pred p, 2, 256, q;\n"
+          "selp.u32 %0, 1, 0, p;\n"
+          "}\n"
+          : "=r"(any_bad)
+          : "r"(ok ? 0u : 1u)
+          : "memory");
+      if (any_bad) break;
+      if (tid == 0) {
+        const int buf = i & 1;
+        if (mbar_wait(&tempty[buf], ((i >> 1) & 1) ^ 1, abort_flag)) {
+          tc_fence_after_sync();
+          // D[128 x 64]: rows 0..63 = tK^T tU.  A is read MN-major with a zero stride between its two 64-wide
+          // atoms, so rows 64..127 repeat rows 0..63 and are ignored.
+          constexpr uint32_t idesc = make_idesc_bf16(128, 64, true, true);
+#pragma unroll
+          for (int k = 0; k < CHUNK / 16; ++k)
+            umma_bf16(tmem + buf * 64, make_smem_desc_sw128(smem_u32(sK) + k * 2048, 0, 1024),
+                      make_smem_desc_sw128(smem_u32(sU) + k * 2048, 0, 1024), idesc, k > 0);
+          umma_commit(&empty[s]);
+          umma_commit(&tfull[buf]);
+        }
+      }
+    }
+  } else {  // warps 8, 9: accumulator lanes 0..31 and 32..63
+    const int ew = warp - 8, row = ew * 32 + lane;
+    int i = 0;
+    for (int tile = first; tile < tiles; tile += step, ++i) {
+      const int buf = i & 1;
+      uint32_t landed = 0;
+      if (lane == 0) landed = mbar_wait(&tfull[buf], (i >> 1) & 1, abort_flag) ? 1u : 0u;
+      if (__shfl_sync(0xffffffffu, landed, 0) == 0u) break;   // the whole warp leaves together
+      tc_fence_after_sync();
+      uint8_t* st = staging + buf * 16384;
+      if (lane == 0) tma_store_wait_read0();   // the store issued two tiles ago from this buffer has read it
+      __syncwarp();
+#pragma unroll
+      for (int c = 0; c < HD; c += 16) {
+        uint32_t v[16];
+        tmem_ld_32x32b_x16(tmem + buf * 64 + (static_cast<uint32_t>(ew * 32) << 16) + c, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; j += 4) {
+          const int col = c + j;
+          uint8_t* dst = st + (col >> 5) * 8192 + row * 128 + ((((col & 31) >> 2) ^ (row & 7)) << 4);
+          *reinterpret_cast<float4*>(dst) =
+              make_float4(__uint_as_float(v[j]) * (1.f / CHUNK), __uint_as_float(v[j + 1]) * (1.f / CHUNK),
+                          __uint_as_float(v[j + 2]) * (1.f / CHUNK), __uint_as_float(v[j + 3]) * (1.f / CHUNK));
+        }
+      }
+      tc_fence_before_sync();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&tempty[buf]);   // this warp's 32 lanes of the accumulator have been read
+        tma_store_2d(&tm_out, st + ew * 4096, 0, tile * HD + ew * 32);
+        tma_store_2d(&tm_out, st + 8192 + ew * 4096, 32, tile * HD + ew * 32);
+        tma_store_commit();
+      }
+    }
+    if (lane == 0) tma_store_wait_all();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (tid == 0 && *abort_flag != 0 && error_flag != nullptr) atomicExch(error_flag, 2);
+  if (warp == 8) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, 128);
   }
 }
 
@@ -359,6 +544,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_const
 
 using namespace ws;
 
+// Which form the tile kernels of the attention block take: 1 = persistent streaming CTAs, 0 = one tile per CTA,
+// -1 = the process default (streaming unless WS_ATTN_STREAM=0 is in the environment).
+static int g_attn_stream_mode = -1;
+extern "C" void ws_attn_set_stream_mode(int mode) { g_attn_stream_mode = mode; }
+extern "C" int ws_attn_stream_form(void) {
+  if (g_attn_stream_mode >= 0) return g_attn_stream_mode != 0;
+  static const bool from_env = [] {
+    const char* e = std::getenv("WS_ATTN_STREAM");
+    return e == nullptr || e[0] != '0';
+  }();
+  return from_env ? 1 : 0;
+}
+
 extern "C" int ws_chunk_writes(const void* qkvgu, const float* rope, float* writes, int B, int T, int H, int d,
                                int* error_flag, cudaStream_t stream) {
   if (T % CHUNK != 0 || d != H * HD) return -1;
@@ -375,8 +573,21 @@ extern "C" int ws_chunk_writes(const void* qkvgu, const float* rope, float* writ
   CUtensorMap to;
   rc = make_map_f32(&to, writes, HD, (uint64_t)tiles * HD, HD, 32, 32);
   if (rc) return rc;
-  launch_dependent(chunk_writes_kernel, dim3(tiles), dim3(128), WR_SMEM, stream, tm, to, reinterpret_cast<const float2*>(rope), T, H, d,
-                                                       error_flag);
+  const bool stream_form = ws_attn_stream_form() != 0;
+  static int sms = 0;
+  if (stream_form && sms == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        cudaFuncSetAttribute(chunk_writes_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, WS_SMEM) != cudaSuccess)
+      return -20;
+  }
+  if (stream_form)
+    launch_dependent(chunk_writes_stream_kernel, dim3(tiles < sms ? tiles : sms), dim3(WS_THREADS), WS_SMEM, stream, tm, to,
+                     reinterpret_cast<const float2*>(rope), T, H, d, tiles, error_flag);
+  else
+    launch_dependent(chunk_writes_kernel, dim3(tiles), dim3(128), WR_SMEM, stream, tm, to, reinterpret_cast<const float2*>(rope), T, H, d,
+                     error_flag);
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }

@@ -134,6 +134,10 @@ int ws_embed_bwd(const void* dx, int dx_bf16, const long long* sorted_ids, const
 // ----------------------------------------------------------------------------- attention / memory
 // qkvgu: BF16 [B*T, 5d] (Q,K,V,gate,U); chunk 128, head_dim 64, d = H*64.  rope: float2 [128][32].
 // writes: FP32 [B, T/128, H, 64, 64] = tanh(rope(K))^T tanh(U) / 128.
+// Form of the attention block's tile kernels: 1 persistent streaming CTAs, 0 one tile per CTA, -1 process default
+// (streaming unless WS_ATTN_STREAM=0).
+void ws_attn_set_stream_mode(int mode);
+int ws_attn_stream_form(void);   // the resolved choice: 1 streaming, 0 one tile per CTA
 int ws_chunk_writes(const void* qkvgu, const float* rope, float* writes, int B, int T, int H, int d,
                     int* error_flag, cudaStream_t stream);
 // states (BF16, may be NULL): mixed state read by each chunk; final_* (FP32 [B,H,64,64], may be NULL);
