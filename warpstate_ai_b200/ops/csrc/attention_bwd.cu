@@ -231,7 +231,8 @@ dstate_stream_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_
           for (int t = 0; t < 4; ++t) {
             const float2 x = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&qw[t]));
             const float2 c = cs[j * 4 + t];
-            qw[t] = pack_bf16x2(x.x * c.x - x.y * c.y, x.y * c.x + x.x * c.y);
+            const float2 qr = rope_rotate(x, c);
+            qw[t] = pack_bf16x2(qr.x, qr.y);
             const float2 dyv = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&dw[t]));
             const float2 gf = __bfloat1622float2(gb[t]);
             dw[t] = pack_bf16x2(dyv.x * (1.f - sigmoid_f(gf.x)) * 0.125f, dyv.y * (1.f - sigmoid_f(gf.y)) * 0.125f);

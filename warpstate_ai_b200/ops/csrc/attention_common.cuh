@@ -16,6 +16,18 @@ __device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
 }
 __device__ __forceinline__ float sigmoid_f(float x) { return sigmoid_fast(x); }
 
+// The arithmetic that two forms of a kernel must share bit for bit is written with explicitly rounded operations,
+// so that the compiler's choice of which product to fuse into which addition cannot differ between them.
+__device__ __forceinline__ float2 rope_rotate(float2 x, float2 cs) {  // (cos, sin) of the pair's angle
+  return make_float2(__fmaf_rn(x.x, cs.x, -__fmul_rn(x.y, cs.y)), __fmaf_rn(x.y, cs.x, __fmul_rn(x.x, cs.y)));
+}
+// exp2((s - m) * k): the unnormalised softmax weight of a score
+__device__ __forceinline__ float softmax_term(float s, float m, float k) { return exp2f(__fmul_rn(__fsub_rn(s, m), k)); }
+// g * (o * inv_l) + (1 - g) * (mem / 8)
+__device__ __forceinline__ float gate_blend(float g, float o, float inv_l, float mem) {
+  return __fmaf_rn(g, __fmul_rn(o, inv_l), __fmul_rn(__fsub_rn(1.f, g), __fmul_rn(mem, 0.125f)));
+}
+
 // Address of the 16-byte chunk `j` (8 BF16 columns) of row `r` in a [rows x 64] swizzled tile.
 __device__ __forceinline__ uint8_t* tile_chunk(uint8_t* tile, int r, int j) {
   return tile + r * 128 + ((j ^ (r & 7)) << 4);
@@ -34,13 +46,7 @@ __device__ __forceinline__ void rope_tanh_row(uint8_t* tile, int r, const float2
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
       float2 x = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&w[t]));
-      if (do_rope) {
-        const float2 cs = rope[(j * 4 + t) * CHUNK + r];
-        const float a = x.x * cs.x - x.y * cs.y;
-        const float b = x.y * cs.x + x.x * cs.y;
-        x.x = a;
-        x.y = b;
-      }
+      if (do_rope) x = rope_rotate(x, rope[(j * 4 + t) * CHUNK + r]);
       if (do_tanh) {
         x.x = tanh_fast(x.x);
         x.y = tanh_fast(x.y);

@@ -222,7 +222,8 @@ chunk_writes_stream_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const _
           for (int t = 0; t < 4; ++t) {
             const float2 x = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&kw[t]));
             const float2 c = cs[j * 4 + t];
-            kw[t] = pack_bf16x2(tanh_fast(x.x * c.x - x.y * c.y), tanh_fast(x.y * c.x + x.x * c.y));
+            const float2 kr = rope_rotate(x, c);
+            kw[t] = pack_bf16x2(tanh_fast(kr.x), tanh_fast(kr.y));
             const float2 u = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&uw[t]));
             uw[t] = pack_bf16x2(tanh_fast(u.x), tanh_fast(u.y));
           }
@@ -464,8 +465,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_const
       tmem_ld_wait();
 #pragma unroll
       for (int j = 0; j < 32; j += 2) {
-        const float p0 = (cc * 32 + j <= tid) ? exp2f((__uint_as_float(r[j]) - row_max) * kScale) : 0.f;
-        const float p1 = (cc * 32 + j + 1 <= tid) ? exp2f((__uint_as_float(r[j + 1]) - row_max) * kScale) : 0.f;
+        const float p0 = (cc * 32 + j <= tid) ? softmax_term(__uint_as_float(r[j]), row_max, kScale) : 0.f;
+        const float p1 = (cc * 32 + j + 1 <= tid) ? softmax_term(__uint_as_float(r[j + 1]), row_max, kScale) : 0.f;
         const __nv_bfloat162 v = __floats2bfloat162_rn(p0, p1);
         const float2 back = __bfloat1622float2(v);
         row_sum += back.x + back.y;  // normalise by what the MMA will actually sum
@@ -515,9 +516,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_const
       for (int t = 0; t < 4; ++t) {
         const float2 gf = __bfloat1622float2(gb[t]);
         const float g0 = sigmoid_f(gf.x), g1 = sigmoid_f(gf.y);
-        const float o0 = __uint_as_float(ro[j + 2 * t]) * inv_l, o1 = __uint_as_float(ro[j + 2 * t + 1]) * inv_l;
-        const float m0 = __uint_as_float(rm[j + 2 * t]) * 0.125f, m1 = __uint_as_float(rm[j + 2 * t + 1]) * 0.125f;
-        ow[t] = pack_bf16x2(g0 * o0 + (1.f - g0) * m0, g1 * o1 + (1.f - g1) * m1);
+        ow[t] = pack_bf16x2(gate_blend(g0, __uint_as_float(ro[j + 2 * t]), inv_l, __uint_as_float(rm[j + 2 * t])),
+                            gate_blend(g1, __uint_as_float(ro[j + 2 * t + 1]), inv_l, __uint_as_float(rm[j + 2 * t + 1])));
       }
       *reinterpret_cast<uint4*>(tile_chunk(sQ, tid, chunk)) = out;
     }
@@ -537,6 +537,294 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_const
   if (warp == 0) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, 128);
+  }
+}
+
+// =============================================================================== attention, streaming form
+// attn_fwd_kernel as one persistent CTA per SM with specialised warps (17 warps):
+//
+//   warp 16        producer: TMA loads of tile i (Q, K, gate, V, state: 72 KiB) into stage i % 3 of a ring
+//   warps 0..7     RoPE workers: thread (row r, half q) rotates four of the eight 16-byte pieces of row r of Q and of
+//                  K in place (its 16 (cos, sin) pairs live in registers); worker 0 then issues S = Qr Kr^T and
+//                  Mem = Qr State into TMEM set i % 2 -- Mem does not depend on the softmax, so it rides with S
+//   warps 8..11    softmax group 0 (tiles 0, 2, 4, ...), warps 12..15 softmax group 1 (tiles 1, 3, ...): one thread per
+//                  token row, as in attn_fwd_kernel: causal softmax straight out of TMEM, unnormalised P (BF16) into
+//                  the tile's K and Q space (both dead once S and Mem are complete; the gate tile stays where it is),
+//                  O = P V issued by the group's first thread into the first 64 columns of S, gate blend from O, Mem
+//                  and the gate tile into the Q space, one TMA store per warp; the store's read of the tile releases
+//                  the ring stage, the group's last TMEM read releases the TMEM set.
+//
+// Two tiles are in their softmax / blend phase at any time while a third is being rotated and a fourth loaded;
+// attn_fwd_kernel gets its overlap from three independent CTAs per SM, each walking the whole chain alone.
+// TMEM: set g = columns [192 g, 192 g + 192): S 128 (O reuses its first 64), Mem 64.  Bit-identical results.
+constexpr int AS_STAGES = 3;
+constexpr int AS_THREADS = 17 * 32;
+constexpr int AS_STAGE_BYTES = 4 * TILE_BYTES + 8192;
+constexpr int AS_SMEM = AS_STAGES * AS_STAGE_BYTES + 1024 + 256;
+
+__global__ void __launch_bounds__(AS_THREADS, 1)
+attn_fwd_stream_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_constant__ CUtensorMap tm_state,
+                       const __grid_constant__ CUtensorMap tm_y, const float2* __restrict__ rope, int T, int H, int d,
+                       int tiles, int* error_flag) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align1024(smem_raw);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + AS_STAGES * AS_STAGE_BYTES);
+  uint64_t* full = bars;                     // [3] stage loaded
+  uint64_t* empty = bars + AS_STAGES;        // [3] stage released (4 warps of the owning group)
+  uint64_t* sfull = bars + 2 * AS_STAGES;    // [2] S and Mem complete
+  uint64_t* ofull = sfull + 2;               // [2] O complete
+  uint64_t* setfree = ofull + 2;             // [2] TMEM set read out (4 warps)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(setfree + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_chunks = T / CHUNK;
+
+  if (tid == 0) {
+    for (int s = 0; s < AS_STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 4);
+    }
+    for (int g = 0; g < 2; ++g) {
+      mbar_init(&sfull[g], 1);
+      mbar_init(&ofull[g], 1);
+      mbar_init(&setfree[g], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_qkvgu);
+    tma_prefetch_desc(&tm_state);
+    tma_prefetch_desc(&tm_y);
+  }
+  if (warp == 8) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  pdl_launch_dependents();
+  pdl_wait();
+
+  const int first = blockIdx.x, step = gridDim.x;
+  auto stage_ptr = [&](int s) { return smem + s * AS_STAGE_BYTES; };  // Q | K | gate | V | state
+
+  if (warp == 16) {
+    if (lane == 0) {
+      int i = 0;
+      for (int tile = first; tile < tiles; tile += step, ++i) {
+        const int s = i % AS_STAGES;
+        if (!mbar_wait(&empty[s], ((i / AS_STAGES) & 1) ^ 1, abort_flag)) break;
+        const int h = tile % H, n = (tile / H) % n_chunks, b = tile / (H * n_chunks);
+        const int row0 = b * T + n * CHUNK;
+        uint8_t* st = stage_ptr(s);
+        mbar_expect_tx(&full[s], AS_STAGE_BYTES);
+        tma_load_2d(st, &tm_qkvgu, &full[s], 0 * d + h * HD, row0);
+        tma_load_2d(st + TILE_BYTES, &tm_qkvgu, &full[s], 1 * d + h * HD, row0);
+        tma_load_2d(st + 2 * TILE_BYTES, &tm_qkvgu, &full[s], 3 * d + h * HD, row0);
+        tma_load_2d(st + 3 * TILE_BYTES, &tm_qkvgu, &full[s], 2 * d + h * HD, row0);
+        tma_load_2d(st + 4 * TILE_BYTES, &tm_state, &full[s], 0, tile * HD);
+      }
+    }
+  } else if (warp < 8) {
+    // ------------------------------------------------------------------ RoPE workers + S / Mem issue
+    const int r = tid & 127, q = tid >> 7;
+    float2 cs[16];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int t = 0; t < 4; ++t) cs[j * 4 + t] = rope[((q * 4 + j) * 4 + t) * CHUNK + r];
+    int i = 0;
+    for (int tile = first; tile < tiles; tile += step, ++i) {
+      const int s = i % AS_STAGES, g = i & 1;
+      uint8_t* sQ = stage_ptr(s);
+      uint8_t* sK = sQ + TILE_BYTES;
+      uint8_t* sSt = sQ + 4 * TILE_BYTES;
+      const bool ok = mbar_wait(&full[s], (i / AS_STAGES) & 1, abort_flag);
+      if (ok) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4* pq = reinterpret_cast<uint4*>(tile_chunk(sQ, r, q * 4 + j));
+          uint4* pk = reinterpret_cast<uint4*>(tile_chunk(sK, r, q * 4 + j));
+          uint4 qv = *pq, kv = *pk;
+          uint32_t* qw = reinterpret_cast<uint32_t*>(&qv);
+          uint32_t* kw = reinterpret_cast<uint32_t*>(&kv);
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const float2 c = cs[j * 4 + t];
+            const float2 x = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&qw[t]));
+            const float2 qr = rope_rotate(x, c);
+            qw[t] = pack_bf16x2(qr.x, qr.y);
+            const float2 kr = rope_rotate(__bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&kw[t])), c);
+            kw[t] = pack_bf16x2(kr.x, kr.y);
+          }
+          *pq = qv;
+          *pk = kv;
+        }
+      }
+      fence_proxy_async_smem();
+      uint32_t any_bad;
+      asm volatile(
+          "{\n"
+          ".reg .pred p, q;\n"
+          "setp.ne.u32 q, %1, 0;\n"
+          "bar.red.or.pred p, 2, 256, q;\n"
+          "selp.u32 %0, 1, 0, p;\n"
+          "}\n"
+          : "=r"(any_bad)
+          : "r"(ok ? 0u : 1u)
+          : "memory");
+      if (any_bad) break;
+      if (tid == 0 && mbar_wait(&setfree[g], ((i >> 1) & 1) ^ 1, abort_flag)) {
+        tc_fence_after_sync();
+        const uint32_t t_s = tmem + g * 192, t_m = t_s + 128;
+        constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
+        constexpr uint32_t idesc_m = make_idesc_bf16(128, 64, false, true);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          umma_bf16(t_s, make_smem_desc_sw128(smem_u32(sQ) + k * 32, 0, 1024),
+                    make_smem_desc_sw128(smem_u32(sK) + k * 32, 0, 1024), idesc_s, k > 0);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)  // Mem = Qr State
+          umma_bf16(t_m, make_smem_desc_sw128(smem_u32(sQ) + k * 32, 0, 1024),
+                    make_smem_desc_sw128(smem_u32(sSt) + k * 2048, 0, 1024), idesc_m, k > 0);
+        umma_commit(&sfull[g]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax groups
+    const int g = (warp - 8) >> 2;
+    const int gt = tid - (256 + g * 128);       // row of the tile = TMEM lane
+    const int wq = gt >> 5;                     // lane quarter of this warp
+    const uint32_t t_s = tmem + g * 192, t_o = t_s, t_m = t_s + 128;
+    const uint32_t lane_base = static_cast<uint32_t>(wq * 32) << 16;
+    const float kScale = 0.125f * 1.4426950408889634f;  // fold log2(e)
+    const int last_chunk = wq;  // columns beyond 32*wq+31 are masked for the whole warp
+    int i = g;
+    for (int tile = first + g * step; tile < tiles; tile += 2 * step, i += 2) {
+      const int s = i % AS_STAGES, k2 = i >> 1;
+      uint8_t* sQ = stage_ptr(s);
+      uint8_t* sK = sQ + TILE_BYTES;
+      uint8_t* sG = sQ + 2 * TILE_BYTES;
+      uint8_t* sV = sQ + 3 * TILE_BYTES;
+      const int h = tile % H, n = (tile / H) % n_chunks, b = tile / (H * n_chunks);
+      const int row0 = b * T + n * CHUNK;
+      uint32_t landed = 0;
+      if (lane == 0) landed = mbar_wait(&sfull[g], k2 & 1, abort_flag) ? 1u : 0u;
+      bool ok = __shfl_sync(0xffffffffu, landed, 0) != 0u;
+      tc_fence_after_sync();
+      float row_sum = 0.f;
+      if (ok) {
+        float row_max = -INFINITY;
+        for (int cc = 0; cc <= last_chunk; ++cc) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(t_s + lane_base + cc * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (cc * 32 + j <= gt) row_max = fmaxf(row_max, __uint_as_float(v[j]));
+        }
+        for (int cc = 0; cc < 4; ++cc) {
+          uint32_t pk[16];
+          if (cc <= last_chunk) {
+            uint32_t v[32];
+            tmem_ld_32x32b_x32(t_s + lane_base + cc * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              const float p0 = (cc * 32 + j <= gt) ? softmax_term(__uint_as_float(v[j]), row_max, kScale) : 0.f;
+              const float p1 = (cc * 32 + j + 1 <= gt) ? softmax_term(__uint_as_float(v[j + 1]), row_max, kScale) : 0.f;
+              const __nv_bfloat162 pv = __floats2bfloat162_rn(p0, p1);
+              const float2 back = __bfloat1622float2(pv);
+              row_sum += back.x + back.y;  // normalise by what the MMA will actually sum
+              pk[j >> 1] = *reinterpret_cast<const uint32_t*>(&pv);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) pk[j] = 0u;
+          }
+          // columns 0..63 of P go to the K tile's space, columns 64..127 to the Q tile's
+          uint8_t* half = (cc < 2) ? sK : sQ;
+          const int j0 = (cc & 1) * 4;
+#pragma unroll
+          for (int w4 = 0; w4 < 4; ++w4)
+            *reinterpret_cast<uint4*>(tile_chunk(half, gt, j0 + w4)) =
+                make_uint4(pk[4 * w4], pk[4 * w4 + 1], pk[4 * w4 + 2], pk[4 * w4 + 3]);
+        }
+      }
+      tc_fence_before_sync();  // every thread's reads of S precede the MMA that overwrites its first columns
+      fence_proxy_async_smem();
+      uint32_t any_bad;
+      if (g == 0)
+        asm volatile("{\n .reg .pred p, q;\n setp.ne.u32 q, %1, 0;\n bar.red.or.pred p, 3, 128, q;\n selp.u32 %0, 1, 0, p;\n}\n"
+                     : "=r"(any_bad) : "r"(ok ? 0u : 1u) : "memory");
+      else
+        asm volatile("{\n .reg .pred p, q;\n setp.ne.u32 q, %1, 0;\n bar.red.or.pred p, 4, 128, q;\n selp.u32 %0, 1, 0, p;\n}\n"
+                     : "=r"(any_bad) : "r"(ok ? 0u : 1u) : "memory");
+      if (any_bad) break;
+      if (gt == 0) {
+        tc_fence_after_sync();
+        constexpr uint32_t idesc_o = make_idesc_bf16(128, 64, false, true);
+#pragma unroll
+        for (int k = 0; k < CHUNK / 16; ++k)
+          umma_bf16(t_o, make_smem_desc_sw128(smem_u32((k >> 2) ? sQ : sK) + (k & 3) * 32, 0, 1024),
+                    make_smem_desc_sw128(smem_u32(sV) + k * 2048, 0, 1024), idesc_o, k > 0);
+        umma_commit(&ofull[g]);
+      }
+      landed = 0;
+      if (lane == 0) landed = mbar_wait(&ofull[g], k2 & 1, abort_flag) ? 1u : 0u;
+      ok = __shfl_sync(0xffffffffu, landed, 0) != 0u;
+      tc_fence_after_sync();
+      if (ok) {
+        // ---- gate blend into the (now idle) Q tile, then one TMA store of the warp's 32 rows
+        const float inv_l = 1.f / row_sum;
+#pragma unroll
+        for (int c = 0; c < HD; c += 16) {
+          uint32_t ro[16], rm[16];
+          tmem_ld_32x32b_x16(t_o + lane_base + c, ro);
+          tmem_ld_32x32b_x16(t_m + lane_base + c, rm);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; j += 8) {
+            const int chunk = (c + j) >> 3;
+            const uint4 gq = *reinterpret_cast<const uint4*>(tile_chunk(sG, gt, chunk));
+            const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&gq);
+            uint4 out;
+            uint32_t* ow = reinterpret_cast<uint32_t*>(&out);
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              const float2 gf = __bfloat1622float2(gb[t]);
+              const float g0 = sigmoid_f(gf.x), g1 = sigmoid_f(gf.y);
+              ow[t] = pack_bf16x2(gate_blend(g0, __uint_as_float(ro[j + 2 * t]), inv_l, __uint_as_float(rm[j + 2 * t])),
+                                  gate_blend(g1, __uint_as_float(ro[j + 2 * t + 1]), inv_l, __uint_as_float(rm[j + 2 * t + 1])));
+            }
+            *reinterpret_cast<uint4*>(tile_chunk(sQ, gt, chunk)) = out;
+          }
+        }
+      }
+      tc_fence_before_sync();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&setfree[g]);   // this warp's lanes of S / O / Mem have been read
+        if (ok) {
+          tma_store_2d(&tm_y, sQ + wq * 4096, h * HD, row0 + wq * 32);
+          tma_store_commit();
+        }
+        tma_store_wait_read0();
+        mbar_arrive(&empty[s]);     // this warp no longer touches the stage
+      }
+      __syncwarp();
+      // a warp that gave up does not leave alone: its next wait fails at once (the abort flag is up), and the
+      // group's vote at the next barrier takes all four warps out together
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (tid == 0 && *abort_flag != 0 && error_flag != nullptr) atomicExch(error_flag, 3);
+  if (warp == 8) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, 512);
   }
 }
 
@@ -620,8 +908,20 @@ extern "C" int ws_attn_fwd(const void* qkvgu, const void* states, const float* r
       return -20;
     configured = true;
   }
-  launch_dependent(attn_fwd_kernel, dim3(tiles), dim3(128), AF_SMEM, stream, tm, ts, ty, reinterpret_cast<const float2*>(rope), T, H, d,
-                                                   error_flag);
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        cudaFuncSetAttribute(attn_fwd_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AS_SMEM) != cudaSuccess)
+      return -20;
+  }
+  if (ws_attn_stream_form() != 0)
+    launch_dependent(attn_fwd_stream_kernel, dim3(tiles < sms ? tiles : sms), dim3(AS_THREADS), AS_SMEM, stream, tm, ts, ty,
+                     reinterpret_cast<const float2*>(rope), T, H, d, tiles, error_flag);
+  else
+    launch_dependent(attn_fwd_kernel, dim3(tiles), dim3(128), AF_SMEM, stream, tm, ts, ty, reinterpret_cast<const float2*>(rope), T, H, d,
+                     error_flag);
   ws_count_launch();
   return cudaGetLastError() == cudaSuccess ? 0 : -21;
 }
