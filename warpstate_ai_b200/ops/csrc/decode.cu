@@ -273,9 +273,17 @@ decode_reduce_norm_kernel(float* __restrict__ x, const float* __restrict__ parti
   float ss = 0.f;
   for (int c = threadIdx.x * 4; c < d; c += 256 * 4) {
     float4 v = *reinterpret_cast<const float4*>(src + c);
-    for (int s = 0; s < splits; ++s) {
-      const float4 q = *reinterpret_cast<const float4*>(partial + (static_cast<size_t>(s) * batch + b) * d + c);
-      v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
+    // up to 16 split partials, all requested before the first is added (the order of the additions is unchanged)
+    float4 q[16];
+#pragma unroll
+    for (int s = 0; s < 16; ++s)
+      if (s < splits) q[s] = *reinterpret_cast<const float4*>(partial + (static_cast<size_t>(s) * batch + b) * d + c);
+#pragma unroll
+    for (int s = 0; s < 16; ++s)
+      if (s < splits) { v.x += q[s].x; v.y += q[s].y; v.z += q[s].z; v.w += q[s].w; }
+    for (int s = 16; s < splits; ++s) {
+      const float4 r = *reinterpret_cast<const float4*>(partial + (static_cast<size_t>(s) * batch + b) * d + c);
+      v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w;
     }
     if (scale != nullptr) {
       const float4 sc = *reinterpret_cast<const float4*>(scale + c), bi = *reinterpret_cast<const float4*>(bias + c);
