@@ -316,3 +316,23 @@ def test_persistent_layer_tail_is_bit_identical_to_the_launch_per_projection_ste
     # 2 + 2 launches per layer + 3: embedding norm, first in_proj, head
     assert fused.graph_counters.kernels_per_replay == 2 * 3 + 3
     assert plain.graph_counters.kernels_per_replay == 7 * 3 + 2
+
+
+def test_decode_greedy_on_cpu_is_the_plain_loop():
+    """Where there is no kernel path (CPU) `decode_greedy` is arg-max after every `step`, across a chunk boundary."""
+    torch.manual_seed(2)
+    cfg = WarpStateConfig(vocab_size=97, d_model=32, n_heads=2, n_cores=2, logical_depth=2, ffn_hidden=48, chunk_size=8,
+                          gradient_checkpointing=False, parallel_memory=True)
+    model = WarpStateLM(cfg).eval().requires_grad_(False)
+    prompt = torch.randint(0, 97, (3, 5))
+    a, b = DecodeEngine(model, dtype=torch.float32), DecodeEngine(model, dtype=torch.float32)
+    token = torch.argmax(a.prefill(prompt), dim=-1)
+    assert torch.equal(torch.argmax(b.prefill(prompt), dim=-1), token)
+    want, t = [], token
+    for _ in range(9):
+        t = torch.argmax(a.step(t), dim=-1)
+        want.append(t)
+    got = b.decode_greedy(token, 9)
+    assert got.shape == (3, 9) and torch.equal(got, torch.stack(want, dim=1))
+    assert b.pos == a.pos == (5 + 9) % 8
+    assert b.decode_greedy(got[:, -1], 0).shape == (3, 0)
