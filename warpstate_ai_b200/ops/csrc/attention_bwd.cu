@@ -137,11 +137,11 @@ dstate_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_constan
 
 // =============================================================================== dState, streaming form
 // dstate_kernel as one persistent CTA per SM with specialised warps, exactly as chunk_writes_stream_kernel
-// (attention_fwd.cu): producer warp with a 3-stage ring of (Q, dy, gate) tiles, 256 workers that turn Q into rope(Q)
+// (attention_fwd.cu): producer warp with a 3-stage ring of (Q, dy, gate) tiles, 512 workers that turn Q into rope(Q)
 // and dy into dy (1 - sigmoid(gate)) / 8 in place, MMA issue into a double-buffered accumulator, two epilogue warps
 // that store the FP32 [64 x 64] result by TMA.  Bit-identical to dstate_kernel.
 constexpr int DSS_STAGES = 3;
-constexpr int DSS_THREADS = 352;
+constexpr int DSS_THREADS = 19 * 32;
 constexpr int DSS_SMEM = DSS_STAGES * 3 * TILE_BYTES + 2 * 16384 + 1024 + 256;
 
 __global__ void __launch_bounds__(DSS_THREADS, 1)
@@ -177,7 +177,7 @@ dstate_stream_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_
     tma_prefetch_desc(&tm_dy);
     tma_prefetch_desc(&tm_out);
   }
-  if (warp == 8) {
+  if (warp == 16) {
     tmem_alloc(tmem_slot, 128);
     tmem_relinquish();
   }
@@ -189,7 +189,7 @@ dstate_stream_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_
   pdl_wait();
 
   const int first = blockIdx.x, step = gridDim.x;
-  if (warp == 10) {
+  if (warp == 18) {
     if (lane == 0) {
       int i = 0;
       for (int tile = first; tile < tiles; tile += step, ++i) {
@@ -203,13 +203,13 @@ dstate_stream_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_
         tma_load_2d(ring + s * 3 * TILE_BYTES + 2 * TILE_BYTES, &tm_qkvgu, &full[s], 3 * d + h * HD, row0);
       }
     }
-  } else if (warp < 8) {
-    const int r = tid & 127, q = tid >> 7;   // row, and which four of its eight pieces
-    float2 cs[16];
+  } else if (warp < 16) {
+    const int r = tid & 127, q = tid >> 7;   // row, and which two of its eight pieces
+    float2 cs[8];
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
+    for (int j = 0; j < 2; ++j)
 #pragma unroll
-      for (int t = 0; t < 4; ++t) cs[j * 4 + t] = rope[((q * 4 + j) * 4 + t) * CHUNK + r];
+      for (int t = 0; t < 4; ++t) cs[j * 4 + t] = rope[((q * 2 + j) * 4 + t) * CHUNK + r];
     int i = 0;
     for (int tile = first; tile < tiles; tile += step, ++i) {
       const int s = i % DSS_STAGES;
@@ -219,11 +219,11 @@ dstate_stream_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_
       const bool ok = mbar_wait(&full[s], (i / DSS_STAGES) & 1, abort_flag);
       if (ok) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint4* pq = reinterpret_cast<uint4*>(tile_chunk(sQ, r, q * 4 + j));
-          uint4* pd = reinterpret_cast<uint4*>(tile_chunk(sD, r, q * 4 + j));
+        for (int j = 0; j < 2; ++j) {
+          uint4* pq = reinterpret_cast<uint4*>(tile_chunk(sQ, r, q * 2 + j));
+          uint4* pd = reinterpret_cast<uint4*>(tile_chunk(sD, r, q * 2 + j));
           uint4 qv = *pq, dv = *pd;
-          const uint4 gv = *reinterpret_cast<const uint4*>(tile_chunk(sGate, r, q * 4 + j));
+          const uint4 gv = *reinterpret_cast<const uint4*>(tile_chunk(sGate, r, q * 2 + j));
           uint32_t* qw = reinterpret_cast<uint32_t*>(&qv);
           uint32_t* dw = reinterpret_cast<uint32_t*>(&dv);
           const __nv_bfloat162* gb = reinterpret_cast<const __nv_bfloat162*>(&gv);
@@ -248,7 +248,7 @@ dstate_stream_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_
           "{\n"
           ".reg .pred p, q;\n"
           "setp.ne.u32 q, %1, 0;\n"
-          "bar.red.or.pred p, 2, 256, q;\n"
+          "bar.red.or.pred p, 2, 512, q;\n"
           "selp.u32 %0, 1, 0, p;\n"
           "}\n"
           : "=r"(any_bad)
@@ -270,8 +270,8 @@ dstate_stream_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_
         }
       }
     }
-  } else {  // warps 8, 9: accumulator lanes 0..31 and 32..63
-    const int ew = warp - 8, row = ew * 32 + lane;
+  } else {  // warps 16, 17: accumulator lanes 0..31 and 32..63
+    const int ew = warp - 16, row = ew * 32 + lane;
     int i = 0;
     for (int tile = first; tile < tiles; tile += step, ++i) {
       const int buf = i & 1;
@@ -310,7 +310,7 @@ dstate_stream_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_
   tc_fence_before_sync();
   __syncthreads();
   if (tid == 0 && *abort_flag != 0 && error_flag != nullptr) atomicExch(error_flag, 4);
-  if (warp == 8) {
+  if (warp == 16) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, 128);
   }

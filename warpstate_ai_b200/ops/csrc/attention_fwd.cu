@@ -127,18 +127,20 @@ chunk_writes_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const __grid_c
 // =============================================================================== writes, streaming form
 // The same product as chunk_writes_kernel, as one persistent CTA per SM with specialised warps:
 //
-//   warp 10      producer: TMA loads of the K and U tiles of tile i into stage i % 4 of a ring (4 x 32 KiB)
-//   warps 0..7   workers (256 threads): thread (row r, half q) turns four of the eight 16-byte pieces of row r of K
-//                into tanh(rope(K)) and of U into tanh(U), in place; its 16 (cos, sin) pairs are loaded once, since
-//                they depend on the row and the column only.  Worker thread 0 then issues the tile's eight MMAs into
+//   warp 18      producer: TMA loads of the K and U tiles of tile i into stage i % 4 of a ring (4 x 32 KiB)
+//   warps 0..15  workers (512 threads): thread (row r, quarter q) turns two of the eight 16-byte pieces of row r of K
+//                into tanh(rope(K)) and of U into tanh(U), in place; its 8 (cos, sin) pairs are loaded once, since
+//                they depend on the row and the column only.  (With 8 worker warps the kernel issued an instruction
+//                in 33 % of the cycles, each warp waiting 8 cycles between two of its own: four warps per scheduler
+//                instead of two hide that.)  Worker thread 0 then issues the tile's eight MMAs into
 //                TMEM buffer i % 2; their completion frees the ring stage and hands the buffer to the epilogue.
-//   warps 8, 9   epilogue (accumulator lanes 0..63): TMEM -> x 1/128 -> swizzled FP32 staging tile -> TMA store
+//   warps 16, 17 epilogue (accumulator lanes 0..63): TMEM -> x 1/128 -> swizzled FP32 staging tile -> TMA store
 //
 // so the loads of the next three tiles, the element-wise work of the current one and the store of the previous
 // one overlap; chunk_writes_kernel gets its overlap from six independent CTAs per SM instead, each of which walks
 // the chain load -> element-wise -> MMA -> store alone.  Results are bit-identical (same arithmetic, same MMA order).
 constexpr int WS_STAGES = 4;
-constexpr int WS_THREADS = 352;
+constexpr int WS_THREADS = 19 * 32;
 constexpr int WS_SMEM = WS_STAGES * 2 * TILE_BYTES + 2 * 16384 + 1024 + 256;
 
 __global__ void __launch_bounds__(WS_THREADS, 1)
@@ -172,7 +174,7 @@ chunk_writes_stream_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const _
     tma_prefetch_desc(&tm_qkvgu);
     tma_prefetch_desc(&tm_out);
   }
-  if (warp == 8) {
+  if (warp == 16) {
     tmem_alloc(tmem_slot, 128);
     tmem_relinquish();
   }
@@ -184,7 +186,7 @@ chunk_writes_stream_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const _
   pdl_wait();
 
   const int first = blockIdx.x, step = gridDim.x;
-  if (warp == 10) {
+  if (warp == 18) {
     if (lane == 0) {
       int i = 0;
       for (int tile = first; tile < tiles; tile += step, ++i) {
@@ -197,13 +199,13 @@ chunk_writes_stream_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const _
         tma_load_2d(ring + s * 2 * TILE_BYTES + TILE_BYTES, &tm_qkvgu, &full[s], 4 * d + h * HD, row0);
       }
     }
-  } else if (warp < 8) {
-    const int r = tid & 127, q = tid >> 7;   // row, and which four of its eight pieces
-    float2 cs[16];
+  } else if (warp < 16) {
+    const int r = tid & 127, q = tid >> 7;   // row, and which two of its eight pieces
+    float2 cs[8];
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
+    for (int j = 0; j < 2; ++j)
 #pragma unroll
-      for (int t = 0; t < 4; ++t) cs[j * 4 + t] = rope[((q * 4 + j) * 4 + t) * CHUNK + r];
+      for (int t = 0; t < 4; ++t) cs[j * 4 + t] = rope[((q * 2 + j) * 4 + t) * CHUNK + r];
     int i = 0;
     for (int tile = first; tile < tiles; tile += step, ++i) {
       const int s = i % WS_STAGES;
@@ -212,9 +214,9 @@ chunk_writes_stream_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const _
       const bool ok = mbar_wait(&full[s], (i / WS_STAGES) & 1, abort_flag);
       if (ok) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint4* pk = reinterpret_cast<uint4*>(tile_chunk(sK, r, q * 4 + j));
-          uint4* pu = reinterpret_cast<uint4*>(tile_chunk(sU, r, q * 4 + j));
+        for (int j = 0; j < 2; ++j) {
+          uint4* pk = reinterpret_cast<uint4*>(tile_chunk(sK, r, q * 2 + j));
+          uint4* pu = reinterpret_cast<uint4*>(tile_chunk(sU, r, q * 2 + j));
           uint4 kv = *pk, uv = *pu;
           uint32_t* kw = reinterpret_cast<uint32_t*>(&kv);
           uint32_t* uw = reinterpret_cast<uint32_t*>(&uv);
@@ -238,7 +240,7 @@ chunk_writes_stream_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const _
           "{\n"
           ".reg .pred p, q;\n"
           "setp.ne.u32 q, %1, 0;\n"
-          "bar.red.or.pred p, 2, 256, q;\n"
+          "bar.red.or.pred p, 2, 512, q;\n"
           "selp.u32 %0, 1, 0, p;\n"
           "}\n"
           : "=r"(any_bad)
@@ -261,8 +263,8 @@ chunk_writes_stream_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const _
         }
       }
     }
-  } else {  // warps 8, 9: accumulator lanes 0..31 and 32..63
-    const int ew = warp - 8, row = ew * 32 + lane;
+  } else {  // warps 16, 17: accumulator lanes 0..31 and 32..63
+    const int ew = warp - 16, row = ew * 32 + lane;
     int i = 0;
     for (int tile = first; tile < tiles; tile += step, ++i) {
       const int buf = i & 1;
@@ -302,7 +304,7 @@ chunk_writes_stream_kernel(const __grid_constant__ CUtensorMap tm_qkvgu, const _
   tc_fence_before_sync();
   __syncthreads();
   if (tid == 0 && *abort_flag != 0 && error_flag != nullptr) atomicExch(error_flag, 2);
-  if (warp == 8) {
+  if (warp == 16) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, 128);
   }
