@@ -61,6 +61,22 @@ def worker(mode: str, rank: int, world: int, out_dir: Path) -> None:
         for peer in got.values():
             os.close(peer)
         os.close(fd)
+    elif mode == "cpu_vote":
+        # a local step that fails on ONE rank must end as the same error on EVERY rank (nobody is left in a collective)
+        owner = symm._OwnAllocation.__new__(symm._OwnAllocation)
+        owner.group, owner.rank, owner.world, owner.handle = None, rank, world, None
+
+        def step():
+            if rank == 1:
+                raise RuntimeError("cuMemCreate refused (simulated)")
+
+        try:
+            owner._together(step, "allocation")
+            report["raised"] = None
+        except symm.SymmetricAllocationError as error:
+            report["raised"] = str(error)
+        owner._together(lambda: None, "allocation")      # and a step that works everywhere goes on
+        report["went_on"] = True
     elif mode == "gpu_buffer":
         import ctypes
         from warpstate_ai_b200.ops import _ext
@@ -122,6 +138,13 @@ def test_descriptor_exchange_between_three_processes(tmp_path):
         others = {str(r): f"hello from {r}" for r in range(3) if r != rank}
         assert report["all_to_all"] == others
         assert report["from_zero"] == ({} if rank == 0 else {"0": "hello from 0"})
+
+
+def test_a_failure_on_one_rank_is_raised_on_every_rank(tmp_path):
+    reports = spawn("cpu_vote", 3, tmp_path, env_extra={"CUDA_VISIBLE_DEVICES": ""})
+    for report in reports:
+        assert report["raised"] == "symmetric memory (allocation) failed: rank 1: cuMemCreate refused (simulated)"
+        assert report["went_on"] is True
 
 
 @pytest.mark.gpu

@@ -145,6 +145,10 @@ def exchange_descriptors(fd: int, rank: int, world: int, group, only_from: int |
     return received
 
 
+class SymmetricAllocationError(RuntimeError):
+    """Raised on every rank of the group together when the library's own allocator could not build a buffer."""
+
+
 class _OwnAllocation:
     """The mappings of one symmetric buffer in this process; released when the buffer is dropped."""
 
@@ -159,33 +163,62 @@ class _OwnAllocation:
         votes = [None] * self.world
         dist.all_gather_object(votes, multicast, group=group)
         multicast = all(votes)
-        self.bytes = int(lib.ws_symm_padded_size(self.device_index, nbytes, self.world, int(multicast)))
-        api.check(self.bytes, "sizing the allocation")
-        handle, ptr, fd = ctypes.c_ulonglong(), ctypes.c_ulonglong(), ctypes.c_int(-1)
-        api.check(lib.ws_symm_create(self.device_index, self.bytes, ctypes.byref(handle), ctypes.byref(ptr), ctypes.byref(fd)),
-                  "creating the local allocation")
-        self.handle, self.ptr = handle.value, ptr.value
+        self.handle, self.ptr = None, 0
         self.imports: list[tuple[int, int]] = []
         self.mc, self.mc_ptr, self.mc_bound = 0, 0, False
         self.peer_ptrs = [0] * self.world
-        self.peer_ptrs[self.rank] = self.ptr
+        fd = ctypes.c_int(-1)
+
+        def create() -> None:
+            self.bytes = int(lib.ws_symm_padded_size(self.device_index, nbytes, self.world, int(multicast)))
+            api.check(self.bytes, "sizing the allocation")
+            handle, ptr = ctypes.c_ulonglong(), ctypes.c_ulonglong()
+            api.check(lib.ws_symm_create(self.device_index, self.bytes, ctypes.byref(handle), ctypes.byref(ptr), ctypes.byref(fd)),
+                      "creating the local allocation")
+            self.handle, self.ptr = handle.value, ptr.value
+            self.peer_ptrs[self.rank] = self.ptr
+
+        self._together(create, "allocation")
         try:
             incoming = exchange_descriptors(fd.value, self.rank, self.world, group)
         finally:
             lib.ws_symm_close_fd(fd.value)
-        for source, peer_fd in sorted(incoming.items()):
-            peer_handle, peer_ptr = ctypes.c_ulonglong(), ctypes.c_ulonglong()
+
+        def map_peers() -> None:
             try:
-                api.check(lib.ws_symm_import(self.device_index, peer_fd, self.bytes, ctypes.byref(peer_handle),
-                                             ctypes.byref(peer_ptr)), f"mapping rank {source}'s allocation")
+                for source, peer_fd in sorted(incoming.items()):
+                    peer_handle, peer_ptr = ctypes.c_ulonglong(), ctypes.c_ulonglong()
+                    api.check(lib.ws_symm_import(self.device_index, peer_fd, self.bytes, ctypes.byref(peer_handle),
+                                                 ctypes.byref(peer_ptr)), f"mapping rank {source}'s allocation")
+                    self.imports.append((peer_handle.value, peer_ptr.value))
+                    self.peer_ptrs[source] = peer_ptr.value
             finally:
-                lib.ws_symm_close_fd(peer_fd)
-            self.imports.append((peer_handle.value, peer_ptr.value))
-            self.peer_ptrs[source] = peer_ptr.value
+                for peer_fd in incoming.values():
+                    lib.ws_symm_close_fd(peer_fd)
+
+        self._together(map_peers, "peer mapping")
         if multicast:
             self._join_multicast(api)
 
+    def _together(self, step, what: str) -> None:
+        """Run a local step on every rank, then let the ranks tell one another how it went: either all go on, or
+        all release what they hold and raise `SymmetricAllocationError` -- no rank is left waiting in a collective
+        for a peer that has already given up."""
+        problem = None
+        try:
+            step()
+        except Exception as error:     # reported to every rank below, then re-raised as one common error
+            problem = f"rank {self.rank}: {error}"
+        reports = [None] * self.world
+        dist.all_gather_object(reports, problem, group=self.group)
+        failed = [r for r in reports if r]
+        if failed:
+            self.close()
+            raise SymmetricAllocationError(f"symmetric memory ({what}) failed: " + "; ".join(failed))
+
     def _join_multicast(self, api: _Library) -> None:
+        """Join the ranks' allocations in one multicast object.  Any rank's failure makes every rank go on without
+        a multimem address (peer loads still work)."""
         lib = api.lib
         mc, fd = ctypes.c_ulonglong(), ctypes.c_int(-1)
         created = 0
@@ -197,21 +230,39 @@ class _OwnAllocation:
         if outcome[0] < 0:
             return                      # the fabric refused the object: every rank goes on without multimem
         incoming = exchange_descriptors(fd.value if self.rank == 0 else -1, self.rank, self.world, self.group, only_from=0)
-        if self.rank == 0:
-            lib.ws_symm_close_fd(fd.value)
-        else:
+
+        def agreed(step) -> bool:
+            fine = True
             try:
-                api.check(lib.ws_symm_multicast_import(incoming[0], ctypes.byref(mc)), "importing the multicast object")
-            finally:
-                lib.ws_symm_close_fd(incoming[0])
-        self.mc = mc.value
-        api.check(lib.ws_symm_multicast_add_device(self.mc, self.device_index), "adding the device to the multicast object")
-        dist.barrier(group=self.group)  # all devices are members before anyone binds
-        mc_ptr = ctypes.c_ulonglong()
-        api.check(lib.ws_symm_multicast_bind(self.mc, self.handle, self.bytes, self.device_index, ctypes.byref(mc_ptr)),
-                  "binding to the multicast object")
-        self.mc_ptr, self.mc_bound = mc_ptr.value, True
-        dist.barrier(group=self.group)  # every rank is bound before anyone issues a multimem instruction
+                step()
+            except Exception:
+                fine = False
+            votes = [None] * self.world
+            dist.all_gather_object(votes, fine, group=self.group)
+            return all(votes)
+
+        def join() -> None:
+            if self.rank == 0:
+                lib.ws_symm_close_fd(fd.value)
+            else:
+                try:
+                    api.check(lib.ws_symm_multicast_import(incoming[0], ctypes.byref(mc)), "importing the multicast object")
+                finally:
+                    lib.ws_symm_close_fd(incoming[0])
+            self.mc = mc.value
+            api.check(lib.ws_symm_multicast_add_device(self.mc, self.device_index), "adding the device to the multicast object")
+
+        def bind() -> None:
+            mc_ptr = ctypes.c_ulonglong()
+            api.check(lib.ws_symm_multicast_bind(self.mc, self.handle, self.bytes, self.device_index, ctypes.byref(mc_ptr)),
+                      "binding to the multicast object")
+            self.mc_ptr, self.mc_bound = mc_ptr.value, True
+
+        # all devices are members before anyone binds; every rank is bound before anyone issues a multimem instruction
+        if not (agreed(join) and agreed(bind)):
+            if self.mc:
+                lib.ws_symm_multicast_release(self.mc, self.mc_ptr, self.bytes, self.device_index, int(self.mc_bound))
+            self.mc, self.mc_ptr, self.mc_bound = 0, 0, False
 
     def close(self) -> None:
         if getattr(self, "handle", None) is None:
@@ -272,4 +323,10 @@ def allocate(numel: int, dtype: torch.dtype, device: torch.device, group=None) -
     group = group if group is not None else dist.group.WORLD
     if provider() == "torch":
         return _allocate_torch(numel, dtype, device, group)
-    return _allocate_own(numel, dtype, device, group)
+    try:
+        return _allocate_own(numel, dtype, device, group)
+    except SymmetricAllocationError as error:
+        # raised on every rank together, so every rank takes the other allocator together
+        if dist.get_rank(group) == 0:
+            print(f"warpstate_ai_b200: {error}; using torch.distributed._symmetric_memory instead", flush=True)
+        return _allocate_torch(numel, dtype, device, group)
