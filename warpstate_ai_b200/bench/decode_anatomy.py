@@ -9,7 +9,7 @@
             graph, and the launch's own phase boundaries from the ``%globaltimer`` stamps every CTA writes into the
             optional ``trace`` tensor.
 
-    python -m warpstate_ai_b200.bench.decode_anatomy parts [--batch 64]
+    python -m warpstate_ai_b200.bench.decode_anatomy parts [--batch 64] [--position 64] [--only attention]
     python -m warpstate_ai_b200.bench.decode_anatomy tail  [--batch 64]
 
 One JSON line per measurement.
@@ -58,7 +58,7 @@ def timed_eager(fn, repeats: int = 10) -> float:
     return start.elapsed_time(stop) / repeats
 
 
-def parts(batch: int) -> None:
+def parts(batch: int, position: int = 0, only=None) -> None:
     from .. import WarpStateLM, warpstate_2b
     from ..serve.engine import DecodeEngine
     torch.manual_seed(0)
@@ -67,6 +67,7 @@ def parts(batch: int) -> None:
     model.eval().requires_grad_(False)
     engine = DecodeEngine(model, dtype=torch.bfloat16)
     engine.new_state(batch)
+    engine.pos_dev.fill_(position)      # the attention step reads the cache rows below this in-chunk position
     k, ops = engine._kbufs, torch.ops.ws_b200
     d, ffn, eps, pos = engine.cfg.d_model, engine.cfg.ffn_hidden, engine.cfg.rms_eps, engine.pos_dev
 
@@ -88,9 +89,10 @@ def parts(batch: int) -> None:
                 ops.decode_reduce_norm(k["x"], k["p_down"], None, None, None, None, w["n2"], eps, k["n"])
 
     everything = ["in_proj", "attention", "out_proj", "norm", "up_gate", "down"]
-    for chosen in (everything, ["in_proj", "out_proj", "up_gate", "down"], ["attention", "norm"], ["in_proj"], ["up_gate"],
-                   ["out_proj"], ["down"], ["attention"], ["norm"]):
-        print(json.dumps({"launches": chosen, "layers": len(engine.weights), "batch": batch, "in_chunk_position": 0,
+    subsets = (everything, ["in_proj", "out_proj", "up_gate", "down"], ["attention", "norm"], ["in_proj"], ["up_gate"],
+               ["out_proj"], ["down"], ["attention"], ["norm"])
+    for chosen in subsets if only is None else [only.split(",")]:
+        print(json.dumps({"launches": chosen, "layers": len(engine.weights), "batch": batch, "in_chunk_position": position,
                           "ms_per_step": round(timed_graph(lambda: step(chosen)), 4)}), flush=True)
 
 
@@ -151,8 +153,13 @@ def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("what", choices=["parts", "tail"])
     ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--position", type=int, default=0, help="parts: in-chunk position of the step (0..127)")
+    ap.add_argument("--only", default=None, help="parts: one comma-separated subset instead of the standard ones")
     a = ap.parse_args()
-    {"parts": parts, "tail": tail}[a.what](a.batch)
+    if a.what == "parts":
+        parts(a.batch, a.position, a.only)
+    else:
+        tail(a.batch)
 
 
 if __name__ == "__main__":

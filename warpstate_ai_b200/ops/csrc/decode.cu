@@ -273,17 +273,9 @@ decode_reduce_norm_kernel(float* __restrict__ x, const float* __restrict__ parti
   float ss = 0.f;
   for (int c = threadIdx.x * 4; c < d; c += 256 * 4) {
     float4 v = *reinterpret_cast<const float4*>(src + c);
-    // up to 16 split partials, all requested before the first is added (the order of the additions is unchanged)
-    float4 q[16];
-#pragma unroll
-    for (int s = 0; s < 16; ++s)
-      if (s < splits) q[s] = *reinterpret_cast<const float4*>(partial + (static_cast<size_t>(s) * batch + b) * d + c);
-#pragma unroll
-    for (int s = 0; s < 16; ++s)
-      if (s < splits) { v.x += q[s].x; v.y += q[s].y; v.z += q[s].z; v.w += q[s].w; }
-    for (int s = 16; s < splits; ++s) {
-      const float4 r = *reinterpret_cast<const float4*>(partial + (static_cast<size_t>(s) * batch + b) * d + c);
-      v.x += r.x; v.y += r.y; v.z += r.z; v.w += r.w;
+    for (int s = 0; s < splits; ++s) {
+      const float4 q = *reinterpret_cast<const float4*>(partial + (static_cast<size_t>(s) * batch + b) * d + c);
+      v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
     }
     if (scale != nullptr) {
       const float4 sc = *reinterpret_cast<const float4*>(scale + c), bi = *reinterpret_cast<const float4*>(bias + c);
@@ -440,6 +432,147 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ qkvgu, __nv_bfloat16* __res
     for (int it = 0; it < HD / 16; ++it) {
       const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&mreg[it]);
       const float qi = sq[rg + it * 16];
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float2 f = __bfloat1622float2(pb[t]);
+        accm[2 * t] += qi * f.x;
+        accm[2 * t + 1] += qi * f.y;
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+      sl[rg][jg * 8 + t] = accl[t];
+      sm[rg][jg * 8 + t] = accm[t];
+    }
+  }
+  __syncthreads();
+  if (tid < HD) {
+    float local = 0.f, mem = 0.f;
+#pragma unroll
+    for (int r = 0; r < 16; ++r) {
+      local += sl[r][tid];
+      mem += sm[r][tid];
+    }
+    local *= inv;
+    mem *= 0.125f;
+    const float g = sigmoid_fast(__bfloat162float(row[3 * d + tid]));
+    y[static_cast<size_t>(b) * d + h * HD + tid] = __float2bfloat16(g * local + (1.f - g) * mem);
+  }
+}
+
+// --------------------------------------------------------------------------- attention step, row-per-thread scores
+// The earlier form of decode_attn_kernel (WS_DECODE_ATTN=rows): thread c computes the score of key c from its own
+// 128-byte cache row, and the value / memory rows are read after the softmax.  Fewer registers (more CTAs per SM),
+// three dependent memory phases.  One CTA of 128 threads per (sequence, head); head_dim 64, chunk 128.
+// qkvgu: [batch, 5*d] BF16 (q | k | v | gate | u); caches kc/vc/uc: [batch, H, 128, 64] BF16;
+// mixed: [batch, H, 64, 64] BF16 (mix*fast + (1-mix)*slow); rope: [128, 32] (cos, sin);
+// y: [batch, d] BF16.  `pos_ptr` is the in-chunk position (device scalar, so that one captured
+// graph serves every position).
+__global__ void __launch_bounds__(128)
+decode_attn_rows_kernel(const __nv_bfloat16* __restrict__ qkvgu, __nv_bfloat16* __restrict__ kc,
+                   __nv_bfloat16* __restrict__ vc, __nv_bfloat16* __restrict__ uc,
+                   const __nv_bfloat16* __restrict__ mixed, const float2* __restrict__ rope,
+                   const long long* __restrict__ pos_ptr, int H, int d, __nv_bfloat16* __restrict__ y) {
+  constexpr int HD = 64, C = 128;
+  __shared__ float sq[HD], sk[HD], sp[C], sl[16][HD + 1], sm[16][HD + 1], sred[4];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int h = blockIdx.x % H, b = blockIdx.x / H;
+  pdl_launch_dependents();
+  pdl_wait();
+  int pos = static_cast<int>(*pos_ptr);
+  pos = pos < 0 ? 0 : (pos >= C ? C - 1 : pos);
+  const __nv_bfloat16* row = qkvgu + static_cast<size_t>(b) * 5 * d + h * HD;
+  const size_t cache = (static_cast<size_t>(b) * H + h) * C * HD;
+  // RoPE (adjacent pairs) of q and k; append k, v, u at `pos`
+  if (tid < 32) {
+    const float2 cs = rope[pos * 32 + tid];
+    const float2 q = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(row + 2 * tid));
+    const float2 k = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(row + d + 2 * tid));
+    // round through BF16 as the cached / batched path does
+    const __nv_bfloat162 qr = __floats2bfloat162_rn(q.x * cs.x - q.y * cs.y, q.y * cs.x + q.x * cs.y);
+    const __nv_bfloat162 kr = __floats2bfloat162_rn(k.x * cs.x - k.y * cs.y, k.y * cs.x + k.x * cs.y);
+    const float2 qf = __bfloat1622float2(qr), kf = __bfloat1622float2(kr);
+    sq[2 * tid] = qf.x; sq[2 * tid + 1] = qf.y;
+    sk[2 * tid] = kf.x; sk[2 * tid + 1] = kf.y;
+    *reinterpret_cast<__nv_bfloat162*>(kc + cache + static_cast<size_t>(pos) * HD + 2 * tid) = kr;
+  } else if (tid < 64) {
+    const int t = tid - 32;
+    *reinterpret_cast<__nv_bfloat162*>(vc + cache + static_cast<size_t>(pos) * HD + 2 * t) =
+        *reinterpret_cast<const __nv_bfloat162*>(row + 2 * d + 2 * t);
+  } else if (tid < 96) {
+    const int t = tid - 64;
+    *reinterpret_cast<__nv_bfloat162*>(uc + cache + static_cast<size_t>(pos) * HD + 2 * t) =
+        *reinterpret_cast<const __nv_bfloat162*>(row + 4 * d + 2 * t);
+  }
+  __syncthreads();
+  // scores: thread c owns key c
+  float score = -INFINITY;
+  if (tid <= pos) {
+    float acc = 0.f;
+    if (tid == pos) {
+#pragma unroll
+      for (int i = 0; i < HD; ++i) acc += sq[i] * sk[i];
+    } else {
+      const uint4* kr = reinterpret_cast<const uint4*>(kc + cache + static_cast<size_t>(tid) * HD);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint4 v = kr[j];
+        const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float2 f = __bfloat1622float2(pb[t]);
+          acc += sq[j * 8 + 2 * t] * f.x + sq[j * 8 + 2 * t + 1] * f.y;
+        }
+      }
+    }
+    score = acc * 0.125f;
+  }
+  float m = score;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if (lane == 0) sred[warp] = m;
+  __syncthreads();
+  m = fmaxf(fmaxf(sred[0], sred[1]), fmaxf(sred[2], sred[3]));
+  const float e = tid <= pos ? __expf(score - m) : 0.f;
+  float s = e;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  __syncthreads();
+  if (lane == 0) sred[warp] = s;
+  sp[tid] = e;
+  __syncthreads();
+  const float inv = 1.f / (sred[0] + sred[1] + sred[2] + sred[3]);
+  // local = sum_c p[c] V[c] and memory = q . M in one pass of wide loads: thread (rg, jg) owns
+  // columns 8*jg .. 8*jg+7 and the rows rg, rg+16, ... of V (keys) and of M; the 16 row groups
+  // are then summed through shared memory.
+  {
+    const int jg = tid & 7, rg = tid >> 3;
+    float accl[8], accm[8];
+#pragma unroll
+    for (int t = 0; t < 8; ++t) { accl[t] = 0.f; accm[t] = 0.f; }
+#pragma unroll
+    for (int it = 0; it < C / 16; ++it) {
+      const int c = rg + it * 16;
+      if (c <= pos) {
+        const uint4 v = (c == pos) ? *reinterpret_cast<const uint4*>(row + 2 * d + jg * 8)
+                                   : *reinterpret_cast<const uint4*>(vc + cache + static_cast<size_t>(c) * HD + jg * 8);
+        const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&v);
+        const float pc = sp[c];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float2 f = __bfloat1622float2(pb[t]);
+          accl[2 * t] += pc * f.x;
+          accl[2 * t + 1] += pc * f.y;
+        }
+      }
+    }
+    const __nv_bfloat16* mbase = mixed + (static_cast<size_t>(b) * H + h) * HD * HD;
+#pragma unroll
+    for (int it = 0; it < HD / 16; ++it) {
+      const int i = rg + it * 16;
+      const uint4 v = *reinterpret_cast<const uint4*>(mbase + i * HD + jg * 8);
+      const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&v);
+      const float qi = sq[i];
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
         const float2 f = __bfloat1622float2(pb[t]);
@@ -670,8 +803,14 @@ extern "C" int ws_decode_reduce_norm(float* x, const float* partial, int splits,
 extern "C" int ws_decode_attn(const void* qkvgu, void* kc, void* vc, void* uc, const void* mixed, const float* rope,
                               const long long* pos, int batch, int H, int d, void* y, cudaStream_t stream) {
   if (d != H * 64 || batch <= 0) return -1;
+  // WS_DECODE_ATTN=rows selects the row-per-thread form of the kernel
+  static const bool rows_form = [] {
+    const char* e = std::getenv("WS_DECODE_ATTN");
+    return e != nullptr && e[0] == 'r';
+  }();
   const cudaError_t err = launch_chained(
-      decode_attn_kernel, dim3(batch * H), dim3(128), 0, stream, static_cast<const __nv_bfloat16*>(qkvgu),
+      rows_form ? decode_attn_rows_kernel : decode_attn_kernel, dim3(batch * H), dim3(128), 0, stream,
+      static_cast<const __nv_bfloat16*>(qkvgu),
       static_cast<__nv_bfloat16*>(kc), static_cast<__nv_bfloat16*>(vc), static_cast<__nv_bfloat16*>(uc),
       static_cast<const __nv_bfloat16*>(mixed), reinterpret_cast<const float2*>(rope), pos, H, d,
       static_cast<__nv_bfloat16*>(y));
