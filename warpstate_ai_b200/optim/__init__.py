@@ -1,4 +1,4 @@
-from .adamw import ArenaAdamW, cosine_lr, linear_warmup_decay_lr, warmup_ratio_cosine_lr
+from .adamw import ArenaAdamW, cosine_lr
 from .arena import ParamArena
 
-__all__ = ["ArenaAdamW", "ParamArena", "cosine_lr", "linear_warmup_decay_lr", "warmup_ratio_cosine_lr"]
+__all__ = ["ArenaAdamW", "ParamArena", "cosine_lr"]

@@ -26,26 +26,6 @@ def cosine_lr(step: int, *, lr: float, min_lr: float, warmup_steps: int, total_s
     return min_lr + (lr - min_lr) * 0.5 * (1 + math.cos(math.pi * (step - warm) / max(1, total_steps - warm)))
 
 
-def warmup_ratio_cosine_lr(step: int, *, lr: float, min_lr_ratio: float, warmup_ratio: float, total_steps: int) -> float:
-    """SFT schedule: warm-up over a fraction of the run, cosine to ``lr*min_lr_ratio``
-    (reference posttrain.py:192-197)."""
-    warm = max(1, int(round(total_steps * warmup_ratio)))
-    if step < warm:
-        return lr * (step + 1) / warm
-    progress = (step - warm) / max(1, total_steps - warm)
-    floor = lr * min_lr_ratio
-    return floor + (lr - floor) * 0.5 * (1 + math.cos(math.pi * min(1.0, progress)))
-
-
-def linear_warmup_decay_lr(step: int, *, lr: float, warmup_steps: int, total_steps: int, final_ratio: float = 0.0) -> float:
-    """DPO schedule: linear warm-up then linear decay (reference dpo.py:92-98)."""
-    if step < warmup_steps:
-        return lr * (step + 1) / max(1, warmup_steps)
-    span = max(1, total_steps - warmup_steps)
-    frac = min(1.0, (step - warmup_steps) / span)
-    return lr * (1.0 - (1.0 - final_ratio) * frac)
-
-
 def host_clip_stats(sumsq: torch.Tensor, max_norm: float, status: torch.Tensor | None = None) -> torch.Tensor:
     """``[norm, coef, norm^2, skip, 0, 0, 0, 0]`` from a sum of squares, as the kernels lay it out."""
     sumsq = sumsq.reshape(()).float()
