@@ -20,7 +20,9 @@ weights that another rank owns.  Checkpoints stay in the reference's unsharded f
 ``torch.optim.AdamW.state_dict()``.
 
 Without symmetric memory (CPU/gloo tests, NCCL fallback) the same ownership is used with
-``all_gather`` of the updated slices; results are bit-identical to the replicated optimizer.
+``all_gather`` of the updated slices; the update is the replicated optimizer's, element for element, given
+the same clip coefficient (the norm is summed per slice in FP64 and rounded once, so it agrees with the
+one-rank norm except where the order of the FP64 additions moves the rounded value).
 """
 from __future__ import annotations
 
@@ -112,10 +114,11 @@ class ShardedAdamW:
             if _ext.available():
                 return torch.ops.ws_b200.grad_norm_clip(grad, float(max_norm), extra_sumsq, status)
         parts = [g.double().pow(2).sum() for g in self.owned(grad) if g.numel()]
-        sumsq = torch.stack(parts).sum().float() if parts else torch.zeros((), device=self.arena.device)
+        sumsq = torch.stack(parts).sum() if parts else torch.zeros((), dtype=torch.float64, device=self.arena.device)
         sumsq = sumsq.reshape(1)
         if self.world > 1:
             dist.all_reduce(sumsq, op=dist.ReduceOp.SUM, group=self.group)
+        sumsq = sumsq.float()      # rounded once, after the ranks' FP64 sums are combined, as the one-rank sum is
         if extra_sumsq is not None:
             sumsq = sumsq + extra_sumsq.reshape(1)
         return host_clip_stats(sumsq, max_norm, status)
