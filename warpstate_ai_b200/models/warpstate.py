@@ -1,20 +1,19 @@
 """WarpState language model.
 
-Public surface and state-dict keys match the reference (warpstate/model.py:15-358):
-``WarpStateLM(cfg)``, ``forward(input_ids, targets=None, *, return_logits=True)``,
-``num_parameters()``, ``init_generation_cache(B, device, dtype)``, ``step(ids[B,1], caches)``;
-keys ``depth_scale, depth_bias, embed.weight, cores.{i}.{fast_decay_logit, slow_decay_logit,
-memory_mix_logit, norm1.weight, in_proj.weight, out_proj.weight, norm2.weight,
-ffn.up_gate.weight, ffn.down.weight}, final_norm.weight``.
+The public surface and the state-dict keys are the reference's (warpstate/model.py:15-358), because checkpoints,
+the entry points and users of ``warpstate.model`` depend on them: ``WarpStateLM(cfg)``,
+``forward(input_ids, targets=None, *, return_logits=True)``, ``num_parameters()``,
+``init_generation_cache(B, device, dtype)``, ``step(ids[B,1], caches)``; keys ``depth_scale, depth_bias,
+embed.weight, cores.{i}.{fast_decay_logit, slow_decay_logit, memory_mix_logit, norm1.weight, in_proj.weight,
+out_proj.weight, norm2.weight, ffn.up_gate.weight, ffn.down.weight}, final_norm.weight``.
 
-Two execution paths share these modules:
+The modules here hold parameters and route; the arithmetic lives elsewhere:
 
-* the plain-PyTorch path (any device, any dtype) is the definition of the model and the oracle
-  for tests; it is what runs on CPU;
-* the fused sm_100a path (`ops.fused`) runs when the input is on a CUDA device, the kernel
-  library is loaded and BF16 autocast is active: one autograd node per core whose forward and
-  backward are sequences of hand-written kernels (tcgen05 GEMMs with fused epilogues, chunk
-  attention + memory, RMSNorm, LM-head cross-entropy).
+* `ops.reference` states every operation in plain PyTorch.  That is the model on a CPU (or on any device without the
+  kernel library) and what the CUDA kernels are tested against;
+* `ops.fused` is the sm_100a path, taken when the input is on a CUDA device, the kernel library is loaded and BF16
+  autocast is active: one autograd node per block whose forward and backward are sequences of hand-written kernels
+  (tcgen05 GEMMs with fused epilogues, chunk attention + memory, RMSNorm, LM-head cross-entropy).
 """
 from __future__ import annotations
 
@@ -24,57 +23,62 @@ from typing import List
 
 import torch
 import torch.nn as nn
-import torch.nn.functional as F
 from torch.utils.checkpoint import checkpoint
 
 from ..config import WarpStateConfig
 from ..ops import reference as R
 
+INIT_STD = 0.02
+# One logit per head: the fast memory starts by keeping 0.90 of itself per chunk, the slow one 0.99, and a read
+# weighs the two equally.
+INITIAL_LOGITS = {"fast_decay_logit": math.log(0.90 / 0.10), "slow_decay_logit": math.log(0.99 / 0.01),
+                  "memory_mix_logit": 0.0}
 
-def _fused_active(x: torch.Tensor) -> bool:
-    if not x.is_cuda:
+
+def _kernels_take(x: torch.Tensor, owner: nn.Module) -> bool:
+    """The fused path handles ``x`` for ``owner`` (whose projections are whole tensors, not row-sharded layers)."""
+    if not x.is_cuda or getattr(owner, "sharded_linears", False):
         return False
     from ..ops import fused
     return fused.active(x)
 
 
+def _projection(inputs: int, outputs: int) -> nn.Linear:
+    return nn.Linear(inputs, outputs, bias=False)
+
+
 class RMSNorm(nn.Module):
     def __init__(self, dim: int, eps: float = 1e-5):
         super().__init__()
-        self.weight = nn.Parameter(torch.ones(dim))
         self.eps = eps
-        self.use_fused = False  # kept for API parity; the CUDA path is selected by `fused.active`
+        self.weight = nn.Parameter(torch.ones(dim))
+        self.use_fused = False      # attribute of the reference's module; the CUDA path is chosen per block, not here
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return R.rmsnorm(x, self.weight, self.eps)
 
 
-# Re-exported helper names of the reference module.
-rotate_half = R.rotate_pairs
-
-
-def rope_cos_sin(length: int, dim: int, device: torch.device, dtype: torch.dtype):
-    return R.rope_tables(length, dim, device, dtype)
-
-
-def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
-    return R.apply_rope(x, cos.view(1, 1, 1, *cos.shape), sin.view(1, 1, 1, *sin.shape))
-
-
 class SwiGLU(nn.Module):
     def __init__(self, dim: int, hidden: int):
         super().__init__()
-        self.up_gate = nn.Linear(dim, hidden * 2, bias=False)
-        self.down = nn.Linear(hidden, dim, bias=False)
+        self.up_gate = _projection(dim, 2 * hidden)
+        self.down = _projection(hidden, dim)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return self.down(R.swiglu(self.up_gate(x)))
 
 
+# Helper names that ``warpstate.model`` exports.
+rotate_half = R.rotate_pairs
+rope_cos_sin = R.rope_tables
+apply_rope = R.apply_rope
+
+
 @dataclass
 class LayerCache:
-    """Decode state of one logical depth: two matrix memories per head, the current chunk's
-    keys/values, and the running (unnormalised) write of the current chunk."""
+    """What one logical depth carries between decode steps: the fast and slow memories of the finished chunks, the
+    keys and values of the chunk in progress, its write so far (not yet divided by the chunk length), and how many
+    positions of the chunk are filled."""
     fast_state: torch.Tensor
     slow_state: torch.Tensor
     k_cache: torch.Tensor
@@ -84,229 +88,191 @@ class LayerCache:
 
 
 class WarpStateCore(nn.Module):
-    """One block: norm -> fused Q/K/V/gate/U projection -> (chunk-local causal attention,
-    fast/slow matrix-memory read) -> gated blend -> out projection -> SwiGLU FFN."""
+    """One block: ``x + out_proj(mix(in_proj(norm1 x)))`` followed by ``x + ffn(norm2 x)``, where ``mix`` is
+    chunk-local causal attention blended with a read of the fast / slow matrix memories (`ops.reference`)."""
 
     def __init__(self, cfg: WarpStateConfig):
         super().__init__()
         self.cfg = cfg
-        d = cfg.d_model
-        self.h = cfg.n_heads
-        self.hd = cfg.head_dim
-        self.chunk = cfg.chunk_size
-        self.norm1 = RMSNorm(d, cfg.rms_eps)
-        self.in_proj = nn.Linear(d, 5 * d, bias=False)
-        self.out_proj = nn.Linear(d, d, bias=False)
-        self.norm2 = RMSNorm(d, cfg.rms_eps)
-        self.ffn = SwiGLU(d, cfg.ffn_hidden)
-        self.fast_decay_logit = nn.Parameter(torch.full((self.h,), math.log(0.90 / 0.10)))
-        self.slow_decay_logit = nn.Parameter(torch.full((self.h,), math.log(0.99 / 0.01)))
-        self.memory_mix_logit = nn.Parameter(torch.zeros(self.h))
-        # Real tables even when the module is built on the meta device (they are not in the state
-        # dict, so a meta-constructed model could never fill them in).
-        table_device = torch.device("cpu") if torch.get_default_device().type == "meta" else None
-        cos, sin = R.rope_tables(self.chunk, self.hd, table_device, torch.float32)
+        self.h, self.hd, self.chunk = cfg.n_heads, cfg.head_dim, cfg.chunk_size
+        width = cfg.d_model
+        self.norm1 = RMSNorm(width, cfg.rms_eps)
+        self.in_proj = _projection(width, 5 * width)         # Q | K | V | gate | U
+        self.out_proj = _projection(width, width)
+        self.norm2 = RMSNorm(width, cfg.rms_eps)
+        self.ffn = SwiGLU(width, cfg.ffn_hidden)
+        for name, logit in INITIAL_LOGITS.items():
+            self.register_parameter(name, nn.Parameter(torch.full((self.h,), logit)))
+        # The rotary tables are not part of the state dict, so a module built on the meta device (as loaders do) could
+        # never fill them in afterwards: they are always computed for real.
+        on_meta = torch.get_default_device().type == "meta"
+        cos, sin = R.rope_tables(self.chunk, self.hd, torch.device("cpu") if on_meta else None, torch.float32)
         self.register_buffer("rope_cos", cos, persistent=False)
         self.register_buffer("rope_sin", sin, persistent=False)
 
-    # ------------------------------------------------------------------ training / prefill
+    def _memory_arguments(self):
+        return (self.fast_decay_logit, self.slow_decay_logit, self.memory_mix_logit, self.h, self.chunk,
+                self.cfg.parallel_memory, self.rope_cos, self.rope_sin)
+
+    def _finish(self, x: torch.Tensor, mixed: torch.Tensor) -> torch.Tensor:
+        x = x + self.out_proj(mixed)
+        return x + self.ffn(self.norm2(x))
+
+    # ------------------------------------------------------------------ whole chunks (training, prefill)
     def forward(self, x: torch.Tensor, depth_scale: torch.Tensor | None = None,
                 depth_bias: torch.Tensor | None = None) -> torch.Tensor:
-        """``x [B,T,d]``.  When ``depth_scale/bias`` are given the depth modulation
-        ``x*(1+scale)+bias`` is applied first (the fused path folds it into its first kernel)."""
-        if x.shape[1] % self.chunk != 0:
+        """``x [B, T, d]`` with ``T`` a whole number of chunks.  ``depth_scale / depth_bias``, when given, are applied
+        first (the fused path folds them into its first kernel)."""
+        if x.shape[1] % self.chunk:
             raise ValueError(f"sequence length {x.shape[1]} must be divisible by chunk_size={self.chunk}")
-        # cores whose projections were replaced by row-sharded layers (parallel/sharded_model.py) take the
-        # module-by-module path: their weights are not whole tensors that the fused layer kernels could read
-        if _fused_active(x) and not getattr(self, "sharded_linears", False):
+        if _kernels_take(x, self):
             from ..ops import fused
             return fused.core_forward(self, x, depth_scale, depth_bias)
         if depth_scale is not None:
             x = x * (1.0 + depth_scale) + depth_bias
-        return self._forward_torch(x)
-
-    def _forward_torch(self, x: torch.Tensor) -> torch.Tensor:
-        z = self.norm1(x)
-        y = R.attention_memory(
-            self.in_proj(z), self.fast_decay_logit, self.slow_decay_logit, self.memory_mix_logit,
-            self.h, self.chunk, self.cfg.parallel_memory, self.rope_cos, self.rope_sin,
-            dropout_p=self.cfg.dropout if self.training else 0.0)
-        x = x + self.out_proj(y)
-        return x + self.ffn(self.norm2(x))
+        drop = self.cfg.dropout if self.training else 0.0
+        return self._finish(x, R.attention_memory(self.in_proj(self.norm1(x)), *self._memory_arguments(), dropout_p=drop))
 
     def forward_with_state(self, x: torch.Tensor):
-        """Prefill helper: like ``forward`` on whole chunks, and also returns the (fast, slow)
-        states after the last chunk (plain-PyTorch path; the CUDA prefill lives in serve/)."""
-        z = self.norm1(x)
-        y, state = R.attention_memory(
-            self.in_proj(z), self.fast_decay_logit, self.slow_decay_logit, self.memory_mix_logit,
-            self.h, self.chunk, self.cfg.parallel_memory, self.rope_cos, self.rope_sin,
-            return_state=True)
-        x = x + self.out_proj(y)
-        return x + self.ffn(self.norm2(x)), state
+        """`forward` in plain PyTorch that also returns the (fast, slow) memories after the last chunk, for a
+        prefill that a decode continues (the CUDA prefill is in `serve.engine`)."""
+        mixed, memories = R.attention_memory(self.in_proj(self.norm1(x)), *self._memory_arguments(), return_state=True)
+        return self._finish(x, mixed), memories
 
-    # ------------------------------------------------------------------ decode
+    # ------------------------------------------------------------------ one position (decode)
     @torch.no_grad()
     def init_cache(self, batch_size: int, device: torch.device, dtype: torch.dtype) -> LayerCache:
-        state = (batch_size, self.h, self.hd, self.hd)
-        kv = (batch_size, self.h, self.chunk, self.hd)
-        z = lambda shape: torch.zeros(shape, device=device, dtype=dtype)
-        return LayerCache(z(state), z(state), z(kv), z(kv), z(state), 0)
+        def zeros(*shape):
+            return torch.zeros((batch_size, self.h, *shape), device=device, dtype=dtype)
+        return LayerCache(fast_state=zeros(self.hd, self.hd), slow_state=zeros(self.hd, self.hd),
+                          k_cache=zeros(self.chunk, self.hd), v_cache=zeros(self.chunk, self.hd),
+                          write_accum=zeros(self.hd, self.hd), chunk_len=0)
 
     @torch.no_grad()
     def step(self, x: torch.Tensor, cache: LayerCache) -> torch.Tensor:
-        """One token (``x [B,1,d]``) with the sequential recurrence (warpstate/model.py:222-274)."""
-        assert x.shape[1] == 1
-        b = x.shape[0]
-        z = self.norm1(x)
-        q, k, v, g, u = (t.view(b, 1, self.h, self.hd).permute(0, 2, 1, 3)
-                         for t in self.in_proj(z).chunk(5, dim=-1))
-        pos = cache.chunk_len
-        cos, sin = R.rope_tables(pos + 1, self.hd, x.device, q.dtype)
-        c = cos[pos:pos + 1].view(1, 1, 1, self.hd)
-        s = sin[pos:pos + 1].view(1, 1, 1, self.hd)
-        q = q * c + R.rotate_pairs(q) * s
-        k = k * c + R.rotate_pairs(k) * s
-        cache.k_cache[:, :, pos:pos + 1].copy_(k)
-        cache.v_cache[:, :, pos:pos + 1].copy_(v)
-        local = F.scaled_dot_product_attention(q, cache.k_cache[:, :, :pos + 1], cache.v_cache[:, :, :pos + 1],
-                                               is_causal=False, dropout_p=0.0)
-        shape = (1, self.h, 1, 1)
-        fast_decay = torch.sigmoid(self.fast_decay_logit).to(q.dtype).view(shape)
-        slow_decay = torch.sigmoid(self.slow_decay_logit).to(q.dtype).view(shape)
-        mix = torch.sigmoid(self.memory_mix_logit).to(q.dtype).view(shape)
-        read_fast = torch.matmul(q, cache.fast_state) / math.sqrt(self.hd)
-        read_slow = torch.matmul(q, cache.slow_state) / math.sqrt(self.hd)
-        memory = mix * read_fast + (1.0 - mix) * read_slow
-        gate = torch.sigmoid(g)
-        y = gate * local + (1.0 - gate) * memory
-        cache.write_accum.add_(torch.matmul(torch.tanh(k).transpose(-2, -1), torch.tanh(u)))
-        y = y.permute(0, 2, 1, 3).contiguous().view(b, 1, self.cfg.d_model)
-        x = x + self.out_proj(y)
-        x = x + self.ffn(self.norm2(x))
-        if pos + 1 == self.chunk:
-            write = cache.write_accum / float(self.chunk)
-            cache.fast_state.mul_(fast_decay).add_(write * (1.0 - fast_decay))
-            cache.slow_state.mul_(slow_decay).add_(write * (1.0 - slow_decay))
-            cache.k_cache.zero_()
-            cache.v_cache.zero_()
-            cache.write_accum.zero_()
-            cache.chunk_len = 0
-        else:
-            cache.chunk_len = pos + 1
-        return x
+        """``x [B, 1, d]``: the next position of every sequence; ``cache`` moves on by one position."""
+        if x.shape[1] != 1:
+            raise ValueError("the decode step takes exactly one position per sequence")
+        batch = x.shape[0]
+        packed = self.in_proj(self.norm1(x)).view(batch, 5, self.h, 1, self.hd)
+        mixed, cache.chunk_len = R.decode_position(
+            *packed.unbind(1), cache.k_cache, cache.v_cache, cache.write_accum, cache.fast_state, cache.slow_state,
+            cache.chunk_len, self.chunk, self.fast_decay_logit, self.slow_decay_logit, self.memory_mix_logit)
+        return self._finish(x, mixed.transpose(1, 2).reshape(batch, 1, self.h * self.hd))
 
 
 class WarpStateLM(nn.Module):
+    """Token embedding, ``logical_depth`` passes through ``n_cores`` shared blocks (block ``depth % n_cores`` at each
+    depth, told apart by a learned per-depth scale and bias), a final norm and a head tied to the embedding."""
+
     def __init__(self, cfg: WarpStateConfig):
         super().__init__()
         cfg.validate()
         self.cfg = cfg
         self.embed = nn.Embedding(cfg.vocab_size, cfg.d_model)
-        self.cores = nn.ModuleList([WarpStateCore(cfg) for _ in range(cfg.n_cores)])
+        self.cores = nn.ModuleList(WarpStateCore(cfg) for _ in range(cfg.n_cores))
         self.depth_scale = nn.Parameter(torch.zeros(cfg.logical_depth, cfg.d_model))
         self.depth_bias = nn.Parameter(torch.zeros(cfg.logical_depth, cfg.d_model))
         self.final_norm = RMSNorm(cfg.d_model, cfg.rms_eps)
         self.reset_parameters()
 
     def reset_parameters(self) -> None:
-        """normal(0, 0.02) for matrices and the embedding; residual-writing projections are
-        scaled by 1/sqrt(2*logical_depth) (warpstate/model.py:291-304)."""
+        """Every matrix and the embedding from ``normal(0, 0.02)``; the two projections of a block that write into
+        the residual stream from a distribution narrower by ``sqrt(2 * logical_depth)``."""
         for module in self.modules():
             if isinstance(module, (nn.Linear, nn.Embedding)):
-                nn.init.normal_(module.weight, mean=0.0, std=0.02)
-        scale = 1.0 / math.sqrt(2.0 * self.cfg.logical_depth)
-        for core in self.cores:
-            nn.init.normal_(core.out_proj.weight, mean=0.0, std=0.02 * scale)
-            nn.init.normal_(core.ffn.down.weight, mean=0.0, std=0.02 * scale)
+                nn.init.normal_(module.weight, mean=0.0, std=INIT_STD)
+        narrow = INIT_STD / math.sqrt(2.0 * self.cfg.logical_depth)
+        for core in self.cores:          # drawn again, after all the others
+            for writer in (core.out_proj, core.ffn.down):
+                nn.init.normal_(writer.weight, mean=0.0, std=narrow)
 
     def num_parameters(self) -> int:
-        return sum(p.numel() for p in self.parameters())
+        return sum(parameter.numel() for parameter in self.parameters())
+
+    def _depths(self):
+        """(depth index, the block that runs at that depth)."""
+        return ((depth, self.cores[depth % self.cfg.n_cores]) for depth in range(self.cfg.logical_depth))
 
     # ------------------------------------------------------------------ trunk
     def hidden_states(self, input_ids: torch.Tensor) -> torch.Tensor:
-        """Embedding, all logical depths and the final norm: ``[B,T] -> [B,T,d]``."""
-        if _fused_active(self.embed.weight) and input_ids.is_cuda and not getattr(self, "sharded_linears", False):
+        """``[B, T]`` token ids -> ``[B, T, d]`` after the final norm."""
+        if input_ids.is_cuda and _kernels_take(self.embed.weight, self):
             from ..ops import fused
             return fused.trunk_forward(self, input_ids)
+        recompute = self.training and self.cfg.gradient_checkpointing and torch.is_grad_enabled()
         x = self.embed(input_ids)
-        for depth in range(self.cfg.logical_depth):
-            core = self.cores[depth % self.cfg.n_cores]
+        for depth, core in self._depths():
             x = x * (1.0 + self.depth_scale[depth]) + self.depth_bias[depth]
-            if self.training and self.cfg.gradient_checkpointing and torch.is_grad_enabled():
-                x = checkpoint(core, x, use_reentrant=False)
-            else:
-                x = core(x)
+            x = checkpoint(core, x, use_reentrant=False) if recompute else core(x)
         return self.final_norm(x)
+
+    def logits_from_hidden(self, x: torch.Tensor) -> torch.Tensor:
+        return torch.matmul(x, self.embed.weight.t())       # the head is the embedding, transposed
 
     def forward(self, input_ids: torch.Tensor, targets: torch.Tensor | None = None, *,
                 return_logits: bool = True):
+        """Three answers, as in the reference: logits when there are no ``targets``; ``(logits, mean loss)`` with
+        targets; ``(None, mean loss over targets != -100)`` with ``return_logits=False``, which never builds the
+        ``[tokens, vocabulary]`` matrix."""
         x = self.hidden_states(input_ids)
-        if targets is not None and not return_logits:
+        if targets is None:
+            return self.logits_from_hidden(x)
+        if not return_logits:
             return None, self.loss_from_hidden(x, targets)
         logits = self.logits_from_hidden(x)
-        if targets is None:
-            return logits
-        loss = F.cross_entropy(logits.reshape(-1, logits.size(-1)), targets.reshape(-1))
-        return logits, loss
-
-    def logits_from_hidden(self, x: torch.Tensor) -> torch.Tensor:
-        return F.linear(x, self.embed.weight)  # tied head
+        return logits, nn.functional.cross_entropy(logits.flatten(0, -2), targets.flatten())
 
     def loss_from_hidden(self, x: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
-        """Mean cross-entropy over labels != -100 without keeping ``[tokens, vocab]`` logits.
-        A rank whose labels are all masked gets a finite 0 (sum / max(count, 1))."""
-        hidden = x.reshape(-1, x.size(-1))
-        labels = targets.reshape(-1)
-        count = labels.ne(-100).sum().clamp_min(1)
-        if _fused_active(hidden):
+        """Mean cross-entropy over the labels that are not -100, a block of rows at a time.  Where every label is
+        masked (a rank without supervised tokens) the result is a finite 0: sum / max(count, 1)."""
+        rows, labels = x.flatten(0, -2), targets.flatten()
+        counted = (labels != R.IGNORE).sum().clamp(min=1)
+        if _kernels_take(rows, None):
             from ..ops import fused
-            return fused.lm_head_loss(hidden, self.embed.weight, labels) / count
-        rows = int(getattr(self, "loss_chunk_size", self.cfg.loss_chunk_size))
-        total = x.new_zeros((), dtype=torch.float32)
-        recompute = self.training and torch.is_grad_enabled()
-        for start in range(0, labels.numel(), rows):
-            h, y = hidden[start:start + rows], labels[start:start + rows]
-            if recompute:
-                total = total + checkpoint(R.lm_head_loss_sum, h, self.embed.weight, y, use_reentrant=False)
-            else:
-                total = total + R.lm_head_loss_sum(h, self.embed.weight, y)
-        return total / count
+            return fused.lm_head_loss(rows, self.embed.weight, labels) / counted
+        block = int(getattr(self, "loss_chunk_size", self.cfg.loss_chunk_size))
+        recompute = self.training and torch.is_grad_enabled()      # keep the hidden rows, not the logits, for backward
+        total = torch.zeros((), dtype=torch.float32, device=x.device)
+        for begin in range(0, labels.numel(), block):
+            piece = (rows[begin:begin + block], self.embed.weight, labels[begin:begin + block])
+            total = total + (checkpoint(R.lm_head_loss_sum, *piece, use_reentrant=False) if recompute
+                             else R.lm_head_loss_sum(*piece))
+        return total / counted
 
     def sequence_logps(self, input_ids: torch.Tensor, targets: torch.Tensor, head_chunk_size: int = 256) -> torch.Tensor:
-        """Per-sequence sum of label log-probabilities over positions whose target is not -100
-        (FP32, ``[B]``), without keeping ``[B, T, vocab]`` logits: the scoring head of DPO
-        (reference dpo.py:130-163)."""
+        """``[B]`` FP32: for each sequence, the sum of the log-probabilities of its targets (positions whose target is
+        -100 add nothing).  The scoring head of DPO (reference dpo.py:130-163); ``[B, T, vocabulary]`` is never held."""
         x = self.hidden_states(input_ids)
-        b, t, d = x.shape
-        if _fused_active(x):
+        batch, length, width = x.shape
+        if _kernels_take(x, None):
             from ..ops import lmhead
-            hidden = x.reshape(b * t, d)
-            if hidden.dtype != torch.bfloat16:
-                hidden = hidden.to(torch.bfloat16)
-            if lmhead.kernels_ready(hidden, self.embed.weight):
-                return lmhead.token_logps(hidden, self.embed.weight, targets.reshape(-1)).view(b, t).sum(dim=1)
+            rows = x.reshape(batch * length, width).to(torch.bfloat16)
+            if lmhead.kernels_ready(rows, self.embed.weight):
+                return lmhead.token_logps(rows, self.embed.weight, targets.reshape(-1)).view(batch, length).sum(dim=1)
 
-        def score(h, weight, labels):
-            return R.lm_head_token_logps(h.reshape(-1, h.size(-1)), weight, labels.reshape(-1)).view(labels.shape).sum(dim=1)
+        def span_score(hidden, weight, labels):
+            flat = R.lm_head_token_logps(hidden.flatten(0, 1), weight, labels.flatten())
+            return flat.view(labels.shape).sum(dim=1)
 
-        logps = x.new_zeros((b,), dtype=torch.float32)
-        for start in range(0, t, head_chunk_size):
-            args = (x[:, start:start + head_chunk_size], self.embed.weight, targets[:, start:start + head_chunk_size])
-            logps = logps + (checkpoint(score, *args, use_reentrant=False) if torch.is_grad_enabled() else score(*args))
-        return logps
+        scores = torch.zeros(batch, dtype=torch.float32, device=x.device)
+        for begin in range(0, length, head_chunk_size):
+            span = slice(begin, begin + head_chunk_size)
+            piece = (x[:, span], self.embed.weight, targets[:, span])
+            scores = scores + (checkpoint(span_score, *piece, use_reentrant=False) if torch.is_grad_enabled()
+                               else span_score(*piece))
+        return scores
 
     # ------------------------------------------------------------------ decode
     @torch.no_grad()
     def init_generation_cache(self, batch_size: int, device: torch.device, dtype: torch.dtype) -> List[LayerCache]:
-        return [self.cores[depth % self.cfg.n_cores].init_cache(batch_size, device, dtype)
-                for depth in range(self.cfg.logical_depth)]
+        """One cache per logical depth: blocks are shared between depths, their decode state is not."""
+        return [core.init_cache(batch_size, device, dtype) for _, core in self._depths()]
 
     @torch.no_grad()
     def step(self, input_ids: torch.Tensor, caches: List[LayerCache]) -> torch.Tensor:
-        """``input_ids [B,1]`` -> logits ``[B,1,V]``; caches are updated in place."""
+        """``input_ids [B, 1]`` -> logits ``[B, 1, V]``; ``caches`` move on by one position."""
         x = self.embed(input_ids)
-        for depth in range(self.cfg.logical_depth):
-            x = x * (1.0 + self.depth_scale[depth]) + self.depth_bias[depth]
-            x = self.cores[depth % self.cfg.n_cores].step(x, caches[depth])
-        return F.linear(self.final_norm(x), self.embed.weight)
+        for depth, core in self._depths():
+            x = core.step(x * (1.0 + self.depth_scale[depth]) + self.depth_bias[depth], caches[depth])
+        return self.logits_from_hidden(self.final_norm(x))
