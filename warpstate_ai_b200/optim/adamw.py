@@ -4,10 +4,8 @@ Same update rule, defaults and state-dict layout as the reference's optimizer
 (``torch.optim.AdamW(lr, betas=(0.9, 0.95), eps=1e-8, weight_decay, fused=True)`` on all
 parameters in one group, reference run_40b.py:534-535; global-norm clip at 1.0 with a
 non-finite check, run_40b.py:751), executed as three kernels over the flat arena on CUDA
-(`ops/csrc/optim.cu`) and as a handful of vector ops on CPU.
-
-With ``shard=(rank, world)`` only a contiguous 1/world slice of the arena is owned: moments exist
-only for the slice, the norm is combined across ranks, and the caller gathers updated weights.
+(`ops/csrc/optim.cu`) and as a handful of vector ops on CPU.  The sharded forms are `parallel.zero.ShardedAdamW`
+(moments per bucket slice) and `parallel.fsdp.ShardedParamAdamW` (parameters, gradients and moments per row owner).
 """
 from __future__ import annotations
 
@@ -49,8 +47,7 @@ def host_adamw(p, grad, m, v, lr, b1, b2, eps, weight_decay, step) -> None:
 
 class ArenaAdamW:
     def __init__(self, arena: ParamArena, lr: float = 1.5e-4, betas=(0.9, 0.95), eps: float = 1e-8,
-                 weight_decay: float = 0.1, max_grad_norm: float | None = 1.0,
-                 shard: tuple[int, int] | None = None):
+                 weight_decay: float = 0.1, max_grad_norm: float | None = 1.0):
         self.arena = arena
         self.lr = lr
         self.betas = betas
@@ -58,15 +55,7 @@ class ArenaAdamW:
         self.weight_decay = weight_decay
         self.max_grad_norm = max_grad_norm
         self.step_count = 0
-        self.shard = shard
-        if shard is None:
-            self.lo, self.hi = 0, arena.numel
-        else:
-            rank, world = shard
-            # arena.numel is a multiple of 256; split on 256-element boundaries, remainder to last rank
-            per = (arena.numel // 256 // world) * 256
-            self.lo = rank * per
-            self.hi = arena.numel if rank == world - 1 else (rank + 1) * per
+        self.lo, self.hi = 0, arena.numel          # the range of the arena this optimizer updates: all of it
         n = self.hi - self.lo
         self.exp_avg = torch.zeros(n, dtype=torch.float32, device=arena.device)
         self.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=arena.device)
@@ -126,8 +115,6 @@ class ArenaAdamW:
     def state_dict(self) -> dict:
         """Same structure as ``torch.optim.AdamW.state_dict()``: integer keys in
         ``model.parameters()`` order with ``step / exp_avg / exp_avg_sq`` and one param group."""
-        if self.shard is not None:
-            raise RuntimeError("gather the shards first (parallel.zero.gather_optimizer_state)")
         a = self.arena
         state = {}
         for index, (name, _p) in enumerate(a.order):

@@ -226,7 +226,7 @@ class ShardedAdamW:
         self.gather_master()
         whole = ArenaAdamW.__new__(ArenaAdamW)
         whole.arena, whole.lr, whole.betas, whole.eps = self.arena, self.lr, self.betas, self.eps
-        whole.weight_decay, whole.step_count, whole.shard = self.weight_decay, self.step_count, None
+        whole.weight_decay, whole.step_count = self.weight_decay, self.step_count
         whole.exp_avg = self.gather_full(self.exp_avg)
         whole.exp_avg_sq = self.gather_full(self.exp_avg_sq)
         return whole.state_dict()
@@ -235,7 +235,7 @@ class ShardedAdamW:
         from ..optim.adamw import ArenaAdamW
         whole = ArenaAdamW.__new__(ArenaAdamW)
         whole.arena, whole.lr, whole.betas, whole.eps = self.arena, self.lr, self.betas, self.eps
-        whole.weight_decay, whole.step_count, whole.shard = self.weight_decay, 0, None
+        whole.weight_decay, whole.step_count = self.weight_decay, 0
         whole.lo, whole.hi = 0, self.arena.numel
         # one arena-sized scratch at a time, on the host for large models
         where = "cpu" if self.arena.numel > (1 << 28) else self.arena.device
