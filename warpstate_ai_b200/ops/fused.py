@@ -95,17 +95,6 @@ def bf16_weight(p: torch.Tensor) -> torch.Tensor:
     return w
 
 
-def _wgrad(dy: torch.Tensor, x: torch.Tensor, p: torch.Tensor):
-    """dW = dy^T x accumulated in FP32.  Returns the tensor autograd should see (or None)."""
-    main = getattr(p, "main_grad", None)
-    if main is not None:
-        G.grad_weight_accumulate(dy, x, main, accumulate=True)
-        return None
-    grad = torch.empty(p.shape, dtype=torch.float32, device=p.device)
-    G.grad_weight_accumulate(dy, x, grad, accumulate=False)
-    return grad.to(p.dtype)
-
-
 def _wgrad_group(items):
     """``items`` = [(dy, x, param), ...] -> list of gradients for autograd (None where the result
     was accumulated into ``param.main_grad``).  All products run as one grouped launch."""

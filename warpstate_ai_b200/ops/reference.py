@@ -70,12 +70,6 @@ def decay_weights(logit: torch.Tensor, n_chunks: int, rows: int | None = None) -
     return torch.where(age >= 0, (1.0 - keep) * torch.pow(keep, age.clamp(min=0)), torch.zeros((), device=logit.device))
 
 
-def prefix_states(writes: torch.Tensor, logit: torch.Tensor) -> torch.Tensor:
-    """``writes [b, n, h, x, y]`` -> the state each chunk reads (decayed sum of the earlier chunks' writes)."""
-    weights = decay_weights(logit, writes.shape[1]).to(writes.dtype)
-    return torch.einsum("hij,bjhxy->bihxy", weights, writes)
-
-
 def states_seen(writes: torch.Tensor, logit: torch.Tensor, parallel: bool):
     """-> (state read by every chunk ``[b, n, h, x, y]``, state after the last chunk ``[b, h, x, y]``).
 

@@ -164,9 +164,6 @@ class ParamArena:
                 target.add_(g.to(target.dtype))
                 s.param.grad = target
 
-    def bucket_ranges(self) -> list[tuple[int, int]]:
-        return [(b.start, b.stop) for b in self.buckets]
-
     # ------------------------------------------------------------------ state dict helpers
     def named_master(self) -> Iterable[tuple[str, torch.Tensor]]:
         for name, p in self.order:
