@@ -137,3 +137,55 @@ def test_shim_package_exports():
     import warpstate
     from warpstate.model import WarpStateLM as Shim
     assert warpstate.WarpStateLM is Shim is WarpStateLM
+
+
+def test_exported_helpers_match_the_reference():
+    """`warpstate.model` also exports the rotary helpers and the small modules; same numbers, same call forms."""
+    _, ref = load_reference()
+    import warpstate.model as ours
+    torch.manual_seed(3)
+    cos_o, sin_o = ours.rope_cos_sin(8, 6, torch.device("cpu"), torch.float32)
+    cos_r, sin_r = ref.rope_cos_sin(8, 6, torch.device("cpu"), torch.float32)
+    assert torch.equal(cos_o, cos_r) and torch.equal(sin_o, sin_r)
+    x = torch.randn(2, 3, 4, 8, 6)
+    assert torch.equal(ours.rotate_half(x), ref.rotate_half(x))
+    assert torch.allclose(ours.apply_rope(x, cos_o, sin_o), ref.apply_rope(x, cos_r, sin_r), rtol=0, atol=1e-7)
+    norm_o, norm_r = ours.RMSNorm(6, eps=1e-5), ref.RMSNorm(6, eps=1e-5)
+    with torch.no_grad():
+        norm_o.weight.normal_()
+        norm_r.weight.copy_(norm_o.weight)
+    for value in (x, x.bfloat16()):
+        assert torch.equal(norm_o(value), norm_r(value))
+    ffn_o, ffn_r = ours.SwiGLU(6, 10), ref.SwiGLU(6, 10)
+    ffn_r.load_state_dict(ffn_o.state_dict())
+    assert torch.allclose(ffn_o(x), ffn_r(x), rtol=1e-6, atol=1e-7)
+    assert [f for f in ours.LayerCache.__dataclass_fields__] == [f for f in ref.LayerCache.__dataclass_fields__]
+
+
+@pytest.mark.parametrize("parallel", [False, True])
+def test_one_core_matches_the_reference_core_with_gradients(parallel):
+    cfg_mod, ref = load_reference()
+    from warpstate_ai_b200.models.warpstate import WarpStateCore
+    torch.manual_seed(4)
+    ours = WarpStateCore(WarpStateConfig(**tiny(parallel)))
+    theirs = ref.WarpStateCore(cfg_mod.WarpStateConfig(**tiny(parallel)))
+    with torch.no_grad():
+        for logit in (ours.fast_decay_logit, ours.slow_decay_logit, ours.memory_mix_logit):
+            logit.add_(torch.randn_like(logit))
+    theirs.load_state_dict(ours.state_dict())
+    assert torch.equal(ours.rope_cos, theirs.rope_cos) and torch.equal(ours.rope_sin, theirs.rope_sin)
+    xo = torch.randn(2, 24, 32, requires_grad=True)
+    xr = xo.detach().clone().requires_grad_(True)
+    weight = torch.randn(2, 24, 32)
+    (ours(xo) * weight).sum().backward()
+    (theirs(xr) * weight).sum().backward()
+    assert torch.allclose(xo.grad, xr.grad, rtol=1e-4, atol=1e-6)
+    for (name, po), (_, pr) in zip(ours.named_parameters(), theirs.named_parameters()):
+        assert torch.allclose(po.grad, pr.grad, rtol=1e-4, atol=2e-6), name
+    caches = (ours.init_cache(2, torch.device("cpu"), torch.float32), theirs.init_cache(2, torch.device("cpu"), torch.float32))
+    for position in range(11):                                   # crosses the 8-position chunk boundary
+        token = torch.randn(2, 1, 32)
+        assert torch.allclose(ours.step(token, caches[0]), theirs.step(token, caches[1]), rtol=1e-5, atol=1e-6)
+        assert caches[0].chunk_len == caches[1].chunk_len == (position + 1) % 8
+        for field in ("fast_state", "slow_state", "k_cache", "v_cache", "write_accum"):
+            assert torch.allclose(getattr(caches[0], field), getattr(caches[1], field), rtol=1e-5, atol=1e-6), field
