@@ -1,0 +1,222 @@
+"""Differential tests: pure functions of this package against the reference's own, with the reference imported as a
+library from ``baseline/_ref`` (skipped where it is not installed).  Random or enumerated inputs, same outputs.
+
+Covered: token windows and update slices, resume-signature decisions, SFT batching and schedules, the SFT and DPO
+renderers and collators, the chat prompt, sampling and n-gram bans, the DPO objective and its schedule.
+"""
+import contextlib
+import importlib
+import itertools
+import random
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+REF = Path(__file__).resolve().parents[1] / "baseline" / "_ref"
+TOK = Path(__file__).resolve().parents[1] / "tokenizer.model"
+SHADOWED = ("warpstate", "ops", "run_40b", "posttrain", "dpo", "chat")
+
+
+@contextlib.contextmanager
+def reference_import_path():
+    """Inside the block, ``import run_40b`` / ``ops.*`` / ``warpstate`` resolve to the reference's files; afterwards the
+    repository's own modules of the same names are back."""
+    def ours(name):
+        return name in SHADOWED or name.split(".")[0] in SHADOWED
+    saved = {name: module for name, module in sys.modules.items() if ours(name)}
+    for name in saved:
+        del sys.modules[name]
+    saved_path = list(sys.path)
+    root = str(REF.parents[1])
+    sys.path[:] = [str(REF)] + [p for p in sys.path if p not in ("", root) and Path(p or ".").resolve() != REF.parents[1]]
+    try:
+        yield
+    finally:
+        sys.path[:] = saved_path
+        for name in [name for name in sys.modules if ours(name)]:
+            del sys.modules[name]
+        sys.modules.update(saved)
+
+
+@pytest.fixture(scope="module")
+def ref():
+    if not (REF / "run_40b.py").exists():
+        pytest.skip("reference not installed under baseline/_ref")
+    with reference_import_path():
+        modules = {name: importlib.import_module(name) for name in
+                   ("run_40b", "posttrain", "dpo", "chat", "ops.posttrain_data", "ops.dpo_data", "ops.posttrain_chat")}
+    for module in modules.values():
+        assert str(REF) in str(module.__file__)
+    return modules
+
+
+@pytest.fixture(scope="module")
+def tokenizer():
+    import sentencepiece as spm
+    return spm.SentencePieceProcessor(model_file=str(TOK))
+
+
+# ------------------------------------------------------------------------------------------- pretraining data path
+def test_token_windows_and_update_slices(ref):
+    from warpstate_ai_b200.data import tokens as T
+    data = np.random.default_rng(0).integers(0, 32768, size=997, dtype=np.uint16)
+    for cursor, batch, length, valid in [(0, 2, 8, 16), (990, 2, 8, 5), (5000, 3, 16, 0), (996, 1, 4, 4), (123, 4, 32, 100)]:
+        ours = T.batches(data, cursor, batch, length, valid, torch.device("cpu"))
+        theirs = ref["run_40b"].batches(data, cursor, batch, length, valid, torch.device("cpu"))
+        assert all(torch.equal(a, b) and a.dtype == b.dtype for a, b in zip(ours, theirs))
+    for target, micro, world in itertools.product((1, 9, 32, 73, 1000), (8, 16, 24), (1, 2, 3)):
+        for rank in range(world):
+            assert list(T.update_slices(target, micro, world, rank)) == list(ref["run_40b"].update_slices(target, micro, world, rank))
+
+
+def test_resume_signature_decisions(ref):
+    from warpstate_ai_b200.train.signature import check_resume_signature
+    base = {"settings": {"seq_len": 2048, "micro_batch": 8, "grad_accum": 4, "train_tokens": 10 ** 10, "lr": 1.5e-4, "min_lr": 1.5e-5,
+                         "warmup_steps": 1000, "weight_decay": 0.1, "seed": 1, "activation_checkpointing": True,
+                         "loss_chunk_size": 128, "compile": False, "world_size": 2},
+            "data": {"tokens": 123, "sha": "abc"}}
+    changes = [{}, {"micro_batch": 4, "grad_accum": 8}, {"micro_batch": 4}, {"world_size": 4, "grad_accum": 2}, {"lr": 1e-4},
+               {"seed": 2}, {"loss_mode": "full"}, {"bf16_residuals": True, "compile_core": True}, {"train_tokens": 5},
+               {"ddp_bucket_cap_mb": 64}, {"gradient_mode": "compiled-autograd"}, {"seq_len": 1024, "micro_batch": 16},
+               {"activation_checkpointing": False, "loss_chunk_size": 256}, {"warmup_steps": 10}, {"matmul_execution": {"plan": 1}}]
+
+    def outcome(check, old, new, reconfigure):
+        try:
+            return check(old, new, reconfigure)
+        except ValueError as problem:
+            return str(problem)
+
+    for change, reconfigure, other_data in itertools.product(changes, (False, True), (False, True)):
+        new = {"settings": dict(base["settings"], **change), "data": dict(base["data"], sha="xyz") if other_data else dict(base["data"])}
+        legacy = {"settings": {k: v for k, v in base["settings"].items() if k != "world_size"}, "data": dict(base["data"])}
+        for old in (base, legacy):
+            assert outcome(check_resume_signature, old, new, reconfigure) == \
+                outcome(ref["run_40b"].check_resume_signature, old, new, reconfigure), (change, reconfigure, other_data)
+
+
+# ------------------------------------------------------------------------------------------- SFT batching, schedules
+def test_sft_batching_and_schedules(ref):
+    from warpstate_ai_b200.data import sft as SD
+    from warpstate_ai_b200.train import sft as ST
+    theirs = ref["posttrain"]
+    for size, seed, epochs, batch in [(10, 3, 2, 4), (7, 0, 3, 7), (33, 9, 1, 8), (5, 1, 2, 16)]:
+        assert list(SD.epoch_order(size, seed, 1)) == list(theirs.epoch_order(size, seed, 1))
+        cursor_a = cursor_b = 0
+        while True:
+            a = SD.update_indices(size, seed, cursor_a, epochs, batch)
+            b = theirs.update_indices(size, seed, cursor_b, epochs, batch)
+            assert (list(a[0]), a[1]) == (list(b[0]), b[1])
+            if not a[0]:
+                break
+            cursor_a, cursor_b = a[1], b[1]
+    records = [{"input_ids": [1, 5, 6, 7], "labels": [-100, -100, 6, 7]}, None, {"input_ids": [1, 9], "labels": [-100, 9]}]
+    for a, b in zip(SD.collate(records, 6, 0), theirs.collate(records, 6, 0)):
+        assert torch.equal(a, b)
+    settings = {"lr": 1e-5, "min_lr": 1e-6, "warmup_ratio": 0.03}
+    for total in (1, 2, 7, 100, 1234):
+        for step in range(0, total, max(1, total // 50)):
+            assert ST.learning_rate(step, total, settings) == pytest.approx(theirs.learning_rate(step, total, settings), rel=1e-12)
+    loss = torch.tensor(2.5)
+    for local, total, world in [(3, 3, 2), (0, 7, 2), (5, 12, 4)]:
+        assert torch.equal(ST.token_weighted_loss(loss, local, total, world), theirs.token_weighted_loss(loss, local, total, world))
+
+
+def test_dpo_schedule_objective_and_identity(ref):
+    from warpstate_ai_b200.train import dpo as DT
+    from warpstate_ai_b200.train.reference_cache import identity_digest
+    theirs = ref["dpo"]
+    settings = {"lr": 5e-7, "min_lr": 0.0, "warmup_ratio": 0.1}
+    for total in (1, 3, 10, 777):
+        for step in range(total):
+            assert DT.learning_rate(step, total, settings) == pytest.approx(theirs.learning_rate(step, total, settings), rel=1e-12, abs=1e-20)
+    torch.manual_seed(0)
+    policy = (torch.randn(6, 2) * 20).requires_grad_(True)
+    reference = torch.randn(6, 2, dtype=torch.float64) * 20
+    counts = torch.randint(1, 50, (6, 2))
+    for objective, beta in (("length-normalized-dpo", 5.0), ("summed-dpo", 0.1)):
+        mine = DT.preference_metrics(policy, reference, counts, beta, objective)
+        other = theirs.preference_metrics(policy, reference, counts, beta, objective)
+        for a, b in zip(mine, other):
+            assert torch.allclose(a, b, rtol=1e-6, atol=1e-7)
+        grad_a, = torch.autograd.grad(mine[0].sum(), policy, retain_graph=True)
+        grad_b, = torch.autograd.grad(other[0].sum(), policy)
+        assert torch.allclose(grad_a, grad_b, rtol=1e-6, atol=1e-8)
+    identity = {"weights": "aa", "nested": {"b": 1, "a": [1, 2.5, None]}, "world": 8}
+    assert identity_digest(identity) == theirs.identity_digest(identity)
+
+
+# ------------------------------------------------------------------------------------------- renderers
+CONVERSATIONS = [
+    [{"role": "user", "content": "Name a colour."}, {"role": "assistant", "content": "Blue."}],
+    [{"role": "system", "content": "Be brief."}, {"role": "user", "content": "2+2?"}, {"role": "assistant", "content": "4"},
+     {"role": "user", "content": "And 3+3?"}, {"role": "assistant", "content": "Six, of course."}],
+    [{"role": "user", "content": "Use the tool."}, {"role": "assistant", "content": "calling"}, {"role": "tool", "content": "{\"x\": 1}"},
+     {"role": "assistant", "content": "It says x is 1.  Ünïcödé too."}],
+]
+
+
+def test_sft_renderer_and_chat_prompt(ref, tokenizer):
+    from warpstate_ai_b200.data import sft as SD
+    from warpstate_ai_b200.serve import posttrain_chat as PC
+    for messages in CONVERSATIONS:
+        assert SD.encode_messages(messages, tokenizer) == ref["ops.posttrain_data"].encode_messages(messages, tokenizer)
+        assert SD.encode_messages(messages, tokenizer, max_length=512) == ref["ops.posttrain_data"].encode_messages(messages, tokenizer, 512)
+        prompt = messages[:-1]
+        assert PC.encode_prompt(prompt, tokenizer) == ref["ops.posttrain_chat"].encode_prompt(prompt, tokenizer)
+    bad = [[], [{"role": "user", "content": "no answer"}], [{"role": "user", "content": ""}, {"role": "assistant", "content": "x"}],
+           [{"role": "wizard", "content": "x"}, {"role": "assistant", "content": "y"}]]
+    for messages in bad:
+        for function in (SD.encode_messages, ref["ops.posttrain_data"].encode_messages):
+            with pytest.raises(ValueError):
+                function(messages, tokenizer)
+    for function in (SD.encode_messages, ref["ops.posttrain_data"].encode_messages):
+        with pytest.raises(ValueError):
+            function(CONVERSATIONS[1], tokenizer, max_length=8)
+
+
+def test_preference_pairs_and_their_collation(ref, tokenizer):
+    from warpstate_ai_b200.data import dpo as DD
+    rows = [{"prompt": conversation[:-1], "chosen": [conversation[-1]], "rejected": [{"role": "assistant", "content": "I would rather not."}]}
+            for conversation in CONVERSATIONS]
+    pairs = []
+    for row in rows:
+        mine = DD.encode_pair(row, tokenizer, 256)
+        assert mine == ref["ops.dpo_data"].encode_pair(row, tokenizer, 256)
+        pairs.append(mine)
+    for a, b in zip(DD.collate_pairs([pairs[0], None, pairs[2]], 96, 0), ref["ops.dpo_data"].collate_pairs([pairs[0], None, pairs[2]], 96, 0)):
+        assert torch.equal(a, b)
+    bad = dict(rows[0], rejected=rows[0]["chosen"])
+    for function in (DD.encode_pair, ref["ops.dpo_data"].encode_pair):
+        with pytest.raises(ValueError):
+            function(bad, tokenizer, 256)
+        with pytest.raises(ValueError):
+            function(dict(rows[1], prompt=CONVERSATIONS[1][:3]), tokenizer, 256)     # prompt ends with an assistant turn
+
+
+# ------------------------------------------------------------------------------------------- sampling
+def test_sampling_and_ngram_bans(ref):
+    from warpstate_ai_b200.serve import sampling as S
+    rng = random.Random(0)
+    for _ in range(200):
+        tokens = [rng.randrange(4) for _ in range(rng.randrange(0, 12))]
+        size = rng.randrange(0, 5)
+        assert set(S.banned_ngram_tokens(tokens, size)) == set(ref["chat"].banned_ngram_tokens(tokens, size)), (tokens, size)
+    torch.manual_seed(1)
+    for case in range(60):
+        logits = torch.randn(24) * 3
+        previous = [rng.randrange(24) for _ in range(rng.randrange(0, 6))]
+        banned = {rng.randrange(24) for _ in range(rng.randrange(0, 4))}
+        settings = dict(temperature=rng.choice([0.0, 0.5, 1.0, 1.7]), top_k=rng.choice([0, 1, 5, 40]), top_p=rng.choice([0.3, 0.9, 1.0]))
+        penalty = rng.choice([1.0, 1.2, 2.0])
+        draws = []
+        for function in (S.sample_token, ref["chat"].sample_token):
+            generator = torch.Generator().manual_seed(case)
+            draws.append([function(logits, settings["temperature"], settings["top_k"], settings["top_p"], generator,
+                                   previous_tokens=previous, repetition_penalty=penalty, banned_tokens=banned) for _ in range(5)])
+        assert draws[0] == draws[1], (case, settings, penalty)
+    everything = set(range(24))
+    assert S.sample_token(torch.zeros(24), 0.0, 0, 1.0, torch.Generator(), banned_tokens=everything) is None
+    assert ref["chat"].sample_token(torch.zeros(24), 0.0, 0, 1.0, torch.Generator(), banned_tokens=everything) is None
