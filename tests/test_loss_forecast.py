@@ -87,7 +87,7 @@ def test_command_line_writes_a_self_describing_report(tmp_path, capsys):
     assert all("cross_2.3_tokens_B" in f for f in report["fits"])
     free = next(f for f in report["fits"] if f["start_B"] == 1 and f["parameters"]["model"] == "power_free")
     assert free["cross_2.3_tokens_B"] == pytest.approx(25.0, rel=0.2)      # 1.5 t^-0.5 = 0.3
-    assert set(free["endpoint_losses"]) == {"40B", "268.435B", "1073.74B"}
+    assert set(free["endpoint_losses"]) == {"40B", "268.435456B", "1073.741824B"}
     assert report["holdouts"] == []                                        # no complete billion after 4 B to test on
     with pytest.raises(SystemExit):
         LF.main(["--input", str(source), "--output", str(source)])

@@ -1,0 +1,157 @@
+"""Differential tests of the analysis and checkpoint tools against the reference's own functions, imported from
+``baseline/_ref`` (skipped where it is not installed): chrome-trace overlap analysis, loss-curve fits and the frozen
+host snapshot of a training state."""
+import copy
+import importlib
+import json
+import random
+from collections import OrderedDict
+
+import numpy as np
+import pytest
+import torch
+
+from test_reference_parity import REF, reference_import_path
+
+
+@pytest.fixture(scope="module")
+def ref():
+    if not (REF / "ops" / "analyze_communication_profile.py").exists():
+        pytest.skip("reference not installed under baseline/_ref")
+    with reference_import_path():
+        return {name: importlib.import_module(name) for name in
+                ("ops.analyze_communication_profile", "ops.loss_curve_forecast", "ops.checkpoint_writer")}
+
+
+# ------------------------------------------------------------------------------------------- trace analysis
+def synthetic_trace(seed, rank=0):
+    rng = random.Random(seed)
+    events = []
+    clock = 1000.0
+    for index in range(120):
+        kind = rng.random()
+        duration = rng.choice([5.0, 40.0, 250.0, 900.0])
+        begin = clock + rng.choice([-30.0, 0.0, 3.0, 60.0])
+        if kind < 0.55:
+            events.append({"ph": "X", "cat": "kernel", "name": f"gemm_kernel_{index % 5}", "ts": begin, "dur": duration,
+                           "args": {"device": 0, "stream": 7}})
+        elif kind < 0.8:
+            events.append({"ph": "X", "cat": "kernel", "name": "ncclDevKernel_AllReduce_Sum_f32_RING_LL(ncclDevKernelArgsStorage<4096ul>)",
+                           "ts": begin, "dur": duration, "args": {"device": 0, "stream": 21}})
+        elif kind < 0.9:
+            events.append({"ph": "X", "cat": "gpu_memcpy", "name": "Memcpy HtoD", "ts": begin, "dur": duration, "args": {"device": 0, "stream": 9}})
+        elif kind < 0.95:
+            events.append({"ph": "X", "cat": "gpu_user_annotation", "name": "range", "ts": begin, "dur": duration, "args": {"device": 0}})
+        else:
+            events.append({"ph": "X", "cat": "cpu_op", "name": "aten::mm", "ts": begin, "dur": duration})
+        clock = begin + duration * rng.choice([0.3, 1.0, 1.0, 1.5])
+    events.append({"ph": "i", "name": "marker", "ts": clock})
+    events.append({"ph": "X", "cat": "gpu_memset", "name": "Memset", "ts": clock + 5, "dur": 0.0, "args": {"device": 1, "stream": 3}})
+    events.append({"ph": "X", "cat": "kernel", "name": "elementwise", "ts": clock + 9, "dur": 12.5, "args": {"device": 1, "stream": 3}})
+    return {"traceEvents": events, "distributedInfo": {"rank": rank, "world_size": 2, "backend": "nccl"}}
+
+
+TIMES = ("activity_span_us", "active_union_us", "idle_within_activity_span_us", "noncommunication_union_us",
+         "communication_union_us", "compute_only_us", "compute_communication_overlap_us", "communication_only_us",
+         "communication_overlap_fraction", "summed_noncommunication_us", "summed_communication_us")
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_overlap_analysis_of_a_trace(ref, seed):
+    from warpstate_ai_b200.bench import comm_profile as CP
+    trace = synthetic_trace(seed, rank=seed % 2)
+    mine, theirs = CP.summarize_trace(copy.deepcopy(trace)), ref["ops.analyze_communication_profile"].summarize_trace(trace)
+    assert mine["rank"] == theirs["rank"] and mine["distributed_info"] == theirs["distributed_info"]
+    assert mine["excluded_gpu_annotation_ranges"] == theirs["excluded_gpu_annotation_ranges"]
+    assert [d["device"] for d in mine["devices"]] == [d["device"] for d in theirs["devices"]] == ["0", "1"]
+    for a, b in zip(mine["devices"], theirs["devices"]):
+        for key in TIMES:
+            assert a[key] == pytest.approx(b[key], rel=1e-12, abs=1e-9), (key, a["device"])
+        assert a["nccl_kernel_names"] == b["nccl_kernel_names"]
+        assert a["nccl_kernel_count"] == b["nccl_kernel_count"]
+
+
+def test_malformed_activities_are_refused_by_both(ref):
+    from warpstate_ai_b200.bench import comm_profile as CP
+    for bad in ({"ts": float("nan"), "dur": 1.0}, {"ts": 1.0, "dur": -2.0}, {"ts": "1", "dur": 1.0}, {"ts": 1.0}):
+        trace = {"traceEvents": [{"ph": "X", "cat": "kernel", "name": "k", "args": {"device": 0}, **bad}]}
+        for function in (CP.summarize_trace, ref["ops.analyze_communication_profile"].summarize_trace):
+            with pytest.raises(ValueError):
+                function(trace)
+    empty = {"traceEvents": []}
+    assert CP.summarize_trace(empty)["devices"] == ref["ops.analyze_communication_profile"].summarize_trace(empty)["devices"] == []
+
+
+# ------------------------------------------------------------------------------------------- loss-curve fits
+def test_curve_fits_predictions_and_crossings(ref):
+    from warpstate_ai_b200.analysis import loss_forecast as LF
+    theirs = ref["ops.loss_curve_forecast"]
+    rng = np.random.default_rng(0)
+    t = np.linspace(1.0, 9.0, 33)
+    curves = [2.0 + 1.3 * t ** -0.4, 1.7 + 0.9 * t ** -0.9 + rng.normal(0, 2e-3, t.size), 3.0 - 0.3 * np.log(t) + rng.normal(0, 1e-3, t.size),
+              np.full_like(t, 2.4) + rng.normal(0, 1e-3, t.size)]
+    for loss in curves:
+        for model in ("log", "power_free", "power_fixed:1.5", "power_fixed:1.9"):
+            mine, other = LF.fit(t, loss, model), theirs.fit(t, loss, model)
+            assert mine["model"] == other["model"]
+            assert mine["rmse"] == pytest.approx(other["rmse"], rel=1e-4, abs=1e-9)                      # same optimum ...
+            budgets = [12.0, 40.0, 268.435456]
+            assert LF.predict(mine, budgets) == pytest.approx(theirs.predict(other, budgets), rel=2e-3)   # ... same forecast
+            for target in (1.0, 2.0, 2.3):
+                a, b = LF.crossing(mine, target), theirs.crossing(other, target)
+                assert (a is None) == (b is None), (model, target)
+                if a is not None and b < 1e6:
+                    assert a == pytest.approx(b, rel=0.05)
+            if model == "log":
+                assert mine["slope"] == pytest.approx(other["slope"], rel=1e-9) and mine["intercept"] == pytest.approx(other["intercept"], rel=1e-9)
+    with pytest.raises(ValueError):
+        LF.fit(t[:2], curves[0][:2], "log")
+    with pytest.raises(ValueError):
+        theirs.fit(t[:2], curves[0][:2], "log")
+
+
+def test_whole_report_on_a_validation_log(ref):
+    from warpstate_ai_b200.analysis import loss_forecast as LF
+    rows = [{"tokens": int(t * 1e9), "loss": 1.8 + 1.1 * t ** -0.45} for t in np.arange(1.0, 7.31, 0.05)]
+    raw = ("\n".join(json.dumps(r) for r in rows) + "\n").encode()
+    mine, theirs = LF.analyze(raw), ref["ops.loss_curve_forecast"].analyze(raw)
+    assert mine["source_sha256"] == theirs["source_sha256"] and mine["source_rows"] == theirs["source_rows"]
+    assert mine["complete_bins_end_B"] == theirs["complete_bins_end_B"] and len(mine["bins"]) == len(theirs["bins"])
+    for a, b in zip(mine["bins"], theirs["bins"]):
+        assert a["count"] == b["count"] and a["loss"] == pytest.approx(b["loss"], rel=1e-12) and a["tokens_B"] == pytest.approx(b["tokens_B"], rel=1e-12)
+    assert [(f["start_B"], f["parameters"]["model"]) for f in mine["fits"]] == [(f["start_B"], f["parameters"]["model"]) for f in theirs["fits"]]
+    for a, b in zip(mine["fits"], theirs["fits"]):
+        assert a["parameters"]["rmse"] == pytest.approx(b["parameters"]["rmse"], rel=1e-3, abs=1e-9)
+        for budget, value in a["endpoint_losses"].items():
+            assert value == pytest.approx(b["endpoint_losses"][budget], rel=2e-3)
+    assert mine["observed_validation"] == theirs["observed_validation"] and mine["latest_validation"] == theirs["latest_validation"]
+    assert len(mine["holdouts"]) == len(theirs["holdouts"])
+    for a, b in zip(mine["holdouts"], theirs["holdouts"]):
+        assert (a["train_end_B"], a["test_end_B"]) == (b["train_end_B"], b["test_end_B"])
+        assert a["actual_mean_loss"] == pytest.approx(b["actual_mean_loss"], rel=1e-12)
+        assert a["predicted_mean_loss"] == pytest.approx(b["predicted_mean_loss"], rel=1e-3)
+
+
+# ------------------------------------------------------------------------------------------- checkpoint snapshots
+def test_frozen_snapshot_of_a_training_state(ref, tmp_path):
+    from warpstate_ai_b200.ckpt import writer as W
+    shared = torch.arange(6.0)
+    state = {"model": OrderedDict(a=shared, b=shared, c=torch.ones(2, 2, requires_grad=True)),
+             "optimizer": {"state": {0: {"step": torch.tensor(3.0), "exp_avg": torch.zeros(3)}}, "param_groups": [{"lr": 1e-3, "params": [0]}]},
+             "rng_numpy": np.random.get_state(), "rng_python": random.getstate(), "history": [("x", 1), ["y", shared]], "step": 3}
+    mine, theirs = W.snapshot_to_cpu(state), ref["ops.checkpoint_writer"].snapshot_to_cpu(state)
+    for snapshot in (mine, theirs):
+        assert snapshot["model"]["a"] is snapshot["model"]["b"] is snapshot["history"][1][1]         # one tensor stays one tensor
+        assert snapshot["model"]["a"] is not shared and isinstance(snapshot["model"], OrderedDict)
+        assert not snapshot["model"]["c"].requires_grad and snapshot["step"] == 3
+    shared.add_(100)
+    state["optimizer"]["state"][0]["exp_avg"].fill_(9)
+    state["optimizer"]["param_groups"][0]["lr"] = 5.0
+    for snapshot in (mine, theirs):
+        assert snapshot["model"]["a"].tolist() == [0, 1, 2, 3, 4, 5] and snapshot["optimizer"]["state"][0]["exp_avg"].sum() == 0
+        assert snapshot["optimizer"]["param_groups"][0]["lr"] == 1e-3
+    W.atomic_torch_save(tmp_path / "mine.pt", mine)
+    ref["ops.checkpoint_writer"].atomic_torch_save(tmp_path / "theirs.pt", theirs)
+    a, b = (torch.load(tmp_path / name, weights_only=False) for name in ("mine.pt", "theirs.pt"))
+    assert list(a) == list(b) and torch.equal(a["model"]["a"], b["model"]["a"]) and a["history"][0] == b["history"][0]
+    assert sorted(p.name for p in tmp_path.iterdir()) == ["mine.pt", "theirs.pt"]                      # no staging file left

@@ -178,7 +178,7 @@ def analyze(raw: bytes, *, bin_width_b: float = 0.25, first_bin_b: float = 1.0, 
             curve = family.fit(t[window], loss[window])
             fits.append({"start_B": start, "end_B": end, "bins": int(window.sum()), "parameters": curve.parameters,
                          f"cross_{target:g}_tokens_B": curve.crossing(target),
-                         "endpoint_losses": {f"{b:g}B": float(curve.predict(b)) for b in budgets_b}})
+                         "endpoint_losses": {f"{b:.12g}B": float(curve.predict(b)) for b in budgets_b}})
     holdouts = []
     for stop in holdout_ends:
         known, unseen = (t >= 2) & (t < stop), (t >= stop) & (t < stop + 1)
@@ -192,7 +192,9 @@ def analyze(raw: bytes, *, bin_width_b: float = 0.25, first_bin_b: float = 1.0, 
                              "predicted_mean_loss": float(guess.mean()), "mean_bias": float((guess - loss[unseen]).mean()),
                              "rmse": float(np.sqrt(np.mean((guess - loss[unseen]) ** 2)))})
     return {"method": METHOD, "caveats": CAVEATS, "source_sha256": hashlib.sha256(raw).hexdigest(),
-            "source_rows": len(rows), "latest_validation": rows[-1], "complete_bins_end_B": end, "bins": bins,
+            "source_rows": len(rows), "latest_validation": rows[-1], "complete_bins_end_B": end,
+            "observed_validation": [{"tokens_B": r["tokens"] / 1e9, "loss": r["loss"]} for r in rows if r["tokens"] >= 1e9],
+            "bins": bins,
             "fits": fits, "holdouts": holdouts}
 
 

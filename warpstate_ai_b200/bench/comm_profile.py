@@ -43,13 +43,12 @@ def is_communication(name: str) -> bool:
 def sweep(compute, communication) -> dict:
     """One pass over all interval boundaries; overlapping streams are counted once per class."""
     points = []
-    for begin, end in compute:
-        points += [(begin, 0, 1), (end, 0, -1)]
-    for begin, end in communication:
-        points += [(begin, 1, 1), (end, 1, -1)]
-    for value, _, _ in points:
-        if not math.isfinite(value):
-            raise ValueError("activity intervals must have finite endpoints")
+    for kind, intervals in enumerate((compute, communication)):
+        for begin, end in intervals:
+            if not (math.isfinite(begin) and math.isfinite(end)):
+                raise ValueError("activity intervals must have finite endpoints")
+            if end > begin:                       # an activity of no duration occupies nothing and bounds nothing
+                points += [(begin, kind, 1), (end, kind, -1)]
     points.sort(key=lambda p: (p[0], -p[2]))  # at equal time open before close: touching intervals merge
     live = [0, 0]
     totals = {"compute_only": 0.0, "communication_only": 0.0, "both": 0.0, "idle": 0.0}
@@ -134,7 +133,7 @@ def summarize_trace(trace: dict) -> dict:
     for device, d in sorted(devices.items()):
         t = sweep(d["compute"], d["communication"])
         comm = t["communication_only"] + t["both"]
-        everything = d["compute"] + d["communication"]
+        everything = [(b, e) for b, e in d["compute"] + d["communication"] if e > b]      # an empty activity spans nothing
         span = (max(e for _, e in everything) - min(b for b, _ in everything)) if everything else 0.0
         rows.append({"device": device, "activity_span_us": span,
                      "active_union_us": t["compute_only"] + t["communication_only"] + t["both"],
