@@ -1,0 +1,163 @@
+"""Files written by one implementation are read by the other: plan documents, the DPO reference-score cache and sealed
+chat exports, with the reference imported as a library from ``baseline/_ref`` (skipped where it is not installed)."""
+import importlib
+import json
+from dataclasses import asdict
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from test_reference_parity import REF, reference_import_path
+
+TOK = Path(__file__).resolve().parents[1] / "tokenizer.model"
+
+
+@pytest.fixture(scope="module")
+def ref():
+    if not (REF / "posttrain.py").exists():
+        pytest.skip("reference not installed under baseline/_ref")
+    with reference_import_path():
+        return {name: importlib.import_module(name) for name in ("posttrain", "dpo", "chat")}
+
+
+# ------------------------------------------------------------------------------------------- plan documents
+TRAINING_SECTIONS = [
+    {}, {"lr": 2e-5, "min_lr": 2e-6, "max_steps": 7}, {"lr": 1, "warmup_ratio": 0}, {"sequence_length": 4096, "micro_batch": 1, "grad_accum": 64},
+    {"compile_core": False, "bf16_residuals": False, "gradient_checkpointing": True, "deterministic": False},
+    # refused by both
+    {"lr": 0}, {"lr": -1e-5}, {"min_lr": 1e-3}, {"lr": "1e-5"}, {"lr": float("inf")}, {"clip_grad_norm": 0}, {"weight_decay": -0.1},
+    {"warmup_ratio": 1}, {"warmup_ratio": True}, {"warmup_ratio": -0.1}, {"micro_batch": 0}, {"micro_batch": 2.0}, {"epochs": True},
+    {"max_steps": 0}, {"max_steps": 1.5}, {"seed": -1}, {"seed": 1.0}, {"compile_core": 1}, {"deterministic": "yes"},
+    {"unknown_key": 1}, {"workers": 0}, {"eval_every": None},
+]
+
+
+def verdict(load, document, path):
+    path.write_text(json.dumps(document))
+    try:
+        return load(path)[1]
+    except ValueError:
+        return "refused"
+
+
+@pytest.mark.parametrize("training", TRAINING_SECTIONS, ids=lambda t: ",".join(f"{k}={v}" for k, v in t.items()) or "defaults")
+def test_plans_mean_the_same_to_both(ref, tmp_path, training):
+    from warpstate_ai_b200.train.plans import DPO_PLAN, SFT_PLAN
+    sft = {"format": "warpstate-posttrain-plan-v1", "stage": "sft", "training": training}
+    assert verdict(SFT_PLAN.read, sft, tmp_path / "a.json") == verdict(ref["posttrain"].load_plan, sft, tmp_path / "b.json")
+    dpo = {"format": "warpstate-dpo-plan-v1", "stage": "dpo", "training": training}
+    mine, theirs = verdict(DPO_PLAN.read, dpo, tmp_path / "c.json"), verdict(ref["dpo"].load_plan, dpo, tmp_path / "d.json")
+    if theirs == "refused":
+        assert mine == "refused"
+    else:
+        assert {k: mine[k] for k in theirs} == theirs and set(mine) - set(theirs) == {"reference_mode"}
+
+
+def test_stage_specific_keys_and_wrong_documents(ref, tmp_path):
+    from warpstate_ai_b200.train.plans import DPO_PLAN, SFT_PLAN
+    cases = [({"loss_mode": "full"}, "sft"), ({"loss_mode": "fused"}, "sft"), ({"beta": 0.1, "objective": "summed-dpo"}, "dpo"),
+             ({"beta": 0}, "dpo"), ({"objective": "ipo"}, "dpo"), ({"head_chunk_size": 0}, "dpo"), ({"beta": 0.1}, "sft"), ({"loss_mode": "full"}, "dpo")]
+    for training, stage in cases:
+        schema, load, plan_format = ((SFT_PLAN, ref["posttrain"].load_plan, "warpstate-posttrain-plan-v1") if stage == "sft"
+                                     else (DPO_PLAN, ref["dpo"].load_plan, "warpstate-dpo-plan-v1"))
+        document = {"format": plan_format, "stage": stage, "training": training}
+        mine, theirs = verdict(schema.read, document, tmp_path / "m.json"), verdict(load, document, tmp_path / "t.json")
+        assert (mine == "refused") == (theirs == "refused"), (training, stage)
+        if theirs != "refused":
+            assert {k: mine[k] for k in theirs} == theirs
+    for document in ({}, {"format": "warpstate-dpo-plan-v1", "stage": "sft"}, {"format": "warpstate-posttrain-plan-v1", "stage": "dpo"}):
+        assert verdict(SFT_PLAN.read, document, tmp_path / "m.json") == verdict(ref["posttrain"].load_plan, document, tmp_path / "t.json") == "refused"
+        assert verdict(DPO_PLAN.read, document, tmp_path / "m.json") == verdict(ref["dpo"].load_plan, document, tmp_path / "t.json") == "refused"
+
+
+# ------------------------------------------------------------------------------------------- DPO reference cache
+def test_a_score_cache_written_here_is_accepted_by_the_reference(ref, tmp_path):
+    from warpstate_ai_b200.train.reference_cache import ReferenceScoreCache
+    identity = {"format": "warpstate-dpo-reference-v1", "weights_sha256": "aa", "data_sha256": "bb", "settings": {"micro_batch": 2},
+                "dropout": 0.0, "world_size": 2}
+    train = [{"id": i} for i in range(9)]
+    val = [{"id": 50 + i} for i in range(4)]
+    score = lambda rows: np.array([[-1.5 * r["id"] - 0.25, -0.5 * r["id"] - 3.0] for r in rows], dtype=np.float64).reshape(-1, 2)
+    caches = [ReferenceScoreCache(tmp_path / "cache", identity, (9, 4)) for _ in range(2)]
+    for rank, cache in enumerate(caches):
+        cache.claim(rank)
+        assert cache.score((train, val), score, 2, rank, 2, lambda: False)
+    caches[0].merge(2)
+    mine = caches[0].verify()
+    theirs = ref["dpo"].validate_cache(tmp_path / "cache", identity, (9, 4))
+    assert np.array_equal(mine[0], theirs[0]) and np.array_equal(mine[1], theirs[1]) and mine[2] == theirs[2]
+    assert np.array_equal(theirs[0], score(train)) and theirs[1].dtype == np.float64
+    with pytest.raises(ValueError):
+        ref["dpo"].validate_cache(tmp_path / "cache", dict(identity, weights_sha256="cc"), (9, 4))
+    with pytest.raises(ValueError):
+        ref["dpo"].validate_cache(tmp_path / "cache", identity, (9, 5))
+    table = np.load(tmp_path / "cache" / "val.npy")
+    table[0, 0] += 1.0
+    np.save(tmp_path / "cache" / "val.npy", table)
+    for check in (caches[0].verify, lambda: ref["dpo"].validate_cache(tmp_path / "cache", identity, (9, 4))):
+        with pytest.raises(ValueError):
+            check()
+
+
+# ------------------------------------------------------------------------------------------- chat exports
+def training_checkpoint(path):
+    from warpstate_ai_b200.ckpt.formats import SERVER_FORMAT
+    from warpstate_ai_b200.config import WarpStateConfig
+    from warpstate_ai_b200.models.warpstate import WarpStateLM
+    from warpstate_ai_b200.utils.io import digest
+    torch.manual_seed(5)
+    cfg = WarpStateConfig(vocab_size=32768, d_model=16, n_heads=2, n_cores=1, logical_depth=2, ffn_hidden=24, chunk_size=4,
+                          gradient_checkpointing=False, parallel_memory=True)
+    model = WarpStateLM(cfg)
+    with torch.no_grad():
+        model.depth_scale.normal_(0, 0.1)
+        model.depth_bias.normal_(0, 0.1)
+    path.parent.mkdir(parents=True, exist_ok=True)
+    torch.save({"format": SERVER_FORMAT, "signature": {"data": {"signature": {"tokenizer_sha256": digest(TOK)}}}, "config": asdict(cfg),
+                "model": model.state_dict(), "optimizer": {"state": {}}, "step": 7, "tokens_seen": 112, "val_loss": 9.5}, path)
+    return model
+
+
+def stepped_logits(model, ids):
+    caches = model.init_generation_cache(1, torch.device("cpu"), torch.float32)
+    with torch.no_grad():
+        return torch.cat([model.step(ids[:, i:i + 1], caches) for i in range(ids.shape[1])], dim=1)
+
+
+def test_exports_of_either_implementation_load_in_the_other(ref, tmp_path):
+    from warpstate_ai_b200.serve.snapshots import SnapshotStore
+    source = tmp_path / "run" / "latest.pt"
+    trained = training_checkpoint(source)
+    ids = torch.randint(0, 32768, (1, 10))
+    wanted = stepped_logits(trained.eval(), ids)
+    store = SnapshotStore(tmp_path / "ours", TOK)
+    exported_here = store.export(source)
+    exported_there = ref["chat"].capture_latest(source, TOK, tmp_path / "theirs")
+    # same layout on disk, same sealed fields
+    seal_here, seal_there = (json.loads(p.with_name("snapshot.json").read_text()) for p in (exported_here, exported_there))
+    assert set(seal_here) == set(seal_there)
+    for key in ("format", "inference_only", "config", "step", "tokens_seen", "val_loss", "tokenizer_sha256", "source"):
+        assert seal_here[key] == seal_there[key], key
+    payload_here, payload_there = (torch.load(p, weights_only=False) for p in (exported_here, exported_there))
+    assert set(payload_here) == set(payload_there) and "optimizer" not in payload_here
+    # each loader accepts the other's export and the model computes the same logits
+    model_a, _, meta_a = ref["chat"].load_model(exported_here, TOK)
+    model_b, _, meta_b = store.load(exported_there)
+    assert meta_a["step"] == meta_b["step"] == 7
+    assert torch.allclose(stepped_logits(model_a, ids), wanted, rtol=1e-5, atol=1e-6)
+    assert torch.allclose(stepped_logits(model_b, ids), wanted, rtol=1e-5, atol=1e-6)
+    assert ref["chat"].resolve_snapshot(exported_here, TOK, tmp_path / "unused") == exported_here
+    assert store.resolve(exported_there) == exported_there and not (tmp_path / "unused").exists()
+    # and both refuse the other's export once it is tampered with
+    exported_here.chmod(0o644)
+    with open(exported_here, "ab") as stream:
+        stream.write(b"x")
+    with pytest.raises(ValueError):
+        ref["chat"].load_model(exported_here, TOK)
+    exported_there.chmod(0o644)
+    with open(exported_there, "ab") as stream:
+        stream.write(b"x")
+    with pytest.raises(ValueError):
+        store.load(exported_there)
