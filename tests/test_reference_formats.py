@@ -161,3 +161,50 @@ def test_exports_of_either_implementation_load_in_the_other(ref, tmp_path):
         stream.write(b"x")
     with pytest.raises(ValueError):
         store.load(exported_there)
+
+
+# ------------------------------------------------------------------------------------------- training checkpoints
+def test_a_checkpoint_of_this_trainer_is_a_reference_checkpoint(ref, tmp_path):
+    """`run_40b.py --device cpu` here, then the reference's own readers: its chat export, its model, its optimizer."""
+    from warpstate_ai_b200.data import prepare as P
+    from warpstate_ai_b200.train import pretrain as T
+    cfg_path = tmp_path / "cfg.json"
+    cfg_path.write_text(json.dumps(dict(vocab_size=32768, d_model=16, n_heads=2, n_cores=2, logical_depth=4, ffn_hidden=24, chunk_size=4,
+                                        gradient_checkpointing=False, parallel_memory=True)))
+    work = tmp_path / "work"
+    P.write_synthetic_corpus(work, TOK, 73, 64, 32768, seed=1)
+    T.STOP = False
+    T.main(["--from-scratch", "--work-dir", str(work), "--config", str(cfg_path), "--tokenizer", str(TOK), "--stage", "train",
+            "--device", "cpu", "--test-small-gpu", "--train-tokens", "73", "--val-tokens", "64", "--seq-len", "8", "--micro-batch", "2",
+            "--grad-accum", "2", "--warmup-steps", "1", "--max-steps", "2", "--eval-batches", "1", "--no-activation-checkpointing",
+            "--dataset", "synthetic/uniform", "--dataset-config", "none", "--revision", "0"])
+    latest = work / "run" / "latest.pt"
+    checkpoint = torch.load(latest, weights_only=False)
+    assert checkpoint["format"] == "warpstate-server-v1" and checkpoint["step"] == 2
+    with reference_import_path():
+        run_40b = importlib.import_module("run_40b")
+        warpstate = importlib.import_module("warpstate")
+    # the reference's resume check reads the stored signature (its keys are all there; ours are extra settings)
+    assert run_40b.check_resume_signature(checkpoint["signature"], checkpoint["signature"]) is False
+    for key in ("seq_len", "micro_batch", "grad_accum", "train_tokens", "lr", "min_lr", "warmup_steps", "weight_decay", "seed",
+                "activation_checkpointing", "loss_chunk_size", "compile", "world_size", "loss_mode", "ddp_bucket_cap_mb"):
+        assert key in checkpoint["signature"]["settings"], key
+    # model and optimizer state load into the reference's classes, parameter for parameter
+    model = warpstate.WarpStateLM(warpstate.WarpStateConfig(**checkpoint["config"]))
+    model.load_state_dict(checkpoint["model"], strict=True)
+    optimizer = torch.optim.AdamW(model.parameters(), lr=1.0, betas=(0.5, 0.5))
+    optimizer.load_state_dict(checkpoint["optimizer"])
+    group = optimizer.param_groups[0]
+    assert group["betas"] == (0.9, 0.95) and group["eps"] == 1e-8 and len(group["params"]) == len(list(model.parameters()))
+    for parameter in model.parameters():
+        state = optimizer.state[parameter]
+        assert state["exp_avg"].shape == parameter.shape == state["exp_avg_sq"].shape and float(state["step"]) == 2.0
+    assert any(float(optimizer.state[p]["exp_avg"].abs().sum()) > 0 for p in model.parameters())
+    for key in ("rng_by_rank", "rng_torch", "rng_cuda", "rng_numpy", "rng_python", "tokens_seen", "val_loss", "origin", "execution_history"):
+        assert key in checkpoint, key
+    # and its chat probe exports and loads it
+    exported = ref["chat"].capture_latest(latest, TOK, tmp_path / "snaps")
+    probe, _, metadata = ref["chat"].load_model(exported, TOK)
+    assert metadata["step"] == 2 and metadata["tokens_seen"] == checkpoint["tokens_seen"]
+    ids = torch.randint(0, 32768, (1, 6))
+    assert torch.allclose(stepped_logits(probe, ids), stepped_logits(model.eval(), ids), rtol=1e-5, atol=1e-6)
