@@ -121,3 +121,33 @@ def test_incomplete_or_capped_runs_are_not_archived(finished_run):
         AD.validate_state(ckpt, reports[0], dict(reports[1], val_loss=0.0), reports[2], data, ref, p)
     with pytest.raises(ValueError, match="fixed-reference identity"):
         AD.validate_state(ckpt, *reports, data, dict(ref, identity=dict(ref["identity"], world_size=2)), p)
+
+
+def test_guardian_records_travel_with_the_archive_and_the_layout_is_the_reference_one(finished_run):
+    root, tok, plan = finished_run
+    without = root / "archives/final"
+    if not without.exists():
+        build(root, tok, plan)
+    for name in AD.GUARDIAN_RECORDS:                       # this run had no guardian: the archive says so
+        assert json.loads((without / name).read_text()) == AD.NO_GUARDIAN
+    records = {"control/execution.json": {"format": "execution", "processes": 1}, "control/handoff.json": {"phase": "complete"},
+               "preflight/report.json": {"passed": True, "ranks": 1}}
+    for leaf, content in records.items():
+        path = root / "dpo" / leaf
+        path.parent.mkdir(parents=True, exist_ok=True)
+        path.write_text(json.dumps(content))
+    build(root, tok, plan, name="guarded")
+    guarded = root / "archives/guarded"
+    for name, leaf in AD.GUARDIAN_RECORDS.items():
+        assert json.loads((guarded / name).read_text()) == records[leaf]
+        assert (guarded / name).stat().st_ino != (root / "dpo" / leaf).stat().st_ino      # an independent copy
+    AD.verify_dpo_archive(guarded)
+    listing = [line.split("  ", 1)[1] for line in (guarded / "SHA256SUMS").read_text().splitlines()]
+    assert listing == list(AD.FILES)
+    reference_list = ROOT / "baseline" / "_ref" / "ops" / "archive_dpo.py"
+    if reference_list.exists():                            # the file list of the reference's archive, read as text
+        import ast
+        tree = ast.parse(reference_list.read_text())
+        files = next(ast.literal_eval(node.value) for node in tree.body
+                     if isinstance(node, ast.Assign) and getattr(node.targets[0], "id", "") == "FILES")
+        assert tuple(files) == AD.FILES

@@ -213,6 +213,27 @@ def test_handoff_state_machine_with_fakes(ws, monkeypatch):
     sealed = torch.load(ws / "archives/sft-final/model.pt", weights_only=False)
     assert sealed["stage"] == "sft" and all(torch.equal(sealed["model"][k], v) for k, v in finished["model"].items())
     assert torch.load(ws / "dpo/run/latest.pt", weights_only=False)["format"] == "warpstate-dpo-v1"
+    # the archive keeps the whole finished SFT run; the DPO stage starts from a three-file copy of its own
+    archive = ws / "archives/sft-final"
+    assert sorted(p.name for p in archive.iterdir()) == sorted((*A.SFT_ARCHIVE_FILES, "SHA256SUMS"))
+    assert digest(archive / "checkpoint.pt") == digest(ws / "sft/run/latest.pt")
+    assert (archive / "checkpoint.pt").stat().st_ino != (ws / "sft/run/latest.pt").stat().st_ino
+    kept = torch.load(archive / "checkpoint.pt", weights_only=False)
+    assert kept["optimizer"]["state"] and kept["rng_by_rank"] and kept["format"] == "warpstate-posttrain-v1"
+    assert json.loads((archive / "sft-handoff.json").read_text()) == json.loads((ws / "sft/control/handoff.json").read_text())
+    assert json.loads((archive / "sft-execution.json").read_text())["plan"]["stage"] == "sft"
+    provenance = json.loads((archive / "PROVENANCE.json").read_text())
+    assert provenance["format"] == "warpstate-sft-archive-v1" and provenance["source_checkpoint_sha256"] == digest(ws / "sft/run/latest.pt")
+    assert provenance["model_sha256"] == digest(archive / "model.pt") and provenance["sft_step"] == finished["step"]
+    for name in ("evaluation.json", "completion.json", "settings.json", "metrics.jsonl"):
+        assert (archive / name).read_bytes() == (ws / "sft/run" / name).read_bytes()
+    assert all(not (p.stat().st_mode & 0o222) for p in archive.iterdir())
+    start = ws / "dpo/initialization"
+    assert sorted(p.name for p in start.iterdir()) == sorted((*A.INIT_FILES, "SHA256SUMS"))
+    assert digest(start / "model.pt") == digest(archive / "model.pt") and (start / "model.pt").stat().st_ino != (archive / "model.pt").stat().st_ino
+    A.verify_archive(archive, H.DpoStage().boundary(dpo_plan), files=A.SFT_ARCHIVE_FILES)
+    with pytest.raises(ValueError):
+        A.verify_archive(archive, H.DpoStage().boundary(dpo_plan))              # not a four-file model archive
     # a parent that stopped one step short is refused by the rule table
     with pytest.raises(ValueError, match="exact planned run"):
         H.DpoStage().validate_parent(dict(finished, step=finished["step"] - 1), dpo_plan, digest(tok))

@@ -11,8 +11,12 @@ reference's hand-off scripts establish them, reference ops/posttrain_handoff.py:
 * what a later stage trains from is a *physical* copy (never a hard link), so no training run can alter
   the archive.
 
-`SealedDirectory` is one such directory; the module functions are its verbs under the names the
-hand-off code uses.
+The archive of a finished SFT run holds more (`SFT_ARCHIVE_FILES`, reference ops/dpo_handoff.py:34-37): the
+byte-identical final checkpoint with its optimizer and RNG state, the run's reports and the guardian's records; the
+DPO stage copies only `INIT_FILES` out of it.
+
+`SealedDirectory` is one such directory with its list of files; the module functions are its verbs under the names
+the hand-off code uses.
 """
 from __future__ import annotations
 
@@ -29,6 +33,13 @@ import torch
 from ..utils.io import digest, fsync_dir, utc_timestamp
 
 ARCHIVE_FILES = ("model.pt", "snapshot.json", "tokenizer.model", "ARCHIVE.md")
+# A finished SFT run is archived whole (reference ops/dpo_handoff.py:34-37): the byte-identical checkpoint with its
+# optimizer and RNG state, the model-only export, the run's reports and what the guardian recorded about it.
+SFT_ARCHIVE_FILES = ("checkpoint.pt", "model.pt", "snapshot.json", "tokenizer.model", "settings.json", "evaluation.json",
+                     "completion.json", "metrics.jsonl", "sft-execution.json", "sft-handoff.json", "PROVENANCE.json",
+                     "ARCHIVE.md")
+# What a later stage needs of an archive to start from it.
+INIT_FILES = ("model.pt", "snapshot.json", "tokenizer.model")
 SUMS = "SHA256SUMS"
 
 
@@ -132,20 +143,25 @@ class SealedDirectory:
         return metadata
 
     # ------------------------------------------------------------------ copies
-    def copy_to(self, destination, boundary: dict, model_hash: str) -> Path:
-        """A verified physical copy at ``destination`` (created if absent); returns the copy's ``model.pt``."""
+    def copy_to(self, destination, boundary: dict, model_hash: str, only=None) -> Path:
+        """A verified physical copy at ``destination`` (created if absent); returns the copy's ``model.pt``.
+        ``only`` names the files to take (a sealed directory of its own, with its own checksum list); by default the
+        whole archive is copied, checksum list included."""
         destination = Path(destination)
         self.verify(boundary, model_hash)
-        names = (*self.files, SUMS)
+        kept = self.files if only is None else tuple(only)
+        names = (*kept, SUMS) if only is None else kept
         if not destination.exists() and not destination.is_symlink():
             destination.parent.mkdir(parents=True, exist_ok=True)
-            staging = SealedDirectory(tempfile.mkdtemp(prefix=".initialization-", dir=destination.parent), self.files)
+            staging = SealedDirectory(tempfile.mkdtemp(prefix=".initialization-", dir=destination.parent), kept)
             for name in names:
                 copy_regular(self.path(name), staging.path(name))
+            if only is not None:
+                staging.seal()
             staging.verify(boundary, model_hash)
             fsync_dir(staging.folder)
             publish_directory(staging.folder, destination)
-        copy = SealedDirectory(destination, self.files)
+        copy = SealedDirectory(destination, kept)
         copy.verify(boundary, model_hash)
         for name in names:
             mine, theirs = self.path(name).stat(), copy.path(name).stat()
@@ -168,8 +184,8 @@ def verify_archive(folder, boundary: dict, expected_model_hash: str | None = Non
     return SealedDirectory(folder, files).verify(boundary, expected_model_hash, sealed)
 
 
-def independent_copy(archive, destination, boundary: dict, model_hash: str) -> Path:
-    return SealedDirectory(archive).copy_to(destination, boundary, model_hash)
+def independent_copy(archive, destination, boundary: dict, model_hash: str, *, files=ARCHIVE_FILES, only=None) -> Path:
+    return SealedDirectory(archive, files).copy_to(destination, boundary, model_hash, only)
 
 
 def tensors_equal(original: dict, exported: dict) -> None:

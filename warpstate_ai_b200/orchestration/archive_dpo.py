@@ -34,13 +34,19 @@ from ..utils.rules import Rule, enforce, finite, fp32_tensors, matches
 from . import archive as A
 
 REPORTS = ("settings.json", "evaluation.json", "completion.json", "metrics.jsonl")
-# archive file name <- where it comes from: (root, leaf) with root one of run / data / cache / tokenizer / plan
+# What the hand-off guardian recorded about this run (`orchestration/handoff.py`), under the run's work directory.
+GUARDIAN_RECORDS = {"dpo-execution.json": "control/execution.json", "dpo-handoff.json": "control/handoff.json",
+                    "gpu-preflight.json": "preflight/report.json"}
+# archive file name <- where it comes from: (root, leaf) with root one of run / work / data / cache / tokenizer / plan
 COPIED = {"checkpoint.pt": ("run", "latest.pt"), "tokenizer.model": ("tokenizer", ""), "plan.json": ("plan", ""),
-          **{name: ("run", name) for name in REPORTS}, "data-manifest.json": ("data", "manifest.json"),
-          "reference-manifest.json": ("cache", "manifest.json"), "reference-train.npy": ("cache", "train.npy"),
-          "reference-val.npy": ("cache", "val.npy")}
-FILES = ("checkpoint.pt", "model.pt", "snapshot.json", "tokenizer.model", "plan.json", *REPORTS, "data-manifest.json",
-         "reference-manifest.json", "reference-train.npy", "reference-val.npy", "PROVENANCE.json", "ARCHIVE.md")
+          **{name: ("run", name) for name in REPORTS}, **{name: ("work", leaf) for name, leaf in GUARDIAN_RECORDS.items()},
+          "data-manifest.json": ("data", "manifest.json"), "reference-manifest.json": ("cache", "manifest.json"),
+          "reference-train.npy": ("cache", "train.npy"), "reference-val.npy": ("cache", "val.npy")}
+# the reference's archive layout (reference ops/archive_dpo.py:35-39)
+FILES = ("checkpoint.pt", "model.pt", "snapshot.json", "tokenizer.model", "plan.json", *REPORTS, *GUARDIAN_RECORDS,
+         "data-manifest.json", "reference-manifest.json", "reference-train.npy", "reference-val.npy", "PROVENANCE.json",
+         "ARCHIVE.md")
+NO_GUARDIAN = {"recorded": False, "reason": "this run was not started by a hand-off guardian; nothing was recorded here"}
 CHAT_FILES = ("model.pt", "snapshot.json", "tokenizer.model", "ARCHIVE.md")
 SCORES = ("val_loss", "reward_margin", "reward_accuracy", "chosen_nll")
 IDENTITIES = ("base_sha256", "data_sha256", "tokenizer_sha256", "reference_sha256")
@@ -190,8 +196,8 @@ Do not modify; copy to continue training or to chat.
 def archive_dpo(run_dir, data_dir, cache_dir, tokenizer, plan_path, destination, revision: str = "") -> dict:
     """Build and publish the sealed archive of a finished DPO run.  The caller holds the locks that
     exclude training; nothing under ``run_dir`` is modified.  Idempotent."""
-    roots = {"run": Path(run_dir), "data": Path(data_dir), "cache": Path(cache_dir), "tokenizer": Path(tokenizer),
-             "plan": Path(plan_path)}
+    roots = {"run": Path(run_dir), "work": Path(run_dir).parent, "data": Path(data_dir), "cache": Path(cache_dir),
+             "tokenizer": Path(tokenizer), "plan": Path(plan_path)}
     destination, source = Path(destination), Path(run_dir) / "latest.pt"
     if source.is_symlink():
         raise ValueError("The checkpoint must not be a symlink")
@@ -211,7 +217,11 @@ def archive_dpo(run_dir, data_dir, cache_dir, tokenizer, plan_path, destination,
     staging = Path(tempfile.mkdtemp(prefix=".dpo-final-", dir=destination.parent))
     export_chat_snapshot(checkpoint, staging, roots["tokenizer"], {"path": str(source), "sha256": whole}, stage="dpo")
     for name, (root, leaf) in COPIED.items():
-        A.copy_regular(roots[root] / leaf if leaf else roots[root], staging / name)
+        origin = roots[root] / leaf if leaf else roots[root]
+        if name in GUARDIAN_RECORDS and not origin.exists():
+            A.write_new(staging / name, json.dumps(NO_GUARDIAN, indent=2) + "\n")     # same layout, and it says so
+        else:
+            A.copy_regular(origin, staging / name)
     provenance = {"created_utc": utc_timestamp(), "revision": revision, "source": str(source), "source_sha256": whole,
                   "torch_version": torch.__version__, "python": sys.version.split()[0], "signature": checkpoint["signature"]}
     A.write_new(staging / "PROVENANCE.json", json.dumps(provenance, indent=2, default=str) + "\n")

@@ -113,6 +113,8 @@ class Stage:
     data_files: tuple = ()
     path_keys: tuple = ()
     trainer_extras: tuple = ()
+    archive_files: tuple = A.ARCHIVE_FILES      # what the sealed archive of the parent holds
+    init_files = None                           # what the new stage copies from it (None: all of it)
 
     def check_paths(self, plan, paths) -> None:
         raise NotImplementedError
@@ -229,6 +231,7 @@ class DpoStage(Stage):
     data_files = ("dpo_train.jsonl", "dpo_val.jsonl")
     path_keys = ("base_work_dir", "sft_work_dir", "supervisor_socket", "archive_dir", "work_dir", "data_dir", "tokenizer")
     trainer_extras = (("--reference-cache-dir", "reference-cache"),)
+    archive_files, init_files = A.SFT_ARCHIVE_FILES, A.INIT_FILES
 
     def check_paths(self, plan, paths):
         work = paths["work_dir"]
@@ -249,32 +252,60 @@ class DpoStage(Stage):
                 *fp32_weights(checkpoint.get("model") or {}, "untouched SFT")]
 
     def make_archive(self, paths, plan, revision):
-        """Sealed SFT archive: tensor-exact ``stage='sft'`` model export + tokenizer + a note; the complete SFT
-        checkpoint is referenced by hash (it stays in the SFT run).  An existing archive is verified instead."""
+        """Sealed archive of the whole finished SFT run: the byte-identical checkpoint (FP32 model, Adam moments, per-rank
+        RNG, cursors, signatures), a tensor-exact ``stage='sft'`` model export, the tokenizer, the run's reports, what the
+        SFT guardian recorded, provenance and a note.  An existing archive is verified instead."""
         from ..ckpt.formats import export_chat_snapshot
         destination, boundary, source = paths["archive_dir"], self.boundary(plan), self.parent_checkpoint(paths)
+        run, sft_work = source.parent, source.parent.parent
+        seen_first = source.stat()
         checkpoint = load_checkpoint(source)
         self.validate_parent(checkpoint, plan, digest(paths["tokenizer"]))
+        whole = digest(source)
 
-        def same_tensors(folder):
+        def intact(folder):
             A.tensors_equal(checkpoint["model"], load_checkpoint(folder / "model.pt")["model"])
+            if digest(folder / "checkpoint.pt") != whole:
+                raise ValueError("the archived SFT checkpoint is not the run's final checkpoint")
 
         if destination.exists():
-            metadata = A.verify_archive(destination, boundary)
-            same_tensors(destination)
+            metadata = A.verify_archive(destination, boundary, files=self.archive_files)
+            intact(destination)
             return metadata
         destination.parent.mkdir(parents=True, exist_ok=True)
         staging = Path(tempfile.mkdtemp(prefix=".sft-final-", dir=destination.parent))
-        whole = {"path": str(source), "sha256": digest(source)}
-        export_chat_snapshot(checkpoint, staging, paths["tokenizer"], whole, stage="sft")
-        same_tensors(staging)
+        A.copy_regular(source, staging / "checkpoint.pt")
+        export_chat_snapshot(checkpoint, staging, paths["tokenizer"], {"path": str(source), "sha256": whole}, stage="sft")
         A.copy_regular(paths["tokenizer"], staging / "tokenizer.model")
+        for name in ("settings.json", "evaluation.json", "completion.json", "metrics.jsonl"):
+            A.copy_regular(run / name, staging / name)
+        for name, leaf in (("sft-execution.json", "control/execution.json"), ("sft-handoff.json", "control/handoff.json")):
+            if (sft_work / leaf).is_file():
+                A.copy_regular(sft_work / leaf, staging / name)
+            else:                                   # an SFT run that no guardian started: same layout, and it says so
+                A.write_new(staging / name, json.dumps({"recorded": False, "reason": "the SFT run was not started by a "
+                                                        "hand-off guardian; nothing was recorded here"}, indent=2) + "\n")
+        model_hash = digest(staging / "model.pt")
+        A.write_new(staging / "PROVENANCE.json", json.dumps({
+            "format": "warpstate-sft-archive-v1", "repository_revision": revision, "source_checkpoint_sha256": whole,
+            "model_sha256": model_hash, "sft_step": checkpoint["step"], "sft_input_tokens": checkpoint["tokens_seen"],
+            "sft_assistant_tokens": checkpoint.get("assistant_tokens_seen"), "base": checkpoint.get("origin"),
+            "data_sha256": checkpoint["signature"].get("data_sha256"), "tokenizer_sha256": boundary["tokenizer_sha256"],
+            "sft_signature": checkpoint["signature"]}, indent=2, default=str) + "\n")
         A.write_new(staging / "ARCHIVE.md", "\n".join([
             f"# KEEP: completed SFT at step {checkpoint['step']}", "", f"Created {utc_timestamp()}.",
-            f"Full SFT checkpoint SHA256: `{whole['sha256']}` ({source}).",
-            f"Final full-holdout loss: {checkpoint['val_loss']}.", f"Repository revision: `{revision}`.", ""]))
-        A.seal(staging)
-        metadata = A.verify_archive(staging, boundary)
+            f"`checkpoint.pt` is the untouched final SFT checkpoint (SHA256 `{whole}`, from {source}): FP32 model, Adam "
+            "moments, per-rank RNG, cursors and signatures.",
+            "`model.pt` is a tensor-exact FP32 model-only export; DPO starts from an independent copy of it with a fresh "
+            "optimizer, and its fixed reference stays at this model.",
+            f"Final full-holdout loss: {checkpoint['val_loss']}.", f"Repository revision: `{revision}`.",
+            "Independent physical files, all read-only. Verify with `sha256sum -c SHA256SUMS`.", ""]))
+        now = source.stat()
+        if (seen_first.st_ino, seen_first.st_size, seen_first.st_mtime_ns) != (now.st_ino, now.st_size, now.st_mtime_ns):
+            raise RuntimeError("the SFT checkpoint changed while it was being archived")
+        A.seal(staging, self.archive_files)
+        metadata = A.verify_archive(staging, boundary, files=self.archive_files)
+        intact(staging)
         A.publish_directory(staging, destination)
         return metadata
 
@@ -434,7 +465,8 @@ class Guardian:
         model_hash = self.stage.make_archive(self.paths, self.plan, self.journal.state["git_revision"])["snapshot_sha256"]
         self.journal.note("copying_initialization", "Creating/verifying the independent initialization",
                           archive_sha256=model_hash)
-        weights = A.independent_copy(self.paths["archive_dir"], self.work / "initialization", self.boundary, model_hash)
+        weights = A.independent_copy(self.paths["archive_dir"], self.work / "initialization", self.boundary, model_hash,
+                                     files=self.stage.archive_files, only=self.stage.init_files)
         while True:
             if STOPPED:
                 return None
@@ -475,7 +507,7 @@ class Guardian:
             self.journal.note("paused", f"{name} stopped before completion; its resume checkpoint is retained")
             return
         completion = self.stage.verify_completion(self.work / "run", self.plan, model_hash)
-        A.verify_archive(self.paths["archive_dir"], self.boundary, model_hash)
+        A.verify_archive(self.paths["archive_dir"], self.boundary, model_hash, files=self.stage.archive_files)
         if digest(weights) != model_hash:
             raise ValueError("Initialization changed during training")
         self.journal.note("complete", f"{name} finished; paused for evaluation.", completion=completion)
