@@ -208,3 +208,58 @@ def test_a_checkpoint_of_this_trainer_is_a_reference_checkpoint(ref, tmp_path):
     assert metadata["step"] == 2 and metadata["tokens_seen"] == checkpoint["tokens_seen"]
     ids = torch.randint(0, 32768, (1, 6))
     assert torch.allclose(stepped_logits(probe, ids), stepped_logits(model.eval(), ids), rtol=1e-5, atol=1e-6)
+
+
+# ------------------------------------------------------------------------------------------- a finished DPO run and its archive
+def test_a_dpo_run_of_this_trainer_satisfies_the_reference_archive_verifier(ref, tmp_path, monkeypatch):
+    """A tiny DPO run to completion with this trainer; the reference's own validator of run records and its verifier of
+    sealed archives accept what was written.  (The one concession: its table of defaults is told about
+    ``reference_mode``, the setting this framework adds to the plan.)"""
+    from warpstate_ai_b200 import WarpStateConfig, WarpStateLM
+    from warpstate_ai_b200.ckpt.formats import export_chat_snapshot
+    from warpstate_ai_b200.data.prepare_posttrain import prepare
+    from warpstate_ai_b200.orchestration import archive_dpo as AD
+    from warpstate_ai_b200.train import dpo as DPO
+    from warpstate_ai_b200.utils.io import digest
+    root = tmp_path / "ws"
+    root.mkdir()
+    monkeypatch.setenv("WARPSTATE_WORKSPACE", str(root))
+    tok = root / "tokenizer.model"
+    tok.write_bytes(TOK.read_bytes())
+    torch.manual_seed(0)
+    cfg = WarpStateConfig(vocab_size=32768, d_model=16, n_heads=2, n_cores=1, logical_depth=2, ffn_hidden=24, chunk_size=8,
+                          gradient_checkpointing=False, parallel_memory=True)
+    sft = {"config": vars(cfg).copy(), "model": WarpStateLM(cfg).state_dict(), "step": 4, "tokens_seen": 400, "assistant_tokens_seen": 90,
+           "val_loss": 9.0, "origin": {"step": 7, "tokens_seen": 700}}
+    exported = export_chat_snapshot(sft, root / "sft-export", tok, {"path": "test"}, stage="sft")
+    assert exported["assistant_tokens_seen"] == 90 and exported["inference_only"] is True and exported["origin"] == sft["origin"]
+    pairs = [{"prompt": [{"role": "user", "content": f"What follows {i}?"}], "chosen": [{"role": "assistant", "content": str(i + 1)}],
+              "rejected": [{"role": "assistant", "content": f"maybe {i + 3} or so"}]} for i in range(14)]
+    prepare(root / "data", tok, 64, dpo_rows=pairs, val_modulus=5)
+    plan = {"format": "warpstate-dpo-plan-v1", "stage": "dpo",
+            "sft": {"step": 4, "tokens_seen": 400, "base_step": 7, "base_tokens_seen": 700, "tokenizer_sha256": digest(tok)},
+            "training": {"sequence_length": 64, "micro_batch": 2, "grad_accum": 2, "lr": 1e-3, "eval_every": 2, "save_every": 2,
+                         "eval_batches": 2, "workers": 1, "beta": 0.5, "head_chunk_size": 16},
+            "handoff": {"processes": 1, "work_dir": "dpo", "data_dir": "data", "tokenizer": "tokenizer.model",
+                        "data_manifest_sha256": digest(root / "data/manifest.json")}}
+    plan_path = root / "plan.json"
+    plan_path.write_text(json.dumps(plan))
+    monkeypatch.setattr(DPO, "STOP", False)
+    DPO.main(["--config", str(plan_path), "--data-dir", str(root / "data"), "--weights", str(root / "sft-export/model.pt"),
+              "--tokenizer", str(tok), "--device", "cpu", "--reference-cache-dir", str(root / "dpo/reference-cache"),
+              "--work-dir", str(root / "dpo/run")])
+    run = root / "dpo/run"
+    with reference_import_path():
+        theirs = importlib.import_module("ops.archive_dpo")
+    monkeypatch.setattr(theirs, "DEFAULTS", dict(theirs.DEFAULTS, reference_mode="cached"))
+    read = lambda path: json.loads(Path(path).read_text())
+    checkpoint = torch.load(run / "latest.pt", weights_only=False)
+    counters = theirs.validate_state(checkpoint, read(run / "evaluation.json"), read(run / "completion.json"), read(run / "settings.json"),
+                                     read(root / "data/manifest.json"), read(root / "dpo/reference-cache/manifest.json"), plan)
+    assert counters["step"] == checkpoint["step"] == 2 and counters["response_tokens_seen"] == checkpoint["response_tokens_seen"]
+    AD.archive_dpo(run, root / "data", root / "dpo/reference-cache", tok, plan_path, root / "archives/final", "rev")
+    metadata, entries = theirs.verify_dpo_archive(root / "archives/final", expected_checkpoint_hash=digest(run / "latest.pt"))
+    mine, my_entries = AD.verify_dpo_archive(root / "archives/final")
+    assert metadata == mine and entries == my_entries and metadata["stage"] == "dpo" and metadata["response_tokens_seen"] == 77
+    with pytest.raises(ValueError):
+        theirs.verify_dpo_archive(root / "archives/final", expected_checkpoint_hash="0" * 64)

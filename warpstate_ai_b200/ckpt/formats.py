@@ -102,25 +102,26 @@ def server_state(*, signature, origin, history, cfg, model, optimizer, step, tok
 # --------------------------------------------------------------------------- chat export
 def export_chat_snapshot(checkpoint: dict, destination: Path, tokenizer: Path, source_info: dict,
                          stage: str | None = None) -> dict:
-    """Model-only inference snapshot + ``snapshot.json`` with its SHA-256 (chat.py:37-102)."""
+    """Model-only inference snapshot + ``snapshot.json``: the metadata stored inside the export, plus the export's
+    SHA-256 and size (reference chat.py:37-102; stage exports ops/dpo_handoff.py:219-232, ops/archive_dpo.py:193-206,
+    which also carry the stage's own token counter and the run's ancestry)."""
     from .writer import atomic_torch_save
     destination = Path(destination)
     destination.mkdir(parents=True, exist_ok=True)
-    payload = {"format": CHAT_FORMAT, "inference_only": True, "config": dict(checkpoint["config"]),
-               "step": checkpoint.get("step"), "tokens_seen": checkpoint.get("tokens_seen"),
-               "val_loss": checkpoint.get("val_loss"), "tokenizer_sha256": digest(tokenizer),
-               "captured_at_utc": utc_timestamp(), "source": source_info, "model": checkpoint["model"]}
+    metadata = {"format": CHAT_FORMAT, "inference_only": True}
     if stage is not None:
-        payload["stage"] = stage
-        payload["origin"] = checkpoint.get("origin")
+        metadata["stage"] = stage
+    metadata.update(config=dict(checkpoint["config"]), step=checkpoint.get("step"), tokens_seen=checkpoint.get("tokens_seen"))
+    for counter in ("assistant_tokens_seen", "response_tokens_seen"):      # SFT resp. DPO checkpoints
+        if stage is not None and counter in checkpoint:
+            metadata[counter] = checkpoint[counter]
+    metadata.update(val_loss=checkpoint.get("val_loss"), tokenizer_sha256=digest(tokenizer))
+    if stage is not None:
+        metadata["origin"] = checkpoint.get("origin")
+    metadata.update(captured_at_utc=utc_timestamp(), source=source_info)
     model_path = destination / "model.pt"
-    atomic_torch_save(model_path, payload)
-    meta = {"format": CHAT_FORMAT, "snapshot_sha256": digest(model_path), "snapshot_bytes": model_path.stat().st_size,
-            "step": payload["step"], "tokens_seen": payload["tokens_seen"], "val_loss": payload["val_loss"],
-            "tokenizer_sha256": payload["tokenizer_sha256"], "captured_at_utc": payload["captured_at_utc"],
-            "source": source_info}
-    if stage is not None:
-        meta["stage"] = stage
+    atomic_torch_save(model_path, {**metadata, "model": checkpoint["model"]})
+    meta = {**metadata, "snapshot_sha256": digest(model_path), "snapshot_bytes": model_path.stat().st_size}
     atomic_json(destination / "snapshot.json", meta)
     return meta
 
