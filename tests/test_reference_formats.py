@@ -263,3 +263,62 @@ def test_a_dpo_run_of_this_trainer_satisfies_the_reference_archive_verifier(ref,
     assert metadata == mine and entries == my_entries and metadata["stage"] == "dpo" and metadata["response_tokens_seen"] == 77
     with pytest.raises(ValueError):
         theirs.verify_dpo_archive(root / "archives/final", expected_checkpoint_hash="0" * 64)
+
+
+def test_an_sft_run_of_this_trainer_satisfies_the_reference_archive_verifier(ref, tmp_path, monkeypatch):
+    """A tiny SFT run to completion, sealed by this framework's SFT -> DPO guardian; the reference's verifier of SFT
+    archives accepts it.  (The one concession: the reference insists on the RNG state of exactly two ranks; this run has
+    one, so its validator is shown the list twice.)"""
+    from warpstate_ai_b200 import WarpStateConfig, WarpStateLM
+    from warpstate_ai_b200.ckpt.formats import export_chat_snapshot
+    from warpstate_ai_b200.data.prepare_posttrain import prepare
+    from warpstate_ai_b200.orchestration import archive as A
+    from warpstate_ai_b200.orchestration import handoff as H
+    from warpstate_ai_b200.train import sft as SFT
+    from warpstate_ai_b200.utils.io import digest
+    root = tmp_path / "ws"
+    root.mkdir()
+    monkeypatch.setenv("WARPSTATE_WORKSPACE", str(root))
+    tok = root / "tokenizer.model"
+    tok.write_bytes(TOK.read_bytes())
+    torch.manual_seed(0)
+    cfg = WarpStateConfig(vocab_size=32768, d_model=16, n_heads=2, n_cores=1, logical_depth=2, ffn_hidden=24, chunk_size=8,
+                          gradient_checkpointing=False, parallel_memory=True)
+    base = {"config": vars(cfg).copy(), "model": WarpStateLM(cfg).state_dict(), "step": 7, "tokens_seen": 700, "val_loss": 9.9}
+    export_chat_snapshot(base, root / "base", tok, {"path": "test"})
+    rows = [{"messages": [{"role": "user", "content": f"What is {i} plus {i + 1}?"}, {"role": "assistant", "content": f"It is {2 * i + 1}."}]}
+            for i in range(12)]
+    prepare(root / "data", tok, 64, sft_rows=rows, val_modulus=5)
+    sft_plan = {"format": "warpstate-posttrain-plan-v1", "stage": "sft", "base": {"step": 7, "tokens_seen": 700, "tokenizer_sha256": digest(tok)},
+                "training": {"sequence_length": 64, "micro_batch": 2, "grad_accum": 2, "lr": 1e-3, "eval_every": 2, "save_every": 2,
+                             "eval_batches": 2, "workers": 1}}
+    (root / "sft-plan.json").write_text(json.dumps(sft_plan))
+    monkeypatch.setattr(SFT, "STOP", False)
+    SFT.main(["--config", str(root / "sft-plan.json"), "--data-dir", str(root / "data"), "--weights", str(root / "base/model.pt"),
+              "--tokenizer", str(tok), "--device", "cpu", "--work-dir", str(root / "sft/run")])
+    latest = root / "sft/run/latest.pt"
+    done = torch.load(latest, weights_only=False)
+    manifest = json.loads((root / "data/manifest.json").read_text())
+    dpo_plan = {"format": "warpstate-dpo-plan-v1", "stage": "dpo",
+                "sft": {"step": done["step"], "tokens_seen": done["tokens_seen"], "tokenizer_sha256": digest(tok),
+                        "train_rows": manifest["outputs"]["sft_train.jsonl"]["rows"], "assistant_tokens_seen": done["assistant_tokens_seen"],
+                        "validation_rows": manifest["outputs"]["sft_val.jsonl"]["rows"], "raw_archive_sha256": done["signature"]["base_sha256"],
+                        "base_step": 7, "base_tokens_seen": 700},
+                "training": {"sequence_length": 64}, "handoff": {"data_manifest_sha256": digest(root / "data/manifest.json")}}
+    paths = {"archive_dir": root / "archives/sft-final", "sft_work_dir": root / "sft", "tokenizer": tok}
+    mine = H.DpoStage().make_archive(paths, dpo_plan, "rev")
+    assert H.DpoStage().make_archive(paths, dpo_plan, "rev") == mine                     # a second call verifies, does not rewrite
+    with reference_import_path():
+        theirs = importlib.import_module("ops.dpo_handoff")
+    two_ranks = theirs.validate_sft
+    monkeypatch.setattr(theirs, "validate_sft", lambda checkpoint, *rest: two_ranks(
+        dict(checkpoint, rng_by_rank=list(checkpoint["rng_by_rank"]) * 2), *rest))
+    metadata, entries = theirs.verify_sft_archive(paths["archive_dir"], dpo_plan, sft_plan, expected_checkpoint_hash=digest(latest))
+    assert metadata == mine and metadata["assistant_tokens_seen"] == done["assistant_tokens_seen"] and metadata["stage"] == "sft"
+    assert tuple(entries) == A.SFT_ARCHIVE_FILES == tuple(theirs.ARCHIVE_FILES) and A.INIT_FILES == tuple(theirs.INIT_FILES)
+    # and the three-file start of the next stage is what the reference's own copy routine would accept
+    start = A.independent_copy(paths["archive_dir"], root / "dpo/initialization", H.DpoStage().boundary(dpo_plan), mine["snapshot_sha256"],
+                               files=A.SFT_ARCHIVE_FILES, only=A.INIT_FILES)
+    assert theirs.initialize_copy(paths["archive_dir"], root / "dpo/initialization", metadata) == start
+    with pytest.raises(ValueError):
+        theirs.verify_sft_archive(paths["archive_dir"], dict(dpo_plan, sft=dict(dpo_plan["sft"], step=done["step"] + 1)), sft_plan)
