@@ -322,3 +322,43 @@ def test_an_sft_run_of_this_trainer_satisfies_the_reference_archive_verifier(ref
     assert theirs.initialize_copy(paths["archive_dir"], root / "dpo/initialization", metadata) == start
     with pytest.raises(ValueError):
         theirs.verify_sft_archive(paths["archive_dir"], dict(dpo_plan, sft=dict(dpo_plan["sft"], step=done["step"] + 1)), sft_plan)
+
+
+def test_the_sealed_base_model_is_what_the_reference_guardian_expects(ref, tmp_path):
+    """Pretraining with this trainer to its planned end, sealed by this framework's base -> SFT guardian; the reference's
+    boundary check, archive verifier and initialization copy accept checkpoint and archive, and refuse them for another
+    boundary."""
+    from warpstate_ai_b200.data import prepare as P
+    from warpstate_ai_b200.orchestration import archive as A
+    from warpstate_ai_b200.orchestration import handoff as H
+    from warpstate_ai_b200.train import pretrain as T
+    from warpstate_ai_b200.utils.io import digest
+    tok = tmp_path / "tokenizer.model"
+    tok.write_bytes(TOK.read_bytes())
+    cfg_path = tmp_path / "cfg.json"
+    cfg_path.write_text(json.dumps(dict(vocab_size=32768, d_model=16, n_heads=2, n_cores=1, logical_depth=2, ffn_hidden=24, chunk_size=8,
+                                        gradient_checkpointing=False, parallel_memory=True)))
+    base_dir = tmp_path / "base"
+    P.write_synthetic_corpus(base_dir, tok, 73, 64, 32768, seed=2)
+    T.STOP = False
+    T.main(["--from-scratch", "--work-dir", str(base_dir), "--config", str(cfg_path), "--tokenizer", str(tok), "--stage", "train",
+            "--device", "cpu", "--test-small-gpu", "--train-tokens", "73", "--val-tokens", "64", "--seq-len", "8", "--micro-batch", "2",
+            "--grad-accum", "2", "--warmup-steps", "1", "--eval-batches", "1", "--no-activation-checkpointing",
+            "--dataset", "synthetic/uniform", "--dataset-config", "none", "--revision", "0"])
+    checkpoint = torch.load(base_dir / "run/latest.pt", weights_only=False)
+    boundary = {"step": checkpoint["step"], "tokens_seen": checkpoint["tokens_seen"], "tokenizer_sha256": digest(tok)}
+    with reference_import_path():
+        theirs = importlib.import_module("ops.posttrain_handoff")
+    theirs.validate_boundary(checkpoint, boundary, digest(tok))
+    with pytest.raises(ValueError):
+        theirs.validate_boundary(checkpoint, dict(boundary, step=boundary["step"] + 1), digest(tok))
+    paths = {"base_work_dir": base_dir, "tokenizer": tok, "archive_dir": base_dir / "archives/final"}
+    mine = H.SftStage().make_archive(paths, {"base": boundary}, "rev")
+    assert theirs.verify_archive(paths["archive_dir"], boundary, mine["snapshot_sha256"]) == mine
+    assert tuple(theirs.ARCHIVE_FILES) == A.ARCHIVE_FILES
+    start = theirs.independent_initialization(paths["archive_dir"], tmp_path / "sft/initialization", boundary, mine["snapshot_sha256"])
+    assert A.independent_copy(paths["archive_dir"], tmp_path / "sft/initialization", boundary, mine["snapshot_sha256"]) == start
+    exported = torch.load(start, weights_only=False)
+    assert all(torch.equal(exported["model"][k], v) for k, v in checkpoint["model"].items()) and "optimizer" not in exported
+    with pytest.raises(ValueError):
+        theirs.verify_archive(paths["archive_dir"], dict(boundary, tokens_seen=1))
