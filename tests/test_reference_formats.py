@@ -322,6 +322,17 @@ def test_an_sft_run_of_this_trainer_satisfies_the_reference_archive_verifier(ref
     assert theirs.initialize_copy(paths["archive_dir"], root / "dpo/initialization", metadata) == start
     with pytest.raises(ValueError):
         theirs.verify_sft_archive(paths["archive_dir"], dict(dpo_plan, sft=dict(dpo_plan["sft"], step=done["step"] + 1)), sft_plan)
+    # the reference's base -> SFT guardian accepts the run's completion records, and its trainer the resume state
+    with reference_import_path():
+        guardian = importlib.import_module("ops.posttrain_handoff")
+        trainer = importlib.import_module("posttrain")
+    completion = guardian.verify_completion(root / "sft/run", sft_plan, done["signature"]["base_sha256"])
+    assert completion == H.SftStage().verify_completion(root / "sft/run", sft_plan, done["signature"]["base_sha256"])
+    with pytest.raises(ValueError):
+        guardian.verify_completion(root / "sft/run", sft_plan, "0" * 64)
+    trainer.validate_resume(done, done["signature"], 1)
+    with pytest.raises(ValueError):
+        trainer.validate_resume(done, dict(done["signature"], world_size=2), 2)
 
 
 def test_the_sealed_base_model_is_what_the_reference_guardian_expects(ref, tmp_path):
