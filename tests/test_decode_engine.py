@@ -336,3 +336,20 @@ def test_decode_greedy_on_cpu_is_the_plain_loop():
     assert got.shape == (3, 9) and torch.equal(got, torch.stack(want, dim=1))
     assert b.pos == a.pos == (5 + 9) % 8
     assert b.decode_greedy(got[:, -1], 0).shape == (3, 0)
+
+
+def test_an_engine_first_used_in_inference_mode_can_be_used_outside_it():
+    """The chat entry points run under ``torch.inference_mode()``; the buffers they leave in the engine cannot be written
+    from ordinary code, so a later direct call gets fresh ones rather than an error."""
+    engine = DecodeEngine(tiny(), dtype=torch.float32)
+    ids = torch.randint(0, 97, (2, 11))
+    with torch.inference_mode():
+        inside = engine.prefill(ids).clone()
+        engine.step(torch.tensor([3, 4]))
+    assert engine.states[0].fast.is_inference()
+    outside = engine.prefill(ids)                      # same batch size: would clear the old buffers in place
+    assert not engine.states[0].fast.is_inference() and torch.equal(outside, inside)
+    following = engine.step(torch.tensor([3, 4]))
+    with torch.inference_mode():
+        again = engine.prefill(ids)
+        assert torch.equal(again, inside) and torch.equal(engine.step(torch.tensor([3, 4])), following)

@@ -220,3 +220,45 @@ def test_sampling_and_ngram_bans(ref):
     everything = set(range(24))
     assert S.sample_token(torch.zeros(24), 0.0, 0, 1.0, torch.Generator(), banned_tokens=everything) is None
     assert ref["chat"].sample_token(torch.zeros(24), 0.0, 0, 1.0, torch.Generator(), banned_tokens=everything) is None
+
+
+# ------------------------------------------------------------------------------------------- cached decode
+@pytest.mark.parametrize("parallel", [False, True])
+def test_chat_generation_follows_the_reference_decoder(ref, tokenizer, parallel):
+    """The same frozen model behind the reference's cached decoder and behind this framework's decode engine (FP32 on the
+    CPU): same prompt tokens, same reply, same stop reason, same record; logits along the way agree to rounding."""
+    from warpstate_ai_b200 import WarpStateConfig, WarpStateLM
+    from warpstate_ai_b200.serve import posttrain_chat as PC
+    from warpstate_ai_b200.serve.engine import DecodeEngine
+    with reference_import_path():
+        their_model_module = importlib.import_module("warpstate")
+    theirs = ref["ops.posttrain_chat"]
+    torch.manual_seed(7)
+    settings = dict(vocab_size=32768, d_model=32, n_heads=4, n_cores=2, logical_depth=4, ffn_hidden=48, chunk_size=8,
+                    gradient_checkpointing=False, parallel_memory=parallel)
+    model = WarpStateLM(WarpStateConfig(**settings))
+    with torch.no_grad():                                  # decisive logits: a reply must not hinge on the seventh digit
+        model.embed.weight.normal_(0, 1.0)
+        model.depth_scale.normal_(0, 0.1)
+        for core in model.cores:
+            core.memory_mix_logit.normal_()
+    model.eval().requires_grad_(False)
+    twin = their_model_module.WarpStateLM(their_model_module.WarpStateConfig(**settings))
+    twin.load_state_dict(model.state_dict())
+    twin.eval().requires_grad_(False)
+    engine, decoder = DecodeEngine(model, dtype=torch.float32), theirs.CachedDecoder(twin, dtype=torch.float32)
+    conversation = [{"role": "system", "content": "Be brief."}, {"role": "user", "content": "Name three colours, please."}]
+    for kwargs in (dict(max_new_tokens=20, max_context=200, temperature=0.0), dict(max_new_tokens=30, max_context=40, temperature=0.0),
+                   dict(max_new_tokens=12, max_context=200, temperature=0.7, seed=5)):
+        mine = PC.generate(engine, tokenizer, conversation, **kwargs)
+        other = theirs.generate(decoder, tokenizer, conversation, **kwargs)
+        assert set(mine) == set(other)
+        for key in ("response", "token_ids", "prompt_tokens", "generated_tokens", "sampled_tokens", "stop_reason", "temperature", "seed"):
+            assert mine[key] == other[key], (key, kwargs)
+    # the prompt's last logits, position by position through two chunk boundaries
+    ids = PC.encode_prompt(conversation, tokenizer)
+    caches = decoder.new_caches()
+    for value in ids:
+        reference_logits = decoder.step(torch.tensor([[value]]), caches)[0, -1]
+    mine = engine.prefill(torch.tensor([ids]))[0]
+    assert len(ids) > 16 and torch.allclose(mine, reference_logits, rtol=1e-4, atol=1e-4)

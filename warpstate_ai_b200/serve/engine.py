@@ -88,7 +88,11 @@ class DecodeEngine:
 
     # ------------------------------------------------------------------ state
     def new_state(self, batch: int) -> None:
-        if self.states is not None and batch == self.batch:
+        # Buffers made under ``torch.inference_mode()`` (as the chat entry points run) cannot be written from outside
+        # it; a caller that then uses the engine directly gets fresh ones (and a fresh graph) instead of an error.
+        stranded = (self.states is not None and self.states[0].fast.is_inference()
+                    and not torch.is_inference_mode_enabled())
+        if self.states is not None and batch == self.batch and not stranded:
             # same shapes: clear in place so that the captured graph and its buffers stay valid
             for st in self.states:
                 for t in (st.fast, st.slow, st.mixed, st.k, st.v, st.u):
