@@ -262,3 +262,34 @@ def test_chat_generation_follows_the_reference_decoder(ref, tokenizer, parallel)
         reference_logits = decoder.step(torch.tensor([[value]]), caches)[0, -1]
     mine = engine.prefill(torch.tensor([ids]))[0]
     assert len(ids) > 16 and torch.allclose(mine, reference_logits, rtol=1e-4, atol=1e-4)
+
+
+def test_probe_generation_follows_the_reference_probe(ref, tokenizer):
+    """The base-model probe (`chat.py`): same model, same prompt, same settings -> the same tokens, for the arg-max, for
+    seeded sampling with the repetition protections on, and when the prompt has to be cut to fit the context."""
+    from warpstate_ai_b200 import WarpStateConfig, WarpStateLM
+    from warpstate_ai_b200.serve import chat as C
+    with reference_import_path():
+        their_model_module = importlib.import_module("warpstate")
+    torch.manual_seed(9)
+    settings = dict(vocab_size=32768, d_model=32, n_heads=4, n_cores=1, logical_depth=3, ffn_hidden=48, chunk_size=8,
+                    gradient_checkpointing=False, parallel_memory=True)
+    model = WarpStateLM(WarpStateConfig(**settings))
+    with torch.no_grad():
+        model.embed.weight.normal_(0, 1.0)
+        model.depth_bias.normal_(0, 0.1)
+    model.eval().requires_grad_(False)
+    twin = their_model_module.WarpStateLM(their_model_module.WarpStateConfig(**settings))
+    twin.load_state_dict(model.state_dict())
+    twin.eval().requires_grad_(False)
+    prompt = "Question: which way does the river run after the bridge?\nAnswer:"
+    cases = [dict(max_new_tokens=24, temperature=0.0, top_k=0, top_p=1.0, repetition_penalty=1.0, no_repeat_ngram_size=0, max_context=256),
+             dict(max_new_tokens=24, temperature=0.0, top_k=0, top_p=1.0, repetition_penalty=1.3, no_repeat_ngram_size=3, max_context=256),
+             dict(max_new_tokens=24, temperature=0.9, top_k=50, top_p=0.92, seed=21, repetition_penalty=1.2, no_repeat_ngram_size=4, max_context=256),
+             dict(max_new_tokens=10, temperature=0.0, top_k=0, top_p=1.0, repetition_penalty=1.2, no_repeat_ngram_size=2, max_context=18)]
+    for case in cases:
+        mine = list(C.generate(model, tokenizer, prompt, **case))
+        other = list(ref["chat"].generate(twin, tokenizer, prompt, **case))
+        assert mine == other and 1 <= len(mine) <= case["max_new_tokens"], case
+    plain, protected = (list(C.generate(model, tokenizer, prompt, **case)) for case in cases[:2])
+    assert plain != protected                                    # the protections did change the reply
