@@ -293,3 +293,46 @@ def test_probe_generation_follows_the_reference_probe(ref, tokenizer):
         assert mine == other and 1 <= len(mine) <= case["max_new_tokens"], case
     plain, protected = (list(C.generate(model, tokenizer, prompt, **case)) for case in cases[:2])
     assert plain != protected                                    # the protections did change the reply
+
+
+@pytest.mark.parametrize("parallel", [False, True])
+def test_sequence_scores_and_masked_loss_follow_the_reference_heads(ref, parallel):
+    """DPO's scoring head and the memory-saving loss head, with gradients, FP32 on the CPU."""
+    from warpstate_ai_b200 import WarpStateConfig, WarpStateLM
+    with reference_import_path():
+        their_model_module = importlib.import_module("warpstate")
+    torch.manual_seed(11)
+    settings = dict(vocab_size=211, d_model=32, n_heads=4, n_cores=2, logical_depth=3, ffn_hidden=48, chunk_size=8,
+                    gradient_checkpointing=False, parallel_memory=parallel, loss_chunk_size=5)
+    model = WarpStateLM(WarpStateConfig(**settings))
+    with torch.no_grad():
+        model.embed.weight.normal_(0, 0.3)
+        model.depth_scale.normal_(0, 0.1)
+    scorer = their_model_module.WarpStateLM(their_model_module.WarpStateConfig(**settings))
+    scorer.load_state_dict(model.state_dict())
+    ref["dpo"].apply_sequence_logps(scorer, 6)
+    x = torch.randint(0, 211, (4, 24))
+    y = torch.randint(0, 211, (4, 24))
+    y[:, :9] = -100
+    y[3] = -100                                                    # a branch with nothing to score
+    mine = model.sequence_logps(x, y, head_chunk_size=6)
+    _, theirs = scorer(x, y, return_logits=False)
+    assert torch.allclose(mine, theirs, rtol=1e-5, atol=1e-5) and float(mine[3].detach()) == 0.0
+    weights = torch.tensor([1.0, -2.0, 0.5, 3.0])
+    (mine * weights).sum().backward()
+    (theirs * weights).sum().backward()
+    for (name, a), (_, b) in zip(model.named_parameters(), scorer.named_parameters()):
+        assert torch.allclose(a.grad, b.grad, rtol=1e-4, atol=1e-6), name
+    # the loss head that never builds [tokens, vocabulary]
+    plain = their_model_module.WarpStateLM(their_model_module.WarpStateConfig(**settings))
+    plain.load_state_dict(model.state_dict())
+    model.zero_grad()
+    _, loss_a = model(x, y, return_logits=False)
+    _, loss_b = plain(x, y, return_logits=False)
+    assert torch.allclose(loss_a, loss_b, rtol=1e-6, atol=1e-6)
+    loss_a.backward()
+    loss_b.backward()
+    for (name, a), (_, b) in zip(model.named_parameters(), plain.named_parameters()):
+        assert torch.allclose(a.grad, b.grad, rtol=1e-4, atol=1e-6), name
+    nothing = torch.full_like(y, -100)
+    assert float(model(x, nothing, return_logits=False)[1]) == float(plain(x, nothing, return_logits=False)[1]) == 0.0
