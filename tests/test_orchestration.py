@@ -326,3 +326,23 @@ def test_process_status_speaks_xmlrpc_over_a_unix_socket(tmp_path):
             H.process_status(path, "missing")
         server.shutdown()
     assert not H.clean_exit({"statename": "EXITED", "exitstatus": 1}) and not H.clean_exit({"statename": "RUNNING"})
+
+
+def test_child_environment_keeps_every_cache_inside_the_workspace(ws):
+    work = ws / "work"
+    work.mkdir()
+    environment = L.training_environment(work)
+    inside = {"TMPDIR": ws / "tmp", "XDG_CACHE_HOME": ws / ".cache", "UV_CACHE_DIR": ws / ".cache/uv", "PIP_CACHE_DIR": ws / ".cache/pip",
+              "TORCH_HOME": ws / ".cache/torch", "CUDA_CACHE_PATH": ws / ".cache/cuda", "TRITON_CACHE_DIR": ws / ".cache/triton",
+              "TORCHINDUCTOR_CACHE_DIR": ws / ".cache/torchinductor", "TORCH_EXTENSIONS_DIR": ws / ".cache/torch-extensions",
+              "HF_HOME": work / "hf-cache", "HF_DATASETS_CACHE": work / "hf-cache/datasets", "HF_XET_CACHE": work / "hf-cache/xet"}
+    for name, place in inside.items():
+        assert environment[name] == str(place) and place.is_dir(), name
+    assert environment["PYTHONDONTWRITEBYTECODE"] == "1"
+    assert environment["WARPSTATE_STOP_FILE"] == str(work / "control/training-stop-request")
+    assert environment["PATH"] == os.environ["PATH"]                        # everything else is inherited
+    single = L.build_command(1, Path("run_40b.py"), work, work / "logs", ["--stage", "train"])
+    assert single == [sys.executable, "run_40b.py", "--work-dir", str(work), "--stage", "train"]
+    many = L.build_command(8, Path("run_40b.py"), work, work / "logs", [])
+    assert many[:4] == [sys.executable, "-m", "torch.distributed.run", "--standalone"] and "127.0.0.1" in many
+    assert many[many.index("--nproc-per-node") + 1] == "8" and many[-3:] == ["run_40b.py", "--work-dir", str(work)]

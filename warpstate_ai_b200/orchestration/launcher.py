@@ -186,7 +186,10 @@ def supervise(command, stop_path, environment, *, grace_seconds: float = 820, te
     return supervisor.run(command, environment, pass_fds, poll_seconds, scan_seconds)
 
 
-CACHE_VARIABLES = {"XDG_CACHE_HOME": "", "PIP_CACHE_DIR": "pip", "TORCH_HOME": "torch", "CUDA_CACHE_PATH": "cuda",
+# every tool that caches on disk is pointed inside the workspace (the reference's list, reference
+# ops/launch_training.py:140-160; the compiler caches matter to the bootstrap and to the PyTorch yardstick arms)
+CACHE_VARIABLES = {"XDG_CACHE_HOME": "", "UV_CACHE_DIR": "uv", "PIP_CACHE_DIR": "pip", "TORCH_HOME": "torch",
+                   "CUDA_CACHE_PATH": "cuda", "TRITON_CACHE_DIR": "triton", "TORCHINDUCTOR_CACHE_DIR": "torchinductor",
                    "TORCH_EXTENSIONS_DIR": "torch-extensions"}
 
 
@@ -194,7 +197,8 @@ def training_environment(work: Path) -> dict:
     """The child's environment: every cache and temporary directory inside the workspace, no bytecode files,
     and the stop file the workers poll."""
     root = workspace_root()
-    places = {"TMPDIR": root / "tmp", "HF_HOME": work / "hf-cache", "HF_DATASETS_CACHE": work / "hf-cache/datasets"}
+    places = {"TMPDIR": root / "tmp", "HF_HOME": work / "hf-cache", "HF_DATASETS_CACHE": work / "hf-cache/datasets",
+              "HF_XET_CACHE": work / "hf-cache/xet"}
     places.update({name: root / ".cache" / sub for name, sub in CACHE_VARIABLES.items()})
     environment = dict(os.environ, PYTHONDONTWRITEBYTECODE="1")
     for name, place in places.items():
