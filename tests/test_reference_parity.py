@@ -336,3 +336,61 @@ def test_sequence_scores_and_masked_loss_follow_the_reference_heads(ref, paralle
         assert torch.allclose(a.grad, b.grad, rtol=1e-4, atol=1e-6), name
     nothing = torch.full_like(y, -100)
     assert float(model(x, nothing, return_logits=False)[1]) == float(plain(x, nothing, return_logits=False)[1]) == 0.0
+
+
+# ------------------------------------------------------------------------------------------- pretraining command line
+def test_pretraining_command_line_reads_like_the_reference(ref, monkeypatch):
+    """Every flag of the reference's ``run_40b.py`` exists here with the same default and the same value checks; this
+    framework adds its own (device, kernels, gradient path, sharding, bootstrap)."""
+    import contextlib
+    import io
+    from warpstate_ai_b200.train import pretrain as T
+    for name in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        monkeypatch.delenv(name, raising=False)
+
+    def theirs(argv):
+        monkeypatch.setattr(sys, "argv", ["run_40b.py", *argv])
+        try:
+            with contextlib.redirect_stderr(io.StringIO()):
+                return vars(ref["run_40b"].arguments())
+        except SystemExit:
+            return "refused"
+
+    def mine(argv):
+        try:
+            with contextlib.redirect_stderr(io.StringIO()):
+                return vars(T.arguments(list(argv)))
+        except SystemExit:
+            return "refused"
+
+    a, b = mine([]), theirs([])
+    assert set(b) <= set(a) and set(a) - set(b) == {"bootstrap", "device", "grad_sync", "kernels", "shard_optimizer", "shard_params"}
+    different = {k for k in b if a[k] != b[k]}
+    assert different == {"config", "tokenizer", "work_dir", "ddp_bucket_cap_mb"}            # three path roots; buckets follow the model here
+    assert (a["config"].name, a["tokenizer"].name, a["work_dir"].name) == (b["config"].name, b["tokenizer"].name, b["work_dir"].name)
+    accepted = [["--micro-batch", "4", "--grad-accum", "16", "--seq-len", "1024"], ["--lr", "3e-4", "--min-lr", "3e-4"],
+                ["--no-activation-checkpointing", "--bf16-residuals", "--loss-mode", "full"], ["--stage", "prepare", "--workers", "2"],
+                ["--max-steps", "5", "--stop-at-step", "3", "--eval-every", "7", "--save-every", "9"],
+                ["--vram-limit-gib", "150", "--vram-headroom-gib", "0"], ["--from-scratch", "--seed", "9"],
+                ["--compile-core", "--compile-mode", "max-autotune-no-cudagraphs"], ["--async-checkpoint"], ["--reconfigure"],
+                ["--ddp-bucket-cap-mb", "64"], ["--test-small-gpu", "--train-tokens", "73", "--val-tokens", "64", "--seq-len", "8"]]
+    for argv in accepted:
+        x, y = mine(argv), theirs(argv)
+        assert x != "refused" and y != "refused", argv
+        assert {k: x[k] for k in y if k not in different} == {k: v for k, v in y.items() if k not in different}, argv
+    refused = [["--micro-batch", "0"], ["--grad-accum", "-1"], ["--seq-len", "0"], ["--lr", "1e-5", "--min-lr", "1e-4"], ["--min-lr", "0"],
+               ["--weight-decay", "-0.1"], ["--max-steps", "0"], ["--stop-at-step", "0"], ["--vram-limit-gib", "0"], ["--vram-limit-gib", "inf"],
+               ["--vram-headroom-gib", "-1"], ["--train-tokens", "1"], ["--val-tokens", "2048"], ["--eval-every", "0"], ["--save-every", "0"],
+               ["--ddp-bucket-cap-mb", "nan"], ["--stage", "evaluate"], ["--loss-mode", "fused"], ["--weights", "w.pt", "--from-scratch"],
+               ["--compile-mode", "max-autotune"], ["--warmup-steps", "0"], ["--loss-chunk-size", "0"]]
+    for argv in refused:
+        assert mine(argv) == theirs(argv) == "refused", argv
+    # combinations of the reference's execution adapters are its own business: the flags are accepted here, reported as
+    # served by the native path, and nothing is selected by them
+    assert theirs(["--compile", "--compile-core"]) == "refused" and mine(["--compile", "--compile-core"]) != "refused"
+    monkeypatch.setenv("WORLD_SIZE", "2")
+    monkeypatch.setenv("RANK", "1")
+    monkeypatch.setenv("LOCAL_RANK", "1")
+    assert mine(["--stage", "all"]) == theirs(["--stage", "all"]) == "refused"              # ranks train; they do not prepare data
+    x, y = mine(["--stage", "train"]), theirs(["--stage", "train"])
+    assert (x["rank"], x["world_size"], x["local_rank"]) == (y["rank"], y["world_size"], y["local_rank"]) == (1, 2, 1)
