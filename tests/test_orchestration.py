@@ -346,3 +346,21 @@ def test_child_environment_keeps_every_cache_inside_the_workspace(ws):
     many = L.build_command(8, Path("run_40b.py"), work, work / "logs", [])
     assert many[:4] == [sys.executable, "-m", "torch.distributed.run", "--standalone"] and "127.0.0.1" in many
     assert many[many.index("--nproc-per-node") + 1] == "8" and many[-3:] == ["run_40b.py", "--work-dir", str(work)]
+
+
+def test_preflight_can_prepare_its_fixture_without_launching_anything(ws, capsys, monkeypatch):
+    from warpstate_ai_b200.orchestration import preflight
+    base = ws / "base"
+    base.mkdir()
+    monkeypatch.setattr(preflight, "run_trainer", lambda *a, **k: pytest.fail("--prepare-only must not launch training"))
+    assert preflight.main(["--stage", "dpo", "--work-dir", str(ws / "dpo/preflight"), "--processes", "2", "--device", "cpu",
+                           "--base-work-dir", str(base), "--prepare-only"]) == 0
+    said = json.loads(capsys.readouterr().out.splitlines()[-1])
+    assert said["prepared"] is True and said["stage"] == "dpo" and said["weights_sha256"] == digest(Path(said["weights"]))
+    plan = json.loads(Path(said["plan"]).read_text())
+    assert plan["handoff"] == {"base_work_dir": "base"} and plan["format"] == "warpstate-dpo-plan-v1"
+    assert (Path(said["data"]) / "manifest.json").is_file() and not (ws / "dpo/preflight/report.json").exists()
+    with pytest.raises(SystemExit):
+        preflight.main(["--work-dir", str(ws / "x"), "--base-work-dir", str(ws / "absent"), "--prepare-only"])
+    with pytest.raises(SystemExit):
+        preflight.main(["--work-dir", str(ws / "x"), "--base-work-dir", "/tmp", "--prepare-only"])      # outside the workspace

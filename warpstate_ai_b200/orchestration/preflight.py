@@ -35,7 +35,9 @@ def fixture_rows(n: int):
     return sft, dpo
 
 
-def build_fixture(root: Path, stage: str, processes: int) -> dict:
+def build_fixture(root: Path, stage: str, processes: int, base_work_dir: Path | None = None) -> dict:
+    """Model export, prepared data and plan of the gate's tiny run.  With ``base_work_dir`` the plan names the
+    pretraining job's work directory, so the trainer children hold its pipeline lock (shared) while they run."""
     from .. import WarpStateConfig, WarpStateLM
     from ..ckpt.formats import export_chat_snapshot
     from ..data.prepare_posttrain import prepare
@@ -58,6 +60,9 @@ def build_fixture(root: Path, stage: str, processes: int) -> dict:
         plan = {"format": "warpstate-dpo-plan-v1", "stage": "dpo", "training": training}
     else:
         plan = {"format": "warpstate-posttrain-plan-v1", "stage": "sft", "training": training}
+    if base_work_dir is not None:
+        from .launcher import workspace_root
+        plan["handoff"] = {"base_work_dir": str(Path(base_work_dir).resolve().relative_to(workspace_root()))}
     (root / "plan.json").write_text(json.dumps(plan))
     return {"tokenizer": tok, "weights": root / "init/model.pt", "data": root / "data", "plan": root / "plan.json"}
 
@@ -89,10 +94,14 @@ def compare(a: dict, b: dict, rtol: float = 1e-5, atol: float = 1e-6) -> None:
                 raise ValueError(f"resumed run differs in optimizer state {index}.{field}")
 
 
-def run(stage: str, work: Path, processes: int, device: str) -> dict:
+def run(stage: str, work: Path, processes: int, device: str, base_work_dir: Path | None = None,
+        prepare_only: bool = False) -> dict:
     os.environ.setdefault("WARPSTATE_WORKSPACE", str(work.resolve()))
     root = work.resolve()
-    fx = build_fixture(root / "fixture", stage, processes)
+    fx = build_fixture(root / "fixture", stage, processes, base_work_dir)
+    if prepare_only:                      # the fixture alone, made on the CPU; nothing is launched
+        return {"prepared": True, "stage": stage, "processes": processes, **{key: str(path) for key, path in fx.items()},
+                "weights_sha256": digest(fx["weights"])}
     base_hash = digest(fx["weights"])
     run_trainer(stage, fx, root / "continuous", processes, device, cache=root / "cache-a")
     run_trainer(stage, fx, root / "split", processes, device, extra=("--max-steps", "1"), cache=root / "cache-b")
@@ -122,10 +131,20 @@ def main(argv=None) -> int:
     p.add_argument("--work-dir", type=Path, required=True)
     p.add_argument("--processes", type=int, default=2)
     p.add_argument("--device", choices=["cuda", "cpu"], default="cuda" if torch.cuda.is_available() else "cpu")
+    p.add_argument("--base-work-dir", type=Path,
+                   help="work directory of the pretraining job: the gate's trainers then hold its pipeline lock (shared)")
+    p.add_argument("--prepare-only", action="store_true", help="create the fixture on the CPU and stop; never launches training")
     a = p.parse_args(argv)
+    if a.base_work_dir is not None:
+        from .launcher import workspace_root
+        if not a.base_work_dir.is_dir() or not a.base_work_dir.resolve().is_relative_to(workspace_root()):
+            p.error("--base-work-dir must be an existing directory inside the workspace")
     a.work_dir.mkdir(parents=True, exist_ok=True)
+    if a.prepare_only:
+        print(json.dumps(run(a.stage, a.work_dir, a.processes, a.device, a.base_work_dir, prepare_only=True)), flush=True)
+        return 0
     try:
-        report = run(a.stage, a.work_dir, a.processes, a.device)
+        report = run(a.stage, a.work_dir, a.processes, a.device, a.base_work_dir)
     except BaseException as error:  # noqa: BLE001
         atomic_json(a.work_dir / "report.json", {"accepted": False, "error": f"{type(error).__name__}: {error}"})
         raise
