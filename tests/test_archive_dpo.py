@@ -151,3 +151,34 @@ def test_guardian_records_travel_with_the_archive_and_the_layout_is_the_referenc
         files = next(ast.literal_eval(node.value) for node in tree.body
                      if isinstance(node, ast.Assign) and getattr(node.targets[0], "id", "") == "FILES")
         assert tuple(files) == AD.FILES
+
+
+def test_a_guarded_run_is_archived_only_after_its_guardian_is_done(tmp_path, monkeypatch):
+    from warpstate_ai_b200.orchestration import handoff as H
+    work = tmp_path / "dpo"
+    (work / "control").mkdir(parents=True)
+    asked = []
+
+    def status(socket_path, program):
+        asked.append((Path(socket_path), program))
+        return state
+
+    monkeypatch.setattr(H, "process_status", status)
+    section = {"supervisor_socket": "control/supervisor.sock"}
+    AD.guardian_done(tmp_path, {"work_dir": "dpo"}, work, "warpstate-dpo")            # no guardian in the plan: nothing to ask
+    assert asked == []
+    state = {"statename": "RUNNING"}
+    with pytest.raises(ValueError, match="must have exited successfully"):
+        AD.guardian_done(tmp_path, section, work, "warpstate-dpo")
+    state = {"statename": "EXITED", "exitstatus": 3}
+    with pytest.raises(ValueError, match="must have exited successfully"):
+        AD.guardian_done(tmp_path, section, work, "warpstate-dpo")
+    state = {"statename": "EXITED", "exitstatus": 0}
+    with pytest.raises(ValueError, match="has not completed its final integrity checks"):
+        AD.guardian_done(tmp_path, section, work, "warpstate-dpo")                    # no journal yet
+    (work / "control/handoff.json").write_text(json.dumps({"phase": "paused"}))
+    with pytest.raises(ValueError, match="has not completed"):
+        AD.guardian_done(tmp_path, section, work, "warpstate-dpo")
+    (work / "control/handoff.json").write_text(json.dumps({"phase": "complete"}))
+    AD.guardian_done(tmp_path, section, work, "my-dpo-program")
+    assert asked[-1] == (tmp_path / "control/supervisor.sock", "my-dpo-program")

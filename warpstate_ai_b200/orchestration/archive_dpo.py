@@ -258,6 +258,19 @@ def chat_copy(archive, destination) -> Path:
     return destination / "model.pt"
 
 
+def guardian_done(root: Path, section: dict, work: Path, program: str) -> None:
+    """Where a guardian ran the job (the plan names its supervisor socket), archive only what it has finished with: the
+    program exited cleanly and its journal reached ``complete`` (reference ops/archive_dpo.py:273-276)."""
+    if "supervisor_socket" not in section:
+        return
+    from .handoff import clean_exit, process_status
+    enforce([Rule("DPO guardian must have exited successfully before archival",
+                  lambda: clean_exit(process_status(root / section["supervisor_socket"], program))),
+             Rule("DPO guardian has not completed its final integrity checks",
+                  lambda: (work / "control/handoff.json").is_file()
+                  and read_json(work / "control/handoff.json")["phase"] == "complete")])
+
+
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--config", type=Path, help="DPO plan (its handoff section names the work and data directories)")
@@ -266,6 +279,9 @@ def main(argv=None) -> int:
     parser.add_argument("--chat-copy", type=Path, help="make a sealed chat copy here instead of archiving")
     parser.add_argument("--verify-only", action="store_true")
     parser.add_argument("--revision", default="")
+    parser.add_argument("--program", default="warpstate-dpo",
+                        help="supervisor program of the DPO guardian: where the plan names a supervisor socket, the archive is "
+                             "made only after that program has exited cleanly and recorded phase 'complete'")
     options = parser.parse_args(argv)
     if options.chat_copy is not None:
         model = chat_copy(options.archive, options.chat_copy)
@@ -279,6 +295,7 @@ def main(argv=None) -> int:
         metadata, _ = verify_dpo_archive(destination)
     else:
         with process_lock(work / "control/launcher.lock"), process_lock(root / "pipeline.lock", shared=True):
+            guardian_done(root, section, work, options.program)
             metadata = archive_dpo(work / "run", root / section["data_dir"], work / "reference-cache", root / section["tokenizer"],
                                    options.config, destination, options.revision)
     print(json.dumps({"archive": str(destination), "step": metadata["step"], "model_sha256": metadata["snapshot_sha256"]}))
