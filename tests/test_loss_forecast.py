@@ -91,3 +91,32 @@ def test_command_line_writes_a_self_describing_report(tmp_path, capsys):
     assert report["holdouts"] == []                                        # no complete billion after 4 B to test on
     with pytest.raises(SystemExit):
         LF.main(["--input", str(source), "--output", str(source)])
+
+
+def test_the_report_can_be_drawn_without_a_plotting_library(tmp_path):
+    import xml.etree.ElementTree as ET
+    rows = [{"tokens": int(t * 1e9), "loss": 1.9 + 1.2 * t ** -0.4} for t in np.arange(1.0, 7.31, 0.05)]
+    source = tmp_path / "val.jsonl"
+    source.write_text("\n".join(json.dumps(r) for r in rows) + "\n")
+    out, picture = tmp_path / "forecast.json", tmp_path / "pictures" / "forecast.svg"
+    assert LF.main(["--input", str(source), "--output", str(out), "--plot", str(picture)]) == 0
+    tree = ET.parse(picture)                                               # well-formed
+    space = "{http://www.w3.org/2000/svg}"
+    root = tree.getroot()
+    assert root.tag == space + "svg" and root.get("width") == "960"
+    report = json.loads(out.read_text())
+    families = {f["parameters"]["model"] for f in report["fits"] if f["start_B"] == 1}
+    lines = root.findall(space + "polyline")
+    assert len(lines) == 1 + 2 * len(families)                             # the bin means; each family solid and dashed
+    assert sum(1 for line in lines if line.get("stroke-dasharray")) == len(families)
+    assert len(root.findall(space + "circle")) == len(report["observed_validation"])
+    labels = " ".join(t.text or "" for t in root.findall(space + "text"))
+    assert all(name in labels for name in families) and "1073.74" in labels and "not confidence intervals" in labels
+    for line in lines:                                                     # every point inside the canvas
+        for point in line.get("points").split():
+            x, y = map(float, point.split(","))
+            assert 0 <= x <= 960 and 0 <= y <= 540
+    with pytest.raises(SystemExit):
+        LF.main(["--input", str(source), "--output", str(out), "--plot", str(out)])
+    with pytest.raises(ValueError, match="nothing to plot"):
+        LF.plot({"bins": [], "fits": []}, tmp_path / "empty.svg")

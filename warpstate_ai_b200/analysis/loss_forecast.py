@@ -198,21 +198,89 @@ def analyze(raw: bytes, *, bin_width_b: float = 0.25, first_bin_b: float = 1.0, 
             "fits": fits, "holdouts": holdouts}
 
 
+# ----------------------------------------------------------------------------------- picture
+PALETTE = ("#2469aa", "#ca6d12", "#238456", "#8051a5", "#cfa323", "#8f3333", "#444444")
+
+
+def plot(report: dict, output: Path, target: float = 2.0) -> None:
+    """The report as a picture, written as plain SVG (no plotting library): every validation, the bin means and, for the
+    earliest fitting window, each family's curve drawn solid over the data and dashed beyond it, on a logarithmic token
+    axis out to the largest budget.  How far apart the dashed lines end is the message of the study."""
+    bins = report["bins"]
+    if not bins or not report["fits"]:
+        raise ValueError("nothing to plot: the report has no bins or no fits")
+    end = report["complete_bins_end_B"]
+    first = min(f["start_B"] for f in report["fits"])
+    curves = [f for f in report["fits"] if f["start_B"] == first]
+    budgets = sorted(float(name[:-1]) for name in curves[0]["endpoint_losses"])
+    far = max(budgets + [end * 1.25])
+    observed = report.get("observed_validation") or [{"tokens_B": b["tokens_B"], "loss": b["loss"]} for b in bins]
+    seen = [row["loss"] for row in observed]
+    low, high = min(min(seen), target) - 0.15, max(seen) + 0.1
+    width, height, left, right, top, bottom = 960, 540, 70, 20, 40, 50
+
+    def at(tokens_b: float, loss: float) -> str:
+        x = left + (math.log(tokens_b) - math.log(first)) / (math.log(far) - math.log(first)) * (width - left - right)
+        y = top + (high - min(max(loss, low), high)) / (high - low) * (height - top - bottom)
+        return f"{x:.1f},{y:.1f}"
+
+    parts = [f'<svg xmlns="http://www.w3.org/2000/svg" width="{width}" height="{height}" viewBox="0 0 {width} {height}" '
+             'font-family="sans-serif" font-size="12">', f'<rect width="{width}" height="{height}" fill="white"/>',
+             f'<text x="{left}" y="22" font-size="14">Validation loss against tokens trained (billions, log axis): '
+             'illustrative scenarios, not confidence intervals</text>']
+    for budget in budgets:
+        x = at(budget, low).split(",")[0]
+        parts.append(f'<line x1="{x}" y1="{top}" x2="{x}" y2="{height - bottom}" stroke="#bbbbbb" stroke-dasharray="2,4"/>')
+        parts.append(f'<text x="{x}" y="{height - bottom + 16}" text-anchor="middle">{budget:g}</text>')
+    for tick in (first, end):
+        x = at(tick, low).split(",")[0]
+        parts.append(f'<text x="{x}" y="{height - bottom + 32}" text-anchor="middle" fill="#666666">{tick:g}</text>')
+    steps = 6
+    for k in range(steps + 1):
+        value = low + (high - low) * k / steps
+        y = at(first, value).split(",")[1]
+        parts.append(f'<line x1="{left}" y1="{y}" x2="{width - right}" y2="{y}" stroke="#eeeeee"/>')
+        parts.append(f'<text x="{left - 8}" y="{y}" text-anchor="end" dominant-baseline="middle">{value:.2f}</text>')
+    y = at(first, target).split(",")[1]
+    parts.append(f'<line x1="{left}" y1="{y}" x2="{width - right}" y2="{y}" stroke="#8f3333" stroke-dasharray="6,4"/>')
+    for row in observed:
+        if row["tokens_B"] >= first:
+            x, y = at(row["tokens_B"], row["loss"]).split(",")
+            parts.append(f'<circle cx="{x}" cy="{y}" r="1.6" fill="#999999"/>')
+    parts.append('<polyline fill="none" stroke="black" stroke-width="1.5" points="'
+                 + " ".join(at(b["tokens_B"], b["loss"]) for b in bins if b["tokens_B"] >= first) + '"/>')
+    for index, fit_row in enumerate(curves):
+        colour, parameters = PALETTE[index % len(PALETTE)], fit_row["parameters"]
+        over = np.linspace(first, end, 60)
+        beyond = np.geomspace(end, far, 120)
+        for grid, dash in ((over, ""), (beyond, ' stroke-dasharray="7,4"')):
+            points = " ".join(at(float(t), float(v)) for t, v in zip(grid, predict(parameters, grid)))
+            parts.append(f'<polyline fill="none" stroke="{colour}" stroke-width="1.3"{dash} points="{points}"/>')
+        parts.append(f'<text x="{width - right - 4}" y="{top + 14 + 15 * index}" text-anchor="end" fill="{colour}">'
+                     f'{parameters["model"]} (fit {first:g}-{end:g} B, rmse {parameters["rmse"]:.4f})</text>')
+    parts.append("</svg>")
+    output.parent.mkdir(parents=True, exist_ok=True)
+    output.write_text("\n".join(parts) + "\n")
+
+
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     p.add_argument("--input", required=True, type=Path, help="frozen validation JSONL snapshot")
     p.add_argument("--output", required=True, type=Path)
     p.add_argument("--bin-width-b", type=float, default=0.25)
     p.add_argument("--target-loss", type=float, default=2.0)
+    p.add_argument("--plot", type=Path, help="also draw the report as an SVG picture here")
     a = p.parse_args(argv)
-    if a.input.resolve() == a.output.resolve():
-        p.error("input and output must be different files")
+    if a.input.resolve() == a.output.resolve() or (a.plot is not None and a.plot.resolve() in (a.input.resolve(), a.output.resolve())):
+        p.error("input, output and plot must be different files")
     report = analyze(a.input.read_bytes(), bin_width_b=a.bin_width_b, target=a.target_loss)
     report["source_path"] = str(a.input)
     report["analysis_sha256"] = hashlib.sha256(Path(__file__).read_bytes()).hexdigest()
     report["versions"] = {"python": platform.python_version(), "numpy": np.__version__}
     a.output.parent.mkdir(parents=True, exist_ok=True)
     a.output.write_text(json.dumps(report, indent=2, allow_nan=False) + "\n")
+    if a.plot is not None:
+        plot(report, a.plot, a.target_loss)
     print(f"Analyzed {report['source_rows']} validation rows through {report['complete_bins_end_B']:g}B complete bins; "
           f"wrote {a.output}")
     return 0
