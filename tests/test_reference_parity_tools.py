@@ -155,3 +155,27 @@ def test_frozen_snapshot_of_a_training_state(ref, tmp_path):
     a, b = (torch.load(tmp_path / name, weights_only=False) for name in ("mine.pt", "theirs.pt"))
     assert list(a) == list(b) and torch.equal(a["model"]["a"], b["model"]["a"]) and a["history"][0] == b["history"][0]
     assert sorted(p.name for p in tmp_path.iterdir()) == ["mine.pt", "theirs.pt"]                      # no staging file left
+
+
+# ------------------------------------------------------------------------------------------- GEMM benchmark cases
+def test_gemm_benchmark_cases_are_the_reference_ones(capsys):
+    """The projection GEMMs the isolated benchmark times: same M, N, K and FLOPs per family and operation."""
+    from warpstate_ai_b200.bench import gemm_bench as GB
+    if not (REF / "ops" / "benchmark_gemm.py").exists():
+        pytest.skip("reference not installed under baseline/_ref")
+    with reference_import_path():
+        theirs = importlib.import_module("ops.benchmark_gemm")
+    for rows in (8192, 16384):
+        mine = GB.projection_cases(["ffn_up_gate", "in_proj", "ffn_down", "out_proj"], rows, ["fwd", "dx", "dw"])
+        other = theirs.projection_cases(["ffn_up_gate", "in_proj", "ffn_down", "out_proj"], rows, ["fwd", "dx", "dw"])
+        assert [(c["operation"], c["m"], c["n"], c["k"], c["flops"], c["a_shape"], c["b_shape"]) for c in mine] == \
+            [(c["operation"], c["m"], c["n"], c["k"], c["flops"], c["a_shape"], c["b_shape"]) for c in other]
+    assert GB.main(["--list-shapes", "--families", "in_proj", "--operations", "dw", "--rows", "8192"]) == 0       # no GPU needed
+    listed = json.loads(capsys.readouterr().out)
+    assert listed == [{"name": "in_proj.dw", "family": "in_proj", "operation": "dw", "m": 10240, "n": 2048, "k": 8192,
+                       "a_shape": [10240, 8192], "b_shape": [8192, 2048], "flops": 2 * 10240 * 2048 * 8192}]
+    a = GB.arguments(["--tokens", "4096", "--iters", "5"])                       # the earlier spellings still work
+    assert (a.rows, a.repeats, a.trials, a.warmup, a.backends) == (4096, 5, 1, 3, ["ours", "cublas"])
+    for bad in (["--rows", "0"], ["--trials", "0"], ["--families", "lm_head"], ["--burnin-seconds", "-1"]):
+        with pytest.raises(SystemExit):
+            GB.arguments(bad)
