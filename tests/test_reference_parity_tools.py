@@ -179,3 +179,18 @@ def test_gemm_benchmark_cases_are_the_reference_ones(capsys):
     for bad in (["--rows", "0"], ["--trials", "0"], ["--families", "lm_head"], ["--burnin-seconds", "-1"]):
         with pytest.raises(SystemExit):
             GB.arguments(bad)
+
+
+def test_gradient_accumulation_benchmark_command_line(capsys):
+    from warpstate_ai_b200.bench import grad_accum_bench as GA
+    assert GA.main(["--list-shapes", "--families", "ffn_down", "in_proj", "--rows", "8192"]) == 0
+    assert json.loads(capsys.readouterr().out) == [
+        {"family": "down", "rows": 8192, "n": 2048, "k": 7168, "flops": 2 * 8192 * 7168 * 2048},
+        {"family": "in_proj", "rows": 8192, "n": 10240, "k": 2048, "flops": 2 * 8192 * 2048 * 10240}]
+    a = GA.arguments(["--tokens", "16384", "--iters", "4", "--accumulation-steps", "4"])
+    assert (a.rows, a.repeats, a.accumulation_steps) == (16384, 4, 4) and "cublas_fp32_addmm" not in a.variants
+    assert "cublas_fp32_addmm" in GA.arguments(["--rows", "4096"]).variants
+    assert GA.arguments(["--variants", "grouped_launch"]).variants == ["grouped_launch"]
+    for bad in (["--accumulation-steps", "0"], ["--variants", "triton"], ["--rows", "-1"]):
+        with pytest.raises(SystemExit):
+            GA.arguments(bad)

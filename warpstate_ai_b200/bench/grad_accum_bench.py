@@ -19,59 +19,104 @@ from __future__ import annotations
 
 import argparse
 import json
+import statistics
+from pathlib import Path
 
-import torch
+from .gemm_bench import ALIASES, FAMILIES, time_fn
 
-from .gemm_bench import FAMILIES, time_fn
+VARIANTS = ("cublas_bf16_cast_add", "cublas_fp32_addmm", "fused_epilogue", "grouped_launch")
+
+
+def arguments(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--families", nargs="+", choices=[*FAMILIES, *ALIASES], default=list(FAMILIES))
+    ap.add_argument("--variants", nargs="+", choices=VARIANTS,
+                    help="default: all; the direct FP32 addmm only up to 4096 rows (it needs FP32 copies of the operands)")
+    ap.add_argument("--rows", "--tokens", dest="rows", type=int, default=16384, help="micro-batch times sequence length")
+    ap.add_argument("--accumulation-steps", type=int, default=1,
+                    help="micro-batches accumulated into the same FP32 gradient per timed launch group")
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--repeats", "--iters", dest="repeats", type=int, default=10)
+    ap.add_argument("--trials", type=int, default=1, help="the median over this many trials is reported")
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--device", type=int, default=0)
+    ap.add_argument("--output-dir", type=Path, help="write results.json here")
+    ap.add_argument("--list-shapes", action="store_true", help="print the dW problems and exit (no GPU needed)")
+    a = ap.parse_args(argv)
+    if min(a.rows, a.accumulation_steps, a.repeats, a.trials) < 1 or a.warmup < 0:
+        ap.error("rows, accumulation steps, repeats and trials must be positive; warmup must not be negative")
+    a.families = list(dict.fromkeys(ALIASES.get(f, f) for f in a.families))
+    if a.variants is None:
+        a.variants = [v for v in VARIANTS if v != "cublas_fp32_addmm" or a.rows <= 4096]
+    return a
+
+
+def problems_of(families, rows: int) -> list[dict]:
+    """The weight-gradient product of each family: ``grad[n, k] += dy[rows, n]^T x[rows, k]``."""
+    return [{"family": f, "rows": rows, "n": FAMILIES[f][1], "k": FAMILIES[f][0], "flops": 2 * rows * FAMILIES[f][0] * FAMILIES[f][1]}
+            for f in families]
 
 
 def main(argv=None) -> int:
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--tokens", type=int, default=16384)
-    ap.add_argument("--iters", type=int, default=10)
-    a = ap.parse_args(argv)
+    a = arguments(argv)
+    shapes = problems_of(a.families, a.rows)
+    if a.list_shapes:
+        print(json.dumps(shapes, indent=1))
+        return 0
+    import torch
     from ..ops import gemm as G
-    device = torch.device("cuda", 0)
+    device = torch.device("cuda", a.device)
+    torch.cuda.set_device(device)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
-    torch.manual_seed(0)
+    torch.manual_seed(a.seed)
     problems = []
-    for name, (k, n) in FAMILIES.items():
-        dy = torch.randn(a.tokens, n, device=device).bfloat16()
-        x = torch.randn(a.tokens, k, device=device).bfloat16()
-        problems.append((name, dy, x, torch.zeros(n, k, device=device)))
-    flops = sum(2 * a.tokens * dy.shape[1] * x.shape[1] for _, dy, x, _ in problems)
+    for shape in shapes:
+        dy = torch.randn(a.rows, shape["n"], device=device).bfloat16()
+        x = torch.randn(a.rows, shape["k"], device=device).bfloat16()
+        problems.append((shape["family"], dy, x, torch.zeros(shape["n"], shape["k"], device=device)))
+    steps = a.accumulation_steps
+    flops = steps * sum(shape["flops"] for shape in shapes)
 
     def baseline():
-        for _, dy, x, grad in problems:
-            grad.add_((dy.T @ x).to(torch.float32))       # BF16 GEMM, cast, FP32 add
+        for _ in range(steps):
+            for _, dy, x, grad in problems:
+                grad.add_((dy.T @ x).to(torch.float32))       # BF16 GEMM, cast, FP32 add
 
     def addmm_fp32():
-        for _, dy, x, grad in problems:
-            grad.addmm_(dy.T.float(), x.float())           # direct FP32 accumulate (TF32/FP32 GEMM)
+        for _ in range(steps):
+            for _, dy, x, grad in problems:
+                grad.addmm_(dy.T.float(), x.float())           # direct FP32 accumulate (TF32/FP32 GEMM)
 
     def fused():
-        for _, dy, x, grad in problems:
-            G.grad_weight_accumulate(dy, x, grad, accumulate=True)
+        for _ in range(steps):
+            for _, dy, x, grad in problems:
+                G.grad_weight_accumulate(dy, x, grad, accumulate=True)
 
     def grouped():
-        G.grad_weight_accumulate_group([(dy, x, grad, True) for _, dy, x, grad in problems])
+        for _ in range(steps):
+            G.grad_weight_accumulate_group([(dy, x, grad, True) for _, dy, x, grad in problems])
 
-    variants = {"cublas_bf16_cast_add": baseline, "fused_epilogue": fused, "grouped_launch": grouped}
-    if a.tokens <= 4096:
-        variants["cublas_fp32_addmm"] = addmm_fp32  # needs FP32 copies of the operands
-    for label, fn in variants.items():
+    launch = {"cublas_bf16_cast_add": baseline, "cublas_fp32_addmm": addmm_fp32, "fused_epilogue": fused, "grouped_launch": grouped}
+    rows = []
+    for label in a.variants:
+        fn = launch[label]
         for _, _, _, grad in problems:
             grad.zero_()
         fn()
         torch.cuda.synchronize()
         worst = 0.0
         for _, dy, x, grad in problems:
-            ref = dy.float().T @ x.float()
+            ref = steps * (dy.float().T @ x.float())
             worst = max(worst, float((grad - ref).pow(2).mean().sqrt() / ref.pow(2).mean().sqrt()))
-        ms = time_fn(fn, a.iters, flush)
-        print(json.dumps({"variant": label, "tokens": a.tokens, "ms_per_layer": round(ms, 4),
-                          "tflops": round(flops / ms / 1e9, 1), "relative_rms_error": worst}), flush=True)
+        ms = statistics.median(time_fn(fn, a.repeats, flush, a.warmup) for _ in range(a.trials))
+        rows.append({"variant": label, "tokens": a.rows, "accumulation_steps": steps, "families": a.families,
+                     "ms_per_layer": round(ms / steps, 4), "tflops": round(flops / ms / 1e9, 1), "relative_rms_error": worst})
+        print(json.dumps(rows[-1]), flush=True)
     G.check_device_errors()
+    if a.output_dir is not None:
+        a.output_dir.mkdir(parents=True, exist_ok=True)
+        (a.output_dir / "results.json").write_text(json.dumps({
+            "rows": rows, "problems": shapes, "gpu": torch.cuda.get_device_name(device), "torch": torch.__version__}, indent=1) + "\n")
     return 0
 
 
