@@ -81,6 +81,8 @@ def main(argv=None) -> int:
     p.add_argument("--minimum-gain", type=float, default=0.01)
     p.add_argument("--maximum-relative-rms", type=float, default=0.003)
     p.add_argument("--seed", type=int, default=1337)
+    p.add_argument("--input-scale", type=float, default=1.0, help="standard deviation of the random activations and gradients")
+    p.add_argument("--device", type=int, default=0, help="CUDA device index")
     p.add_argument("--list-cases", action="store_true")
     p.add_argument("--output-dir", type=Path, required=True)
     a = p.parse_args(argv)
@@ -90,7 +92,8 @@ def main(argv=None) -> int:
         return 0
     from ..ops import _ext, gemm as G
     lib = _ext.cdll()
-    device = torch.device("cuda", 0)
+    device = torch.device("cuda", a.device)
+    torch.cuda.set_device(device)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
     a.output_dir.mkdir(parents=True, exist_ok=True)
     report = {"started": time.time(), "device": torch.cuda.get_device_name(device), "arguments": vars(a) | {"output_dir": str(a.output_dir)},
@@ -123,9 +126,9 @@ def main(argv=None) -> int:
     gen = torch.Generator(device=device).manual_seed(a.seed)
     for case in selected:
         t, k, n = case["tokens"], case["in_features"], case["out_features"]
-        x = torch.randn(t, k, device=device, generator=gen).bfloat16()
+        x = (torch.randn(t, k, device=device, generator=gen) * a.input_scale).bfloat16()
         w = (torch.randn(n, k, device=device, generator=gen) * 0.02).bfloat16()
-        dy = torch.randn(t, n, device=device, generator=gen).bfloat16()
+        dy = (torch.randn(t, n, device=device, generator=gen) * a.input_scale).bfloat16()
         grad = torch.zeros(n, k, device=device)
         if case["operation"] == "fwd":
             control, ours, flops = (lambda: x @ w.T), (lambda: G.linear(x, w)), 2 * t * n * k
