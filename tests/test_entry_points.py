@@ -30,3 +30,31 @@ def test_tools_are_importable_modules_with_a_main(name):
     module = importlib.import_module(f"warpstate_ai_b200.{name}")
     assert callable(getattr(module, "main", None)), name
     assert (module.__doc__ or "").strip(), f"{name} says nothing about itself"
+
+
+REFERENCE = ROOT / "baseline" / "_ref"
+SAME_FLAGS = ["posttrain.py", "dpo.py", "chat.py", "ops/posttrain_chat.py", "ops/launch_training.py", "ops/transfer_artifacts.py",
+              "ops/posttrain_handoff.py", "ops/dpo_handoff.py", "ops/compare_communication_benchmarks.py",
+              "ops/analyze_communication_profile.py", "ops/evaluate_sft_snapshot.py", "ops/archive_dpo.py",
+              "ops/loss_curve_forecast.py", "ops/posttrain_preflight.py", "ops/dpo_preflight.py"]
+
+
+def _flags(script, cwd):
+    import re
+    run = subprocess.run([sys.executable, script, "--help"], capture_output=True, text=True, cwd=cwd, timeout=300)
+    assert run.returncode == 0, (script, str(cwd), run.stderr[-1500:])
+    return set(re.findall(r"(?<![\w-])--[a-z][a-z0-9-]*", run.stdout))
+
+
+def test_every_flag_of_the_reference_entry_points_exists_here():
+    """``--help`` of each script at the reference's path, here and in the installed reference: no flag of the reference
+    is missing (this framework adds some of its own)."""
+    if not (REFERENCE / "posttrain.py").exists():
+        pytest.skip("reference not installed under baseline/_ref")
+    from concurrent.futures import ThreadPoolExecutor
+    jobs = [(script, where) for script in SAME_FLAGS for where in (ROOT, REFERENCE)]
+    with ThreadPoolExecutor(max_workers=8) as pool:
+        found = dict(zip(jobs, pool.map(lambda job: _flags(*job), jobs)))
+    for script in SAME_FLAGS:
+        missing = found[(script, REFERENCE)] - found[(script, ROOT)]
+        assert not missing, (script, sorted(missing))
