@@ -7,6 +7,7 @@ renderers and collators, the chat prompt, sampling and n-gram bans, the DPO obje
 import contextlib
 import importlib
 import itertools
+import json
 import random
 import sys
 from pathlib import Path
@@ -394,3 +395,69 @@ def test_pretraining_command_line_reads_like_the_reference(ref, monkeypatch):
     assert mine(["--stage", "all"]) == theirs(["--stage", "all"]) == "refused"              # ranks train; they do not prepare data
     x, y = mine(["--stage", "train"]), theirs(["--stage", "train"])
     assert (x["rank"], x["world_size"], x["local_rank"]) == (y["rank"], y["world_size"], y["local_rank"]) == (1, 2, 1)
+
+
+# ------------------------------------------------------------------------------------------- corpus preparation
+def test_corpus_preparation_writes_the_reference_bytes(ref, tmp_path, monkeypatch):
+    """The same streamed documents through both ``prepare`` stages (a stand-in ``datasets`` module, the real tokenizer):
+    byte-identical token files, the same manifest, and each implementation accepts the other's finished directory."""
+    import types
+    from warpstate_ai_b200.data import prepare as P
+    rng = random.Random(4)
+    words = "the of river stone and light seven quiet under machine green follows window".split()
+    docs = [{"text": " ".join(rng.choice(words) for _ in range(rng.randrange(3, 40)))} for _ in range(3000)]
+    docs[5] = {"text": "   "}                                                         # blank documents are skipped by both
+    # holdout documents are rare (1 in 1000): make sure the stream has enough of them to fill the validation file
+    from itertools import count
+    held = []
+    for i in count():
+        text = f"validation candidate {i} " + " ".join(rng.choice(words) for _ in range(12))
+        if P.is_holdout(text):
+            held.append({"text": text})
+        if len(held) == 12:
+            break
+    for position, document in zip(range(7, len(docs), 211), held):
+        docs.insert(position, document)
+    assert all(P.is_holdout(d["text"]) == ref["run_40b"].is_holdout(d["text"]) for d in docs[:400])
+
+    class Stream:
+        def __init__(self):
+            self.position = 0
+
+        def __iter__(self):
+            while self.position < len(docs):
+                self.position += 1
+                yield docs[self.position - 1]
+
+        def state_dict(self):
+            return {"position": self.position}
+
+        def load_state_dict(self, state):
+            self.position = state["position"]
+
+    monkeypatch.setitem(sys.modules, "datasets", types.SimpleNamespace(__version__="fake-1", load_dataset=lambda *a, **k: Stream()))
+    monkeypatch.setitem(sys.modules, "huggingface_hub", types.SimpleNamespace(HfApi=lambda: types.SimpleNamespace(
+        dataset_info=lambda name, revision: types.SimpleNamespace(sha="0123abcd"))))
+
+    def arguments(work):
+        return types.SimpleNamespace(work_dir=work, tokenizer=TOK, dataset="corpus/name", dataset_config="cfg", revision="main",
+                                     train_tokens=20000, val_tokens=150, workers=1, documents_per_batch=64, test_small_gpu=True,
+                                     verify_data=True)
+
+    mine, theirs = arguments(tmp_path / "mine"), arguments(tmp_path / "theirs")
+    assert P.prepare(mine) is True
+    assert ref["run_40b"].prepare(theirs) is True
+    for name in ("train.bin", "val.bin"):
+        a, b = (mine.work_dir / "data" / name).read_bytes(), (theirs.work_dir / "data" / name).read_bytes()
+        assert a == b and len(a) == 2 * (20000 if name == "train.bin" else 150), name
+    m, t = (json.loads((w.work_dir / "data/manifest.json").read_text()) for w in (mine, theirs))
+    assert m["signature"] == t["signature"] and m["sha256"] == t["sha256"] and m["source_revision"] == t["source_revision"] == "0123abcd"
+    assert m["documents_read"] == t["documents_read"] and m["complete"] is t["complete"] is True and set(t) <= set(m)
+    # a finished directory of either is "already complete" to the other
+    assert ref["run_40b"].prepare(mine) is True and P.prepare(theirs) is True
+    assert ref["run_40b"].check_manifest(mine)["sha256"] == m["sha256"]
+    other_budget = arguments(tmp_path / "mine")
+    other_budget.train_tokens = 20001
+    for prepare in (P.prepare, ref["run_40b"].prepare):
+        with pytest.raises(ValueError):
+            prepare(other_budget)

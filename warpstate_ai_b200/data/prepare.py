@@ -35,7 +35,7 @@ from pathlib import Path
 
 from ..utils.io import atomic_write, digest
 
-RECIPE = "fineweb-edu-sentencepiece-uint16-v1"
+RECIPE = 1          # version of the file format below; run_40b.py:22 writes the same number, so either side reads the other's corpus
 COMMIT_TOKENS = 8_000_000
 HOLDOUT_RULE = "sha256(raw-text) modulo 1000 == 0; train excludes all holdout documents"
 SPLITS = ("train", "val")
