@@ -85,6 +85,17 @@ def test_compare_runs_pairs_updates_and_rejects_mismatches(bench_dirs, tmp_path)
     assert report["maximum_absolute_loss_difference"] == 0.0  # same seed, same data: same numbers
     assert report["maximum_relative_grad_norm_difference"] == 0.0
     assert len(report["paired_updates"]) == 2 and report["throughput_ratio"] > 0
+    assert [p["update"] for p in report["paired_updates"]] == [2, 3]     # numbered from one; the first was warm-up
+    assert report["paired_updates"][0]["ranks"][0]["grad_norm_difference"] == 0.0
+    assert len(json.loads(out.read_text())["limitations"]) == 5 and not out.with_name("cmp.json.partial").exists()
+    # several candidates after one flag, the flag repeated, and the rules on the report's path
+    many = tmp_path / "many.json"
+    assert CR.main(["--control", str(bench_dirs / "a"), "--candidate", str(bench_dirs / "b"), str(bench_dirs / "a"),
+                    "--candidate", str(bench_dirs / "b"), "--output", str(many)]) == 0
+    assert [Path(c["candidate"]["directory"]).name for c in json.loads(many.read_text())["comparisons"]] == ["b", "a", "b"]
+    for refused in (many, tmp_path / "report.txt"):
+        with pytest.raises(SystemExit):
+            CR.main(["--control", str(bench_dirs / "a"), "--candidate", str(bench_dirs / "b"), "--output", str(refused)])
     with pytest.raises(ValueError, match="unprofiled"):
         CR.load_run(bench_dirs / "profiled")
     # a run with another geometry is not comparable

@@ -20,7 +20,8 @@ def ref():
         pytest.skip("reference not installed under baseline/_ref")
     with reference_import_path():
         return {name: importlib.import_module(name) for name in
-                ("ops.analyze_communication_profile", "ops.loss_curve_forecast", "ops.checkpoint_writer")}
+                ("ops.analyze_communication_profile", "ops.loss_curve_forecast", "ops.checkpoint_writer",
+                 "ops.compare_communication_benchmarks")}
 
 
 # ------------------------------------------------------------------------------------------- trace analysis
@@ -194,3 +195,28 @@ def test_gradient_accumulation_benchmark_command_line(capsys):
     for bad in (["--accumulation-steps", "0"], ["--variants", "triton"], ["--rows", "-1"]):
         with pytest.raises(SystemExit):
             GA.arguments(bad)
+
+
+def test_run_comparison_statistics(ref):
+    """Timing statistics and the table of differences of the run comparator, on the same numbers."""
+    from warpstate_ai_b200.bench import compare_runs as CR
+    theirs = ref["ops.compare_communication_benchmarks"]
+    rng = random.Random(11)
+    for count in (1, 4, 5, 9, 10, 37):
+        seconds = [rng.uniform(0.7, 0.9) for _ in range(count)]
+        assert CR.timing_statistics(seconds, 131072) == theirs.timing_statistics(seconds, 131072)
+    left = {"a": 1, "b": [1, 2], "c": {"x": 1}, "only_left": None, "same": "s"}
+    right = {"a": 2, "b": [1, 2], "c": {"x": 2}, "only_right": 0, "same": "s"}
+    assert CR.differences(left, right) == theirs.differences(left, right)
+    assert CR.differences(left, left) == theirs.differences(left, left) == {}
+    for bad in (float("nan"), float("inf"), True, "1", None):
+        with pytest.raises(ValueError):
+            CR.finite(bad, "x")
+        with pytest.raises(ValueError):
+            theirs.finite_number(bad, "x")
+    for value in (0, -1.5):
+        assert CR.finite(value, "x") == theirs.finite_number(value, "x")
+        with pytest.raises(ValueError):
+            CR.finite(value, "x", positive=True)
+        with pytest.raises(ValueError):
+            theirs.finite_number(value, "x", positive=True)

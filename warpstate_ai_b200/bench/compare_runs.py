@@ -24,6 +24,13 @@ from pathlib import Path
 
 MUST_MATCH = ("world_size", "geometry", "precision", "optimizer_state", "warmup_updates", "measured_updates")
 IDENTITIES = ("checkpoint", "data")
+LIMITATIONS = [
+    "Checkpoint and data identities are recorded path, size and modification time, not content hashes.",
+    "Elapsed time of an update is the slowest rank's; ranks are never added up.",
+    "Consecutive update pairs are neither randomised trials nor independent samples: no confidence interval follows.",
+    "Recorded differences (gradient path, optimizer, sources, library, device) are disclosed, not judged.",
+    "No threshold names a winner: read the drift, the numerical differences and the peak memory.",
+]
 MAY_DIFFER = ("grad_sync", "optimizer", "source_sha256", "torch", "device")
 
 
@@ -74,8 +81,13 @@ def load_run(directory: Path) -> dict:
 
 
 def differences(left: dict, right: dict) -> dict:
-    return {k: {"control": left.get(k), "candidate": right.get(k)} for k in sorted(set(left) | set(right))
-            if left.get(k) != right.get(k)}
+    """Keys whose values differ, or that only one side recorded (an absent key is not the same as a recorded ``None``)."""
+    table = {}
+    for key in sorted(set(left) | set(right)):
+        if (key in left) != (key in right) or left.get(key) != right.get(key):
+            table[key] = {"control": left.get(key), "candidate": right.get(key),
+                          "control_recorded": key in left, "candidate_recorded": key in right}
+    return table
 
 
 def timing_statistics(seconds: list, tokens: int) -> dict:
@@ -105,11 +117,11 @@ def compare(control: dict, candidate: dict) -> dict:
             x, y = control["ranks"][rank][index], candidate["ranks"][rank][index]
             per_rank.append({"rank": rank, "control_loss": x["loss"], "candidate_loss": y["loss"],
                              "loss_difference": y["loss"] - x["loss"], "control_grad_norm": x["grad_norm"],
-                             "candidate_grad_norm": y["grad_norm"],
+                             "candidate_grad_norm": y["grad_norm"], "grad_norm_difference": y["grad_norm"] - x["grad_norm"],
                              "grad_norm_relative_difference": abs(y["grad_norm"] - x["grad_norm"]) / max(abs(x["grad_norm"]), 1e-30)})
         cs = max(rows[index]["seconds"] for rows in control["ranks"].values())
         ds = max(rows[index]["seconds"] for rows in candidate["ranks"].values())
-        paired.append({"update": index, "control_seconds": cs, "candidate_seconds": ds, "throughput_ratio": cs / ds,
+        paired.append({"update": index + 1, "control_seconds": cs, "candidate_seconds": ds, "throughput_ratio": cs / ds,
                        "ranks": per_rank})
     ct = timing_statistics([p["control_seconds"] for p in paired], tokens)
     dt = timing_statistics([p["candidate_seconds"] for p in paired], tokens)
@@ -124,26 +136,30 @@ def compare(control: dict, candidate: dict) -> dict:
             "maximum_absolute_loss_difference": max(abs(r["loss_difference"]) for p in paired for r in p["ranks"]),
             "maximum_relative_grad_norm_difference": max(r["grad_norm_relative_difference"] for p in paired for r in p["ranks"]),
             "paired_updates": paired, "rank_peak_memory": memory,
-            "recorded_differences": differences({k: a.get(k) for k in MAY_DIFFER}, {k: b.get(k) for k in MAY_DIFFER})}
+            "recorded_differences": differences({k: a[k] for k in MAY_DIFFER if k in a}, {k: b[k] for k in MAY_DIFFER if k in b})}
 
 
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     p.add_argument("--control", required=True, type=Path)
-    p.add_argument("--candidate", required=True, type=Path, action="append")
+    p.add_argument("--candidate", required=True, type=Path, nargs="+", action="append",
+                   help="one or more run directories; the flag may be repeated")
     p.add_argument("--output", required=True, type=Path)
     a = p.parse_args(argv)
-    if a.output.exists():
-        p.error("output already exists; choose a new report path")
+    if a.output.suffix != ".json" or a.output.exists():
+        p.error("the report is a new .json file; this path exists already or has another suffix")
     control = load_run(a.control)
     report = {"format": "warpstate-benchmark-comparison-v1", "control": {k: control[k] for k in ("directory", "input_files")},
               "comparisons": []}
-    for directory in a.candidate:
+    for directory in (path for group in a.candidate for path in group):
         candidate = load_run(directory)
         report["comparisons"].append({"candidate": {k: candidate[k] for k in ("directory", "input_files")},
                                       **compare(control, candidate)})
+    report["limitations"] = LIMITATIONS
     a.output.parent.mkdir(parents=True, exist_ok=True)
-    a.output.write_text(json.dumps(report, indent=2, allow_nan=False) + "\n")
+    partial = a.output.with_name(a.output.name + ".partial")
+    partial.write_text(json.dumps(report, indent=2, allow_nan=False) + "\n")
+    partial.replace(a.output)                                                # a reader never sees half a report
     print(json.dumps({"output": str(a.output), "throughput_ratios": [c["throughput_ratio"] for c in report["comparisons"]]}))
     return 0
 
