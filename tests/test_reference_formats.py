@@ -373,3 +373,102 @@ def test_the_sealed_base_model_is_what_the_reference_guardian_expects(ref, tmp_p
     assert all(torch.equal(exported["model"][k], v) for k, v in checkpoint["model"].items()) and "optimizer" not in exported
     with pytest.raises(ValueError):
         theirs.verify_archive(paths["archive_dir"], dict(boundary, tokens_seen=1))
+
+
+# ------------------------------------------------------------------------------------------- the same run, both trainers
+def metric_rows(path):
+    rows = [json.loads(line) for line in path.read_text().splitlines()]
+    for row in rows:
+        for key in [k for k in row if k == "timestamp" or "second" in k or k == "checkpoint"]:
+            row.pop(key)
+    return rows
+
+
+def assert_same_course(mine, theirs, exact, close, rel):
+    """Two metric logs tell the same story: the same events in the same order, counters and schedule exactly equal,
+    measured values within the difference between FP32 and BF16-autocast arithmetic on the host."""
+    assert [row["event"] for row in mine] == [row["event"] for row in theirs]
+    for a, b in zip(mine, theirs):
+        assert set(b) <= set(a), (set(b) - set(a), a["event"])
+        for key in b:
+            if key in close:
+                assert a[key] == pytest.approx(b[key], rel=rel[key] if isinstance(rel, dict) else rel), (key, a, b)
+            else:
+                assert key in exact or isinstance(b[key], (str, bool, int)), key
+                assert a[key] == b[key], (key, a, b)
+
+
+@pytest.fixture
+def host_settings():
+    """The trainers set process-wide torch switches; a test that runs them in-process puts them back."""
+    threads, deterministic = torch.get_num_threads(), torch.are_deterministic_algorithms_enabled()
+    yield
+    torch.set_num_threads(threads)
+    torch.use_deterministic_algorithms(deterministic)
+
+
+def test_the_same_sft_run_through_both_trainers(ref, tmp_path, monkeypatch, host_settings):
+    """One model export, one prepared data directory, one plan (two epochs, warm-up, a last update that is not full):
+    this framework's SFT trainer and the reference's, each on the host, log the same course of training, and end with the
+    same weights.  (Prepared data names the hash of the renderer's source file, by design of both; the reference's copy
+    of the directory differs in that one field.)"""
+    import argparse
+    from warpstate_ai_b200 import WarpStateConfig, WarpStateLM
+    from warpstate_ai_b200.ckpt.formats import export_chat_snapshot
+    from warpstate_ai_b200.data.prepare_posttrain import prepare
+    from warpstate_ai_b200.train import sft as SFT
+    from warpstate_ai_b200.utils.io import digest
+    root = tmp_path / "ws"
+    root.mkdir()
+    monkeypatch.setenv("WARPSTATE_WORKSPACE", str(root))
+    tok = root / "tokenizer.model"
+    tok.write_bytes(TOK.read_bytes())
+    torch.manual_seed(0)
+    cfg = WarpStateConfig(vocab_size=32768, d_model=16, n_heads=2, n_cores=1, logical_depth=2, ffn_hidden=24, chunk_size=8,
+                          gradient_checkpointing=False, parallel_memory=True)
+    base = {"config": vars(cfg).copy(), "model": WarpStateLM(cfg).state_dict(), "step": 7, "tokens_seen": 700, "val_loss": 9.9}
+    export_chat_snapshot(base, root / "base", tok, {"path": "test"})
+    rows = [{"messages": [{"role": "user", "content": f"What is {i} plus {i + 1}?" + " please" * (i % 4)},
+                          {"role": "assistant", "content": f"It is {2 * i + 1}." + " Indeed." * (i % 3)}]} for i in range(23)]
+    prepare(root / "data", tok, 64, sft_rows=rows, val_modulus=5)
+    plan = {"format": "warpstate-posttrain-plan-v1", "stage": "sft", "base": {"step": 7, "tokens_seen": 700, "tokenizer_sha256": digest(tok)},
+            "training": {"sequence_length": 64, "micro_batch": 2, "grad_accum": 2, "lr": 1e-3, "min_lr": 1e-4, "warmup_ratio": 0.25,
+                         "epochs": 2, "eval_every": 2, "save_every": 3, "eval_batches": 1, "workers": 1, "weight_decay": 0.05,
+                         "compile_core": False, "loss_mode": "full", "bf16_residuals": False}}
+    (root / "plan.json").write_text(json.dumps(plan))
+    monkeypatch.setattr(SFT, "STOP", False)
+    SFT.main(["--config", str(root / "plan.json"), "--data-dir", str(root / "data"), "--weights", str(root / "base/model.pt"),
+              "--tokenizer", str(tok), "--device", "cpu", "--work-dir", str(root / "mine/run")])
+    theirs = ref["posttrain"]
+    data = root / "their-data"
+    data.mkdir()
+    for file in (root / "data").iterdir():
+        (data / file.name).write_bytes(file.read_bytes())
+    with reference_import_path():
+        manifest = json.loads((data / "manifest.json").read_text())
+        manifest["renderer_sha256"] = importlib.import_module("ops.posttrain_data").renderer_sha256()
+        (data / "manifest.json").write_text(json.dumps(manifest))
+        monkeypatch.setattr(theirs, "WORKSPACE", root)
+        monkeypatch.setattr(theirs, "STOP", False)
+        theirs.train(argparse.Namespace(config=root / "plan.json", work_dir=root / "theirs/run", data_dir=data,
+                                        weights=root / "base/model.pt", tokenizer=tok, max_steps=None, stop_file=None, device="cpu"))
+    a, b = metric_rows(root / "mine/run/metrics.jsonl"), metric_rows(root / "theirs/run/metrics.jsonl")
+    assert sum(row["event"] == "train" for row in b) >= 8 and {row.get("update_samples") for row in b} >= {4, 1}
+    assert_same_course(a, b, exact={"lr"}, close={"loss", "val_loss", "val_perplexity", "grad_norm"},
+                       rel={"loss": 1e-4, "val_loss": 1e-4, "val_perplexity": 2e-3, "grad_norm": 2e-2})
+    mine_end, their_end = (torch.load(root / side / "run/latest.pt", weights_only=False) for side in ("mine", "theirs"))
+    for key in ("step", "sample_cursor", "tokens_seen", "assistant_tokens_seen", "completed", "total_steps", "val_step", "format"):
+        assert mine_end[key] == their_end[key], key
+    assert mine_end["val_loss"] == pytest.approx(their_end["val_loss"], rel=1e-4)
+    # Adam divides by the gradient's own magnitude, so where a gradient is rounding noise (vocabulary rows that no
+    # example touches) the two arithmetics may step in different directions; judged against how far training moved them
+    for name, tensor in their_end["model"].items():
+        moved = (tensor - base["model"][name]).abs().mean()
+        apart = (mine_end["model"][name] - tensor).abs().mean()
+        assert moved > 1e-3 and apart < 0.01 * moved, (name, float(moved), float(apart))
+    for name in ("completion.json", "evaluation.json", "settings.json"):
+        x, y = (json.loads((root / side / "run" / name).read_text()) for side in ("mine", "theirs"))
+        assert set(y) <= set(x), (name, set(y) - set(x))
+    done = [json.loads((root / side / "run/completion.json").read_text()) for side in ("mine", "theirs")]
+    for key in ("format", "stage", "completed", "paused_for_evaluation", "step", "total_steps", "base_step", "tokens_seen", "assistant_tokens_seen"):
+        assert done[0][key] == done[1][key], key
