@@ -472,3 +472,84 @@ def test_the_same_sft_run_through_both_trainers(ref, tmp_path, monkeypatch, host
     done = [json.loads((root / side / "run/completion.json").read_text()) for side in ("mine", "theirs")]
     for key in ("format", "stage", "completed", "paused_for_evaluation", "step", "total_steps", "base_step", "tokens_seen", "assistant_tokens_seen"):
         assert done[0][key] == done[1][key], key
+
+
+def test_the_same_dpo_run_through_both_trainers(ref, tmp_path, monkeypatch, host_settings):
+    """One SFT export, one directory of preference pairs, one plan: both DPO trainers on the host score the frozen
+    reference model alike (the cache files hold the same numbers), then log the same course of training: the same pairs
+    per update (updates of three pairs included), the same schedule and counters, objective values within BF16 noise."""
+    import argparse
+    from warpstate_ai_b200 import WarpStateConfig, WarpStateLM
+    from warpstate_ai_b200.ckpt.formats import export_chat_snapshot
+    from warpstate_ai_b200.data.prepare_posttrain import prepare
+    from warpstate_ai_b200.train import dpo as DPO
+    from warpstate_ai_b200.utils.io import digest
+    root = tmp_path / "ws"
+    root.mkdir()
+    monkeypatch.setenv("WARPSTATE_WORKSPACE", str(root))
+    tok = root / "tokenizer.model"
+    tok.write_bytes(TOK.read_bytes())
+    torch.manual_seed(0)
+    cfg = WarpStateConfig(vocab_size=32768, d_model=16, n_heads=2, n_cores=1, logical_depth=2, ffn_hidden=24, chunk_size=8,
+                          gradient_checkpointing=False, parallel_memory=True)
+    model = WarpStateLM(cfg)
+    with torch.no_grad():
+        model.embed.weight.normal_(0, 0.3)
+    sft = {"config": vars(cfg).copy(), "model": model.state_dict(), "step": 4, "tokens_seen": 400, "assistant_tokens_seen": 90,
+           "val_loss": 9.0, "origin": {"step": 7, "tokens_seen": 700}}
+    export_chat_snapshot(sft, root / "sft-export", tok, {"path": "test"}, stage="sft")
+    pairs = [{"prompt": [{"role": "user", "content": f"What follows {i}?" + " now" * (i % 3)}],
+              "chosen": [{"role": "assistant", "content": str(i + 1)}],
+              "rejected": [{"role": "assistant", "content": f"maybe {i + 3} or so" + " hm" * (i % 4)}]} for i in range(23)]
+    prepare(root / "data", tok, 64, dpo_rows=pairs, val_modulus=5)
+    plan = {"format": "warpstate-dpo-plan-v1", "stage": "dpo",
+            "sft": {"step": 4, "tokens_seen": 400, "base_step": 7, "base_tokens_seen": 700, "tokenizer_sha256": digest(tok)},
+            "training": {"sequence_length": 64, "micro_batch": 2, "grad_accum": 2, "lr": 1e-3, "min_lr": 1e-4, "warmup_ratio": 0.25,
+                         "epochs": 2, "eval_every": 2, "save_every": 3, "eval_batches": 1, "workers": 1, "beta": 0.5,
+                         "head_chunk_size": 16, "compile_core": False, "bf16_residuals": False}}
+    (root / "plan.json").write_text(json.dumps(plan))
+    monkeypatch.setattr(DPO, "STOP", False)
+    DPO.main(["--config", str(root / "plan.json"), "--data-dir", str(root / "data"), "--weights", str(root / "sft-export/model.pt"),
+              "--tokenizer", str(tok), "--device", "cpu", "--reference-cache-dir", str(root / "mine/reference-cache"),
+              "--work-dir", str(root / "mine/run")])
+    theirs = ref["dpo"]
+    data = root / "their-data"
+    data.mkdir()
+    for file in (root / "data").iterdir():
+        (data / file.name).write_bytes(file.read_bytes())
+    (root / "theirs/reference-cache").mkdir(parents=True)
+    with reference_import_path():
+        manifest = json.loads((data / "manifest.json").read_text())
+        manifest["renderer_sha256"] = importlib.import_module("ops.posttrain_data").renderer_sha256()
+        (data / "manifest.json").write_text(json.dumps(manifest))
+        for module in (theirs, ref["posttrain"]):
+            monkeypatch.setattr(module, "WORKSPACE", root)
+            monkeypatch.setattr(module, "STOP", False)
+        theirs.train(argparse.Namespace(config=root / "plan.json", work_dir=root / "theirs/run", data_dir=data,
+                                        weights=root / "sft-export/model.pt", tokenizer=tok, max_steps=None, stop_file=root / "theirs/stop",
+                                        device="cpu", reference_cache_dir=root / "theirs/reference-cache", reference_only=False))
+    for name in ("train.npy", "val.npy"):
+        x, y = (np.load(root / side / "reference-cache" / name) for side in ("mine", "theirs"))
+        assert x.shape == y.shape and x.dtype == y.dtype and np.allclose(x, y, rtol=1e-3, atol=5e-2), name
+    a, b = metric_rows(root / "mine/run/metrics.jsonl"), metric_rows(root / "theirs/run/metrics.jsonl")
+    assert sum(row["event"] == "train" for row in b) == 8 and {row.get("update_samples") for row in b} >= {4, 3}
+    measured = {"loss": 3e-3, "val_loss": 3e-3, "chosen_nll": 1e-3, "grad_norm": 2e-2}
+    for row in a + b:                                           # margins start at zero: an absolute bound for them, below
+        row["margin"] = row.pop("reward_margin", None)
+    assert_same_course([{k: v for k, v in row.items() if k != "margin"} for row in a],
+                       [{k: v for k, v in row.items() if k != "margin"} for row in b], exact={"lr", "reward_accuracy"},
+                       close=set(measured), rel=measured)
+    for x, y in zip(a, b):
+        assert (x["margin"] is None) == (y["margin"] is None)
+        assert x["margin"] is None or abs(x["margin"] - y["margin"]) < 3e-3
+    assert b[-2]["margin"] > 0.05 and b[-2]["val_loss"] < 0.66          # the run did learn the preference
+    mine_end, their_end = (torch.load(root / side / "run/latest.pt", weights_only=False) for side in ("mine", "theirs"))
+    for key in ("step", "sample_cursor", "tokens_seen", "response_tokens_seen", "completed", "total_steps", "format"):
+        assert mine_end[key] == their_end[key], key
+    for name, tensor in their_end["model"].items():
+        moved = (tensor - sft["model"][name]).abs().mean()
+        apart = (mine_end["model"][name] - tensor).abs().mean()
+        assert moved > 1e-3 and apart < 0.05 * moved, (name, float(moved), float(apart))
+    for name in ("completion.json", "evaluation.json", "settings.json"):
+        x, y = (json.loads((root / side / "run" / name).read_text()) for side in ("mine", "theirs"))
+        assert set(y) <= set(x), (name, set(y) - set(x))
