@@ -220,3 +220,42 @@ def test_run_comparison_statistics(ref):
             CR.finite(value, "x", positive=True)
         with pytest.raises(ValueError):
             theirs.finite_number(value, "x", positive=True)
+
+
+def test_transfer_manifest_and_confinement(tmp_path, monkeypatch):
+    """The chunk manifest of a file (what a resumed transfer is checked against) and the rule that confines both
+    endpoints to the workspace, against the reference's transfer tool."""
+    from warpstate_ai_b200.orchestration import transfer_agent as TA
+    if not (REF / "ops" / "transfer_artifacts.py").exists():
+        pytest.skip("reference not installed under baseline/_ref")
+    with reference_import_path():
+        theirs = importlib.import_module("ops.transfer_artifacts")
+    rng = random.Random(3)
+    monkeypatch.setenv("WARPSTATE_WORKSPACE", str(tmp_path))
+    for size, chunk in ((0, 1024), (1, 1024), (1024, 1024), (1025, 1024), (5 * 1024 * 1024 + 17, 2 * 1024 * 1024), (4096, 4096 * 4)):
+        path = tmp_path / f"blob-{size}-{chunk}"
+        path.write_bytes(rng.randbytes(size))
+        expected, identity = theirs.source_manifest(path, chunk)
+        with path.open("rb") as stream:
+            assert TA.chunk_manifest(stream, chunk) == expected
+        assert TA.file_identity(path.stat()) == list(identity)
+        for offset, count in ((0, None), (0, min(size, 7)), (min(size, 1000), None)):
+            import hashlib
+            data = path.read_bytes()[offset:None if count is None else offset + count]
+            assert TA.sha_range(path, offset, count) == hashlib.sha256(data).hexdigest()
+    root = tmp_path / "workspace"
+    (root / "inside").mkdir(parents=True)
+    (root / "inside/file").write_text("x")
+    (tmp_path / "outside").mkdir()
+    (root / "link").symlink_to(tmp_path / "outside")
+    monkeypatch.setattr(theirs, "ROOT", root)
+    monkeypatch.setenv("WARPSTATE_WORKSPACE", str(root))
+    for candidate in (root / "inside/file", root / "inside/new", root, tmp_path / "outside/x", root / "inside/../../outside/x",
+                      root / "link/x", root / "link"):
+        verdicts = []
+        for rule in (theirs.workspace_path, TA.confined):
+            try:
+                verdicts.append(str(rule(str(candidate))))
+            except ValueError:
+                verdicts.append("refused")
+        assert verdicts[0] == verdicts[1], candidate
