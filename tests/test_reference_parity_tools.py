@@ -2,6 +2,8 @@
 ``baseline/_ref`` (skipped where it is not installed): chrome-trace overlap analysis, loss-curve fits and the frozen
 host snapshot of a training state."""
 import copy
+import os
+from pathlib import Path
 import importlib
 import json
 import random
@@ -259,3 +261,102 @@ def test_transfer_manifest_and_confinement(tmp_path, monkeypatch):
             except ValueError:
                 verdicts.append("refused")
         assert verdicts[0] == verdicts[1], candidate
+
+
+# ------------------------------------------------------------------------------------------- launcher
+WORKER = """
+import os, signal, subprocess, sys, time
+mode = os.environ["MODE"]
+if len(sys.argv) > 1:                                   # a worker in a session of its own, as torchrun starts them
+    signal.signal(signal.SIGTERM, signal.SIG_IGN)
+    while True:
+        if mode == "graceful" and os.path.exists(os.environ["STOP_FILE"]):
+            open(os.environ["MARK"], "w").write("saved")
+            sys.exit(0)
+        time.sleep(0.05)
+open(os.environ["MARK"] + ".started", "w").write("x")
+if mode == "exit3":
+    sys.exit(3)
+worker = subprocess.Popen([sys.executable, __file__, "worker"], start_new_session=True)
+open(os.environ["PIDFILE"], "w").write(str(worker.pid))
+if mode == "stubborn":
+    signal.signal(signal.SIGTERM, signal.SIG_IGN)
+sys.exit(worker.wait())
+"""
+
+
+@pytest.fixture
+def launchers(tmp_path, monkeypatch):
+    from warpstate_ai_b200.orchestration import launcher as mine
+    if not (REF / "ops" / "launch_training.py").exists():
+        pytest.skip("reference not installed under baseline/_ref")
+    with reference_import_path():
+        theirs = importlib.import_module("ops.launch_training")
+    monkeypatch.setattr(theirs, "WORKSPACE", tmp_path.resolve())
+    monkeypatch.setenv("WARPSTATE_WORKSPACE", str(tmp_path))
+    return mine, theirs
+
+
+@pytest.mark.parametrize("mode", ["exit3", "already-stopped", "graceful", "terminated", "stubborn"])
+def test_both_supervisors_end_a_job_the_same_way(launchers, tmp_path, mode):
+    """A job that exits by itself, one that is never started because a stop request is pending, one whose workers save
+    and leave when asked, one that has to be terminated, and one that has to be killed, workers included."""
+    import os
+    import signal
+    import sys
+    import threading
+    import time
+    from pathlib import Path
+    script = tmp_path / "job.py"
+    script.write_text(WORKER)
+    outcomes = []
+    for index, module in enumerate(launchers):
+        place = tmp_path / f"run{index}"
+        (place / "control").mkdir(parents=True)
+        stop = place / "control/training-stop-request"
+        environment = dict(os.environ, MODE=mode, STOP_FILE=str(stop), MARK=str(place / "mark"), PIDFILE=str(place / "pid"))
+        if mode == "already-stopped":
+            stop.write_text("")
+
+        def trigger(place=place):
+            for _ in range(200):
+                if (place / "pid").exists():
+                    break
+                time.sleep(0.05)
+            time.sleep(0.3)
+            os.kill(os.getpid(), signal.SIGUSR1)
+
+        if mode in ("graceful", "terminated", "stubborn"):
+            threading.Thread(target=trigger, daemon=True).start()
+        code = module.supervise([sys.executable, str(script)], stop, environment, grace_seconds=0.6, terminate_seconds=0.6)
+        time.sleep(0.2)
+        worker_alive = False
+        if (place / "pid").exists():
+            pid = int((place / "pid").read_text())
+            status = Path(f"/proc/{pid}/stat")
+            worker_alive = status.exists() and status.read_text().rsplit(")", 1)[1].split()[0] != "Z"
+        outcomes.append({"code": code, "started": (place / "mark.started").exists(), "saved": (place / "mark").exists(),
+                         "stop_file": stop.exists(), "worker_alive": worker_alive})
+    assert outcomes[0] == outcomes[1], outcomes
+    expected = {"exit3": (3, True, False, False), "already-stopped": (0, False, False, True), "graceful": (0, True, True, True),
+                "terminated": (-signal.SIGTERM, True, False, True), "stubborn": (-signal.SIGKILL, True, False, True)}[mode]
+    assert tuple(outcomes[0][key] for key in ("code", "started", "saved", "stop_file")) == expected
+    assert outcomes[0]["worker_alive"] is False
+
+
+def test_both_launchers_give_the_job_the_same_environment(launchers, tmp_path, monkeypatch):
+    mine, theirs = launchers
+    monkeypatch.setenv("PIP_CACHE_DIR", "/somewhere/else")
+    work = tmp_path / "job/work"
+    a, b = mine.training_environment(work), theirs.training_environment(work)
+    assert {k: a.get(k) for k in b} == b and a["PIP_CACHE_DIR"] == str(tmp_path / ".cache/pip")
+    assert all(Path(a[name]).is_dir() for name in ("TMPDIR", "HF_HOME", "TORCH_EXTENSIONS_DIR", "TRITON_CACHE_DIR"))
+    assert mine.process_info(os.getpid()) == theirs.process_info(os.getpid()) and mine.process_info(2 ** 22 + 5) is None
+    for place in (tmp_path / "x/../y", tmp_path, "/etc/passwd", tmp_path / ".." / "escape"):
+        verdicts = []
+        for rule in (mine.workspace_path, theirs.workspace_path):
+            try:
+                verdicts.append(str(rule(place)))
+            except ValueError:
+                verdicts.append("refused")
+        assert verdicts[0] == verdicts[1], place
