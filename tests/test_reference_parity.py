@@ -461,3 +461,77 @@ def test_corpus_preparation_writes_the_reference_bytes(ref, tmp_path, monkeypatc
     for prepare in (P.prepare, ref["run_40b"].prepare):
         with pytest.raises(ValueError):
             prepare(other_budget)
+
+
+# ------------------------------------------------------------------------------------------- prompt suites, interactive loop
+SUITES = [
+    [{"prompt": "one"}, {"prompt": "two", "id": "b", "system": "Be brief."}], {"prompts": [{"prompt": "x", "id": 4}, {"prompt": "y", "id": "4"}]},
+    {"prompts": [{"prompt": "x", "note": "kept"}]}, [{"prompt": "a", "id": "1"}, {"prompt": "b"}],
+    # refused by both
+    [], {}, {"prompts": []}, {"prompts": "x"}, "text", 5, [{"prompt": ""}], [{"prompt": "  \n"}], [{"prompt": 3}], ["bare"], [{"question": "x"}],
+    [{"prompt": "a", "id": "k"}, {"prompt": "b", "id": "k"}], [{"prompt": "a", "id": 1.5}], [{"prompt": "a", "id": None}], [{"prompt": "a", "id": ["l"]}],
+    [{"prompt": "a"}, {"prompt": "b", "id": "0"}],
+]
+
+
+@pytest.mark.parametrize("document", SUITES, ids=[str(i) for i in range(len(SUITES))])
+def test_prompt_suites_are_read_alike(tmp_path, document):
+    import json
+    from warpstate_ai_b200.serve import posttrain_chat as PC
+    if not (REF / "ops" / "posttrain_chat.py").exists():
+        pytest.skip("reference not installed under baseline/_ref")
+    with reference_import_path():
+        theirs = importlib.import_module("ops.posttrain_chat")
+    path = tmp_path / "suite.json"
+    path.write_text(json.dumps(document))
+    verdicts = []
+    for read in (lambda p: PC.PromptSuite.read(p).rows, theirs.read_prompts):
+        try:
+            verdicts.append(read(path))
+        except ValueError:
+            verdicts.append("refused")
+    assert verdicts[0] == verdicts[1]
+
+
+def test_interactive_conversations_ask_the_model_the_same_things(monkeypatch, capsys):
+    """The same typed lines (cancellations, blank lines, a prompt that is too long, a blank reply, /reset, /quit and the
+    end of input among them) lead both interactive loops to the same sequence of model calls."""
+    import builtins
+    from warpstate_ai_b200.serve import posttrain_chat as PC
+    if not (REF / "ops" / "posttrain_chat.py").exists():
+        pytest.skip("reference not installed under baseline/_ref")
+    with reference_import_path():
+        theirs = importlib.import_module("ops.posttrain_chat")
+    typed = ["hello", KeyboardInterrupt, "", "interrupt me", "too long", "say nothing", "  again  ", "/reset", "fresh", "more",
+             "/exit", "unreachable"]
+    transcripts = []
+    for side in ("mine", "theirs", "mine-eof", "theirs-eof"):
+        asked = []
+
+        def answer(messages, seed):
+            asked.append(([dict(m) for m in messages], seed))
+            text = messages[-1]["content"]
+            if text == "interrupt me":
+                raise KeyboardInterrupt
+            if text == "too long":
+                raise ValueError("the context limit is 2048")
+            return {"response": "   " if text == "say nothing" else f"reply to {text}"}
+
+        script = iter(typed[:3] if side.endswith("eof") else typed)
+
+        def fake_input(prompt="", script=script):
+            item = next(script, EOFError)
+            if isinstance(item, type) and issubclass(item, BaseException):
+                raise item
+            return item
+        monkeypatch.setattr(builtins, "input", fake_input)
+        if side.startswith("mine"):
+            assert PC.Conversation(answer, "Be kind.", seed=3).loop() == 0
+        else:
+            assert theirs.interactive_chat(lambda conversation, seed: answer(conversation, seed),
+                                           lambda prompt: PC.conversation(prompt, "Be kind."), seed=3) == 0
+        transcripts.append(asked)
+        shown = capsys.readouterr().out
+        assert shown.count("Cancelled.") == (1 if side.endswith("eof") else 2)
+    assert transcripts[0] == transcripts[1] and len(transcripts[0]) == 7
+    assert transcripts[2] == transcripts[3] and len(transcripts[2]) == 1
