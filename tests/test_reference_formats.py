@@ -553,3 +553,52 @@ def test_the_same_dpo_run_through_both_trainers(ref, tmp_path, monkeypatch, host
     for name in ("completion.json", "evaluation.json", "settings.json"):
         x, y = (json.loads((root / side / "run" / name).read_text()) for side in ("mine", "theirs"))
         assert set(y) <= set(x), (name, set(y) - set(x))
+
+
+# ------------------------------------------------------------------------------------------- locks
+def test_locks_of_either_implementation_exclude_the_other(ref, tmp_path, monkeypatch):
+    """A mixed installation stays safe: the pretraining lock and the shared pipeline lock are the same advisory locks on
+    the same files, so a job of one implementation keeps out a job of the other."""
+    from warpstate_ai_b200.train import stage as S
+    from warpstate_ai_b200.utils.io import LockHeld, process_lock
+    with reference_import_path():
+        their_lock = importlib.import_module("run_40b").process_lock
+    theirs = ref["posttrain"]
+    monkeypatch.setattr(theirs, "WORKSPACE", tmp_path.resolve())
+    monkeypatch.setenv("WARPSTATE_WORKSPACE", str(tmp_path))
+    base = tmp_path / "base"
+    base.mkdir()
+    lock = base / "pipeline.lock"
+    plan = {"handoff": {"base_work_dir": "base"}}
+    with process_lock(lock):                                     # pretraining of this framework runs
+        with pytest.raises(BlockingIOError):
+            with their_lock(lock):
+                pass
+        with pytest.raises(RuntimeError):
+            with theirs.base_pipeline_lock(plan):
+                pass
+    with their_lock(lock):                                       # the reference's pretraining runs
+        with pytest.raises(LockHeld):
+            with process_lock(lock):
+                pass
+        with pytest.raises(RuntimeError):
+            with S.base_pipeline_lock(plan):
+                pass
+    with theirs.base_pipeline_lock(plan), S.base_pipeline_lock(plan):      # post-training ranks of both share it
+        with pytest.raises(LockHeld):
+            with process_lock(lock):
+                pass
+        with pytest.raises(BlockingIOError):
+            with their_lock(lock):
+                pass
+    with process_lock(lock), pytest.raises(LockHeld):
+        with process_lock(lock):
+            pass
+    for bad in ({"handoff": {"base_work_dir": "missing"}}, {"handoff": {"base_work_dir": "../outside"}}, {"handoff": {"base_work_dir": "."}}):
+        for implementation in (theirs.base_pipeline_lock, S.base_pipeline_lock):
+            with pytest.raises(ValueError):
+                with implementation(bad):
+                    pass
+    for implementation in (theirs.base_pipeline_lock, S.base_pipeline_lock):
+        with implementation({}):                                 # no base job named: nothing to hold
+            pass
