@@ -78,6 +78,26 @@ def test_train_bench_records(bench_dirs):
     assert {"forward_backward", "sync_clip_step", "read_back"} <= set(stalls["host_stage_seconds"])
 
 
+def test_train_bench_records_the_reference_execution_flags_it_ignores(tmp_path):
+    common = ["--model", "smoke", "--device", "cpu", "--micro-batch", "2", "--seq-len", "128", "--global-tokens-per-update", "256",
+              "--warmup-updates", "0", "--measured-updates", "1"]
+    assert TB.main(common + ["--output-dir", str(tmp_path / "a"), "--gradient-mode", "compiled-autograd-overlap", "--compile-cores",
+                             "--overlap-memory-budget", "0.1", "--blas-backend", "cublaslt", "--cudagraph-diagnostics",
+                             "--no-autocast-cache", "--matmul-plan", "plan.json", "--ddp-bucket-cap-mb", "128", "--bf16-residuals"]) == 0
+    summary = json.loads((tmp_path / "a/summary.json").read_text())
+    assert summary["reference_execution_flags"] == {
+        "--gradient-mode": "compiled-autograd-overlap", "--compile-cores": True, "--overlap-memory-budget": 0.1, "--blas-backend": "cublaslt",
+        "--cudagraph-diagnostics": True, "--autocast-cache": False, "--matmul-plan": "plan.json"}
+    assert summary["bucket_cap_mb"] == 128 and summary["precision"]["residual_stream"] == "bf16"
+    assert TB.main(common + ["--output-dir", str(tmp_path / "b")]) == 0
+    plain = json.loads((tmp_path / "b/summary.json").read_text())
+    assert plain["reference_execution_flags"] == {} and plain["precision"]["residual_stream"] == "fp32"
+    assert plain["updates"][0]["loss"] == pytest.approx(summary["updates"][0]["loss"], rel=1e-5)   # nothing that ran changed (host path)
+    for bad in (["--loss-chunk-size", "0"], ["--ddp-bucket-cap-mb", "-1"], ["--overlap-memory-budget", "-0.1"], ["--loss-mode", "fused"]):
+        with pytest.raises(SystemExit):
+            TB.main(common + ["--output-dir", str(tmp_path / "c"), *bad])
+
+
 def test_compare_runs_pairs_updates_and_rejects_mismatches(bench_dirs, tmp_path):
     out = tmp_path / "cmp.json"
     assert CR.main(["--control", str(bench_dirs / "a"), "--candidate", str(bench_dirs / "b"), "--output", str(out)]) == 0
@@ -163,6 +183,18 @@ def test_tuner_pairing_policy_and_loader(tmp_path):
     assert G._policy_key(False, False, 16384, 10240, 2048) == policy["entries"][0]["key"]
     G._policy.clear()
     assert TG.main(["--list-cases", "--output-dir", str(tmp_path / "x")]) == 0
+    # the SwiGLU screening is one problem, keyed like the launch `linear_swiglu` makes (one output tile per up/gate pair)
+    fused = TG.cases(16384, ["fwd", "dx", "dw"], kind="swiglu")
+    assert len(fused) == 1 and TG.policy_key(fused[0]) == "fwd:16384x7168x2048"
+    assert TG.policy_key(TG.cases(16384, ["fwd"])[2]) == "fwd:16384x14336x2048"
+    # candidates: the default sweep, one kernel of it, or exactly what --tile names
+    assert len(TG.candidates_of(None, None)) == 4 and {c["kernel"] for c in TG.candidates_of(["single"], None)} == {"single"}
+    assert TG.candidates_of(["single"], ["pair,116", "single,0"]) == [{"kernel": "pair", "sm_limit": 116}, {"kernel": "single", "sm_limit": 0}]
+    for bad in ("pair", "pair,", "triple,4", "pair,149", "pair,-1", "128,128,64,4,3"):
+        with pytest.raises(ValueError):
+            TG.candidates_of(None, [bad])
+        with pytest.raises(SystemExit):
+            TG.main(["--list-cases", "--output-dir", str(tmp_path / "x"), "--tile", bad])
 
 
 def test_profile_step_idle_gap_arithmetic():

@@ -36,7 +36,8 @@ REFERENCE = ROOT / "baseline" / "_ref"
 SAME_FLAGS = ["posttrain.py", "dpo.py", "chat.py", "ops/posttrain_chat.py", "ops/launch_training.py", "ops/transfer_artifacts.py",
               "ops/posttrain_handoff.py", "ops/dpo_handoff.py", "ops/compare_communication_benchmarks.py",
               "ops/analyze_communication_profile.py", "ops/evaluate_sft_snapshot.py", "ops/archive_dpo.py",
-              "ops/loss_curve_forecast.py", "ops/posttrain_preflight.py", "ops/dpo_preflight.py"]
+              "ops/loss_curve_forecast.py", "ops/posttrain_preflight.py", "ops/dpo_preflight.py", "ops/benchmark_training.py",
+              "ops/benchmark_gemm.py", "ops/benchmark_gradient_accumulation.py", "ops/tune_matmul.py", "ops/prepare_data.py", "run_40b.py"]
 
 
 def _flags(script, cwd):

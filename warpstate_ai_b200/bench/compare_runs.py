@@ -31,7 +31,7 @@ LIMITATIONS = [
     "Recorded differences (gradient path, optimizer, sources, library, device) are disclosed, not judged.",
     "No threshold names a winner: read the drift, the numerical differences and the peak memory.",
 ]
-MAY_DIFFER = ("grad_sync", "optimizer", "source_sha256", "torch", "device")
+MAY_DIFFER = ("grad_sync", "optimizer", "bucket_cap_mb", "reference_execution_flags", "source_sha256", "torch", "device")
 
 
 def finite(value, name: str, positive: bool = False) -> float:

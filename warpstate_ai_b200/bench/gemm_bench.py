@@ -57,6 +57,36 @@ def time_fn(fn, iters: int, flush, warmup: int = 3) -> float:
     return total / iters
 
 
+def add_library_arm_flags(ap) -> None:
+    """How the cuBLAS arm is run (the arm this library's kernel is compared with; the kernel itself has neither choice)."""
+    ap.add_argument("--blas-backend", choices=["default", "cublas", "cublaslt"], default="default",
+                    help="PyTorch's BLAS preference for the cuBLAS arm; default keeps the process's own")
+    ap.add_argument("--allow-reduced-precision-reduction", action=argparse.BooleanOptionalAction, default=True,
+                    help="let the cuBLAS arm reduce in BF16 between split-K partial sums, as PyTorch does by default")
+
+
+def apply_library_arm_flags(a) -> dict:
+    """Apply the two cuBLAS-arm settings to this process; -> what is now in force (for the record)."""
+    import torch
+    if a.blas_backend != "default":
+        torch.backends.cuda.preferred_blas_library(a.blas_backend)
+    torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = bool(a.allow_reduced_precision_reduction)
+    return {"blas_backend": a.blas_backend, "allow_bf16_reduced_precision_reduction": bool(a.allow_reduced_precision_reduction)}
+
+
+def burn_in(seconds: float) -> None:
+    """Keep the GPU busy for ``seconds`` so that the first case is not timed on cold clocks."""
+    import torch
+    if seconds <= 0:
+        return
+    a = torch.randn(8192, 8192, device="cuda").bfloat16()
+    until = time.monotonic() + seconds
+    while time.monotonic() < until:
+        for _ in range(20):
+            torch.matmul(a, a)
+        torch.cuda.synchronize()
+
+
 def arguments(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--families", nargs="+", choices=[*FAMILIES, *ALIASES], default=list(FAMILIES))
@@ -73,6 +103,7 @@ def arguments(argv=None):
     ap.add_argument("--output-dir", type=Path, help="write cases.json and results.json here")
     ap.add_argument("--out", type=str, default=None, help="write the result rows to this file")
     ap.add_argument("--list-shapes", action="store_true", help="print the cases and exit (no GPU needed)")
+    add_library_arm_flags(ap)
     a = ap.parse_args(argv)
     if a.rows < 1 or a.warmup < 0 or a.repeats < 1 or a.trials < 1 or a.burnin_seconds < 0:
         ap.error("rows, repeats and trials must be positive; warmup and burn-in must not be negative")
@@ -90,14 +121,8 @@ def main(argv=None) -> int:
     torch.cuda.set_device(args.device)
     torch.manual_seed(args.seed)
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
-    if args.burnin_seconds:
-        a = torch.randn(8192, 8192, device="cuda").bfloat16()
-        until = time.monotonic() + args.burnin_seconds
-        while time.monotonic() < until:
-            for _ in range(20):
-                torch.matmul(a, a)
-            torch.cuda.synchronize()
-        del a
+    library_arm = apply_library_arm_flags(args)
+    burn_in(args.burnin_seconds)
     rows = []
     m = args.rows
     for family in dict.fromkeys(ALIASES.get(f, f) for f in args.families):
@@ -132,7 +157,7 @@ def main(argv=None) -> int:
         (args.output_dir / "cases.json").write_text(json.dumps(cases, indent=1) + "\n")
         (args.output_dir / "results.json").write_text(json.dumps({
             "rows": rows, "arguments": {k: (str(v) if isinstance(v, Path) else v) for k, v in vars(args).items()},
-            "gpu": torch.cuda.get_device_name(args.device), "torch": torch.__version__}, indent=1) + "\n")
+            "library_arm": library_arm, "gpu": torch.cuda.get_device_name(args.device), "torch": torch.__version__}, indent=1) + "\n")
     return 0
 
 

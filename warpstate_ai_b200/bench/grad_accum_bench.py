@@ -22,7 +22,7 @@ import json
 import statistics
 from pathlib import Path
 
-from .gemm_bench import ALIASES, FAMILIES, time_fn
+from .gemm_bench import ALIASES, FAMILIES, add_library_arm_flags, apply_library_arm_flags, burn_in, time_fn
 
 VARIANTS = ("cublas_bf16_cast_add", "cublas_fp32_addmm", "fused_epilogue", "grouped_launch")
 
@@ -42,8 +42,10 @@ def arguments(argv=None):
     ap.add_argument("--device", type=int, default=0)
     ap.add_argument("--output-dir", type=Path, help="write results.json here")
     ap.add_argument("--list-shapes", action="store_true", help="print the dW problems and exit (no GPU needed)")
+    ap.add_argument("--burnin-seconds", type=float, default=0.0, help="keep the GPU busy this long before the first variant")
+    add_library_arm_flags(ap)
     a = ap.parse_args(argv)
-    if min(a.rows, a.accumulation_steps, a.repeats, a.trials) < 1 or a.warmup < 0:
+    if min(a.rows, a.accumulation_steps, a.repeats, a.trials) < 1 or a.warmup < 0 or a.burnin_seconds < 0:
         ap.error("rows, accumulation steps, repeats and trials must be positive; warmup must not be negative")
     a.families = list(dict.fromkeys(ALIASES.get(f, f) for f in a.families))
     if a.variants is None:
@@ -69,6 +71,8 @@ def main(argv=None) -> int:
     torch.cuda.set_device(device)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
     torch.manual_seed(a.seed)
+    library_arm = apply_library_arm_flags(a)
+    burn_in(a.burnin_seconds)
     problems = []
     for shape in shapes:
         dy = torch.randn(a.rows, shape["n"], device=device).bfloat16()
@@ -116,7 +120,7 @@ def main(argv=None) -> int:
     if a.output_dir is not None:
         a.output_dir.mkdir(parents=True, exist_ok=True)
         (a.output_dir / "results.json").write_text(json.dumps({
-            "rows": rows, "problems": shapes, "gpu": torch.cuda.get_device_name(device), "torch": torch.__version__}, indent=1) + "\n")
+            "rows": rows, "problems": shapes, "library_arm": library_arm, "gpu": torch.cuda.get_device_name(device), "torch": torch.__version__}, indent=1) + "\n")
     return 0
 
 

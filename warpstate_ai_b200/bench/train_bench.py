@@ -15,11 +15,13 @@ uses, and writes into ``--output-dir``:
 * with ``--diagnose-stalls``: host wall time per stage (stage / forward+backward / gradient sync /
   optimizer / read-back) and a traceback dump every 10 s while an update is in flight.
 
-    torchrun --nproc-per-node 2 -m warpstate_ai_b200.bench.train_bench --micro-batch 8 \
+    torchrun --standalone --nproc-per-node 2 -m warpstate_ai_b200.bench.train_bench --micro-batch 8 \
         --global-tokens-per-update 131072 --output-dir bench-out
 
-Same outputs and flags as the reference's ops/benchmark_training.py:28-593, minus the flags that
-select between its execution adapters (there is one execution path here).
+Same outputs and flags as the reference's ops/benchmark_training.py:28-593.  The flags that select between
+its execution adapters (compiled cores, loss and activation variants, compiled autograd and its overlap
+scheduler, BLAS preference, CUDA-graph replay counting) are accepted and recorded in ``summary.json`` under
+``reference_execution_flags``; there is one execution path here, so they change nothing that runs.
 """
 from __future__ import annotations
 
@@ -58,7 +60,35 @@ def arguments(argv=None):
     p.add_argument("--grad-sync", choices=["auto", "fused", "nccl"], default="auto")
     p.add_argument("--shard-optimizer", action="store_true")
     p.add_argument("--shard-params", choices=["off", "stream", "resident"], default="off")
-    return p.parse_args(argv)
+    p.add_argument("--bf16-residuals", action="store_true", help="BF16 residual stream (FP32 by default)")
+    p.add_argument("--loss-chunk-size", type=int, default=1024, help="rows per block of the host (CPU) loss head")
+    p.add_argument("--ddp-bucket-cap-mb", type=float, default=0.0,
+                   help="largest gradient range reduced by one launch, in MiB of FP32 gradients; 0 = one bucket per core")
+    from ..train.flags import REFERENCE_EXECUTION_FLAGS, Flag
+    compat = p.add_argument_group("reference execution experiments", "accepted and recorded; no effect on what runs here")
+    one_path = "no tracing compiler: every core is one autograd node over hand-written kernels"
+    for flag in (*[f for f in REFERENCE_EXECUTION_FLAGS if f.name not in ("--compile", "--compile-core")],
+                 Flag("--compile-cores", "toggle", False, native=one_path),
+                 Flag("--fused-rms-norm", "toggle", False, native="RMSNorm is one kernel with the depth modulation folded in"),
+                 Flag("--blas-backend", str, None, choices=("default", "cublas", "cublaslt"),
+                      native="GEMMs are this library's tcgen05 kernels, not a BLAS call"),
+                 Flag("--cudagraph-diagnostics", "switch", native="training launches no CUDA graph; decode counts its own "
+                                                                  "(serve/graph_stats.py)")):
+        flag.add_to(compat)
+        INERT.append(flag)
+    a = p.parse_args(argv)
+    if a.loss_chunk_size < 1 or a.ddp_bucket_cap_mb < 0 or a.overlap_memory_budget < 0:
+        p.error("--loss-chunk-size must be positive; --ddp-bucket-cap-mb and --overlap-memory-budget must not be negative")
+    return a
+
+
+INERT: list = []            # the reference-execution flags of the last `arguments` call
+
+
+def inert_settings(a) -> dict:
+    """Reference-execution flags that were given a non-default value, for the record."""
+    return {flag.name: str(getattr(a, flag.dest)) if isinstance(getattr(a, flag.dest), Path) else getattr(a, flag.dest)
+            for flag in INERT if getattr(a, flag.dest) != (False if flag.kind == "switch" else flag.default)}
 
 
 def file_identity(path: Path | None):
@@ -222,6 +252,7 @@ def benchmark(a) -> dict:
     else:
         cfg = warpstate_2b() if a.model == "2b" else warpstate_smoke()
     cfg.gradient_checkpointing = a.activation_checkpointing
+    cap = int(a.ddp_bucket_cap_mb * 2 ** 20)
     if a.profile:
         # kernels launched as programmatic dependents wait for their predecessor inside the kernel, which a
         # profiler books as their own time: the profiled run uses plain launches
@@ -230,15 +261,17 @@ def benchmark(a) -> dict:
         model = WarpStateLM(cfg)
     if checkpoint is not None:
         model.load_state_dict(checkpoint["model"])
+    model.loss_chunk_size = a.loss_chunk_size
+    model.bf16_residuals = bool(a.bf16_residuals)
     model.train()
     sync = None
     if world > 1:
         from ..parallel.grad_sync import make_grad_sync
         sync = make_grad_sync(device, world, rank, None,
-                              kind={"auto": "auto", "fused": "fused", "nccl": "collective"}[a.grad_sync])
+                              kind={"auto": "auto", "fused": "fused", "nccl": "collective"}[a.grad_sync], bucket_cap_bytes=cap)
     trainer = Trainer(model, device=device, rank=rank, world_size=world, grad_sync=sync,
                       shard_optimizer=a.shard_optimizer,
-                      shard_params=None if a.shard_params == "off" else a.shard_params)
+                      shard_params=None if a.shard_params == "off" else a.shard_params, bucket_cap_bytes=cap)
     if checkpoint is not None and a.optimizer_state == "resume":
         trainer.optimizer.load_state_dict(checkpoint["optimizer"])
     del checkpoint
@@ -309,7 +342,9 @@ def benchmark(a) -> dict:
                "model": {"parameters": model.num_parameters(), "config": vars(cfg).copy()},
                "geometry": {"micro_batch": a.micro_batch, "seq_len": a.seq_len, "global_tokens_per_update": tokens,
                             "grad_accum": tokens // per_update},
-               "precision": {"compute": "bf16" if device.type == "cuda" else "fp32", "master": "fp32", "grads": "fp32"},
+               "precision": {"compute": "bf16" if device.type == "cuda" else "fp32", "master": "fp32", "grads": "fp32",
+                             "residual_stream": "bf16" if a.bf16_residuals else "fp32"},
+               "bucket_cap_mb": a.ddp_bucket_cap_mb, "reference_execution_flags": inert_settings(a),
                "grad_sync": getattr(sync, "kind", "none"), "optimizer": "sharded" if a.shard_optimizer and world > 1 else "replicated",
                "checkpoint": file_identity(a.checkpoint), "data": file_identity(a.data) or "synthetic",
                "optimizer_state": a.optimizer_state if a.checkpoint else "fresh",

@@ -44,7 +44,12 @@ def paired_timing_metrics(trials: list, minimum_gain: float) -> dict:
                                                   for c, t in zip(controls, trials))}
 
 
-def cases(rows: int, operations) -> list:
+def cases(rows: int, operations, kind: str = "mm") -> list:
+    """The problems of one screening: every family and operation, or (``kind="swiglu"``) the forward up/gate projection
+    with the SwiGLU epilogue, which no other family has."""
+    if kind == "swiglu":
+        k, n = FAMILIES["up_gate"]
+        return [{"family": "up_gate", "operation": "fwd", "kind": "swiglu", "tokens": rows, "in_features": k, "out_features": n}]
     out = []
     for name, (k, n) in FAMILIES.items():
         for op in operations:
@@ -52,7 +57,24 @@ def cases(rows: int, operations) -> list:
     return out
 
 
+def candidates_of(algorithms, tiles) -> list:
+    """The candidates of a screening: the default sweep restricted to ``algorithms`` (kernels), or exactly the
+    ``KERNEL,SMS`` pairs given with ``--tile`` (tile shapes are fixed when the kernels are built; what can be chosen at
+    run time is the kernel and how many SMs it may occupy, 0 = all)."""
+    if tiles:
+        chosen = []
+        for text in tiles:
+            kernel, _, sms = text.partition(",")
+            if kernel not in ("pair", "single") or not sms.strip().isdigit() or int(sms) > 148:
+                raise ValueError(f"--tile {text!r}: expected KERNEL,SMS with KERNEL pair or single and SMS from 0 (all) to 148")
+            chosen.append({"kernel": kernel, "sm_limit": int(sms)})
+        return chosen
+    return [c for c in CANDIDATES if algorithms is None or c["kernel"] in algorithms]
+
+
 def policy_key(case: dict) -> str:
+    if case.get("kind") == "swiglu":           # the launch `ops.gemm.linear_swiglu` makes: one output tile per (up, gate) pair
+        return f"fwd:{case['tokens']}x{case['out_features'] // 2}x{case['in_features']}"
     return f"{case['operation']}:{case['tokens']}x{case['out_features']}x{case['in_features']}"
 
 
@@ -72,7 +94,13 @@ def select_policy(results: list) -> dict:
 
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    p.add_argument("--kind", choices=["mm", "swiglu"], default="mm",
+                   help="plain projections, or the forward up/gate projection with the SwiGLU epilogue")
     p.add_argument("--operations", nargs="+", choices=["fwd", "dx", "dw"], default=["fwd", "dx", "dw"])
+    p.add_argument("--algorithms", nargs="+", choices=["pair", "single"],
+                   help="kernels of the default sweep (CTA pair, single CTA); both when omitted")
+    p.add_argument("--tile", action="append", metavar="KERNEL,SMS",
+                   help="repeat to screen exactly these candidates instead of the default sweep, e.g. pair,116")
     p.add_argument("--rows", type=int, default=16384)
     p.add_argument("--repeats", type=int, default=10)
     p.add_argument("--trials", type=int, default=3)
@@ -86,7 +114,11 @@ def main(argv=None) -> int:
     p.add_argument("--list-cases", action="store_true")
     p.add_argument("--output-dir", type=Path, required=True)
     a = p.parse_args(argv)
-    selected = cases(a.rows, a.operations)
+    selected = cases(a.rows, a.operations, a.kind)
+    try:
+        candidates = candidates_of(a.algorithms, a.tile)
+    except ValueError as problem:
+        p.error(str(problem))
     if a.list_cases:
         print(json.dumps(selected, indent=1))
         return 0
@@ -130,16 +162,26 @@ def main(argv=None) -> int:
         w = (torch.randn(n, k, device=device, generator=gen) * 0.02).bfloat16()
         dy = (torch.randn(t, n, device=device, generator=gen) * a.input_scale).bfloat16()
         grad = torch.zeros(n, k, device=device)
-        if case["operation"] == "fwd":
+        if case.get("kind") == "swiglu":
+            def control():
+                up, gate = (x @ w.T).chunk(2, dim=-1)
+                return torch.nn.functional.silu(gate) * up
+            ours, flops = (lambda: G.linear_swiglu(x, w)[1]), 2 * t * n * k
+        elif case["operation"] == "fwd":
             control, ours, flops = (lambda: x @ w.T), (lambda: G.linear(x, w)), 2 * t * n * k
         elif case["operation"] == "dx":
             control, ours, flops = (lambda: dy @ w), (lambda: G.grad_input(dy, w)), 2 * t * n * k
         else:
             control = lambda: grad.add_((dy.T @ x).float())  # noqa: E731  (BF16 product, cast, FP32 add)
             ours, flops = (lambda: G.grad_weight_accumulate(dy, x, grad, accumulate=False)), 2 * t * n * k
-        reference = (x.float() @ w.float().T if case["operation"] == "fwd" else dy.float() @ w.float()
-                     if case["operation"] == "dx" else dy.float().T @ x.float())
-        for candidate in CANDIDATES:
+        if case.get("kind") == "swiglu":
+            up, gate = (x.float() @ w.float().T).bfloat16().float().chunk(2, dim=-1)
+            reference = torch.nn.functional.silu(gate) * up
+            del up, gate
+        else:
+            reference = (x.float() @ w.float().T if case["operation"] == "fwd" else dy.float() @ w.float()
+                         if case["operation"] == "dx" else dy.float().T @ x.float())
+        for candidate in candidates:
             row = {"case": case, "candidate": candidate, "status": "running"}
             lib.ws_gemm_set_pair_mode(1 if candidate["kernel"] == "pair" else 0)
             lib.ws_gemm_set_sm_limit(candidate["sm_limit"])
