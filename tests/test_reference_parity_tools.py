@@ -360,3 +360,92 @@ def test_both_launchers_give_the_job_the_same_environment(launchers, tmp_path, m
             except ValueError:
                 verdicts.append("refused")
         assert verdicts[0] == verdicts[1], place
+
+
+def reference_benchmark_directory(root, world=2, warmup=1, measured=3, seed=0, scale=1.0):
+    """A benchmark directory in the reference's layout (``summary.json`` with embedded ranks)."""
+    rng = random.Random(seed)
+    args = {"global_tokens_per_update": 1024 * world, "seq_len": 128, "micro_batch": 2, "warmup_updates": warmup,
+            "measured_updates": measured, "seed": 1337, "optimizer_state": "fresh", "bf16_residuals": False, "profile": False,
+            "ddp_bucket_cap_mb": 128}
+    identity = {"path": "/workspace/WarpState/ckpt.pt", "size": 10, "inode": 3, "mtime_ns": 5}
+    config = {"checkpoint": identity, "checkpoint_step": 10, "checkpoint_tokens": 4096, "data": dict(identity, path="/workspace/WarpState/train.bin"),
+              "world_size": world, "grad_accum": 4, "parameters": 12345, "parameter_dtype": "float32", "autocast_dtype": "bfloat16",
+              "optimizer": "AdamW(fused=True)", "torch": "2.x", "cuda": "12", "gpu": "GPU", "update_timing_includes_gradient_zeroing": True,
+              "args": args, "source_sha256": {"run_40b.py": "0" * 64}}
+    losses = [5.0 - 0.1 * i for i in range(warmup + measured)]
+    ranks = []
+    for rank in range(world):
+        updates = []
+        for index in range(warmup + measured):
+            seconds = scale * rng.uniform(0.9, 1.1)
+            updates.append({"event": "update", "update": index + 1, "phase": "warmup" if index < warmup else "measured", "rank": rank,
+                            "global_tokens": args["global_tokens_per_update"], "profiled": False, "seconds": seconds,
+                            "tokens_per_second": args["global_tokens_per_update"] / seconds, "loss": losses[index] + 0.01 * rank,
+                            "grad_norm": 1.0 + 0.1 * index, "peak_allocated_gib": 1.5 + rank, "peak_reserved_gib": 2.0 + rank})
+        ranks.append({"configuration": dict(config, rank=rank), "updates": updates, "checkpoint_path_identity_after": identity})
+    root.mkdir(parents=True)
+    summary = {"configuration": dict(config, rank=0), "updates": ranks[0]["updates"], "ranks": ranks,
+               "checkpoint_path_identity_after": identity}
+    (root / "summary.json").write_text(json.dumps(summary))
+    return summary
+
+
+def test_a_reference_benchmark_directory_is_read_and_paired_with_ours(ref, tmp_path, monkeypatch):
+    """The comparator here reads the reference benchmark's own record layout (the fixture is first shown to the
+    reference's comparator, which accepts it), reports the same timing figures for it as the reference's comparator does,
+    and pairs it with a run recorded in this framework's layout."""
+    from warpstate_ai_b200.bench import compare_runs as CR
+    theirs = ref["ops.compare_communication_benchmarks"]
+    monkeypatch.setattr(theirs, "WORKSPACE", tmp_path.resolve())
+    control = reference_benchmark_directory(tmp_path / "control", seed=1)
+    reference_benchmark_directory(tmp_path / "candidate", seed=2, scale=0.8)
+    expected = theirs.compare_summaries(theirs.load_run(tmp_path / "control")["summary"], theirs.load_run(tmp_path / "candidate")["summary"])
+    mine = CR.compare(CR.load_run(tmp_path / "control"), CR.load_run(tmp_path / "candidate"))
+    for key in ("control_timing", "candidate_timing", "throughput_ratio", "maximum_absolute_loss_difference",
+                "maximum_relative_grad_norm_difference"):
+        assert mine[key] == expected[key], key
+    for a, b in zip(mine["paired_updates"], expected["paired_updates"]):
+        assert {k: a[k] for k in ("update", "control_seconds", "candidate_seconds", "throughput_ratio")} == \
+               {k: b[k] for k in ("update", "control_seconds", "candidate_seconds", "throughput_ratio")}
+        for x, y in zip(a["ranks"], b["ranks"]):
+            assert {k: x[k] for k in x} == {k: y[k] for k in x}
+    assert [row["control"]["peak_allocated_bytes"] for row in mine["rank_peak_memory"]] == [int(1.5 * 2 ** 30), int(2.5 * 2 ** 30)]
+    # a run in this framework's layout with the same geometry, checkpoint and data
+    args = control["configuration"]["args"]
+    ours = tmp_path / "ours"
+    ours.mkdir()
+    rows_by_rank = CR.load_run(tmp_path / "control")["ranks"]
+    native = {"format": "warpstate-training-benchmark-v1", "world_size": 2, "model": {"parameters": 12345, "config": {"d_model": 8}},
+              "geometry": {"micro_batch": 2, "seq_len": 128, "global_tokens_per_update": args["global_tokens_per_update"], "grad_accum": 4},
+              "precision": {"compute": "bf16", "master": "fp32", "grads": "fp32", "residual_stream": "fp32"}, "grad_sync": "fused",
+              "optimizer": "replicated", "checkpoint": {"path": "/workspace/WarpState/ckpt.pt", "bytes": 10, "mtime_ns": 5},
+              "data": {"path": "/workspace/WarpState/train.bin", "bytes": 10, "mtime_ns": 5}, "optimizer_state": "fresh",
+              "warmup_updates": 1, "measured_updates": 3, "profile": None}
+    (ours / "summary.json").write_text(json.dumps(native))
+    for rank, rows in rows_by_rank.items():
+        faster = [dict(row, seconds=row["seconds"] / 2, slowest_rank_seconds=row["seconds"] / 2, tokens_per_second=row["tokens"] / (row["seconds"] / 2))
+                  for row in rows]
+        (ours / f"rank-{rank}.jsonl").write_text("\n".join(json.dumps(row) for row in faster) + "\n")
+    mixed = CR.compare(CR.load_run(tmp_path / "control"), CR.load_run(ours))
+    assert mixed["throughput_ratio"] == pytest.approx(2.0) and mixed["maximum_absolute_loss_difference"] == 0.0
+    assert {"grad_sync", "optimizer"} <= set(mixed["recorded_differences"])
+    (ours / "summary.json").write_text(json.dumps(dict(native, model={"parameters": 999, "config": {}})))
+    with pytest.raises(ValueError, match="parameter count"):
+        CR.compare(CR.load_run(tmp_path / "control"), CR.load_run(ours))
+    # what the reference's comparator refuses in its own layout is refused here too
+    for name, damage in (("profiled", lambda s: s["ranks"][1]["updates"][2].update(profiled=True)),
+                         ("gap", lambda s: s["ranks"][0]["updates"][1].update(update=7)),
+                         ("throughput", lambda s: s["ranks"][1]["updates"][0].update(tokens_per_second=1.0)),
+                         ("short", lambda s: s["ranks"][1]["updates"].pop()),
+                         ("nan", lambda s: s["ranks"][0]["updates"][0].update(loss=float("nan"))),
+                         ("same-rank", lambda s: s["ranks"][1]["configuration"].update(rank=0))):
+        summary = json.loads((tmp_path / "control/summary.json").read_text())
+        damage(summary)
+        summary["updates"] = summary["ranks"][0]["updates"]
+        bad = tmp_path / f"bad-{name}"
+        bad.mkdir()
+        (bad / "summary.json").write_text(json.dumps(summary))
+        for load in (theirs.load_run, CR.load_run):
+            with pytest.raises(ValueError):
+                load(bad)

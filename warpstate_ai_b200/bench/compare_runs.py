@@ -11,7 +11,10 @@ statistics (mean, median, population std, first-five vs last-five drift) and pea
     python -m warpstate_ai_b200.bench.compare_runs --control dir_a --candidate dir_b --output cmp.json
 
 Same checks and report as the reference's ops/compare_communication_benchmarks.py:50-234, over
-this framework's benchmark records (rank-<r>.jsonl + summary.json).
+this framework's benchmark records (rank-<r>.jsonl + summary.json).  A directory written by the
+reference's own benchmark (``summary.json`` with a ``configuration`` and embedded ranks) is read as
+well, so a run of the reference and a run of this framework from the same checkpoint and data can be
+paired; between the two layouts the model is matched by its parameter count.
 """
 from __future__ import annotations
 
@@ -50,6 +53,8 @@ def load_run(directory: Path) -> dict:
         return data
 
     summary = json.loads(read(directory / "summary.json"))
+    if "format" not in summary and "configuration" in summary:
+        return _load_reference_run(directory, summary, read, inputs)
     if summary.get("format") != "warpstate-training-benchmark-v1":
         raise ValueError(f"{directory}: not a training-benchmark summary")
     world = summary["world_size"]
@@ -80,6 +85,70 @@ def load_run(directory: Path) -> dict:
     return {"directory": str(directory), "summary": summary, "ranks": ranks, "input_files": inputs}
 
 
+def _load_reference_run(directory: Path, summary: dict, read, inputs: list) -> dict:
+    """A directory written by the reference's benchmark (ops/benchmark_training.py:455-590: ``configuration`` with the
+    parsed ``args``, updates numbered from one with a ``phase``, peaks in GiB), brought to this comparator's terms, so
+    that a run of the reference and a run of this framework from the same checkpoint and data can be paired."""
+    config = summary["configuration"]
+    args = config["args"]
+    world, warmup, measured = config["world_size"], args["warmup_updates"], args["measured_updates"]
+    tokens = args["global_tokens_per_update"]
+    if tokens != world * config["grad_accum"] * args["micro_batch"] * args["seq_len"]:
+        raise ValueError("global batch does not match world size, accumulation, micro-batch and sequence length")
+    if args.get("profile") or config.get("checkpoint_writes"):
+        raise ValueError("comparisons need unprofiled runs without checkpoint writes")
+    sources = summary.get("ranks") or ([summary] if world == 1 else None)
+    if sources is None:                      # older summaries: the per-rank files are the record
+        sources = []
+        for rank in range(world):
+            rows = [json.loads(line) for line in read(directory / f"rank-{rank}.jsonl").splitlines() if line.strip()]
+            sources.append({"configuration": {"rank": rank}, "updates": [row for row in rows if row.get("event") == "update"]})
+    ranks = {}
+    for source in sources:
+        rank = source["configuration"].get("rank", 0)
+        if type(rank) is not int or not 0 <= rank < world or rank in ranks:
+            raise ValueError("rank records must be complete and distinct")
+        if len(source["updates"]) != warmup + measured:
+            raise ValueError(f"rank {rank}: {len(source['updates'])} records, expected {warmup + measured}")
+        rows = []
+        for index, update in enumerate(source["updates"]):
+            if update.get("update") != index + 1 or update.get("phase") != ("warmup" if index < warmup else "measured"):
+                raise ValueError("update records must describe one continuous benchmark")
+            if update.get("profiled") is not False:
+                raise ValueError("profiled updates cannot be compared")
+            if update.get("global_tokens") != tokens:
+                raise ValueError("update token count differs from the geometry")
+            seconds = finite(update["seconds"], "update seconds", positive=True)
+            if not math.isclose(update.get("tokens_per_second", 0), tokens / seconds, rel_tol=1e-9):
+                raise ValueError("recorded throughput disagrees with tokens and elapsed time")
+            rows.append({"update": index, "measured": index >= warmup, "seconds": seconds, "tokens": tokens,
+                         "loss": finite(update["loss"], "loss"), "grad_norm": finite(update["grad_norm"], "grad_norm"),
+                         "tokens_per_second": update["tokens_per_second"], "slowest_rank_seconds": seconds,
+                         "peak_allocated_bytes": int(finite(update["peak_allocated_gib"], "peak_allocated_gib") * 2 ** 30),
+                         "peak_reserved_bytes": int(finite(update["peak_reserved_gib"], "peak_reserved_gib") * 2 ** 30)})
+        ranks[rank] = rows
+    if len(ranks) != world:
+        raise ValueError("rank records must be complete and distinct")
+
+    def identity(entry):
+        return None if entry is None else {"path": entry["path"], "bytes": entry["size"], "mtime_ns": entry["mtime_ns"]}
+
+    dtype = {"float32": "fp32", "bfloat16": "bf16", "float16": "fp16"}
+    view = {"format": "warpstate-training-benchmark-v1", "implementation": "reference", "world_size": world,
+            "device": config.get("gpu"), "model": {"parameters": config["parameters"], "config": None},
+            "geometry": {"micro_batch": args["micro_batch"], "seq_len": args["seq_len"], "global_tokens_per_update": tokens,
+                         "grad_accum": config["grad_accum"]},
+            "precision": {"compute": dtype.get(config["autocast_dtype"], config["autocast_dtype"]),
+                          "master": dtype.get(config["parameter_dtype"], config["parameter_dtype"]),
+                          "grads": dtype.get(config["parameter_dtype"], config["parameter_dtype"]),
+                          "residual_stream": "bf16" if args.get("bf16_residuals") else "fp32"},
+            "grad_sync": "ddp", "optimizer": config.get("optimizer"), "bucket_cap_mb": args.get("ddp_bucket_cap_mb"),
+            "checkpoint": identity(config.get("checkpoint")), "data": identity(config.get("data")),
+            "optimizer_state": args["optimizer_state"], "warmup_updates": warmup, "measured_updates": measured,
+            "source_sha256": config.get("source_sha256"), "torch": config.get("torch"), "profile": None}
+    return {"directory": str(directory), "summary": view, "ranks": ranks, "input_files": inputs}
+
+
 def differences(left: dict, right: dict) -> dict:
     """Keys whose values differ, or that only one side recorded (an absent key is not the same as a recorded ``None``)."""
     table = {}
@@ -104,7 +173,10 @@ def compare(control: dict, candidate: dict) -> dict:
     for key in MUST_MATCH:
         if a.get(key) != b.get(key):
             raise ValueError(f"incompatible runs: {key} differs ({a.get(key)} vs {b.get(key)})")
-    if a["model"]["config"] != b["model"]["config"]:
+    if "reference" in (a.get("implementation"), b.get("implementation")):      # its record has no model configuration
+        if a["model"]["parameters"] != b["model"]["parameters"]:
+            raise ValueError("incompatible runs: parameter count differs")
+    elif a["model"]["config"] != b["model"]["config"]:
         raise ValueError("incompatible runs: model configuration differs")
     for key in IDENTITIES:
         if a.get(key) != b.get(key):
