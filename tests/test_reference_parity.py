@@ -535,3 +535,37 @@ def test_interactive_conversations_ask_the_model_the_same_things(monkeypatch, ca
         assert shown.count("Cancelled.") == (1 if side.endswith("eof") else 2)
     assert transcripts[0] == transcripts[1] and len(transcripts[0]) == 7
     assert transcripts[2] == transcripts[3] and len(transcripts[2]) == 1
+
+
+def test_a_reference_run_resumes_here_as_an_execution_change(ref, monkeypatch):
+    """The signature the reference stores for a command line, against the one this framework computes for the same
+    command line: same objective, same schedule, same data; what differs is execution (kernels, gradient path, bucket
+    size), so its checkpoint resumes here with ``--reconfigure`` and is refused without -- and a changed objective is
+    refused either way."""
+    import contextlib
+    import io
+    from warpstate_ai_b200.train import pretrain as T
+    from warpstate_ai_b200.train import signature as S
+    for name in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        monkeypatch.delenv(name, raising=False)
+    manifest = {"signature": {"recipe": 1, "train_tokens": 10 ** 9}, "sha256": {"train.bin": "a" * 64}, "complete": True}
+    for argv in ([], ["--micro-batch", "4", "--grad-accum", "8"], ["--bf16-residuals", "--no-activation-checkpointing", "--lr", "2e-4", "--min-lr", "2e-5"],
+                 ["--compile-core", "--loss-mode", "full", "--gradient-mode", "compiled-autograd", "--ddp-bucket-cap-mb", "64"]):
+        monkeypatch.setattr(sys, "argv", ["run_40b.py", *argv])
+        with contextlib.redirect_stderr(io.StringIO()):
+            theirs, mine = ref["run_40b"].arguments(), T.arguments(list(argv))
+        stored, fresh = ref["run_40b"].train_signature(theirs, manifest), S.train_signature(mine, manifest)
+        assert set(stored["settings"]) <= set(fresh["settings"])
+        differing = {k for k in stored["settings"] if stored["settings"][k] != fresh["settings"][k]}
+        assert differing <= {"ddp_bucket_cap_mb"} and differing <= S.EXECUTION_KEYS
+        assert {k: fresh["settings"][k] for k in S.OBJECTIVE_KEYS} == {k: stored["settings"][k] for k in S.OBJECTIVE_KEYS}
+        assert S.check_resume_signature(stored, fresh, reconfigure=True) is True
+        with pytest.raises(ValueError, match="--reconfigure"):
+            S.check_resume_signature(stored, fresh, reconfigure=False)
+        for key, value in (("lr", 9e-4), ("seed", 3), ("train_tokens", 5), ("seq_len", 4096)):
+            changed = {"settings": dict(fresh["settings"], **{key: value}), "data": fresh["data"]}
+            with pytest.raises(ValueError, match="objective and global tokens per update must stay fixed"):
+                S.check_resume_signature(stored, changed, reconfigure=True)
+        other_corpus = {"settings": fresh["settings"], "data": dict(manifest, sha256={"train.bin": "b" * 64})}
+        with pytest.raises(ValueError):
+            S.check_resume_signature(stored, other_corpus, reconfigure=True)
