@@ -602,3 +602,76 @@ def test_locks_of_either_implementation_exclude_the_other(ref, tmp_path, monkeyp
     for implementation in (theirs.base_pipeline_lock, S.base_pipeline_lock):
         with implementation({}):                                 # no base job named: nothing to hold
             pass
+
+
+# ------------------------------------------------------------------------------------------- guardians: is the data ready?
+def test_both_guardians_judge_prepared_data_alike(ref, tmp_path):
+    """Data prepared here, shown to the readiness checks of the reference's two guardians and of this framework's: ready,
+    verified, and -- after each kind of damage -- the same answer (not yet ready) or the same refusal."""
+    from warpstate_ai_b200.data.prepare_posttrain import prepare
+    from warpstate_ai_b200.orchestration import handoff as H
+    from warpstate_ai_b200.utils.io import digest
+    with reference_import_path():
+        their = {"sft": importlib.import_module("ops.posttrain_handoff").data_readiness,
+                 "dpo": importlib.import_module("ops.dpo_handoff").data_readiness}
+    sft_rows = [{"messages": [{"role": "user", "content": f"Q{i}"}, {"role": "assistant", "content": f"A{i}"}]} for i in range(9)]
+    dpo_rows = [{"prompt": [{"role": "user", "content": f"Q{i}"}], "chosen": [{"role": "assistant", "content": "yes"}],
+                 "rejected": [{"role": "assistant", "content": "no, not at all"}]} for i in range(9)]
+
+    def fresh(name):
+        folder = tmp_path / name
+        prepare(folder, TOK, 64, sft_rows=sft_rows, dpo_rows=dpo_rows, val_modulus=4)
+        return folder
+
+    def plans(folder, **training):
+        settings = dict({"sequence_length": 64}, **training)
+        tokenizer = digest(TOK)
+        return {"sft": {"base": {"tokenizer_sha256": tokenizer}, "training": settings, "handoff": {}},
+                "dpo": {"sft": {"tokenizer_sha256": tokenizer}, "training": settings,
+                        "handoff": {"data_manifest_sha256": digest(folder / "manifest.json") if (folder / "manifest.json").is_file() else "-"}}}
+
+    def verdicts(folder, plan_of, verify):
+        out = {}
+        for stage in ("sft", "dpo"):
+            for side, check in (("theirs", lambda: their[stage](folder, plan_of[stage], verify=verify)),
+                                ("mine", lambda: H.data_readiness(folder, plan_of[stage], H.STAGES[stage], verify=verify))):
+                try:
+                    answer = check()
+                    out[stage, side] = bool(answer[0] if isinstance(answer, tuple) else answer)
+                except ValueError:
+                    out[stage, side] = "refused"
+        return out
+
+    good = fresh("good")
+    for verify in (False, True):
+        assert set(verdicts(good, plans(good), verify).values()) == {True}
+    assert set(verdicts(good, plans(good, sequence_length=128), False).values()) == {"refused"}      # another context length
+    other_tokenizer = plans(good)
+    other_tokenizer["sft"]["base"]["tokenizer_sha256"] = other_tokenizer["dpo"]["sft"]["tokenizer_sha256"] = "0" * 64
+    assert set(verdicts(good, other_tokenizer, False).values()) == {"refused"}
+    missing = tmp_path / "nothing-yet"
+    missing.mkdir()
+    assert set(verdicts(missing, plans(missing), False).values()) == {False}
+    partial = fresh("partial")
+    manifest = json.loads((partial / "manifest.json").read_text())
+    (partial / "manifest.json").write_text(json.dumps(dict(manifest, complete=False)))
+    assert set(verdicts(partial, plans(partial), False).values()) == {False}
+    for name in ("sft_val.jsonl", "dpo_train.jsonl"):
+        stage = name[:3]
+        gone = fresh(f"gone-{stage}")
+        plan_of = plans(gone)
+        (gone / name).unlink()
+        found = verdicts(gone, plan_of, False)
+        assert found[stage, "theirs"] == found[stage, "mine"] == "refused"
+        edited = fresh(f"edited-{stage}")
+        plan_of = plans(edited)
+        with (edited / name).open("a") as stream:
+            stream.write("\n")
+        assert verdicts(edited, plan_of, False)[stage, "mine"] is True and verdicts(edited, plan_of, False)[stage, "theirs"] is True
+        found = verdicts(edited, plan_of, True)                                                     # only hashing sees it
+        assert found[stage, "theirs"] == found[stage, "mine"] == "refused"
+    repinned = fresh("repinned")
+    plan_of = plans(repinned)
+    (repinned / "manifest.json").write_text((repinned / "manifest.json").read_text() + "\n")         # the DPO plan pins the manifest
+    found = verdicts(repinned, plan_of, False)
+    assert found["dpo", "theirs"] == found["dpo", "mine"] == "refused" and found["sft", "theirs"] is found["sft", "mine"] is True
