@@ -675,3 +675,63 @@ def test_both_guardians_judge_prepared_data_alike(ref, tmp_path):
     (repinned / "manifest.json").write_text((repinned / "manifest.json").read_text() + "\n")         # the DPO plan pins the manifest
     found = verdicts(repinned, plan_of, False)
     assert found["dpo", "theirs"] == found["dpo", "mine"] == "refused" and found["sft", "theirs"] is found["sft", "mine"] is True
+
+
+# ------------------------------------------------------------------------------------------- guardians: directory layout rules
+def test_guardian_plans_are_accepted_and_refused_alike(tmp_path, monkeypatch):
+    """Directory layouts of a hand-off plan through both guardians' plan loaders.  Both keep the stage's outputs apart from the
+    base run, the archives, the parent run and the data, and check the SFT parent named by a DPO plan.  Two conventions of the
+    reference are not imposed here and are listed as such: DPO output below ``<base>/posttrain`` with its archive below
+    ``<base>/archives``, and a polling interval of at least a second."""
+    import sys
+    from warpstate_ai_b200.orchestration import handoff as H
+    if not (REF / "ops" / "dpo_handoff.py").exists():
+        pytest.skip("reference not installed under baseline/_ref")
+    root = tmp_path.resolve()
+    monkeypatch.setenv("WARPSTATE_WORKSPACE", str(root))
+    with reference_import_path():
+        loaders = {"sft": importlib.import_module("ops.posttrain_handoff"), "dpo": importlib.import_module("ops.dpo_handoff")}
+        modules = [*loaders.values(), importlib.import_module("ops.launch_training"), sys.modules["launch_training"]]
+    for module in modules:
+        monkeypatch.setattr(module, "WORKSPACE", root)
+    parent = {"step": 7, "tokens_seen": 700, "tokenizer_sha256": "t"}
+    documents = {"sft": {"format": "warpstate-posttrain-plan-v1", "stage": "sft", "after_completion": "pause_for_evaluation", "base": parent},
+                 "dpo": {"format": "warpstate-dpo-plan-v1", "stage": "dpo", "after_completion": "pause_for_evaluation",
+                         "sft": {"base_step": 7, "base_tokens_seen": 700, "tokenizer_sha256": "t", "step": 4, "tokens_seen": 400}}}
+    (root / "sft-plan.json").write_text(json.dumps(documents["sft"]))
+    common = {"base_work_dir": "work", "supervisor_socket": "run/s.sock", "data_dir": "work/posttrain/data", "tokenizer": "tokenizer.model",
+              "processes": 2, "poll_seconds": 5}
+    layouts = {"sft": dict(common, archive_dir="work/archives/a", work_dir="work/posttrain/sft"),
+               "dpo": dict(common, sft_work_dir="work/posttrain/sft", sft_plan="sft-plan.json", archive_dir="work/archives/sft-final",
+                           work_dir="work/posttrain/dpo")}
+    cases = {"sft": [{}, {"work_dir": "work"}, {"work_dir": "work/run/x"}, {"work_dir": "work/archives/x"}, {"work_dir": "work/archives/a/x"},
+                     {"archive_dir": "work/posttrain/sft/arch"}, {"data_dir": "work/posttrain/sft/data"}, {"work_dir": "work/posttrain/data/run"},
+                     {"work_dir": "elsewhere/sft"}, {"work_dir": "../outside"}, {"poll_seconds": 61}, {"poll_seconds": 0}],
+             "dpo": [{}, {"work_dir": "work"}, {"work_dir": "work/posttrain"}, {"work_dir": "work/posttrain/sft/dpo"}, {"work_dir": "work/posttrain/data/dpo"},
+                     {"work_dir": "work/run/dpo"}, {"work_dir": "work/archives/dpo"}, {"archive_dir": "work/posttrain/dpo/archive"},
+                     {"sft_work_dir": "work/posttrain/dpo/sft"}, {"data_dir": "work/posttrain/dpo/data"}, {"poll_seconds": 0},
+                     {"work_dir": "work/posttrain/dpo/../sft"}, {"sft": {"base_step": 8}}, {"sft": {"base_tokens_seen": 1}}, {"sft": {"tokenizer_sha256": "u"}}]}
+    conventions = {"sft": [{"poll_seconds": 0.5}], "dpo": [{"work_dir": "elsewhere/dpo"}, {"archive_dir": "work/archives"}, {"archive_dir": "elsewhere/archive"}]}
+
+    def verdicts(stage, change):
+        document = dict(documents[stage], handoff=dict(layouts[stage], **{k: v for k, v in change.items() if k != "sft"}))
+        if "sft" in change:
+            document["sft"] = dict(document["sft"], **change["sft"])
+        path = root / "plan.json"
+        path.write_text(json.dumps(document))
+        found = []
+        for load in (lambda: H.load_plan(path, H.STAGES[stage]), lambda: loaders[stage].load_plan(path)):
+            try:
+                found.append({key: str(value) for key, value in load()[1].items() if key != "sft_plan"})
+            except ValueError:
+                found.append("refused")
+        return found
+
+    for stage in ("sft", "dpo"):
+        for change in cases[stage]:
+            mine, theirs = verdicts(stage, change)
+            assert mine == theirs, (stage, change)
+        assert verdicts(stage, {})[0] != "refused"
+        for change in conventions[stage]:
+            mine, theirs = verdicts(stage, change)
+            assert mine != "refused" and theirs == "refused", (stage, change)

@@ -235,8 +235,15 @@ class DpoStage(Stage):
 
     def check_paths(self, plan, paths):
         work = paths["work_dir"]
-        protected = [paths["base_work_dir"] / "run", paths["sft_work_dir"], paths["archive_dir"], paths["data_dir"]]
+        base = paths["base_work_dir"]
+        protected = [base / "run", base / "archives", paths["sft_work_dir"], paths["archive_dir"], paths["data_dir"]]
         enforce(Rule(f"DPO outputs overlap protected inputs: {p}", lambda p=p: not overlaps(work, p)) for p in protected)
+        named = plan["handoff"].get("sft_plan")
+        if named is not None:                # the SFT plan on file must describe the parent that the DPO plan pins
+            original = read_json(workspace_path(workspace_root() / named))["base"]
+            enforce([Rule("SFT parent identity differs from the DPO plan",
+                          lambda: (original["step"], original["tokens_seen"], original["tokenizer_sha256"])
+                          == (plan["sft"]["base_step"], plan["sft"]["base_tokens_seen"], plan["sft"]["tokenizer_sha256"]))])
 
     def parent_rules(self, checkpoint, plan, tokenizer_hash):
         want = plan["sft"]
